@@ -1,0 +1,187 @@
+"""Numerics of every sm_100a kernel against the plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+from xllm_b200 import ops
+from xllm_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _close(a, b, atol, rtol=2e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    assert bool((err <= tol).all()), f"max err {err.max().item():.4g} (tol {atol})"
+
+
+@pytest.mark.parametrize("tokens,hidden", [(1, 4096), (7, 4096), (300, 5120), (33, 1024), (5, 7168)])
+def test_rmsnorm(tokens, hidden):
+    torch.manual_seed(0)
+    x = torch.randn(tokens, hidden, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(hidden, device=DEV) * 0.1 + 1).to(torch.bfloat16)
+    y = ops.rmsnorm(x, w, 1e-6)
+    yr, _ = ref.rmsnorm(x, w, 1e-6)
+    _close(y, yr, 2e-2)
+    res = torch.randn_like(x)
+    res2 = res.clone()
+    y = ops.rmsnorm(x, w, 1e-6, residual=res)
+    yr, rr = ref.rmsnorm(x, w, 1e-6, residual=res2)
+    _close(res, rr, 1e-2)
+    _close(y, yr, 3e-2)
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu", "gelu_tanh"])
+def test_act_and_mul(act):
+    torch.manual_seed(1)
+    x = torch.randn(37, 2 * 1536, device=DEV, dtype=torch.bfloat16)
+    _close(ops.act_and_mul(x, act), ref.act_and_mul(x, act), 2e-2)
+
+
+@pytest.mark.parametrize("d,rot,interleaved,qk_norm", [(128, 128, False, True), (128, 64, False, False),
+                                                      (64, 64, True, False), (64, 64, False, True)])
+def test_rope_kv_write(d, rot, interleaved, qk_norm):
+    torch.manual_seed(2)
+    T, nq, nkv, page, nblocks = 45, 8, 2, 16, 12
+    qkv = torch.randn(T, (nq + 2 * nkv) * d, device=DEV, dtype=torch.bfloat16)
+    pos = torch.randint(0, 500, (T,), device=DEV)
+    cs = ref.build_cos_sin_cache(rot, 512, 1e6, None, DEV)
+    qw = (torch.randn(d, device=DEV) * 0.1 + 1).to(torch.bfloat16) if qk_norm else None
+    kw = (torch.randn(d, device=DEV) * 0.1 + 1).to(torch.bfloat16) if qk_norm else None
+    slots = torch.randperm(nblocks * page, device=DEV)[:T].to(torch.int32)
+    slots[3] = -1
+    kc = torch.zeros(nblocks, nkv, page, d, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    q = ops.rope_kv_write(qkv, nq, nkv, d, pos, cs, rot, slots, kc, vc, qw, kw, 1e-6, interleaved)
+    qr, kr, vr = ref.rope_kv(qkv, nq, nkv, d, pos, cs, rot, qw, kw, 1e-6, interleaved)
+    kcr, vcr = torch.zeros_like(kc), torch.zeros_like(vc)
+    ref.write_kv_cache(kr, vr, kcr, vcr, slots)
+    _close(q, qr, 3e-2)
+    _close(kc, kcr, 3e-2)
+    assert torch.equal(vc, vcr)
+
+
+def _paged_setup(B, nq, nkv, d, page, lens, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    max_blocks = max((L + page - 1) // page for L in lens) + 1
+    nblocks = B * max_blocks + 2
+    kc = torch.randn(nblocks, nkv, page, d, device=DEV, dtype=torch.bfloat16, generator=g)
+    vc = torch.randn(nblocks, nkv, page, d, device=DEV, dtype=torch.bfloat16, generator=g)
+    perm = torch.randperm(nblocks - 1, device=DEV, generator=g)[: B * max_blocks] + 1
+    bt = perm.view(B, max_blocks).to(torch.int32)
+    return kc, vc, bt
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [(32, 8, 128, 16), (8, 8, 128, 16), (16, 2, 64, 32), (40, 2, 128, 64),
+                                           (4, 1, 256, 16)])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_paged_decode_attention(nq, nkv, d, page, splits):
+    lens = [1, 17, 200, 555, 64, 1023]
+    B = len(lens)
+    kc, vc, bt = _paged_setup(B, nq, nkv, d, page, lens)
+    q = torch.randn(B, nq, d, device=DEV, dtype=torch.bfloat16)
+    sl = torch.tensor(lens, device=DEV, dtype=torch.int32)
+    scale = 1 / math.sqrt(d)
+    y = ops.paged_decode_attention(q, kc, vc, bt, sl, scale, splits=splits)
+    yr = ref.paged_decode_attention(q, kc, vc, bt, sl, scale)
+    _close(y, yr, 2e-2)
+
+
+def test_paged_decode_padding_rows_are_zero():
+    kc, vc, bt = _paged_setup(3, 8, 2, 128, 16, [40, 40, 40])
+    q = torch.randn(3, 8, 128, device=DEV, dtype=torch.bfloat16)
+    sl = torch.tensor([40, 0, 7], device=DEV, dtype=torch.int32)
+    y = ops.paged_decode_attention(q, kc, vc, bt, sl, 0.1, splits=2)
+    assert torch.count_nonzero(y[1]) == 0
+    assert torch.isfinite(y.float()).all()
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (4, 4, 64, 32), (16, 2, 128, 128)])
+def test_paged_prefill_attention(nq, nkv, d, page):
+    q_lens = [5, 64, 130, 1, 257]
+    kv_lens = [5, 64, 300, 90, 257]  # third and fourth sequences have cached context
+    B = len(q_lens)
+    kc, vc, bt = _paged_setup(B, nq, nkv, d, page, kv_lens, seed=4)
+    T = sum(q_lens)
+    q = torch.randn(T, nq, d, device=DEV, dtype=torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device=DEV, dtype=torch.int32)
+    kl = torch.tensor(kv_lens, device=DEV, dtype=torch.int32)
+    scale = 1 / math.sqrt(d)
+    y = ops.paged_prefill_attention(q, kc, vc, bt, cu, kl, max(q_lens), scale)
+    yr = ref.paged_attention(q, kc, vc, bt, cu, kl, scale)
+    _close(y, yr, 2e-2)
+    yw = ops.paged_prefill_attention(q, kc, vc, bt, cu, kl, max(q_lens), scale, window=48)
+    ywr = ref.paged_attention(q, kc, vc, bt, cu, kl, scale, window=48)
+    _close(yw, ywr, 2e-2)
+
+
+def test_sample_greedy_and_logprob():
+    torch.manual_seed(5)
+    logits = torch.randn(9, 151936, device=DEV, dtype=torch.bfloat16)
+    ids, _ = ops.sample(logits)
+    assert torch.equal(ids, logits.float().argmax(-1))
+    ids, lp = ops.sample(logits, want_logprob=True)
+    lpr = torch.log_softmax(logits.float(), -1).gather(1, ids[:, None])[:, 0]
+    _close(lp, lpr, 1e-3, 1e-3)
+
+
+def test_sample_topk_topp_support_and_distribution():
+    torch.manual_seed(6)
+    V, B = 4096, 4
+    logits = torch.randn(B, V, device=DEV) * 3
+    temp = torch.tensor([0.7, 1.0, 1.3, 0.0], device=DEV)
+    top_k = torch.tensor([5, 0, 50, 3], device=DEV, dtype=torch.int32)
+    top_p = torch.tensor([1.0, 0.6, 0.9, 1.0], device=DEV)
+    probs = ref.filtered_distribution(logits, temp, top_k, top_p)
+    counts = torch.zeros(B, V, device=DEV)
+    N = 400
+    for i in range(N):
+        ids, lp = ops.sample(logits, temp, top_k, top_p, seed=11, offset=4 * i, want_logprob=True)
+        counts[torch.arange(B), ids] += 1
+        assert bool((probs[torch.arange(B), ids] > 0).all()), "sampled a filtered token"
+    _close(lp[:3], torch.log(probs[torch.arange(3), ids[:3]]), 1e-3, 1e-3)
+    emp = counts / N
+    # total variation distance small for the random rows; greedy row is deterministic
+    tv = 0.5 * (emp - probs).abs().sum(-1)
+    assert bool((tv[:3] < 0.2).all()), tv
+    assert emp[3].max().item() == 1.0 and int(emp[3].argmax()) == int(logits[3].argmax())
+
+
+def test_penalties():
+    torch.manual_seed(7)
+    logits = torch.randn(3, 1000, device=DEV)
+    ids = torch.tensor([[1, 5, 9, -1], [2, 2, -1, -1], [7, 8, 9, 10]], device=DEV, dtype=torch.int32)
+    ids[1, 1] = 3
+    cnt = torch.tensor([[1, 2, 3, 0], [4, 1, 0, 0], [1, 1, 1, 1]], device=DEV, dtype=torch.int32)
+    f = torch.tensor([0.5, 0.0, 0.1], device=DEV)
+    p = torch.tensor([0.2, 0.0, 0.0], device=DEV)
+    r = torch.tensor([1.0, 1.3, 1.1], device=DEV)
+    want = ref.apply_penalties(logits.clone().cpu(), ids.cpu(), cnt.cpu(), f.cpu(), p.cpu(), r.cpu())
+    got = ops.apply_penalties(logits.clone(), ids, cnt, f, p, r)
+    _close(got.cpu(), want, 1e-5, 1e-5)
+
+
+def test_embedding_gather_blockcopy_advance():
+    torch.manual_seed(8)
+    table = torch.randn(1000, 256, device=DEV, dtype=torch.bfloat16)
+    ids = torch.randint(0, 1000, (77,), device=DEV)
+    assert torch.equal(ops.embedding(ids, table), table[ids])
+    part = ops.embedding(ids, table[500:], vocab_start=500)
+    want = torch.where((ids >= 500)[:, None], table[ids], torch.zeros_like(table[ids]))
+    assert torch.equal(part, want)
+    idx = torch.randint(0, 1000, (33,), device=DEV)
+    assert torch.equal(ops.gather_rows(table, idx), table[idx])
+    cache = torch.randn(2, 10, 4, 16, 64, device=DEV, dtype=torch.bfloat16)  # [layers, blocks, ...]
+    want = cache.clone()
+    want[:, 7] = want[:, 2]
+    want[:, 9] = want[:, 3]
+    ptrs = torch.tensor([cache[0].data_ptr(), cache[1].data_ptr()], device=DEV, dtype=torch.int64)
+    pairs = torch.tensor([[2, 7], [3, 9]], device=DEV, dtype=torch.int32)
+    ops.block_copy(ptrs, 2, pairs, cache[0, 0].numel() * 2)
+    assert torch.equal(cache, want)
+    toks = torch.tensor([-1, 5, -3], device=DEV)
+    ops.resolve_placeholders(toks, torch.tensor([11, 12, 13], device=DEV))
+    assert toks.tolist() == [11, 5, 13]

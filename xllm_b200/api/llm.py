@@ -1,0 +1,218 @@
+"""Offline Python entry points: LLM.generate / beam_search / embed, SamplingParams, RequestOutput.
+
+API parity with the reference's pybind front end (xllm/pybind/llm.py:82-519, params.py): same class
+and argument names where they carry over.  Prompts may be strings (tokenised by the C++ tokenizer of
+the model directory) or lists of token ids.
+"""
+from __future__ import annotations
+
+import itertools
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..engine.llm_engine import EngineConfig, LLMEngine
+
+
+@dataclass
+class SamplingParams:
+    """Mirrors xllm.SamplingParams (xllm/pybind/params.py)."""
+    n: int = 1
+    best_of: Optional[int] = None
+    max_tokens: int = 16
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = -1
+    frequency_penalty: float = 0.0
+    presence_penalty: float = 0.0
+    repetition_penalty: float = 1.0
+    logprobs: bool = False
+    top_logprobs: int = 0
+    skip_special_tokens: bool = True
+    ignore_eos: bool = False
+    stop: Optional[List[str]] = None
+    stop_token_ids: Optional[List[int]] = None
+    seed: Optional[int] = None
+    echo: bool = False
+
+
+@dataclass
+class BeamSearchParams:
+    beam_width: int = 4
+    max_tokens: int = 16
+    length_penalty: float = 1.0
+    ignore_eos: bool = False
+
+
+@dataclass
+class SequenceOutput:
+    index: int
+    text: str = ""
+    token_ids: List[int] = field(default_factory=list)
+    finish_reason: Optional[str] = None
+    logprobs: Optional[List[float]] = None
+
+
+@dataclass
+class Usage:
+    num_prompt_tokens: int = 0
+    num_generated_tokens: int = 0
+    num_total_tokens: int = 0
+    num_cached_tokens: int = 0
+
+
+@dataclass
+class RequestOutput:
+    request_id: str
+    prompt: Optional[str] = None
+    prompt_token_ids: List[int] = field(default_factory=list)
+    outputs: List[SequenceOutput] = field(default_factory=list)
+    finished: bool = False
+    cancelled: bool = False
+    usage: Usage = field(default_factory=Usage)
+
+
+class LLM:
+    """Offline batch inference over one engine (single GPU, or one rank of a TP job)."""
+
+    _ids = itertools.count()
+
+    def __init__(self, model: str = "tiny", devices: Optional[str] = None, dtype: str = "auto",
+                 block_size: int = 16, max_cache_size: int = 0, max_memory_utilization: float = 0.9,
+                 enable_prefix_cache: bool = True, max_tokens_per_batch: int = 8192,
+                 max_seqs_per_batch: int = 256, max_tokens_per_chunk_for_prefill: int = -1,
+                 enable_chunked_prefill: bool = True, enable_schedule_overlap: bool = False,
+                 enable_graph: bool = True, max_model_len: int = 0, num_blocks: int = 0,
+                 policy: str = "prefill_first", seed: int = 0, random_weights: bool = False,
+                 parallel_state=None, tokenizer=None, **kwargs):
+        device = "auto"
+        if devices:
+            device = devices.split(",")[0].strip()
+            if device == "cuda":
+                device = "cuda:0"
+        cfg = EngineConfig(model=model, dtype=dtype, device=device, block_size=block_size,
+                           num_blocks=num_blocks, max_memory_utilization=max_memory_utilization,
+                           max_cache_size=max_cache_size, max_seqs_per_batch=max_seqs_per_batch,
+                           max_tokens_per_batch=max_tokens_per_batch, max_model_len=max_model_len,
+                           enable_prefix_cache=enable_prefix_cache,
+                           enable_chunked_prefill=enable_chunked_prefill,
+                           max_tokens_per_chunk_for_prefill=max_tokens_per_chunk_for_prefill,
+                           policy=policy, enable_schedule_overlap=enable_schedule_overlap,
+                           enable_graph=enable_graph, seed=seed, random_weights=random_weights)
+        for k, v in kwargs.items():
+            if hasattr(cfg, k):
+                setattr(cfg, k, v)
+        self.engine = LLMEngine(cfg, ps=parallel_state)
+        self.tokenizer = tokenizer
+        if tokenizer is None:
+            import os
+            if os.path.isdir(model):
+                from ..utils.tokenizer import load_tokenizer
+                self.tokenizer = load_tokenizer(model)
+
+    # ------------------------------------------------------------------ helpers
+    def _encode(self, p) -> List[int]:
+        if isinstance(p, str):
+            if self.tokenizer is None:
+                raise ValueError("string prompts need a tokenizer; pass token ids instead")
+            return list(self.tokenizer.encode(p))
+        if isinstance(p, torch.Tensor):
+            return p.tolist()
+        return list(p)
+
+    def _decode(self, ids: Sequence[int], skip_special=True) -> str:
+        if self.tokenizer is None:
+            return ""
+        return self.tokenizer.decode(list(ids), skip_special)
+
+    # ------------------------------------------------------------------ generate
+    def generate(self, prompts, sampling_params: Union[SamplingParams, List[SamplingParams], None] = None,
+                 max_concurrency: int = 0, on_token=None) -> List[RequestOutput]:
+        """Run every prompt to completion.  `max_concurrency` > 0 keeps at most that many requests in
+        flight (a closed loop: a finished request admits the next one), 0 submits everything."""
+        if isinstance(prompts, (str, torch.Tensor)) or (prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        n = len(prompts)
+        sps = sampling_params if isinstance(sampling_params, list) else [sampling_params or SamplingParams()] * n
+        outs: List[RequestOutput] = []
+        by_id: Dict[str, RequestOutput] = {}
+        todo = []
+        for i, (p, sp) in enumerate(zip(prompts, sps)):
+            ids = self._encode(p)
+            rid = f"req-{next(LLM._ids)}"
+            ro = RequestOutput(rid, p if isinstance(p, str) else None, ids,
+                               [SequenceOutput(j) for j in range(sp.n)])
+            ro.usage.num_prompt_tokens = len(ids)
+            outs.append(ro)
+            by_id[rid] = ro
+            todo.append((rid, ids, sp))
+        eng = self.engine
+        in_flight = 0
+        cursor = 0
+
+        def submit_some():
+            nonlocal cursor, in_flight
+            while cursor < n and (max_concurrency <= 0 or in_flight < max_concurrency):
+                rid, ids, sp = todo[cursor]
+                cursor += 1
+                stop_seqs = None
+                if sp.stop and self.tokenizer is not None:
+                    stop_seqs = [list(self.tokenizer.encode(s)) for s in sp.stop]
+                ok = eng.add_request(rid, ids, temperature=sp.temperature, top_p=sp.top_p, top_k=sp.top_k,
+                                     max_tokens=sp.max_tokens, ignore_eos=sp.ignore_eos,
+                                     stop_token_ids=sp.stop_token_ids, stop_sequences=stop_seqs,
+                                     frequency_penalty=sp.frequency_penalty,
+                                     presence_penalty=sp.presence_penalty,
+                                     repetition_penalty=sp.repetition_penalty, logprobs=sp.logprobs,
+                                     top_logprobs=sp.top_logprobs, seed=sp.seed, n=sp.n, offline=True)
+                if not ok:
+                    by_id[rid].finished = True
+                    by_id[rid].cancelled = True
+                else:
+                    in_flight += 1
+
+        submit_some()
+        while eng.has_unfinished() or cursor < n:
+            for e in eng.step():
+                ro = by_id.get(e.request_id)
+                if ro is None:
+                    continue
+                so = ro.outputs[e.seq_index]
+                if e.token >= 0:
+                    so.token_ids.append(e.token)
+                    if e.has_logprob:
+                        if so.logprobs is None:
+                            so.logprobs = []
+                        so.logprobs.append(e.logprob)
+                    if on_token is not None:
+                        on_token(ro, so, e.token)
+                if e.finished:
+                    so.finish_reason = e.finish_reason
+                    ro.usage.num_cached_tokens = max(ro.usage.num_cached_tokens, e.prefix_hit_tokens)
+                if e.request_finished and not ro.finished:
+                    ro.finished = True
+                    ro.cancelled = e.finish_reason == "abort"
+                    in_flight -= 1
+            submit_some()
+        for ro, (_, _, sp) in zip(outs, todo):
+            gen = 0
+            for so in ro.outputs:
+                gen += len(so.token_ids)
+                so.text = self._decode(so.token_ids, sp.skip_special_tokens)
+            ro.usage.num_generated_tokens = gen
+            ro.usage.num_total_tokens = gen + ro.usage.num_prompt_tokens
+        return outs
+
+    # ------------------------------------------------------------------ control
+    def sleep(self, level: int = 1):
+        self.engine.pause("KEEP")
+
+    def wake_up(self):
+        self.engine.resume()
+
+    def update_weights(self, weights):
+        self.engine.update_weights(weights)
+
+    def stats(self):
+        return self.engine.stats()

@@ -1,0 +1,58 @@
+// Gated activations: out[t, :d] = act(x[t, :d]) * x[t, d:2d]   (bf16, fp32 math)
+//
+// Parity: act_and_mul_kernel (silu/gelu/gelu_tanh) of the reference
+// (xllm/core/kernels/cuda/activation.cu:45-159).  Flat grid over 16-byte
+// vectors so that small token counts still fill the 148 SMs.
+#include "common.cuh"
+
+namespace xllm {
+
+__device__ __forceinline__ float act_silu(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float act_gelu(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678f)); }
+__device__ __forceinline__ float act_gelu_tanh(float x) {
+  const float k = 0.7978845608f;
+  return 0.5f * x * (1.f + tanhf(k * (x + 0.044715f * x * x * x)));
+}
+
+template <int ACT>
+__global__ void __launch_bounds__(256)
+act_and_mul_kernel(bf16* __restrict__ out, const bf16* __restrict__ x, int64_t tokens, int d,
+                   int64_t x_stride) {
+  const int vec_per_row = d >> 3;
+  const int64_t total = tokens * vec_per_row;
+  pdl_wait();
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / vec_per_row;
+    const int v = (int)(i - t * vec_per_row);
+    const bf16x8* row = reinterpret_cast<const bf16x8*>(x + t * x_stride);
+    float a[8], b[8], o[8];
+    unpack8(row[v], a);
+    unpack8(row[v + vec_per_row], b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float g = ACT == 0 ? act_silu(a[j]) : (ACT == 1 ? act_gelu(a[j]) : act_gelu_tanh(a[j]));
+      o[j] = g * b[j];
+    }
+    reinterpret_cast<bf16x8*>(out + t * (int64_t)d)[v] = pack8(o);
+  }
+  pdl_launch_dependents();
+}
+
+}  // namespace xllm
+
+// act: 0 silu, 1 gelu(erf), 2 gelu(tanh).  x:[tokens, 2d] with row stride x_stride, out:[tokens, d].
+XLLM_API int xllm_act_and_mul(void* out, const void* x, int64_t tokens, int d, int64_t x_stride,
+                              int act, void* stream) {
+  using namespace xllm;
+  if (tokens == 0) return 0;
+  if (d % 8 != 0) return (int)cudaErrorInvalidValue;
+  const int64_t total = tokens * (d >> 3);
+  int grid = (int)((total + 255) / 256);
+  if (grid > 148 * 16) grid = 148 * 16;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (act == 0) act_and_mul_kernel<0><<<grid, 256, 0, s>>>((bf16*)out, (const bf16*)x, tokens, d, x_stride);
+  else if (act == 1) act_and_mul_kernel<1><<<grid, 256, 0, s>>>((bf16*)out, (const bf16*)x, tokens, d, x_stride);
+  else act_and_mul_kernel<2><<<grid, 256, 0, s>>>((bf16*)out, (const bf16*)x, tokens, d, x_stride);
+  return XLLM_LAUNCH_CHECK();
+}

@@ -1,0 +1,276 @@
+"""LLM engine: owns the model, the KV cache, the C++ scheduler and the step loop.
+
+Capability parity with the reference's LLMEngine + the scheduler loop of LLMMaster
+(xllm/core/distributed_runtime/llm_engine.cpp:188-222 init, 447-763 KV capacity + allocation,
+1081-1232 step / overlap result fetch; llm_master.cpp:305-334).  One engine per process; with
+tensor parallelism every rank runs the same deterministic scheduler on the same request stream,
+so no per-step control traffic is needed — the only cross-rank traffic is the model's collectives.
+"""
+from __future__ import annotations
+
+import os
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+from .. import _build  # noqa: F401  (keeps the build helper importable from the package)
+from ..models import ModelArgs, create_model, load_model_args, preset
+from ..parallel.state import ParallelState, single
+from .model_runner import ModelRunner, StepOutput
+
+
+def _rt():
+    try:
+        from .. import _rt as rt
+    except ImportError:
+        _build.build_runtime()
+        from .. import _rt as rt
+    return rt
+
+
+@dataclass
+class EngineConfig:
+    model: str = "tiny"                 # preset name or a HuggingFace model directory
+    dtype: str = "auto"
+    device: str = "auto"
+    block_size: int = 16
+    num_blocks: int = 0                 # 0: derive from free memory
+    max_memory_utilization: float = 0.9
+    max_cache_size: int = 0             # bytes; 0: no explicit cap
+    max_seqs_per_batch: int = 256
+    max_tokens_per_batch: int = 8192
+    max_model_len: int = 0              # 0: model's max_position_embeddings (capped at 32768)
+    enable_prefix_cache: bool = True
+    enable_chunked_prefill: bool = True
+    max_tokens_per_chunk_for_prefill: int = -1
+    policy: str = "prefill_first"
+    priority_strategy: str = "fcfs"
+    enable_schedule_overlap: bool = False
+    enable_graph: bool = True
+    graph_buckets: Optional[List[int]] = None
+    seed: int = 0
+    random_weights: bool = False
+    load_format: str = "auto"
+    dp_size: int = 1
+    ep_size: int = 1
+    num_speculative_tokens: int = 0
+    draft_model: str = ""
+    activation_reserve_bytes: int = 0   # 0: estimated from max_tokens_per_batch
+
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float16": torch.float16,
+           "fp16": torch.float16, "float32": torch.float32, "fp32": torch.float32}
+
+
+class LLMEngine:
+    def __init__(self, cfg: EngineConfig, ps: Optional[ParallelState] = None, model=None,
+                 model_args: Optional[ModelArgs] = None):
+        self.cfg = cfg
+        self.ps = ps or single()
+        rt = _rt()
+        self.rt = rt
+        # ---- device / dtype
+        if cfg.device == "auto":
+            self.device = self.ps.device if self.ps.world_size > 1 else \
+                torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+        else:
+            self.device = torch.device(cfg.device)
+        if model_args is not None:
+            self.args = model_args
+        elif os.path.isdir(cfg.model):
+            self.args = load_model_args(cfg.model)
+        else:
+            self.args = preset(cfg.model)
+        if cfg.dtype == "auto":
+            self.dtype = torch.bfloat16 if self.device.type == "cuda" else _DTYPES.get(self.args.dtype, torch.float32)
+            if self.device.type == "cpu" and self.dtype == torch.bfloat16:
+                self.dtype = torch.float32
+        else:
+            self.dtype = _DTYPES[cfg.dtype]
+        # ---- model
+        t0 = time.time()
+        if model is not None:
+            self.model = model
+        else:
+            self.model = create_model(self.args, self.dtype, self.device, self.ps)
+            if os.path.isdir(cfg.model) and not cfg.random_weights:
+                from ..utils.loader import iterate_weights
+                self.model.load_weights(iterate_weights(cfg.model), strict=False)
+            else:
+                self.model.init_random(seed=cfg.seed)
+        self.load_seconds = time.time() - t0
+        # ---- KV capacity
+        max_len = cfg.max_model_len or min(self.args.max_position_embeddings, 32768)
+        self.max_model_len = max_len
+        nkv = self.model.num_kv_heads_local
+        per_block = ModelRunner.kv_bytes_per_block(self.args, nkv, cfg.block_size, self.dtype)
+        num_blocks = cfg.num_blocks or self._estimate_blocks(per_block)
+        self.num_blocks = num_blocks
+        self.runner = ModelRunner(self.model, cfg.block_size, num_blocks, cfg.max_seqs_per_batch,
+                                  cfg.max_tokens_per_batch, max_len, self.device, self.dtype,
+                                  enable_graph=cfg.enable_graph, graph_buckets=cfg.graph_buckets)
+        self.runner.overlap = cfg.enable_schedule_overlap
+        # ---- scheduler
+        sc = rt.SchedulerConfig()
+        sc.max_tokens_per_batch = cfg.max_tokens_per_batch
+        sc.max_seqs_per_batch = cfg.max_seqs_per_batch
+        sc.enable_chunked_prefill = cfg.enable_chunked_prefill
+        sc.max_tokens_per_chunk_for_prefill = cfg.max_tokens_per_chunk_for_prefill
+        sc.enable_prefix_cache = cfg.enable_prefix_cache
+        sc.block_size = cfg.block_size
+        sc.num_blocks = num_blocks
+        sc.policy = cfg.policy
+        sc.priority_strategy = cfg.priority_strategy
+        sc.enable_schedule_overlap = cfg.enable_schedule_overlap
+        sc.dp_size = 1  # one scheduler instance per DP replica
+        sc.num_speculative_tokens = cfg.num_speculative_tokens
+        self.scheduler = rt.Scheduler(sc)
+        self._pending: Optional[StepOutput] = None
+        self.steps = 0
+        self.step_log: List[tuple] = []
+        self.record_steps = False
+
+    # ------------------------------------------------------------------ capacity
+    def _estimate_blocks(self, per_block: int) -> int:
+        """KV blocks that fit next to the weights: (free memory x utilisation - activation reserve)
+        / bytes per block (the reference profiles the same quantity: kv_cache_estimation.cpp)."""
+        cfg = self.cfg
+        if self.device.type != "cuda":
+            return 4096
+        free, total = torch.cuda.mem_get_info(self.device)
+        used_other = total - free
+        budget = int(total * cfg.max_memory_utilization) - used_other
+        a = self.args
+        tp = self.ps.tp_size
+        T = cfg.max_tokens_per_batch
+        # widest live activations of one step: qkv + gate_up + a few hidden-size buffers + logits
+        inter = max(a.intermediate_size, a.moe_intermediate_size * max(a.num_experts_per_tok, 1)) // tp
+        act = T * (2 * inter + 6 * a.hidden_size + (a.num_attention_heads + 2 * a.num_key_value_heads) * a.head_dim // tp) * 2 * 2
+        act += cfg.max_seqs_per_batch * a.vocab_size * 4 * 2
+        reserve = cfg.activation_reserve_bytes or (act + (2 << 30))
+        budget -= reserve
+        if cfg.max_cache_size > 0:
+            budget = min(budget, cfg.max_cache_size)
+        n = budget // per_block
+        if n < 8:
+            raise RuntimeError(f"not enough device memory for a KV cache ({budget} bytes left)")
+        return int(n)
+
+    # ------------------------------------------------------------------ intake
+    def add_request(self, request_id: str, prompt_token_ids, temperature=0.0, top_p=1.0, top_k=-1,
+                    max_tokens=16, ignore_eos=False, stop_token_ids=None, stop_sequences=None,
+                    frequency_penalty=0.0, presence_penalty=0.0, repetition_penalty=1.0,
+                    logprobs=False, top_logprobs=0, seed=None, n=1, priority=0, deadline=0.0,
+                    offline=False, stream=False, eos_token_id=None) -> bool:
+        rt = self.rt
+        sp = rt.SamplingParams()
+        sp.temperature = float(temperature)
+        sp.top_p = float(top_p)
+        sp.top_k = int(top_k)
+        sp.frequency_penalty = float(frequency_penalty)
+        sp.presence_penalty = float(presence_penalty)
+        sp.repetition_penalty = float(repetition_penalty)
+        sp.logprobs = bool(logprobs)
+        sp.top_logprobs = int(top_logprobs)
+        sp.seed = int(seed if seed is not None else self.cfg.seed)
+        st = rt.StoppingParams()
+        st.max_tokens = int(max_tokens)
+        st.max_context_len = int(self.max_model_len)
+        st.eos_token_id = int(self.args.eos_token_id if eos_token_id is None else eos_token_id)
+        st.ignore_eos = bool(ignore_eos)
+        extra = [t for t in self.args.stop_token_ids if t != st.eos_token_id]
+        st.stop_token_ids = list(stop_token_ids or []) + extra
+        st.stop_sequences = [list(s) for s in (stop_sequences or [])]
+        toks = [int(t) for t in prompt_token_ids]
+        if len(toks) >= self.max_model_len:
+            return False
+        return self.scheduler.add_request(request_id, toks, sp, st, n, priority, deadline, offline, stream)
+
+    def abort(self, request_id: str) -> bool:
+        return self.scheduler.abort_request(request_id)
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished() or self._pending is not None
+
+    # ------------------------------------------------------------------ stepping
+    def _finish(self, out: StepOutput):
+        ids, lp = out.wait()
+        return self.scheduler.process_output(out.batch_id, ids, lp)
+
+    def step(self):
+        """One scheduler iteration. Returns the list of OutputEvent produced by it."""
+        events = []
+        batches = self.scheduler.schedule()
+        batch = batches[0] if batches else None
+        if self.cfg.enable_schedule_overlap:
+            new = self.runner.execute(batch) if batch is not None else None
+            if self._pending is not None:
+                events = self._finish(self._pending)
+            self._pending = new
+        else:
+            if batch is not None:
+                out = self.runner.execute(batch)
+                events = self._finish(out)
+            else:
+                events = self.scheduler.take_pending_events()
+        if batch is not None:
+            self.steps += 1
+            if self.record_steps:
+                self.step_log.append((batch.n_decode, batch.n_prefill, batch.n_tokens))
+        return events
+
+    def drain(self):
+        events = []
+        if self._pending is not None:
+            events = self._finish(self._pending)
+            self._pending = None
+        return events
+
+    def run_until_done(self, on_event: Optional[Callable] = None, max_steps: int = 0):
+        n = 0
+        while self.has_unfinished():
+            evs = self.step()
+            if on_event is not None:
+                for e in evs:
+                    on_event(e)
+            n += 1
+            if max_steps and n >= max_steps:
+                break
+        return n
+
+    # ------------------------------------------------------------------ control (RL-style)
+    def pause(self, mode="KEEP"):
+        self.drain()
+        self.scheduler.pause(getattr(self.rt.PauseMode, mode))
+
+    def resume(self):
+        self.scheduler.resume()
+
+    def reset_prefix_cache(self):
+        self.scheduler.reset_prefix_cache()
+
+    def update_weights(self, weights):
+        """Hot-swap weights from an iterable of (name, tensor); the prefix cache is dropped because
+        cached KV was computed with the old weights (the reference resets it on wake-up,
+        llm_master.cpp:660-671)."""
+        self.drain()
+        self.model.load_weights(weights, strict=False)
+        self.reset_prefix_cache()
+
+    def stats(self) -> Dict[str, float]:
+        bs = self.scheduler.block_stats(0)
+        return {
+            "steps": self.steps,
+            "num_waiting": self.scheduler.num_waiting,
+            "num_running": self.scheduler.num_running,
+            "kv_utilization": self.scheduler.kv_utilization(0),
+            "num_blocks": bs.num_blocks,
+            "prefix_hit_blocks": bs.match_hits_blocks,
+            "prefix_query_blocks": bs.match_query_blocks,
+            "preemptions": self.scheduler.num_preemptions,
+            "graph_replays": self.runner.graph_replays,
+            "h2d_bytes": self.runner.h2d_bytes,
+            "d2h_bytes": self.runner.d2h_bytes,
+        }

@@ -1,0 +1,364 @@
+"""Layer building blocks shared by the model zoo: TP linears, embedding, attention, MLP, norms.
+
+Capability parity with the reference's layers/common (ColumnParallel / QKVParallel / RowParallel /
+Replicated linears `linear.cpp:609-745, 1198-1285, 1647-1942`; `word_embedding_impl.cpp:48-56`;
+`qwen2_attention.cpp:56-195` incl. KV-head replication when n_kv_heads < tp; `dense_mlp.cpp:124-170`;
+`rms_norm.cpp`).  Modules are thin holders of inference-only tensors; every forward is a sequence of
+ops from ``xllm_b200.ops`` (sm_100a kernels on CUDA, PyTorch references on CPU).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Callable, Dict, Iterable, List, Optional, Tuple
+
+import torch
+
+from .. import ops
+from ..ops import reference
+from ..parallel.state import ParallelState, single
+
+
+# ----------------------------------------------------------------------------------- metadata
+@dataclass
+class AttentionMetadata:
+    """Per-step attention inputs (device tensors).  Decode sequences occupy the first `n_decode`
+    rows of every per-sequence tensor and the first `n_decode` token rows."""
+    n_decode: int
+    n_prefill: int
+    slots: torch.Tensor          # [T] int32 cache slot of every new token (-1: skip)
+    block_table: torch.Tensor    # [B, max_blocks] int32
+    kv_lens: torch.Tensor        # [B] int32
+    cu_q: torch.Tensor           # [B + 1] int32
+    max_q_len: int = 1
+    max_kv_len: int = 0
+    decode_splits: int = 1
+    decode_workspace: Optional[torch.Tensor] = None
+
+    @property
+    def n_seqs(self):
+        return self.n_decode + self.n_prefill
+
+
+# ----------------------------------------------------------------------------------- param registry
+class Module:
+    """Minimal parameter container: name -> (tensor, loader).  Loaders copy (a shard of) a
+    checkpoint tensor into the parameter; fused parameters register one loader per source name."""
+
+    def __init__(self):
+        self._params: Dict[str, torch.Tensor] = {}
+        self._loaders: Dict[str, Callable[[torch.Tensor], None]] = {}
+        self._children: Dict[str, "Module"] = {}
+
+    def add_param(self, name, tensor, loaders: Optional[Dict[str, Callable]] = None):
+        self._params[name] = tensor
+        if loaders is None:
+            loaders = {name: lambda w, t=tensor: t.copy_(w.to(t.dtype))}
+        self._loaders.update(loaders)
+        return tensor
+
+    def add_module(self, name, mod):
+        self._children[name] = mod
+        return mod
+
+    def named_params(self, prefix=""):
+        for n, t in self._params.items():
+            yield prefix + n, t
+        for cn, c in self._children.items():
+            yield from c.named_params(prefix + cn + ".")
+
+    def named_loaders(self, prefix=""):
+        for n, f in self._loaders.items():
+            yield prefix + n, f
+        for cn, c in self._children.items():
+            yield from c.named_loaders(prefix + cn + ".")
+
+    def param_bytes(self):
+        return sum(t.numel() * t.element_size() for _, t in self.named_params())
+
+    def load_weights(self, weights: Iterable[Tuple[str, torch.Tensor]], strict=True):
+        loaders = dict(self.named_loaders())
+        seen = set()
+        for name, w in weights:
+            f = loaders.get(name)
+            if f is None:
+                continue
+            f(w)
+            seen.add(name)
+        missing = [n for n in loaders if n not in seen]
+        if strict and missing:
+            raise KeyError(f"weights missing from checkpoint: {missing[:8]} (+{max(0, len(missing) - 8)} more)")
+        return missing
+
+    @torch.no_grad()
+    def init_random(self, std=0.02, seed=0):
+        """Deterministic N(0, std) weights; norm weights are set to 1."""
+        for i, (name, t) in enumerate(self.named_params()):
+            if t.dtype in (torch.float8_e4m3fn, torch.uint8, torch.int32, torch.int64):
+                continue
+            if name.endswith("norm.weight") or name.endswith("layernorm.weight") or ".norm." in name \
+                    or name.endswith("_norm.weight"):
+                t.fill_(1.0)
+                continue
+            g = torch.Generator(device=t.device)
+            g.manual_seed(seed * 1000003 + i)
+            t.normal_(0.0, std, generator=g)
+
+
+def _shard(w, dim, rank, size):
+    if size == 1:
+        return w
+    n = w.shape[dim] // size
+    return w.narrow(dim, rank * n, n)
+
+
+class Linear(Module):
+    """y = x W^T (+ b). `parallel`: None (replicated), 'column' (shard dim 0), 'row' (shard dim 1)."""
+
+    def __init__(self, in_f, out_f, bias, dtype, device, ps: ParallelState = None, parallel=None,
+                 reduce=True, gather_output=False):
+        super().__init__()
+        self.ps = ps or single()
+        tp, rank = self.ps.tp_size, self.ps.tp_rank
+        self.parallel = parallel if tp > 1 else None
+        self.reduce = reduce
+        self.gather_output = gather_output
+        out_l = out_f // tp if self.parallel == "column" else out_f
+        in_l = in_f // tp if self.parallel == "row" else in_f
+        self.weight = torch.empty(out_l, in_l, dtype=dtype, device=device)
+        dim = {"column": 0, "row": 1}.get(self.parallel)
+
+        def load_w(w, t=self.weight):
+            t.copy_((_shard(w, dim, rank, tp) if dim is not None else w).to(t.dtype))
+
+        self.add_param("weight", self.weight, {"weight": load_w})
+        self.bias = None
+        if bias:
+            self.bias = torch.zeros(out_l, dtype=dtype, device=device)
+
+            def load_b(b, t=self.bias):
+                t.copy_((_shard(b, 0, rank, tp) if self.parallel == "column" else b).to(t.dtype))
+
+            self.add_param("bias", self.bias, {"bias": load_b})
+
+    def forward(self, x):
+        bias = self.bias
+        if self.parallel == "row" and self.ps.tp_rank != 0:
+            bias = None  # added once, by rank 0, before the reduction
+        y = ops.linear(x, self.weight, bias)
+        if self.parallel == "row" and self.reduce:
+            y = self.ps.all_reduce(y)
+        elif self.parallel == "column" and self.gather_output:
+            y = self.ps.all_gather(y, dim=-1)
+        return y
+
+    __call__ = forward
+
+
+class MergedColumnLinear(Module):
+    """Several column-parallel projections of the same input fused into one GEMM
+    (gate_proj|up_proj, q|k|v).  `sizes` are full (unsharded) output sizes, `names` the checkpoint
+    sub-module names; `replicas[i]` > 1 means that shard i is replicated across that many ranks
+    (KV heads when n_kv_heads < tp)."""
+
+    def __init__(self, in_f, sizes: List[int], names: List[str], bias, dtype, device,
+                 ps: ParallelState = None, shard_counts: Optional[List[int]] = None):
+        super().__init__()
+        self.ps = ps or single()
+        tp, rank = self.ps.tp_size, self.ps.tp_rank
+        counts = shard_counts or [tp] * len(sizes)
+        self.local_sizes = [s // c for s, c in zip(sizes, counts)]
+        total = sum(self.local_sizes)
+        self.weight = torch.empty(total, in_f, dtype=dtype, device=device)
+        self.bias = torch.zeros(total, dtype=dtype, device=device) if bias else None
+        loaders = {}
+        off = 0
+        for name, full, cnt, loc in zip(names, sizes, counts, self.local_sizes):
+            idx = rank * cnt // tp  # which shard of this projection the rank holds
+
+            def lw(w, o=off, n=loc, i=idx, t=self.weight):
+                t[o:o + n].copy_(w.narrow(0, i * n, n).to(t.dtype))
+
+            loaders[f"{name}.weight"] = lw
+            if bias:
+                def lb(b, o=off, n=loc, i=idx, t=self.bias):
+                    t[o:o + n].copy_(b.narrow(0, i * n, n).to(t.dtype))
+
+                loaders[f"{name}.bias"] = lb
+            off += loc
+        self._params["weight"] = self.weight
+        if bias:
+            self._params["bias"] = self.bias
+        self._loaders.update(loaders)
+
+    def forward(self, x):
+        return ops.linear(x, self.weight, self.bias)
+
+    __call__ = forward
+
+
+class VocabEmbedding(Module):
+    """Vocabulary-sharded embedding: each TP rank holds V/tp rows, out-of-shard ids give zeros and
+    the partial results are summed (the reference shards the hidden dim and all-gathers,
+    word_embedding_impl.cpp:48-56; summing a vocab-sharded lookup lets the lm_head share the
+    same shard when embeddings are tied)."""
+
+    def __init__(self, vocab, hidden, dtype, device, ps: ParallelState = None):
+        super().__init__()
+        self.ps = ps or single()
+        tp, rank = self.ps.tp_size, self.ps.tp_rank
+        self.vocab = vocab
+        self.shard = (vocab + tp - 1) // tp
+        self.start = rank * self.shard
+        rows = max(0, min(self.shard, vocab - self.start))
+        self.rows = rows
+        self.weight = torch.zeros(self.shard, hidden, dtype=dtype, device=device)
+
+        def lw(w, t=self.weight):
+            t[:rows].copy_(w[self.start:self.start + rows].to(t.dtype))
+
+        self.add_param("weight", self.weight, {"weight": lw})
+
+    def forward(self, ids):
+        y = ops.embedding(ids, self.weight, self.start)
+        if self.ps.tp_size > 1:
+            y = self.ps.all_reduce(y)
+        return y
+
+    __call__ = forward
+
+
+class LMHead(Module):
+    """Vocab-parallel output projection with all-gather of the logits shards."""
+
+    def __init__(self, vocab, hidden, dtype, device, ps: ParallelState = None, tied: Optional[VocabEmbedding] = None):
+        super().__init__()
+        self.ps = ps or single()
+        tp, rank = self.ps.tp_size, self.ps.tp_rank
+        self.vocab = vocab
+        self.shard = (vocab + tp - 1) // tp
+        self.start = rank * self.shard
+        rows = max(0, min(self.shard, vocab - self.start))
+        if tied is not None:
+            self.weight = tied.weight
+        else:
+            self.weight = torch.zeros(self.shard, hidden, dtype=dtype, device=device)
+
+            def lw(w, t=self.weight):
+                t[:rows].copy_(w[self.start:self.start + rows].to(t.dtype))
+
+            self.add_param("weight", self.weight, {"weight": lw})
+
+    def forward(self, x):
+        y = ops.linear(x, self.weight)
+        if self.ps.tp_size > 1:
+            y = self.ps.all_gather(y, dim=-1)
+        return y[..., :self.vocab] if y.shape[-1] != self.vocab else y
+
+    __call__ = forward
+
+
+class RMSNorm(Module):
+    def __init__(self, hidden, eps, dtype, device, gemma=False):
+        super().__init__()
+        self.eps = eps
+        self.gemma = gemma
+        self.weight = self.add_param("weight", torch.ones(hidden, dtype=dtype, device=device))
+
+    def forward(self, x, residual=None):
+        return ops.rmsnorm(x, self.weight, self.eps, residual=residual, gemma=self.gemma)
+
+    __call__ = forward
+
+
+class RotaryEmbedding:
+    """fp32 cos/sin cache [max_pos, rot_dim] built once per (rot_dim, theta, scaling)."""
+    _cache: Dict[Tuple, torch.Tensor] = {}
+
+    def __init__(self, rot_dim, max_pos, theta, scaling, device, interleaved=False):
+        key = (rot_dim, max_pos, theta, str(scaling), str(device))
+        if key not in RotaryEmbedding._cache:
+            RotaryEmbedding._cache[key] = reference.build_cos_sin_cache(rot_dim, max_pos, theta, scaling, device)
+        self.cos_sin = RotaryEmbedding._cache[key]
+        self.rot_dim = rot_dim
+        self.interleaved = interleaved
+
+
+class Attention(Module):
+    """GQA self-attention over the paged cache: fused QKV GEMM -> (qk-norm + RoPE + KV write) ->
+    paged decode / prefill attention -> row-parallel o_proj."""
+
+    def __init__(self, args, layer_idx, dtype, device, ps: ParallelState = None, rope: RotaryEmbedding = None):
+        super().__init__()
+        self.ps = ps or single()
+        tp = self.ps.tp_size
+        self.d = args.head_dim
+        self.nq = args.num_attention_heads // tp
+        self.nkv_total = args.num_key_value_heads
+        self.nkv = max(1, self.nkv_total // tp)
+        kv_shards = min(tp, self.nkv_total)  # KV heads are replicated when there are fewer than tp
+        H = args.hidden_size
+        self.qkv = self.add_module("qkv_proj", MergedColumnLinear(
+            H, [args.num_attention_heads * self.d, self.nkv_total * self.d, self.nkv_total * self.d],
+            ["q_proj", "k_proj", "v_proj"], args.attention_bias, dtype, device, self.ps,
+            shard_counts=[tp, kv_shards, kv_shards]))
+        self.o_proj = self.add_module("o_proj", Linear(args.num_attention_heads * self.d, H, False, dtype, device,
+                                                       self.ps, parallel="row"))
+        self.q_norm = self.k_norm = None
+        if args.qk_norm:
+            self.q_norm = self.add_module("q_norm", RMSNorm(self.d, args.rms_norm_eps, dtype, device))
+            self.k_norm = self.add_module("k_norm", RMSNorm(self.d, args.rms_norm_eps, dtype, device))
+        self.eps = args.rms_norm_eps
+        self.rope = rope
+        self.scale = 1.0 / math.sqrt(self.d)
+        self.window = args.sliding_window
+
+    # checkpoint names are self_attn.{q,k,v}_proj -> route them into the fused module
+    def named_loaders(self, prefix=""):
+        for n, f in super().named_loaders(prefix):
+            yield n.replace("qkv_proj.", ""), f
+
+    def forward(self, x, positions, meta: AttentionMetadata, k_cache, v_cache):
+        qkv = self.qkv(x)
+        q = ops.rope_kv_write(qkv, self.nq, self.nkv, self.d, positions, self.rope.cos_sin, self.rope.rot_dim,
+                              slots=meta.slots, k_cache=k_cache, v_cache=v_cache,
+                              q_norm_w=self.q_norm.weight if self.q_norm else None,
+                              k_norm_w=self.k_norm.weight if self.k_norm else None, eps=self.eps,
+                              interleaved=self.rope.interleaved)
+        T = q.shape[0]
+        out = torch.empty((T, self.nq, self.d), dtype=q.dtype, device=q.device)
+        nd = meta.n_decode
+        if nd > 0:
+            ops.paged_decode_attention(q[:nd], k_cache, v_cache, meta.block_table[:nd], meta.kv_lens[:nd],
+                                       self.scale, splits=meta.decode_splits,
+                                       workspace=meta.decode_workspace, out=out[:nd])
+        if meta.n_prefill > 0:
+            # cu_q holds absolute token rows, so the full q / out tensors are passed
+            ops.paged_prefill_attention(q, k_cache, v_cache, meta.block_table[nd:], meta.cu_q[nd:],
+                                        meta.kv_lens[nd:], meta.max_q_len, self.scale, causal=True,
+                                        window=self.window, out=out)
+        return self.o_proj(out.view(T, self.nq * self.d))
+
+    __call__ = forward
+
+
+class DenseMLP(Module):
+    """SwiGLU MLP: fused gate|up column-parallel GEMM -> silu·mul -> row-parallel down GEMM."""
+
+    def __init__(self, hidden, inter, act, dtype, device, ps: ParallelState = None, reduce=True):
+        super().__init__()
+        self.ps = ps or single()
+        self.act = act
+        self.gate_up = self.add_module("gate_up_proj", MergedColumnLinear(
+            hidden, [inter, inter], ["gate_proj", "up_proj"], False, dtype, device, self.ps))
+        self.down = self.add_module("down_proj", Linear(inter, hidden, False, dtype, device, self.ps,
+                                                        parallel="row", reduce=reduce))
+
+    def named_loaders(self, prefix=""):
+        for n, f in super().named_loaders(prefix):
+            yield n.replace("gate_up_proj.", ""), f
+
+    def forward(self, x):
+        return self.down(ops.act_and_mul(self.gate_up(x), self.act))
+
+    __call__ = forward

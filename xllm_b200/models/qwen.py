@@ -1,0 +1,95 @@
+"""Dense decoder family: Qwen2 / Qwen2.5 / Qwen3 / Llama-style (pre-norm, GQA, SwiGLU).
+
+Parity: `Qwen2DecoderLayerImpl::forward` (xllm/core/layers/qwen2_decoder_layer.cpp:87-109),
+`LlmModelImplBase::forward` (xllm/models/llm/llm_model_base.h:85-210), qwen2.h / qwen3.h model
+definitions and their `REGISTER_CAUSAL_MODEL` entries.  The residual stream is carried through the
+fused add+RMSNorm kernel, exactly one read and one write of the hidden state per norm.
+"""
+from __future__ import annotations
+
+import torch
+
+from .layers import (Attention, AttentionMetadata, DenseMLP, LMHead, Module, RMSNorm, RotaryEmbedding,
+                     VocabEmbedding)
+from .registry import register_model
+from ..parallel.state import ParallelState, single
+
+
+class DecoderLayer(Module):
+    def __init__(self, args, idx, dtype, device, ps, rope, mlp=None):
+        super().__init__()
+        self.input_layernorm = self.add_module("input_layernorm", RMSNorm(args.hidden_size, args.rms_norm_eps, dtype, device))
+        self.self_attn = self.add_module("self_attn", Attention(args, idx, dtype, device, ps, rope))
+        self.post_attention_layernorm = self.add_module(
+            "post_attention_layernorm", RMSNorm(args.hidden_size, args.rms_norm_eps, dtype, device))
+        self.mlp = self.add_module("mlp", mlp if mlp is not None else
+                                   DenseMLP(args.hidden_size, args.intermediate_size, args.hidden_act, dtype, device, ps))
+
+    def forward(self, x, residual, positions, meta, k_cache, v_cache):
+        # `residual` holds the running sum; None on the first layer (x is the embedding itself)
+        if residual is None:
+            residual = x
+            h = self.input_layernorm(x)
+        else:
+            h = self.input_layernorm(x, residual=residual)
+        h = self.self_attn(h, positions, meta, k_cache, v_cache)
+        h = self.post_attention_layernorm(h, residual=residual)
+        h = self.mlp(h)
+        return h, residual
+
+    __call__ = forward
+
+
+class DenseCausalLM(Module):
+    """model.embed_tokens -> N x DecoderLayer -> model.norm -> lm_head."""
+
+    def __init__(self, args, dtype=torch.bfloat16, device="cpu", ps: ParallelState = None, make_mlp=None):
+        super().__init__()
+        self.args = args
+        self.ps = ps or single()
+        self.dtype = dtype
+        self.device = torch.device(device)
+        inner = Module()
+        self.add_module("model", inner)
+        self.embed = inner.add_module("embed_tokens", VocabEmbedding(args.vocab_size, args.hidden_size, dtype, device, self.ps))
+        self.rope = RotaryEmbedding(args.rotary_dim, args.max_position_embeddings, args.rope_theta,
+                                    args.rope_scaling, device, args.rope_interleaved)
+        layers = Module()
+        inner.add_module("layers", layers)
+        self.layers = []
+        for i in range(args.num_hidden_layers):
+            mlp = make_mlp(i) if make_mlp is not None else None
+            self.layers.append(layers.add_module(str(i), DecoderLayer(args, i, dtype, device, self.ps, self.rope, mlp)))
+        self.norm = inner.add_module("norm", RMSNorm(args.hidden_size, args.rms_norm_eps, dtype, device))
+        self.lm_head = LMHead(args.vocab_size, args.hidden_size, dtype, device, self.ps,
+                              tied=self.embed if args.tie_word_embeddings else None)
+        if not args.tie_word_embeddings:
+            self.add_module("lm_head", self.lm_head)
+
+    # KV geometry of one layer on this rank
+    @property
+    def num_kv_heads_local(self):
+        return self.layers[0].self_attn.nkv
+
+    @property
+    def head_dim(self):
+        return self.args.head_dim
+
+    def forward(self, tokens, positions, meta: AttentionMetadata, kv_caches):
+        """tokens/positions: [T] int64.  kv_caches: list of (k_cache, v_cache) per layer.
+        Returns the final-norm hidden states [T, H]."""
+        x = self.embed(tokens)
+        residual = None
+        for layer, (kc, vc) in zip(self.layers, kv_caches):
+            x, residual = layer(x, residual, positions, meta, kc, vc)
+        return self.norm(x, residual=residual)
+
+    def logits(self, hidden_rows):
+        return self.lm_head(hidden_rows)
+
+    __call__ = forward
+
+
+@register_model("qwen3", "qwen2", "llama", "mistral", "Qwen3ForCausalLM", "Qwen2ForCausalLM", "LlamaForCausalLM")
+def build_dense(args, dtype, device, ps):
+    return DenseCausalLM(args, dtype, device, ps)

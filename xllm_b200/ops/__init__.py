@@ -1,0 +1,285 @@
+"""Operator front end: every op runs the hand-written sm_100a kernel on CUDA tensors and the
+PyTorch reference on CPU tensors (no third path).
+
+Counterpart of the platform-dispatching `xllm::kernel::*` free functions of the reference
+(xllm/core/kernels/ops_api.h:27-290) — minus the dispatch: there is one target.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib, reference
+from ._lib import check, ptr, stream
+
+_launch_count = 0
+
+
+def launches() -> int:
+    """Number of library kernel launchers invoked by this process (eager calls; a CUDA-graph
+    replay re-issues the launches recorded at capture without passing through here)."""
+    return _launch_count
+
+
+def _count(n=1):
+    global _launch_count
+    _launch_count += n
+
+
+def _lib_():
+    return _lib.load()
+
+
+def _bf16(t, name):
+    if t.dtype != torch.bfloat16:
+        raise TypeError(f"{name}: CUDA kernels take bf16, got {t.dtype}")
+
+
+# ----------------------------------------------------------------------------- norms / act
+def rmsnorm(x, w, eps=1e-6, residual=None, out=None, gemma=False):
+    """y = rmsnorm(x (+ residual)) * w.  `residual`, when given, is updated in place to x + residual."""
+    if not x.is_cuda:
+        y, new_res = reference.rmsnorm(x, w, eps, residual, gemma)
+        if residual is not None:
+            residual.copy_(new_res)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    _bf16(x, "rmsnorm")
+    hidden = x.shape[-1]
+    x2 = x.reshape(-1, hidden)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    if out is None:
+        out = torch.empty(x2.shape, dtype=x.dtype, device=x.device)
+    o2 = out.reshape(-1, hidden)
+    if residual is not None:
+        assert residual.is_contiguous()
+    check(_lib_().xllm_rmsnorm(ptr(o2), ptr(x2), ptr(residual), ptr(w), x2.shape[0], hidden, eps,
+                               x2.stride(0), o2.stride(0), int(gemma), stream()), "rmsnorm")
+    _count()
+    return out.reshape(x.shape)
+
+
+def act_and_mul(x, act="silu", out=None):
+    if not x.is_cuda:
+        return reference.act_and_mul(x, act)
+    _bf16(x, "act_and_mul")
+    d = x.shape[-1] // 2
+    x2 = x.reshape(-1, 2 * d)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    if out is None:
+        out = torch.empty((x2.shape[0], d), dtype=x.dtype, device=x.device)
+    code = {"silu": 0, "gelu": 1, "gelu_tanh": 2, "gelu_pytorch_tanh": 2}[act]
+    check(_lib_().xllm_act_and_mul(ptr(out), ptr(x2), x2.shape[0], d, x2.stride(0), code, stream()),
+          "act_and_mul")
+    _count()
+    return out.reshape(*x.shape[:-1], d)
+
+
+def silu_and_mul(x, out=None):
+    return act_and_mul(x, "silu", out)
+
+
+# ----------------------------------------------------------------------------- rope + kv write
+def rope_kv_write(qkv, nq, nkv, d, positions, cos_sin, rot, slots=None, k_cache=None, v_cache=None,
+                  q_norm_w=None, k_norm_w=None, eps=1e-6, interleaved=False, q_out=None,
+                  return_kv=False):
+    """Per-head RMSNorm (optional) + RoPE on packed QKV, K/V scattered into the paged cache.
+
+    Returns q [T, nq, d] (and dense k, v when return_kv)."""
+    T = qkv.shape[0]
+    if not qkv.is_cuda:
+        q, k, v = reference.rope_kv(qkv, nq, nkv, d, positions, cos_sin, rot, q_norm_w, k_norm_w,
+                                    eps, interleaved)
+        if k_cache is not None and slots is not None:
+            reference.write_kv_cache(k, v, k_cache, v_cache, slots)
+        return (q, k, v) if return_kv else q
+    _bf16(qkv, "rope_kv_write")
+    assert qkv.stride(-1) == 1
+    if q_out is None:
+        q_out = torch.empty((T, nq, d), dtype=qkv.dtype, device=qkv.device)
+    k_out = v_out = None
+    if return_kv:
+        k_out = torch.empty((T, nkv, d), dtype=qkv.dtype, device=qkv.device)
+        v_out = torch.empty((T, nkv, d), dtype=qkv.dtype, device=qkv.device)
+    page = k_cache.shape[2] if k_cache is not None else 1
+    check(_lib_().xllm_rope_kv(ptr(qkv), qkv.stride(0), ptr(q_out), ptr(k_cache), ptr(v_cache),
+                               ptr(k_out), ptr(v_out), ptr(q_norm_w), ptr(k_norm_w), ptr(cos_sin),
+                               ptr(positions), ptr(slots), T, nq, nkv, d, rot, page,
+                               int(interleaved), eps, stream()), "rope_kv")
+    _count()
+    return (q_out, k_out, v_out) if return_kv else q_out
+
+
+# ----------------------------------------------------------------------------- attention
+def decode_splits(batch, nkv, group, max_kv_len=None, n_sm=148):
+    """Split-KV factor: enough CTAs to cover ~2 per SM, never more than one split per 256 tokens."""
+    ctas = batch * nkv * ((group + 15) // 16)
+    s = max(1, min(16, (2 * n_sm + ctas - 1) // ctas))
+    if max_kv_len is not None:
+        s = max(1, min(s, (max_kv_len + 255) // 256))
+    return s
+
+
+def decode_workspace(batch, nq, d, splits, device):
+    if splits <= 1:
+        return None
+    return torch.empty(batch * nq * splits * (d + 1), dtype=torch.float32, device=device)
+
+
+def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, scale, splits=None,
+                           workspace=None, out=None):
+    """q: [B, nq, d] (one query token per sequence) -> [B, nq, d]."""
+    if not q.is_cuda:
+        y = reference.paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, scale)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    _bf16(q, "paged_decode_attention")
+    B, nq, d = q.shape
+    nkv, page = k_cache.shape[1], k_cache.shape[2]
+    if splits is None:
+        splits = decode_splits(B, nkv, nq // nkv)
+    if splits > 1 and workspace is None:
+        workspace = decode_workspace(B, nq, d, splits, q.device)
+    if out is None:
+        out = torch.empty((B, nq, d), dtype=q.dtype, device=q.device)
+    assert q.stride(-1) == 1 and q.stride(1) == d
+    check(_lib_().xllm_paged_decode_attn(ptr(out), ptr(q), q.stride(0), ptr(k_cache), ptr(v_cache),
+                                         ptr(block_table), block_table.stride(0), ptr(seq_lens), B,
+                                         nq, nkv, d, page, scale, splits, ptr(workspace), stream()),
+          "paged_decode_attn")
+    _count(2 if splits > 1 else 1)
+    return out
+
+
+def paged_prefill_attention(q, k_cache, v_cache, block_table, cu_q, kv_lens, max_q_len, scale,
+                            causal=True, window=0, out=None):
+    """q: [T, nq, d] ragged by cu_q -> [T, nq, d]; attends to cache positions [0, kv_len)."""
+    if not q.is_cuda:
+        y = reference.paged_attention(q, k_cache, v_cache, block_table, cu_q, kv_lens, scale,
+                                      causal, window)
+        if out is not None:
+            r0 = int(cu_q[0])
+            out[r0:].copy_(y[r0:])
+            return out
+        return y
+    _bf16(q, "paged_prefill_attention")
+    T, nq, d = q.shape
+    nkv, page = k_cache.shape[1], k_cache.shape[2]
+    if out is None:
+        out = torch.empty((T, nq, d), dtype=q.dtype, device=q.device)
+    assert q.stride(-1) == 1 and q.stride(1) == d
+    B = kv_lens.shape[0]
+    check(_lib_().xllm_paged_prefill_attn(ptr(out), out.stride(0), ptr(q), q.stride(0), ptr(k_cache),
+                                          ptr(v_cache), ptr(block_table), block_table.stride(0),
+                                          ptr(cu_q), ptr(kv_lens), B, int(max_q_len), nq, nkv, d,
+                                          page, scale, int(causal), int(window), stream()),
+          "paged_prefill_attn")
+    _count()
+    return out
+
+
+# ----------------------------------------------------------------------------- sampling
+def sample(logits, temperature=None, top_k=None, top_p=None, seed=0, offset=0, want_logprob=False,
+           generator=None, out_ids=None):
+    """Returns (ids int64 [B], logprob fp32 [B] | None)."""
+    if not logits.is_cuda:
+        return reference.sample(logits, temperature, top_k, top_p, generator, want_logprob)
+    B, V = logits.shape
+    assert logits.stride(-1) == 1
+    dt = 0 if logits.dtype == torch.bfloat16 else 1
+    if dt == 1 and logits.dtype != torch.float32:
+        logits = logits.float()
+    if out_ids is None:
+        out_ids = torch.empty(B, dtype=torch.int64, device=logits.device)
+    lp = torch.empty(B, dtype=torch.float32, device=logits.device) if want_logprob else None
+    check(_lib_().xllm_sample(ptr(logits), logits.stride(0), dt, B, V, ptr(temperature), ptr(top_k),
+                              ptr(top_p), ptr(out_ids), ptr(lp), int(seed), int(offset), stream()),
+          "sample")
+    _count()
+    return out_ids, lp
+
+
+def apply_penalties(logits, ids, counts, freq=None, presence=None, repetition=None):
+    if not logits.is_cuda:
+        return reference.apply_penalties(logits, ids, counts, freq, presence, repetition)
+    B, V = logits.shape
+    dt = 0 if logits.dtype == torch.bfloat16 else 1
+    check(_lib_().xllm_apply_penalties(ptr(logits), logits.stride(0), dt, B, V, ptr(ids), ptr(counts),
+                                       ids.shape[1], ptr(freq), ptr(presence), ptr(repetition),
+                                       stream()), "apply_penalties")
+    _count()
+    return logits
+
+
+# ----------------------------------------------------------------------------- data movement
+def embedding(ids, table, vocab_start=0, out=None):
+    if not table.is_cuda:
+        loc = ids - vocab_start
+        ok = (loc >= 0) & (loc < table.shape[0])
+        y = table[loc.clamp(0, table.shape[0] - 1)]
+        return y * ok[:, None].to(y.dtype)
+    _bf16(table, "embedding")
+    T, H = ids.shape[0], table.shape[1]
+    if out is None:
+        out = torch.empty((T, H), dtype=table.dtype, device=table.device)
+    check(_lib_().xllm_embedding(ptr(out), ptr(table), ptr(ids), T, H, vocab_start,
+                                 vocab_start + table.shape[0], stream()), "embedding")
+    _count()
+    return out
+
+
+def gather_rows(x, idx, out=None):
+    if not x.is_cuda:
+        return x[idx]
+    rows = idx.shape[0]
+    row_bytes = x.shape[1] * x.element_size()
+    if row_bytes % 16 != 0 or (x.stride(0) * x.element_size()) % 16 != 0:
+        return x[idx]
+    if out is None:
+        out = torch.empty((rows, x.shape[1]), dtype=x.dtype, device=x.device)
+    check(_lib_().xllm_gather_rows(ptr(out), ptr(x), ptr(idx), rows, row_bytes,
+                                   x.stride(0) * x.element_size(), stream()), "gather_rows")
+    _count()
+    return out
+
+
+def block_copy(cache_ptr_table, n_layers, pairs, block_bytes):
+    """cache_ptr_table: int64 device tensor of base pointers; pairs: int32 [n, 2] device tensor."""
+    check(_lib_().xllm_block_copy(ptr(cache_ptr_table), n_layers, ptr(pairs), pairs.shape[0],
+                                  block_bytes, stream()), "block_copy")
+    _count()
+
+
+def decode_advance(tokens, positions, seq_lens, slots, block_table, sampled, page):
+    if not tokens.is_cuda:
+        m = seq_lens > 0
+        tokens[m] = sampled[m]
+        positions[m] += 1
+        seq_lens[m] += 1
+        pos = positions[m]
+        rows = torch.nonzero(m).flatten()
+        slots[m] = (block_table[rows, (pos // page).long()] * page + (pos % page)).to(slots.dtype)
+        return
+    check(_lib_().xllm_decode_advance(ptr(tokens), ptr(positions), ptr(seq_lens), ptr(slots),
+                                      ptr(block_table), block_table.stride(0), ptr(sampled),
+                                      tokens.shape[0], page, stream()), "decode_advance")
+    _count()
+
+
+def resolve_placeholders(tokens, prev):
+    if not tokens.is_cuda:
+        neg = tokens < 0
+        tokens[neg] = prev[(-tokens[neg] - 1).long()]
+        return tokens
+    check(_lib_().xllm_resolve_placeholders(ptr(tokens), ptr(prev), tokens.numel(), prev.numel(),
+                                            stream()), "resolve_placeholders")
+    _count()
+    return tokens
+
+
+from .gemm import linear  # noqa: E402,F401
