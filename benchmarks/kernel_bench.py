@@ -1,0 +1,158 @@
+#!/usr/bin/env python
+"""Per-kernel timings against the roofline (CUDA events, warm-up, L2 flushed between iterations).
+
+    python benchmarks/kernel_bench.py [--what gemm,decode,prefill,small] [--json out.json]
+
+Prints, for every kernel and shape of the Qwen3-8B serving step, the achieved TFLOP/s or GB/s, the
+fraction of the measured peak (MEASURED_PEAKS.json when present) and the cuBLAS / PyTorch number for
+the same shape where one exists.
+"""
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from xllm_b200 import ops  # noqa: E402
+from xllm_b200.ops import gemm_tcgen05  # noqa: E402
+
+
+def peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+_flush = None
+
+
+def bench(fn, iters=10, warmup=3):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(iters):
+        _flush.zero_()  # evict L2 (126 MB) between timed runs
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2] * 1e-3
+
+
+def gemm_rows(results, hbm, tf, tag):
+    shapes = []
+    for M in (8192, 2048, 256, 64, 8):
+        shapes += [(M, 6144, 4096, "qkv"), (M, 4096, 4096, "o"), (M, 24576, 4096, "gate_up"), (M, 4096, 12288, "down")]
+    shapes.append((256, 151936, 4096, "lm_head"))
+    for M, N, K, name in shapes:
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        t_mine = bench(lambda: gemm_tcgen05.gemm_nt(x, w, out=out))
+        t_lib = bench(lambda: torch.nn.functional.linear(x, w))
+        flops = 2.0 * M * N * K
+        bytes_ = 2.0 * (M * K + N * K + M * N)
+        ideal = max(flops / (tf * 1e12), bytes_ / (hbm * 1e9))
+        r = dict(kernel="gemm_bf16_tcgen05", shape=f"{name} M={M} N={N} K={K}", ms=t_mine * 1e3,
+                 tflops=flops / t_mine / 1e12, gbs=bytes_ / t_mine / 1e9, frac_of_roofline=ideal / t_mine,
+                 cublas_ms=t_lib * 1e3, vs_cublas=t_lib / t_mine, peaks=tag)
+        results.append(r)
+        print(f"gemm {r['shape']:<34} {r['ms']:8.3f} ms {r['tflops']:8.1f} TF/s  {r['gbs']:7.0f} GB/s  "
+              f"roofline {r['frac_of_roofline']:.2f} ({tag})  cuBLAS {r['cublas_ms']:.3f} ms  x{r['vs_cublas']:.2f}")
+        assert gemm_tcgen05.error_status() == 0
+
+
+def decode_rows(results, hbm, tf, tag):
+    nq, nkv, d, page = 32, 8, 128, 16
+    for B, ctx in ((256, 1280), (256, 1536), (64, 4096), (16, 8192), (1, 32768)):
+        nb = B * ((ctx + page - 1) // page) + 1
+        kc = torch.randn(nb, nkv, page, d, device="cuda", dtype=torch.bfloat16)
+        vc = torch.randn(nb, nkv, page, d, device="cuda", dtype=torch.bfloat16)
+        bt = (torch.randperm(nb - 1, device="cuda")[: B * ((ctx + page - 1) // page)] + 1).view(B, -1).to(torch.int32)
+        q = torch.randn(B, nq, d, device="cuda", dtype=torch.bfloat16)
+        sl = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+        out = torch.empty_like(q)
+        splits = ops.decode_splits(B, nkv, nq // nkv)
+        ws = ops.decode_workspace(B, nq, d, splits, "cuda")
+        t = bench(lambda: ops.paged_decode_attention(q, kc, vc, bt, sl, 1 / math.sqrt(d), splits=splits, workspace=ws, out=out))
+        bytes_ = 2.0 * B * ctx * nkv * d * 2
+        r = dict(kernel="paged_decode_kernel", shape=f"B={B} ctx={ctx} nq={nq} nkv={nkv} splits={splits}", ms=t * 1e3,
+                 gbs=bytes_ / t / 1e9, frac_of_roofline=bytes_ / t / 1e9 / hbm, peaks=tag)
+        results.append(r)
+        print(f"decode-attn {r['shape']:<44} {r['ms']:8.3f} ms {r['gbs']:7.0f} GB/s  {r['frac_of_roofline']:.2f} of {tag} HBM")
+
+
+def prefill_rows(results, hbm, tf, tag):
+    nq, nkv, d, page = 32, 8, 128, 16
+    for B, L in ((8, 1024), (16, 1024), (2, 4096), (1, 8192)):
+        nb = B * (L // page) + 1
+        kc = torch.randn(nb, nkv, page, d, device="cuda", dtype=torch.bfloat16)
+        vc = torch.randn(nb, nkv, page, d, device="cuda", dtype=torch.bfloat16)
+        bt = (torch.arange(B * (L // page), device="cuda") + 1).view(B, -1).to(torch.int32)
+        q = torch.randn(B * L, nq, d, device="cuda", dtype=torch.bfloat16)
+        cu = (torch.arange(B + 1, device="cuda") * L).to(torch.int32)
+        kl = torch.full((B,), L, device="cuda", dtype=torch.int32)
+        out = torch.empty_like(q)
+        t = bench(lambda: ops.paged_prefill_attention(q, kc, vc, bt, cu, kl, L, 1 / math.sqrt(d), out=out))
+        flops = 4.0 * B * nq * d * L * L / 2
+        r = dict(kernel="paged_prefill_kernel", shape=f"B={B} L={L}", ms=t * 1e3, tflops=flops / t / 1e12,
+                 frac_of_roofline=flops / t / 1e12 / tf, peaks=tag)
+        results.append(r)
+        print(f"prefill-attn {r['shape']:<20} {r['ms']:8.3f} ms {r['tflops']:8.1f} TF/s  {r['frac_of_roofline']:.2f} of {tag} bf16 peak")
+
+
+def small_rows(results, hbm, tf, tag):
+    H = 4096
+    for T in (256, 8192):
+        x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+        res = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+        w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty_like(x)
+        t = bench(lambda: ops.rmsnorm(x, w, 1e-6, residual=res, out=out))
+        b = T * H * 2 * 4.0
+        results.append(dict(kernel="add_rmsnorm", shape=f"T={T} H={H}", ms=t * 1e3, gbs=b / t / 1e9,
+                            frac_of_roofline=b / t / 1e9 / hbm, peaks=tag))
+        print(f"add_rmsnorm T={T:<6} {t*1e3:8.3f} ms {b/t/1e9:7.0f} GB/s")
+        gu = torch.randn(T, 2 * 12288, device="cuda", dtype=torch.bfloat16)
+        o2 = torch.empty(T, 12288, device="cuda", dtype=torch.bfloat16)
+        t = bench(lambda: ops.silu_and_mul(gu, out=o2))
+        b = T * 12288 * 2 * 3.0
+        results.append(dict(kernel="silu_and_mul", shape=f"T={T} I=12288", ms=t * 1e3, gbs=b / t / 1e9,
+                            frac_of_roofline=b / t / 1e9 / hbm, peaks=tag))
+        print(f"silu_and_mul T={T:<6} {t*1e3:8.3f} ms {b/t/1e9:7.0f} GB/s")
+    logits = torch.randn(256, 151936, device="cuda", dtype=torch.bfloat16)
+    t = bench(lambda: ops.sample(logits))
+    b = logits.numel() * 2.0
+    results.append(dict(kernel="sample_greedy", shape="B=256 V=151936", ms=t * 1e3, gbs=b / t / 1e9,
+                        frac_of_roofline=b / t / 1e9 / hbm, peaks=tag))
+    print(f"sample greedy B=256 {t*1e3:8.3f} ms {b/t/1e9:7.0f} GB/s")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", default="gemm,decode,prefill,small")
+    ap.add_argument("--json", default="")
+    a = ap.parse_args()
+    hbm, tf, tag = peaks()
+    results = []
+    for w in a.what.split(","):
+        {"gemm": gemm_rows, "decode": decode_rows, "prefill": prefill_rows, "small": small_rows}[w](results, hbm, tf, tag)
+    if a.json:
+        with open(a.json, "w") as f:
+            json.dump(results, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,35 @@
+"""tcgen05 GEMM against an fp32 PyTorch reference (and cuBLAS bf16 for scale)."""
+import pytest
+import torch
+
+from xllm_b200.ops import gemm_tcgen05 as g
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (1, 4096, 4096), (7, 1024, 512),
+                                   (256, 6144, 4096), (300, 4096, 12288), (1000, 24576, 4096),
+                                   (129, 264, 136), (4096, 4096, 4096), (64, 151936, 1024)])
+@pytest.mark.parametrize("tile_n", [0, 256, 64])
+def test_gemm_matches_fp32(M, N, K, tile_n):
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05)
+    y = g.gemm_nt(x, w, tile_n=tile_n)
+    assert g.error_status() == 0
+    ref = x.float() @ w.float().T
+    err = (y.float() - ref).abs()
+    tol = 2e-2 + 1e-2 * ref.abs()
+    assert bool((err <= tol).all()), f"max err {err.max().item()} at M={M} N={N} K={K}"
+
+
+def test_gemm_bias_and_strided_rows():
+    torch.manual_seed(0)
+    big = torch.randn(200, 1024 + 64, device="cuda", dtype=torch.bfloat16)
+    x = big[:, :1024]  # row stride 1088
+    w = torch.randn(512, 1024, device="cuda", dtype=torch.bfloat16) * 0.05
+    b = torch.randn(512, device="cuda", dtype=torch.bfloat16)
+    y = g.gemm_nt(x, w, bias=b)
+    ref = x.float() @ w.float().T + b.float()
+    assert torch.allclose(y.float(), ref, atol=3e-2, rtol=2e-2)
+    assert g.error_status() == 0

@@ -1,0 +1,392 @@
+// bf16 GEMM on the 5th-generation tensor cores:  C[M,N] = A[M,K] · W[N,K]^T (+ bias[N])
+//
+// This is the engine's dense linear (qkv / o / gate_up / down / lm_head / router); the reference
+// sends all of these to cuBLAS through torch::nn::functional::linear
+// (xllm/core/kernels/cuda/matmul.cpp:21-25).
+//
+// Structure (one persistent CTA per SM, 192 threads, warp-specialised):
+//   warp 0   TMA producer : cp.async.bulk.tensor 2-D tiles of A (128 x 64) and W (BN x 64) into a
+//                           STAGES-deep shared-memory ring, 128-byte swizzle, completion on mbarriers
+//   warp 1   MMA issuer   : one elected thread issues tcgen05.mma (cta_group::1, kind::f16,
+//                           M = 128, N = BN, K = 16) straight from shared-memory descriptors into a
+//                           TMEM accumulator; tcgen05.commit releases ring slots and publishes the
+//                           finished accumulator
+//   warps 2-5 epilogue    : tcgen05.ld the fp32 accumulator (each warp owns its 32 TMEM lanes),
+//                           add bias, convert to bf16, 16-byte global stores
+// The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue of tile i overlaps
+// the main loop of tile i+1.  Both operands are K-major, which is exactly the layout of activations
+// [tokens, in] and of nn.Linear weights [out, in]: no transposes anywhere.
+//
+// Every mbarrier wait is bounded (clock64 budget); on expiry the kernel raises an error word in
+// global memory, all roles leave their loops, TMEM is released and the kernel returns normally.
+#include "common.cuh"
+#include <cuda.h>
+
+namespace xllm {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr long long kWaitBudgetCycles = 4000000000LL;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the budget ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  int spins = 0;
+  while (true) {
+    if (mbar_try(bar, parity)) return true;
+    if ((++spins & 63) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitBudgetCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024
+// bytes apart (the layout TMA writes with CU_TENSOR_MAP_SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                         // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                         // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;                         // SWIZZLE_128B
+  return d;
+}
+
+// kind::f16 instruction descriptor: D = f32, A = B = bf16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int A_BYTES = kBM * kBK * 2;
+  static constexpr int B_BYTES = BN * kBK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFF + (2 * STAGES + 4) * 8 + 16 + 1024;  // + alignment slack
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                         bf16* __restrict__ C, const bf16* __restrict__ bias, int M, int N, int K,
+                         int64_t ldc, int* __restrict__ err_word) {
+  using S = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzled tiles need 1024-byte aligned bases
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + S::BAR_OFF;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::BAR_OFF + (2 * STAGES + 4) * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + BN - 1) / BN;
+  const int total_tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // TMEM allocation is a warp-wide operation
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                 "r"(2 * BN));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int armed = 0;  // loads issued so far (for the drain on an aborted run)
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * kBM, n0 = (tile / m_tiles) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(full_bar(stage), S::STAGE_BYTES);
+          const uint32_t a_dst = sbase + stage * S::STAGE_BYTES;
+          tma_load_2d(a_dst, &tma_a, kb * kBK, m0, full_bar(stage));
+          tma_load_2d(a_dst + S::A_BYTES, &tma_b, kb * kBK, n0, full_bar(stage));
+          ++armed;
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // give the copies that are still in flight a bounded chance to land before the CTA exits
+        const int pending = armed < STAGES ? armed : STAGES;
+        for (int i = 0; i < pending; ++i) {
+          int s = stage - 1 - i;
+          uint32_t ph = phase;
+          if (s < 0) { s += STAGES; ph ^= 1; }
+          const long long t0 = clock64();
+          while (!mbar_try(full_bar(s), ph) && clock64() - t0 < 20000000LL) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ MMA issuer
+      constexpr uint32_t idesc = umma_idesc_bf16(BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int t = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+        const int acc = t & 1;
+        const uint32_t use = (uint32_t)(t >> 1);
+        if (!mbar_wait(tempty_bar(acc), (use & 1) ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = sbase + stage * S::STAGE_BYTES;
+          const uint64_t adesc = umma_smem_desc(a_addr);
+          const uint64_t bdesc = umma_smem_desc(a_addr + S::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            // +32 bytes (2 x 16-byte units) along K inside the swizzled row per UMMA_K = 16
+            umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+          }
+          umma_commit(empty_bar(stage));  // slot reusable once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(tfull_bar(acc));  // accumulator complete
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------- epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    bool ok = true;
+    int t = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+      const int m0 = (tile % m_tiles) * kBM, n0 = (tile / m_tiles) * BN;
+      const int acc = t & 1;
+      const uint32_t use = (uint32_t)(t >> 1);
+      if (!mbar_wait(tfull_bar(acc), use & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      bf16* crow = C + (int64_t)row * ldc + n0;
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < M) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int col = col0 + j * 8;
+            if (col < N) {
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j * 8 + e]);
+              if (bias != nullptr) {
+                float bv[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(bias + col), bv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] += bv[e];
+              }
+              *reinterpret_cast<bf16x8*>(crow + c * 32 + j * 8) = pack8(f);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+  }
+  pdl_launch_dependents();
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && err_word != nullptr) atomicExch(err_word, 1);
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN));
+  }
+}
+
+// ------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] (row stride ld elements), box = [box_rows, 64 cols], 128B swizzle.
+static bool make_tmap(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+static int* g_err_word[64] = {};
+
+template <int BN, int STAGES>
+static int launch_gemm(const void* a, const void* w, void* c, const void* bias, int M, int N, int K, int64_t lda,
+                       int64_t ldw, int64_t ldc, int max_ctas, cudaStream_t s) {
+  using S = GemmSmem<BN, STAGES>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static bool attr_done[64] = {};
+  if (!attr_done[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    attr_done[dev & 63] = true;
+  }
+  if (g_err_word[dev & 63] == nullptr) {
+    // one 4-byte status word per device, allocated on first use (not during stream capture)
+    if (cudaMalloc(&g_err_word[dev & 63], sizeof(int)) != cudaSuccess) return (int)cudaErrorMemoryAllocation;
+    cudaMemset(g_err_word[dev & 63], 0, sizeof(int));
+  }
+  CUtensorMap ta, tb;
+  if (!make_tmap(&ta, a, M, K, lda, kBM) || !make_tmap(&tb, w, N, K, ldw, BN)) return (int)cudaErrorInvalidValue;
+  const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+  int grid = tiles < max_ctas ? tiles : max_ctas;
+  gemm_bf16_tcgen05_kernel<BN, STAGES><<<grid, 192, S::TOTAL, s>>>(ta, tb, (bf16*)c, (const bf16*)bias, M, N, K, ldc,
+                                                                 g_err_word[dev & 63]);
+  return XLLM_LAUNCH_CHECK();
+}
+
+}  // namespace xllm
+
+// C[M,N] = A[M,K] · W[N,K]^T (+ bias).  bf16 row-major, leading dimensions in elements.
+// Requirements: K % 8 == 0, N % 8 == 0, lda/ldw/ldc % 8 == 0, 16-byte aligned base pointers.
+// tile_n: 0 = choose from the problem shape; else one of 32, 64, 128, 256.
+XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* bias, int M, int N, int K,
+                            int64_t lda, int64_t ldw, int64_t ldc, int tile_n, void* stream) {
+  using namespace xllm;
+  if (M == 0 || N == 0) return 0;
+  if (K % 8 || N % 8 || lda % 8 || ldw % 8 || ldc % 8) return (int)cudaErrorInvalidValue;
+  if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15) return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int sms = 148;
+  if (tile_n == 0) {
+    const int mt = (M + kBM - 1) / kBM;
+    // widest tile that still gives every SM work; narrow tiles for skinny (decode) problems
+    tile_n = 256;
+    while (tile_n > 32 && mt * ((N + tile_n - 1) / tile_n) < sms) tile_n >>= 1;
+  }
+  switch (tile_n) {
+    case 256: return launch_gemm<256, 4>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
+    case 128: return launch_gemm<128, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
+    case 64: return launch_gemm<64, 8>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
+    case 32: return launch_gemm<32, 10>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
+    default: return (int)cudaErrorInvalidValue;
+  }
+}
+
+// 0 = no bounded wait has expired on this device since the last call; the word is cleared.
+XLLM_API int xllm_gemm_error_status() {
+  using namespace xllm;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (g_err_word[dev & 63] == nullptr) return 0;
+  int v = 0;
+  cudaMemcpy(&v, g_err_word[dev & 63], sizeof(int), cudaMemcpyDeviceToHost);
+  if (v != 0) cudaMemset(g_err_word[dev & 63], 0, sizeof(int));
+  return v;
+}
