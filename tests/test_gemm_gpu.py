@@ -10,12 +10,12 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (1, 4096, 4096), (7, 1024, 512),
                                    (256, 6144, 4096), (300, 4096, 12288), (1000, 24576, 4096),
                                    (129, 264, 136), (4096, 4096, 4096), (64, 151936, 1024)])
-@pytest.mark.parametrize("tile_n", [0, 256, 64])
-def test_gemm_matches_fp32(M, N, K, tile_n):
+@pytest.mark.parametrize("tile_n,pair", [(0, -1), (256, 0), (64, 0), (256, 1), (128, 1), (64, 1)])
+def test_gemm_matches_fp32(M, N, K, tile_n, pair):
     torch.manual_seed(M + N + K)
     x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
     w = (torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05)
-    y = g.gemm_nt(x, w, tile_n=tile_n)
+    y = g.gemm_nt(x, w, tile_n=tile_n, pair=pair)
     assert g.error_status() == 0
     ref = x.float() @ w.float().T
     err = (y.float() - ref).abs()

@@ -12,7 +12,8 @@
 //                           TMEM accumulator; tcgen05.commit releases ring slots and publishes the
 //                           finished accumulator
 //   warps 2-5 epilogue    : tcgen05.ld the fp32 accumulator (each warp owns its 32 TMEM lanes),
-//                           add bias, convert to bf16, 16-byte global stores
+//                           add bias, convert to bf16, stage 32 x 64 chunks in swizzled shared
+//                           memory and write them out with TMA stores (full 128-byte rows)
 // The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue of tile i overlaps
 // the main loop of tile i+1.  Both operands are K-major, which is exactly the layout of activations
 // [tokens, in] and of nn.Linear weights [out, in]: no transposes anywhere.
@@ -21,6 +22,7 @@
 // global memory, all roles leave their loops, TMEM is released and the kernel returns normally.
 #include "common.cuh"
 #include <cuda.h>
+#include <cstdlib>
 
 namespace xllm {
 
@@ -119,20 +121,83 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+constexpr int kEpiCols = 64;                       // columns per epilogue chunk (128 bytes of bf16)
+constexpr int kEpiBufBytes = 32 * kEpiCols * 2;    // one warp's chunk: 32 rows x 64 cols
+constexpr int kEpiBytes = 4 * 2 * kEpiBufBytes;    // 4 warps x 2 buffers
+
+// Drain one warp's 32 x BN slice of a TMEM accumulator: tcgen05.ld -> (+bias) -> bf16 -> 128-byte
+// swizzled shared memory -> TMA store (full 128-byte rows, clipped at the M / N edges by the
+// tensor map).  Two chunk buffers per warp keep a store in flight while the next chunk is built.
+template <int BN>
+__device__ __forceinline__ void epilogue_slice(uint32_t taddr, const CUtensorMap* tmap_c, uint32_t warp_stage,
+                                               int row0, int n0, const bf16* __restrict__ bias, int N, int lane,
+                                               int& buf) {
+#pragma unroll 1
+  for (int c = 0; c < BN / kEpiCols; ++c) {
+    uint32_t r[64];
+    tmem_ld32(taddr + c * kEpiCols, r);
+    tmem_ld32(taddr + c * kEpiCols + 32, r + 32);
+    tmem_ld_wait();
+    if (lane == 0) bulk_wait_read<1>();  // the store that last read this buffer has finished reading
+    __syncwarp();
+    const uint32_t sb = warp_stage + buf * kEpiBufBytes;
+    const int col0 = n0 + c * kEpiCols;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j * 8 + e]);
+      if (bias != nullptr && col0 + j * 8 < N) {
+        float bv[8];
+        unpack8(*reinterpret_cast<const bf16x8*>(bias + col0 + j * 8), bv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] += bv[e];
+      }
+      const bf16x8 v = pack8(f);
+      const uint4 u = *reinterpret_cast<const uint4*>(&v);
+      const uint32_t dst = sb + lane * 128 + ((j ^ (lane & 7)) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w)
+                   : "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tmap_c, sb, col0, row0);
+      bulk_commit();
+    }
+    buf ^= 1;
+  }
+}
+
 template <int BN, int STAGES>
 struct GemmSmem {
   static constexpr int A_BYTES = kBM * kBK * 2;
   static constexpr int B_BYTES = BN * kBK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+  static constexpr int EPI_OFF = STAGES * STAGE_BYTES;  // 1024-byte aligned: stages are multiples of 1 KB
+  static constexpr int BAR_OFF = EPI_OFF + kEpiBytes;
   static constexpr int TOTAL = BAR_OFF + (2 * STAGES + 4) * 8 + 16 + 1024;  // + alignment slack
+  static_assert(TOTAL <= 232448, "exceeds the 227 KB of shared memory per CTA");
 };
 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                         bf16* __restrict__ C, const bf16* __restrict__ bias, int M, int N, int K,
-                         int64_t ldc, int* __restrict__ err_word) {
+                         const __grid_constant__ CUtensorMap tma_c, const bf16* __restrict__ bias, int M, int N,
+                         int K, int* __restrict__ err_word) {
   using S = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles need 1024-byte aligned bases
@@ -240,45 +305,20 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     // -------------------------------------------------------------------- epilogue (warps 2..5)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     bool ok = true;
-    int t = 0;
+    int t = 0, ebuf = 0;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
       const int m0 = (tile % m_tiles) * kBM, n0 = (tile / m_tiles) * BN;
       const int acc = t & 1;
       const uint32_t use = (uint32_t)(t >> 1);
       if (!mbar_wait(tfull_bar(acc), use & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
-      bf16* crow = C + (int64_t)row * ldc + n0;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (row < M) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int col = col0 + j * 8;
-            if (col < N) {
-              float f[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j * 8 + e]);
-              if (bias != nullptr) {
-                float bv[8];
-                unpack8(*reinterpret_cast<const bf16x8*>(bias + col), bv);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] += bv[e];
-              }
-              *reinterpret_cast<bf16x8*>(crow + c * 32 + j * 8) = pack8(f);
-            }
-          }
-        }
-      }
+      epilogue_slice<BN>(taddr, &tma_c, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, bias, N, lane, ebuf);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
     }
+    if (lane == 0) bulk_wait_all();  // every output store has completed before the CTA exits
   }
   pdl_launch_dependents();
   tc_fence_before();
@@ -287,6 +327,231 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN));
+  }
+}
+
+// ===================================================================================== 2-CTA
+// cta_group::2 variant: a cluster of two CTAs (a pair of SMs) computes one 256 x BN tile.  Each
+// CTA loads its own 128 rows of A and its own BN/2 rows of W, so every operand byte is fetched
+// once per pair and a ring stage costs 16 KB + BN*64 bytes per CTA — deeper pipelines than the
+// 1-CTA kernel at the same tile area.  The leader CTA (cluster rank 0) issues
+// tcgen05.mma.cta_group::2 (M = 256); the accumulator rows 0-127 live in the leader's TMEM and
+// rows 128-255 in the peer's.  Loads of both CTAs complete on the leader's "full" barrier;
+// tcgen05.commit signals the "empty" / "accumulator full" barriers of both CTAs at once; the
+// epilogue warps of both CTAs arrive on the leader's "accumulator empty" barrier.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  int spins = 0;
+  while (true) {
+    if (mbar_try_cluster(bar, parity)) return true;
+    if ((++spins & 63) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitBudgetCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+// TMA tile load issued by either CTA of the pair; completion bytes are counted on the barrier of
+// the pair's leader (bit 24 of a shared-window address selects the CTA inside the pair).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t bar) {
+  const uint32_t leader_bar = bar & 0xFEFFFFFFu;
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive on the barrier at this shared-memory offset in both CTAs of the pair
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"(mask)
+      : "memory");
+}
+__host__ __device__ constexpr uint32_t umma_idesc_bf16_m256(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+template <int BN, int STAGES>
+struct GemmSmem2 {
+  static constexpr int A_BYTES = kBM * kBK * 2;         // this CTA's 128 rows of A
+  static constexpr int B_BYTES = (BN / 2) * kBK * 2;    // this CTA's half of the W tile
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int EPI_OFF = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFF = EPI_OFF + kEpiBytes;
+  static constexpr int TOTAL = BAR_OFF + (2 * STAGES + 4) * 8 + 16 + 1024;
+  static_assert(TOTAL <= 232448, "exceeds the 227 KB of shared memory per CTA");
+};
+
+template <int BN, int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                              const __grid_constant__ CUtensorMap tma_c, const bf16* __restrict__ bias, int M,
+                              int N, int K, int* __restrict__ err_word) {
+  using S = GemmSmem2<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + S::BAR_OFF;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::BAR_OFF + (2 * STAGES + 4) * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM), n_tiles = (N + BN - 1) / BN;
+  const int total_tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 8);  // 4 epilogue warps in each CTA of the pair
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                 "r"(2 * BN));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anything can signal them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ TMA producer (both CTAs)
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+        const int m0 = (tile % m_tiles) * (2 * kBM) + (int)rank * kBM;
+        const int n0 = (tile / m_tiles) * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_cluster(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
+          if (leader) mbar_expect_tx(full_bar(stage), 2 * S::STAGE_BYTES);
+          const uint32_t a_dst = sbase + stage * S::STAGE_BYTES;
+          tma_load_2d_pair(a_dst, &tma_a, kb * kBK, m0, full_bar(stage));
+          tma_load_2d_pair(a_dst + S::A_BYTES, &tma_b, kb * kBK, n0, full_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 20000000LL) {}  // bounded grace period for copies still in flight
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      // ------------------------------------------------------------------ MMA issuer (leader only)
+      constexpr uint32_t idesc = umma_idesc_bf16_m256(BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int t = 0;
+      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++t) {
+        const int acc = t & 1;
+        const uint32_t use = (uint32_t)(t >> 1);
+        if (!mbar_wait_cluster(tempty_bar(acc), (use & 1) ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_cluster(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = sbase + stage * S::STAGE_BYTES;
+          const uint64_t adesc = umma_smem_desc(a_addr);
+          const uint64_t bdesc = umma_smem_desc(a_addr + S::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k)
+            umma_bf16_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+          umma_commit_pair(empty_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit_pair(tfull_bar(acc));
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------- epilogue (both CTAs)
+    const int q = warp & 3;
+    const uint32_t leader_tempty0 = map_to_cta(tempty_bar(0), 0);
+    bool ok = true;
+    int t = 0, ebuf = 0;
+    for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++t) {
+      const int m0 = (tile % m_tiles) * (2 * kBM) + (int)rank * kBM, n0 = (tile / m_tiles) * BN;
+      const int acc = t & 1;
+      const uint32_t use = (uint32_t)(t >> 1);
+      if (!mbar_wait_cluster(tfull_bar(acc), use & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      epilogue_slice<BN>(taddr, &tma_c, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, bias, N, lane, ebuf);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(leader_tempty0 + 8u * acc);
+    }
+    if (lane == 0) bulk_wait_all();
+  }
+  pdl_launch_dependents();
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && err_word != nullptr) atomicExch(err_word, 1);
+  cluster_sync_all();  // neither CTA leaves while the other may still touch its barriers / smem
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN));
   }
 }
 
@@ -309,7 +574,8 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D bf16 row-major [rows, cols] (row stride ld elements), box = [box_rows, 64 cols], 128B swizzle.
-static bool make_tmap(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+static bool make_tmap(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows,
+                      bool promote = true) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return false;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -317,7 +583,8 @@ static bool make_tmap(CUtensorMap* map, const void* ptr, int64_t rows, int64_t c
   cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  promote ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -342,12 +609,42 @@ static int launch_gemm(const void* a, const void* w, void* c, const void* bias, 
     if (cudaMalloc(&g_err_word[dev & 63], sizeof(int)) != cudaSuccess) return (int)cudaErrorMemoryAllocation;
     cudaMemset(g_err_word[dev & 63], 0, sizeof(int));
   }
-  CUtensorMap ta, tb;
-  if (!make_tmap(&ta, a, M, K, lda, kBM) || !make_tmap(&tb, w, N, K, ldw, BN)) return (int)cudaErrorInvalidValue;
+  CUtensorMap ta, tb, tc;
+  if (!make_tmap(&ta, a, M, K, lda, kBM) || !make_tmap(&tb, w, N, K, ldw, BN) ||
+      !make_tmap(&tc, c, M, N, ldc, 32, false))
+    return (int)cudaErrorInvalidValue;
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
   int grid = tiles < max_ctas ? tiles : max_ctas;
-  gemm_bf16_tcgen05_kernel<BN, STAGES><<<grid, 192, S::TOTAL, s>>>(ta, tb, (bf16*)c, (const bf16*)bias, M, N, K, ldc,
+  gemm_bf16_tcgen05_kernel<BN, STAGES><<<grid, 192, S::TOTAL, s>>>(ta, tb, tc, (const bf16*)bias, M, N, K,
                                                                  g_err_word[dev & 63]);
+  return XLLM_LAUNCH_CHECK();
+}
+
+template <int BN, int STAGES>
+static int launch_gemm_pair(const void* a, const void* w, void* c, const void* bias, int M, int N, int K, int64_t lda,
+                            int64_t ldw, int64_t ldc, int max_ctas, cudaStream_t s) {
+  using S = GemmSmem2<BN, STAGES>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static bool attr_done[64] = {};
+  if (!attr_done[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_pair_kernel<BN, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    attr_done[dev & 63] = true;
+  }
+  if (g_err_word[dev & 63] == nullptr) {
+    if (cudaMalloc(&g_err_word[dev & 63], sizeof(int)) != cudaSuccess) return (int)cudaErrorMemoryAllocation;
+    cudaMemset(g_err_word[dev & 63], 0, sizeof(int));
+  }
+  CUtensorMap ta, tb, tc;
+  if (!make_tmap(&ta, a, M, K, lda, kBM) || !make_tmap(&tb, w, N, K, ldw, BN / 2) ||
+      !make_tmap(&tc, c, M, N, ldc, 32, false))
+    return (int)cudaErrorInvalidValue;
+  const int tiles = ((M + 2 * kBM - 1) / (2 * kBM)) * ((N + BN - 1) / BN);
+  int pairs = tiles < max_ctas / 2 ? tiles : max_ctas / 2;
+  gemm_bf16_tcgen05_pair_kernel<BN, STAGES><<<2 * pairs, 192, S::TOTAL, s>>>(ta, tb, tc, (const bf16*)bias, M, N, K,
+                                                                            g_err_word[dev & 63]);
   return XLLM_LAUNCH_CHECK();
 }
 
@@ -355,26 +652,44 @@ static int launch_gemm(const void* a, const void* w, void* c, const void* bias, 
 
 // C[M,N] = A[M,K] · W[N,K]^T (+ bias).  bf16 row-major, leading dimensions in elements.
 // Requirements: K % 8 == 0, N % 8 == 0, lda/ldw/ldc % 8 == 0, 16-byte aligned base pointers.
-// tile_n: 0 = choose from the problem shape; else one of 32, 64, 128, 256.
+// tile_n: 0 = choose from the problem shape; else one of 64, 128, 256.
+// pair: -1 = choose; 0 = one CTA per 128 x tile_n tile; 1 = a CTA pair (cta_group::2) per 256 x tile_n tile.
 XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* bias, int M, int N, int K,
-                            int64_t lda, int64_t ldw, int64_t ldc, int tile_n, void* stream) {
+                            int64_t lda, int64_t ldw, int64_t ldc, int tile_n, int pair, void* stream) {
   using namespace xllm;
   if (M == 0 || N == 0) return 0;
   if (K % 8 || N % 8 || lda % 8 || ldw % 8 || ldc % 8) return (int)cudaErrorInvalidValue;
   if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15) return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
-  const int sms = 148;
+  static int sms = 0;
+  if (sms == 0) {
+    // XLLM_GEMM_MAX_CTAS caps the persistent grid (for experiments and for leaving SMs to a
+    // concurrent communication kernel); default: every SM of a B200
+    const char* e = getenv("XLLM_GEMM_MAX_CTAS");
+    sms = e ? atoi(e) : 148;
+    if (sms < 2 || sms > 148) sms = 148;
+  }
+  if (pair < 0) pair = M > kBM ? 1 : 0;
   if (tile_n == 0) {
-    const int mt = (M + kBM - 1) / kBM;
-    // widest tile that still gives every SM work; narrow tiles for skinny (decode) problems
+    const int rows = pair ? 2 * kBM : kBM;
+    const int units = pair ? sms / 2 : sms;
+    const int mt = (M + rows - 1) / rows;
+    // widest tile that still gives every SM (pair) work; narrow tiles for skinny (decode) problems
     tile_n = 256;
-    while (tile_n > 32 && mt * ((N + tile_n - 1) / tile_n) < sms) tile_n >>= 1;
+    while (tile_n > 64 && mt * ((N + tile_n - 1) / tile_n) < units) tile_n >>= 1;
+  }
+  if (pair) {
+    switch (tile_n) {
+      case 256: return launch_gemm_pair<256, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
+      case 128: return launch_gemm_pair<128, 8>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
+      case 64: return launch_gemm_pair<64, 9>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
+      default: return (int)cudaErrorInvalidValue;
+    }
   }
   switch (tile_n) {
     case 256: return launch_gemm<256, 4>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
     case 128: return launch_gemm<128, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
     case 64: return launch_gemm<64, 8>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
-    case 32: return launch_gemm<32, 10>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
     default: return (int)cudaErrorInvalidValue;
   }
 }

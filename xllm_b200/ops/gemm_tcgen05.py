@@ -8,7 +8,7 @@ import torch
 from . import _lib
 from ._lib import I, L, P, check, ptr, stream
 
-_lib.register_signature("xllm_gemm_bf16", [P, P, P, P, I, I, I, L, L, L, I, P])
+_lib.register_signature("xllm_gemm_bf16", [P, P, P, P, I, I, I, L, L, L, I, I, P])
 _lib.register_signature("xllm_gemm_error_status", [], I)
 
 
@@ -24,7 +24,7 @@ def supported(x, w) -> bool:
     return True
 
 
-def gemm_nt(x, w, bias=None, out=None, tile_n: int = 0):
+def gemm_nt(x, w, bias=None, out=None, tile_n: int = 0, pair: int = -1):
     """y[..., N] = x[..., K] @ w[N, K]^T (+ bias)."""
     K = x.shape[-1]
     N = w.shape[0]
@@ -40,7 +40,7 @@ def gemm_nt(x, w, bias=None, out=None, tile_n: int = 0):
         assert bias.dtype == torch.bfloat16 and bias.is_contiguous()
     from . import _count
     check(_lib.load().xllm_gemm_bf16(ptr(x2), ptr(w), ptr(o2), ptr(bias), M, N, K, x2.stride(0), w.stride(0),
-                                     o2.stride(0), tile_n, stream()), "gemm_bf16")
+                                     o2.stride(0), tile_n, pair, stream()), "gemm_bf16")
     _count()
     return out.reshape(*x.shape[:-1], N)
 
