@@ -33,3 +33,18 @@ def test_gemm_bias_and_strided_rows():
     ref = x.float() @ w.float().T + b.float()
     assert torch.allclose(y.float(), ref, atol=3e-2, rtol=2e-2)
     assert g.error_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 4096, 12288), (256, 6144, 4096), (300, 512, 192), (2048, 24576, 4096)])
+@pytest.mark.parametrize("tile_n,pair", [(0, -1), (64, 0), (256, 0), (64, 1), (128, 1), (256, 1)])
+def test_gemm_packed_weight(M, N, K, tile_n, pair):
+    torch.manual_seed(1)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    pw = g.pack_weight(w)
+    assert torch.equal(g.unpack_weight(pw), w)
+    y = g.gemm_nt(x, pw, tile_n=tile_n, pair=pair)
+    ref = x.float() @ w.float().T
+    err = (y.float() - ref).abs()
+    assert bool((err <= 2e-2 + 1e-2 * ref.abs()).all()), err.max().item()
+    assert g.error_status() == 0

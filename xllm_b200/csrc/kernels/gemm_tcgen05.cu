@@ -197,7 +197,7 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          const __grid_constant__ CUtensorMap tma_c, const bf16* __restrict__ bias, int M, int N,
-                         int K, int* __restrict__ err_word) {
+                         int K, int a_box_rows, int w_packed, int* __restrict__ err_word) {
   using S = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles need 1024-byte aligned bases
@@ -250,10 +250,20 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         const int m0 = (tile % m_tiles) * kBM, n0 = (tile / m_tiles) * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(full_bar(stage), S::STAGE_BYTES);
+          // for M < 128 the A box only covers the rows that exist; the rest of the 128-row operand
+          // is whatever the slot held before and only feeds output rows that are never stored
+          mbar_expect_tx(full_bar(stage), S::B_BYTES + a_box_rows * kBK * 2);
           const uint32_t a_dst = sbase + stage * S::STAGE_BYTES;
           tma_load_2d(a_dst, &tma_a, kb * kBK, m0, full_bar(stage));
-          tma_load_2d(a_dst + S::A_BYTES, &tma_b, kb * kBK, n0, full_bar(stage));
+          if (!w_packed) {
+            tma_load_2d(a_dst + S::A_BYTES, &tma_b, kb * kBK, n0, full_bar(stage));
+          } else {
+            // tile-packed weights: every 64 x 64 block is one contiguous 8 KB run
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(a_dst + S::A_BYTES + j * 8192, &tma_b, 0, ((n0 / 64 + j) * k_blocks + kb) * 64,
+                          full_bar(stage));
+          }
           ++armed;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -427,7 +437,7 @@ template <int BN, int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                               const __grid_constant__ CUtensorMap tma_c, const bf16* __restrict__ bias, int M,
-                              int N, int K, int* __restrict__ err_word) {
+                              int N, int K, int w_packed, int* __restrict__ err_word) {
   using S = GemmSmem2<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -486,7 +496,17 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
           if (leader) mbar_expect_tx(full_bar(stage), 2 * S::STAGE_BYTES);
           const uint32_t a_dst = sbase + stage * S::STAGE_BYTES;
           tma_load_2d_pair(a_dst, &tma_a, kb * kBK, m0, full_bar(stage));
-          tma_load_2d_pair(a_dst + S::A_BYTES, &tma_b, kb * kBK, n0, full_bar(stage));
+          if (!w_packed) {
+            tma_load_2d_pair(a_dst + S::A_BYTES, &tma_b, kb * kBK, n0, full_bar(stage));
+          } else {
+            constexpr int ROWS = BN / 2 < 64 ? BN / 2 : 64;  // rows per packed-block load
+#pragma unroll
+            for (int j = 0; j < (BN / 2) / ROWS; ++j) {
+              const int n = n0 + j * ROWS;
+              tma_load_2d_pair(a_dst + S::A_BYTES + j * ROWS * 128, &tma_b, 0,
+                               ((n / 64) * k_blocks + kb) * 64 + (n % 64), full_bar(stage));
+            }
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -593,7 +613,7 @@ static int* g_err_word[64] = {};
 
 template <int BN, int STAGES>
 static int launch_gemm(const void* a, const void* w, void* c, const void* bias, int M, int N, int K, int64_t lda,
-                       int64_t ldw, int64_t ldc, int max_ctas, cudaStream_t s) {
+                       int64_t ldw, int64_t ldc, int max_ctas, int w_packed, cudaStream_t s) {
   using S = GemmSmem<BN, STAGES>;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -610,19 +630,20 @@ static int launch_gemm(const void* a, const void* w, void* c, const void* bias, 
     cudaMemset(g_err_word[dev & 63], 0, sizeof(int));
   }
   CUtensorMap ta, tb, tc;
-  if (!make_tmap(&ta, a, M, K, lda, kBM) || !make_tmap(&tb, w, N, K, ldw, BN) ||
-      !make_tmap(&tc, c, M, N, ldc, 32, false))
+  const int a_box = M >= kBM ? kBM : ((M + 7) & ~7);
+  const bool okb = w_packed ? make_tmap(&tb, w, (int64_t)N * (K / 64), 64, 64, 64) : make_tmap(&tb, w, N, K, ldw, BN);
+  if (!make_tmap(&ta, a, M, K, lda, a_box) || !okb || !make_tmap(&tc, c, M, N, ldc, 32, false))
     return (int)cudaErrorInvalidValue;
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
   int grid = tiles < max_ctas ? tiles : max_ctas;
-  gemm_bf16_tcgen05_kernel<BN, STAGES><<<grid, 192, S::TOTAL, s>>>(ta, tb, tc, (const bf16*)bias, M, N, K,
-                                                                 g_err_word[dev & 63]);
+  gemm_bf16_tcgen05_kernel<BN, STAGES><<<grid, 192, S::TOTAL, s>>>(ta, tb, tc, (const bf16*)bias, M, N, K, a_box,
+                                                                 w_packed, g_err_word[dev & 63]);
   return XLLM_LAUNCH_CHECK();
 }
 
 template <int BN, int STAGES>
 static int launch_gemm_pair(const void* a, const void* w, void* c, const void* bias, int M, int N, int K, int64_t lda,
-                            int64_t ldw, int64_t ldc, int max_ctas, cudaStream_t s) {
+                            int64_t ldw, int64_t ldc, int max_ctas, int w_packed, cudaStream_t s) {
   using S = GemmSmem2<BN, STAGES>;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -638,13 +659,14 @@ static int launch_gemm_pair(const void* a, const void* w, void* c, const void* b
     cudaMemset(g_err_word[dev & 63], 0, sizeof(int));
   }
   CUtensorMap ta, tb, tc;
-  if (!make_tmap(&ta, a, M, K, lda, kBM) || !make_tmap(&tb, w, N, K, ldw, BN / 2) ||
-      !make_tmap(&tc, c, M, N, ldc, 32, false))
+  const bool okb = w_packed ? make_tmap(&tb, w, (int64_t)N * (K / 64), 64, 64, BN / 2 < 64 ? BN / 2 : 64)
+                            : make_tmap(&tb, w, N, K, ldw, BN / 2);
+  if (!make_tmap(&ta, a, M, K, lda, kBM) || !okb || !make_tmap(&tc, c, M, N, ldc, 32, false))
     return (int)cudaErrorInvalidValue;
   const int tiles = ((M + 2 * kBM - 1) / (2 * kBM)) * ((N + BN - 1) / BN);
   int pairs = tiles < max_ctas / 2 ? tiles : max_ctas / 2;
   gemm_bf16_tcgen05_pair_kernel<BN, STAGES><<<2 * pairs, 192, S::TOTAL, s>>>(ta, tb, tc, (const bf16*)bias, M, N, K,
-                                                                            g_err_word[dev & 63]);
+                                                                            w_packed, g_err_word[dev & 63]);
   return XLLM_LAUNCH_CHECK();
 }
 
@@ -654,11 +676,16 @@ static int launch_gemm_pair(const void* a, const void* w, void* c, const void* b
 // Requirements: K % 8 == 0, N % 8 == 0, lda/ldw/ldc % 8 == 0, 16-byte aligned base pointers.
 // tile_n: 0 = choose from the problem shape; else one of 64, 128, 256.
 // pair: -1 = choose; 0 = one CTA per 128 x tile_n tile; 1 = a CTA pair (cta_group::2) per 256 x tile_n tile.
+// w_packed: W is stored tile-packed as [N/64][K/64][64][64] (see xllm_pack_weight_bf16); needs
+// N % 64 == 0 and K % 64 == 0.  Each 64 x 64 block is then one contiguous 8 KB run, which is what
+// lets a weight-streaming (small M) GEMM pull HBM at full rate.
 XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* bias, int M, int N, int K,
-                            int64_t lda, int64_t ldw, int64_t ldc, int tile_n, int pair, void* stream) {
+                            int64_t lda, int64_t ldw, int64_t ldc, int tile_n, int pair, int w_packed,
+                            void* stream) {
   using namespace xllm;
   if (M == 0 || N == 0) return 0;
   if (K % 8 || N % 8 || lda % 8 || ldw % 8 || ldc % 8) return (int)cudaErrorInvalidValue;
+  if (w_packed && (N % 64 || K % 64)) return (int)cudaErrorInvalidValue;
   if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15) return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   static int sms = 0;
@@ -669,29 +696,68 @@ XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* b
     sms = e ? atoi(e) : 148;
     if (sms < 2 || sms > 148) sms = 148;
   }
-  if (pair < 0) pair = M > kBM ? 1 : 0;
-  if (tile_n == 0) {
-    const int rows = pair ? 2 * kBM : kBM;
-    const int units = pair ? sms / 2 : sms;
-    const int mt = (M + rows - 1) / rows;
-    // widest tile that still gives every SM (pair) work; narrow tiles for skinny (decode) problems
-    tile_n = 256;
-    while (tile_n > 64 && mt * ((N + tile_n - 1) / tile_n) < units) tile_n >>= 1;
+  if (pair < 0 || tile_n == 0) {
+    // Cost model: a tile costs max(operand bytes its SM must pull from L2 at ~85 GB/s per SM,
+    // tensor-core time of its MMAs); a launch costs that times the number of waves.
+    double best = 1e30;
+    int bp = 0, bt = 256;
+    for (int p = 0; p < 2; ++p) {
+      if (pair >= 0 && p != pair) continue;
+      if (p == 1 && M <= kBM) continue;
+      for (int tn = 64; tn <= 256; tn <<= 1) {
+        if (tile_n != 0 && tn != tile_n) continue;
+        const int rows = p ? 2 * kBM : kBM, units = p ? sms / 2 : sms;
+        const long tiles = (long)((M + rows - 1) / rows) * ((N + tn - 1) / tn);
+        const long waves = (tiles + units - 1) / units;
+        const double a_rows = M < kBM ? (double)((M + 7) & ~7) : (double)kBM;
+        const double b_rows = p ? tn / 2 : tn;
+        const double t_in = (a_rows + b_rows) * K * 2.0 / 85e9;
+        const double t_mma = (K / 16.0) * (tn / 2.0) / 1.6e9;  // 128 x tn x 16 per SM: tn/2 cycles
+        const double t_epi = 128.0 * tn * 2.0 / 200e9;
+        const double cost = waves * ((t_in > t_mma ? t_in : t_mma) + 0.3 * t_epi) + t_epi;
+        if (cost < best) { best = cost; bp = p; bt = tn; }
+      }
+    }
+    pair = bp;
+    tile_n = bt;
   }
   if (pair) {
     switch (tile_n) {
-      case 256: return launch_gemm_pair<256, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
-      case 128: return launch_gemm_pair<128, 8>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
-      case 64: return launch_gemm_pair<64, 9>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
+      case 256: return launch_gemm_pair<256, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s);
+      case 128: return launch_gemm_pair<128, 8>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s);
+      case 64: return launch_gemm_pair<64, 9>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s);
       default: return (int)cudaErrorInvalidValue;
     }
   }
   switch (tile_n) {
-    case 256: return launch_gemm<256, 4>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
-    case 128: return launch_gemm<128, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
-    case 64: return launch_gemm<64, 8>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, s);
+    case 256: return launch_gemm<256, 4>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s);
+    case 128: return launch_gemm<128, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s);
+    case 64: return launch_gemm<64, 8>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s);
     default: return (int)cudaErrorInvalidValue;
   }
+}
+
+namespace xllm {
+// dst[(n/64), (k/64), n%64, k%64] = src[n, k]; one thread moves 16 bytes
+__global__ void pack_weight_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, int N, int K, int64_t ld) {
+  const int kc = K >> 3;  // 16-byte chunks per source row
+  const int64_t total = (int64_t)N * kc;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t n = i / kc;
+    const int c = (int)(i - n * kc);
+    const int kb = c >> 3, cc = c & 7;
+    const int64_t d = (((n >> 6) * (K >> 6) + kb) * 64 + (n & 63)) * 8 + cc;
+    dst[d] = src[n * (ld >> 3) + c];
+  }
+}
+}  // namespace xllm
+
+// Re-lay a row-major bf16 weight [N, K] (row stride ld) into the tile-packed form.  dst != src.
+XLLM_API int xllm_pack_weight_bf16(void* dst, const void* src, int N, int K, int64_t ld, void* stream) {
+  using namespace xllm;
+  if (N % 64 || K % 64 || ld % 8 || dst == src) return (int)cudaErrorInvalidValue;
+  pack_weight_kernel<<<148 * 8, 256, 0, (cudaStream_t)stream>>>((uint4*)dst, (const uint4*)src, N, K, ld);
+  return XLLM_LAUNCH_CHECK();
 }
 
 // 0 = no bounded wait has expired on this device since the last call; the word is cleared.
