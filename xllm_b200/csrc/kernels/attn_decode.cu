@@ -314,3 +314,70 @@ XLLM_API int xllm_attn_merge(void* out, const void* o_part, const void* lse_part
       (bf16*)out, (const float*)o_part, (const float*)lse_part, splits, d);
   return XLLM_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant (declared in no_alloc.h, which states who needs it and the contract).
+// The split-KV partials live in this file-scope array instead of a caller-provided workspace.
+#include "no_alloc.h"
+#include <cstdio>
+
+namespace xllm {
+static __device__ __align__(256) unsigned char g_noalloc_scratch[XLLM_NO_ALLOC_SCRATCH_BYTES];
+// Device address of the array, per device.  In host code `g_noalloc_scratch` is only a handle of
+// the symbol — passing it to a kernel would hand the GPU a host address — so the address is
+// resolved once per device with cudaGetSymbolAddress and cached here.
+static float* g_noalloc_ptr[64] = {};
+static thread_local char g_noalloc_msg[192] = "";
+}  // namespace xllm
+
+XLLM_API const char* xllm_no_alloc_last_error(void) { return xllm::g_noalloc_msg; }
+
+XLLM_API int xllm_paged_decode_attn_noalloc(void* out, const void* q, int64_t q_stride, const void* k_cache,
+                                            const void* v_cache, const void* block_table, int bt_stride,
+                                            const void* seq_lens, int batch, int nq, int nkv, int d,
+                                            int page_size, float scale, int splits, void* stream) {
+  using namespace xllm;
+  g_noalloc_msg[0] = 0;
+  if (batch == 0) return 0;
+  if (nkv <= 0 || nq % nkv != 0 || page_size % 16 != 0 || splits < 1) return (int)cudaErrorInvalidValue;
+  const long long need = splits > 1 ? (long long)batch * nq * splits * (d + 1) * 4 : 0;
+  if (need > (long long)XLLM_NO_ALLOC_SCRATCH_BYTES) {
+    snprintf(g_noalloc_msg, sizeof(g_noalloc_msg),
+             "decode attention needs %lld bytes of split-KV scratch (batch %d x heads %d x splits %d), the "
+             "built-in array holds %u; lower `splits` or the batch",
+             need, batch, nq, splits, (unsigned)XLLM_NO_ALLOC_SCRATCH_BYTES);
+    return XLLM_NO_ALLOC_TOO_LARGE;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "no current CUDA device (or device index >= 64)");
+    return XLLM_NO_ALLOC_SETUP_FAILED;
+  }
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // set-up, once per device, with that device current
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return XLLM_NO_ALLOC_SETUP_FAILED;
+    }
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  DecodeParams p;
+  p.q = (const bf16*)q; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
+  p.block_table = (const int32_t*)block_table; p.seq_lens = (const int32_t*)seq_lens;
+  p.out = (bf16*)out; p.q_stride = q_stride; p.bt_stride = bt_stride; p.nq = nq; p.nkv = nkv;
+  p.group = nq / nkv; p.page_size = page_size; p.splits = splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.o_part = splits > 1 ? g_noalloc_ptr[dev] : nullptr;
+  p.lse_part = p.o_part ? p.o_part + (int64_t)batch * nq * splits * d : nullptr;
+  cudaStream_t s = (cudaStream_t)stream;
+  int rc;
+  if (d == 128) rc = launch_decode<128, 3>(p, batch, s);
+  else if (d == 64) rc = launch_decode<64, 4>(p, batch, s);
+  else if (d == 256) rc = launch_decode<256, 2>(p, batch, s);
+  else return (int)cudaErrorInvalidValue;
+  if (rc != 0 || splits == 1) return rc;
+  attn_merge_kernel<<<batch * nq, d < 128 ? d : 128, 0, s>>>(p.out, p.o_part, p.lse_part, splits, d);
+  return XLLM_LAUNCH_CHECK();
+}
