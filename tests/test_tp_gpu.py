@@ -1,0 +1,42 @@
+"""Tensor parallelism on 2+ GPUs: fused all-reduce + RMSNorm kernel and a TP engine run.
+
+Each test spawns one process per GPU with torchrun (rendezvous on 127.0.0.1) and is skipped when
+fewer than two GPUs are visible.
+"""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(script, nproc, extra_env=None, timeout=300):
+    env = dict(os.environ)
+    env.update(extra_env or {})
+    env["PYTHONPATH"] = ROOT + os.pathsep + env.get("PYTHONPATH", "")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", "29571", os.path.join(ROOT, "tests", script)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return r.stdout
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("multimem", ["1", "0"])
+def test_fused_allreduce_norm(multimem):
+    out = _run("mp_tp_allreduce_norm.py", min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2, {"XLLM_TP_MULTIMEM": multimem})
+    assert "ALLREDUCE_NORM_OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_tp_engine_matches_single_gpu():
+    out = _run("mp_tp_engine.py", 2)
+    assert "TP_ENGINE_OK" in out

@@ -89,6 +89,10 @@ class LLMEngine:
                 self.dtype = torch.float32
         else:
             self.dtype = _DTYPES[cfg.dtype]
+        # ---- fused tensor-parallel communicator (symmetric memory), before the model is built
+        if self.ps.tp_size > 1 and self.device.type == "cuda" and self.ps.comm is None:
+            from ..parallel import symm
+            symm.attach(self.ps, max(cfg.max_tokens_per_batch, cfg.max_seqs_per_batch), self.args.hidden_size)
         # ---- model
         t0 = time.time()
         if model is not None:

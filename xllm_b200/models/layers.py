@@ -145,6 +145,13 @@ class Linear(Module):
         bias = self.bias
         if self.parallel == "row" and self.ps.tp_rank != 0:
             bias = None  # added once, by rank 0, before the reduction
+        if self.parallel == "row" and self.reduce:
+            comm = self.ps.comm
+            if comm is not None and x.is_cuda:
+                # the partial result goes to the symmetric buffer; the cross-rank sum is fused
+                # into the add+RMSNorm that follows (TpComm.allreduce_norm)
+                T = x.shape[0]
+                return ops.linear(x, self.weight, bias, out=comm.partial_buffer(T))
         y = ops.linear(x, self.weight, bias)
         if self.parallel == "row" and self.reduce:
             y = self.ps.all_reduce(y)
@@ -220,6 +227,11 @@ class VocabEmbedding(Module):
         self.add_param("weight", self.weight, {"weight": lw})
 
     def forward(self, ids):
+        comm = self.ps.comm
+        if self.ps.tp_size > 1 and comm is not None and self.weight.is_cuda:
+            T = ids.shape[0]
+            ops.embedding(ids, self.weight, self.start, out=comm.partial_buffer(T))
+            return comm.allreduce(T)
         y = ops.embedding(ids, self.weight, self.start)
         if self.ps.tp_size > 1:
             y = self.ps.all_reduce(y)

@@ -26,6 +26,9 @@ class DecoderLayer(Module):
                                    DenseMLP(args.hidden_size, args.intermediate_size, args.hidden_act, dtype, device, ps))
 
     def forward(self, x, residual, positions, meta, k_cache, v_cache):
+        comm = self.self_attn.ps.comm
+        if comm is not None and x.is_cuda:
+            return self._forward_tp_fused(comm, x, residual, positions, meta, k_cache, v_cache)
         # `residual` holds the running sum; None on the first layer (x is the embedding itself)
         if residual is None:
             residual = x
@@ -35,6 +38,25 @@ class DecoderLayer(Module):
         h = self.self_attn(h, positions, meta, k_cache, v_cache)
         h = self.post_attention_layernorm(h, residual=residual)
         h = self.mlp(h)
+        return h, residual
+
+    def _forward_tp_fused(self, comm, x, residual, positions, meta, k_cache, v_cache):
+        """Tensor-parallel path with the reductions fused into the norms: row-parallel GEMMs leave
+        their partial sums in the symmetric buffer, `allreduce_norm` sums them across ranks, adds the
+        residual and normalises.  The residual stream is sharded by token rows: each rank keeps (and
+        updates) only the rows it reduces."""
+        T = x.shape[0]
+        eps = self.input_layernorm.eps
+        if residual is None:
+            b, e, S = comm.shard(T)
+            residual = torch.zeros((S, x.shape[1]), dtype=x.dtype, device=x.device)
+            residual[: e - b].copy_(x[b:e])
+            h = self.input_layernorm(x)
+        else:
+            h = comm.allreduce_norm(T, residual, self.input_layernorm.weight, eps)
+        self.self_attn(h, positions, meta, k_cache, v_cache)  # partial -> comm.x
+        h = comm.allreduce_norm(T, residual, self.post_attention_layernorm.weight, eps)
+        h = self.mlp(h)                                       # partial -> comm.x
         return h, residual
 
     __call__ = forward
@@ -82,6 +104,9 @@ class DenseCausalLM(Module):
         residual = None
         for layer, (kc, vc) in zip(self.layers, kv_caches):
             x, residual = layer(x, residual, positions, meta, kc, vc)
+        comm = self.ps.comm
+        if comm is not None and x.is_cuda:
+            return comm.allreduce_norm(x.shape[0], residual, self.norm.weight, self.norm.eps)
         return self.norm(x, residual=residual)
 
     def logits(self, hidden_rows):
