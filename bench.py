@@ -256,8 +256,13 @@ def run(args):
         }
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        # Every collective of this process finished behind the barrier that closed the last timed
+        # region, so nothing is in flight.  Leave without tearing the process group down: destroying
+        # NCCL communicators that CUDA graphs still reference has been seen to block at exit.
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
