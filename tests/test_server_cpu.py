@@ -1,0 +1,119 @@
+"""HTTP service end to end on CPU with the tiny model: completions (plain + SSE), chat with a
+tokenizer and chat template, admin routes, health, metrics, disconnect handling."""
+import http.client
+import json
+import threading
+import time
+
+import pytest
+import torch
+
+from xllm_b200 import _rt
+from xllm_b200.api.server import ApiServer
+from xllm_b200.engine.llm_engine import EngineConfig, LLMEngine
+from xllm_b200.utils.tokenizer import TokenizerWrapper
+
+
+def _tokenizer(tmp_path):
+    from tokenizers import Regex, Tokenizer, decoders, models, pre_tokenizers, trainers
+    tok = Tokenizer(models.BPE())
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+    tok.decoder = decoders.ByteLevel()
+    trainer = trainers.BpeTrainer(vocab_size=400, special_tokens=["<|im_start|>", "<|im_end|>", "<|endoftext|>"],
+                                  initial_alphabet=pre_tokenizers.ByteLevel.alphabet())
+    tok.train_from_iterator(["hello world this is a tiny corpus for the server test " * 5, "user assistant system\n"], trainer)
+    p = tmp_path / "tokenizer.json"
+    tok.save(str(p))
+    impl = _rt.BpeTokenizer()
+    impl.load_hf_file(str(p))
+    return TokenizerWrapper(impl, "", {}, "qwen3")
+
+
+@pytest.fixture()
+def server(tmp_path):
+    eng = LLMEngine(EngineConfig(model="tiny", device="cpu", dtype="float32", num_blocks=128, enable_graph=False,
+                                 max_seqs_per_batch=8, max_tokens_per_batch=256))
+    srv = ApiServer(eng, _tokenizer(tmp_path), model_name="tiny", host="127.0.0.1", port=0,
+                    reasoning_parser="qwen3", tool_call_parser="qwen25")
+    t = threading.Thread(target=srv.serve_forever, args=(10,), daemon=True)
+    t.start()
+    yield srv
+    srv.shutdown()
+    t.join(timeout=5)
+
+
+def _post(port, path, body, stream=False):
+    c = http.client.HTTPConnection("127.0.0.1", port, timeout=60)
+    c.request("POST", path, json.dumps(body), {"Content-Type": "application/json"})
+    r = c.getresponse()
+    data = r.read().decode()
+    c.close()
+    return r.status, data
+
+
+def test_completions_plain_and_stream(server):
+    st, data = _post(server.port, "/v1/completions", {"prompt": [5, 6, 7, 8, 9], "max_tokens": 6, "temperature": 0,
+                                                      "ignore_eos": True})
+    assert st == 200
+    obj = json.loads(data)
+    assert obj["object"] == "text_completion" and obj["usage"]["completion_tokens"] == 6
+    assert obj["choices"][0]["finish_reason"] == "length"
+    text = obj["choices"][0]["text"]
+    st, data = _post(server.port, "/v1/completions", {"prompt": [5, 6, 7, 8, 9], "max_tokens": 6, "temperature": 0,
+                                                      "ignore_eos": True, "stream": True,
+                                                      "stream_options": {"include_usage": True}})
+    assert st == 200
+    events = [json.loads(l[6:]) for l in data.split("\n") if l.startswith("data: ") and l != "data: [DONE]"]
+    assert data.rstrip().endswith("data: [DONE]")
+    assert "".join(e["choices"][0]["text"] for e in events if e["choices"]) == text
+    assert events[-1]["usage"]["completion_tokens"] == 6
+
+
+def test_chat_models_health_metrics_admin(server):
+    st, data = _post(server.port, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hello world"}],
+                                                           "max_tokens": 5, "temperature": 0, "ignore_eos": True})
+    assert st == 200
+    obj = json.loads(data)
+    assert obj["object"] == "chat.completion" and obj["choices"][0]["message"]["role"] == "assistant"
+    assert obj["usage"]["prompt_tokens"] > 5
+    st, data = _post(server.port, "/v1/messages", {"messages": [{"role": "user", "content": "hello"}], "system": "s",
+                                                   "max_tokens": 4, "temperature": 0, "ignore_eos": True})
+    assert st == 200 and json.loads(data)["type"] == "message" and json.loads(data)["stop_reason"] == "max_tokens"
+    c = http.client.HTTPConnection("127.0.0.1", server.port, timeout=10)
+    c.request("GET", "/v1/models")
+    assert json.loads(c.getresponse().read())["data"][0]["id"] == "tiny"
+    c.request("GET", "/health")
+    r = c.getresponse()
+    assert r.status == 200 and json.loads(r.read())["status"] == "ok"
+    c.request("GET", "/metrics")
+    m = c.getresponse().read().decode()
+    assert "num_generated_tokens_total" in m and "time_to_first_token_latency_milliseconds_bucket" in m
+    c.close()
+    assert _post(server.port, "/pause", {"mode": "KEEP"})[0] == 200
+    assert _post(server.port, "/v1/completions", {"prompt": [1, 2, 3], "max_tokens": 2})[0] == 503
+    assert _post(server.port, "/resume", {})[0] == 200
+    assert _post(server.port, "/v1/completions", {"prompt": [1, 2, 3], "max_tokens": 2, "ignore_eos": True})[0] == 200
+    assert _post(server.port, "/v1/nope", {})[0] == 404
+    st, data = _post(server.port, "/v1/embeddings", {"input": ["hello world", "tiny corpus"]})
+    assert st == 200 and len(json.loads(data)["data"]) == 2 and len(json.loads(data)["data"][0]["embedding"]) == 256
+    server.healthy, server.unhealthy_reason = False, "worker 1 did not answer"
+    c = http.client.HTTPConnection("127.0.0.1", server.port, timeout=10)
+    c.request("GET", "/health")
+    r = c.getresponse()
+    assert r.status == 503 and "worker 1" in r.read().decode()
+    c.close()
+
+
+def test_client_disconnect_aborts_request(server):
+    import socket
+    s = socket.create_connection(("127.0.0.1", server.port))
+    body = json.dumps({"prompt": list(range(3, 40)), "max_tokens": 2000, "ignore_eos": True, "stream": True})
+    s.sendall(f"POST /v1/completions HTTP/1.1\r\nHost: x\r\nContent-Length: {len(body)}\r\n\r\n{body}".encode())
+    s.recv(200)
+    s.close()
+    for _ in range(400):
+        if not server.engine.has_unfinished() and not server.calls:
+            break
+        time.sleep(0.02)
+    assert not server.calls and not server.engine.has_unfinished()
+    assert server.engine.stats()["kv_utilization"] == 0.0

@@ -1,0 +1,434 @@
+"""OpenAI-compatible HTTP service on top of the engine.
+
+Route parity with the reference's APIService / XllmServer (xllm/server/xllm_server.cpp:39-60,
+xllm/api_service/*): `/v1/completions`, `/v1/chat/completions` (SSE streaming and plain),
+`/v1/models`, `/v1/embeddings`, `/v1/messages` (Anthropic), `/health`, `/metrics` and the admin
+endpoints `/sleep`, `/wakeup`, `/pause`, `/resume`, `/start_profile`, `/stop_profile`.
+Tool-call and reasoning parsing of chat responses uses the C++ stream parsers; request ids,
+`max_concurrent_requests` rate limiting and client-disconnect aborts follow
+chat_service_impl.cpp:702-860 / continuous_scheduler.cpp:964-1018.
+
+Transport is the C++ epoll server (`_rt.HttpServer`); this module is one loop: take new HTTP
+requests, step the engine, turn output events into response chunks.
+"""
+from __future__ import annotations
+
+import json
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+from .. import _rt
+from ..engine.llm_engine import LLMEngine
+
+
+@dataclass
+class _Call:
+    http_id: int
+    request_id: str
+    kind: str                      # "completion" | "chat" | "anthropic"
+    stream: bool
+    model: str
+    created: int
+    n: int = 1
+    prompt_tokens: int = 0
+    decoders: List[object] = field(default_factory=list)
+    texts: List[str] = field(default_factory=list)
+    token_ids: List[List[int]] = field(default_factory=list)
+    finish: List[Optional[str]] = field(default_factory=list)
+    logprobs: List[List[float]] = field(default_factory=list)
+    reasoning: List[object] = field(default_factory=list)
+    reasoning_text: List[str] = field(default_factory=list)
+    tools: List[object] = field(default_factory=list)
+    tool_calls: List[List[dict]] = field(default_factory=list)
+    want_logprobs: bool = False
+    include_usage: bool = False
+    echo_text: str = ""
+    t_arrival: float = 0.0
+    t_first: float = 0.0
+    started: bool = False
+
+
+class ApiServer:
+    def __init__(self, engine: LLMEngine, tokenizer, model_name: str = "xllm_b200", host: str = "", port: int = 8010,
+                 max_concurrent_requests: int = 200, tool_call_parser: str = "", reasoning_parser: str = ""):
+        self.engine = engine
+        self.tok = tokenizer
+        self.model_name = model_name
+        self.http = _rt.HttpServer()
+        self.port = self.http.start(host, port)
+        self.max_concurrent = max_concurrent_requests
+        self.tool_kind = tool_call_parser
+        self.reason_kind = reasoning_parser
+        self.calls: Dict[str, _Call] = {}
+        self.healthy = True
+        self.unhealthy_reason = ""
+        self.profiler = None
+        self._stop = False
+
+    # ------------------------------------------------------------------ plumbing
+    def _json(self, http_id, status, obj):
+        self.http.respond(http_id, status, "application/json", json.dumps(obj, ensure_ascii=False))
+
+    def _error(self, http_id, status, message, typ="invalid_request_error"):
+        _rt.metric_counter_add("server_request_total_fail")
+        self._json(http_id, status, {"error": {"message": message, "type": typ, "code": status}})
+
+    def shutdown(self):
+        self._stop = True
+
+    def serve_forever(self, idle_poll_ms: int = 50):
+        while not self._stop:
+            self.run_once(idle_poll_ms)
+        self.http.stop()
+
+    def run_once(self, idle_poll_ms: int = 0):
+        busy = self.engine.has_unfinished()
+        for req in self.http.poll(0 if busy else idle_poll_ms):
+            try:
+                self._route(req)
+            except Exception as e:  # a malformed request must never take the loop down
+                self._error(req.id, 500, f"{type(e).__name__}: {e}", "internal_error")
+        # client went away: abort its request (frees its KV blocks at once)
+        for rid, call in list(self.calls.items()):
+            if self.http.is_disconnected(call.http_id):
+                self.engine.abort(rid)
+                self.calls.pop(rid, None)
+        if self.engine.has_unfinished():
+            for ev in self.engine.step():
+                self._on_event(ev)
+        s = self.engine.scheduler
+        _rt.metric_gauge_set("num_running_requests", float(s.num_running))
+        _rt.metric_gauge_set("num_waiting_requests", float(s.num_waiting))
+        _rt.metric_gauge_set("kv_cache_utilization", float(s.kv_utilization(0)))
+
+    # ------------------------------------------------------------------ routing
+    def _route(self, req):
+        path, method = req.path.rstrip("/") or "/", req.method
+        _rt.metric_counter_add("server_request_in_total")
+        if path == "/health":
+            if self.healthy:
+                return self._json(req.id, 200, {"status": "ok"})
+            return self._json(req.id, 503, {"status": "unhealthy", "reason": self.unhealthy_reason})
+        if path == "/metrics":
+            return self.http.respond(req.id, 200, "text/plain; version=0.0.4", _rt.metrics_text())
+        if path in ("/v1/models", "/models"):
+            return self._json(req.id, 200, {"object": "list", "data": [
+                {"id": self.model_name, "object": "model", "created": int(time.time()), "owned_by": "xllm_b200"}]})
+        if method != "POST":
+            return self._error(req.id, 405 if path.startswith("/v1") else 404, f"{method} {path} not supported")
+        body = {}
+        if req.body:
+            try:
+                body = json.loads(req.body)
+            except json.JSONDecodeError as e:
+                return self._error(req.id, 400, f"invalid JSON body: {e}")
+        if path == "/v1/completions":
+            return self._completion(req, body)
+        if path == "/v1/chat/completions":
+            return self._chat(req, body, "chat")
+        if path == "/v1/messages":
+            return self._chat(req, body, "anthropic")
+        if path == "/v1/embeddings":
+            return self._embeddings(req, body)
+        if path in ("/sleep", "/pause"):
+            self.engine.pause(str(body.get("mode", "KEEP")).upper())
+            return self._json(req.id, 200, {"status": "paused"})
+        if path in ("/wakeup", "/resume"):
+            self.engine.resume()
+            return self._json(req.id, 200, {"status": "running"})
+        if path == "/start_profile":
+            return self._profile(req, True, body)
+        if path == "/stop_profile":
+            return self._profile(req, False, body)
+        return self._error(req.id, 404, f"unknown route {path}")
+
+    def _profile(self, req, start, body):
+        import torch
+        if start:
+            if self.profiler is None:
+                acts = [torch.profiler.ProfilerActivity.CPU]
+                if torch.cuda.is_available():
+                    acts.append(torch.profiler.ProfilerActivity.CUDA)
+                self.profiler = torch.profiler.profile(activities=acts)
+                self.profiler.__enter__()
+            return self._json(req.id, 200, {"status": "profiling"})
+        path = ""
+        if self.profiler is not None:
+            self.profiler.__exit__(None, None, None)
+            path = f"{body.get('profile_dir', '.')}/xllm_rank{self.engine.ps.rank}_{int(time.time())}.pt.trace.json"
+            self.profiler.export_chrome_trace(path)
+            self.profiler = None
+        return self._json(req.id, 200, {"status": "stopped", "trace": path})
+
+    # ------------------------------------------------------------------ request intake
+    def _sampling(self, body, max_default=5120):
+        mt = body.get("max_completion_tokens") or body.get("max_tokens") or max_default
+        stop = body.get("stop")
+        if isinstance(stop, str):
+            stop = [stop]
+        lp = body.get("logprobs")
+        return dict(temperature=float(body.get("temperature", 1.0)), top_p=float(body.get("top_p", 1.0)),
+                    top_k=int(body.get("top_k", -1)), max_tokens=int(mt),
+                    frequency_penalty=float(body.get("frequency_penalty", 0.0)),
+                    presence_penalty=float(body.get("presence_penalty", 0.0)),
+                    repetition_penalty=float(body.get("repetition_penalty", 1.0)),
+                    ignore_eos=bool(body.get("ignore_eos", False)), seed=body.get("seed"),
+                    logprobs=bool(lp) if not isinstance(lp, int) else lp > 0,
+                    stop_token_ids=body.get("stop_token_ids")), (stop or [])
+
+    def _admit(self, req, call: _Call, prompt_ids, sampling, stops):
+        if self.max_concurrent and len(self.calls) >= self.max_concurrent:
+            return self._error(req.id, 429, "too many concurrent requests", "rate_limit_error")
+        if self.engine.scheduler.paused():
+            return self._error(req.id, 503, "the instance is paused", "unavailable")
+        n = call.n
+        call.prompt_tokens = len(prompt_ids)
+        call.t_arrival = time.time()
+        call.want_logprobs = sampling["logprobs"]
+        for _ in range(n):
+            call.decoders.append(self.tok.incremental_decoder(stops, True) if self.tok else None)
+            call.texts.append("")
+            call.token_ids.append([])
+            call.finish.append(None)
+            call.logprobs.append([])
+            call.reasoning.append(_rt.ReasoningParser(self.reason_kind) if self.reason_kind and call.kind != "completion" else None)
+            call.reasoning_text.append("")
+            call.tools.append(_rt.ToolCallParser(self.tool_kind) if self.tool_kind and call.kind != "completion" else None)
+            call.tool_calls.append([])
+        ok = self.engine.add_request(call.request_id, prompt_ids, n=n, stream=call.stream, **sampling)
+        if not ok:
+            return self._error(req.id, 400, "prompt is empty or longer than the model's context window")
+        self.calls[call.request_id] = call
+        _rt.metric_counter_add("server_request_total_ok", 0)
+
+    def _completion(self, req, body):
+        prompt = body.get("prompt", "")
+        if isinstance(prompt, list) and prompt and isinstance(prompt[0], int):
+            ids = list(prompt)
+            text = ""
+        else:
+            if isinstance(prompt, list):
+                prompt = prompt[0] if prompt else ""
+            if self.tok is None:
+                return self._error(req.id, 400, "this server has no tokenizer: send token ids as `prompt`")
+            ids, text = self.tok.encode(prompt), prompt
+        sampling, stops = self._sampling(body, 16)
+        rid = req.header("x-request-id") or f"cmpl-{uuid.uuid4().hex}"
+        call = _Call(req.id, rid, "completion", bool(body.get("stream")), body.get("model") or self.model_name,
+                     int(time.time()), n=int(body.get("n", 1)), echo_text=text if body.get("echo") else "",
+                     include_usage=bool((body.get("stream_options") or {}).get("include_usage")))
+        self._admit(req, call, ids, sampling, stops)
+
+    def _chat(self, req, body, kind):
+        if self.tok is None:
+            return self._error(req.id, 400, "chat needs a tokenizer with a chat template")
+        messages = list(body.get("messages") or [])
+        if kind == "anthropic" and body.get("system"):
+            sys_text = body["system"] if isinstance(body["system"], str) else "".join(p.get("text", "") for p in body["system"])
+            messages = [{"role": "system", "content": sys_text}] + messages
+        if not messages:
+            return self._error(req.id, 400, "`messages` must not be empty")
+        kwargs = dict(body.get("chat_template_kwargs") or {})
+        prompt = self.tok.apply_chat_template(messages, tools=body.get("tools"), add_generation_prompt=True,
+                                              enable_thinking=bool(kwargs.get("enable_thinking", True)))
+        ids = self.tok.encode(prompt)
+        sampling, stops = self._sampling(body)
+        rid = req.header("x-request-id") or (f"msg_{uuid.uuid4().hex}" if kind == "anthropic" else f"chatcmpl-{uuid.uuid4().hex}")
+        call = _Call(req.id, rid, kind, bool(body.get("stream")), body.get("model") or self.model_name,
+                     int(time.time()), n=int(body.get("n", 1)),
+                     include_usage=bool((body.get("stream_options") or {}).get("include_usage")))
+        self._admit(req, call, ids, sampling, stops)
+
+    def _embeddings(self, req, body):
+        inp = body.get("input", "")
+        items = inp if isinstance(inp, list) and not (inp and isinstance(inp[0], int)) else [inp]
+        from .embedding import embed_token_lists
+        ids = [self.tok.encode(x) if isinstance(x, str) else list(x) for x in items]
+        vecs = embed_token_lists(self.engine, ids)
+        data = [{"object": "embedding", "index": i, "embedding": v} for i, v in enumerate(vecs)]
+        n_tok = sum(len(x) for x in ids)
+        self._json(req.id, 200, {"object": "list", "data": data, "model": self.model_name,
+                                 "usage": {"prompt_tokens": n_tok, "total_tokens": n_tok}})
+
+    # ------------------------------------------------------------------ output events
+    def _sse(self, call, obj):
+        self.http.stream_send(call.http_id, "data: " + json.dumps(obj, ensure_ascii=False) + "\n\n")
+
+    def _chunk(self, call, i, delta=None, text=None, finish=None):
+        if call.kind == "completion":
+            return {"id": call.request_id, "object": "text_completion", "created": call.created, "model": call.model,
+                    "choices": [{"index": i, "text": text or "", "finish_reason": finish}]}
+        return {"id": call.request_id, "object": "chat.completion.chunk", "created": call.created, "model": call.model,
+                "choices": [{"index": i, "delta": delta or {}, "finish_reason": finish}]}
+
+    def _emit_text(self, call, i, piece):
+        """Route a piece of decoded text through the reasoning / tool-call parsers; stream it."""
+        if not piece:
+            return
+        reasoning_piece, content_piece = "", piece
+        if call.reasoning[i] is not None:
+            reasoning_piece, content_piece = call.reasoning[i].push(piece)
+        new_calls = []
+        if call.tools[i] is not None and content_piece:
+            content_piece, new_calls = call.tools[i].push(content_piece)
+        call.reasoning_text[i] += reasoning_piece
+        call.texts[i] += content_piece
+        for idx, name, args in new_calls:
+            while len(call.tool_calls[i]) <= idx:
+                call.tool_calls[i].append({"id": f"call_{uuid.uuid4().hex[:24]}", "type": "function",
+                                           "function": {"name": "", "arguments": ""}})
+            tc = call.tool_calls[i][idx]
+            if name:
+                tc["function"]["name"] = name
+            tc["function"]["arguments"] += args
+        if not call.stream:
+            return
+        if call.kind == "completion":
+            if content_piece:
+                self._sse(call, self._chunk(call, i, text=content_piece))
+        elif call.kind == "chat":
+            if reasoning_piece:
+                self._sse(call, self._chunk(call, i, delta={"reasoning_content": reasoning_piece}))
+            if content_piece:
+                self._sse(call, self._chunk(call, i, delta={"content": content_piece}))
+            for idx, name, args in new_calls:
+                d = {"index": idx, "function": {"arguments": args}}
+                if name:
+                    d.update(id=call.tool_calls[i][idx]["id"], type="function")
+                    d["function"]["name"] = name
+                self._sse(call, self._chunk(call, i, delta={"tool_calls": [d]}))
+        else:  # anthropic
+            if content_piece:
+                self.http.stream_send(call.http_id, "event: content_block_delta\ndata: " + json.dumps(
+                    {"type": "content_block_delta", "index": 0, "delta": {"type": "text_delta", "text": content_piece}}) + "\n\n")
+
+    def _start_stream(self, call):
+        call.started = True
+        self.http.stream_begin(call.http_id, 200, "text/event-stream")
+        if call.kind == "chat":
+            for i in range(call.n):
+                self._sse(call, self._chunk(call, i, delta={"role": "assistant", "content": ""}))
+        elif call.kind == "anthropic":
+            self.http.stream_send(call.http_id, "event: message_start\ndata: " + json.dumps(
+                {"type": "message_start", "message": {"id": call.request_id, "type": "message", "role": "assistant",
+                                                      "model": call.model, "content": [],
+                                                      "usage": {"input_tokens": call.prompt_tokens, "output_tokens": 0}}}) + "\n\n")
+            self.http.stream_send(call.http_id, "event: content_block_start\ndata: " + json.dumps(
+                {"type": "content_block_start", "index": 0, "content_block": {"type": "text", "text": ""}}) + "\n\n")
+        elif call.echo_text:
+            self._sse(call, self._chunk(call, 0, text=call.echo_text))
+
+    def _on_event(self, ev):
+        call = self.calls.get(ev.request_id)
+        if call is None:
+            return
+        i = ev.seq_index
+        now = time.time()
+        if call.stream and not call.started:
+            self._start_stream(call)
+        if ev.token >= 0:
+            if call.t_first == 0.0:
+                call.t_first = now
+                _rt.metric_histogram_observe("time_to_first_token_latency_milliseconds", (now - call.t_arrival) * 1e3)
+            call.token_ids[i].append(ev.token)
+            if ev.has_logprob:
+                call.logprobs[i].append(ev.logprob)
+            dec = call.decoders[i]
+            if dec is not None and call.finish[i] is None:
+                piece, stopped = dec.push(ev.token)
+                self._emit_text(call, i, piece)
+                if stopped:
+                    call.finish[i] = "stop"
+        if ev.finished and ev.finish_reason != "abort":
+            if call.decoders[i] is not None and call.finish[i] is None:
+                self._emit_text(call, i, call.decoders[i].flush())
+            for parser, is_reason in ((call.reasoning[i], True), (call.tools[i], False)):
+                if parser is not None and is_reason:
+                    r, c = parser.flush()
+                    call.reasoning_text[i] += r
+                    if c:
+                        if call.tools[i] is not None:
+                            c, _ = call.tools[i].push(c)
+                        call.texts[i] += c
+                        if call.stream and call.kind == "chat" and c:
+                            self._sse(call, self._chunk(call, i, delta={"content": c}))
+            if call.finish[i] is None:
+                call.finish[i] = ev.finish_reason or "stop"
+            if call.tool_calls[i] and call.finish[i] == "stop":
+                call.finish[i] = "tool_calls"
+            if call.stream and call.kind != "anthropic":
+                self._sse(call, self._chunk(call, i, delta={}, text="", finish=call.finish[i]))
+        if ev.request_finished:
+            self._finish_call(call, aborted=ev.finish_reason == "abort")
+
+    def _usage(self, call):
+        gen = sum(len(t) for t in call.token_ids)
+        return {"prompt_tokens": call.prompt_tokens, "completion_tokens": gen, "total_tokens": call.prompt_tokens + gen}
+
+    def _finish_call(self, call, aborted=False):
+        self.calls.pop(call.request_id, None)
+        now = time.time()
+        gen = sum(len(t) for t in call.token_ids)
+        _rt.metric_counter_add("server_request_total_ok" if not aborted else "server_request_total_fail")
+        _rt.metric_counter_add("num_generated_tokens_total", gen)
+        _rt.metric_counter_add("num_prompt_tokens_total", call.prompt_tokens)
+        _rt.metric_histogram_observe("end_2_end_latency_milliseconds", (now - call.t_arrival) * 1e3)
+        if gen > 1 and call.t_first:
+            _rt.metric_histogram_observe("inter_token_latency_milliseconds", (now - call.t_first) * 1e3 / (gen - 1))
+        usage = self._usage(call)
+        if call.stream:
+            if not call.started:
+                self._start_stream(call)
+            if call.kind == "anthropic":
+                s = self.http.stream_send
+                s(call.http_id, "event: content_block_stop\ndata: " + json.dumps({"type": "content_block_stop", "index": 0}) + "\n\n")
+                s(call.http_id, "event: message_delta\ndata: " + json.dumps(
+                    {"type": "message_delta", "delta": {"stop_reason": _anthropic_reason(call.finish[0])},
+                     "usage": {"output_tokens": usage["completion_tokens"]}}) + "\n\n")
+                s(call.http_id, "event: message_stop\ndata: " + json.dumps({"type": "message_stop"}) + "\n\n")
+            else:
+                if call.include_usage:
+                    obj = self._chunk(call, 0)
+                    obj["choices"] = []
+                    obj["usage"] = usage
+                    self._sse(call, obj)
+                self.http.stream_send(call.http_id, "data: [DONE]\n\n")
+            self.http.stream_end(call.http_id)
+            return
+        if call.kind == "completion":
+            choices = []
+            for i in range(call.n):
+                c = {"index": i, "text": call.echo_text + call.texts[i], "finish_reason": call.finish[i] or "stop"}
+                if call.want_logprobs:
+                    c["logprobs"] = {"token_logprobs": call.logprobs[i], "tokens": call.token_ids[i]}
+                if self.tok is None:
+                    c["token_ids"] = call.token_ids[i]
+                choices.append(c)
+            return self._json(call.http_id, 200, {"id": call.request_id, "object": "text_completion",
+                                                  "created": call.created, "model": call.model, "choices": choices,
+                                                  "usage": usage})
+        if call.kind == "anthropic":
+            return self._json(call.http_id, 200, {
+                "id": call.request_id, "type": "message", "role": "assistant", "model": call.model,
+                "content": [{"type": "text", "text": call.texts[0]}], "stop_reason": _anthropic_reason(call.finish[0]),
+                "usage": {"input_tokens": call.prompt_tokens, "output_tokens": usage["completion_tokens"]}})
+        choices = []
+        for i in range(call.n):
+            msg = {"role": "assistant", "content": call.texts[i]}
+            if call.reasoning_text[i]:
+                msg["reasoning_content"] = call.reasoning_text[i]
+            if call.tool_calls[i]:
+                msg["tool_calls"] = call.tool_calls[i]
+            c = {"index": i, "message": msg, "finish_reason": call.finish[i] or "stop"}
+            if call.want_logprobs:
+                c["logprobs"] = {"content": [{"token": self.tok.decode([t], False), "logprob": lp}
+                                             for t, lp in zip(call.token_ids[i], call.logprobs[i])]}
+            choices.append(c)
+        self._json(call.http_id, 200, {"id": call.request_id, "object": "chat.completion", "created": call.created,
+                                       "model": call.model, "choices": choices, "usage": usage})
+
+
+def _anthropic_reason(finish):
+    return {"length": "max_tokens", "tool_calls": "tool_use"}.get(finish or "stop", "end_turn")

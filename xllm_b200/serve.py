@@ -1,0 +1,91 @@
+"""`python -m xllm_b200.serve --model <dir> [flags]` — start the OpenAI-compatible server.
+
+Counterpart of the reference's `xllm` binary entry (xllm/xllm.cpp:585-625: parse flags, load the
+optional JSON config, validate, build options, create the master and the HTTP server) and of its
+`xllm serve` launcher (xllm/launch_server.py).  Flag names and defaults are the reference's; with
+`--nnodes N` the process joins an N-rank tensor-parallel job (one process per GPU; rank 0 hosts the
+HTTP server and broadcasts each step's new requests to the other ranks).
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+
+def build_engine_config(flags):
+    from .engine.llm_engine import EngineConfig
+    return EngineConfig(
+        model=flags.get("model") or "tiny", dtype="auto", device=("auto" if flags.get("devices") == "auto" else flags.get("devices")),
+        block_size=flags.get_int("block_size"), max_memory_utilization=flags.get_double("max_memory_utilization"),
+        max_cache_size=flags.get_int("max_cache_size"), max_seqs_per_batch=flags.get_int("max_seqs_per_batch"),
+        max_tokens_per_batch=flags.get_int("max_tokens_per_batch"), max_model_len=flags.get_int("max_model_len"),
+        enable_prefix_cache=flags.get_bool("enable_prefix_cache"),
+        enable_chunked_prefill=flags.get_bool("enable_chunked_prefill"),
+        max_tokens_per_chunk_for_prefill=flags.get_int("max_tokens_per_chunk_for_prefill"),
+        policy=flags.get("scheduler_policy"), priority_strategy=flags.get("priority_strategy"),
+        enable_schedule_overlap=flags.get_bool("enable_schedule_overlap"),
+        enable_graph=flags.get_bool("enable_cuda_graph"), random_weights=flags.get_bool("random_weights"),
+        dp_size=flags.get_int("dp_size"), ep_size=flags.get_int("ep_size"),
+        num_speculative_tokens=flags.get_int("num_speculative_tokens"), draft_model=flags.get("draft_model"))
+
+
+def main(argv=None):
+    from . import _rt
+    flags = _rt.FlagRegistry()
+    try:
+        flags.parse_args(list(sys.argv[1:] if argv is None else argv))
+    except ValueError as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 2
+    if flags.help_requested():
+        print(flags.help())
+        return 0
+    problems = flags.validate()
+    if problems:
+        for p in problems:
+            print(f"error: {p}", file=sys.stderr)
+        return 2
+    if flags.get_bool("enable_dump_config_json"):
+        with open(flags.get("dump_config_json_file"), "w") as f:
+            f.write(flags.to_json())
+    os.environ.setdefault("XLLM_GEMM", "auto" if flags.get("gemm_backend") == "tcgen05" else flags.get("gemm_backend"))
+    os.environ.setdefault("XLLM_TP_COMM", flags.get("tp_comm"))
+    from .api.server import ApiServer
+    from .engine.llm_engine import LLMEngine
+    from .parallel.state import init_parallel
+    from .utils.tokenizer import load_tokenizer
+
+    nnodes = flags.get_int("nnodes")
+    ps = None
+    if nnodes > 1:
+        addr = flags.get("master_node_addr")
+        host, _, port = addr.partition(":")
+        os.environ.setdefault("MASTER_ADDR", host or "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", port or "19888")
+        os.environ.setdefault("WORLD_SIZE", str(nnodes))
+        os.environ.setdefault("RANK", str(flags.get_int("node_rank")))
+        os.environ.setdefault("LOCAL_RANK", str(flags.get_int("node_rank")))
+        ps = init_parallel(dp_size=flags.get_int("dp_size"), ep_size=flags.get_int("ep_size"))
+    engine = LLMEngine(build_engine_config(flags), ps=ps)
+    model = flags.get("model")
+    tok = load_tokenizer(model) if model and os.path.isdir(model) else None
+    name = flags.get("model_id") or (os.path.basename(model.rstrip("/")) if model else "xllm_b200")
+    if ps is not None and ps.rank != 0:
+        from .engine.replica import follow_rank0
+        return follow_rank0(engine, ps)
+    srv = ApiServer(engine, tok, model_name=name, host=flags.get("host"), port=flags.get_int("port"),
+                    max_concurrent_requests=flags.get_int("max_concurrent_requests"),
+                    tool_call_parser=flags.get("tool_call_parser"), reasoning_parser=flags.get("reasoning_parser"))
+    if ps is not None:
+        from .engine.replica import lead_ranks
+        lead_ranks(srv, ps)
+    print(f"xllm_b200 serving {name} on port {srv.port}", flush=True)
+    try:
+        srv.serve_forever()
+    except KeyboardInterrupt:
+        srv.shutdown()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
