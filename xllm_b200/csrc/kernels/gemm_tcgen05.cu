@@ -197,7 +197,8 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          const __grid_constant__ CUtensorMap tma_c, const bf16* __restrict__ bias, int M, int N,
-                         int K, int a_box_rows, int w_packed, int* __restrict__ err_word) {
+                         int K, int a_box_rows, int w_packed, const int32_t* __restrict__ tile_expert, int expert_rows,
+                         int* __restrict__ err_word) {
   using S = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles need 1024-byte aligned bases
@@ -247,7 +248,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       bool ok = true;
       int armed = 0;  // loads issued so far (for the drain on an aborted run)
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % m_tiles) * kBM, n0 = (tile / m_tiles) * BN;
+        const int m0 = (tile % m_tiles) * kBM;
+        int n0 = (tile / m_tiles) * BN;
+        if (tile_expert != nullptr) {
+          // grouped (MoE) mode: the row tile belongs to one expert, whose weights start
+          // expert_rows * e rows into W; unused tail tiles are skipped by every role alike
+          const int e = tile_expert[tile % m_tiles];
+          if (e < 0) continue;
+          n0 += e * expert_rows;
+        }
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
           // for M < 128 the A box only covers the rows that exist; the rest of the 128-row operand
@@ -288,9 +297,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       uint32_t phase = 0;
       bool ok = true;
       int t = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        if (tile_expert != nullptr && tile_expert[tile % m_tiles] < 0) continue;
         const int acc = t & 1;
         const uint32_t use = (uint32_t)(t >> 1);
+        ++t;
         if (!mbar_wait(tempty_bar(acc), (use & 1) ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -316,10 +327,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     bool ok = true;
     int t = 0, ebuf = 0;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      if (tile_expert != nullptr && tile_expert[tile % m_tiles] < 0) continue;
       const int m0 = (tile % m_tiles) * kBM, n0 = (tile / m_tiles) * BN;
       const int acc = t & 1;
       const uint32_t use = (uint32_t)(t >> 1);
+      ++t;
       if (!mbar_wait(tfull_bar(acc), use & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
@@ -613,7 +626,8 @@ static int* g_err_word[64] = {};
 
 template <int BN, int STAGES>
 static int launch_gemm(const void* a, const void* w, void* c, const void* bias, int M, int N, int K, int64_t lda,
-                       int64_t ldw, int64_t ldc, int max_ctas, int w_packed, cudaStream_t s) {
+                       int64_t ldw, int64_t ldc, int max_ctas, int w_packed, cudaStream_t s,
+                       const int32_t* tile_expert = nullptr, int n_experts = 1) {
   using S = GemmSmem<BN, STAGES>;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -631,13 +645,14 @@ static int launch_gemm(const void* a, const void* w, void* c, const void* bias, 
   }
   CUtensorMap ta, tb, tc;
   const int a_box = M >= kBM ? kBM : ((M + 7) & ~7);
-  const bool okb = w_packed ? make_tmap(&tb, w, (int64_t)N * (K / 64), 64, 64, 64) : make_tmap(&tb, w, N, K, ldw, BN);
+  const bool okb = w_packed ? make_tmap(&tb, w, (int64_t)N * (K / 64), 64, 64, 64)
+                            : make_tmap(&tb, w, (int64_t)N * n_experts, K, ldw, BN);
   if (!make_tmap(&ta, a, M, K, lda, a_box) || !okb || !make_tmap(&tc, c, M, N, ldc, 32, false))
     return (int)cudaErrorInvalidValue;
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
   int grid = tiles < max_ctas ? tiles : max_ctas;
   gemm_bf16_tcgen05_kernel<BN, STAGES><<<grid, 192, S::TOTAL, s>>>(ta, tb, tc, (const bf16*)bias, M, N, K, a_box,
-                                                                 w_packed, g_err_word[dev & 63]);
+                                                                 w_packed, tile_expert, N, g_err_word[dev & 63]);
   return XLLM_LAUNCH_CHECK();
 }
 
@@ -735,6 +750,22 @@ XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* b
     case 64: return launch_gemm<64, 8>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s);
     default: return (int)cudaErrorInvalidValue;
   }
+}
+
+// Grouped (mixture-of-experts) GEMM: rows of A are grouped by expert in 128-row tiles
+// (tile_expert[i] = expert of row tile i, -1 = unused); W is [n_experts, N, K].
+// C[rows of tile i, :] = A[rows of tile i, :] · W[tile_expert[i]]^T.  M is the padded row count.
+// N must be a multiple of the tile width so that a tile never mixes two experts' weights.
+XLLM_API int xllm_gemm_bf16_grouped(const void* a, const void* w, void* c, const void* tile_expert, int M, int N,
+                                    int K, int n_experts, int64_t lda, int64_t ldc, void* stream) {
+  using namespace xllm;
+  if (M == 0 || N == 0) return 0;
+  if (K % 8 || N % 64 || lda % 8 || ldc % 8 || M % kBM) return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int32_t* te = (const int32_t*)tile_expert;
+  if (N % 256 == 0) return launch_gemm<256, 4>(a, w, c, nullptr, M, N, K, lda, K, ldc, 148, 0, s, te, n_experts);
+  if (N % 128 == 0) return launch_gemm<128, 6>(a, w, c, nullptr, M, N, K, lda, K, ldc, 148, 0, s, te, n_experts);
+  return launch_gemm<64, 8>(a, w, c, nullptr, M, N, K, lda, K, ldc, 148, 0, s, te, n_experts);
 }
 
 namespace xllm {

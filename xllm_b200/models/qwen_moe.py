@@ -1,0 +1,108 @@
+"""Sparse-MoE decoders: Qwen3-MoE (softmax top-k routing, no shared expert) and the generic
+MoE block reused by DeepSeek-style models (sigmoid grouped routing, shared experts).
+
+Parity: Qwen3MoeDecoderLayer (xllm/core/layers/qwen3_moe_decoder_layer.cpp:141-160), FusedMoE
+(layers/cuda/fused_moe.cpp:96-124) and models/llm/qwen3_moe.h.  Expert parallelism places
+E / ep experts on each EP rank; with ep_size == 1 every rank holds all experts with the expert
+intermediate dimension sharded across the TP group.  Either way a rank produces a partial sum over
+"its" part of the experts and the partials are reduced by the same fused all-reduce(+norm) that the
+dense layers use — the reference reduces with two NCCL all-reduces (moe_tp then moe_ep).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..ops import moe as moe_ops
+from .layers import DenseMLP, Linear, Module
+from .qwen import DenseCausalLM
+from .registry import register_model
+from ..parallel.state import single
+
+
+class SparseMoeBlock(Module):
+    def __init__(self, args, dtype, device, ps=None):
+        super().__init__()
+        self.ps = ps or single()
+        self.args = args
+        E, H, I = args.num_experts, args.hidden_size, args.moe_intermediate_size
+        ep = self.ps.ep_size if self.ps.ep_size > 1 else 1
+        tp = self.ps.tp_size
+        self.ep = ep
+        if ep > 1:
+            self.e_local = E // ep
+            self.e_begin = self.ps.ep_rank * self.e_local
+            self.i_local, i_rank, i_parts = I, 0, 1
+        else:
+            self.e_local, self.e_begin = E, 0
+            self.i_local, i_rank, i_parts = I // tp, self.ps.tp_rank, tp
+        self.top_k = args.num_experts_per_tok
+        self.gate = self.add_module("gate", Linear(H, E, False, dtype, device, self.ps))  # replicated router
+        self.w_gate_up = torch.empty(self.e_local, 2 * self.i_local, H, dtype=dtype, device=device)
+        self.w_down = torch.empty(self.e_local, H, self.i_local, dtype=dtype, device=device)
+        self._params["experts.gate_up"] = self.w_gate_up
+        self._params["experts.down"] = self.w_down
+        il = self.i_local
+        for e in range(self.e_local):
+            ge = e + self.e_begin
+
+            def lg(w, e=e):
+                self.w_gate_up[e, :il].copy_(w.narrow(0, i_rank * il, il).to(dtype))
+
+            def lu(w, e=e):
+                self.w_gate_up[e, il:].copy_(w.narrow(0, i_rank * il, il).to(dtype))
+
+            def ld(w, e=e):
+                self.w_down[e].copy_(w.narrow(1, i_rank * il, il).to(dtype))
+
+            self._loaders[f"experts.{ge}.gate_proj.weight"] = lg
+            self._loaders[f"experts.{ge}.up_proj.weight"] = lu
+            self._loaders[f"experts.{ge}.down_proj.weight"] = ld
+        self.bias = None
+        if args.router_bias:
+            self.bias = torch.zeros(E, dtype=torch.float32, device=device)
+            self.add_param("gate.e_score_correction_bias", self.bias)
+        self.shared = None
+        if args.n_shared_experts > 0:
+            si = args.shared_expert_intermediate_size or args.moe_intermediate_size * args.n_shared_experts
+            self.shared = self.add_module("shared_experts", DenseMLP(H, si, args.hidden_act, dtype, device, self.ps, reduce=False))
+        self._ws = None
+
+    def forward(self, x):
+        a = self.args
+        T = x.shape[0]
+        logits = self.gate(x)
+        shared_out = None
+        if self.shared is not None:
+            # the shared expert is TP-sharded like a dense MLP: its partial joins the routed partial.
+            # With EP every rank would add the full shared output, so only the rank that owns
+            # expert 0 contributes it.
+            shared_out = ops.linear(ops.act_and_mul(self.shared.gate_up(x), a.hidden_act), self.shared.down.weight)
+            if self.ep > 1 and self.e_begin != 0 and self.shared.ps.tp_size == 1:
+                shared_out = None
+        comm = self.ps.comm
+        out = comm.partial_buffer(T) if (comm is not None and x.is_cuda) else None
+        if x.is_cuda and (self._ws is None or self._ws.max_tokens < T):
+            self._ws = moe_ops.MoeWorkspace(max(T, 256), self.top_k, a.num_experts, self.e_local, a.hidden_size,
+                                            self.i_local, x.device, x.dtype)
+        y = moe_ops.fused_moe(x, logits, self.w_gate_up, self.w_down, self.top_k, a.scoring_func, self.bias,
+                              a.n_group, a.topk_group, a.norm_topk_prob, a.routed_scaling_factor, self.e_begin,
+                              a.num_experts, shared_out, self._ws, out)
+        if out is None and self.ps.tp_size > 1:
+            y = self.ps.all_reduce(y)
+        return y
+
+    __call__ = forward
+
+
+def _make_mlp(args, dtype, device, ps):
+    def make(i):
+        if args.is_moe_layer(i):
+            return SparseMoeBlock(args, dtype, device, ps)
+        return DenseMLP(args.hidden_size, args.intermediate_size, args.hidden_act, dtype, device, ps)
+    return make
+
+
+@register_model("qwen3_moe", "qwen2_moe", "Qwen3MoeForCausalLM", "Qwen2MoeForCausalLM")
+def build_qwen_moe(args, dtype, device, ps):
+    return DenseCausalLM(args, dtype, device, ps, make_mlp=_make_mlp(args, dtype, device, ps))
