@@ -101,6 +101,26 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// kind::f8f6f4 with A = B = e4m3 (format code 0), D = f32; K per instruction is 32 elements (32 bytes)
+__host__ __device__ constexpr uint32_t umma_idesc_e4m3(int n) {
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_fp8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Operand type and output scaling of a launch.  fp8 == 0: bf16 operands, no scaling.
+// fp8 == 1: e4m3 operands, C = acc * a_scale[row or 0] * b_scale[col or 0] (+ bias).
+struct GemmMode {
+  const float* a_scale;
+  const float* b_scale;
+  int fp8, a_per_row, b_per_col;
+};
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
@@ -144,7 +164,13 @@ constexpr int kEpiBytes = 4 * 2 * kEpiBufBytes;    // 4 warps x 2 buffers
 template <int BN>
 __device__ __forceinline__ void epilogue_slice(uint32_t taddr, const CUtensorMap* tmap_c, uint32_t warp_stage,
                                                int row0, int n0, const bf16* __restrict__ bias, int N, int lane,
-                                               int& buf) {
+                                               int& buf, const GemmMode mode = GemmMode{nullptr, nullptr, 0, 0, 0},
+                                               int M = 0) {
+  float a_s = 1.f;
+  if (mode.fp8 && mode.a_scale != nullptr) {
+    const int r = row0 + lane;
+    a_s = mode.a_per_row ? (r < M ? mode.a_scale[r] : 0.f) : mode.a_scale[0];
+  }
 #pragma unroll 1
   for (int c = 0; c < BN / kEpiCols; ++c) {
     uint32_t r[64];
@@ -160,6 +186,13 @@ __device__ __forceinline__ void epilogue_slice(uint32_t taddr, const CUtensorMap
       float f[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j * 8 + e]);
+      if (mode.fp8 && col0 + j * 8 < N) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float b_s = mode.b_scale == nullptr ? 1.f : (mode.b_per_col ? mode.b_scale[col0 + j * 8 + e] : mode.b_scale[0]);
+          f[e] *= a_s * b_s;
+        }
+      }
       if (bias != nullptr && col0 + j * 8 < N) {
         float bv[8];
         unpack8(*reinterpret_cast<const bf16x8*>(bias + col0 + j * 8), bv);
@@ -198,7 +231,7 @@ __global__ void __launch_bounds__(192, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          const __grid_constant__ CUtensorMap tma_c, const bf16* __restrict__ bias, int M, int N,
                          int K, int a_box_rows, int w_packed, const int32_t* __restrict__ tile_expert, int expert_rows,
-                         int* __restrict__ err_word) {
+                         const GemmMode mode, int* __restrict__ err_word) {
   using S = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles need 1024-byte aligned bases
@@ -215,7 +248,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + BN - 1) / BN;
   const int total_tiles = m_tiles * n_tiles;
-  const int k_blocks = (K + kBK - 1) / kBK;
+  const int k_elems = mode.fp8 ? 2 * kBK : kBK;  // elements per 128-byte K block
+  const int k_blocks = (K + k_elems - 1) / k_elems;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -263,9 +297,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           // is whatever the slot held before and only feeds output rows that are never stored
           mbar_expect_tx(full_bar(stage), S::B_BYTES + a_box_rows * kBK * 2);
           const uint32_t a_dst = sbase + stage * S::STAGE_BYTES;
-          tma_load_2d(a_dst, &tma_a, kb * kBK, m0, full_bar(stage));
+          tma_load_2d(a_dst, &tma_a, kb * k_elems, m0, full_bar(stage));
           if (!w_packed) {
-            tma_load_2d(a_dst + S::A_BYTES, &tma_b, kb * kBK, n0, full_bar(stage));
+            tma_load_2d(a_dst + S::A_BYTES, &tma_b, kb * k_elems, n0, full_bar(stage));
           } else {
             // tile-packed weights: every 64 x 64 block is one contiguous 8 KB run
 #pragma unroll
@@ -292,7 +326,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   } else if (warp == 1) {
     if (lane == 0) {
       // ------------------------------------------------------------------ MMA issuer
-      constexpr uint32_t idesc = umma_idesc_bf16(BN);
+      const uint32_t idesc = mode.fp8 ? umma_idesc_e4m3(BN) : umma_idesc_bf16(BN);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -314,7 +348,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
             // +32 bytes (2 x 16-byte units) along K inside the swizzled row per UMMA_K = 16
-            umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+            if (mode.fp8) umma_fp8(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+            else umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
           }
           umma_commit(empty_bar(stage));  // slot reusable once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -336,7 +371,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       if (!mbar_wait(tfull_bar(acc), use & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-      epilogue_slice<BN>(taddr, &tma_c, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, bias, N, lane, ebuf);
+      epilogue_slice<BN>(taddr, &tma_c, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, bias, N, lane, ebuf, mode, M);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -608,14 +643,14 @@ static EncodeTiledFn get_encode_fn() {
 
 // 2-D bf16 row-major [rows, cols] (row stride ld elements), box = [box_rows, 64 cols], 128B swizzle.
 static bool make_tmap(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows,
-                      bool promote = true) {
+                      bool promote = true, bool bytes = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return false;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * (bytes ? 1 : 2)};
+  cuuint32_t box[2] = {(cuuint32_t)(bytes ? 2 * kBK : kBK), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+  CUresult r = fn(map, bytes ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   promote ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -627,7 +662,8 @@ static int* g_err_word[64] = {};
 template <int BN, int STAGES>
 static int launch_gemm(const void* a, const void* w, void* c, const void* bias, int M, int N, int K, int64_t lda,
                        int64_t ldw, int64_t ldc, int max_ctas, int w_packed, cudaStream_t s,
-                       const int32_t* tile_expert = nullptr, int n_experts = 1) {
+                       const int32_t* tile_expert = nullptr, int n_experts = 1,
+                       GemmMode mode = GemmMode{nullptr, nullptr, 0, 0, 0}) {
   using S = GemmSmem<BN, STAGES>;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -646,13 +682,13 @@ static int launch_gemm(const void* a, const void* w, void* c, const void* bias, 
   CUtensorMap ta, tb, tc;
   const int a_box = M >= kBM ? kBM : ((M + 7) & ~7);
   const bool okb = w_packed ? make_tmap(&tb, w, (int64_t)N * (K / 64), 64, 64, 64)
-                            : make_tmap(&tb, w, (int64_t)N * n_experts, K, ldw, BN);
-  if (!make_tmap(&ta, a, M, K, lda, a_box) || !okb || !make_tmap(&tc, c, M, N, ldc, 32, false))
+                            : make_tmap(&tb, w, (int64_t)N * n_experts, K, ldw, BN, true, mode.fp8 != 0);
+  if (!make_tmap(&ta, a, M, K, lda, a_box, true, mode.fp8 != 0) || !okb || !make_tmap(&tc, c, M, N, ldc, 32, false))
     return (int)cudaErrorInvalidValue;
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
   int grid = tiles < max_ctas ? tiles : max_ctas;
   gemm_bf16_tcgen05_kernel<BN, STAGES><<<grid, 192, S::TOTAL, s>>>(ta, tb, tc, (const bf16*)bias, M, N, K, a_box,
-                                                                 w_packed, tile_expert, N, g_err_word[dev & 63]);
+                                                                 w_packed, tile_expert, N, mode, g_err_word[dev & 63]);
   return XLLM_LAUNCH_CHECK();
 }
 
@@ -766,6 +802,28 @@ XLLM_API int xllm_gemm_bf16_grouped(const void* a, const void* w, void* c, const
   if (N % 256 == 0) return launch_gemm<256, 4>(a, w, c, nullptr, M, N, K, lda, K, ldc, 148, 0, s, te, n_experts);
   if (N % 128 == 0) return launch_gemm<128, 6>(a, w, c, nullptr, M, N, K, lda, K, ldc, 148, 0, s, te, n_experts);
   return launch_gemm<64, 8>(a, w, c, nullptr, M, N, K, lda, K, ldc, 148, 0, s, te, n_experts);
+}
+
+// fp8 (e4m3) scaled GEMM: C[M,N] (bf16) = (A_fp8[M,K] · W_fp8[N,K]^T) * a_scale * b_scale (+ bias).
+// a_scale: one float (per tensor) or M floats (per token, a_per_row = 1); b_scale: one float or N
+// floats (per output channel, b_per_col = 1).  K % 16 == 0; leading dimensions in elements (= bytes).
+// Same capability as the reference's CUTLASS scaled_mm for sm_100
+// (xllm/core/kernels/cuda/cutlass_w8a8/c3x/scaled_mm_sm100_fp8_dispatch.cuh:34-429).
+XLLM_API int xllm_gemm_fp8(const void* a, const void* w, void* c, const void* bias, const void* a_scale,
+                           const void* b_scale, int a_per_row, int b_per_col, int M, int N, int K, int64_t lda,
+                           int64_t ldw, int64_t ldc, void* stream) {
+  using namespace xllm;
+  if (M == 0 || N == 0) return 0;
+  if (K % 16 || N % 8 || lda % 16 || ldw % 16 || ldc % 8) return (int)cudaErrorInvalidValue;
+  if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15) return (int)cudaErrorInvalidValue;
+  GemmMode mode{(const float*)a_scale, (const float*)b_scale, 1, a_per_row, b_per_col};
+  cudaStream_t s = (cudaStream_t)stream;
+  const int mt = (M + kBM - 1) / kBM;
+  int tile_n = 256;
+  while (tile_n > 64 && mt * ((N + tile_n - 1) / tile_n) < 148) tile_n >>= 1;
+  if (tile_n == 256) return launch_gemm<256, 4>(a, w, c, bias, M, N, K, lda, ldw, ldc, 148, 0, s, nullptr, 1, mode);
+  if (tile_n == 128) return launch_gemm<128, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, 148, 0, s, nullptr, 1, mode);
+  return launch_gemm<64, 8>(a, w, c, bias, M, N, K, lda, ldw, ldc, 148, 0, s, nullptr, 1, mode);
 }
 
 namespace xllm {

@@ -1,0 +1,108 @@
+"""fp8 (e4m3) quantisation and scaled GEMM.
+
+`scaled_mm` is the tcgen05 `kind::f8f6f4` GEMM with per-tensor / per-token / per-channel scales (the
+capability of the reference's CUTLASS `cutlass_scaled_mm`, cutlass_w8a8/scaled_mm_entry.cu:56-108).
+128 x 128 block-scaled weights (DeepSeek-V3 checkpoints) are held in fp8 and expanded to bf16 by
+`dequant_block128` right before the bf16 GEMM.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import I, L, P, check, ptr, stream
+
+_lib.register_signature("xllm_gemm_fp8", [P, P, P, P, P, P, I, I, I, I, I, L, L, L, P])
+_lib.register_signature("xllm_quant_fp8_per_token", [P, P, P, P, L, I, L, P])
+_lib.register_signature("xllm_quant_fp8_group128", [P, P, P, L, I, L, P])
+_lib.register_signature("xllm_dequant_fp8_block128", [P, P, P, L, I, P])
+
+FP8 = torch.float8_e4m3fn
+FP8_MAX = 448.0
+
+
+# ------------------------------------------------------------------ references (CPU path / oracle)
+def quant_per_token_ref(x, static_scale=None):
+    xf = x.float()
+    if static_scale is not None:
+        s = static_scale.float().reshape(())
+        return (xf / s).clamp(-FP8_MAX, FP8_MAX).to(FP8), None
+    s = xf.abs().amax(-1).clamp_min(1e-10) / FP8_MAX
+    return (xf / s[:, None]).clamp(-FP8_MAX, FP8_MAX).to(FP8), s
+
+
+def quant_group128_ref(x):
+    T, H = x.shape
+    g = x.float().view(T, H // 128, 128)
+    s = g.abs().amax(-1).clamp_min(1e-10) / FP8_MAX
+    return (g / s[..., None]).clamp(-FP8_MAX, FP8_MAX).to(FP8).view(T, H), s
+
+
+def quant_block128_ref(w):
+    """[N, K] -> (fp8 [N, K], scales [ceil(N/128), ceil(K/128)])."""
+    N, K = w.shape
+    Np, Kp = (N + 127) // 128 * 128, (K + 127) // 128 * 128
+    wp = torch.zeros(Np, Kp, dtype=torch.float32, device=w.device)
+    wp[:N, :K] = w.float()
+    b = wp.view(Np // 128, 128, Kp // 128, 128)
+    s = b.abs().amax((1, 3)).clamp_min(1e-10) / FP8_MAX
+    q = (b / s[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).view(Np, Kp)[:N, :K].to(FP8)
+    return q.contiguous(), s
+
+
+def dequant_block128_ref(q, scales, dtype=torch.bfloat16):
+    N, K = q.shape
+    s = scales.repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)[:, :K]
+    return (q.float() * s).to(dtype)
+
+
+# ------------------------------------------------------------------ kernels
+def quant_per_token(x, static_scale=None):
+    if not x.is_cuda:
+        return quant_per_token_ref(x, static_scale)
+    T, H = x.shape
+    q = torch.empty(T, H, dtype=FP8, device=x.device)
+    s = None if static_scale is not None else torch.empty(T, dtype=torch.float32, device=x.device)
+    check(_lib.load().xllm_quant_fp8_per_token(ptr(q), ptr(s), ptr(x), ptr(static_scale), T, H, x.stride(0), stream()),
+          "quant_fp8_per_token")
+    return q, s
+
+
+def quant_group128(x):
+    if not x.is_cuda:
+        return quant_group128_ref(x)
+    T, H = x.shape
+    q = torch.empty(T, H, dtype=FP8, device=x.device)
+    s = torch.empty(T, H // 128, dtype=torch.float32, device=x.device)
+    check(_lib.load().xllm_quant_fp8_group128(ptr(q), ptr(s), ptr(x), T, H, x.stride(0), stream()), "quant_fp8_group128")
+    return q, s
+
+
+def dequant_block128(q, scales, out=None):
+    if not q.is_cuda:
+        return dequant_block128_ref(q, scales)
+    N, K = q.shape
+    if out is None:
+        out = torch.empty(N, K, dtype=torch.bfloat16, device=q.device)
+    check(_lib.load().xllm_dequant_fp8_block128(ptr(out), ptr(q), ptr(scales), N, K, stream()), "dequant_fp8_block128")
+    return out
+
+
+def scaled_mm(a_q, w_q, a_scale, w_scale, bias=None, out=None):
+    """bf16 C = (a_q @ w_q^T) * a_scale * w_scale (+ bias).  a_scale: scalar tensor or [M];
+    w_scale: scalar tensor or [N]."""
+    if not a_q.is_cuda:
+        y = (a_q.float() * a_scale.float().reshape(-1, 1)) @ (w_q.float() * w_scale.float().reshape(-1, 1)).T
+        if bias is not None:
+            y = y + bias.float()
+        return y.to(torch.bfloat16)
+    M, K = a_q.shape
+    N = w_q.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a_q.device)
+    check(_lib.load().xllm_gemm_fp8(ptr(a_q), ptr(w_q), ptr(out), ptr(bias), ptr(a_scale), ptr(w_scale),
+                                    int(a_scale.numel() > 1), int(w_scale.numel() > 1), M, N, K, a_q.stride(0),
+                                    w_q.stride(0), out.stride(0), stream()), "gemm_fp8")
+    from . import _count
+    _count()
+    return out
