@@ -56,7 +56,8 @@ def _rt_path() -> Path:
 
 
 def _sha(paths, extra: str) -> str:
-    h = hashlib.sha256(extra.encode())
+    # the tree may be copied anywhere: absolute paths must not influence staleness
+    h = hashlib.sha256(extra.replace(str(ROOT), "<root>").encode())
     for p in sorted(paths):
         h.update(str(p.relative_to(ROOT)).encode())
         h.update(p.read_bytes())
@@ -83,8 +84,38 @@ def kernel_sources():
     return sorted((CSRC / "kernels").glob("*.cu"))
 
 
+class _BuildLock:
+    """Inter-process lock: several ranks importing the package at once must not build concurrently."""
+
+    def __init__(self):
+        LIBDIR.mkdir(exist_ok=True)
+        self.path = LIBDIR / ".build.lock"
+
+    def __enter__(self):
+        import fcntl
+        self.f = open(self.path, "w")
+        fcntl.flock(self.f, fcntl.LOCK_EX)
+        return self
+
+    def __exit__(self, *a):
+        import fcntl
+        fcntl.flock(self.f, fcntl.LOCK_UN)
+        self.f.close()
+
+
+def _link_atomic(cmd_prefix, out: Path, objs, tail, verbose):
+    tmp = out.with_name(out.name + f".tmp{os.getpid()}")
+    _run([*cmd_prefix, "-o", tmp, *objs, *tail], verbose)
+    os.replace(tmp, out)  # readers never see a half-written library
+
+
 def build_kernels(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
     """Compile every ``csrc/kernels/*.cu`` for sm_100a and link the C-ABI library."""
+    with _BuildLock():
+        return _build_kernels(force, verbose, ptxas_info)
+
+
+def _build_kernels(force, verbose, ptxas_info) -> Path:
     srcs = kernel_sources()
     hdrs = _headers("kernels")
     flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_info else [])
@@ -114,7 +145,7 @@ def build_kernels(force: bool = False, verbose: bool = False, ptxas_info: bool =
     want = _sha(srcs + hdrs, " ".join(flags))
     if todo or force or not KERNEL_LIB.exists() or not link_stamp.exists() \
             or link_stamp.read_text() != want:
-        _run([NVCC, "-shared", "-o", KERNEL_LIB, *objs, "-lcudart"], verbose)
+        _link_atomic([NVCC, "-shared"], KERNEL_LIB, objs, ["-lcudart"], verbose)
         link_stamp.write_text(want)
     return KERNEL_LIB
 
@@ -128,6 +159,11 @@ def runtime_sources():
 
 def build_runtime(force: bool = False, verbose: bool = False) -> Path:
     """Compile the C++ runtime + pybind11 module ``xllm_b200._rt``."""
+    with _BuildLock():
+        return _build_runtime(force, verbose)
+
+
+def _build_runtime(force, verbose) -> Path:
     import pybind11
 
     srcs = runtime_sources()
@@ -158,7 +194,7 @@ def build_runtime(force: bool = False, verbose: bool = False) -> Path:
     want = _sha(srcs + hdrs, " ".join(flags))
     if todo or force or not out.exists() or not link_stamp.exists() \
             or link_stamp.read_text() != want:
-        _run([CXX, "-shared", "-o", out, *objs, "-pthread", "-lrt"], verbose)
+        _link_atomic([CXX, "-shared"], out, objs, ["-pthread", "-lrt"], verbose)
         link_stamp.write_text(want)
     return out
 
