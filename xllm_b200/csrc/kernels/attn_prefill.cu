@@ -250,5 +250,6 @@ XLLM_API int xllm_paged_prefill_attn(void* out, int64_t o_stride, const void* q,
   cudaStream_t s = (cudaStream_t)stream;
   if (d == 128) return launch_prefill<128>(p, batch, max_q_len, s);
   if (d == 64) return launch_prefill<64>(p, batch, max_q_len, s);
+  if (d == 256) return launch_prefill<256>(p, batch, max_q_len, s);
   return (int)cudaErrorInvalidValue;
 }

@@ -100,8 +100,11 @@ class LLMEngine:
         else:
             self.model = create_model(self.args, self.dtype, self.device, self.ps)
             if os.path.isdir(cfg.model) and not cfg.random_weights:
-                from ..utils.loader import iterate_weights
-                self.model.load_weights(iterate_weights(cfg.model), strict=False)
+                from ..utils.loader import dequant_fp8_stream, iterate_weights
+                weights = iterate_weights(cfg.model)
+                if self.args.quant_method == "fp8":
+                    weights = dequant_fp8_stream(weights)
+                self.model.load_weights(weights, strict=False)
             else:
                 self.model.init_random(seed=cfg.seed)
         self.load_seconds = time.time() - t0

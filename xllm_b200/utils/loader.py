@@ -80,3 +80,26 @@ def save_file(tensors: Dict[str, torch.Tensor], path: str, metadata: Dict[str, s
         f.write(hj)
         for b in blobs:
             f.write(b)
+
+
+def dequant_fp8_stream(weights):
+    """Pair every block-scaled fp8 tensor `X.weight` with its `X.weight_scale_inv` (128 x 128 blocks,
+    DeepSeek-V3 checkpoints) and yield the bf16 weight; everything else passes through."""
+    from ..ops import fp8
+    pending_w, pending_s = {}, {}
+    for name, t in weights:
+        if name.endswith(".weight_scale_inv"):
+            base = name[: -len("_scale_inv")]
+            if base in pending_w:
+                yield base, fp8.dequant_block128_ref(pending_w.pop(base), t.float())
+            else:
+                pending_s[base] = t
+        elif t.dtype == torch.float8_e4m3fn:
+            if name in pending_s:
+                yield name, fp8.dequant_block128_ref(t, pending_s.pop(name).float())
+            else:
+                pending_w[name] = t
+        else:
+            yield name, t
+    for name, t in pending_w.items():  # fp8 tensors without scales: plain cast
+        yield name, t.to(torch.bfloat16)
