@@ -48,3 +48,45 @@ def test_gemm_packed_weight(M, N, K, tile_n, pair):
     err = (y.float() - ref).abs()
     assert bool((err <= 2e-2 + 1e-2 * ref.abs()).all()), err.max().item()
     assert g.error_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 4096, 12288), (256, 4096, 4096), (256, 4096, 12288), (300, 6144, 4096),
+                                   (129, 264, 1352), (512, 4096, 12288)])
+@pytest.mark.parametrize("tile_n,pair,split_k", [(0, -1, 0), (64, 0, 2), (128, 0, 4), (256, 0, 3), (256, 1, 4),
+                                                 (128, 1, 8), (64, 1, 16)])
+@pytest.mark.parametrize("packed", [False, True])
+def test_gemm_split_k(M, N, K, tile_n, pair, split_k, packed):
+    """K cut into slices whose fp32 partials meet in the device scratch; run twice so that the
+    arrival counters are seen to be left at zero by the first launch."""
+    if packed and (N % 64 or K % 64):
+        pytest.skip("packed weights need multiples of 64")
+    torch.manual_seed(M + N + K + split_k)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    b = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    ww = g.pack_weight(w) if packed else w
+    ref = x.float() @ w.float().T + b.float()
+    tol = 3e-2 + 1e-2 * ref.abs()
+    for _ in range(2):
+        y = g.gemm_nt(x, ww, bias=b, tile_n=tile_n, pair=pair, split_k=split_k)
+        assert g.error_status() == 0
+        err = (y.float() - ref).abs()
+        assert bool((err <= tol).all()), f"max err {err.max().item()}"
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 1024, 4096), (256, 4096, 4096), (300, 512, 200), (129, 264, 1352)])
+@pytest.mark.parametrize("tile_n,pair,split_k", [(64, 0, 1), (128, 0, 1), (128, 0, 3), (64, 1, 1), (128, 1, 2)])
+def test_gemm_one_k_block_per_stage(M, N, K, tile_n, pair, split_k):
+    """The narrow tiles default to two K blocks per ring stage; the one-block kernels stay covered."""
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    ref = x.float() @ w.float().T
+    tol = 3e-2 + 1e-2 * ref.abs()
+    g.set_k_per_stage(1)
+    try:
+        y = g.gemm_nt(x, w, tile_n=tile_n, pair=pair, split_k=split_k)
+    finally:
+        g.set_k_per_stage(2)
+    assert g.error_status() == 0
+    assert bool(((y.float() - ref).abs() <= tol).all())

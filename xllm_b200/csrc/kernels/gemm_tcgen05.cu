@@ -116,16 +116,40 @@ __device__ __forceinline__ void umma_fp8(uint32_t tmem_d, uint64_t adesc, uint64
 }
 // Operand type and output scaling of a launch.  fp8 == 0: bf16 operands, no scaling.
 // fp8 == 1: e4m3 operands, C = acc * a_scale[row or 0] * b_scale[col or 0] (+ bias).
+// ks > 1: split-K.  Work unit = (tile, K slice).  Every unit adds its fp32 partial tile into the
+// zero-filled scratch `ws` ([m_pad][N]) with TMA reduce-add (the adds happen in L2), waits for
+// them to complete and bumps the tile's counter; the unit that arrives last reads the sum once,
+// writes zeros back (the scratch is clean again for the next launch), adds the bias and stores the
+// bf16 rows.  Nobody waits for anybody, so the scheme cannot deadlock.
 struct GemmMode {
   const float* a_scale;
   const float* b_scale;
   int fp8, a_per_row, b_per_col;
+  int ks;
+  float* ws;
+  int* counters;
+  bf16* c;      // output base and row stride (elements) for the split-K finishing pass
+  int64_t ldc;
 };
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+// One lane of a converged warp.  The producer and MMA warps run their loops with all 32 lanes and
+// only predicate the TMA / tcgen05 instructions on the elected lane: loop state, shared-memory
+// addresses and descriptors then stay warp-uniform, which is what these instructions take as
+// operands (a loop run by a single lane under divergence pays a register-file round trip per
+// operand: measured ~120 cycles per tcgen05.mma issue against ~30 here).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+// Whole-warp bounded wait: every lane polls, the verdict is made uniform.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
@@ -164,7 +188,7 @@ constexpr int kEpiBytes = 4 * 2 * kEpiBufBytes;    // 4 warps x 2 buffers
 template <int BN>
 __device__ __forceinline__ void epilogue_slice(uint32_t taddr, const CUtensorMap* tmap_c, uint32_t warp_stage,
                                                int row0, int n0, const bf16* __restrict__ bias, int N, int lane,
-                                               int& buf, const GemmMode mode = GemmMode{nullptr, nullptr, 0, 0, 0},
+                                               int& buf, const GemmMode mode = GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0},
                                                int M = 0) {
   float a_s = 1.f;
   if (mode.fp8 && mode.a_scale != nullptr) {
@@ -215,10 +239,111 @@ __device__ __forceinline__ void epilogue_slice(uint32_t taddr, const CUtensorMap
   }
 }
 
-template <int BN, int STAGES>
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_src), "r"(x), "r"(y)
+               : "memory");
+}
+
+// Split-K epilogue of one warp: add its 32 x BN fp32 slice into the scratch (32 x 32 chunks staged
+// in swizzled shared memory, one TMA reduce-add each), then (all four epilogue warps together)
+// bump the tile counter; returns true in the warps of the unit that arrived last.
+template <int BN>
+__device__ __forceinline__ bool splitk_dump(uint32_t taddr, const CUtensorMap* tmap_ws, uint32_t warp_stage,
+                                            const GemmMode& mode, int counter_idx, int row0, int n0, int lane,
+                                            int q, int& buf, volatile int* s_last) {
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(taddr + c * 32, r);
+    tmem_ld_wait();
+    if (lane == 0) bulk_wait_read<1>();
+    __syncwarp();
+    const uint32_t sb = warp_stage + buf * kEpiBufBytes;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t dst = sb + lane * 128 + ((j ^ (lane & 7)) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(r[4 * j]), "r"(r[4 * j + 1]),
+                   "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
+                   : "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+      tma_reduce_add_2d(tmap_ws, sb, n0 + c * 32, row0);
+      bulk_commit();
+    }
+    buf ^= 1;
+  }
+  if (lane == 0) {
+    bulk_wait_all();  // the adds have been performed, not merely read from shared memory
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __threadfence();
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+  if (q == 0 && lane == 0) {
+    const int old = atomicAdd(mode.counters + counter_idx, 1);
+    const int last = old == mode.ks - 1;
+    if (last) mode.counters[counter_idx] = 0;  // ready for the next launch
+    *s_last = last;
+    __threadfence();
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  return *s_last != 0;
+}
+
+// Finishing pass of the last arriver, one warp per 32 rows: read the summed fp32 rows (coalesced,
+// from L2), put zeros back, add the bias and store bf16.  16 rows are in flight per step.
+template <int BN>
+__device__ __forceinline__ void splitk_finish(const GemmMode& mode, const bf16* __restrict__ bias, int row0, int n0,
+                                              int M, int N, int lane) {
+  constexpr int RB = 16;
+#pragma unroll 1
+  for (int cc = 0; cc < BN; cc += 128) {
+    const int col = n0 + cc + lane * 4;
+    if (cc + lane * 4 >= BN || col >= N) continue;
+    float bv[4] = {0.f, 0.f, 0.f, 0.f};
+    if (bias != nullptr) {
+      const uint2 b = *reinterpret_cast<const uint2*>(bias + col);
+      const __nv_bfloat162 b0 = *reinterpret_cast<const __nv_bfloat162*>(&b.x);
+      const __nv_bfloat162 b1 = *reinterpret_cast<const __nv_bfloat162*>(&b.y);
+      bv[0] = __low2float(b0); bv[1] = __high2float(b0); bv[2] = __low2float(b1); bv[3] = __high2float(b1);
+    }
+#pragma unroll 1
+    for (int r0 = 0; r0 < 32; r0 += RB) {
+      float4 v[RB];
+#pragma unroll
+      for (int i = 0; i < RB; ++i) {
+        const int row = row0 + r0 + i;
+        v[i] = row < M ? __ldcg(reinterpret_cast<const float4*>(mode.ws + (int64_t)row * N + col))
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int i = 0; i < RB; ++i) {
+        const int row = row0 + r0 + i;
+        if (row < M) {
+          __stcg(reinterpret_cast<float4*>(mode.ws + (int64_t)row * N + col), make_float4(0.f, 0.f, 0.f, 0.f));
+          const __nv_bfloat162 o0 = __floats2bfloat162_rn(v[i].x + bv[0], v[i].y + bv[1]);
+          const __nv_bfloat162 o1 = __floats2bfloat162_rn(v[i].z + bv[2], v[i].w + bv[3]);
+          uint2 o;
+          o.x = *reinterpret_cast<const uint32_t*>(&o0);
+          o.y = *reinterpret_cast<const uint32_t*>(&o1);
+          *reinterpret_cast<uint2*>(mode.c + (int64_t)row * mode.ldc + col) = o;
+        }
+      }
+    }
+  }
+}
+
+// KS = 64-element K blocks per ring stage.  A stage costs one barrier wait, one commit and one
+// producer round trip whatever it holds (~600 cycles measured); narrow tiles, whose MMAs are short,
+// take two K blocks per stage so that this fixed cost is paid half as often.
+template <int BN, int STAGES, int KS = 1>
 struct GemmSmem {
-  static constexpr int A_BYTES = kBM * kBK * 2;
-  static constexpr int B_BYTES = BN * kBK * 2;
+  static constexpr int A_KB = kBM * kBK * 2;  // one K block of A
+  static constexpr int B_KB = BN * kBK * 2;
+  static constexpr int A_BYTES = KS * A_KB;
+  static constexpr int B_BYTES = KS * B_KB;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_OFF = STAGES * STAGE_BYTES;  // 1024-byte aligned: stages are multiples of 1 KB
   static constexpr int BAR_OFF = EPI_OFF + kEpiBytes;
@@ -226,13 +351,13 @@ struct GemmSmem {
   static_assert(TOTAL <= 232448, "exceeds the 227 KB of shared memory per CTA");
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int KS>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                         const __grid_constant__ CUtensorMap tma_c, const bf16* __restrict__ bias, int M, int N,
-                         int K, int a_box_rows, int w_packed, const int32_t* __restrict__ tile_expert, int expert_rows,
+                         const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_ws,
+                         const bf16* __restrict__ bias, int M, int N, int K, int a_box_rows, int w_packed, const int32_t* __restrict__ tile_expert, int expert_rows,
                          const GemmMode mode, int* __restrict__ err_word) {
-  using S = GemmSmem<BN, STAGES>;
+  using S = GemmSmem<BN, STAGES, KS>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles need 1024-byte aligned bases
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -244,12 +369,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::BAR_OFF + (2 * STAGES + 4) * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  volatile int* s_last = reinterpret_cast<volatile int*>(tmem_holder + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + BN - 1) / BN;
   const int total_tiles = m_tiles * n_tiles;
   const int k_elems = mode.fp8 ? 2 * kBK : kBK;  // elements per 128-byte K block
   const int k_blocks = (K + k_elems - 1) / k_elems;
+  const int ks = mode.ks;
+  const int k_steps = (k_blocks + KS - 1) / KS;  // ring stages along K (a tail block past K reads as zeros)
+  const int kbs = (k_steps + ks - 1) / ks;       // stages per split
+  const int total_units = total_tiles * ks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -275,13 +405,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   pdl_wait();
 
   if (warp == 0) {
-    if (lane == 0) {
+    {
       // ------------------------------------------------------------------ TMA producer
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int armed = 0;  // loads issued so far (for the drain on an aborted run)
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+        const int tile = unit % total_tiles, kslice = unit / total_tiles;
+        const int kb0 = kslice * kbs, kb1 = min(k_steps, kb0 + kbs);
         const int m0 = (tile % m_tiles) * kBM;
         int n0 = (tile / m_tiles) * BN;
         if (tile_expert != nullptr) {
@@ -291,22 +423,29 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
           if (e < 0) continue;
           n0 += e * expert_rows;
         }
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
-          // for M < 128 the A box only covers the rows that exist; the rest of the 128-row operand
-          // is whatever the slot held before and only feeds output rows that are never stored
-          mbar_expect_tx(full_bar(stage), S::B_BYTES + a_box_rows * kBK * 2);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_warp(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
           const uint32_t a_dst = sbase + stage * S::STAGE_BYTES;
-          tma_load_2d(a_dst, &tma_a, kb * k_elems, m0, full_bar(stage));
-          if (!w_packed) {
-            tma_load_2d(a_dst + S::A_BYTES, &tma_b, kb * k_elems, n0, full_bar(stage));
-          } else {
-            // tile-packed weights: every 64 x 64 block is one contiguous 8 KB run
+          if (elect_one()) {
+            // for M < 128 the A box only covers the rows that exist; the rest of the 128-row operand
+            // is whatever the slot held before and only feeds output rows that are never stored
+            mbar_expect_tx(full_bar(stage), S::B_BYTES + KS * a_box_rows * kBK * 2);
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(a_dst + S::A_BYTES + j * 8192, &tma_b, 0, ((n0 / 64 + j) * k_blocks + kb) * 64,
-                          full_bar(stage));
+            for (int s = 0; s < KS; ++s)
+              tma_load_2d(a_dst + s * S::A_KB, &tma_a, (kb * KS + s) * k_elems, m0, full_bar(stage));
+            if (!w_packed) {
+#pragma unroll
+              for (int s = 0; s < KS; ++s)
+                tma_load_2d(a_dst + S::A_BYTES + s * S::B_KB, &tma_b, (kb * KS + s) * k_elems, n0, full_bar(stage));
+            } else {
+              // tile-packed weights: every 64 x 64 block is one contiguous 8 KB run
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(a_dst + S::A_BYTES + j * 8192, &tma_b, 0, ((n0 / 64 + j) * k_blocks + kb) * 64,
+                            full_bar(stage));
+            }
           }
+          __syncwarp();
           ++armed;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -324,37 +463,46 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
       // ------------------------------------------------------------------ MMA issuer
       const uint32_t idesc = mode.fp8 ? umma_idesc_e4m3(BN) : umma_idesc_bf16(BN);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int t = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+        const int tile = unit % total_tiles, kslice = unit / total_tiles;
+        const int kb0 = kslice * kbs, kb1 = min(k_steps, kb0 + kbs);
         if (tile_expert != nullptr && tile_expert[tile % m_tiles] < 0) continue;
         const int acc = t & 1;
         const uint32_t use = (uint32_t)(t >> 1);
         ++t;
-        if (!mbar_wait(tempty_bar(acc), (use & 1) ^ 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(tempty_bar(acc), (use & 1) ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_warp(full_bar(stage), phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = sbase + stage * S::STAGE_BYTES;
-          const uint64_t adesc = umma_smem_desc(a_addr);
-          const uint64_t bdesc = umma_smem_desc(a_addr + S::A_BYTES);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) {
-            // +32 bytes (2 x 16-byte units) along K inside the swizzled row per UMMA_K = 16
-            if (mode.fp8) umma_fp8(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
-            else umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+            for (int s = 0; s < KS; ++s) {
+              const uint64_t adesc = umma_smem_desc(a_addr + s * S::A_KB);
+              const uint64_t bdesc = umma_smem_desc(a_addr + S::A_BYTES + s * S::B_KB);
+#pragma unroll
+              for (int k = 0; k < kBK / 16; ++k) {
+                // +32 bytes (2 x 16-byte units) along K inside the swizzled row per UMMA_K = 16
+                if (mode.fp8) umma_fp8(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, ((kb - kb0) | s | k) != 0);
+                else umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, ((kb - kb0) | s | k) != 0);
+              }
+            }
+            umma_commit(empty_bar(stage));  // slot reusable once these MMAs have read it
           }
-          umma_commit(empty_bar(stage));  // slot reusable once these MMAs have read it
+          __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(tfull_bar(acc));  // accumulator complete
+        if (ok && elect_one()) umma_commit(tfull_bar(acc));  // accumulator complete
+        __syncwarp();
       }
     }
   } else {
@@ -362,7 +510,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     bool ok = true;
     int t = 0, ebuf = 0;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+    for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
+      const int tile = unit % total_tiles;
       if (tile_expert != nullptr && tile_expert[tile % m_tiles] < 0) continue;
       const int m0 = (tile % m_tiles) * kBM, n0 = (tile / m_tiles) * BN;
       const int acc = t & 1;
@@ -371,7 +520,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       if (!mbar_wait(tfull_bar(acc), use & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-      epilogue_slice<BN>(taddr, &tma_c, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, bias, N, lane, ebuf, mode, M);
+      if (ks == 1) {
+        epilogue_slice<BN>(taddr, &tma_c, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, bias, N, lane, ebuf, mode, M);
+      } else {
+        const bool last = splitk_dump<BN>(taddr, &tma_ws, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, mode, tile,
+                                          m0 + q * 32, n0, lane, q, ebuf, s_last);
+        // the accumulator has been read out: release it before the (longer) finishing pass
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        if (last) splitk_finish<BN>(mode, bias, m0 + q * 32, n0, M, N, lane);
+        continue;
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -397,6 +557,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
 // rows 128-255 in the peer's.  Loads of both CTAs complete on the leader's "full" barrier;
 // tcgen05.commit signals the "empty" / "accumulator full" barriers of both CTAs at once; the
 // epilogue warps of both CTAs arrive on the leader's "accumulator empty" barrier.
+__device__ __forceinline__ bool mbar_wait_cluster_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag);
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -439,6 +600,9 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
     }
   }
 }
+__device__ __forceinline__ bool mbar_wait_cluster_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait_cluster(bar, parity, abort_flag));
+}
 // TMA tile load issued by either CTA of the pair; completion bytes are counted on the barrier of
 // the pair's leader (bit 24 of a shared-window address selects the CTA inside the pair).
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* map, int x, int y,
@@ -470,10 +634,12 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16_m256(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int KS = 1>
 struct GemmSmem2 {
-  static constexpr int A_BYTES = kBM * kBK * 2;         // this CTA's 128 rows of A
-  static constexpr int B_BYTES = (BN / 2) * kBK * 2;    // this CTA's half of the W tile
+  static constexpr int A_KB = kBM * kBK * 2;            // this CTA's 128 rows of A, one K block
+  static constexpr int B_KB = (BN / 2) * kBK * 2;       // this CTA's half of the W tile
+  static constexpr int A_BYTES = KS * A_KB;
+  static constexpr int B_BYTES = KS * B_KB;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_OFF = STAGES * STAGE_BYTES;
   static constexpr int BAR_OFF = EPI_OFF + kEpiBytes;
@@ -481,12 +647,12 @@ struct GemmSmem2 {
   static_assert(TOTAL <= 232448, "exceeds the 227 KB of shared memory per CTA");
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int KS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                              const __grid_constant__ CUtensorMap tma_c, const bf16* __restrict__ bias, int M,
-                              int N, int K, int w_packed, int* __restrict__ err_word) {
-  using S = GemmSmem2<BN, STAGES>;
+                              const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_ws,
+                              const bf16* __restrict__ bias, int M, int N, int K, int w_packed, const GemmMode mode, int* __restrict__ err_word) {
+  using S = GemmSmem2<BN, STAGES, KS>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
@@ -497,6 +663,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
   auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::BAR_OFF + (2 * STAGES + 4) * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  volatile int* s_last = reinterpret_cast<volatile int*>(tmem_holder + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -505,6 +672,10 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
   const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM), n_tiles = (N + BN - 1) / BN;
   const int total_tiles = m_tiles * n_tiles;
   const int k_blocks = (K + kBK - 1) / kBK;
+  const int ks = mode.ks;
+  const int k_steps = (k_blocks + KS - 1) / KS;
+  const int kbs = (k_steps + ks - 1) / ks;
+  const int total_units = total_tiles * ks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -531,30 +702,39 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
   pdl_wait();
 
   if (warp == 0) {
-    if (lane == 0) {
+    {
       // ------------------------------------------------------------------ TMA producer (both CTAs)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+      for (int unit = pair; unit < total_units && ok; unit += n_pairs) {
+        const int tile = unit % total_tiles, kslice = unit / total_tiles;
+        const int kb0 = kslice * kbs, kb1 = min(k_steps, kb0 + kbs);
         const int m0 = (tile % m_tiles) * (2 * kBM) + (int)rank * kBM;
         const int n0 = (tile / m_tiles) * BN + (int)rank * (BN / 2);
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait_cluster(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
-          if (leader) mbar_expect_tx(full_bar(stage), 2 * S::STAGE_BYTES);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_cluster_warp(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
           const uint32_t a_dst = sbase + stage * S::STAGE_BYTES;
-          tma_load_2d_pair(a_dst, &tma_a, kb * kBK, m0, full_bar(stage));
-          if (!w_packed) {
-            tma_load_2d_pair(a_dst + S::A_BYTES, &tma_b, kb * kBK, n0, full_bar(stage));
-          } else {
-            constexpr int ROWS = BN / 2 < 64 ? BN / 2 : 64;  // rows per packed-block load
+          if (elect_one()) {
+            if (leader) mbar_expect_tx(full_bar(stage), 2 * S::STAGE_BYTES);
 #pragma unroll
-            for (int j = 0; j < (BN / 2) / ROWS; ++j) {
-              const int n = n0 + j * ROWS;
-              tma_load_2d_pair(a_dst + S::A_BYTES + j * ROWS * 128, &tma_b, 0,
-                               ((n / 64) * k_blocks + kb) * 64 + (n % 64), full_bar(stage));
+            for (int s = 0; s < KS; ++s)
+              tma_load_2d_pair(a_dst + s * S::A_KB, &tma_a, (kb * KS + s) * kBK, m0, full_bar(stage));
+            if (!w_packed) {
+#pragma unroll
+              for (int s = 0; s < KS; ++s)
+                tma_load_2d_pair(a_dst + S::A_BYTES + s * S::B_KB, &tma_b, (kb * KS + s) * kBK, n0, full_bar(stage));
+            } else {
+              constexpr int ROWS = BN / 2 < 64 ? BN / 2 : 64;  // rows per packed-block load
+#pragma unroll
+              for (int j = 0; j < (BN / 2) / ROWS; ++j) {
+                const int n = n0 + j * ROWS;
+                tma_load_2d_pair(a_dst + S::A_BYTES + j * ROWS * 128, &tma_b, 0,
+                                 ((n / 64) * k_blocks + kb) * 64 + (n % 64), full_bar(stage));
+              }
             }
           }
+          __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -564,32 +744,41 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && leader) {
+    if (leader) {
       // ------------------------------------------------------------------ MMA issuer (leader only)
       constexpr uint32_t idesc = umma_idesc_bf16_m256(BN);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int t = 0;
-      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++t) {
+      for (int unit = pair; unit < total_units && ok; unit += n_pairs, ++t) {
+        const int kslice = unit / total_tiles;
+        const int kb0 = kslice * kbs, kb1 = min(k_steps, kb0 + kbs);
         const int acc = t & 1;
         const uint32_t use = (uint32_t)(t >> 1);
-        if (!mbar_wait_cluster(tempty_bar(acc), (use & 1) ^ 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_cluster_warp(tempty_bar(acc), (use & 1) ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait_cluster(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_cluster_warp(full_bar(stage), phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = sbase + stage * S::STAGE_BYTES;
-          const uint64_t adesc = umma_smem_desc(a_addr);
-          const uint64_t bdesc = umma_smem_desc(a_addr + S::A_BYTES);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k)
-            umma_bf16_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
-          umma_commit_pair(empty_bar(stage));
+            for (int s = 0; s < KS; ++s) {
+              const uint64_t adesc = umma_smem_desc(a_addr + s * S::A_KB);
+              const uint64_t bdesc = umma_smem_desc(a_addr + S::A_BYTES + s * S::B_KB);
+#pragma unroll
+              for (int k = 0; k < kBK / 16; ++k)
+                umma_bf16_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, ((kb - kb0) | s | k) != 0);
+            }
+            umma_commit_pair(empty_bar(stage));
+          }
+          __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit_pair(tfull_bar(acc));
+        if (ok && elect_one()) umma_commit_pair(tfull_bar(acc));
+        __syncwarp();
       }
     }
   } else {
@@ -598,14 +787,26 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
     const uint32_t leader_tempty0 = map_to_cta(tempty_bar(0), 0);
     bool ok = true;
     int t = 0, ebuf = 0;
-    for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++t) {
+    for (int unit = pair; unit < total_units && ok; unit += n_pairs, ++t) {
+      const int tile = unit % total_tiles;
       const int m0 = (tile % m_tiles) * (2 * kBM) + (int)rank * kBM, n0 = (tile / m_tiles) * BN;
       const int acc = t & 1;
       const uint32_t use = (uint32_t)(t >> 1);
       if (!mbar_wait_cluster(tfull_bar(acc), use & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-      epilogue_slice<BN>(taddr, &tma_c, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, bias, N, lane, ebuf);
+      if (ks == 1) {
+        epilogue_slice<BN>(taddr, &tma_c, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, bias, N, lane, ebuf);
+      } else {
+        // one counter per (tile, CTA of the pair): each CTA finishes its own 128 rows
+        const bool last = splitk_dump<BN>(taddr, &tma_ws, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, mode,
+                                          tile * 2 + (int)rank, m0 + q * 32, n0, lane, q, ebuf, s_last);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(leader_tempty0 + 8u * acc);
+        if (last) splitk_finish<BN>(mode, bias, m0 + q * 32, n0, M, N, lane);
+        continue;
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(leader_tempty0 + 8u * acc);
@@ -657,19 +858,72 @@ static bool make_tmap(CUtensorMap* map, const void* ptr, int64_t rows, int64_t c
   return r == CUDA_SUCCESS;
 }
 
-static int* g_err_word[64] = {};
+// fp32 row-major [rows, cols], box 32 x 32 (128-byte rows), 128B swizzle: the split-K scratch.
+static bool make_tmap_f32(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
-template <int BN, int STAGES>
+static int* g_err_word[64] = {};
+static int g_k_per_stage = 2;  // preferred K blocks per ring stage for tiles narrower than 256
+
+// Split-K scratch of one device: the zero-filled fp32 accumulation area and the per-tile arrival counters.  Allocated
+// once (never during stream capture); split-K GEMMs of one device must be stream-ordered with
+// respect to one another, which holds for the single compute stream of the engine.
+constexpr size_t kSplitWsBytes = 64u << 20;
+constexpr int kSplitCounters = 16384;
+static float* g_split_ws[64] = {};
+static int* g_split_cnt[64] = {};
+
+static bool split_scratch_ready(int dev, cudaStream_t s) {
+  if (g_split_ws[dev & 63] != nullptr) return true;
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &st) != cudaSuccess || st != cudaStreamCaptureStatusNone) return false;
+  float* ws = nullptr;
+  int* cnt = nullptr;
+  if (cudaMalloc(&ws, kSplitWsBytes) != cudaSuccess) return false;
+  if (cudaMalloc(&cnt, kSplitCounters * sizeof(int)) != cudaSuccess) {
+    cudaFree(ws);
+    return false;
+  }
+  cudaMemset(cnt, 0, kSplitCounters * sizeof(int));
+  cudaMemset(ws, 0, kSplitWsBytes);  // every launch leaves the scratch zero-filled again
+  g_split_ws[dev & 63] = ws;
+  g_split_cnt[dev & 63] = cnt;
+  return true;
+}
+
+// Clamp a requested split so that every K slice is non-empty and the scratch is large enough.
+static int usable_split(int ks, int M, int N, int K, int k_per_stage, int counters_needed, int dev, cudaStream_t s) {
+  const int k_blocks = (K + kBK * k_per_stage - 1) / (kBK * k_per_stage);  // ring stages along K
+  if (ks > k_blocks) ks = k_blocks;
+  if (ks <= 1 || N % 4) return 1;
+  const int kbs = (k_blocks + ks - 1) / ks;
+  ks = (k_blocks + kbs - 1) / kbs;
+  if (ks <= 1 || counters_needed > kSplitCounters) return 1;
+  if ((size_t)M * (size_t)N * sizeof(float) > kSplitWsBytes) return 1;
+  if (!split_scratch_ready(dev, s)) return 1;
+  return ks;
+}
+
+template <int BN, int STAGES, int KS = 1>
 static int launch_gemm(const void* a, const void* w, void* c, const void* bias, int M, int N, int K, int64_t lda,
                        int64_t ldw, int64_t ldc, int max_ctas, int w_packed, cudaStream_t s,
                        const int32_t* tile_expert = nullptr, int n_experts = 1,
-                       GemmMode mode = GemmMode{nullptr, nullptr, 0, 0, 0}) {
-  using S = GemmSmem<BN, STAGES>;
+                       GemmMode mode = GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0}, int split_k = 1) {
+  using S = GemmSmem<BN, STAGES, KS>;
   int dev = 0;
   cudaGetDevice(&dev);
   static bool attr_done[64] = {};
   if (!attr_done[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, STAGES, KS>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (e != cudaSuccess) return (int)e;
     attr_done[dev & 63] = true;
@@ -686,21 +940,31 @@ static int launch_gemm(const void* a, const void* w, void* c, const void* bias, 
   if (!make_tmap(&ta, a, M, K, lda, a_box, true, mode.fp8 != 0) || !okb || !make_tmap(&tc, c, M, N, ldc, 32, false))
     return (int)cudaErrorInvalidValue;
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
-  int grid = tiles < max_ctas ? tiles : max_ctas;
-  gemm_bf16_tcgen05_kernel<BN, STAGES><<<grid, 192, S::TOTAL, s>>>(ta, tb, tc, (const bf16*)bias, M, N, K, a_box,
+  if (split_k > 1 && tile_expert == nullptr && !mode.fp8) {
+    mode.ks = usable_split(split_k, M, N, K, KS, tiles, dev, s);
+    mode.ws = g_split_ws[dev & 63];
+    mode.counters = g_split_cnt[dev & 63];
+    mode.c = (bf16*)c;
+    mode.ldc = ldc;
+  }
+  CUtensorMap tws = tc;
+  if (mode.ks > 1 && !make_tmap_f32(&tws, mode.ws, M, N)) return (int)cudaErrorInvalidValue;
+  const int units = tiles * mode.ks;
+  int grid = units < max_ctas ? units : max_ctas;
+  gemm_bf16_tcgen05_kernel<BN, STAGES, KS><<<grid, 192, S::TOTAL, s>>>(ta, tb, tc, tws, (const bf16*)bias, M, N, K, a_box,
                                                                  w_packed, tile_expert, N, mode, g_err_word[dev & 63]);
   return XLLM_LAUNCH_CHECK();
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int KS = 1>
 static int launch_gemm_pair(const void* a, const void* w, void* c, const void* bias, int M, int N, int K, int64_t lda,
-                            int64_t ldw, int64_t ldc, int max_ctas, int w_packed, cudaStream_t s) {
-  using S = GemmSmem2<BN, STAGES>;
+                            int64_t ldw, int64_t ldc, int max_ctas, int w_packed, cudaStream_t s, int split_k = 1) {
+  using S = GemmSmem2<BN, STAGES, KS>;
   int dev = 0;
   cudaGetDevice(&dev);
   static bool attr_done[64] = {};
   if (!attr_done[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_pair_kernel<BN, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_pair_kernel<BN, STAGES, KS>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (e != cudaSuccess) return (int)e;
     attr_done[dev & 63] = true;
@@ -715,9 +979,20 @@ static int launch_gemm_pair(const void* a, const void* w, void* c, const void* b
   if (!make_tmap(&ta, a, M, K, lda, kBM) || !okb || !make_tmap(&tc, c, M, N, ldc, 32, false))
     return (int)cudaErrorInvalidValue;
   const int tiles = ((M + 2 * kBM - 1) / (2 * kBM)) * ((N + BN - 1) / BN);
-  int pairs = tiles < max_ctas / 2 ? tiles : max_ctas / 2;
-  gemm_bf16_tcgen05_pair_kernel<BN, STAGES><<<2 * pairs, 192, S::TOTAL, s>>>(ta, tb, tc, (const bf16*)bias, M, N, K,
-                                                                            w_packed, g_err_word[dev & 63]);
+  GemmMode mode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0};
+  if (split_k > 1) {
+    mode.ks = usable_split(split_k, M, N, K, KS, 2 * tiles, dev, s);
+    mode.ws = g_split_ws[dev & 63];
+    mode.counters = g_split_cnt[dev & 63];
+    mode.c = (bf16*)c;
+    mode.ldc = ldc;
+  }
+  CUtensorMap tws = tc;
+  if (mode.ks > 1 && !make_tmap_f32(&tws, mode.ws, M, N)) return (int)cudaErrorInvalidValue;
+  const int units = tiles * mode.ks;
+  int pairs = units < max_ctas / 2 ? units : max_ctas / 2;
+  gemm_bf16_tcgen05_pair_kernel<BN, STAGES, KS><<<2 * pairs, 192, S::TOTAL, s>>>(ta, tb, tc, tws, (const bf16*)bias, M, N, K,
+                                                                            w_packed, mode, g_err_word[dev & 63]);
   return XLLM_LAUNCH_CHECK();
 }
 
@@ -730,9 +1005,12 @@ static int launch_gemm_pair(const void* a, const void* w, void* c, const void* b
 // w_packed: W is stored tile-packed as [N/64][K/64][64][64] (see xllm_pack_weight_bf16); needs
 // N % 64 == 0 and K % 64 == 0.  Each 64 x 64 block is then one contiguous 8 KB run, which is what
 // lets a weight-streaming (small M) GEMM pull HBM at full rate.
+// split_k: 0 = choose; 1 = off; n > 1 = cut K into (at most) n slices whose fp32 partial tiles meet
+// in a per-device scratch; the CTA that arrives last at a tile reduces and stores it.  This is what
+// fills all 148 SMs when M x N alone gives fewer tiles than SMs (decode-size batches).
 XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* bias, int M, int N, int K,
                             int64_t lda, int64_t ldw, int64_t ldc, int tile_n, int pair, int w_packed,
-                            void* stream) {
+                            int split_k, void* stream) {
   using namespace xllm;
   if (M == 0 || N == 0) return 0;
   if (K % 8 || N % 8 || lda % 8 || ldw % 8 || ldc % 8) return (int)cudaErrorInvalidValue;
@@ -747,7 +1025,30 @@ XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* b
     sms = e ? atoi(e) : 148;
     if (sms < 2 || sms > 148) sms = 148;
   }
-  if (pair < 0 || tile_n == 0) {
+  if ((pair < 0 || tile_n == 0 || split_k == 0) && M <= 512) {
+    // Decode-size batches (few row tiles).  Measured on B200: an MMA instruction costs ~75 cycles
+    // whatever its width below 128 columns, so tiles narrower than 128 waste the tensor pipe; a
+    // 128-wide tile is used while that gives every SM (or SM pair) at most one tile, else 256;
+    // left-over SMs are filled by cutting K, as long as a slice keeps enough K to amortise the
+    // reduce (~6 us for the scratch round trip).
+    const int p = pair >= 0 ? pair : (M > kBM ? 1 : 0);
+    const int rows = p ? 2 * kBM : kBM, slots = p ? sms / 2 : sms;
+    const int m_t = (M + rows - 1) / rows;
+    int tn = tile_n;
+    if (tn == 0) tn = m_t * ((N + 127) / 128) <= slots ? 128 : 256;
+    int sk = split_k;
+    if (sk == 0) {
+      const int tiles = m_t * ((N + tn - 1) / tn);
+      const int min_k = p ? 3072 : 1024;
+      sk = slots / tiles;
+      if (sk > 8) sk = 8;
+      while (sk > 1 && K / sk < min_k) --sk;
+      if (sk < 1 || (size_t)M * N * 4 > kSplitWsBytes) sk = 1;
+    }
+    pair = p;
+    tile_n = tn;
+    split_k = sk;
+  } else if (pair < 0 || tile_n == 0 || split_k == 0) {
     // Cost model: a tile costs max(operand bytes its SM must pull from L2 at ~85 GB/s per SM,
     // tensor-core time of its MMAs); a launch costs that times the number of waves.
     double best = 1e30;
@@ -760,10 +1061,9 @@ XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* b
         const int rows = p ? 2 * kBM : kBM, units = p ? sms / 2 : sms;
         const long tiles = (long)((M + rows - 1) / rows) * ((N + tn - 1) / tn);
         const long waves = (tiles + units - 1) / units;
-        const double a_rows = M < kBM ? (double)((M + 7) & ~7) : (double)kBM;
         const double b_rows = p ? tn / 2 : tn;
-        const double t_in = (a_rows + b_rows) * K * 2.0 / 85e9;
-        const double t_mma = (K / 16.0) * (tn / 2.0) / 1.6e9;  // 128 x tn x 16 per SM: tn/2 cycles
+        const double t_in = ((double)kBM + b_rows) * K * 2.0 / 85e9;
+        const double t_mma = (K / 16.0) * (tn > 150 ? tn / 2.0 : 75.0) / 1.8e9;
         const double t_epi = 128.0 * tn * 2.0 / 200e9;
         const double cost = waves * ((t_in > t_mma ? t_in : t_mma) + 0.3 * t_epi) + t_epi;
         if (cost < best) { best = cost; bp = p; bt = tn; }
@@ -771,19 +1071,35 @@ XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* b
     }
     pair = bp;
     tile_n = bt;
+    if (split_k == 0) split_k = 1;
   }
+  // narrow tiles take two K blocks per ring stage unless the weight is tile-packed (whose block
+  // addressing has no zero-filled tail) or the caller asked for the one-block form
+  const bool two = g_k_per_stage != 1 && !w_packed && K > kBK;
   if (pair) {
     switch (tile_n) {
-      case 256: return launch_gemm_pair<256, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s);
-      case 128: return launch_gemm_pair<128, 8>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s);
-      case 64: return launch_gemm_pair<64, 9>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s);
+      case 256: return launch_gemm_pair<256, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
+      case 128:
+        if (two) return launch_gemm_pair<128, 4, 2>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
+        return launch_gemm_pair<128, 8>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
+      case 64:
+        if (two) return launch_gemm_pair<64, 4, 2>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
+        return launch_gemm_pair<64, 9>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
       default: return (int)cudaErrorInvalidValue;
     }
   }
+  const GemmMode plain{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0};
+  if (two && tile_n == 128)
+    return launch_gemm<128, 3, 2>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1, plain, split_k);
+  if (two && tile_n == 64)
+    return launch_gemm<64, 4, 2>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1, plain, split_k);
   switch (tile_n) {
-    case 256: return launch_gemm<256, 4>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s);
-    case 128: return launch_gemm<128, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s);
-    case 64: return launch_gemm<64, 8>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s);
+    case 256: return launch_gemm<256, 4>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1,
+                                          GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0}, split_k);
+    case 128: return launch_gemm<128, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1,
+                                          GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0}, split_k);
+    case 64: return launch_gemm<64, 8>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1,
+                                          GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0}, split_k);
     default: return (int)cudaErrorInvalidValue;
   }
 }
@@ -816,7 +1132,7 @@ XLLM_API int xllm_gemm_fp8(const void* a, const void* w, void* c, const void* bi
   if (M == 0 || N == 0) return 0;
   if (K % 16 || N % 8 || lda % 16 || ldw % 16 || ldc % 8) return (int)cudaErrorInvalidValue;
   if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15) return (int)cudaErrorInvalidValue;
-  GemmMode mode{(const float*)a_scale, (const float*)b_scale, 1, a_per_row, b_per_col};
+  GemmMode mode{(const float*)a_scale, (const float*)b_scale, 1, a_per_row, b_per_col, 1, nullptr, nullptr, nullptr, 0};
   cudaStream_t s = (cudaStream_t)stream;
   const int mt = (M + kBM - 1) / kBM;
   int tile_n = 256;
@@ -849,6 +1165,17 @@ XLLM_API int xllm_pack_weight_bf16(void* dst, const void* src, int N, int K, int
   return XLLM_LAUNCH_CHECK();
 }
 
+// 1 = one 64-element K block per ring stage everywhere; 2 (default) = two for tiles narrower than 256.
+XLLM_API void xllm_gemm_set_k_per_stage(int n) { xllm::g_k_per_stage = n == 1 ? 1 : 2; }
+
+// Allocate the per-device split-K scratch now (call once per device before capturing CUDA graphs).
+XLLM_API int xllm_gemm_prepare() {
+  using namespace xllm;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return split_scratch_ready(dev, nullptr) ? 0 : (int)cudaErrorMemoryAllocation;
+}
+
 // 0 = no bounded wait has expired on this device since the last call; the word is cleared.
 XLLM_API int xllm_gemm_error_status() {
   using namespace xllm;
@@ -857,6 +1184,13 @@ XLLM_API int xllm_gemm_error_status() {
   if (g_err_word[dev & 63] == nullptr) return 0;
   int v = 0;
   cudaMemcpy(&v, g_err_word[dev & 63], sizeof(int), cudaMemcpyDeviceToHost);
-  if (v != 0) cudaMemset(g_err_word[dev & 63], 0, sizeof(int));
+  if (v != 0) {
+    cudaMemset(g_err_word[dev & 63], 0, sizeof(int));
+    // an aborted split-K launch may have left arrival counters half-way
+    if (g_split_cnt[dev & 63] != nullptr) {
+      cudaMemset(g_split_cnt[dev & 63], 0, kSplitCounters * sizeof(int));
+      cudaMemset(g_split_ws[dev & 63], 0, kSplitWsBytes);
+    }
+  }
   return v;
 }

@@ -180,6 +180,8 @@ class ModelRunner:
 
     def capture_graph(self, Bp):
         """Capture forward + lm_head for a padded decode batch of Bp rows."""
+        from ..ops import gemm_tcgen05
+        gemm_tcgen05.prepare()   # per-device scratch must exist before a capture starts
         off = self._graph_offsets(Bp)
         gin = torch.zeros(off[11], dtype=torch.uint8, device=self.device)
         _view(gin, off[3], Bp, torch.int32).fill_(-1)   # slots: no KV write during warm-up

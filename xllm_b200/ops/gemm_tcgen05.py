@@ -8,8 +8,10 @@ import torch
 from . import _lib
 from ._lib import I, L, P, check, ptr, stream
 
-_lib.register_signature("xllm_gemm_bf16", [P, P, P, P, I, I, I, L, L, L, I, I, I, P])
+_lib.register_signature("xllm_gemm_bf16", [P, P, P, P, I, I, I, L, L, L, I, I, I, I, P])
 _lib.register_signature("xllm_gemm_error_status", [], I)
+_lib.register_signature("xllm_gemm_prepare", [], I)
+_lib.register_signature("xllm_gemm_set_k_per_stage", [I], None)
 _lib.register_signature("xllm_pack_weight_bf16", [P, P, I, I, L, P])
 
 
@@ -54,7 +56,7 @@ def unpack_weight(pw: PackedWeight):
     return pw.data.view(N // 64, K // 64, 64, 64).permute(0, 2, 1, 3).reshape(N, K)
 
 
-def gemm_nt(x, w, bias=None, out=None, tile_n: int = 0, pair: int = -1):
+def gemm_nt(x, w, bias=None, out=None, tile_n: int = 0, pair: int = -1, split_k: int = 0):
     """y[..., N] = x[..., K] @ w[N, K]^T (+ bias).  `w` is a tensor or a PackedWeight."""
     packed = isinstance(w, PackedWeight)
     if packed:
@@ -75,9 +77,19 @@ def gemm_nt(x, w, bias=None, out=None, tile_n: int = 0, pair: int = -1):
         assert bias.dtype == torch.bfloat16 and bias.is_contiguous()
     from . import _count
     check(_lib.load().xllm_gemm_bf16(ptr(x2), w_ptr, ptr(o2), ptr(bias), M, N, K, x2.stride(0), w_ld,
-                                     o2.stride(0), tile_n, pair, int(packed), stream()), "gemm_bf16")
+                                     o2.stride(0), tile_n, pair, int(packed), split_k, stream()), "gemm_bf16")
     _count()
     return out.reshape(*x.shape[:-1], N)
+
+
+def set_k_per_stage(n: int):
+    """1 = one 64-element K block per ring stage; 2 (default) = two for tiles narrower than 256."""
+    _lib.load().xllm_gemm_set_k_per_stage(int(n))
+
+
+def prepare():
+    """Allocate the split-K scratch of the current device (before CUDA-graph capture)."""
+    check(_lib.load().xllm_gemm_prepare(), "gemm_prepare")
 
 
 def error_status() -> int:
