@@ -37,6 +37,17 @@ def test_fused_allreduce_norm(multimem):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-def test_tp_engine_matches_single_gpu():
-    out = _run("mp_tp_engine.py", 2)
+@pytest.mark.parametrize("multimem", ["1", "0"])
+def test_fused_gemm_reduce_scatter_norm(multimem):
+    """tcgen05 GEMM whose epilogue pushes tiles to the owner ranks + owner-side reduce/norm/all-gather."""
+    out = _run("mp_tp_gemm_rs.py", min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2, {"XLLM_TP_MULTIMEM": multimem})
+    assert "GEMM_RS_OK" in out
+    print(out[out.index("GEMM_RS_OK"):].splitlines()[0])
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("push_min", ["512", "8"])
+def test_tp_engine_matches_single_gpu(push_min):
+    """push_min=8 sends every prefill through the GEMM -> reduce-scatter push path."""
+    out = _run("mp_tp_engine.py", 2, {"XLLM_TP_PUSH_MIN_TOKENS": push_min})
     assert "TP_ENGINE_OK" in out

@@ -130,6 +130,17 @@ struct GemmMode {
   int* counters;
   bf16* c;      // output base and row stride (elements) for the split-K finishing pass
   int64_t ldc;
+  // Push mode (the reduce-scatter half of a tensor-parallel row-linear, fused into the GEMM): the
+  // token rows are sharded over the ranks, S rows each; the epilogue stores every finished
+  // 32-row slice of this rank's partial product straight into the owner rank's inbox
+  // [world][S][N] over NVLink (plain 16-byte peer stores) and then releases the owner's arrival
+  // counter (system-scope red.add of the row count), so the transfer of tile i overlaps the MMAs of
+  // tile i+1 and the owner can start reducing as soon as its counter is full.
+  void* const* push_bufs;  // [world] base pointers of the symmetric buffer; null = mode off
+  void* const* push_sigs;  // [world] base pointers of the signal pads
+  int64_t push_off;        // byte offset of the inbox inside the symmetric buffer
+  int64_t push_sig_idx;    // uint32 index of the arrival counter inside a signal pad
+  int push_S, push_rank, push_world;
 };
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -188,7 +199,7 @@ constexpr int kEpiBytes = 4 * 2 * kEpiBufBytes;    // 4 warps x 2 buffers
 template <int BN>
 __device__ __forceinline__ void epilogue_slice(uint32_t taddr, const CUtensorMap* tmap_c, uint32_t warp_stage,
                                                int row0, int n0, const bf16* __restrict__ bias, int N, int lane,
-                                               int& buf, const GemmMode mode = GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0},
+                                               int& buf, const GemmMode mode = GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0},
                                                int M = 0) {
   float a_s = 1.f;
   if (mode.fp8 && mode.a_scale != nullptr) {
@@ -236,6 +247,60 @@ __device__ __forceinline__ void epilogue_slice(uint32_t taddr, const CUtensorMap
       bulk_commit();
     }
     buf ^= 1;
+  }
+}
+
+// Push-mode epilogue of one warp (see GemmMode): tcgen05.ld -> bf16 -> swizzled shared memory ->
+// coalesced 16-byte stores into the owners' inboxes (4 rows x 128 bytes per warp instruction),
+// then one system-scope red.add per owner present in the slice.
+template <int BN>
+__device__ __forceinline__ void epilogue_push(uint32_t taddr, uint32_t warp_stage, int row0, int n0, int M, int N,
+                                              int lane, const GemmMode& mode) {
+  const int S = mode.push_S;
+#pragma unroll 1
+  for (int c = 0; c < BN / kEpiCols; ++c) {
+    uint32_t r[64];
+    tmem_ld32(taddr + c * kEpiCols, r);
+    tmem_ld32(taddr + c * kEpiCols + 32, r + 32);
+    tmem_ld_wait();
+    __syncwarp();  // the copy-out of the previous chunk has finished reading the staging buffer
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j * 8 + e]);
+      const bf16x8 v = pack8(f);
+      const uint4 u = *reinterpret_cast<const uint4*>(&v);
+      const uint32_t dst = warp_stage + lane * 128 + ((j ^ (lane & 7)) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w)
+                   : "memory");
+    }
+    __syncwarp();
+    const int unit = lane & 7;
+    const int col = n0 + c * kEpiCols + unit * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = i * 4 + (lane >> 3);
+      const int row = row0 + rr;
+      if (row < M && col < N) {
+        uint4 u;
+        const uint32_t src = warp_stage + rr * 128 + ((unit ^ (rr & 7)) << 4);
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "r"(src));
+        const int owner = row / S;
+        uint8_t* base = reinterpret_cast<uint8_t*>(mode.push_bufs[owner]) + mode.push_off;
+        const int64_t slot = (int64_t)mode.push_rank * S + (row - owner * S);
+        *reinterpret_cast<uint4*>(base + (slot * N + col) * 2) = u;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncwarp();
+  const int row = row0 + lane;
+  const int owner = row < M ? row / S : -1;
+  const unsigned grp = __match_any_sync(0xffffffffu, owner);
+  if (owner >= 0 && lane == __ffs(grp) - 1) {
+    uint32_t* cnt = reinterpret_cast<uint32_t*>(mode.push_sigs[owner]) + mode.push_sig_idx;
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(cnt), "r"((uint32_t)__popc(grp)) : "memory");
   }
 }
 
@@ -520,7 +585,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       if (!mbar_wait(tfull_bar(acc), use & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-      if (ks == 1) {
+      if (mode.push_bufs != nullptr) {
+        epilogue_push<BN>(taddr, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, M, N, lane, mode);
+      } else if (ks == 1) {
         epilogue_slice<BN>(taddr, &tma_c, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, bias, N, lane, ebuf, mode, M);
       } else {
         const bool last = splitk_dump<BN>(taddr, &tma_ws, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, mode, tile,
@@ -917,7 +984,7 @@ template <int BN, int STAGES, int KS = 1>
 static int launch_gemm(const void* a, const void* w, void* c, const void* bias, int M, int N, int K, int64_t lda,
                        int64_t ldw, int64_t ldc, int max_ctas, int w_packed, cudaStream_t s,
                        const int32_t* tile_expert = nullptr, int n_experts = 1,
-                       GemmMode mode = GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0}, int split_k = 1) {
+                       GemmMode mode = GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0}, int split_k = 1) {
   using S = GemmSmem<BN, STAGES, KS>;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -937,8 +1004,9 @@ static int launch_gemm(const void* a, const void* w, void* c, const void* bias, 
   const int a_box = M >= kBM ? kBM : ((M + 7) & ~7);
   const bool okb = w_packed ? make_tmap(&tb, w, (int64_t)N * (K / 64), 64, 64, 64)
                             : make_tmap(&tb, w, (int64_t)N * n_experts, K, ldw, BN, true, mode.fp8 != 0);
-  if (!make_tmap(&ta, a, M, K, lda, a_box, true, mode.fp8 != 0) || !okb || !make_tmap(&tc, c, M, N, ldc, 32, false))
-    return (int)cudaErrorInvalidValue;
+  if (!make_tmap(&ta, a, M, K, lda, a_box, true, mode.fp8 != 0) || !okb) return (int)cudaErrorInvalidValue;
+  if (mode.push_bufs != nullptr) tc = ta;  // push mode stores through peer pointers, the map is unused
+  else if (!make_tmap(&tc, c, M, N, ldc, 32, false)) return (int)cudaErrorInvalidValue;
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
   if (split_k > 1 && tile_expert == nullptr && !mode.fp8) {
     mode.ks = usable_split(split_k, M, N, K, KS, tiles, dev, s);
@@ -979,7 +1047,7 @@ static int launch_gemm_pair(const void* a, const void* w, void* c, const void* b
   if (!make_tmap(&ta, a, M, K, lda, kBM) || !okb || !make_tmap(&tc, c, M, N, ldc, 32, false))
     return (int)cudaErrorInvalidValue;
   const int tiles = ((M + 2 * kBM - 1) / (2 * kBM)) * ((N + BN - 1) / BN);
-  GemmMode mode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0};
+  GemmMode mode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0};
   if (split_k > 1) {
     mode.ks = usable_split(split_k, M, N, K, KS, 2 * tiles, dev, s);
     mode.ws = g_split_ws[dev & 63];
@@ -1088,20 +1156,44 @@ XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* b
       default: return (int)cudaErrorInvalidValue;
     }
   }
-  const GemmMode plain{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0};
+  const GemmMode plain{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0};
   if (two && tile_n == 128)
     return launch_gemm<128, 3, 2>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1, plain, split_k);
   if (two && tile_n == 64)
     return launch_gemm<64, 4, 2>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1, plain, split_k);
   switch (tile_n) {
     case 256: return launch_gemm<256, 4>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1,
-                                          GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0}, split_k);
+                                          GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0}, split_k);
     case 128: return launch_gemm<128, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1,
-                                          GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0}, split_k);
+                                          GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0}, split_k);
     case 64: return launch_gemm<64, 8>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1,
-                                          GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0}, split_k);
+                                          GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0}, split_k);
     default: return (int)cudaErrorInvalidValue;
   }
+}
+
+// Row-parallel linear fused with the scatter half of a reduce-scatter (see GemmMode "push mode").
+// a [M, K] and w [N, K] are this rank's operands; nothing is written locally: row r of the partial
+// product goes to rank r / S, into inbox[rank][r % S][:] at byte offset `inbox_off` of that rank's
+// symmetric buffer, and the rank's arrival counter (uint32 `sig_idx` of its signal pad) grows by
+// one per (row, column tile).  The owner therefore expects rows_owned * ceil(N / tile_n) * world
+// arrivals.  tile_n: 128 or 256.  peer_bufs / signal_pads: device arrays of `world` pointers.
+XLLM_API int xllm_gemm_bf16_push(const void* a, const void* w, const void* peer_bufs, const void* signal_pads,
+                                 int64_t inbox_off, int64_t sig_idx, int M, int N, int K, int64_t lda, int64_t ldw,
+                                 int S, int rank, int world, int tile_n, void* stream) {
+  using namespace xllm;
+  if (M == 0 || N == 0) return 0;
+  if (K % 8 || N % 8 || lda % 8 || ldw % 8 || (inbox_off & 15) || S <= 0 || (int64_t)S * world < M)
+    return (int)cudaErrorInvalidValue;
+  if (((uintptr_t)a | (uintptr_t)w) & 15) return (int)cudaErrorInvalidValue;
+  GemmMode mode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, (void* const*)peer_bufs,
+                (void* const*)signal_pads, inbox_off, sig_idx, S, rank, world};
+  cudaStream_t s = (cudaStream_t)stream;
+  if (tile_n == 256)
+    return launch_gemm<256, 4>(a, w, const_cast<void*>(a), nullptr, M, N, K, lda, ldw, lda, 148, 0, s, nullptr, 1, mode);
+  if (tile_n == 128)
+    return launch_gemm<128, 3, 2>(a, w, const_cast<void*>(a), nullptr, M, N, K, lda, ldw, lda, 148, 0, s, nullptr, 1, mode);
+  return (int)cudaErrorInvalidValue;
 }
 
 // Grouped (mixture-of-experts) GEMM: rows of A are grouped by expert in 128-row tiles
@@ -1132,7 +1224,7 @@ XLLM_API int xllm_gemm_fp8(const void* a, const void* w, void* c, const void* bi
   if (M == 0 || N == 0) return 0;
   if (K % 16 || N % 8 || lda % 16 || ldw % 16 || ldc % 8) return (int)cudaErrorInvalidValue;
   if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15) return (int)cudaErrorInvalidValue;
-  GemmMode mode{(const float*)a_scale, (const float*)b_scale, 1, a_per_row, b_per_col, 1, nullptr, nullptr, nullptr, 0};
+  GemmMode mode{(const float*)a_scale, (const float*)b_scale, 1, a_per_row, b_per_col, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0};
   cudaStream_t s = (cudaStream_t)stream;
   const int mt = (M + kBM - 1) / kBM;
   int tile_n = 256;

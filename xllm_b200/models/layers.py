@@ -151,6 +151,10 @@ class Linear(Module):
                 # the partial result goes to the symmetric buffer; the cross-rank sum is fused
                 # into the add+RMSNorm that follows (TpComm.allreduce_norm)
                 T = x.shape[0]
+                if comm.push_supported(x, self.weight, bias):
+                    # prefill-size batches: the GEMM's epilogue pushes each tile to the rank that
+                    # reduces those rows (GEMM -> reduce-scatter in one kernel, TpComm.push_gemm)
+                    return comm.push_gemm(x, self.weight)
                 return ops.linear(x, self.weight, bias, out=comm.partial_buffer(T))
         y = ops.linear(x, self.weight, bias)
         if self.parallel == "row" and self.reduce:

@@ -15,6 +15,7 @@ its C++ path uses NCCL, layers/common/linear.cpp:1938-1940).
 """
 from __future__ import annotations
 
+import ctypes
 import os
 from typing import Optional
 
@@ -25,6 +26,9 @@ from ..ops._lib import I, L, P, check, ptr, stream
 
 F = _lib.F
 _lib.register_signature("xllm_tp_allreduce_norm", [P, P, _lib.U64, L, L, L, P, P, P, P, I, I, I, I, I, F, I, P])
+_lib.register_signature("xllm_tp_inbox_norm", [P, P, _lib.U64, L, L, L, L, ctypes.c_uint32, P, P, P, P, I, I, I, I, I, F,
+                                               I, P])
+_lib.register_signature("xllm_gemm_bf16_push", [P, P, P, P, L, L, I, I, I, L, L, I, I, I, I, P])
 
 
 class TpComm:
@@ -52,6 +56,9 @@ class TpComm:
         # flag slots live in the upper half of the signal pad (the lower half is left to torch's own
         # barrier helpers)
         self.sig_off = self.hdl.signal_pad_size // 8
+        self.counter_idx = self.sig_off + 32   # arrival counter of the push-mode GEMM (flags use [0, world))
+        self._pushed = None                     # (T, expected arrivals) of a push-mode GEMM awaiting its reduction
+        self.push_min_tokens = int(os.environ.get("XLLM_TP_PUSH_MIN_TOKENS", "512"))
         self.state = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.x = self.buf[: self.max_tokens * row_bytes].view(torch.bfloat16).view(self.max_tokens, hidden)
@@ -70,7 +77,21 @@ class TpComm:
 
     def _launch(self, T, residual, weight, eps, mode):
         S = (T + self.world - 1) // self.world
-        n_ctas = max(1, min(S, 148))
+        # two 256-thread CTAs fit on an SM (127 registers per thread), and every CTA works on one row at
+        # a time, so 296 co-resident CTAs double the rows in flight
+        n_ctas = max(1, min(S, 296))
+        if self._pushed is not None:
+            pT, expected = self._pushed
+            self._pushed = None
+            assert pT == T, "the reduction must follow the pushed GEMM of the same token count"
+            check(_lib.load().xllm_tp_inbox_norm(self.peer_ptrs, self.signal_ptrs, self.mc_base, self.x_off,
+                                                 self.out_off, self.sig_off, self.counter_idx, expected,
+                                                 ptr(self.state), ptr(residual), ptr(weight), ptr(self.err), T,
+                                                 self.hidden, self.rank, self.world, mode, float(eps), n_ctas,
+                                                 stream()), "tp_inbox_norm")
+            from ..ops import _count
+            _count()
+            return self.out[:T]
         check(_lib.load().xllm_tp_allreduce_norm(self.peer_ptrs, self.signal_ptrs, self.mc_base, self.x_off,
                                                  self.out_off, self.sig_off, ptr(self.state), ptr(residual),
                                                  ptr(weight), ptr(self.err), T, self.hidden, self.rank,
@@ -78,6 +99,51 @@ class TpComm:
         from ..ops import _count
         _count()
         return self.out[:T]
+
+    # ---- fused row-parallel GEMM -> reduce-scatter -> (+residual, RMSNorm) -> all-gather
+    def gemm_rs_norm(self, x_local: torch.Tensor, weight: torch.Tensor, residual_shard, norm_weight, eps: float,
+                     tile_n: int = 0):
+        """out[:T] = rmsnorm(sum_ranks(x_local @ weight^T) + residual) * w on every rank.
+
+        Two launches: the tcgen05 GEMM whose epilogue pushes each finished tile into the owner
+        rank's inbox over NVLink while the next tile's MMAs run (`xllm_gemm_bf16_push`), and the
+        owner-side kernel that waits for its arrival counter, reduces, normalises and broadcasts
+        (`xllm_tp_inbox_norm`).  The reference does this as cuBLAS + NCCL all-reduce + a norm kernel
+        (layers/common/linear.cpp:1938-1940); its sequence-parallel NPU path has the fused
+        matmul+reduce-scatter shape (common/flash_comm1_context.*).  With `norm_weight=None` the
+        result is the plain sum."""
+        T = x_local.shape[0]
+        self.push_gemm(x_local, weight, tile_n)
+        if norm_weight is None:
+            return self.allreduce(T)
+        return self.allreduce_norm(T, residual_shard, norm_weight, eps)
+
+    def push_gemm(self, x_local: torch.Tensor, weight: torch.Tensor, tile_n: int = 0):
+        """Launch the row-parallel GEMM in push mode; the next `allreduce` / `allreduce_norm` call
+        (same T) completes the operation from the inbox instead of running its opening barrier."""
+        T, K = x_local.shape
+        N = weight.shape[0]
+        assert N == self.hidden and T <= self.max_tokens and self._pushed is None
+        assert x_local.stride(1) == 1 and weight.stride(1) == 1
+        S = (T + self.world - 1) // self.world
+        if tile_n == 0:
+            tile_n = 256 if T > 512 else 128
+        n_tiles = (N + tile_n - 1) // tile_n
+        b, e, _ = self.shard(T)
+        check(_lib.load().xllm_gemm_bf16_push(ptr(x_local), ptr(weight), self.peer_ptrs, self.signal_ptrs, self.x_off,
+                                              self.counter_idx, T, N, K, x_local.stride(0), weight.stride(0), S,
+                                              self.rank, self.world, tile_n, stream()), "gemm_bf16_push")
+        from ..ops import _count
+        _count()
+        self._pushed = (T, (e - b) * n_tiles * self.world)
+        return self.x[:T]  # placeholder with the right shape; the data lives in the owners' inboxes
+
+    def push_supported(self, x, weight, bias) -> bool:
+        """Whether a row-parallel linear of this shape should take the push path."""
+        return (bias is None and x.dim() == 2 and x.shape[0] >= self.push_min_tokens and x.dtype == torch.bfloat16
+                and weight.dtype == torch.bfloat16 and x.stride(1) == 1 and weight.stride(1) == 1
+                and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
+                and not torch.cuda.is_current_stream_capturing())
 
     def allreduce_norm(self, T: int, residual_shard: torch.Tensor, weight: torch.Tensor, eps: float):
         """x[:T] (partials of all ranks) -> out[:T] = rmsnorm(sum + residual) * w on every rank;
