@@ -1,0 +1,55 @@
+"""Speculative decoding (n-gram drafter + one-pass verification) on the tiny CPU model: the token
+stream must be identical to plain greedy decoding, and repetitive text must be accepted in bulk."""
+import numpy as np
+import torch
+
+from xllm_b200 import LLM, SamplingParams
+from xllm_b200.engine.speculative import NgramDrafter
+
+
+def _llm(**kw):
+    return LLM("tiny", devices="cpu", dtype="float32", block_size=16, num_blocks=128, max_seqs_per_batch=8,
+               max_tokens_per_batch=256, enable_graph=False, enable_schedule_overlap=False, **kw)
+
+
+def test_ngram_drafter_finds_latest_match():
+    d = NgramDrafter(3, max_ngram=3)
+    toks = np.array([5, 6, 7, 8, 9, 1, 2, 6, 7, 3, 4, 6, 7], dtype=np.int32)
+    assert d.propose_one(toks).tolist() == [3, 4, 6]       # latest "6 7" is followed by 3 4 6
+    assert d.propose_one(np.array([1, 2, 3], dtype=np.int32)).tolist() == [3, 3, 3]  # no match: repeat
+
+
+def test_speculative_greedy_equals_plain_greedy():
+    g = torch.Generator().manual_seed(3)
+    base = torch.randint(0, 32000, (12,), generator=g).tolist()
+    prompts = [base * 3, torch.randint(0, 32000, (40,), generator=g).tolist(), (base[:5] * 6)[:29]]
+    sp = SamplingParams(max_tokens=24, temperature=0.0, ignore_eos=True)
+    plain = [o.outputs[0].token_ids for o in _llm().generate(prompts, sp)]
+    for k in (1, 3):
+        llm = _llm(num_speculative_tokens=k)
+        outs = llm.generate(prompts, sp)
+        assert [o.outputs[0].token_ids for o in outs] == plain
+        assert all(len(o.outputs[0].token_ids) == 24 for o in outs)
+        assert llm.engine.spec.steps > 0
+
+
+def test_speculative_accepts_repetition_and_stops_mid_row():
+    # a model-free check of the multi-token bookkeeping: a stop token inside an accepted run ends
+    # the sequence there and drops the rest of the run
+    llm = _llm(num_speculative_tokens=3)
+    eng = llm.engine
+    prompt = list(range(100, 120))
+    eng.add_request("r", prompt, temperature=0.0, max_tokens=50, stop_token_ids=[777], eos_token_id=-1)
+    got = []
+    while eng.has_unfinished():
+        batches = eng.scheduler.schedule()
+        if not batches:
+            break
+        b = batches[0]
+        if b.n_prefill > 0:
+            evs = eng._finish(eng.runner.execute(b))
+        else:
+            evs = eng.scheduler.process_output_multi(b.batch_id, np.array([1, 2, 777, 4], dtype=np.int64),
+                                                     np.array([4], dtype=np.int32))
+        got += [e.token for e in evs if e.token >= 0]
+    assert got[1:] == [1, 2, 777] and len(got) == 4

@@ -158,6 +158,17 @@ PYBIND11_MODULE(_rt, m) {
       .def_property_readonly("repetition_penalty", [](const Batch& b) { return to_np(b.rep_pen); })
       .def_property_readonly("seeds", [](const Batch& b) { return to_np(b.seeds); })
       .def_property_readonly("seq_ids", [](const Batch& b) { return to_np(b.seq_ids); })
+      // the last `max_n` tokens (prompt + generated) of sequence `i` of the batch (all when max_n <= 0)
+      .def("history",
+           [](const Batch& b, int64_t i, int64_t max_n) {
+             const std::vector<int32_t>& t = b.seqs.at((size_t)i)->tokens;
+             const size_t n = max_n > 0 && (size_t)max_n < t.size() ? (size_t)max_n : t.size();
+             py::array_t<int32_t> a((py::ssize_t)n);
+             std::memcpy(a.mutable_data(), t.data() + (t.size() - n), n * sizeof(int32_t));
+             return a;
+           },
+           py::arg("i"), py::arg("max_n") = 0)
+      .def("request_id", [](const Batch& b, int64_t i) { return b.seqs.at((size_t)i)->request->request_id; })
       // Pack every per-step device input into ONE caller-owned (pinned) byte buffer so that a step
       // costs a single H2D copy.  Segments are 16-byte aligned, in this order:
       //   tokens i64[T] | positions i64[T] | sample_rows i64[NS] | slots i32[T] | kv_lens i32[S] |
@@ -285,6 +296,21 @@ PYBIND11_MODULE(_rt, m) {
              return s.process_output(batch_id, toks.data(), (int64_t)toks.size(), lp);
            },
            py::arg("batch_id"), py::arg("next_tokens"), py::arg("logprobs") = py::none())
+      .def("process_output_multi",
+           [](Scheduler& s, int64_t batch_id, py::array_t<int64_t, py::array::c_style | py::array::forcecast> toks,
+              py::array_t<int32_t, py::array::c_style | py::array::forcecast> counts, py::object logprobs) {
+             const float* lp = nullptr;
+             py::array_t<float, py::array::c_style | py::array::forcecast> lpa;
+             if (!logprobs.is_none()) {
+               lpa = logprobs.cast<py::array_t<float, py::array::c_style | py::array::forcecast>>();
+               lp = lpa.data();
+             }
+             int64_t total = 0;
+             for (py::ssize_t i = 0; i < counts.size(); ++i) total += std::max<int32_t>(counts.data()[i], 1);
+             if (total > (int64_t)toks.size()) throw std::invalid_argument("process_output_multi: too few tokens");
+             return s.process_output_multi(batch_id, toks.data(), counts.data(), (int64_t)counts.size(), lp);
+           },
+           py::arg("batch_id"), py::arg("tokens"), py::arg("counts"), py::arg("logprobs") = py::none())
       .def("take_pending_events", &Scheduler::take_pending_events)
       .def("pause", &Scheduler::pause)
       .def("resume", &Scheduler::resume)

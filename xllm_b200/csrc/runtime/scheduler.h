@@ -176,6 +176,17 @@ class Scheduler {
   // next_tokens: one id per sample row of the batch (in order).  logprobs may be null.
   std::vector<OutputEvent> process_output(int64_t batch_id, const int64_t* next_tokens, int64_t n,
                                           const float* logprobs) {
+    return process_output_multi(batch_id, next_tokens, nullptr, n, logprobs);
+  }
+
+  // Speculative decoding: sample row r appends counts[r] >= 1 tokens (the accepted draft tokens
+  // followed by the bonus / corrected token), read consecutively from `tokens` (and `logprobs`).
+  // counts == null means one token per row.  The KV of every appended token but the last is in the
+  // cache already (the verification pass wrote it), which keeps the invariant
+  // kv_computed == num_tokens - 1 for sequences in decode.  A stop condition met in the middle of
+  // a row drops the rest of that row.
+  std::vector<OutputEvent> process_output_multi(int64_t batch_id, const int64_t* tokens, const int32_t* counts,
+                                                int64_t n_rows, const float* logprobs) {
     std::vector<OutputEvent> ev;
     ev.swap(pending_events_);
     auto it = in_flight_batches_.find(batch_id);
@@ -194,28 +205,37 @@ class Scheduler {
           s->stage = SeqStage::DECODE;
           release_siblings(s);
         }
-      } else {
+      } else if (counts == nullptr) {
         s->kv_computed += 1;
       }
     }
-    const int64_t ns = std::min<int64_t>(n, (int64_t)b.sample_seq.size());
+    const int64_t ns = std::min<int64_t>(n_rows, (int64_t)b.sample_seq.size());
+    int64_t cursor = 0;
     for (int64_t r = 0; r < ns; ++r) {
-      Sequence* s = b.seqs[b.sample_seq[r]];
+      const int32_t cnt = counts ? std::max<int32_t>(counts[r], 1) : 1;
+      const int64_t base = cursor;
+      cursor += cnt;
+      const int32_t si = b.sample_seq[r];
+      Sequence* s = b.seqs[si];
       if (s->pending_samples > 0) s->pending_samples--;
       if (s->finished()) continue;  // finished (or aborted) while this step was in flight
-      const int32_t tok = (int32_t)next_tokens[r];
-      s->tokens.push_back(tok);
-      if (s->first_token_time == 0) s->first_token_time = t;
-      s->last_token_time = t;
-      const bool want_lp = s->request->sampling.logprobs && logprobs != nullptr;
-      if (want_lp) s->logprobs.push_back(logprobs[r]);
-      const FinishReason fr = check_stop(*s, s->request->stopping);
-      if (fr != FinishReason::NONE) {
-        remove_from_queues(s);
-        finish_seq(s, fr);
+      for (int32_t j = 0; j < cnt; ++j) {
+        const int32_t tok = (int32_t)tokens[base + j];
+        s->tokens.push_back(tok);
+        if (counts != nullptr && si < b.n_decode) s->kv_computed += 1;
+        if (s->first_token_time == 0) s->first_token_time = t;
+        s->last_token_time = t;
+        const bool want_lp = s->request->sampling.logprobs && logprobs != nullptr;
+        if (want_lp) s->logprobs.push_back(logprobs[base + j]);
+        const FinishReason fr = check_stop(*s, s->request->stopping);
+        if (fr != FinishReason::NONE) {
+          remove_from_queues(s);
+          finish_seq(s, fr);
+        }
+        ev.push_back(make_event(s, tok, want_lp ? logprobs[base + j] : 0.f, want_lp));
+        if (s->request->all_finished()) ev.back().request_finished = true;
+        if (s->finished()) break;
       }
-      ev.push_back(make_event(s, tok, want_lp ? logprobs[r] : 0.f, want_lp));
-      if (s->request->all_finished()) ev.back().request_finished = true;
     }
     // free blocks of sequences that finished earlier but still had this step in flight
     for (Sequence* s : b.seqs)

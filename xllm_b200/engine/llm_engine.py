@@ -56,6 +56,7 @@ class EngineConfig:
     dp_size: int = 1
     ep_size: int = 1
     num_speculative_tokens: int = 0
+    speculative_method: str = "ngram"   # drafter: "ngram" (suffix / prompt lookup, no draft model)
     draft_model: str = ""
     activation_reserve_bytes: int = 0   # 0: estimated from max_tokens_per_batch
 
@@ -135,6 +136,14 @@ class LLMEngine:
         sc.num_speculative_tokens = cfg.num_speculative_tokens
         self.scheduler = rt.Scheduler(sc)
         self._pending: Optional[StepOutput] = None
+        self.spec = None
+        if cfg.num_speculative_tokens > 0:
+            if cfg.enable_schedule_overlap:
+                raise ValueError("speculative decoding needs enable_schedule_overlap=False: the number of tokens "
+                                 "a step appends is only known after verification")
+            from .speculative import SpecDecoder, make_drafter
+            self.spec = SpecDecoder(self, make_drafter(cfg.speculative_method, cfg.num_speculative_tokens, self),
+                                    cfg.num_speculative_tokens)
         self.steps = 0
         self.step_log: List[tuple] = []
         self.record_steps = False
@@ -217,7 +226,10 @@ class LLMEngine:
                 events = self._finish(self._pending)
             self._pending = new
         else:
-            if batch is not None:
+            if batch is not None and self.spec is not None and batch.n_prefill == 0 and batch.n_decode > 0:
+                flat, counts, lp = self.spec.step(batch)
+                events = self.scheduler.process_output_multi(batch.batch_id, flat, counts, lp)
+            elif batch is not None:
                 out = self.runner.execute(batch)
                 events = self._finish(out)
             else:
@@ -280,4 +292,5 @@ class LLMEngine:
             "graph_replays": self.runner.graph_replays,
             "h2d_bytes": self.runner.h2d_bytes,
             "d2h_bytes": self.runner.d2h_bytes,
+            "spec_acceptance_rate": self.spec.acceptance_rate if self.spec is not None else 0.0,
         }

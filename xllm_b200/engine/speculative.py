@@ -1,0 +1,161 @@
+"""Speculative decoding: draft k tokens per sequence, verify them with ONE target forward.
+
+Parity: `SpeculativeEngine` / `SpeculativeWorkerImpl` with its MTP, Eagle3 and suffix drafters
+(xllm/core/distributed_runtime/speculative_engine.h:96-120, runtime/mtp_worker_impl.cpp:1245-1850,
+runtime/suffix_worker_impl.*) and `RejectionSampler` (framework/sampling/rejection_sampler.cpp:65-360).
+
+Flow of a decode step for B sequences and k draft tokens:
+  1. the drafter proposes d_1..d_k for every sequence,
+  2. the target model runs once over [last token, d_1..d_k] of every sequence: these are k+1-token
+     "prompt chunks" against the paged cache, so the prefill attention kernel handles them and the
+     KV of every position is written as a side effect,
+  3. verification keeps the longest prefix of drafts the target agrees with (greedy: equality
+     with the argmax; sampling: the rejection rule of the device kernel `xllm_spec_verify`) and adds
+     the target's own next token, so every step yields between 1 and k+1 tokens,
+  4. the scheduler appends the accepted tokens; KV written for rejected drafts is simply
+     overwritten by later steps (the sequence's kv length never counted it).
+Steps that contain prompt chunks run unspeculated.
+
+Drafters:
+  * `NgramDrafter` — prompt-lookup / suffix matching on the sequence's own tokens, no model,
+  * `DraftModelDrafter` — any small causal LM sharing the tokenizer (run without a KV cache of its
+    own over a short window; enough for Eagle-style single-layer drafts).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..models.layers import AttentionMetadata
+from ..ops import spec as spec_ops
+
+
+class NgramDrafter:
+    """Propose the continuation of the most recent earlier occurrence of the longest suffix
+    (up to `max_ngram` tokens) of the sequence.  Without a match the last token is repeated, which
+    costs nothing but a rejected draft."""
+
+    name = "ngram"
+
+    def __init__(self, k: int, max_ngram: int = 4, min_ngram: int = 1, window: int = 2048):
+        self.k, self.max_ngram, self.min_ngram, self.window = k, max_ngram, min_ngram, window
+
+    def propose_one(self, toks: np.ndarray) -> np.ndarray:
+        k = self.k
+        n = len(toks)
+        out = np.full(k, toks[-1] if n else 0, dtype=np.int64)
+        for g in range(min(self.max_ngram, n - 1), self.min_ngram - 1, -1):
+            suffix = toks[n - g:]
+            # candidate starts i with toks[i:i+g] == suffix and i + g < n, latest first
+            first = np.nonzero(toks[: n - g] == suffix[0])[0]
+            for i in first[::-1]:
+                if i + g <= n - 1 and np.array_equal(toks[i:i + g], suffix):
+                    cont = toks[i + g:i + g + k]
+                    if len(cont) > 0:
+                        out[: len(cont)] = cont
+                        if len(cont) < k:
+                            out[len(cont):] = cont[-1]
+                        return out
+        return out
+
+    def propose(self, batch, n_rows: int, **_) -> np.ndarray:
+        return np.stack([self.propose_one(batch.history(i, self.window)) for i in range(n_rows)])
+
+    def observe(self, *a, **kw):
+        pass
+
+
+class DraftModelDrafter:
+    """Greedy k-token drafts from a small causal LM run over the last `window` tokens of every
+    sequence without a persistent cache (callable: tokens [B, W] -> logits [B, W, V])."""
+
+    name = "draft_model"
+
+    def __init__(self, fn, k: int, window: int = 64):
+        self.fn, self.k, self.window = fn, k, window
+
+    def propose(self, batch, n_rows: int, **_) -> np.ndarray:
+        out = np.zeros((n_rows, self.k), dtype=np.int64)
+        for i in range(n_rows):
+            ctx = list(batch.history(i, self.window))
+            for j in range(self.k):
+                logits = self.fn(torch.tensor([ctx[-self.window:]], dtype=torch.int64))
+                t = int(logits[0, -1].argmax())
+                out[i, j] = t
+                ctx.append(t)
+        return out
+
+    def observe(self, *a, **kw):
+        pass
+
+
+class SpecDecoder:
+    """Runs the verification pass on the engine's model runner."""
+
+    def __init__(self, engine, drafter, k: int):
+        self.engine, self.runner, self.drafter, self.k = engine, engine.runner, drafter, k
+        self.block_size = engine.cfg.block_size
+        self.proposed = 0
+        self.accepted = 0
+        self.steps = 0
+
+    @property
+    def acceptance_rate(self) -> float:
+        return self.accepted / self.proposed if self.proposed else 0.0
+
+    def step(self, batch):
+        """`batch` is a decode-only batch.  Returns (tokens_flat int64, counts int32, logprobs|None)."""
+        k, bs = self.k, self.block_size
+        B = batch.n_decode
+        dev = self.runner.device
+        kv0 = np.asarray(batch.kv_lens)[:B].astype(np.int64)       # context incl. the last token
+        last = np.asarray(batch.tokens)[:B].astype(np.int64)
+        drafts = self.drafter.propose(batch, B).astype(np.int64)    # [B, k]
+        toks = np.concatenate([last[:, None], drafts], axis=1)      # [B, k+1]
+        pos = (kv0 - 1)[:, None] + np.arange(k + 1)[None, :]        # position of every input token
+        bt = np.asarray(batch.block_tables)[:B]
+        slots = (bt[np.arange(B)[:, None], pos // bs].astype(np.int64) * bs + pos % bs).astype(np.int32)
+        T = B * (k + 1)
+        t_tokens = torch.from_numpy(toks.reshape(-1)).to(dev)
+        t_pos = torch.from_numpy(pos.reshape(-1)).to(dev)
+        meta = AttentionMetadata(
+            n_decode=0, n_prefill=B,
+            slots=torch.from_numpy(slots.reshape(-1)).to(dev),
+            block_table=torch.from_numpy(np.ascontiguousarray(bt)).to(dev),
+            kv_lens=torch.from_numpy((kv0 + k).astype(np.int32)).to(dev),
+            cu_q=torch.arange(0, T + 1, k + 1, dtype=torch.int32, device=dev),
+            max_q_len=k + 1, max_kv_len=int(kv0.max()) + k)
+        hidden = self.runner.model.forward(t_tokens, t_pos, meta, self.runner.kv_caches)
+        logits = self.runner.model.logits(hidden).float().view(B, k + 1, -1)
+        temperature = np.asarray(batch.temperature)[:B]
+        greedy = temperature <= 0
+        d_dev = torch.from_numpy(drafts).to(dev)
+        if greedy.all():
+            tgt = logits.argmax(-1)                                           # [B, k+1]
+            agree = (tgt[:, :k] == d_dev).to(torch.int32)
+            n_acc = torch.cumprod(agree, dim=1).sum(1)                        # accepted drafts per row
+            counts = (n_acc + 1).to(torch.int32)
+            out = tgt                                                         # tokens 0..n_acc are the target's own
+        else:
+            t = torch.from_numpy(np.where(greedy, 1.0, temperature).astype(np.float32)).to(dev)
+            probs = torch.softmax(logits / t.view(B, 1, 1), dim=-1).contiguous()
+            out, counts = spec_ops.verify(d_dev, probs, None, torch.from_numpy(greedy).to(dev),
+                                          seed=int(batch.seeds[0]), offset=self.runner.sample_offset)
+            self.runner.sample_offset += 4
+        counts_h = counts.cpu().numpy().astype(np.int32)
+        out_h = out.cpu().numpy()
+        flat = np.concatenate([out_h[i, : counts_h[i]] for i in range(B)]).astype(np.int64)
+        self.drafter.observe(batch, B, hidden.view(B, k + 1, -1), counts_h)
+        self.proposed += B * k
+        self.accepted += int(counts_h.sum()) - B
+        self.steps += 1
+        return flat, counts_h, None
+
+
+def make_drafter(kind: str, k: int, engine=None, **kw):
+    if kind in ("ngram", "suffix", "prompt_lookup"):
+        return NgramDrafter(k, **kw)
+    raise ValueError(f"unknown drafter {kind!r}")
