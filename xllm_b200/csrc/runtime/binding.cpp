@@ -113,7 +113,9 @@ PYBIND11_MODULE(_rt, m) {
       .def_readwrite("enable_schedule_overlap", &SchedulerConfig::enable_schedule_overlap)
       .def_readwrite("enable_online_preempt_offline", &SchedulerConfig::enable_online_preempt_offline)
       .def_readwrite("dp_size", &SchedulerConfig::dp_size)
-      .def_readwrite("num_speculative_tokens", &SchedulerConfig::num_speculative_tokens);
+      .def_readwrite("num_speculative_tokens", &SchedulerConfig::num_speculative_tokens)
+      .def_readwrite("max_decode_batch", &SchedulerConfig::max_decode_batch)
+      .def_readwrite("hold_finished_blocks", &SchedulerConfig::hold_finished_blocks);
 
   py::enum_<PauseMode>(m, "PauseMode")
       .value("KEEP", PauseMode::KEEP)
@@ -283,6 +285,11 @@ PYBIND11_MODULE(_rt, m) {
            py::arg("sampling"), py::arg("stopping"), py::arg("n") = 1, py::arg("priority") = 0,
            py::arg("deadline") = 0.0, py::arg("offline") = false, py::arg("stream") = false)
       .def("abort_request", &Scheduler::abort_request)
+      .def("adopt_prefilled", &Scheduler::adopt_prefilled, py::arg("request_id"), py::arg("tokens"),
+           py::arg("num_prompt_tokens"), py::arg("sampling"), py::arg("stopping"), py::arg("priority") = 0,
+           py::arg("offline") = false, py::arg("stream") = false)
+      .def("held_blocks", &Scheduler::held_blocks)
+      .def("release_held", &Scheduler::release_held)
       .def("schedule", &Scheduler::schedule, py::call_guard<py::gil_scoped_release>())
       .def("process_output",
            [](Scheduler& s, int64_t batch_id, py::array_t<int64_t, py::array::c_style | py::array::forcecast> toks,

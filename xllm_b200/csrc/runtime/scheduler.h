@@ -50,6 +50,9 @@ struct SchedulerConfig {
   int32_t dp_size = 1;
   int32_t num_speculative_tokens = 0;  // extra KV slots reserved per decode step
   int32_t max_decode_batch = 0;        // 0: max_seqs_per_batch
+  // PD disaggregation, prefill side: a sequence that finishes keeps its KV blocks until
+  // release_held() so that they can be pushed to the decode instance first.
+  bool hold_finished_blocks = false;
 };
 
 enum class PauseMode : int { KEEP = 0, ABORT = 1, WAIT = 2 };
@@ -135,6 +138,57 @@ class Scheduler {
     if (!(cfg_.enable_prefix_cache && n > 1))
       for (int32_t i = 1; i < n; ++i) enqueue_waiting(r->seqs[i].get());
     return true;
+  }
+
+  // PD disaggregation, decode side: take over a request whose prompt was prefilled elsewhere.
+  // `tokens` = prompt + the first generated token; KV of all but the last token is (about to be)
+  // in the blocks returned here, which the caller fills through the KV transfer.  The sequence
+  // enters the running queue in decode stage.  Returns an empty vector when blocks are short.
+  std::vector<int32_t> adopt_prefilled(const std::string& id, const std::vector<int32_t>& tokens,
+                                       int32_t num_prompt_tokens, const SamplingParams& sp, const StoppingParams& st,
+                                       int32_t priority, bool offline, bool stream) {
+    std::vector<int32_t> none;
+    if (requests_.count(id) || (int32_t)tokens.size() < 2 || num_prompt_tokens < 1 ||
+        num_prompt_tokens >= (int32_t)tokens.size())
+      return none;
+    BlockManager& bm = *bm_[0];
+    const int32_t need = ((int32_t)tokens.size() + 1 + cfg_.num_speculative_tokens + cfg_.block_size - 1) / cfg_.block_size;
+    std::vector<int32_t> blocks = bm.allocate(need);
+    if ((int32_t)blocks.size() < need) return none;
+    auto req = std::make_unique<Request>();
+    req->request_id = id;
+    req->sampling = sp;
+    req->stopping = st;
+    req->priority = priority;
+    req->offline = offline;
+    req->stream = stream;
+    req->arrival_time = now_seconds();
+    auto s = std::make_unique<Sequence>();
+    s->seq_id = next_seq_id_++;
+    s->request = req.get();
+    s->tokens = tokens;
+    s->num_prompt_tokens = num_prompt_tokens;
+    s->kv_computed = (int32_t)tokens.size() - 1;
+    s->blocks = blocks;
+    s->stage = SeqStage::DECODE;
+    s->first_token_time = req->arrival_time;
+    Sequence* sp_ = s.get();
+    req->seqs.push_back(std::move(s));
+    requests_.emplace(id, std::move(req));
+    running_.push_back(sp_);
+    return blocks;
+  }
+
+  // Blocks of a finished sequence that hold_finished_blocks kept alive (empty if none).
+  std::vector<int32_t> held_blocks(const std::string& id) const {
+    auto it = held_.find(id);
+    return it == held_.end() ? std::vector<int32_t>() : it->second;
+  }
+  void release_held(const std::string& id) {
+    auto it = held_.find(id);
+    if (it == held_.end()) return;
+    bm_[0]->free_blocks(it->second);
+    held_.erase(it);
   }
 
   bool abort_request(const std::string& id) {
@@ -293,6 +347,7 @@ class Scheduler {
   int64_t num_preemptions() const { return preemptions_; }
 
  private:
+  std::unordered_map<std::string, std::vector<int32_t>> held_;
   struct InFlight {
     std::vector<Sequence*> seqs;
     std::vector<int32_t> q_lens, sample_seq;
@@ -357,6 +412,13 @@ class Scheduler {
 
   void release_blocks(Sequence* s) {
     if (s->blocks.empty()) return;
+    if (cfg_.hold_finished_blocks && s->finished() && s->finish_reason != FinishReason::ABORT && s->index == 0 &&
+        !held_.count(s->request->request_id)) {
+      held_[s->request->request_id] = s->blocks;  // ownership moves to the hold table
+      s->blocks.clear();
+      s->cached_blocks = 0;
+      return;
+    }
     bm_[s->dp_rank]->free_blocks(s->blocks);
     s->blocks.clear();
     s->cached_blocks = 0;

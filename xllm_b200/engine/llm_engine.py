@@ -67,7 +67,7 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float16": torch.
 
 class LLMEngine:
     def __init__(self, cfg: EngineConfig, ps: Optional[ParallelState] = None, model=None,
-                 model_args: Optional[ModelArgs] = None):
+                 model_args: Optional[ModelArgs] = None, hold_finished_blocks: bool = False):
         self.cfg = cfg
         self.ps = ps or single()
         rt = _rt()
@@ -134,6 +134,7 @@ class LLMEngine:
         sc.enable_schedule_overlap = cfg.enable_schedule_overlap
         sc.dp_size = 1  # one scheduler instance per DP replica
         sc.num_speculative_tokens = cfg.num_speculative_tokens
+        sc.hold_finished_blocks = hold_finished_blocks   # PD disaggregation, prefill side
         self.scheduler = rt.Scheduler(sc)
         self._pending: Optional[StepOutput] = None
         self.spec = None
