@@ -57,6 +57,10 @@ PYBIND11_MODULE(_rt, m) {
            },
            py::arg("tokens"), py::arg("blocks"), py::arg("start_block") = 0, py::arg("extra") = 0)
       .def("reset_prefix_cache", &BlockManager::reset_prefix_cache)
+      .def("set_track_evictions", &BlockManager::set_track_evictions)
+      .def("take_evictions", &BlockManager::take_evictions)
+      .def("lookup", &BlockManager::lookup)
+      .def("insert_cached", &BlockManager::insert_cached)
       .def("ref_count", &BlockManager::ref_count)
       .def("is_cached", &BlockManager::is_cached)
       .def_property_readonly("num_free_blocks", &BlockManager::num_free_blocks)
@@ -329,6 +333,8 @@ PYBIND11_MODULE(_rt, m) {
       .def_property_readonly("num_running", &Scheduler::num_running)
       .def_property_readonly("num_requests", &Scheduler::num_requests)
       .def_property_readonly("num_preemptions", &Scheduler::num_preemptions)
+      .def("block_manager", [](Scheduler& s, int dp) -> BlockManager& { return s.block_manager(dp); },
+           py::arg("dp") = 0, py::return_value_policy::reference_internal)
       .def("block_stats", [](Scheduler& s, int dp) { return s.block_manager(dp).stats(); }, py::arg("dp") = 0)
       .def("kv_utilization", [](Scheduler& s, int dp) { return s.block_manager(dp).utilization(); },
            py::arg("dp") = 0);

@@ -10,6 +10,7 @@
 // shared).  `allocate` takes free blocks first and evicts from the cold end of the LRU list only
 // when it must, so a cache hit costs nothing until memory is actually short.
 #pragma once
+#include <tuple>
 #include <algorithm>
 #include <cstdint>
 #include <list>
@@ -140,6 +141,44 @@ class BlockManager {
     }
   }
 
+  // ---- hooks for a second (host-memory) tier of the prefix cache
+  // With tracking on, every eviction is logged as (block, hash) so that the owner of the cache
+  // tensors can save the block's contents before the block is written again.
+  void set_track_evictions(bool on) { track_evictions_ = on; }
+  std::vector<std::tuple<int32_t, uint64_t, uint64_t>> take_evictions() {
+    std::vector<std::tuple<int32_t, uint64_t, uint64_t>> out;
+    out.swap(evicted_);
+    return out;
+  }
+  // Device block that caches `h`, or -1.
+  int32_t lookup(uint64_t lo, uint64_t hi) const {
+    Hash128 h;
+    h.lo = lo;
+    h.hi = hi;
+    auto it = table_.find(h);
+    return it == table_.end() ? -1 : it->second;
+  }
+  // Take a block, register it under `h` and leave it cached and unreferenced (most recently
+  // used): the caller then fills it from the host tier.  -1 when no block can be had or the hash is
+  // already cached.
+  int32_t insert_cached(uint64_t lo, uint64_t hi) {
+    Hash128 h;
+    h.lo = lo;
+    h.hi = hi;
+    if (!prefix_ || table_.find(h) != table_.end() || num_free_blocks() < 1) return -1;
+    if (free_.empty()) evict_one();
+    const int32_t b = free_.back();
+    free_.pop_back();
+    Meta& m = meta_[b];
+    m.ref = 0;
+    m.cached = true;
+    m.hash = h;
+    table_.emplace(h, b);
+    lru_.push_front(b);
+    m.lru_it = lru_.begin();
+    return b;
+  }
+
   int32_t ref_count(int32_t b) const { return meta_[b].ref; }
   bool is_cached(int32_t b) const { return meta_[b].cached; }
 
@@ -174,6 +213,7 @@ class BlockManager {
     m.cached = false;
     free_.push_back(b);
     stats_evictions_++;
+    if (track_evictions_) evicted_.emplace_back(b, m.hash.lo, m.hash.hi);
   }
 
   int32_t num_blocks_, block_size_;
@@ -183,6 +223,8 @@ class BlockManager {
   std::list<int32_t> lru_;  // front = most recently released
   std::unordered_map<Hash128, int32_t, Hash128Hasher> table_;
   int64_t stats_queries_ = 0, stats_hit_blocks_ = 0, stats_query_blocks_ = 0, stats_evictions_ = 0;
+  bool track_evictions_ = false;
+  std::vector<std::tuple<int32_t, uint64_t, uint64_t>> evicted_;
 };
 
 }  // namespace xllm

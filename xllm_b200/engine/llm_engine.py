@@ -56,6 +56,7 @@ class EngineConfig:
     dp_size: int = 1
     ep_size: int = 1
     num_speculative_tokens: int = 0
+    host_kv_blocks: int = 0             # > 0: keep evicted prefix-cache blocks in host memory (second tier)
     speculative_method: str = "ngram"   # drafter: "ngram" (suffix / prompt lookup, no draft model)
     draft_model: str = ""
     activation_reserve_bytes: int = 0   # 0: estimated from max_tokens_per_batch
@@ -137,6 +138,11 @@ class LLMEngine:
         sc.hold_finished_blocks = hold_finished_blocks   # PD disaggregation, prefill side
         self.scheduler = rt.Scheduler(sc)
         self._pending: Optional[StepOutput] = None
+        self.host_tier = None
+        if cfg.host_kv_blocks > 0 and cfg.enable_prefix_cache:
+            from .host_tier import HostKVTier
+            self.host_tier = HostKVTier(self.runner.kv_caches, cfg.host_kv_blocks, self.scheduler.block_manager(0), rt,
+                                        cfg.block_size)
         self.spec = None
         if cfg.num_speculative_tokens > 0:
             if cfg.enable_schedule_overlap:
@@ -203,6 +209,8 @@ class LLMEngine:
         toks = [int(t) for t in prompt_token_ids]
         if len(toks) >= self.max_model_len:
             return False
+        if self.host_tier is not None:
+            self.host_tier.prefetch(toks)
         return self.scheduler.add_request(request_id, toks, sp, st, n, priority, deadline, offline, stream)
 
     def abort(self, request_id: str) -> bool:
@@ -221,6 +229,8 @@ class LLMEngine:
         events = []
         batches = self.scheduler.schedule()
         batch = batches[0] if batches else None
+        if self.host_tier is not None:
+            self.host_tier.save_evicted()   # before this step's kernels overwrite the evicted blocks
         if self.cfg.enable_schedule_overlap:
             new = self.runner.execute(batch) if batch is not None else None
             if self._pending is not None:
