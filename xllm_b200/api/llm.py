@@ -205,6 +205,21 @@ class LLM:
         return outs
 
     # ------------------------------------------------------------------ control
+    def beam_search(self, prompts, beam_width: int = 4, max_tokens: int = 16, length_penalty: float = 1.0,
+                    ignore_eos: bool = False):
+        """Beam search for every prompt (token-id lists or strings); returns, per prompt, the
+        `beam_width` best continuations as `BeamOutput`s (xllm/pybind/llm.py beam_search)."""
+        from ..engine.beam import beam_search
+        outs = []
+        for p in (prompts if isinstance(prompts, (list, tuple)) and not (prompts and isinstance(prompts[0], int)) else [prompts]):
+            ids = self._encode(p) if isinstance(p, str) else [int(t) for t in p]
+            res = beam_search(self.engine, ids, beam_width, max_tokens, length_penalty, ignore_eos=ignore_eos)
+            if self.tokenizer is not None:
+                for r in res:
+                    r.text = self.tokenizer.decode(r.token_ids)
+            outs.append(res)
+        return outs
+
     def sleep(self, level: int = 1):
         self.engine.pause("KEEP")
 
