@@ -138,6 +138,7 @@ class LLMEngine:
         sc.hold_finished_blocks = hold_finished_blocks   # PD disaggregation, prefill side
         self.scheduler = rt.Scheduler(sc)
         self._pending: Optional[StepOutput] = None
+        self.grammar = None
         self.host_tier = None
         if cfg.host_kv_blocks > 0 and cfg.enable_prefix_cache:
             from .host_tier import HostKVTier
@@ -186,7 +187,7 @@ class LLMEngine:
                     max_tokens=16, ignore_eos=False, stop_token_ids=None, stop_sequences=None,
                     frequency_penalty=0.0, presence_penalty=0.0, repetition_penalty=1.0,
                     logprobs=False, top_logprobs=0, seed=None, n=1, priority=0, deadline=0.0,
-                    offline=False, stream=False, eos_token_id=None) -> bool:
+                    offline=False, stream=False, eos_token_id=None, json_object=False) -> bool:
         rt = self.rt
         sp = rt.SamplingParams()
         sp.temperature = float(temperature)
@@ -211,7 +212,38 @@ class LLMEngine:
             return False
         if self.host_tier is not None:
             self.host_tier.prefetch(toks)
+        if json_object:
+            if self.grammar is None:
+                raise ValueError("json_object needs set_grammar_vocab() (the token strings of the tokenizer)")
+            if self.cfg.enable_schedule_overlap:
+                raise ValueError("constrained decoding needs enable_schedule_overlap=False")
+            self.grammar.start(request_id)
         return self.scheduler.add_request(request_id, toks, sp, st, n, priority, deadline, offline, stream)
+
+    def set_grammar_vocab(self, token_text, eos_token_id=None, top_n: int = 64):
+        """Enable `json_object=True` requests: `token_text[i]` is the text of token i."""
+        from .grammar import GrammarFilter
+        self.grammar = GrammarFilter(token_text, top_n, self.args.eos_token_id if eos_token_id is None else eos_token_id)
+        self.runner.logits_hook = self._grammar_hook
+
+    def _grammar_hook(self, batch, logits):
+        if not self.grammar.state:
+            return
+        seq_of_row = batch.sample_seq
+        for r in range(int(batch.n_samples)):
+            rid = batch.request_id(int(seq_of_row[r]))
+            if rid in self.grammar.state:
+                self.grammar.filter_row(rid, logits[r])
+
+    def _grammar_advance(self, events):
+        if self.grammar is None or not self.grammar.state:
+            return
+        for ev in events:
+            if ev.request_id in self.grammar.state:
+                if ev.token >= 0:
+                    self.grammar.advance(ev.request_id, int(ev.token))
+                if ev.request_finished:
+                    self.grammar.forget(ev.request_id)
 
     def abort(self, request_id: str) -> bool:
         return self.scheduler.abort_request(request_id)
@@ -245,6 +277,7 @@ class LLMEngine:
                 events = self._finish(out)
             else:
                 events = self.scheduler.take_pending_events()
+        self._grammar_advance(events)
         if batch is not None:
             self.steps += 1
             if self.record_steps:

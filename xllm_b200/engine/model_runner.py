@@ -99,6 +99,7 @@ class ModelRunner:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.graph_replays = 0
+        self.logits_hook = None
         self.graph_launches_per_replay: Dict[int, int] = {}
         # CUDA graphs
         self.buckets = graph_buckets or default_buckets(max_seqs)
@@ -269,6 +270,8 @@ class ModelRunner:
         top_p = _view(src, off[9], NS, torch.float32)
         if batch.any_penalty:
             self._apply_penalties(batch, logits)
+        if self.logits_hook is not None:
+            self.logits_hook(batch, logits)   # e.g. grammar masks of constrained requests
         want_lp = batch.any_logprobs
         if batch.all_greedy and not want_lp:
             ids, lp = ops.sample(logits, None, None, None)
