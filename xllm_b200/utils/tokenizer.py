@@ -39,6 +39,9 @@ class TokenizerWrapper:
         return self.impl.token_to_id(tok)
 
     def incremental_decoder(self, stops=None, skip_special=True):
+        if not isinstance(self.impl, self._rt.BpeTokenizer):
+            from .tokenizer_extra import PyIncrementalDecoder
+            return PyIncrementalDecoder(self.impl, skip_special)
         return self._rt.IncrementalDecoder(self.impl, list(stops or []), skip_special)
 
     def apply_chat_template(self, messages, tools=None, add_generation_prompt=True, enable_thinking=True,
@@ -79,6 +82,15 @@ def load_tokenizer(model_dir: str, model_type: str = "") -> Optional[TokenizerWr
             with open(c) as f:
                 model_type = json.load(f).get("model_type", "")
     tj = os.path.join(model_dir, "tokenizer.json")
+    spm_file = os.path.join(model_dir, "tokenizer.model")
+    rwkv = [x for x in os.listdir(model_dir) if x.startswith("rwkv_vocab") and x.endswith(".txt")]
+    if not os.path.exists(tj) and os.path.exists(spm_file):
+        from .tokenizer_extra import SentencePieceTokenizer
+        return TokenizerWrapper(SentencePieceTokenizer(spm_file, bool(cfg.get("add_bos_token")),
+                                                       bool(cfg.get("add_eos_token"))), model_dir, cfg, model_type)
+    if not os.path.exists(tj) and rwkv:
+        from .tokenizer_extra import RwkvTokenizer
+        return TokenizerWrapper(RwkvTokenizer(os.path.join(model_dir, rwkv[0])), model_dir, cfg, model_type)
     tok = _rt.BpeTokenizer()
     if os.path.exists(tj):
         tok.load_hf_file(tj)
