@@ -46,6 +46,14 @@ def test_fused_gemm_reduce_scatter_norm(multimem):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_all_to_all():
+    """Dispatch / combine over peer memory around the grouped GEMMs against a one-rank reference."""
+    out = _run("mp_ep_a2a.py", min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2)
+    assert "EP_A2A_OK" in out
+    print(out[out.index("EP_A2A_OK"):].splitlines()[0])
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("push_min", ["512", "8"])
 def test_tp_engine_matches_single_gpu(push_min):
     """push_min=8 sends every prefill through the GEMM -> reduce-scatter push path."""
