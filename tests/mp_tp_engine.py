@@ -23,15 +23,32 @@ def hf_names(model):
             base = n[: -len("gate_up_proj.weight")]
             yield base + "gate_proj.weight", g
             yield base + "up_proj.weight", u
+        elif n.endswith("experts.gate_up"):
+            base = n[: -len("gate_up")]
+            for e in range(t.shape[0]):
+                g, u = t[e].chunk(2)
+                yield f"{base}{e}.gate_proj.weight", g
+                yield f"{base}{e}.up_proj.weight", u
+        elif n.endswith("experts.down"):
+            base = n[: -len("down")]
+            for e in range(t.shape[0]):
+                yield f"{base}{e}.down_proj.weight", t[e]
         else:
             yield n, t
 
 
 def main():
-    ps = init_parallel()
+    import os
+    moe = os.environ.get("MODEL", "dense") == "moe"
+    ps = init_parallel(ep_size=int(os.environ.get("WORLD_SIZE", "1")) if moe else 1)
     args = ModelArgs(model_type="qwen3", vocab_size=32000, hidden_size=1024, num_hidden_layers=3,
                      num_attention_heads=8, num_key_value_heads=2, head_dim=128, intermediate_size=3072,
                      tie_word_embeddings=False, max_position_embeddings=4096)
+    if moe:
+        args = ModelArgs(model_type="qwen3_moe", vocab_size=32000, hidden_size=1024, num_hidden_layers=3,
+                         num_attention_heads=8, num_key_value_heads=2, head_dim=128, intermediate_size=3072,
+                         num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256, norm_topk_prob=True,
+                         tie_word_embeddings=False, max_position_embeddings=4096)
     full = create_model(args, torch.bfloat16, ps.device, single())
     full.init_random(seed=7)
     weights = list(hf_names(full))
@@ -62,7 +79,7 @@ def main():
     assert ps.comm.error_status() == 0
     dist.barrier()
     if ps.rank == 0:
-        print("TP_ENGINE_OK", flush=True)
+        print("TP_ENGINE_OK", "moe-ep-a2a" if moe else "dense", flush=True)
     dist.destroy_process_group()
 
 

@@ -59,3 +59,11 @@ def test_tp_engine_matches_single_gpu(push_min):
     """push_min=8 sends every prefill through the GEMM -> reduce-scatter push path."""
     out = _run("mp_tp_engine.py", 2, {"XLLM_TP_PUSH_MIN_TOKENS": push_min})
     assert "TP_ENGINE_OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_moe_engine_with_expert_parallel_all_to_all():
+    """Qwen3-MoE-shaped model, TP=EP=2: prefill through the all-to-all path, decode graphs through the
+    replicate path; tokens must match the single-GPU engine."""
+    out = _run("mp_tp_engine.py", 2, {"MODEL": "moe"})
+    assert "TP_ENGINE_OK moe-ep-a2a" in out

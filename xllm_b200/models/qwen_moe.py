@@ -82,6 +82,8 @@ class SparseMoeBlock(Module):
                 shared_out = None
         comm = self.ps.comm
         out = comm.partial_buffer(T) if (comm is not None and x.is_cuda) else None
+        if self._use_a2a(x, comm):
+            return self._forward_a2a(x, logits, shared_out, comm, out)
         if x.is_cuda and (self._ws is None or self._ws.max_tokens < T):
             self._ws = moe_ops.MoeWorkspace(max(T, 256), self.top_k, a.num_experts, self.e_local, a.hidden_size,
                                             self.i_local, x.device, x.dtype)
@@ -91,6 +93,42 @@ class SparseMoeBlock(Module):
         if out is None and self.ps.tp_size > 1:
             y = self.ps.all_reduce(y)
         return y
+
+    # ---- expert parallelism by all-to-all (parallel/ep.py): every rank routes the token rows it owns
+    # in the sequence-sharded residual stream, tokens visit the owners of their experts and come
+    # back; the rows land in this rank's part of the partial buffer (zeros elsewhere), so the fused
+    # all-reduce + norm that follows assembles the full activation without summing duplicates.
+    def _use_a2a(self, x, comm) -> bool:
+        import os
+        return (self.ep > 1 and x.is_cuda and comm is not None and self.ep == self.ps.tp_size
+                and os.environ.get("XLLM_EP_MODE", "a2a") == "a2a" and not torch.cuda.is_current_stream_capturing())
+
+    def _forward_a2a(self, x, logits, shared_out, comm, out):
+        a = self.args
+        T = x.shape[0]
+        ep = getattr(self.ps, "ep_comm", None)
+        if ep is None:
+            from ..parallel.ep import EpComm
+            ep = EpComm(self.ps.tp_group, self.ps.tp_rank, self.ps.tp_size, x.device, a.num_experts, a.hidden_size,
+                        self.top_k, max_local_tokens=comm.max_tokens // self.ps.tp_size + 1)
+            self.ps.ep_comm = ep
+        b, e, _ = comm.shard(T)
+        out.zero_()
+        if shared_out is not None:
+            out.copy_(shared_out)            # TP-sharded shared expert: a partial sum over all rows
+        if e > b:
+            ep.moe(x[b:e], logits[b:e], self.w_gate_up, self.w_down, a.scoring_func, self.bias, a.n_group, a.topk_group,
+                   a.norm_topk_prob, a.routed_scaling_factor, None, out=self._a2a_rows(e - b, x))
+            out[b:e] += self._rows[: e - b]
+        else:
+            ep.moe(x[:0], logits[:0], self.w_gate_up, self.w_down, a.scoring_func, self.bias, a.n_group, a.topk_group,
+                   a.norm_topk_prob, a.routed_scaling_factor, None, out=x[:0])   # idle ranks still join the exchange
+        return out
+
+    def _a2a_rows(self, n, x):
+        if getattr(self, "_rows", None) is None or self._rows.shape[0] < n:
+            self._rows = torch.empty(max(n, 64), x.shape[1], dtype=x.dtype, device=x.device)
+        return self._rows[:n]
 
     __call__ = forward
 
