@@ -90,3 +90,27 @@ def test_gemm_one_k_block_per_stage(M, N, K, tile_n, pair, split_k):
         g.set_k_per_stage(2)
     assert g.error_status() == 0
     assert bool(((y.float() - ref).abs() <= tol).all())
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 1024, 4096), (256, 4096, 4096), (300, 512, 200), (129, 264, 1352), (64, 512, 64),
+                                   (200, 384, 128)])
+@pytest.mark.parametrize("tile_n,pair,split_k", [(64, 0, 1), (128, 0, 1), (128, 0, 3), (64, 1, 1), (128, 1, 2)])
+@pytest.mark.parametrize("dual", [True, False])
+def test_gemm_dual_issue_and_single_issue(M, N, K, tile_n, pair, split_k, dual):
+    """Narrow tiles: two MMA-issuing warps with one accumulator each (summed in the epilogue), and
+    the single-issuer form of the same kernels; K = 64 / 128 gives units of one ring stage, where
+    the second accumulator is never written and must not be read."""
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    b = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    ref = x.float() @ w.float().T + b.float()
+    tol = 3e-2 + 1e-2 * ref.abs()
+    g.set_dual_issue(dual)
+    try:
+        for _ in range(2):
+            y = g.gemm_nt(x, w, bias=b, tile_n=tile_n, pair=pair, split_k=split_k)
+            assert g.error_status() == 0
+            assert bool(((y.float() - ref).abs() <= tol).all())
+    finally:
+        g.set_dual_issue(False)

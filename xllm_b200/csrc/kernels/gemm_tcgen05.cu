@@ -189,6 +189,15 @@ __device__ __forceinline__ void bulk_wait_read() {
 }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// r[i] += TMEM[taddr2 + i] for 32 columns: the second accumulator of a dual-issuer tile.
+__device__ __forceinline__ void tmem_add32(uint32_t taddr2, uint32_t* r) {
+  uint32_t t[32];
+  tmem_ld32(taddr2, t);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(t[i]));
+}
+
 constexpr int kEpiCols = 64;                       // columns per epilogue chunk (128 bytes of bf16)
 constexpr int kEpiBufBytes = 32 * kEpiCols * 2;    // one warp's chunk: 32 rows x 64 cols
 constexpr int kEpiBytes = 4 * 2 * kEpiBufBytes;    // 4 warps x 2 buffers
@@ -200,7 +209,7 @@ template <int BN>
 __device__ __forceinline__ void epilogue_slice(uint32_t taddr, const CUtensorMap* tmap_c, uint32_t warp_stage,
                                                int row0, int n0, const bf16* __restrict__ bias, int N, int lane,
                                                int& buf, const GemmMode mode = GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0},
-                                               int M = 0) {
+                                               int M = 0, uint32_t taddr2 = 0) {
   float a_s = 1.f;
   if (mode.fp8 && mode.a_scale != nullptr) {
     const int r = row0 + lane;
@@ -212,6 +221,10 @@ __device__ __forceinline__ void epilogue_slice(uint32_t taddr, const CUtensorMap
     tmem_ld32(taddr + c * kEpiCols, r);
     tmem_ld32(taddr + c * kEpiCols + 32, r + 32);
     tmem_ld_wait();
+    if (taddr2 != 0) {
+      tmem_add32(taddr2 + c * kEpiCols, r);
+      tmem_add32(taddr2 + c * kEpiCols + 32, r + 32);
+    }
     if (lane == 0) bulk_wait_read<1>();  // the store that last read this buffer has finished reading
     __syncwarp();
     const uint32_t sb = warp_stage + buf * kEpiBufBytes;
@@ -255,7 +268,7 @@ __device__ __forceinline__ void epilogue_slice(uint32_t taddr, const CUtensorMap
 // then one system-scope red.add per owner present in the slice.
 template <int BN>
 __device__ __forceinline__ void epilogue_push(uint32_t taddr, uint32_t warp_stage, int row0, int n0, int M, int N,
-                                              int lane, const GemmMode& mode) {
+                                              int lane, const GemmMode& mode, uint32_t taddr2 = 0) {
   const int S = mode.push_S;
 #pragma unroll 1
   for (int c = 0; c < BN / kEpiCols; ++c) {
@@ -263,6 +276,10 @@ __device__ __forceinline__ void epilogue_push(uint32_t taddr, uint32_t warp_stag
     tmem_ld32(taddr + c * kEpiCols, r);
     tmem_ld32(taddr + c * kEpiCols + 32, r + 32);
     tmem_ld_wait();
+    if (taddr2 != 0) {
+      tmem_add32(taddr2 + c * kEpiCols, r);
+      tmem_add32(taddr2 + c * kEpiCols + 32, r + 32);
+    }
     __syncwarp();  // the copy-out of the previous chunk has finished reading the staging buffer
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -316,12 +333,13 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32
 template <int BN>
 __device__ __forceinline__ bool splitk_dump(uint32_t taddr, const CUtensorMap* tmap_ws, uint32_t warp_stage,
                                             const GemmMode& mode, int counter_idx, int row0, int n0, int lane,
-                                            int q, int& buf, volatile int* s_last) {
+                                            int q, int& buf, volatile int* s_last, uint32_t taddr2 = 0) {
 #pragma unroll 1
   for (int c = 0; c < BN / 32; ++c) {
     uint32_t r[32];
     tmem_ld32(taddr + c * 32, r);
     tmem_ld_wait();
+    if (taddr2 != 0) tmem_add32(taddr2 + c * 32, r);
     if (lane == 0) bulk_wait_read<1>();
     __syncwarp();
     const uint32_t sb = warp_stage + buf * kEpiBufBytes;
@@ -416,13 +434,22 @@ struct GemmSmem {
   static_assert(TOTAL <= 232448, "exceeds the 227 KB of shared memory per CTA");
 };
 
-template <int BN, int STAGES, int KS>
-__global__ void __launch_bounds__(192, 1)
+template <int BN, int STAGES, int KS, bool DUAL>
+__global__ void __launch_bounds__(DUAL ? 224 : 192, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_ws,
                          const bf16* __restrict__ bias, int M, int N, int K, int a_box_rows, int w_packed, const int32_t* __restrict__ tile_expert, int expert_rows,
                          const GemmMode mode, int* __restrict__ err_word) {
   using S = GemmSmem<BN, STAGES, KS>;
+  // DUAL: a second MMA-issuing warp (warp 6) owns the odd ring stages and accumulates them into an
+  // accumulator of its own; the epilogue adds the two.  One issuing warp spends ~500 cycles per stage
+  // on waits, commits and issue latency, which hides under 256-wide MMAs but not under narrow ones.
+  // Ownership goes by STAGE, not by step within a tile: a warp then waits on each of its barriers
+  // every pass of the ring, and a parity wait is only meaningful for a waiter that never skips a
+  // phase of the barrier (with an even ring, stage parity = parity of the global step count).
+  constexpr int NACC = DUAL ? 2 : 1;
+  static_assert(!DUAL || STAGES % 2 == 0, "stage ownership by parity needs an even ring");
+  static_assert(2 * NACC * BN <= 512, "TMEM has 512 columns");
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles need 1024-byte aligned bases
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -452,7 +479,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(tfull_bar(a), 1);
+      mbar_init(tfull_bar(a), NACC);
       mbar_init(tempty_bar(a), 4);
     }
     *abort_flag = 0;
@@ -460,7 +487,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   }
   if (warp == 1) {  // TMEM allocation is a warp-wide operation
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
-                 "r"(2 * BN));
+                 "r"(2 * NACC * BN));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   tc_fence_before();
@@ -527,9 +554,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || (DUAL && warp == 6)) {
     {
-      // ------------------------------------------------------------------ MMA issuer
+      // ------------------------------------------------------------------ MMA issuer(s)
+      const int mw = warp == 1 ? 0 : 1;  // which issuer this warp is
       const uint32_t idesc = mode.fp8 ? umma_idesc_e4m3(BN) : umma_idesc_bf16(BN);
       int stage = 0;
       uint32_t phase = 0;
@@ -544,8 +572,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         ++t;
         if (!mbar_wait_warp(tempty_bar(acc), (use & 1) ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + (acc * NACC + mw) * BN;
+        bool fresh = true;  // this issuer has not written its accumulator for this unit yet
         for (int kb = kb0; kb < kb1; ++kb) {
+          if (DUAL && (stage & 1) != mw) {  // the other issuer's stage
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            continue;
+          }
           if (!mbar_wait_warp(full_bar(stage), phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = sbase + stage * S::STAGE_BYTES;
@@ -557,13 +590,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
 #pragma unroll
               for (int k = 0; k < kBK / 16; ++k) {
                 // +32 bytes (2 x 16-byte units) along K inside the swizzled row per UMMA_K = 16
-                if (mode.fp8) umma_fp8(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, ((kb - kb0) | s | k) != 0);
-                else umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, ((kb - kb0) | s | k) != 0);
+                if (mode.fp8) umma_fp8(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, !fresh || (s | k) != 0);
+                else umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, !fresh || (s | k) != 0);
               }
             }
             umma_commit(empty_bar(stage));  // slot reusable once these MMAs have read it
           }
           __syncwarp();
+          fresh = false;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (ok && elect_one()) umma_commit(tfull_bar(acc));  // accumulator complete
@@ -575,23 +609,32 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     bool ok = true;
     int t = 0, ebuf = 0;
+    int steps_done = 0;  // ring steps of the units before this one: its parity says who owns the first stage
     for (int unit = blockIdx.x; unit < total_units && ok; unit += gridDim.x) {
-      const int tile = unit % total_tiles;
+      const int tile = unit % total_tiles, kslice = unit / total_tiles;
       if (tile_expert != nullptr && tile_expert[tile % m_tiles] < 0) continue;
       const int m0 = (tile % m_tiles) * kBM, n0 = (tile / m_tiles) * BN;
+      const int n_steps = min(k_steps, kslice * kbs + kbs) - kslice * kbs;
       const int acc = t & 1;
       const uint32_t use = (uint32_t)(t >> 1);
       ++t;
       if (!mbar_wait(tfull_bar(acc), use & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      uint32_t taddr = tmem_base + acc * NACC * BN + ((uint32_t)(q * 32) << 16);
+      uint32_t taddr2 = 0u;
+      if (DUAL) {
+        // which accumulators this unit wrote: both from two steps on, else the owner of its only stage
+        if (n_steps >= 2) taddr2 = taddr + BN;
+        else if (steps_done & 1) taddr += BN;
+        steps_done += n_steps;
+      }
       if (mode.push_bufs != nullptr) {
-        epilogue_push<BN>(taddr, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, M, N, lane, mode);
+        epilogue_push<BN>(taddr, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, M, N, lane, mode, taddr2);
       } else if (ks == 1) {
-        epilogue_slice<BN>(taddr, &tma_c, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, bias, N, lane, ebuf, mode, M);
+        epilogue_slice<BN>(taddr, &tma_c, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, bias, N, lane, ebuf, mode, M, taddr2);
       } else {
         const bool last = splitk_dump<BN>(taddr, &tma_ws, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, mode, tile,
-                                          m0 + q * 32, n0, lane, q, ebuf, s_last);
+                                          m0 + q * 32, n0, lane, q, ebuf, s_last, taddr2);
         // the accumulator has been read out: release it before the (longer) finishing pass
         tc_fence_before();
         __syncwarp();
@@ -611,7 +654,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   if (threadIdx.x == 0 && *abort_flag && err_word != nullptr) atomicExch(err_word, 1);
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * NACC * BN));
   }
 }
 
@@ -714,12 +757,15 @@ struct GemmSmem2 {
   static_assert(TOTAL <= 232448, "exceeds the 227 KB of shared memory per CTA");
 };
 
-template <int BN, int STAGES, int KS>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+template <int BN, int STAGES, int KS, bool DUAL>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(DUAL ? 224 : 192, 1)
 gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                               const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_ws,
                               const bf16* __restrict__ bias, int M, int N, int K, int w_packed, const GemmMode mode, int* __restrict__ err_word) {
   using S = GemmSmem2<BN, STAGES, KS>;
+  constexpr int NACC = DUAL ? 2 : 1;  // accumulators per tile: one per MMA-issuing warp of the leader
+  static_assert(2 * NACC * BN <= 512, "TMEM has 512 columns");
+  static_assert(!DUAL || STAGES % 2 == 0, "stage ownership by parity needs an even ring");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
@@ -750,7 +796,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(tfull_bar(a), 1);
+      mbar_init(tfull_bar(a), NACC);
       mbar_init(tempty_bar(a), 8);  // 4 epilogue warps in each CTA of the pair
     }
     *abort_flag = 0;
@@ -758,7 +804,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
-                 "r"(2 * BN));
+                 "r"(2 * NACC * BN));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
   }
   tc_fence_before();
@@ -810,9 +856,10 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
         while (clock64() - t0 < 20000000LL) {}  // bounded grace period for copies still in flight
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || (DUAL && warp == 6)) {
     if (leader) {
-      // ------------------------------------------------------------------ MMA issuer (leader only)
+      // ------------------------------------------------------------------ MMA issuer(s) (leader only)
+      const int mw = warp == 1 ? 0 : 1;
       constexpr uint32_t idesc = umma_idesc_bf16_m256(BN);
       int stage = 0;
       uint32_t phase = 0;
@@ -825,8 +872,13 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
         const uint32_t use = (uint32_t)(t >> 1);
         if (!mbar_wait_cluster_warp(tempty_bar(acc), (use & 1) ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + (acc * NACC + mw) * BN;
+        bool fresh = true;
         for (int kb = kb0; kb < kb1; ++kb) {
+          if (DUAL && (stage & 1) != mw) {
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            continue;
+          }
           if (!mbar_wait_cluster_warp(full_bar(stage), phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = sbase + stage * S::STAGE_BYTES;
@@ -837,11 +889,12 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
               const uint64_t bdesc = umma_smem_desc(a_addr + S::A_BYTES + s * S::B_KB);
 #pragma unroll
               for (int k = 0; k < kBK / 16; ++k)
-                umma_bf16_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, ((kb - kb0) | s | k) != 0);
+                umma_bf16_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, !fresh || (s | k) != 0);
             }
             umma_commit_pair(empty_bar(stage));
           }
           __syncwarp();
+          fresh = false;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (ok && elect_one()) umma_commit_pair(tfull_bar(acc));
@@ -854,20 +907,29 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
     const uint32_t leader_tempty0 = map_to_cta(tempty_bar(0), 0);
     bool ok = true;
     int t = 0, ebuf = 0;
+    int steps_done = 0;
     for (int unit = pair; unit < total_units && ok; unit += n_pairs, ++t) {
-      const int tile = unit % total_tiles;
+      const int tile = unit % total_tiles, kslice = unit / total_tiles;
       const int m0 = (tile % m_tiles) * (2 * kBM) + (int)rank * kBM, n0 = (tile / m_tiles) * BN;
+      const int n_steps = min(k_steps, kslice * kbs + kbs) - kslice * kbs;
       const int acc = t & 1;
       const uint32_t use = (uint32_t)(t >> 1);
       if (!mbar_wait_cluster(tfull_bar(acc), use & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      uint32_t taddr = tmem_base + acc * NACC * BN + ((uint32_t)(q * 32) << 16);
+      uint32_t taddr2 = 0u;
+      if (DUAL) {
+        if (n_steps >= 2) taddr2 = taddr + BN;
+        else if (steps_done & 1) taddr += BN;
+        steps_done += n_steps;
+      }
       if (ks == 1) {
-        epilogue_slice<BN>(taddr, &tma_c, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, bias, N, lane, ebuf);
+        epilogue_slice<BN>(taddr, &tma_c, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, bias, N, lane, ebuf,
+                           GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0}, 0, taddr2);
       } else {
         // one counter per (tile, CTA of the pair): each CTA finishes its own 128 rows
         const bool last = splitk_dump<BN>(taddr, &tma_ws, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, mode,
-                                          tile * 2 + (int)rank, m0 + q * 32, n0, lane, q, ebuf, s_last);
+                                          tile * 2 + (int)rank, m0 + q * 32, n0, lane, q, ebuf, s_last, taddr2);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_remote(leader_tempty0 + 8u * acc);
@@ -887,7 +949,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
   cluster_sync_all();  // neither CTA leaves while the other may still touch its barriers / smem
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN));
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * NACC * BN));
   }
 }
 
@@ -939,6 +1001,10 @@ static bool make_tmap_f32(CUtensorMap* map, const void* ptr, int64_t rows, int64
 }
 
 static int* g_err_word[64] = {};
+// Two MMA-issuing warps for the narrow-tile kernels.  Off by default: measured on B200 the decode-size
+// GEMMs are bound by what one SM can pull from L2/HBM (~100 GB/s), not by MMA issue, and the second
+// issuer changes nothing (16.8 vs 16.4 us at 256 x 4096 x 4096).
+static int g_dual = 0;
 static int g_k_per_stage = 2;  // preferred K blocks per ring stage for tiles narrower than 256
 
 // Split-K scratch of one device: the zero-filled fp32 accumulation area and the per-tile arrival counters.  Allocated
@@ -980,7 +1046,7 @@ static int usable_split(int ks, int M, int N, int K, int k_per_stage, int counte
   return ks;
 }
 
-template <int BN, int STAGES, int KS = 1>
+template <int BN, int STAGES, int KS = 1, bool DUAL = false>
 static int launch_gemm(const void* a, const void* w, void* c, const void* bias, int M, int N, int K, int64_t lda,
                        int64_t ldw, int64_t ldc, int max_ctas, int w_packed, cudaStream_t s,
                        const int32_t* tile_expert = nullptr, int n_experts = 1,
@@ -990,7 +1056,7 @@ static int launch_gemm(const void* a, const void* w, void* c, const void* bias, 
   cudaGetDevice(&dev);
   static bool attr_done[64] = {};
   if (!attr_done[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, STAGES, KS>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, STAGES, KS, DUAL>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (e != cudaSuccess) return (int)e;
     attr_done[dev & 63] = true;
@@ -1019,12 +1085,12 @@ static int launch_gemm(const void* a, const void* w, void* c, const void* bias, 
   if (mode.ks > 1 && !make_tmap_f32(&tws, mode.ws, M, N)) return (int)cudaErrorInvalidValue;
   const int units = tiles * mode.ks;
   int grid = units < max_ctas ? units : max_ctas;
-  gemm_bf16_tcgen05_kernel<BN, STAGES, KS><<<grid, 192, S::TOTAL, s>>>(ta, tb, tc, tws, (const bf16*)bias, M, N, K, a_box,
+  gemm_bf16_tcgen05_kernel<BN, STAGES, KS, DUAL><<<grid, DUAL ? 224 : 192, S::TOTAL, s>>>(ta, tb, tc, tws, (const bf16*)bias, M, N, K, a_box,
                                                                  w_packed, tile_expert, N, mode, g_err_word[dev & 63]);
   return XLLM_LAUNCH_CHECK();
 }
 
-template <int BN, int STAGES, int KS = 1>
+template <int BN, int STAGES, int KS = 1, bool DUAL = false>
 static int launch_gemm_pair(const void* a, const void* w, void* c, const void* bias, int M, int N, int K, int64_t lda,
                             int64_t ldw, int64_t ldc, int max_ctas, int w_packed, cudaStream_t s, int split_k = 1) {
   using S = GemmSmem2<BN, STAGES, KS>;
@@ -1032,7 +1098,7 @@ static int launch_gemm_pair(const void* a, const void* w, void* c, const void* b
   cudaGetDevice(&dev);
   static bool attr_done[64] = {};
   if (!attr_done[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_pair_kernel<BN, STAGES, KS>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_pair_kernel<BN, STAGES, KS, DUAL>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (e != cudaSuccess) return (int)e;
     attr_done[dev & 63] = true;
@@ -1059,7 +1125,7 @@ static int launch_gemm_pair(const void* a, const void* w, void* c, const void* b
   if (mode.ks > 1 && !make_tmap_f32(&tws, mode.ws, M, N)) return (int)cudaErrorInvalidValue;
   const int units = tiles * mode.ks;
   int pairs = units < max_ctas / 2 ? units : max_ctas / 2;
-  gemm_bf16_tcgen05_pair_kernel<BN, STAGES, KS><<<2 * pairs, 192, S::TOTAL, s>>>(ta, tb, tc, tws, (const bf16*)bias, M, N, K,
+  gemm_bf16_tcgen05_pair_kernel<BN, STAGES, KS, DUAL><<<2 * pairs, DUAL ? 224 : 192, S::TOTAL, s>>>(ta, tb, tc, tws, (const bf16*)bias, M, N, K,
                                                                             w_packed, mode, g_err_word[dev & 63]);
   return XLLM_LAUNCH_CHECK();
 }
@@ -1148,15 +1214,21 @@ XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* b
     switch (tile_n) {
       case 256: return launch_gemm_pair<256, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
       case 128:
+        if (two && g_dual) return launch_gemm_pair<128, 4, 2, true>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
         if (two) return launch_gemm_pair<128, 4, 2>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
         return launch_gemm_pair<128, 8>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
       case 64:
+        if (two && g_dual) return launch_gemm_pair<64, 4, 2, true>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
         if (two) return launch_gemm_pair<64, 4, 2>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
         return launch_gemm_pair<64, 9>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
       default: return (int)cudaErrorInvalidValue;
     }
   }
   const GemmMode plain{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0};
+  if (two && g_dual && tile_n == 128)
+    return launch_gemm<128, 6, 1, true>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1, plain, split_k);
+  if (two && g_dual && tile_n == 64)
+    return launch_gemm<64, 4, 2, true>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1, plain, split_k);
   if (two && tile_n == 128)
     return launch_gemm<128, 3, 2>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1, plain, split_k);
   if (two && tile_n == 64)
@@ -1259,6 +1331,8 @@ XLLM_API int xllm_pack_weight_bf16(void* dst, const void* src, int N, int K, int
 
 // 1 = one 64-element K block per ring stage everywhere; 2 (default) = two for tiles narrower than 256.
 XLLM_API void xllm_gemm_set_k_per_stage(int n) { xllm::g_k_per_stage = n == 1 ? 1 : 2; }
+// 1 = the narrow-tile kernels use two MMA-issuing warps; 0 (default) = one.
+XLLM_API void xllm_gemm_set_dual_issue(int on) { xllm::g_dual = on ? 1 : 0; }
 
 // Allocate the per-device split-K scratch now (call once per device before capturing CUDA graphs).
 XLLM_API int xllm_gemm_prepare() {

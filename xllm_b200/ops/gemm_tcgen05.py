@@ -12,6 +12,7 @@ _lib.register_signature("xllm_gemm_bf16", [P, P, P, P, I, I, I, L, L, L, I, I, I
 _lib.register_signature("xllm_gemm_error_status", [], I)
 _lib.register_signature("xllm_gemm_prepare", [], I)
 _lib.register_signature("xllm_gemm_set_k_per_stage", [I], None)
+_lib.register_signature("xllm_gemm_set_dual_issue", [I], None)
 _lib.register_signature("xllm_pack_weight_bf16", [P, P, I, I, L, P])
 
 
@@ -85,6 +86,11 @@ def gemm_nt(x, w, bias=None, out=None, tile_n: int = 0, pair: int = -1, split_k:
 def set_k_per_stage(n: int):
     """1 = one 64-element K block per ring stage; 2 (default) = two for tiles narrower than 256."""
     _lib.load().xllm_gemm_set_k_per_stage(int(n))
+
+
+def set_dual_issue(on: bool):
+    """Two MMA-issuing warps or one (default) for the narrow-tile kernels."""
+    _lib.load().xllm_gemm_set_dual_issue(int(bool(on)))
 
 
 def prepare():
