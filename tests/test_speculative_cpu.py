@@ -53,3 +53,49 @@ def test_speculative_accepts_repetition_and_stops_mid_row():
                                                      np.array([4], dtype=np.int32))
         got += [e.token for e in evs if e.token >= 0]
     assert got[1:] == [1, 2, 777] and len(got) == 4
+
+
+def test_mtp_drafter_on_deepseek_matches_plain_greedy():
+    """DeepSeek-style model + its MTP layer as the drafter (own paged KV cache, hidden states of the
+    verified rows): the token stream must not depend on whether drafts are accepted."""
+    from test_deepseek_cpu import _args
+    from xllm_b200.engine.llm_engine import EngineConfig, LLMEngine
+
+    def make(**kw):
+        llm = LLM.__new__(LLM)
+        llm.engine = LLMEngine(EngineConfig(model="d", device="cpu", dtype="float32", num_blocks=96, enable_graph=False,
+                                            max_tokens_per_batch=24, enable_schedule_overlap=False, **kw), model_args=_args())
+        llm.tokenizer = None
+        return llm
+
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 500, (n,), generator=g).tolist() for n in (9, 40, 17)]   # 40 > 24: chunked prefill
+    sp = SamplingParams(max_tokens=10, temperature=0.0, ignore_eos=True)
+    plain = [o.outputs[0].token_ids for o in make().generate(prompts, sp)]
+    llm = make(num_speculative_tokens=1, speculative_method="mtp")
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert got == plain
+    spec = llm.engine.spec
+    assert spec.steps > 0 and spec.proposed > 0
+    assert len(spec.drafter.draft) > 0
+    # a drafter that already knows the answer gets everything accepted, so two tokens per step
+    llm2 = make(num_speculative_tokens=1, speculative_method="mtp")
+    truth = {tuple(p): t for p, t in zip(prompts, plain)}
+
+    class Oracle:
+        k = 1
+        def propose(self, batch, n, **_):
+            out = np.zeros((n, 1), dtype=np.int64)
+            for i in range(n):
+                h = batch.history(i, 0).tolist()
+                for p, t in truth.items():
+                    if tuple(h[: len(p)]) == p:
+                        j = len(h) - len(p)
+                        out[i, 0] = t[j] if j < len(t) else 0
+            return out
+        def observe(self, *a, **kw): pass
+        def after_execute(self, *a, **kw): pass
+
+    llm2.engine.spec.drafter = Oracle()
+    got2 = [o.outputs[0].token_ids for o in llm2.generate(prompts, sp)]
+    assert got2 == plain and llm2.engine.spec.acceptance_rate > 0.9

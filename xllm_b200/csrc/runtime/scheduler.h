@@ -700,7 +700,8 @@ class Scheduler {
       b.cu_q.push_back(b.cu_q.back() + p.n_new);
       b.max_q_len = std::max(b.max_q_len, p.n_new);
       b.max_kv_len = std::max(b.max_kv_len, kv_len);
-      b.max_blocks = std::max(b.max_blocks, (kv_len + bs - 1) / bs);
+      // with speculative decoding the table also covers the slots reserved for the draft tokens
+      b.max_blocks = std::max(b.max_blocks, (kv_len + cfg_.num_speculative_tokens + bs - 1) / bs);
       b.seqs.push_back(s);
       b.seq_ids.push_back(s->seq_id);
       const bool samples = p.decode || (start + p.n_new >= s->num_tokens());

@@ -150,6 +150,10 @@ class LLMEngine:
                 raise ValueError("speculative decoding needs enable_schedule_overlap=False: the number of tokens "
                                  "a step appends is only known after verification")
             from .speculative import SpecDecoder, make_drafter
+            if cfg.speculative_method == "mtp":
+                from ..models.deepseek import MTPDraft
+                self.mtp = MTPDraft(self.args, self.model, self.dtype, self.device, self.ps)
+                self.mtp.init_random(seed=cfg.seed + 17)   # replaced by load_weights() for real checkpoints
             self.spec = SpecDecoder(self, make_drafter(cfg.speculative_method, cfg.num_speculative_tokens, self),
                                     cfg.num_speculative_tokens)
         self.steps = 0
@@ -274,7 +278,12 @@ class LLMEngine:
                 events = self.scheduler.process_output_multi(batch.batch_id, flat, counts, lp)
             elif batch is not None:
                 out = self.runner.execute(batch)
-                events = self._finish(out)
+                if self.spec is not None:
+                    ids, lp = out.wait()
+                    self.spec.drafter.after_execute(batch, ids)
+                    events = self.scheduler.process_output(out.batch_id, ids, lp)
+                else:
+                    events = self._finish(out)
             else:
                 events = self.scheduler.take_pending_events()
         self._grammar_advance(events)

@@ -100,6 +100,8 @@ class ModelRunner:
         self.d2h_bytes = 0
         self.graph_replays = 0
         self.logits_hook = None
+        self.keep_hidden = False     # speculative decoding with a draft layer needs the step's hidden states
+        self.last_hidden = self.last_meta = self.last_positions = None
         self.graph_launches_per_replay: Dict[int, int] = {}
         # CUDA graphs
         self.buckets = graph_buckets or default_buckets(max_seqs)
@@ -260,6 +262,8 @@ class ModelRunner:
                 ops.resolve_placeholders(tokens, self.prev_ids)
             meta = self._meta_from(buf, off, nd, npf, batch.max_q_len, batch.max_kv_len, bt_stride)
             hidden = self.model.forward(tokens, positions, meta, self.kv_caches)
+            if self.keep_hidden:
+                self.last_hidden, self.last_meta, self.last_positions = hidden, meta, positions
             rows = _view(buf, off[2], NS, torch.int64)
             h = hidden if (NS == T and npf == 0) else ops.gather_rows(hidden, rows)
             logits = self.model.logits(h)

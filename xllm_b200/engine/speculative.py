@@ -18,6 +18,8 @@ Steps that contain prompt chunks run unspeculated.
 
 Drafters:
   * `NgramDrafter` — prompt-lookup / suffix matching on the sequence's own tokens, no model,
+  * `MTPDrafter` — the multi-token-prediction layer of DeepSeek-V3-style checkpoints with its own
+    paged KV cache, fed with the target's hidden states,
   * `DraftModelDrafter` — any small causal LM sharing the tokenizer (run without a KV cache of its
     own over a short window; enough for Eagle-style single-layer drafts).
 """
@@ -67,6 +69,105 @@ class NgramDrafter:
     def observe(self, *a, **kw):
         pass
 
+    def after_execute(self, *a, **kw):
+        pass
+
+
+class MTPDrafter:
+    """One-token drafts from a multi-token-prediction layer (`models.deepseek.MTPDraft`,
+    DeepSeek-V3 `num_nextn_predict_layers`; reference: runtime/mtp_worker_impl.cpp:1245-1850).
+
+    The layer at position p consumes the target's hidden state h_p and the embedding of token
+    x_{p+1} and predicts x_{p+2}.  It has a paged KV cache of its own with the geometry of one
+    target layer, addressed through the same block tables, and is run over exactly the rows the
+    target has verified: every prompt chunk and unspeculated decode row (`after_execute`), and the
+    accepted rows of a verification pass (`observe`).  The prediction made at the last verified
+    position of a sequence is its draft for the next step."""
+
+    name = "mtp"
+
+    def __init__(self, engine, k: int = 1):
+        assert k == 1, "one MTP layer drafts one token per step"
+        self.k = 1
+        self.engine = engine
+        self.mtp = engine.mtp
+        k0, v0 = engine.runner.kv_caches[0]
+        self.kv = (torch.zeros_like(k0), torch.zeros_like(v0))
+        self.draft = {}
+        engine.runner.keep_hidden = True
+
+    def propose(self, batch, n_rows: int, **_) -> np.ndarray:
+        out = np.zeros((n_rows, 1), dtype=np.int64)
+        for i in range(n_rows):
+            d = self.draft.get(batch.request_id(i))
+            out[i, 0] = int(batch.history(i, 1)[0]) if d is None else d
+        return out
+
+    def _run(self, next_tokens, hidden, positions, meta, last_rows, request_ids):
+        h = self.mtp.forward(next_tokens, hidden, positions, meta, self.kv[0], self.kv[1])
+        if len(last_rows) == 0:
+            return
+        rows = torch.as_tensor(last_rows, dtype=torch.long, device=h.device)
+        ids = self.mtp.logits(h[rows]).argmax(-1).cpu().tolist()
+        for rid, t in zip(request_ids, ids):
+            self.draft[rid] = int(t)
+
+    def after_execute(self, batch, sampled_ids):
+        """After a normal (unspeculated) step: run the layer over all of its rows."""
+        runner = self.engine.runner
+        hidden, meta, positions = runner.last_hidden, runner.last_meta, runner.last_positions
+        if hidden is None:
+            return
+        cu = np.asarray(batch.cu_q)
+        pos_h = np.asarray(batch.positions)
+        nseq = batch.n_decode + batch.n_prefill
+        sample_seq = np.asarray(batch.sample_seq)
+        sampled = {int(sample_seq[r]): int(sampled_ids[r]) for r in range(len(sample_seq))}
+        nxt = np.zeros(int(cu[nseq]), dtype=np.int64)
+        last_rows, rids = [], []
+        for i in range(nseq):
+            a, b = int(cu[i]), int(cu[i + 1])
+            hist = batch.history(i, 0)
+            p0 = int(pos_h[a])
+            want = hist[p0 + 1:p0 + 1 + (b - a)]
+            nxt[a:a + len(want)] = want
+            if i in sampled:                       # the row of the last position takes the new token
+                nxt[b - 1] = sampled[i]
+                last_rows.append(b - 1)
+                rids.append(batch.request_id(i))
+        self._run(torch.from_numpy(nxt).to(hidden.device), hidden[: len(nxt)], positions[: len(nxt)], meta, last_rows, rids)
+
+    def observe(self, batch, n_rows, hidden_rows, counts, tokens=None, kv0=None, block_tables=None):
+        """After a verification pass: hidden_rows [B, 2, H]; row j < counts[i] of sequence i is
+        verified and its next token is tokens[i, j]."""
+        dev = hidden_rows.device
+        bs = self.engine.cfg.block_size
+        sel, nxt, pos, slots, cu, last_rows, rids = [], [], [], [], [0], [], []
+        for i in range(n_rows):
+            c = int(counts[i])
+            for j in range(c):
+                p = int(kv0[i]) - 1 + j
+                sel.append(i * hidden_rows.shape[1] + j)
+                nxt.append(int(tokens[i, j]))
+                pos.append(p)
+                slots.append(int(block_tables[i, p // bs]) * bs + p % bs)
+            cu.append(cu[-1] + c)
+            last_rows.append(cu[-1] - 1)
+            rids.append(batch.request_id(i))
+        H = hidden_rows.shape[-1]
+        hid = hidden_rows.reshape(-1, H)[torch.as_tensor(sel, dtype=torch.long, device=dev)]
+        meta = AttentionMetadata(
+            n_decode=0, n_prefill=n_rows, slots=torch.tensor(slots, dtype=torch.int32, device=dev),
+            block_table=torch.from_numpy(np.ascontiguousarray(block_tables)).to(dev),
+            kv_lens=torch.tensor([int(kv0[i]) - 1 + int(counts[i]) for i in range(n_rows)], dtype=torch.int32, device=dev),
+            cu_q=torch.tensor(cu, dtype=torch.int32, device=dev), max_q_len=int(max(counts)),
+            max_kv_len=int(max(kv0)) + 1)
+        self._run(torch.tensor(nxt, dtype=torch.int64, device=dev), hid, torch.tensor(pos, dtype=torch.int64, device=dev),
+                  meta, last_rows, rids)
+
+    def forget(self, request_id):
+        self.draft.pop(request_id, None)
+
 
 class DraftModelDrafter:
     """Greedy k-token drafts from a small causal LM run over the last `window` tokens of every
@@ -89,6 +190,9 @@ class DraftModelDrafter:
         return out
 
     def observe(self, *a, **kw):
+        pass
+
+    def after_execute(self, *a, **kw):
         pass
 
 
@@ -148,7 +252,7 @@ class SpecDecoder:
         counts_h = counts.cpu().numpy().astype(np.int32)
         out_h = out.cpu().numpy()
         flat = np.concatenate([out_h[i, : counts_h[i]] for i in range(B)]).astype(np.int64)
-        self.drafter.observe(batch, B, hidden.view(B, k + 1, -1), counts_h)
+        self.drafter.observe(batch, B, hidden.view(B, k + 1, -1), counts_h, tokens=out_h, kv0=kv0, block_tables=bt)
         self.proposed += B * k
         self.accepted += int(counts_h.sum()) - B
         self.steps += 1
@@ -158,4 +262,6 @@ class SpecDecoder:
 def make_drafter(kind: str, k: int, engine=None, **kw):
     if kind in ("ngram", "suffix", "prompt_lookup"):
         return NgramDrafter(k, **kw)
+    if kind == "mtp":
+        return MTPDrafter(engine, k)
     raise ValueError(f"unknown drafter {kind!r}")
