@@ -1,0 +1,110 @@
+"""Qwen2-VL-style model on CPU: image processor, prompt expansion, M-RoPE positions, and the engine
+path (image embeddings merged at prefill, 3-axis rotary table, chunked prefill, paged decode)
+against a dense textbook forward."""
+import math
+
+import numpy as np
+import torch
+
+from xllm_b200.api.vlm import VLM
+from xllm_b200.api.llm import SamplingParams
+from xllm_b200.engine.llm_engine import EngineConfig, LLMEngine
+from xllm_b200.models import ModelArgs
+from xllm_b200.multimodal import Qwen2VLImageProcessor, expand_image_tokens, mrope_positions, smart_resize
+
+IMG, VSTART, VEND = 900, 901, 902
+
+
+def _args():
+    return ModelArgs(model_type="qwen2_vl", vocab_size=1000, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=16, intermediate_size=128, qk_norm=False, attention_bias=True,
+                     rope_theta=10000.0, max_position_embeddings=512, tie_word_embeddings=False, image_token_id=IMG,
+                     vision_start_token_id=VSTART, mrope_section=[2, 3, 3],
+                     vision_config=dict(embed_dim=32, num_heads=2, depth=2, mlp_ratio=2, patch_size=14,
+                                        spatial_merge_size=2, temporal_patch_size=2, in_chans=3))
+
+
+def test_processor_and_positions():
+    assert smart_resize(100, 200, 28, 56 * 56, 10 ** 6) == (112, 196)
+    proc = Qwen2VLImageProcessor()
+    img = (np.random.default_rng(0).random((60, 90, 3)) * 255).astype(np.uint8)
+    pv, grid = proc([img])
+    h, w = smart_resize(60, 90, 28, 56 * 56, proc.max_pixels)
+    assert grid.tolist() == [[1, h // 14, w // 14]] and pv.shape == ((h // 14) * (w // 14), 3 * 2 * 14 * 14)
+    n = proc.tokens_per_image(grid)[0]
+    ids = expand_image_tokens([5, VSTART, IMG, VEND, 6, 7], IMG, [n])
+    assert ids.count(IMG) == n and len(ids) == 5 + n
+    pos, delta = mrope_positions(ids, IMG, grid, 2)
+    gh, gw = grid[0, 1].item() // 2, grid[0, 2].item() // 2
+    assert pos[:, 0].tolist() == [0, 0, 0] and pos[:, 1].tolist() == [1, 1, 1]
+    assert pos[0, 2:2 + n].unique().tolist() == [2]                       # one temporal position for a still image
+    assert pos[1, 2:2 + n].max().item() == 2 + gh - 1 and pos[2, 2:2 + n].max().item() == 2 + gw - 1
+    nxt = 2 + max(gh, gw)
+    assert pos[:, 2 + n].tolist() == [nxt] * 3 and delta == (nxt + 3) - len(ids)
+
+
+def _dense_reference(model, ids, embeds_rows, embeds_vals, pos3):
+    """Textbook forward over the whole sequence: merged embeddings, M-RoPE, causal attention."""
+    a = model.args
+    sd = dict(model.named_params())
+    x = sd["model.embed_tokens.weight"][ids].clone()
+    x[embeds_rows] = embeds_vals
+    T = ids.shape[0]
+    d, nq, nkv = a.head_dim, a.num_attention_heads, a.num_key_value_heads
+    half = d // 2
+    inv = 1.0 / (a.rope_theta ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / d))
+    axis = torch.repeat_interleave(torch.arange(3), torch.tensor(model.mrope_section))
+    ang = (pos3.double()[axis] * inv[:, None]).T
+    cos, sin = ang.cos().float()[:, None, :], ang.sin().float()[:, None, :]
+
+    def norm(v, w):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + a.rms_norm_eps) * w
+
+    def rope(v):
+        v1, v2 = v[..., :half], v[..., half:]
+        return torch.cat([v1 * cos - v2 * sin, v2 * cos + v1 * sin], -1)
+
+    for i in range(a.num_hidden_layers):
+        p = f"model.layers.{i}."
+        h = norm(x, sd[p + "input_layernorm.weight"])
+        qkv = h @ sd[p + "self_attn.qkv_proj.weight"].T + sd[p + "self_attn.qkv_proj.bias"]
+        q, k, v = qkv.split([nq * d, nkv * d, nkv * d], -1)
+        q, k, v = rope(q.view(T, nq, d)), rope(k.view(T, nkv, d)), v.view(T, nkv, d)
+        k, v = k.repeat_interleave(nq // nkv, 1), v.repeat_interleave(nq // nkv, 1)
+        s = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(d)
+        s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+        o = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(T, nq * d)
+        x = x + o @ sd[p + "self_attn.o_proj.weight"].T
+        h = norm(x, sd[p + "post_attention_layernorm.weight"])
+        g, u = (h @ sd[p + "mlp.gate_up_proj.weight"].T).chunk(2, -1)
+        x = x + (torch.nn.functional.silu(g) * u) @ sd[p + "mlp.down_proj.weight"].T
+    return norm(x, sd["model.norm.weight"]) @ sd["lm_head.weight"].T
+
+
+def test_vlm_engine_matches_dense_reference():
+    vlm = VLM.__new__(VLM)
+    vlm.engine = LLMEngine(EngineConfig(model="v", device="cpu", dtype="float32", num_blocks=64, enable_graph=False,
+                                        max_tokens_per_batch=16, enable_schedule_overlap=False), model_args=_args())   # prompts span chunks
+    vlm.tokenizer = None
+    model = vlm.engine.model
+    model.init_random(std=0.05, seed=3)
+    vlm.processor = Qwen2VLImageProcessor(14, 2, 2, min_pixels=56 * 56, max_pixels=112 * 112)
+    vlm.image_token_id = IMG
+    rng = np.random.default_rng(1)
+    img_a = (rng.random((80, 100, 3)) * 255).astype(np.uint8)
+    img_b = (rng.random((56, 56, 3)) * 255).astype(np.uint8)
+    reqs = [dict(prompt_token_ids=[11, 12, VSTART, IMG, VEND, 13, 14, 15], images=[img_a]),
+            dict(prompt_token_ids=[21, 22, 23, 24], images=[]),
+            dict(prompt_token_ids=[31, VSTART, IMG, VEND, 32, VSTART, IMG, VEND, 33], images=[img_b, img_a])]
+    got = vlm.generate_mm(reqs, SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True))
+    for r, g in zip(reqs, got):
+        ids, mm = vlm.prepare(r["prompt_token_ids"], r["images"])
+        seq = list(ids)
+        for _ in range(5):
+            L = len(seq)
+            pos3 = torch.cat([mm.mrope, (torch.arange(mm.mrope.shape[1], L) + mm.delta).repeat(3, 1)], dim=1)
+            rows = torch.tensor(mm.positions, dtype=torch.long)
+            logits = _dense_reference(model, torch.tensor(seq), rows, mm.embeds, pos3)
+            seq.append(int(logits[-1].argmax()))
+        assert g == seq[len(ids):], (g, seq[len(ids):])
+    assert not vlm.engine.mm

@@ -287,7 +287,8 @@ PYBIND11_MODULE(_rt, m) {
       .def(py::init<const SchedulerConfig&>())
       .def("add_request", &Scheduler::add_request, py::arg("request_id"), py::arg("prompt_tokens"),
            py::arg("sampling"), py::arg("stopping"), py::arg("n") = 1, py::arg("priority") = 0,
-           py::arg("deadline") = 0.0, py::arg("offline") = false, py::arg("stream") = false)
+           py::arg("deadline") = 0.0, py::arg("offline") = false, py::arg("stream") = false,
+           py::arg("extra_hash_key") = 0)
       .def("abort_request", &Scheduler::abort_request)
       .def("adopt_prefilled", &Scheduler::adopt_prefilled, py::arg("request_id"), py::arg("tokens"),
            py::arg("num_prompt_tokens"), py::arg("sampling"), py::arg("stopping"), py::arg("priority") = 0,

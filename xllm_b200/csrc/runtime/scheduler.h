@@ -106,7 +106,7 @@ class Scheduler {
   // ---------------------------------------------------------------- intake
   bool add_request(const std::string& id, const std::vector<int32_t>& prompt, const SamplingParams& sp,
                    const StoppingParams& st, int32_t n, int32_t priority, double deadline, bool offline,
-                   bool stream) {
+                   bool stream, uint64_t extra_hash_key = 0) {
     if (requests_.count(id) || prompt.empty() || n < 1) return false;
     auto req = std::make_unique<Request>();
     req->request_id = id;
@@ -124,6 +124,7 @@ class Scheduler {
       s->request = req.get();
       s->tokens = prompt;
       s->num_prompt_tokens = (int32_t)prompt.size();
+      s->extra_hash_key = extra_hash_key;  // e.g. content hash of the images of a multimodal prompt
       req->seqs.push_back(std::move(s));
     }
     Request* r = req.get();

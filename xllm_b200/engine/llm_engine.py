@@ -139,6 +139,7 @@ class LLMEngine:
         self.scheduler = rt.Scheduler(sc)
         self._pending: Optional[StepOutput] = None
         self.grammar = None
+        self.mm = {}                 # request id -> MMInput of multimodal requests
         self.host_tier = None
         if cfg.host_kv_blocks > 0 and cfg.enable_prefix_cache:
             from .host_tier import HostKVTier
@@ -191,7 +192,7 @@ class LLMEngine:
                     max_tokens=16, ignore_eos=False, stop_token_ids=None, stop_sequences=None,
                     frequency_penalty=0.0, presence_penalty=0.0, repetition_penalty=1.0,
                     logprobs=False, top_logprobs=0, seed=None, n=1, priority=0, deadline=0.0,
-                    offline=False, stream=False, eos_token_id=None, json_object=False) -> bool:
+                    offline=False, stream=False, eos_token_id=None, json_object=False, mm=None) -> bool:
         rt = self.rt
         sp = rt.SamplingParams()
         sp.temperature = float(temperature)
@@ -222,6 +223,13 @@ class LLMEngine:
             if self.cfg.enable_schedule_overlap:
                 raise ValueError("constrained decoding needs enable_schedule_overlap=False")
             self.grammar.start(request_id)
+        if mm is not None:
+            if not hasattr(self.model, "mrope_section"):
+                raise ValueError("this model takes no multimodal input")
+            self.mm[request_id] = mm
+            self.runner.mm_hook = self._mm_hook
+            return self.scheduler.add_request(request_id, toks, sp, st, n, priority, deadline, offline, stream,
+                                              int(mm.hash_key) & ((1 << 63) - 1))
         return self.scheduler.add_request(request_id, toks, sp, st, n, priority, deadline, offline, stream)
 
     def set_grammar_vocab(self, token_text, eos_token_id=None, top_n: int = 64):
@@ -229,6 +237,49 @@ class LLMEngine:
         from .grammar import GrammarFilter
         self.grammar = GrammarFilter(token_text, top_n, self.args.eos_token_id if eos_token_id is None else eos_token_id)
         self.runner.logits_hook = self._grammar_hook
+
+    # ------------------------------------------------------------------ multimodal inputs
+    def _mm_hook(self, batch):
+        """Per-step inputs of multimodal requests: the image embeddings of the placeholder rows in
+        this step's prompt chunks and the 3-axis rotary table of all rows.  None when no sequence of
+        the batch is multimodal."""
+        if not self.mm:
+            return None
+        import bisect
+
+        import numpy as np
+
+        from ..multimodal.image import mrope_table
+        nseq = batch.n_decode + batch.n_prefill
+        rids = [batch.request_id(i) for i in range(nseq)]
+        if not any(r in self.mm for r in rids):
+            return None
+        cu = np.asarray(batch.cu_q)
+        pos_h = np.asarray(batch.positions).astype(np.int64)
+        T = int(cu[nseq])
+        pos3 = torch.from_numpy(pos_h[:T]).repeat(3, 1)
+        rows, vals = [], []
+        for i, rid in enumerate(rids):
+            m = self.mm.get(rid)
+            if m is None:
+                continue
+            a, b = int(cu[i]), int(cu[i + 1])
+            p0 = int(pos_h[a])
+            L = m.mrope.shape[1]
+            for r in range(a, b):
+                p = p0 + (r - a)
+                pos3[:, r] = m.mrope[:, p] if p < L else p + m.delta
+            lo = bisect.bisect_left(m.positions, p0)
+            hi = bisect.bisect_left(m.positions, p0 + (b - a))
+            if hi > lo:
+                rows.extend(a + (m.positions[j] - p0) for j in range(lo, hi))
+                vals.append(m.embeds[lo:hi])
+        dev = self.runner.device
+        table = mrope_table(pos3.to(dev), self.args.rotary_dim, self.args.rope_theta, self.model.mrope_section)
+        embeds = None
+        if rows:
+            embeds = (torch.tensor(rows, dtype=torch.long, device=dev), torch.cat(vals).to(dev))
+        return embeds, table, torch.arange(T, dtype=torch.int64, device=dev)
 
     def _grammar_hook(self, batch, logits):
         if not self.grammar.state:
@@ -287,6 +338,10 @@ class LLMEngine:
             else:
                 events = self.scheduler.take_pending_events()
         self._grammar_advance(events)
+        if self.mm:
+            for ev in events:
+                if ev.request_finished:
+                    self.mm.pop(ev.request_id, None)
         if batch is not None:
             self.steps += 1
             if self.record_steps:

@@ -100,6 +100,7 @@ class ModelRunner:
         self.d2h_bytes = 0
         self.graph_replays = 0
         self.logits_hook = None
+        self.mm_hook = None          # multimodal requests: (batch) -> None | (embeds, rope_table, rope_rows)
         self.keep_hidden = False     # speculative decoding with a draft layer needs the step's hidden states
         self.last_hidden = self.last_meta = self.last_positions = None
         self.graph_launches_per_replay: Dict[int, int] = {}
@@ -229,8 +230,9 @@ class ModelRunner:
         st = self.staging[self._turn % len(self.staging)]
         self._turn += 1
         nd, npf = batch.n_decode, batch.n_prefill
+        mm = self.mm_hook(batch) if self.mm_hook is not None else None
         use_graph = self.enable_graph and npf == 0 and self._bucket(nd) is not None \
-            and batch.max_blocks <= self.bt_cols
+            and batch.max_blocks <= self.bt_cols and mm is None
         Bp = self._bucket(nd) if use_graph else 0
         bt_stride = self.bt_cols if use_graph else max(8, (batch.max_blocks + 7) // 8 * 8)
         off = batch.fill_packed(st.host.data_ptr(), st.host.numel(), bt_stride, Bp)
@@ -261,7 +263,11 @@ class ModelRunner:
             if self.overlap and self.prev_ids is not None:
                 ops.resolve_placeholders(tokens, self.prev_ids)
             meta = self._meta_from(buf, off, nd, npf, batch.max_q_len, batch.max_kv_len, bt_stride)
-            hidden = self.model.forward(tokens, positions, meta, self.kv_caches)
+            if mm is not None:
+                embeds, meta.rope_table, meta.rope_rows = mm
+                hidden = self.model.forward(tokens, positions, meta, self.kv_caches, embeds=embeds)
+            else:
+                hidden = self.model.forward(tokens, positions, meta, self.kv_caches)
             if self.keep_hidden:
                 self.last_hidden, self.last_meta, self.last_positions = hidden, meta, positions
             rows = _view(buf, off[2], NS, torch.int64)

@@ -68,6 +68,8 @@ class ModelArgs:
     vision_config: Optional[Dict[str, Any]] = None
     image_token_id: int = -1
     video_token_id: int = -1
+    vision_start_token_id: int = -1
+    mrope_section: List[int] = field(default_factory=list)   # rotary pairs per (t, h, w) axis
     extra: Dict[str, Any] = field(default_factory=dict)
 
     @property
@@ -154,6 +156,9 @@ def model_args_from_dict(cfg: Dict[str, Any]) -> ModelArgs:
         a.quant_block = list(q.get("weight_block_size") or [])
     a.vision_config = cfg.get("vision_config")
     a.image_token_id = _g(cfg, "image_token_id", default=-1)
+    a.vision_start_token_id = _g(cfg, "vision_start_token_id", default=-1)
+    rs = cfg.get("rope_scaling") or (cfg.get("text_config") or {}).get("rope_scaling") or {}
+    a.mrope_section = list(rs.get("mrope_section") or [])
     a.video_token_id = _g(cfg, "video_token_id", default=-1)
     return a
 

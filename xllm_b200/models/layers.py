@@ -34,6 +34,10 @@ class AttentionMetadata:
     max_kv_len: int = 0
     decode_splits: int = 1
     decode_workspace: Optional[torch.Tensor] = None
+    # multimodal rotary embedding: per-row cos|sin table [T, rot_dim] used instead of the model's
+    # position-indexed cache (row i of the table belongs to token row i)
+    rope_table: Optional[torch.Tensor] = None
+    rope_rows: Optional[torch.Tensor] = None
 
     @property
     def n_seqs(self):
@@ -336,7 +340,10 @@ class Attention(Module):
 
     def forward(self, x, positions, meta: AttentionMetadata, k_cache, v_cache):
         qkv = self.qkv(x)
-        q = ops.rope_kv_write(qkv, self.nq, self.nkv, self.d, positions, self.rope.cos_sin, self.rope.rot_dim,
+        cos_sin = self.rope.cos_sin
+        if meta.rope_table is not None:
+            cos_sin, positions = meta.rope_table, meta.rope_rows
+        q = ops.rope_kv_write(qkv, self.nq, self.nkv, self.d, positions, cos_sin, self.rope.rot_dim,
                               slots=meta.slots, k_cache=k_cache, v_cache=v_cache,
                               q_norm_w=self.q_norm.weight if self.q_norm else None,
                               k_norm_w=self.k_norm.weight if self.k_norm else None, eps=self.eps,

@@ -97,10 +97,14 @@ class DenseCausalLM(Module):
     def head_dim(self):
         return self.args.head_dim
 
-    def forward(self, tokens, positions, meta: AttentionMetadata, kv_caches):
+    def forward(self, tokens, positions, meta: AttentionMetadata, kv_caches, embeds=None):
         """tokens/positions: [T] int64.  kv_caches: list of (k_cache, v_cache) per layer.
-        Returns the final-norm hidden states [T, H]."""
+        `embeds` = (rows, values): input embeddings that replace the token embedding of those rows
+        (image tokens of a multimodal prompt).  Returns the final-norm hidden states [T, H]."""
         x = self.embed(tokens)
+        if embeds is not None:
+            x = x.clone() if x.data_ptr() == self.embed.weight.data_ptr() else x
+            x[embeds[0]] = embeds[1].to(x.dtype)
         residual = None
         for layer, (kc, vc) in zip(self.layers, kv_caches):
             x, residual = layer(x, residual, positions, meta, kc, vc)

@@ -1,0 +1,137 @@
+"""Qwen2-VL / Qwen2.5-VL: vision transformer + patch merger in front of the dense decoder, with
+multimodal rotary position ids.
+
+Parity: xllm/models/vlm/qwen2_vl.h, qwen2_5_vl.h (vision blocks, `Qwen2VisionPatchMerger`, merging
+of image embeddings into the input embeddings, M-RoPE sections).  The language model is the shared
+`DenseCausalLM`: image tokens enter through its `embeds` override, and the 3-axis rotary positions
+through a per-row cos|sin table in the attention metadata, so the fused rope/KV-write kernel and the
+paged attention kernels run unchanged.  The vision tower runs once per image at admission; it uses
+torch's attention (one call per image, full attention inside an image).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .layers import Module
+from .qwen import DenseCausalLM
+from .registry import register_model
+from ..parallel.state import single
+
+
+def _rot_half(x):
+    x1, x2 = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2:]
+    return torch.cat([-x2, x1], dim=-1)
+
+
+class VisionBlock(Module):
+    def __init__(self, dim, heads, mlp_dim, dtype, device, act="quick_gelu"):
+        super().__init__()
+        self.heads, self.act = heads, act
+        mk = lambda *s: torch.zeros(*s, dtype=dtype, device=device)
+        for name, shape in (("norm1.weight", (dim,)), ("norm1.bias", (dim,)), ("norm2.weight", (dim,)), ("norm2.bias", (dim,)),
+                            ("attn.qkv.weight", (3 * dim, dim)), ("attn.qkv.bias", (3 * dim,)),
+                            ("attn.proj.weight", (dim, dim)), ("attn.proj.bias", (dim,)),
+                            ("mlp.fc1.weight", (mlp_dim, dim)), ("mlp.fc1.bias", (mlp_dim,)),
+                            ("mlp.fc2.weight", (dim, mlp_dim)), ("mlp.fc2.bias", (dim,))):
+            self.add_param(name, mk(*shape))
+        self.p = self._params
+
+    def forward(self, x, cos, sin, cu):
+        p = self.p
+        h = F.layer_norm(x, x.shape[-1:], p["norm1.weight"], p["norm1.bias"], 1e-6)
+        T, D = h.shape
+        q, k, v = F.linear(h, p["attn.qkv.weight"], p["attn.qkv.bias"]).view(T, 3, self.heads, D // self.heads).unbind(1)
+        q = q * cos + _rot_half(q) * sin
+        k = k * cos + _rot_half(k) * sin
+        outs = []
+        for a, b in zip(cu[:-1], cu[1:]):          # full attention inside each image
+            o = F.scaled_dot_product_attention(q[a:b].transpose(0, 1)[None], k[a:b].transpose(0, 1)[None],
+                                               v[a:b].transpose(0, 1)[None])[0]
+            outs.append(o.transpose(0, 1).reshape(b - a, D))
+        x = x + F.linear(torch.cat(outs), p["attn.proj.weight"], p["attn.proj.bias"])
+        h = F.layer_norm(x, x.shape[-1:], p["norm2.weight"], p["norm2.bias"], 1e-6)
+        h = F.linear(h, p["mlp.fc1.weight"], p["mlp.fc1.bias"])
+        h = h * torch.sigmoid(1.702 * h) if self.act == "quick_gelu" else F.gelu(h)
+        return x + F.linear(h, p["mlp.fc2.weight"], p["mlp.fc2.bias"])
+
+    __call__ = forward
+
+
+class VisionTower(Module):
+    def __init__(self, vc: dict, out_hidden: int, dtype, device):
+        super().__init__()
+        self.dim = vc.get("embed_dim", vc.get("hidden_size", 1280))
+        self.heads = vc.get("num_heads", 16)
+        self.patch = vc.get("patch_size", 14)
+        self.merge = vc.get("spatial_merge_size", 2)
+        self.tp = vc.get("temporal_patch_size", 2)
+        in_ch = vc.get("in_chans", vc.get("in_channels", 3))
+        depth = vc.get("depth", 32)
+        mlp_dim = int(self.dim * vc.get("mlp_ratio", 4))
+        mk = lambda *s: torch.zeros(*s, dtype=dtype, device=device)
+        # Conv3d(kernel = stride = patch) over non-overlapping patches is a linear map of the patch
+        self.add_param("patch_embed.proj.weight", mk(self.dim, in_ch * self.tp * self.patch * self.patch),
+                       {"patch_embed.proj.weight": lambda w, t=None: self._params["patch_embed.proj.weight"].copy_(
+                           w.reshape(self.dim, -1).to(dtype))})
+        blocks = Module()
+        self.add_module("blocks", blocks)
+        self.blocks = [blocks.add_module(str(i), VisionBlock(self.dim, self.heads, mlp_dim, dtype, device,
+                                                             vc.get("hidden_act", "quick_gelu"))) for i in range(depth)]
+        m2 = self.merge * self.merge
+        for name, shape in (("merger.ln_q.weight", (self.dim,)), ("merger.ln_q.bias", (self.dim,)),
+                            ("merger.mlp.0.weight", (self.dim * m2, self.dim * m2)), ("merger.mlp.0.bias", (self.dim * m2,)),
+                            ("merger.mlp.2.weight", (out_hidden, self.dim * m2)), ("merger.mlp.2.bias", (out_hidden,))):
+            self.add_param(name, mk(*shape))
+
+    def rot_pos_emb(self, grid_thw, device):
+        """2-D rotary angles per patch, in the merge-window order the processor emits patches in."""
+        hd = self.dim // self.heads
+        inv = 1.0 / (10000.0 ** (torch.arange(0, hd // 2, 2, dtype=torch.float32, device=device) / (hd // 2)))
+        out = []
+        m = self.merge
+        for t, h, w in grid_thw.tolist():
+            hp = torch.arange(h, device=device).view(h, 1).expand(h, w)
+            wp = torch.arange(w, device=device).view(1, w).expand(h, w)
+            order = lambda z: z.reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).reshape(-1)
+            ids = torch.stack([order(hp), order(wp)], dim=-1).repeat(t, 1).float()       # [t*h*w, 2]
+            ang = (ids[:, :, None] * inv[None, None, :]).reshape(ids.shape[0], -1)        # [N, hd/2]
+            out.append(ang)
+        ang = torch.cat(out)
+        emb = torch.cat([ang, ang], dim=-1)                                             # [N, hd]
+        return emb.cos()[:, None, :], emb.sin()[:, None, :]
+
+    def forward(self, pixel_values, grid_thw):
+        """pixel_values [N_patches, C*tp*p*p] -> image token embeddings [N_patches / merge^2, hidden]."""
+        p = self._params
+        x = F.linear(pixel_values.to(p["patch_embed.proj.weight"].dtype), p["patch_embed.proj.weight"])
+        cos, sin = self.rot_pos_emb(grid_thw, x.device)
+        cos, sin = cos.to(x.dtype), sin.to(x.dtype)
+        sizes = [int(t * h * w) for t, h, w in grid_thw.tolist()]
+        cu = [0]
+        for s in sizes:
+            cu.append(cu[-1] + s)
+        for blk in self.blocks:
+            x = blk(x, cos, sin, cu)
+        x = F.layer_norm(x, x.shape[-1:], p["merger.ln_q.weight"], p["merger.ln_q.bias"], 1e-6)
+        x = x.view(-1, self.dim * self.merge * self.merge)
+        x = F.gelu(F.linear(x, p["merger.mlp.0.weight"], p["merger.mlp.0.bias"]))
+        return F.linear(x, p["merger.mlp.2.weight"], p["merger.mlp.2.bias"])
+
+    __call__ = forward
+
+
+class Qwen2VLForConditionalGeneration(DenseCausalLM):
+    def __init__(self, args, dtype=torch.bfloat16, device="cpu", ps=None):
+        super().__init__(args, dtype, device, ps or single())
+        self.visual = self.add_module("visual", VisionTower(args.vision_config or {}, args.hidden_size, dtype, device))
+        half = args.rotary_dim // 2
+        self.mrope_section = list(args.mrope_section) or [half - 2 * (half * 3 // 8), half * 3 // 8, half * 3 // 8]
+
+    def encode_images(self, pixel_values, grid_thw):
+        return self.visual(pixel_values.to(self.device), grid_thw)
+
+
+@register_model("qwen2_vl", "qwen2_5_vl", "Qwen2VLForConditionalGeneration", "Qwen2_5_VLForConditionalGeneration")
+def build_qwen2_vl(args, dtype, device, ps):
+    return Qwen2VLForConditionalGeneration(args, dtype, device, ps)
