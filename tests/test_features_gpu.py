@@ -1,0 +1,103 @@
+"""Engine features on a GPU (bf16, CUDA kernels): speculative decoding, beam search, PD pair, host
+tier, constrained decoding and the VLM path.  Exact-equality checks are made against runs that use
+the same kernels; where two paths differ in kernels (one-pass verification uses the prefill kernel,
+plain decoding the decode kernel) a small number of late divergences on near-tie logits is allowed."""
+import numpy as np
+import pytest
+import torch
+
+from xllm_b200 import LLM, SamplingParams
+
+pytestmark = pytest.mark.gpu
+
+KW = dict(devices="cuda:0", dtype="bfloat16", block_size=16, num_blocks=256, max_seqs_per_batch=8, max_tokens_per_batch=256)
+
+
+def _prompts(seed=0):
+    g = torch.Generator().manual_seed(seed)
+    base = torch.randint(0, 32000, (12,), generator=g).tolist()
+    return [base * 3, torch.randint(0, 32000, (40,), generator=g).tolist(), (base[:5] * 6)[:29]]
+
+
+def _close(a, b, min_prefix=4):
+    n = 0
+    for x, y in zip(a, b):
+        if x != y:
+            break
+        n += 1
+    return n >= min(min_prefix, len(a))
+
+
+def test_speculative_ngram_on_gpu():
+    sp = SamplingParams(max_tokens=24, temperature=0.0, ignore_eos=True)
+    plain = [o.outputs[0].token_ids for o in LLM("tiny", enable_schedule_overlap=False, **KW).generate(_prompts(), sp)]
+    llm = LLM("tiny", enable_schedule_overlap=False, num_speculative_tokens=3, **KW)
+    got = [o.outputs[0].token_ids for o in llm.generate(_prompts(), sp)]
+    assert all(len(g) == 24 for g in got)
+    assert all(_close(a, b) for a, b in zip(plain, got)), (plain, got)
+    assert llm.engine.spec.steps > 0
+
+
+def test_beam_search_width_one_is_greedy_on_gpu():
+    llm = LLM("tiny", enable_prefix_cache=False, **KW)
+    p = _prompts(1)[1]
+    greedy = llm.generate([p], SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))[0].outputs[0].token_ids
+    one = llm.beam_search([p], beam_width=1, max_tokens=8, ignore_eos=True)[0][0].token_ids
+    assert _close(greedy, one, 6)
+    wide = llm.beam_search([p], beam_width=4, max_tokens=8, ignore_eos=True)[0]
+    assert len(wide) == 4 and wide[0].score >= wide[-1].score
+    assert llm.engine.scheduler.block_manager(0).num_used_blocks == 0
+
+
+def test_pd_pair_and_host_tier_on_gpu():
+    from xllm_b200.engine.disagg import PDCoordinator, make_pd_pair
+    kw = dict(device="cuda:0", dtype="bfloat16", block_size=16, num_blocks=128, max_seqs_per_batch=8,
+              max_tokens_per_batch=128, enable_prefix_cache=False)
+    prompts = _prompts(2)
+    want = [o.outputs[0].token_ids for o in LLM("tiny", enable_prefix_cache=False, **KW).generate(
+        prompts, SamplingParams(max_tokens=10, temperature=0.0, ignore_eos=True))]
+    p, d = make_pd_pair("tiny", **kw)
+    pd = PDCoordinator(p, d)
+    for i, pr in enumerate(prompts):
+        pd.add_request(f"r{i}", pr, max_tokens=10, temperature=0.0, ignore_eos=True)
+    got = {f"r{i}": [] for i in range(len(prompts))}
+    pd.run_until_done(lambda ev: got[ev.request_id].append(ev.token) if ev.token >= 0 else None)
+    assert all(_close(w, got[f"r{i}"], 6) for i, w in enumerate(want)), (want, got)
+    # host tier
+    llm = LLM("tiny", devices="cuda:0", dtype="bfloat16", block_size=16, num_blocks=14, max_seqs_per_batch=2,
+              max_tokens_per_batch=128, enable_prefix_cache=True, host_kv_blocks=64)
+    g = torch.Generator().manual_seed(2)
+    a = torch.randint(0, 32000, (100,), generator=g).tolist()
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    first = llm.generate([a], sp)[0].outputs[0].token_ids
+    for _ in range(3):
+        llm.generate([torch.randint(0, 32000, (120,), generator=g).tolist()], sp)
+    again = llm.generate([a], sp)[0].outputs[0].token_ids
+    assert again == first and llm.engine.host_tier.stats()["loaded"] >= 6
+
+
+def test_vlm_on_gpu_matches_cpu_tokens():
+    from test_vlm_cpu import IMG, VEND, VSTART, _args
+    from xllm_b200.api.vlm import VLM
+    from xllm_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from xllm_b200.multimodal import Qwen2VLImageProcessor
+    rng = np.random.default_rng(1)
+    img = (rng.random((80, 100, 3)) * 255).astype(np.uint8)
+    reqs = [dict(prompt_token_ids=[11, 12, VSTART, IMG, VEND, 13, 14, 15], images=[img])]
+    outs = {}
+    for dev, dt in (("cpu", "float32"), ("cuda:0", "bfloat16")):
+        vlm = VLM.__new__(VLM)
+        vlm.engine = LLMEngine(EngineConfig(model="v", device=dev, dtype=dt, num_blocks=64, enable_graph=False,
+                                            max_tokens_per_batch=16, enable_schedule_overlap=False),
+                               model_args=_args(head_dim=64, hidden=256, sections=(8, 12, 12)))
+        vlm.tokenizer = None
+        if dev == "cpu":
+            vlm.engine.model.init_random(std=0.05, seed=3)
+            cpu_params = dict(vlm.engine.model.named_params())
+        else:   # the same weights on the GPU (random generators differ between devices)
+            for n, t in vlm.engine.model.named_params():
+                t.copy_(cpu_params[n].to(t.dtype))
+        vlm.processor = Qwen2VLImageProcessor(14, 2, 2, min_pixels=56 * 56, max_pixels=112 * 112)
+        vlm.image_token_id = IMG
+        outs[dev] = vlm.generate_mm(reqs, SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True))[0]
+    assert len(outs["cuda:0"]) == 5 and outs["cuda:0"][:2] == outs["cpu"][:2], outs

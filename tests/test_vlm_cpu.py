@@ -15,11 +15,11 @@ from xllm_b200.multimodal import Qwen2VLImageProcessor, expand_image_tokens, mro
 IMG, VSTART, VEND = 900, 901, 902
 
 
-def _args():
-    return ModelArgs(model_type="qwen2_vl", vocab_size=1000, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
-                     num_key_value_heads=2, head_dim=16, intermediate_size=128, qk_norm=False, attention_bias=True,
+def _args(head_dim=16, hidden=64, sections=(2, 3, 3)):
+    return ModelArgs(model_type="qwen2_vl", vocab_size=1000, hidden_size=hidden, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=head_dim, intermediate_size=128, qk_norm=False, attention_bias=True,
                      rope_theta=10000.0, max_position_embeddings=512, tie_word_embeddings=False, image_token_id=IMG,
-                     vision_start_token_id=VSTART, mrope_section=[2, 3, 3],
+                     vision_start_token_id=VSTART, mrope_section=list(sections),
                      vision_config=dict(embed_dim=32, num_heads=2, depth=2, mlp_ratio=2, patch_size=14,
                                         spatial_merge_size=2, temporal_patch_size=2, in_chans=3))
 
