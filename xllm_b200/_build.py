@@ -157,6 +157,28 @@ def runtime_sources():
     return out
 
 
+def build_c_api(force: bool = False, verbose: bool = False) -> Path:
+    """Compile ``libxllm_c.so``: the C interface (csrc/c_api/xllm.h) over an embedded interpreter."""
+    with _BuildLock():
+        src = CSRC / "c_api" / "xllm_c_api.cpp"
+        hdr = CSRC / "c_api" / "xllm.h"
+        out = LIBDIR / "libxllm_c.so"
+        stamp = LIBDIR / "libxllm_c.sha"
+        ldlib = sysconfig.get_config_var("LDLIBRARY") or "libpython3.so"
+        libname = ldlib[3:].split(".so")[0] if ldlib.startswith("lib") else "python3"
+        flags = CXX_FLAGS + ["-I", sysconfig.get_paths()["include"]]
+        libs = ["-L", sysconfig.get_config_var("LIBDIR") or "/usr/lib", "-l" + libname, "-pthread", "-ldl"]
+        want = _sha([src, hdr], " ".join(map(str, flags + libs)))
+        if force or not out.exists() or not stamp.exists() or stamp.read_text() != want:
+            LIBDIR.mkdir(parents=True, exist_ok=True)
+            OBJDIR.mkdir(parents=True, exist_ok=True)
+            obj = OBJDIR / "c_api.o"
+            _run([CXX, *flags, "-c", src, "-o", obj], verbose)
+            _link_atomic([CXX, "-shared"], out, [obj], libs, verbose)
+            stamp.write_text(want)
+        return out
+
+
 def build_runtime(force: bool = False, verbose: bool = False) -> Path:
     """Compile the C++ runtime + pybind11 module ``xllm_b200._rt``."""
     with _BuildLock():
@@ -202,6 +224,7 @@ def _build_runtime(force, verbose) -> Path:
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_kernels(force=force, verbose=verbose)
     build_runtime(force=force, verbose=verbose)
+    build_c_api(force=force, verbose=verbose)
 
 
 if __name__ == "__main__":
@@ -211,9 +234,11 @@ if __name__ == "__main__":
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--ptxas", action="store_true", help="print registers/spills/smem per kernel")
-    ap.add_argument("--only", choices=["kernels", "runtime"], default=None)
+    ap.add_argument("--only", choices=["kernels", "runtime", "c_api"], default=None)
     a = ap.parse_args()
     if a.only in (None, "kernels"):
         print(build_kernels(force=a.force or a.ptxas, verbose=a.verbose, ptxas_info=a.ptxas))
     if a.only in (None, "runtime"):
         print(build_runtime(force=a.force, verbose=a.verbose))
+    if a.only in (None, "c_api"):
+        print(build_c_api(force=a.force, verbose=a.verbose))
