@@ -117,3 +117,22 @@ def test_client_disconnect_aborts_request(server):
         time.sleep(0.02)
     assert not server.calls and not server.engine.has_unfinished()
     assert server.engine.stats()["kv_utilization"] == 0.0
+
+
+def test_rerank_and_sample_routes(server):
+    st, data = _post(server.port, "/v1/rerank", {"query": "hello world", "documents": ["hello world", "tiny corpus", "user"],
+                                                 "top_n": 2})
+    assert st == 200
+    obj = json.loads(data)
+    assert len(obj["results"]) == 2 and obj["results"][0]["index"] == 0          # the identical text ranks first
+    assert obj["results"][0]["relevance_score"] >= obj["results"][1]["relevance_score"]
+    st, data = _post(server.port, "/v1/sample", {"prompt": "this is a tiny corpus for this test", "logprobs": 3,
+                                                 "selector": {"type": "literal", "value": "this"}})
+    assert st == 200
+    obj = json.loads(data)
+    assert obj["object"] == "sample_completion" and len(obj["choices"]) == 2     # "this" occurs twice
+    for c in obj["choices"]:
+        lp = c["logprobs"]["token_logprobs"]
+        assert len(lp) == 3 and lp[0] >= lp[1] >= lp[2] and lp[0] <= 0
+    st, _ = _post(server.port, "/v1/sample", {"prompt": "x", "selector": {"type": "regex", "value": "x"}})
+    assert st == 400

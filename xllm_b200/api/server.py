@@ -132,6 +132,10 @@ class ApiServer:
             return self._chat(req, body, "anthropic")
         if path == "/v1/embeddings":
             return self._embeddings(req, body)
+        if path == "/v1/rerank":
+            return self._rerank(req, body)
+        if path == "/v1/sample":
+            return self._sample(req, body)
         if path in ("/sleep", "/pause"):
             self.engine.pause(str(body.get("mode", "KEEP")).upper())
             return self._json(req.id, 200, {"status": "paused"})
@@ -251,6 +255,49 @@ class ApiServer:
         n_tok = sum(len(x) for x in ids)
         self._json(req.id, 200, {"object": "list", "data": data, "model": self.model_name,
                                  "usage": {"prompt_tokens": n_tok, "total_tokens": n_tok}})
+
+    def _rerank(self, req, body):
+        from .embedding import rerank_scores
+        docs = [d if isinstance(d, str) else d.get("text", "") for d in body.get("documents", [])]
+        if not docs or "query" not in body:
+            return self._error(req.id, 400, "rerank needs `query` and `documents`")
+        trunc = int(body.get("truncate_prompt_tokens") or 0)
+        enc = lambda t: self.tok.encode(t)[-trunc:] if trunc > 0 else self.tok.encode(t)
+        q, ds = enc(body["query"]), [enc(d) for d in docs]
+        scores = rerank_scores(self.engine, q, ds)
+        order = sorted(range(len(docs)), key=lambda i: -scores[i])
+        top_n = int(body.get("top_n") or len(docs))
+        results = [{"index": i, "relevance_score": scores[i], "document": {"text": docs[i]}} for i in order[:top_n]]
+        n_tok = len(q) + sum(len(d) for d in ds)
+        self._json(req.id, 200, {"id": "rerank-" + str(req.id), "model": self.model_name, "results": results,
+                                 "usage": {"prompt_tokens": n_tok, "total_tokens": n_tok}})
+
+    def _sample(self, req, body):
+        """Next-token distributions at every place of the prompt where the selector's literal ends."""
+        from .embedding import next_token_logprobs
+        prompt = body.get("prompt", "")
+        sel = body.get("selector") or {}
+        if sel.get("type", "literal") != "literal" or not sel.get("value"):
+            return self._error(req.id, 400, "selector must be {\"type\": \"literal\", \"value\": ...}")
+        n_lp = max(1, min(5, int(body.get("logprobs") or 1)))
+        ids = self.tok.encode(prompt)
+        ends, start = [], 0
+        while True:
+            k = prompt.find(sel["value"], start)
+            if k < 0:
+                break
+            ends.append(k + len(sel["value"]))
+            start = k + 1
+        positions = [max(len(self.tok.encode(prompt[:e])), 1) - 1 for e in ends]
+        tops = next_token_logprobs(self.engine, ids, positions, n_lp) if positions else []
+        choices = []
+        for i, (pos, top) in enumerate(zip(positions, tops)):
+            choices.append({"index": i, "text": self.tok.decode([top[0][0]]), "token_position": pos,
+                            "logprobs": {"tokens": [self.tok.decode([t]) for t, _ in top], "token_ids": [t for t, _ in top],
+                                         "token_logprobs": [v for _, v in top]}})
+        self._json(req.id, 200, {"id": body.get("request_id") or "sample-" + str(req.id), "object": "sample_completion",
+                                 "created": int(time.time()), "model": self.model_name, "choices": choices,
+                                 "usage": {"prompt_tokens": len(ids), "total_tokens": len(ids)}})
 
     # ------------------------------------------------------------------ output events
     def _sse(self, call, obj):
