@@ -185,3 +185,34 @@ def test_embedding_gather_blockcopy_advance():
     toks = torch.tensor([-1, 5, -3], device=DEV)
     ops.resolve_placeholders(toks, torch.tensor([11, 12, 13], device=DEV))
     assert toks.tolist() == [11, 5, 13]
+
+
+@pytest.mark.parametrize("nq,nkv,page", [(8, 2, 16), (4, 4, 32), (16, 2, 64), (8, 8, 128)])
+@pytest.mark.parametrize("impl", ["tcgen05", "legacy"])
+def test_paged_prefill_attention_tcgen05_and_legacy(nq, nkv, page, impl, monkeypatch):
+    """head_dim 128: the tcgen05/TMEM kernel and the mma.sync kernel against the fp32 reference on
+    ragged batches with cached context (chunked prefill), tiles that end inside a page, one-token
+    queries and a long sequence with several kv tiles per query tile."""
+    monkeypatch.setenv("XLLM_PREFILL_ATTN", impl)
+    q_lens = [5, 64, 130, 1, 257, 128, 700]
+    kv_lens = [5, 64, 300, 90, 257, 128 + 256, 700 + 3]
+    B = len(q_lens)
+    kc, vc, bt = _paged_setup(B, nq, nkv, 128, page, kv_lens, seed=9)
+    T = sum(q_lens)
+    big = torch.randn(T, nq * 128 + 64, device=DEV, dtype=torch.bfloat16)
+    q = big[:, : nq * 128].view(T, nq, 128)                      # strided rows, like a slice of the fused QKV output
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device=DEV, dtype=torch.int32)
+    kl = torch.tensor(kv_lens, device=DEV, dtype=torch.int32)
+    scale = 1 / math.sqrt(128)
+    out = torch.zeros(T, nq, 128, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):
+        y = ops.paged_prefill_attention(q, kc, vc, bt, cu, kl, max(q_lens), scale, out=out)
+    yr = ref.paged_attention(q, kc, vc, bt, cu, kl, scale)
+    _close(y, yr, 2e-2)
+    from xllm_b200.ops import _lib
+    assert _lib.load().xllm_fmha_error_status() == 0
+    # a decode-first mixed batch: the prefill kernel only sees the tail of cu_q / kv_lens / block_table
+    y2 = ops.paged_prefill_attention(q, kc, vc, bt[2:], cu[2:], kl[2:], max(q_lens), scale, out=torch.zeros_like(out))
+    r0 = int(cu[2])
+    _close(y2[r0:], yr[r0:], 2e-2)
+    assert torch.count_nonzero(y2[:r0]) == 0

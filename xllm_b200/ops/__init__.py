@@ -6,6 +6,8 @@ Counterpart of the platform-dispatching `xllm::kernel::*` free functions of the 
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib, reference
@@ -174,6 +176,16 @@ def paged_prefill_attention(q, k_cache, v_cache, block_table, cu_q, kv_lens, max
         out = torch.empty((T, nq, d), dtype=q.dtype, device=q.device)
     assert q.stride(-1) == 1 and q.stride(1) == d
     B = kv_lens.shape[0]
+    if (d == 128 and window == 0 and page in (16, 32, 64, 128) and k_cache.is_contiguous() and v_cache.is_contiguous()
+            and os.environ.get("XLLM_PREFILL_ATTN", "tcgen05") != "legacy"):
+        # tcgen05 / TMEM kernel (csrc/kernels/attn_prefill_tc.cu)
+        check(_lib_().xllm_paged_prefill_attn_tc(ptr(out), out.stride(0), ptr(q), q.stride(0), T, ptr(k_cache),
+                                                 ptr(v_cache), k_cache.shape[0], ptr(block_table),
+                                                 block_table.stride(0), ptr(cu_q), ptr(kv_lens), B, int(max_q_len),
+                                                 nq, nkv, page, scale, int(causal), stream()),
+              "paged_prefill_attn_tc")
+        _count()
+        return out
     check(_lib_().xllm_paged_prefill_attn(ptr(out), out.stride(0), ptr(q), q.stride(0), ptr(k_cache),
                                           ptr(v_cache), ptr(block_table), block_table.stride(0),
                                           ptr(cu_q), ptr(kv_lens), B, int(max_q_len), nq, nkv, d,

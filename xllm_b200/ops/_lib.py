@@ -66,6 +66,8 @@ def _declare(lib):
         "xllm_paged_decode_attn": [P, P, L, P, P, P, I, P, I, I, I, I, I, F, I, P, P],
         "xllm_attn_merge": [P, P, P, L, I, I, P],
         "xllm_paged_prefill_attn": [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P],
+        "xllm_paged_prefill_attn_tc": [P, L, P, L, L, P, P, L, P, I, P, P, I, I, I, I, I, F, I, P],
+        "xllm_fmha_error_status": [],
         "xllm_sample": [P, L, I, I, I, P, P, P, P, P, U64, U64, P],
         "xllm_apply_penalties": [P, L, I, I, I, P, P, I, P, P, P, P],
         "xllm_embedding": [P, P, P, L, I, L, L, P],
