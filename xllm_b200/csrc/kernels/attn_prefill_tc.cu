@@ -203,19 +203,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_consta
       const int st = j & 1;
       if (!mbar_wait_warp(kv_empty(st), ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
       const int pg = j * pages + lane;
-      int myblk = (lane < pages && pg < n_blk) ? bt[pg] : 0;   // pages past the sequence read block 0 (masked)
+      const int myblk = (lane < pages && pg < n_blk) ? bt[pg] : 0;   // pages past the sequence read block 0 (masked)
       if (lane == 0) mbar_expect_tx(kv_full(st), 2 * kTile);
+      __syncwarp();
       const uint32_t kdst = sbase + KV_OFF + st * 2 * kTile, vdst = kdst + kTile;
-      for (int i = 0; i < pages; ++i) {
-        const int blk = __shfl_sync(0xffffffffu, myblk, i);
-        if (lane == 0) {
-          const int y = (blk * p.nkv + hk) * p.page;
-          const uint32_t off = (uint32_t)(i * p.page * 128);
-          tma_load_2d(kdst + off, &tma_k, 0, y, kv_full(st));
-          tma_load_2d(kdst + kHalf + off, &tma_k, 64, y, kv_full(st));
-          tma_load_2d(vdst + off, &tma_v, 0, y, kv_full(st));
-          tma_load_2d(vdst + kHalf + off, &tma_v, 64, y, kv_full(st));
-        }
+      if (lane < pages) {
+        // every lane gathers its own page: the four copies of all pages issue together
+        const int y = (myblk * p.nkv + hk) * p.page;
+        const uint32_t off = (uint32_t)(lane * p.page * 128);
+        tma_load_2d(kdst + off, &tma_k, 0, y, kv_full(st));
+        tma_load_2d(kdst + kHalf + off, &tma_k, 64, y, kv_full(st));
+        tma_load_2d(vdst + off, &tma_v, 0, y, kv_full(st));
+        tma_load_2d(vdst + kHalf + off, &tma_v, 64, y, kv_full(st));
       }
       __syncwarp();
     }
