@@ -21,6 +21,7 @@ act_and_mul_kernel(bf16* __restrict__ out, const bf16* __restrict__ x, int64_t t
   const int vec_per_row = d >> 3;
   const int64_t total = tokens * vec_per_row;
   pdl_wait();
+  pdl_launch_dependents();  // dependents may be scheduled now; they block in their own pdl_wait()
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t t = i / vec_per_row;
@@ -36,7 +37,6 @@ act_and_mul_kernel(bf16* __restrict__ out, const bf16* __restrict__ x, int64_t t
     }
     reinterpret_cast<bf16x8*>(out + t * (int64_t)d)[v] = pack8(o);
   }
-  pdl_launch_dependents();
 }
 
 }  // namespace xllm
@@ -51,8 +51,8 @@ XLLM_API int xllm_act_and_mul(void* out, const void* x, int64_t tokens, int d, i
   int grid = (int)((total + 255) / 256);
   if (grid > 148 * 16) grid = 148 * 16;
   cudaStream_t s = (cudaStream_t)stream;
-  if (act == 0) act_and_mul_kernel<0><<<grid, 256, 0, s>>>((bf16*)out, (const bf16*)x, tokens, d, x_stride);
-  else if (act == 1) act_and_mul_kernel<1><<<grid, 256, 0, s>>>((bf16*)out, (const bf16*)x, tokens, d, x_stride);
-  else act_and_mul_kernel<2><<<grid, 256, 0, s>>>((bf16*)out, (const bf16*)x, tokens, d, x_stride);
+  if (act == 0) launch_pdl(act_and_mul_kernel<0>, dim3(grid), dim3(256), 0, s, (bf16*)out, (const bf16*)x, tokens, d, x_stride);
+  else if (act == 1) launch_pdl(act_and_mul_kernel<1>, dim3(grid), dim3(256), 0, s, (bf16*)out, (const bf16*)x, tokens, d, x_stride);
+  else launch_pdl(act_and_mul_kernel<2>, dim3(grid), dim3(256), 0, s, (bf16*)out, (const bf16*)x, tokens, d, x_stride);
   return XLLM_LAUNCH_CHECK();
 }

@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(DecodeParams p) {
   const int kvh = blockIdx.x / qtiles, qt = blockIdx.x - kvh * qtiles;
   const int b = blockIdx.y, split = blockIdx.z;
   pdl_wait();
+  pdl_launch_dependents();  // dependents may be scheduled now; they block in their own pdl_wait()
   const int seq_len = p.seq_lens[b];
   const int tiles_total = (seq_len + 15) >> 4;
   const int tps = (tiles_total + p.splits - 1) / p.splits;
@@ -178,7 +179,6 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(DecodeParams p) {
     }
   }
   cp_async_wait<0>();
-  pdl_launch_dependents();
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
@@ -234,6 +234,7 @@ __global__ void attn_merge_kernel(bf16* __restrict__ out, const float* __restric
                                   const float* __restrict__ lse, int splits, int D) {
   const int64_t row = blockIdx.x;
   pdl_wait();
+  pdl_launch_dependents();  // dependents may be scheduled now; they block in their own pdl_wait()
   float M = -INFINITY;
   for (int s = 0; s < splits; ++s) M = fmaxf(M, lse[row * splits + s]);
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
@@ -263,7 +264,7 @@ static int launch_decode(const DecodeParams& p, int batch, cudaStream_t s) {
   }
   const int qtiles = (p.group + 15) / 16;
   dim3 grid(p.nkv * qtiles, batch, p.splits);
-  paged_decode_kernel<D, STAGES><<<grid, 128, SMEM, s>>>(p);
+  launch_pdl(paged_decode_kernel<D, STAGES>, dim3(grid), dim3(128), SMEM, s, p);
   return XLLM_LAUNCH_CHECK();
 }
 
@@ -301,7 +302,7 @@ XLLM_API int xllm_paged_decode_attn(void* out, const void* q, int64_t q_stride, 
   else if (d == 256) rc = launch_decode<256, 2>(p, batch, s);
   else return (int)cudaErrorInvalidValue;
   if (rc != 0 || splits == 1) return rc;
-  attn_merge_kernel<<<batch * nq, d < 128 ? d : 128, 0, s>>>(p.out, p.o_part, p.lse_part, splits, d);
+  launch_pdl(attn_merge_kernel, dim3(batch * nq), dim3(d < 128 ? d : 128), 0, s, p.out, p.o_part, p.lse_part, splits, d);
   return XLLM_LAUNCH_CHECK();
 }
 
@@ -310,7 +311,7 @@ XLLM_API int xllm_attn_merge(void* out, const void* o_part, const void* lse_part
                              int splits, int d, void* stream) {
   using namespace xllm;
   if (rows == 0) return 0;
-  attn_merge_kernel<<<(unsigned)rows, d < 128 ? d : 128, 0, (cudaStream_t)stream>>>(
+  launch_pdl(attn_merge_kernel, dim3((unsigned)rows), dim3(d < 128 ? d : 128), 0, (cudaStream_t)stream, 
       (bf16*)out, (const float*)o_part, (const float*)lse_part, splits, d);
   return XLLM_LAUNCH_CHECK();
 }
@@ -378,6 +379,6 @@ XLLM_API int xllm_paged_decode_attn_noalloc(void* out, const void* q, int64_t q_
   else if (d == 256) rc = launch_decode<256, 2>(p, batch, s);
   else return (int)cudaErrorInvalidValue;
   if (rc != 0 || splits == 1) return rc;
-  attn_merge_kernel<<<batch * nq, d < 128 ? d : 128, 0, s>>>(p.out, p.o_part, p.lse_part, splits, d);
+  launch_pdl(attn_merge_kernel, dim3(batch * nq), dim3(d < 128 ? d : 128), 0, s, p.out, p.o_part, p.lse_part, splits, d);
   return XLLM_LAUNCH_CHECK();
 }

@@ -4,6 +4,7 @@
 // takes raw device pointers, allocates nothing unless stated, launches on the given
 // stream and returns the cudaError_t of the launch as an int (0 == success).
 #pragma once
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -77,6 +78,34 @@ __device__ __forceinline__ bf16x8 pack8(const float* f) {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// Launch with the programmatic-dependent-launch attribute: the kernel may start (and run its
+// prologue up to `pdl_wait()`) while the tail of the previous kernel of the stream is still running.
+// Only for kernels that execute pdl_wait() before their first access to global memory.
+// XLLM_PDL=0 turns the attribute off.
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("XLLM_PDL");
+    v = (e == nullptr || atoi(e) != 0) ? 1 : 0;
+  }
+  return v == 1;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 // Programmatic dependent launch hooks (no-ops when the launch carries no PDL attribute).

@@ -495,6 +495,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   pdl_wait();
+  pdl_launch_dependents();  // dependents may be scheduled now; they block in their own pdl_wait()
 
   if (warp == 0) {
     {
@@ -648,7 +649,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     }
     if (lane == 0) bulk_wait_all();  // every output store has completed before the CTA exits
   }
-  pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag && err_word != nullptr) atomicExch(err_word, 1);
@@ -813,6 +813,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   pdl_wait();
+  pdl_launch_dependents();  // dependents may be scheduled now; they block in their own pdl_wait()
 
   if (warp == 0) {
     {
@@ -942,7 +943,6 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
     }
     if (lane == 0) bulk_wait_all();
   }
-  pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag && err_word != nullptr) atomicExch(err_word, 1);
@@ -1085,7 +1085,7 @@ static int launch_gemm(const void* a, const void* w, void* c, const void* bias, 
   if (mode.ks > 1 && !make_tmap_f32(&tws, mode.ws, M, N)) return (int)cudaErrorInvalidValue;
   const int units = tiles * mode.ks;
   int grid = units < max_ctas ? units : max_ctas;
-  gemm_bf16_tcgen05_kernel<BN, STAGES, KS, DUAL><<<grid, DUAL ? 224 : 192, S::TOTAL, s>>>(ta, tb, tc, tws, (const bf16*)bias, M, N, K, a_box,
+  launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, KS, DUAL>, dim3(grid), dim3(DUAL ? 224 : 192), S::TOTAL, s, ta, tb, tc, tws, (const bf16*)bias, M, N, K, a_box,
                                                                  w_packed, tile_expert, N, mode, g_err_word[dev & 63]);
   return XLLM_LAUNCH_CHECK();
 }
@@ -1125,7 +1125,7 @@ static int launch_gemm_pair(const void* a, const void* w, void* c, const void* b
   if (mode.ks > 1 && !make_tmap_f32(&tws, mode.ws, M, N)) return (int)cudaErrorInvalidValue;
   const int units = tiles * mode.ks;
   int pairs = units < max_ctas / 2 ? units : max_ctas / 2;
-  gemm_bf16_tcgen05_pair_kernel<BN, STAGES, KS, DUAL><<<2 * pairs, DUAL ? 224 : 192, S::TOTAL, s>>>(ta, tb, tc, tws, (const bf16*)bias, M, N, K,
+  launch_pdl(gemm_bf16_tcgen05_pair_kernel<BN, STAGES, KS, DUAL>, dim3(2 * pairs), dim3(DUAL ? 224 : 192), S::TOTAL, s, ta, tb, tc, tws, (const bf16*)bias, M, N, K,
                                                                             w_packed, mode, g_err_word[dev & 63]);
   return XLLM_LAUNCH_CHECK();
 }

@@ -16,6 +16,7 @@ embedding_kernel(bf16* __restrict__ out, const bf16* __restrict__ table,
   const int vec = hidden >> 3;
   const int64_t total = tokens * vec;
   pdl_wait();
+  pdl_launch_dependents();  // dependents may be scheduled now; they block in their own pdl_wait()
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t t = i / vec;
@@ -26,7 +27,6 @@ embedding_kernel(bf16* __restrict__ out, const bf16* __restrict__ table,
       val = reinterpret_cast<const uint4*>(table + (id - vocab_start) * hidden)[v];
     reinterpret_cast<uint4*>(out + t * hidden)[v] = val;
   }
-  pdl_launch_dependents();
 }
 
 // out[i, :] = in[idx[i], :]  (rows of `row_bytes` bytes, multiple of 16)
@@ -36,13 +36,13 @@ gather_rows_kernel(uint4* __restrict__ out, const uint4* __restrict__ in,
                    int64_t in_stride_vec) {
   const int64_t total = rows * vec_per_row;
   pdl_wait();
+  pdl_launch_dependents();  // dependents may be scheduled now; they block in their own pdl_wait()
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / vec_per_row;
     const int v = (int)(i - r * vec_per_row);
     out[i] = in[idx[r] * in_stride_vec + v];
   }
-  pdl_launch_dependents();
 }
 
 // Copy whole KV blocks src -> dst for `n_layers` caches given as a device pointer table.
@@ -102,7 +102,7 @@ XLLM_API int xllm_embedding(void* out, const void* table, const void* ids, int64
   const int64_t total = tokens * (hidden >> 3);
   int grid = (int)((total + 255) / 256);
   if (grid > 148 * 16) grid = 148 * 16;
-  embedding_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((bf16*)out, (const bf16*)table,
+  launch_pdl(embedding_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (bf16*)out, (const bf16*)table,
                                                           (const int64_t*)ids, tokens, hidden,
                                                           vocab_start, vocab_end);
   return XLLM_LAUNCH_CHECK();
@@ -117,7 +117,7 @@ XLLM_API int xllm_gather_rows(void* out, const void* in, const void* idx, int64_
   const int64_t total = rows * vec;
   int grid = (int)((total + 255) / 256);
   if (grid > 148 * 16) grid = 148 * 16;
-  gather_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
+  launch_pdl(gather_rows_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, 
       (uint4*)out, (const uint4*)in, (const int64_t*)idx, rows, vec, in_stride_bytes / 16);
   return XLLM_LAUNCH_CHECK();
 }

@@ -27,6 +27,7 @@ rmsnorm_kernel(bf16* __restrict__ out, uint8_t* __restrict__ out_q, const bf16* 
   bf16x8* rr = residual ? reinterpret_cast<bf16x8*>(residual + row * (int64_t)hidden) : nullptr;
   const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
   pdl_wait();
+  pdl_launch_dependents();  // dependents may be scheduled now; they block in their own pdl_wait()
   float vals[kNormMaxVec][8];
   float ss = 0.f;
 #pragma unroll
@@ -53,7 +54,6 @@ rmsnorm_kernel(bf16* __restrict__ out, uint8_t* __restrict__ out_q, const bf16* 
   const float inv = rsqrtf(ss / (float)hidden + eps);
   float qs = 1.f;
   if (QUANT == 1) qs = 1.f / (*qscale);
-  pdl_launch_dependents();
 #pragma unroll
   for (int i = 0; i < kNormMaxVec; ++i) {
     const int v = threadIdx.x + i * kNormThreads;
@@ -89,7 +89,7 @@ XLLM_API int xllm_rmsnorm(void* out, const void* x, void* residual, const void* 
   using namespace xllm;
   if (tokens == 0) return 0;
   if (hidden % 8 != 0 || hidden > kNormThreads * kNormMaxVec * 8) return (int)cudaErrorInvalidValue;
-  rmsnorm_kernel<0><<<tokens, kNormThreads, 0, (cudaStream_t)stream>>>(
+  launch_pdl(rmsnorm_kernel<0>, dim3(tokens), dim3(kNormThreads), 0, (cudaStream_t)stream, 
       (bf16*)out, nullptr, (const bf16*)x, (bf16*)residual, (const bf16*)w, nullptr, hidden, eps,
       x_stride, out_stride, gemma);
   return XLLM_LAUNCH_CHECK();
@@ -102,7 +102,7 @@ XLLM_API int xllm_rmsnorm_static_fp8(void* out_q, const void* x, void* residual,
   using namespace xllm;
   if (tokens == 0) return 0;
   if (hidden % 8 != 0 || hidden > kNormThreads * kNormMaxVec * 8) return (int)cudaErrorInvalidValue;
-  rmsnorm_kernel<1><<<tokens, kNormThreads, 0, (cudaStream_t)stream>>>(
+  launch_pdl(rmsnorm_kernel<1>, dim3(tokens), dim3(kNormThreads), 0, (cudaStream_t)stream, 
       nullptr, (uint8_t*)out_q, (const bf16*)x, (bf16*)residual, (const bf16*)w,
       (const float*)scale, hidden, eps, hidden, hidden, 0);
   return XLLM_LAUNCH_CHECK();

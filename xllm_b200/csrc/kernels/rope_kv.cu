@@ -38,6 +38,7 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(RopeKvParams p) {
   const int64_t gh = (int64_t)blockIdx.x * heads_per_block + local;
   const bool active = gh < (int64_t)p.tokens * total_heads;
   pdl_wait();
+  pdl_launch_dependents();  // dependents may be scheduled now; they block in their own pdl_wait()
   const int64_t t = active ? gh / total_heads : 0;
   const int h = active ? (int)(gh - t * total_heads) : 0;
   const int e0 = g * 8;
@@ -102,7 +103,6 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(RopeKvParams p) {
       }
     }
   }
-  pdl_launch_dependents();
   if (!active) return;
   const bf16x8 o = pack8(x);
   if (is_q) {
@@ -149,6 +149,6 @@ XLLM_API int xllm_rope_kv(const void* qkv, int64_t qkv_stride, void* q_out, void
   const int heads_per_block = 256 / tph;
   const int64_t total = (int64_t)tokens * (nq + 2 * nkv);
   const int grid = (int)((total + heads_per_block - 1) / heads_per_block);
-  rope_kv_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+  launch_pdl(rope_kv_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, p);
   return XLLM_LAUNCH_CHECK();
 }

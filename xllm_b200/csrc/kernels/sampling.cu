@@ -213,8 +213,8 @@ XLLM_API int xllm_sample(const void* logits, int64_t row_stride, int dtype, int 
   p.top_k = (const int32_t*)top_k; p.top_p = (const float*)top_p; p.out_ids = (int64_t*)out_ids;
   p.out_logprob = (float*)out_logprob; p.V = vocab; p.seed = seed; p.offset = offset;
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == 0) sample_kernel<bf16><<<batch, kSampleThreads, 0, s>>>(p);
-  else sample_kernel<float><<<batch, kSampleThreads, 0, s>>>(p);
+  if (dtype == 0) launch_pdl(sample_kernel<bf16>, dim3(batch), dim3(kSampleThreads), 0, s, p);
+  else launch_pdl(sample_kernel<float>, dim3(batch), dim3(kSampleThreads), 0, s, p);
   return XLLM_LAUNCH_CHECK();
 }
 
