@@ -124,6 +124,8 @@ class LLMEngine:
         # ---- scheduler
         sc = rt.SchedulerConfig()
         sc.max_tokens_per_batch = cfg.max_tokens_per_batch
+        if self.ps is not single():
+            self.ps.max_tokens_per_batch = cfg.max_tokens_per_batch   # sizes the expert-parallel receive buffers
         sc.max_seqs_per_batch = cfg.max_seqs_per_batch
         sc.enable_chunked_prefill = cfg.enable_chunked_prefill
         sc.max_tokens_per_chunk_for_prefill = cfg.max_tokens_per_chunk_for_prefill
@@ -139,6 +141,7 @@ class LLMEngine:
         self.scheduler = rt.Scheduler(sc)
         self._pending: Optional[StepOutput] = None
         self.grammar = None
+        self.dp_steps = self.fake_steps = 0
         self.mm = {}                 # request id -> MMInput of multimodal requests
         self.host_tier = None
         if cfg.host_kv_blocks > 0 and cfg.enable_prefix_cache:
@@ -316,6 +319,8 @@ class LLMEngine:
         events = []
         batches = self.scheduler.schedule()
         batch = batches[0] if batches else None
+        if self.ps.dp_size > 1 and self.ps.ep_size > 1:
+            self._dp_lockstep(batch)
         if self.host_tier is not None:
             self.host_tier.save_evicted()   # before this step's kernels overwrite the evicted blocks
         if self.cfg.enable_schedule_overlap:
@@ -368,6 +373,41 @@ class LLMEngine:
         return n
 
     # ------------------------------------------------------------------ control (RL-style)
+    # ------------------------------------------------------------------ data-parallel attention
+    def _dp_lockstep(self, batch):
+        """With data-parallel attention and expert parallelism every rank has its own requests but the
+        MoE layers are collective: a rank without a batch this step runs a one-token dummy forward
+        whenever any other rank runs a real one, so that the collectives pair up (the reference's
+        fake inputs for empty DP ranks, llm_engine.cpp prepare_inputs + dp_global_token_nums)."""
+        import torch.distributed as dist
+        flag = torch.tensor([1 if batch is not None else 0], dtype=torch.int32,
+                            device=self.device if self.device.type == "cuda" else "cpu")
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.ps.world_group)
+        self.dp_steps += int(flag.item())
+        if batch is None and int(flag.item()) > 0:
+            self._fake_forward()
+
+    def dp_has_unfinished(self) -> bool:
+        """True while ANY data-parallel rank still has work (ranks leave the serving loop together)."""
+        import torch.distributed as dist
+        flag = torch.tensor([1 if self.has_unfinished() else 0], dtype=torch.int32,
+                            device=self.device if self.device.type == "cuda" else "cpu")
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.ps.world_group)
+        return bool(flag.item())
+
+    @torch.no_grad()
+    def _fake_forward(self):
+        from ..models.layers import AttentionMetadata
+        dev = self.device
+        meta = AttentionMetadata(
+            n_decode=1, n_prefill=0, slots=torch.full((1,), -1, dtype=torch.int32, device=dev),
+            block_table=torch.zeros((1, 8), dtype=torch.int32, device=dev),
+            kv_lens=torch.zeros(1, dtype=torch.int32, device=dev), cu_q=torch.tensor([0, 1], dtype=torch.int32, device=dev),
+            max_q_len=1, max_kv_len=0)
+        self.model.forward(torch.zeros(1, dtype=torch.int64, device=dev), torch.zeros(1, dtype=torch.int64, device=dev),
+                           meta, self.runner.kv_caches)
+        self.fake_steps += 1
+
     def pause(self, mode="KEEP"):
         self.drain()
         self.scheduler.pause(getattr(self.rt.PauseMode, mode))

@@ -78,8 +78,10 @@ class SparseMoeBlock(Module):
             # With EP every rank would add the full shared output, so only the rank that owns
             # expert 0 contributes it.
             shared_out = ops.linear(ops.act_and_mul(self.shared.gate_up(x), a.hidden_act), self.shared.down.weight)
-            if self.ep > 1 and self.e_begin != 0 and self.shared.ps.tp_size == 1:
+            if self.ep > 1 and self.e_begin != 0 and self.shared.ps.tp_size == 1 and self.ps.dp_size == 1:
                 shared_out = None
+        if self.ep > 1 and self.ps.dp_size > 1:
+            return self._forward_dp(x, logits, shared_out)
         comm = self.ps.comm
         out = comm.partial_buffer(T) if (comm is not None and x.is_cuda) else None
         if self._use_a2a(x, comm):
@@ -124,6 +126,51 @@ class SparseMoeBlock(Module):
             ep.moe(x[:0], logits[:0], self.w_gate_up, self.w_down, a.scoring_func, self.bias, a.n_group, a.topk_group,
                    a.norm_topk_prob, a.routed_scaling_factor, None, out=x[:0])   # idle ranks still join the exchange
         return out
+
+    # ---- data-parallel attention: every rank holds DIFFERENT tokens (its own requests) and the
+    # experts are spread over all ranks.  On CUDA the tokens go through the all-to-all kernels; the
+    # library path (CPU, or XLLM_EP_MODE=gather) is the reference's scheme: all-gather the tokens of
+    # all DP ranks (ragged: padded to the longest), run the local experts over everything,
+    # all-reduce, keep the own rows (xllm/core/framework/parallel_state/dp_utils.h:55-104).
+    def _forward_dp(self, x, logits, shared_out):
+        import os
+
+        import torch.distributed as dist
+        a = self.args
+        ps = self.ps
+        group = ps.moe_ep_group or ps.world_group
+        T = x.shape[0]
+        if x.is_cuda and os.environ.get("XLLM_EP_MODE", "a2a") == "a2a" and not torch.cuda.is_current_stream_capturing():
+            ep = getattr(ps, "ep_comm", None)
+            if ep is None:
+                from ..parallel.ep import EpComm
+                ep = EpComm(group, ps.ep_rank, ps.ep_size, x.device, a.num_experts, a.hidden_size, self.top_k,
+                            max_local_tokens=int(getattr(ps, "max_tokens_per_batch", 8192)))
+                ps.ep_comm = ep
+            return ep.moe(x, logits, self.w_gate_up, self.w_down, a.scoring_func, self.bias, a.n_group, a.topk_group,
+                          a.norm_topk_prob, a.routed_scaling_factor, shared_out)
+        W = ps.ep_size
+        counts = torch.zeros(W, dtype=torch.int64, device=x.device)
+        counts[ps.ep_rank] = T
+        dist.all_reduce(counts, group=group)
+        cl = counts.tolist()
+        mx = max(max(cl), 1)
+        pad_x = torch.zeros(mx, x.shape[1], dtype=x.dtype, device=x.device)
+        pad_l = torch.zeros(mx, logits.shape[1], dtype=logits.dtype, device=x.device)
+        pad_x[:T], pad_l[:T] = x, logits
+        gx = [torch.empty_like(pad_x) for _ in range(W)]
+        gl = [torch.empty_like(pad_l) for _ in range(W)]
+        dist.all_gather(gx, pad_x, group=group)
+        dist.all_gather(gl, pad_l, group=group)
+        ax = torch.cat([g[:n] for g, n in zip(gx, cl)])
+        al = torch.cat([g[:n] for g, n in zip(gl, cl)])
+        y = moe_ops.fused_moe(ax, al, self.w_gate_up, self.w_down, self.top_k, a.scoring_func, self.bias, a.n_group,
+                              a.topk_group, a.norm_topk_prob, a.routed_scaling_factor, self.e_begin, a.num_experts)
+        y = y.float() if not y.is_cuda else y
+        dist.all_reduce(y, group=group)
+        off = sum(cl[: ps.ep_rank])
+        mine = y[off:off + T].to(x.dtype)
+        return mine + shared_out if shared_out is not None else mine
 
     def _a2a_rows(self, n, x):
         if getattr(self, "_rows", None) is None or self._rows.shape[0] < n:
