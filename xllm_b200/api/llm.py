@@ -221,10 +221,11 @@ class LLM:
         return outs
 
     def sleep(self, level: int = 1):
-        self.engine.pause("KEEP")
+        """Release the KV cache (level 1) and also move the weights to host memory (level 2)."""
+        self.engine.sleep(level)
 
     def wake_up(self):
-        self.engine.resume()
+        self.engine.wake_up()
 
     def update_weights(self, weights):
         self.engine.update_weights(weights)

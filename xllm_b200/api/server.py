@@ -136,11 +136,17 @@ class ApiServer:
             return self._rerank(req, body)
         if path == "/v1/sample":
             return self._sample(req, body)
-        if path in ("/sleep", "/pause"):
+        if path == "/pause":
             self.engine.pause(str(body.get("mode", "KEEP")).upper())
             return self._json(req.id, 200, {"status": "paused"})
-        if path in ("/wakeup", "/resume"):
+        if path == "/resume":
             self.engine.resume()
+            return self._json(req.id, 200, {"status": "running"})
+        if path == "/sleep":      # releases the KV cache (level 1) and the weights too (level 2)
+            self.engine.sleep(int(body.get("level", 1)))
+            return self._json(req.id, 200, {"status": "sleeping", "level": int(body.get("level", 1))})
+        if path == "/wakeup":
+            self.engine.wake_up()
             return self._json(req.id, 200, {"status": "running"})
         if path == "/start_profile":
             return self._profile(req, True, body)

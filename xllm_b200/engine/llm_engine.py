@@ -141,6 +141,8 @@ class LLMEngine:
         self.scheduler = rt.Scheduler(sc)
         self._pending: Optional[StepOutput] = None
         self.grammar = None
+        self.asleep = 0
+        self._host_weights = None
         self.dp_steps = self.fake_steps = 0
         self.mm = {}                 # request id -> MMInput of multimodal requests
         self.host_tier = None
@@ -414,6 +416,60 @@ class LLMEngine:
 
     def resume(self):
         self.scheduler.resume()
+
+    # ------------------------------------------------------------------ sleep / wake-up
+    def sleep(self, level: int = 1):
+        """Give the device memory back while the instance is idle (the reference's sleep / wakeup /
+        fork_master on its VMM page pool, llm_master.cpp:640-700, framework/xtensor/*).
+
+        level 1: running sequences are preempted (they re-prefill after wake-up), the KV cache
+        tensors are released; level 2: the weights move to pinned host memory as well.  The cached
+        CUDA graphs reference the old cache tensors and are dropped."""
+        if self.asleep:
+            return
+        self.pause("KEEP")
+        self.reset_prefix_cache()
+        r = self.runner
+        self._kv_shapes = [(k.shape, v.shape, k.dtype, k.device) for k, v in r.kv_caches]
+        r.graphs.clear()
+        r.graph_in.clear()
+        r.graph_logits.clear()
+        r.graph_pool = None
+        for i in range(len(r.kv_caches)):
+            r.kv_caches[i] = None
+        if getattr(self.spec, "drafter", None) is not None and hasattr(self.spec.drafter, "kv"):
+            self.spec.drafter.kv = None
+        self._host_weights = None
+        if level >= 2:
+            self._host_weights = []
+            for name, t in self.model.named_params():
+                h = torch.empty(t.shape, dtype=t.dtype, pin_memory=t.is_cuda)
+                h.copy_(t)
+                self._host_weights.append((t, h, t.shape))
+                t.set_(torch.empty(0, dtype=t.dtype, device=t.device))
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+        self.asleep = level
+
+    def wake_up(self):
+        if not self.asleep:
+            return
+        if self._host_weights is not None:
+            for t, h, shape in self._host_weights:
+                t.set_(torch.empty(shape, dtype=t.dtype, device=self.device))
+                t.copy_(h, non_blocking=True)
+            self._host_weights = None
+        r = self.runner
+        for i, (ks, vs, dt, dev) in enumerate(self._kv_shapes):
+            r.kv_caches[i] = (torch.zeros(ks, dtype=dt, device=dev), torch.zeros(vs, dtype=dt, device=dev))
+        if getattr(self.spec, "drafter", None) is not None and hasattr(self.spec.drafter, "kv"):
+            k0, v0 = r.kv_caches[0]
+            self.spec.drafter.kv = (torch.zeros_like(k0), torch.zeros_like(v0))
+        if self.host_tier is not None:
+            self.host_tier.kv = r.kv_caches
+        self.asleep = 0
+        self.resume()
 
     def reset_prefix_cache(self):
         self.scheduler.reset_prefix_cache()
