@@ -53,7 +53,7 @@ def main():
             for pair in (0, 1):
                 if pair and M <= 128:
                     continue
-                for tn in (64, 128, 256):
+                for tn in (64, 128, 192, 256):
                     for ks in (1, 2, 3, 4, 6, 8):
                         if M * N * 4 > (64 << 20) and ks > 1:
                             continue

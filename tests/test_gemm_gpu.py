@@ -114,3 +114,19 @@ def test_gemm_dual_issue_and_single_issue(M, N, K, tile_n, pair, split_k, dual):
             assert bool(((y.float() - ref).abs() <= tol).all())
     finally:
         g.set_dual_issue(False)
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 24576, 512), (256, 24576, 1024), (300, 600, 320), (512, 4096, 4096), (129, 200, 136)])
+@pytest.mark.parametrize("pair,split_k", [(0, 1), (1, 1), (0, 2), (1, 2)])
+def test_gemm_192_wide_tiles(M, N, K, pair, split_k):
+    """192-column tiles (three 64-column epilogue chunks, 384 of 512 TMEM columns) including ragged N."""
+    if pair and M <= 128:
+        pytest.skip("pair tiles need more than 128 rows")
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    b = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    ref = x.float() @ w.float().T + b.float()
+    y = g.gemm_nt(x, w, bias=b, tile_n=192, pair=pair, split_k=split_k)
+    assert g.error_status() == 0
+    assert bool(((y.float() - ref).abs() <= 3e-2 + 1e-2 * ref.abs()).all())

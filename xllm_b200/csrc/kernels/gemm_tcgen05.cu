@@ -198,6 +198,11 @@ __device__ __forceinline__ void tmem_add32(uint32_t taddr2, uint32_t* r) {
   for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(t[i]));
 }
 
+// TMEM is allocated in powers of two (32..512 columns).
+__host__ __device__ constexpr int tmem_alloc_cols(int need) {
+  return need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512;
+}
+
 constexpr int kEpiCols = 64;                       // columns per epilogue chunk (128 bytes of bf16)
 constexpr int kEpiBufBytes = 32 * kEpiCols * 2;    // one warp's chunk: 32 rows x 64 cols
 constexpr int kEpiBytes = 4 * 2 * kEpiBufBytes;    // 4 warps x 2 buffers
@@ -449,7 +454,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   // phase of the barrier (with an even ring, stage parity = parity of the global step count).
   constexpr int NACC = DUAL ? 2 : 1;
   static_assert(!DUAL || STAGES % 2 == 0, "stage ownership by parity needs an even ring");
-  static_assert(2 * NACC * BN <= 512, "TMEM has 512 columns");
+  static_assert(2 * NACC * BN <= 512 && BN % 64 == 0, "TMEM has 512 columns; the epilogue works in 64-column chunks");
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles need 1024-byte aligned bases
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -487,7 +492,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   }
   if (warp == 1) {  // TMEM allocation is a warp-wide operation
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
-                 "r"(2 * NACC * BN));
+                 "r"(tmem_alloc_cols(2 * NACC * BN)));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   tc_fence_before();
@@ -654,7 +659,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
   if (threadIdx.x == 0 && *abort_flag && err_word != nullptr) atomicExch(err_word, 1);
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * NACC * BN));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_alloc_cols(2 * NACC * BN)));
   }
 }
 
@@ -764,7 +769,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
                               const bf16* __restrict__ bias, int M, int N, int K, int w_packed, const GemmMode mode, int* __restrict__ err_word) {
   using S = GemmSmem2<BN, STAGES, KS>;
   constexpr int NACC = DUAL ? 2 : 1;  // accumulators per tile: one per MMA-issuing warp of the leader
-  static_assert(2 * NACC * BN <= 512, "TMEM has 512 columns");
+  static_assert(2 * NACC * BN <= 512 && BN % 64 == 0, "TMEM has 512 columns; the epilogue works in 64-column chunks");
   static_assert(!DUAL || STAGES % 2 == 0, "stage ownership by parity needs an even ring");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -804,7 +809,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
-                 "r"(2 * NACC * BN));
+                 "r"(tmem_alloc_cols(2 * NACC * BN)));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
   }
   tc_fence_before();
@@ -949,7 +954,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
   cluster_sync_all();  // neither CTA leaves while the other may still touch its barriers / smem
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * NACC * BN));
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_alloc_cols(2 * NACC * BN)));
   }
 }
 
@@ -1134,7 +1139,7 @@ static int launch_gemm_pair(const void* a, const void* w, void* c, const void* b
 
 // C[M,N] = A[M,K] · W[N,K]^T (+ bias).  bf16 row-major, leading dimensions in elements.
 // Requirements: K % 8 == 0, N % 8 == 0, lda/ldw/ldc % 8 == 0, 16-byte aligned base pointers.
-// tile_n: 0 = choose from the problem shape; else one of 64, 128, 256.
+// tile_n: 0 = choose from the problem shape; else one of 64, 128, 192, 256.
 // pair: -1 = choose; 0 = one CTA per 128 x tile_n tile; 1 = a CTA pair (cta_group::2) per 256 x tile_n tile.
 // w_packed: W is stored tile-packed as [N/64][K/64][64][64] (see xllm_pack_weight_bf16); needs
 // N % 64 == 0 and K % 64 == 0.  Each 64 x 64 block is then one contiguous 8 KB run, which is what
@@ -1169,7 +1174,21 @@ XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* b
     const int rows = p ? 2 * kBM : kBM, slots = p ? sms / 2 : sms;
     const int m_t = (M + rows - 1) / rows;
     int tn = tile_n;
-    if (tn == 0) tn = m_t * ((N + 127) / 128) <= slots ? 128 : 256;
+    if (tn == 0) {
+      // one wave of 128-wide tiles if that fits; else the width (128 / 192 / 256) with the least
+      // waves x time per tile, the measured time of a K block growing as ~0.18 + 0.0008 * width us
+      if (m_t * ((N + 127) / 128) <= slots) {
+        tn = 128;
+      } else {
+        double best = 1e30;
+        for (int cand : {128, 192, 256}) {
+          if (cand == 192 && w_packed) continue;
+          const long tiles = (long)m_t * ((N + cand - 1) / cand);
+          const double cost = (double)((tiles + slots - 1) / slots) * (0.18 + 0.0008 * cand);
+          if (cost < best - 1e-9) { best = cost; tn = cand; }
+        }
+      }
+    }
     int sk = split_k;
     if (sk == 0) {
       const int tiles = m_t * ((N + tn - 1) / tn);
@@ -1210,9 +1229,11 @@ XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* b
   // narrow tiles take two K blocks per ring stage unless the weight is tile-packed (whose block
   // addressing has no zero-filled tail) or the caller asked for the one-block form
   const bool two = g_k_per_stage != 1 && !w_packed && K > kBK;
+  if (tile_n == 192 && w_packed) tile_n = 256;  // packed blocks are 64 rows: a 96-row half tile would straddle them
   if (pair) {
     switch (tile_n) {
       case 256: return launch_gemm_pair<256, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
+      case 192: return launch_gemm_pair<192, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
       case 128:
         if (two && g_dual) return launch_gemm_pair<128, 4, 2, true>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
         if (two) return launch_gemm_pair<128, 4, 2>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, split_k);
@@ -1234,6 +1255,7 @@ XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* b
   if (two && tile_n == 64)
     return launch_gemm<64, 4, 2>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1, plain, split_k);
   switch (tile_n) {
+    case 192: return launch_gemm<192, 4>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1, plain, split_k);
     case 256: return launch_gemm<256, 4>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1,
                                           GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0}, split_k);
     case 128: return launch_gemm<128, 6>(a, w, c, bias, M, N, K, lda, ldw, ldc, sms, w_packed, s, nullptr, 1,
