@@ -1197,6 +1197,9 @@ XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* b
       if (sk > 8) sk = 8;
       while (sk > 1 && K / sk < min_k) --sk;
       if (sk < 1 || (size_t)M * N * 4 > kSplitWsBytes) sk = 1;
+      // pairs, no split, and even 64-wide tiles fit in one wave: the narrower tile is quicker
+      // (256 x 4096 x 4096: 15.0 us against 16.4)
+      if (tile_n == 0 && p == 1 && sk == 1 && tn == 128 && !w_packed && m_t * ((N + 63) / 64) <= slots) tn = 64;
     }
     pair = p;
     tile_n = tn;
