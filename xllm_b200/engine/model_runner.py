@@ -195,7 +195,7 @@ class ModelRunner:
 
         def run():
             h = self.model.forward(tokens, positions, meta, self.kv_caches)
-            return self.model.logits(h)
+            return self.model.logits_local(h)   # this rank's vocabulary shard; gathered (or not) after the graph
 
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream())
@@ -272,18 +272,26 @@ class ModelRunner:
                 self.last_hidden, self.last_meta, self.last_positions = hidden, meta, positions
             rows = _view(buf, off[2], NS, torch.int64)
             h = hidden if (NS == T and npf == 0) else ops.gather_rows(hidden, rows)
-            logits = self.model.logits(h)
+            logits = self.model.logits_local(h)
             src = buf
 
         temperature = _view(src, off[8], NS, torch.float32)
         top_k = _view(src, off[7], NS, torch.int32)
         top_p = _view(src, off[9], NS, torch.float32)
+        want_lp = batch.any_logprobs
+        sharded = self.model.ps.tp_size > 1
+        greedy_sharded = (sharded and batch.all_greedy and not want_lp and not batch.any_penalty
+                          and self.logits_hook is None)
+        if sharded and not greedy_sharded:
+            logits = self.model.gather_logits(logits)
         if batch.any_penalty:
             self._apply_penalties(batch, logits)
         if self.logits_hook is not None:
             self.logits_hook(batch, logits)   # e.g. grammar masks of constrained requests
-        want_lp = batch.any_logprobs
-        if batch.all_greedy and not want_lp:
+        if greedy_sharded:
+            # vocabulary-sharded argmax: only (value, index) pairs cross the link
+            ids, lp = self.model.greedy_from_local(logits), None
+        elif batch.all_greedy and not want_lp:
             ids, lp = ops.sample(logits, None, None, None)
         else:
             ids, lp = ops.sample(logits, temperature, top_k, top_p, seed=int(batch.seeds[0]) if n_real else 0,

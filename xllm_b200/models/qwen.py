@@ -116,6 +116,16 @@ class DenseCausalLM(Module):
     def logits(self, hidden_rows):
         return self.lm_head(hidden_rows)
 
+    # the two halves of `logits`, for callers that can avoid the all-gather (greedy sampling)
+    def logits_local(self, hidden_rows):
+        return self.lm_head.forward_local(hidden_rows)
+
+    def gather_logits(self, local):
+        return self.lm_head.gather(local)
+
+    def greedy_from_local(self, local):
+        return self.lm_head.greedy_from_local(local)
+
     __call__ = forward
 
 
