@@ -37,9 +37,14 @@ def main():
 
     from xllm_b200 import LLM
 
-    dev = torch.device("cuda", 0)
+    ps = None
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:        # under torchrun: a tensor-parallel engine, rank 0 reports
+        from xllm_b200.parallel.state import init_parallel
+        ps = init_parallel()
+    dev = ps.device if ps else torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    llm = LLM(args.model, devices=str(dev), dtype="bfloat16", block_size=16,
+    quiet = ps is not None and ps.rank != 0
+    llm = LLM(args.model, devices=str(dev), dtype="bfloat16", block_size=16, parallel_state=ps,
               max_seqs_per_batch=args.concurrency, max_tokens_per_batch=args.max_tokens_per_batch,
               max_model_len=args.input_len + args.output_len + 16, enable_prefix_cache=False,
               enable_chunked_prefill=True, enable_schedule_overlap=True, enable_graph=True,
@@ -77,8 +82,9 @@ def main():
         step()
     e1.record()
     torch.cuda.synchronize()
-    print(f"unprofiled: {args.steps} steps, {e0.elapsed_time(e1) / args.steps:.2f} ms/step on the device clock, "
-          f"{(time.perf_counter() - t0) * 1e3 / args.steps:.2f} ms/step wall")
+    if not quiet:
+        print(f"unprofiled: {args.steps} steps, {e0.elapsed_time(e1) / args.steps:.2f} ms/step on the device clock, "
+              f"{(time.perf_counter() - t0) * 1e3 / args.steps:.2f} ms/step wall")
     kinds = collections.Counter()
     t0 = time.perf_counter()
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
@@ -98,6 +104,9 @@ def main():
             per[ev.name][0] += dt
             per[ev.name][1] += 1
             total += dt
+    if quiet:
+        torch.cuda.synchronize()
+        os._exit(0)
     print(f"window: {args.steps} steps, wall {wall * 1e3 / args.steps:.2f} ms/step, "
           f"device busy {total / 1e3 / args.steps:.2f} ms/step")
     if kinds:
@@ -109,3 +118,6 @@ def main():
 
 if __name__ == "__main__":
     main()
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        sys.stdout.flush()
+        os._exit(0)
