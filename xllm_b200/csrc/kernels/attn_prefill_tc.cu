@@ -1,6 +1,6 @@
 // Varlen causal prefill attention over the paged KV cache on the 5th-generation tensor cores.
 //
-// One CTA = (sequence, query head, tile of 128 query tokens), head_dim 128, 192 threads:
+// One CTA = (sequence, query head, tile of 128 query tokens), head_dim 128, 320 threads:
 //   warp 0      TMA producer: the Q tile once, then K and V tiles of 128 tokens into a two-stage
 //               shared-memory ring; a tile is gathered page by page through the block table (one
 //               [page x 64]-element box per page and half of the head dimension)
@@ -9,11 +9,10 @@
 //               with V as an MN-major operand (the cache keeps head_dim contiguous), into one of two
 //               O accumulators.  QK of tile j+1 is issued before PV of tile j, so the tensor pipe
 //               works while the softmax of tile j runs.
-//   warps 2-5   softmax: one thread per query row (tcgen05.ld gives a thread its own row, so row
-//               max and row sum need no shuffles); S is read twice (max, then exp) to keep the
-//               register budget for the 128 fp32 output values a thread carries; P goes to shared
-//               memory as bf16 in the 128-byte swizzled K-major layout; the finished O tile of the
-//               previous step is added with the usual rescaling O = (O + O_tile) * alpha.
+//   warps 2-9   softmax: two threads per query row, 64 columns each (tcgen05.ld gives a thread its
+//               own row; the two halves exchange their row maximum through shared memory); P goes to
+//               shared memory as bf16 in the 128-byte swizzled K-major layout; the finished O tile
+//               of the previous step is added with the usual rescaling O = (O + O_tile) * alpha.
 // The reference reaches the same op through FlashInfer's fa2 kernels
 // (xllm/core/kernels/cuda/flashinfer_attention.cpp:239-301); the mma.sync kernel of attn_prefill.cu
 // stays as the path for other head sizes, sliding windows and small pages.
@@ -37,7 +36,8 @@ constexpr int Q_OFF = 0;
 constexpr int KV_OFF = kTile;                       // 2 stages x (K, V)
 constexpr int P_OFF = KV_OFF + 4 * kTile;
 constexpr int BAR_OFF = P_OFF + kTile;
-constexpr int SMEM_TOTAL = BAR_OFF + 16 * 8 + 16 + 1024;
+constexpr int XCH_OFF = BAR_OFF + 24 * 8 + 16;          // row-max / row-sum exchange between the two halves of a row
+constexpr int SMEM_TOTAL = XCH_OFF + (2 * 2 + 2) * kBM * 4 + 1024;
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -120,6 +120,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
       : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 struct Params {
   bf16* out;
@@ -132,7 +144,7 @@ struct Params {
   int* err;
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                   const __grid_constant__ CUtensorMap tma_v, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -140,15 +152,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_consta
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = sbase + BAR_OFF;
   // barrier slots
+  // K and V have rings of their own: a K slot is free again as soon as the QK product that read it
+  // has completed, a V slot after its PV product, so the load of K_{j+2} starts a whole tile earlier
+  // than with a joint slot and the loads stay off the critical path.
   const uint32_t q_full = bar0;
-  auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
-  auto kv_empty = [&](int s) { return bar0 + 8u * (3 + s); };
-  auto s_full = [&](int b) { return bar0 + 8u * (5 + b); };
-  auto s_free = [&](int b) { return bar0 + 8u * (7 + b); };
-  const uint32_t p_full = bar0 + 8u * 9, p_free = bar0 + 8u * 10;
-  auto o_full = [&](int b) { return bar0 + 8u * (11 + b); };
-  auto o_free = [&](int b) { return bar0 + 8u * (13 + b); };
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + BAR_OFF + 16 * 8);
+  auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bar0 + 8u * (3 + s); };
+  auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
+  auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
+  auto s_full = [&](int b) { return bar0 + 8u * (9 + b); };
+  auto s_free = [&](int b) { return bar0 + 8u * (11 + b); };
+  const uint32_t p_full = bar0 + 8u * 13, p_free = bar0 + 8u * 14;
+  const uint32_t o_full = bar0 + 8u * 15;             // the last PV product has completed
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + BAR_OFF + 24 * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -165,15 +181,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(o_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(kv_full(s), 1);
-      mbar_init(kv_empty(s), 1);
+      mbar_init(k_full(s), 1);
+      mbar_init(k_empty(s), 1);
+      mbar_init(v_full(s), 1);
+      mbar_init(v_empty(s), 1);
       mbar_init(s_full(s), 1);
-      mbar_init(s_free(s), 4);
-      mbar_init(o_full(s), 1);
-      mbar_init(o_free(s), 4);
+      mbar_init(s_free(s), 8);
     }
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     mbar_init(p_free, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -186,7 +203,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_holder;
-  const uint32_t TS0 = tmem, TO0 = tmem + 256;        // S[b] = TS0 + 128 b, O[b] = TO0 + 128 b
+  const uint32_t TS0 = tmem, TO0 = tmem + 256;        // S[b] = TS0 + 128 b; O accumulates at TO0 over all tiles
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -201,20 +218,25 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_consta
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j & 1;
-      if (!mbar_wait_warp(kv_empty(st), ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
       const int pg = j * pages + lane;
       const int myblk = (lane < pages && pg < n_blk) ? bt[pg] : 0;   // pages past the sequence read block 0 (masked)
-      if (lane == 0) mbar_expect_tx(kv_full(st), 2 * kTile);
-      __syncwarp();
+      const int y = (myblk * p.nkv + hk) * p.page;
+      const uint32_t off = (uint32_t)(lane * p.page * 128);
       const uint32_t kdst = sbase + KV_OFF + st * 2 * kTile, vdst = kdst + kTile;
+      // every lane gathers its own page: the copies of all pages issue together
+      if (!mbar_wait_warp(k_empty(st), ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+      if (lane == 0) mbar_expect_tx(k_full(st), kTile);
+      __syncwarp();
       if (lane < pages) {
-        // every lane gathers its own page: the four copies of all pages issue together
-        const int y = (myblk * p.nkv + hk) * p.page;
-        const uint32_t off = (uint32_t)(lane * p.page * 128);
-        tma_load_2d(kdst + off, &tma_k, 0, y, kv_full(st));
-        tma_load_2d(kdst + kHalf + off, &tma_k, 64, y, kv_full(st));
-        tma_load_2d(vdst + off, &tma_v, 0, y, kv_full(st));
-        tma_load_2d(vdst + kHalf + off, &tma_v, 64, y, kv_full(st));
+        tma_load_2d(kdst + off, &tma_k, 0, y, k_full(st));
+        tma_load_2d(kdst + kHalf + off, &tma_k, 64, y, k_full(st));
+      }
+      if (!mbar_wait_warp(v_empty(st), ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+      if (lane == 0) mbar_expect_tx(v_full(st), kTile);
+      __syncwarp();
+      if (lane < pages) {
+        tma_load_2d(vdst + off, &tma_v, 0, y, v_full(st));
+        tma_load_2d(vdst + kHalf + off, &tma_v, 64, y, v_full(st));
       }
       __syncwarp();
     }
@@ -236,168 +258,172 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_consta
           umma(TS0 + (j & 1) * 128, smem_desc(sbase + Q_OFF + o, 16, 1024), smem_desc(kaddr + o, 16, 1024), ID_QK, ks != 0);
         }
         umma_commit(s_full(j & 1));
+        umma_commit(k_empty(j & 1));   // the K slot may be refilled once these MMAs have read it
       }
       __syncwarp();
     };
     if (ok && n_tiles > 0) {
-      ok = mbar_wait_warp(kv_full(0), 0, abort_flag);
+      ok = mbar_wait_warp(k_full(0), 0, abort_flag);
       tc_fence_after();
       if (ok) issue_qk(0);
     }
     for (int j = 0; j < n_tiles && ok; ++j) {
       if (j + 1 < n_tiles) {
         const int nb = (j + 1) & 1, use = (j + 1) >> 1;
-        if (!mbar_wait_warp(kv_full(nb), use & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(k_full(nb), use & 1, abort_flag)) { ok = false; break; }
         if (!mbar_wait_warp(s_free(nb), (use & 1) ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         issue_qk(j + 1);
       }
-      const int ob = j & 1, use = j >> 1;
-      if (!mbar_wait_warp(p_full, j & 1, abort_flag)) { ok = false; break; }
-      if (!mbar_wait_warp(o_free(ob), (use & 1) ^ 1, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(v_full(j & 1), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(p_full, j & 1, abort_flag)) { ok = false; break; }   // also: O has been rescaled if need be
       tc_fence_after();
       if (lane == 0) {
-        // O_tile[ob] = P V_j : 8 steps of 16 kv tokens; V is MN-major (rows = tokens, 128-byte rows of
+        // O += P V_j : 8 steps of 16 kv tokens; V is MN-major (rows = tokens, 128-byte rows of
         // 64 head_dim elements, second half of head_dim one half-tile further)
         const uint32_t vaddr = sbase + KV_OFF + (j & 1) * 2 * kTile + kTile;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint32_t pa = sbase + P_OFF + (ks >> 2) * kHalf + (ks & 3) * 32;
-          umma(TO0 + ob * 128, smem_desc(pa, 16, 1024), smem_desc(vaddr + ks * 16 * 128, kHalf, 1024), ID_PV, ks != 0);
+          umma(TO0, smem_desc(pa, 16, 1024), smem_desc(vaddr + ks * 16 * 128, kHalf, 1024), ID_PV, (j | ks) != 0);
         }
-        umma_commit(o_full(ob));
         umma_commit(p_free);
-        umma_commit(kv_empty(j & 1));
+        if (j == n_tiles - 1) umma_commit(o_full);
+        umma_commit(v_empty(j & 1));
       }
       __syncwarp();
     }
   } else {
-    // ------------------------------------------------------------------ softmax / output (warps 2..5)
+    // ------------------------------------------------------------------ softmax / output (warps 2..9)
+    // Two threads per query row: warps 2-5 take kv columns / head_dim columns 0..63 of the row, warps
+    // 6-9 take 64..127 (two warps per scheduler hide each other's TMEM round trips, and 64 instead of
+    // 128 output values per thread leave room to keep the S row in registers: S is read once).
     const int quarter = warp & 3;                     // TMEM lanes this warp may read
-    const int row = quarter * 32 + lane;              // query row of this thread inside the tile
+    const int half = (warp - 2) >> 2;                 // which 64 columns
+    const int row = quarter * 32 + lane;              // query row inside the tile
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const int q_pos = ctx_off + m0 + row;             // absolute position of this query token
     const int limit = p.causal ? min(kv_len - 1, q_pos) : kv_len - 1;   // last kv index this row may see
+    float* smax = reinterpret_cast<float*>(smem + XCH_OFF);             // [2 tile parities][2 halves][128 rows]
+    float* lsum = smax + 2 * 2 * kBM;                                   // [2 halves][128 rows]
+    // O stays in TMEM and the MMAs accumulate into it over all kv tiles.  The exponent uses a row
+    // maximum m that lags the true one: it moves (and O and l are rescaled) only when the true
+    // maximum has grown by more than 2^kLag, so after the first tiles the rescale is rare and the
+    // common tile costs no pass over O at all.  P stays below 2^kLag, well inside bf16 and fp32 range.
+    constexpr float kLag = 8.f;
     float m = -INFINITY, l = 0.f;
-    float o[kD];
-#pragma unroll
-    for (int i = 0; i < kD; ++i) o[i] = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
+    const uint32_t oaddr = TO0 + half * 64 + lane_addr;
+    // Every thread runs every iteration and every named barrier even after a wait has given up (the
+    // waits then fail at once): a thread that left early would strand its partners in bar.sync.
+    for (int j = 0; j < n_tiles; ++j) {
       const int sb = j & 1;
-      if (!mbar_wait(s_full(sb), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      ok = ok && mbar_wait(s_full(sb), (j >> 1) & 1, abort_flag);
       tc_fence_after();
-      const uint32_t saddr = TS0 + sb * 128 + lane_addr;
-      const int kv0 = j * kBN;
-      const bool full_tile = kv0 + kBN - 1 <= limit;
-      // pass 1: row maximum
+      const uint32_t saddr = TS0 + sb * 128 + half * 64 + lane_addr;
+      const int kv0 = j * kBN + half * 64;
+      const bool full_tile = kv0 + 63 <= limit;
+      uint32_t sv[64];
+      tmem_ld32(saddr, sv);
+      tmem_ld32(saddr + 32, sv + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free(sb));         // S has been read out: the next QK may overwrite it
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(saddr + c * 32, r);
-        tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float v = __uint_as_float(r[i]);
-          if (full_tile || kv0 + c * 32 + i <= limit) mx = fmaxf(mx, v);
-        }
+      for (int i = 0; i < 64; ++i)
+        if (full_tile || kv0 + i <= limit) mx = fmaxf(mx, __uint_as_float(sv[i]));
+      smax[(sb * 2 + half) * kBM + row] = mx;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      mx = fmaxf(mx, smax[(sb * 2 + (half ^ 1)) * kBM + row]);
+      const float m_true = fmaxf(m, mx * p.scale_log2);
+      float factor = 1.f;
+      if (m_true - m > kLag) {                        // also the first tile that shows this row a key (m = -inf)
+        factor = exp2f(m - m_true);                   // 0 when m was -inf: nothing accumulated yet
+        m = m_true;
       }
-      const float m_new = fmaxf(m, mx * p.scale_log2);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = exp2f(m - m_use);
-      // P may be overwritten once the PV product of the previous tile has read it
-      if (!mbar_wait(p_free, (j & 1) ^ 1, abort_flag)) { ok = false; break; }
-      // pass 2: probabilities -> bf16 -> swizzled shared memory, row sum
-      float rs = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(saddr + c * 32, r);
-        tmem_ld_wait();
-        uint32_t packed[16];
+      const float m_use = m == -INFINITY ? 0.f : m;
+      // P may be overwritten, and O touched, once the PV product of the previous tile has completed
+      ok = ok && mbar_wait(p_free, (j & 1) ^ 1, abort_flag);
+      if (j > 0 && __any_sync(0xffffffffu, factor != 1.f)) {
+        tc_fence_after();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(r[i]) * p.scale_log2 - m_use);
-          float p1 = exp2f(__uint_as_float(r[i + 1]) * p.scale_log2 - m_use);
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld32(oaddr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+          tmem_st32(oaddr + c * 32, r);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+      }
+      float rs = 0.f;
+      const uint32_t pbase = sbase + P_OFF + half * kHalf + row * 128;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          const int i = u * 8 + e;
+          float p0 = exp2f(__uint_as_float(sv[i]) * p.scale_log2 - m_use);
+          float p1 = exp2f(__uint_as_float(sv[i + 1]) * p.scale_log2 - m_use);
           if (!full_tile) {
-            if (kv0 + c * 32 + i > limit) p0 = 0.f;
-            if (kv0 + c * 32 + i + 1 > limit) p1 = 0.f;
+            if (kv0 + i > limit) p0 = 0.f;
+            if (kv0 + i + 1 > limit) p1 = 0.f;
           }
           rs += p0 + p1;
           const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-          packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
+          packed[e >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
         }
-        // 32 kv tokens = 64 bytes = 4 units of 16 bytes in half (c >> 1), units (c & 1) * 4 ..
-        const uint32_t base = sbase + P_OFF + (c >> 1) * kHalf + row * 128;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const uint32_t dst = base + ((((c & 1) * 4 + u) ^ (row & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * u]), "r"(packed[4 * u + 1]),
-                       "r"(packed[4 * u + 2]), "r"(packed[4 * u + 3])
-                       : "memory");
-        }
+        const uint32_t dst = pbase + ((u ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[0]), "r"(packed[1]), "r"(packed[2]),
+                     "r"(packed[3])
+                     : "memory");
       }
-      tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(s_free(sb));
-        mbar_arrive(p_full);
-      }
-      l = l * alpha + rs;
-      m = m_new;
-      // fold in the O tile of the previous step: O = (O + O_tile) * alpha
-      if (j > 0) {
-        const int ob = (j - 1) & 1;
-        if (!mbar_wait(o_full(ob), ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t oaddr = TO0 + ob * 128 + lane_addr;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld32(oaddr + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(r[i])) * alpha;
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(o_free(ob));
-      }
+      if (lane == 0) mbar_arrive(p_full);
+      l = l * factor + rs;
     }
-    if (ok && n_tiles > 0) {
-      const int ob = (n_tiles - 1) & 1;
-      ok = mbar_wait(o_full(ob), ((n_tiles - 1) >> 1) & 1, abort_flag);
+    float o[64];
+    if (n_tiles > 0) {
+      ok = ok && mbar_wait(o_full, 0, abort_flag);
       tc_fence_after();
-      if (ok) {
-        const uint32_t oaddr = TO0 + ob * 128 + lane_addr;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld32(oaddr + c * 32, r);
-          tmem_ld_wait();
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tmem_ld32(oaddr + c * 32, r);
+        tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(r[i]);
-        }
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = __uint_as_float(r[i]);
       }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 64; ++i) o[i] = 0.f;
     }
-    // ---- output: normalise, stage the tile in shared memory (the Q buffer is free now), store rows
+    // ---- output: the two halves of a row add their sums, normalise, stage the tile in shared memory
+    // (the Q buffer is free now), store rows
+    lsum[half * kBM + row] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l += lsum[(half ^ 1) * kBM + row];
     const float inv = l > 0.f ? 1.f / l : 0.f;
     uint8_t* stage = smem + Q_OFF;                    // [128 rows][256 bytes], 16-byte units XOR-swizzled by row
 #pragma unroll
-    for (int u = 0; u < 16; ++u) {
+    for (int u = 0; u < 8; ++u) {
       float f[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[e] = o[u * 8 + e] * inv;
       const bf16x8 v = pack8(f);
-      *reinterpret_cast<uint4*>(stage + row * 256 + ((u ^ (row & 15)) << 4)) = *reinterpret_cast<const uint4*>(&v);
+      *reinterpret_cast<uint4*>(stage + row * 256 + (((half * 8 + u) ^ (row & 15)) << 4)) = *reinterpret_cast<const uint4*>(&v);
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync 1, 256;" ::: "memory");
     if (ok) {
-      const int t = threadIdx.x - 64;                 // 0..127
+      const int t = threadIdx.x - 64;                 // 0..255
       const int u = t & 15;
-      for (int r0 = t >> 4; r0 < kBM; r0 += 8) {      // 8 rows per pass, 16 threads x 16 bytes per row
+      for (int r0 = t >> 4; r0 < kBM; r0 += 16) {     // 16 rows per pass, 16 threads x 16 bytes per row
         if (m0 + r0 < q_len) {
           const uint4 v = *reinterpret_cast<const uint4*>(stage + r0 * 256 + ((u ^ (r0 & 15)) << 4));
           *reinterpret_cast<uint4*>(p.out + (int64_t)(q_begin + m0 + r0) * p.o_stride + h * kD + u * 8) = v;
@@ -481,7 +507,7 @@ XLLM_API int xllm_paged_prefill_attn_tc(void* out, int64_t o_stride, const void*
   p.kv_lens = (const int32_t*)kv_lens; p.o_stride = o_stride; p.bt_stride = bt_stride; p.nq = nq; p.nkv = nkv;
   p.page = page_size; p.causal = causal; p.scale_log2 = scale * 1.4426950408889634f; p.err = g_err[dev & 63];
   dim3 grid((max_q_len + kBM - 1) / kBM, nq, batch);
-  prefill_tc_kernel<<<grid, 192, SMEM_TOTAL, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  prefill_tc_kernel<<<grid, 320, SMEM_TOTAL, (cudaStream_t)stream>>>(tq, tk, tv, p);
   return XLLM_LAUNCH_CHECK();
 }
 
