@@ -1,0 +1,81 @@
+"""Every decoder family against its HuggingFace implementation: a tiny random model is built with
+`transformers`, saved as a checkpoint directory (config.json + safetensors), loaded by this
+framework's config parser and safetensors reader, and run through the engine on CPU in fp32.  Greedy
+continuations must be identical and the logits of a whole sequence must agree to 1e-4.  This pins
+the config mapping, the checkpoint name mapping and the layer arithmetic of each family."""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from xllm_b200 import LLM, SamplingParams  # noqa: E402
+from xllm_b200.api.embedding import hidden_states  # noqa: E402
+
+COMMON = dict(vocab_size=512, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              intermediate_size=128, max_position_embeddings=512, rms_norm_eps=1e-6, tie_word_embeddings=False)
+
+
+def _case(fam):
+    t = transformers
+    if fam == "llama":
+        return t.LlamaConfig(**COMMON, head_dim=16), t.LlamaForCausalLM
+    if fam == "mistral":
+        return t.MistralConfig(**COMMON, head_dim=16, sliding_window=None), t.MistralForCausalLM
+    if fam == "qwen2":
+        return t.Qwen2Config(**COMMON), t.Qwen2ForCausalLM
+    if fam == "qwen3":
+        return t.Qwen3Config(**COMMON, head_dim=32), t.Qwen3ForCausalLM
+    if fam == "qwen3_moe":
+        return t.Qwen3MoeConfig(**COMMON, head_dim=16, moe_intermediate_size=32, num_experts=8, num_experts_per_tok=2,
+                                norm_topk_prob=True), t.Qwen3MoeForCausalLM
+    if fam == "deepseek_v3":
+        return t.DeepseekV3Config(**COMMON, moe_intermediate_size=32, n_routed_experts=8, num_experts_per_tok=2,
+                                  n_shared_experts=1, first_k_dense_replace=1, n_group=2, topk_group=1, q_lora_rank=32,
+                                  kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                                  routed_scaling_factor=2.5), t.DeepseekV3ForCausalLM
+    if fam == "glm4":
+        return t.Glm4Config(**COMMON, head_dim=16, partial_rotary_factor=0.5, pad_token_id=0), t.Glm4ForCausalLM
+    if fam == "glm4_moe":
+        return t.Glm4MoeConfig(**COMMON, head_dim=16, partial_rotary_factor=0.5, moe_intermediate_size=32,
+                               n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=1, first_k_dense_replace=1,
+                               n_group=1, topk_group=1, use_qk_norm=True, routed_scaling_factor=1.5), t.Glm4MoeForCausalLM
+    if fam == "minimax_m2":
+        return t.MiniMaxM2Config(**COMMON, head_dim=16, num_local_experts=8, num_experts_per_tok=2,
+                                 rope_parameters={"rope_theta": 10000.0, "rope_type": "default",
+                                                  "partial_rotary_factor": 0.5}), t.MiniMaxM2ForCausalLM
+    raise KeyError(fam)
+
+
+FAMILIES = ["llama", "mistral", "qwen2", "qwen3", "qwen3_moe", "deepseek_v3", "glm4", "glm4_moe", "minimax_m2"]
+
+
+@pytest.mark.parametrize("fam", FAMILIES)
+def test_family_matches_huggingface(fam, tmp_path):
+    try:
+        cfg, cls = _case(fam)
+    except (AttributeError, TypeError) as e:      # this transformers build lacks the family
+        pytest.skip(str(e))
+    torch.manual_seed(0)
+    hf = cls(cfg).float().eval()
+    with torch.no_grad():                         # norms away from 1 and biases away from 0, so that both matter
+        for n, p in hf.named_parameters():
+            if "norm" in n:
+                p.copy_(1 + 0.1 * torch.randn_like(p))
+            elif n.endswith("bias"):
+                p.copy_(0.1 * torch.randn_like(p))
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (9, 21, 33)]
+    llm = LLM(str(tmp_path), devices="cpu", dtype="float32", block_size=16, num_blocks=64, max_seqs_per_batch=8,
+              max_tokens_per_batch=256, enable_graph=False)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=10, temperature=0.0, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        with torch.no_grad():
+            ref = hf.generate(torch.tensor([p]), max_new_tokens=10, do_sample=False, eos_token_id=None,
+                              pad_token_id=0)[0, len(p):].tolist()
+        assert o.outputs[0].token_ids == ref
+    seq = prompts[2] + outs[2].outputs[0].token_ids
+    ours = llm.engine.model.logits(hidden_states(llm.engine, seq)).float()
+    with torch.no_grad():
+        ref = hf(torch.tensor([seq])).logits[0]
+    assert float((ours - ref).abs().max()) < 1e-4

@@ -119,6 +119,14 @@ def model_args_from_dict(cfg: Dict[str, Any]) -> ModelArgs:
     if isinstance(a.rope_scaling, dict) and "rope_theta" in a.rope_scaling:
         a.rope_theta = float(a.rope_scaling["rope_theta"])
     a.partial_rotary_factor = float(_g(text, "partial_rotary_factor", default=1.0))
+    rp = _g(text, "rope_parameters")       # newer configs keep theta, the partial factor and the scaling here
+    if isinstance(rp, dict):
+        a.rope_theta = float(rp.get("rope_theta", a.rope_theta))
+        a.partial_rotary_factor = float(rp.get("partial_rotary_factor", a.partial_rotary_factor))
+        if rp.get("rope_type", "default") not in ("default", None) and a.rope_scaling is None:
+            a.rope_scaling = dict(rp)
+    if _g(text, "rotary_dim") and a.partial_rotary_factor == 1.0:
+        a.partial_rotary_factor = float(text["rotary_dim"]) / a.head_dim
     a.max_position_embeddings = _g(text, "max_position_embeddings", default=32768)
     a.tie_word_embeddings = bool(_g(cfg, "tie_word_embeddings", default=_g(text, "tie_word_embeddings", default=False)))
     a.sliding_window = int(_g(text, "sliding_window", default=0) or 0) if _g(text, "use_sliding_window", default=False) else 0
@@ -126,8 +134,9 @@ def model_args_from_dict(cfg: Dict[str, Any]) -> ModelArgs:
     a.eos_token_id, a.stop_token_ids = _eos_list(_g(text, "eos_token_id", default=_g(cfg, "eos_token_id")))
     a.dtype = _g(text, "torch_dtype", "dtype", default=_g(cfg, "torch_dtype", "dtype", default="bfloat16"))
     base = mt.lower()
-    a.qk_norm = base.startswith("qwen3") or base in ("mimo_v2",)
-    a.attention_bias = bool(_g(text, "attention_bias", default=base.startswith("qwen2")))
+    a.qk_norm = bool(_g(text, "use_qk_norm", default=base.startswith("qwen3") or base in ("mimo_v2", "minimax_m2")))
+    a.attention_bias = bool(_g(text, "attention_bias", default=base.startswith("qwen2") or base == "mimo"))
+    a.rope_interleaved = base in ("glm4", "glm")    # GLM dense rotates adjacent pairs
     # MoE
     a.num_experts = _g(text, "num_experts", "n_routed_experts", "num_local_experts", default=0)
     a.num_experts_per_tok = _g(text, "num_experts_per_tok", default=0)
@@ -138,11 +147,14 @@ def model_args_from_dict(cfg: Dict[str, Any]) -> ModelArgs:
     a.first_k_dense_replace = _g(text, "first_k_dense_replace", default=0)
     a.moe_layer_freq = _g(text, "moe_layer_freq", "decoder_sparse_step", default=1)
     a.mlp_only_layers = list(_g(text, "mlp_only_layers", default=[]))
-    a.scoring_func = _g(text, "scoring_func", default="softmax")
+    _v3_like = base in ("deepseek_v3", "deepseek_v32", "glm4_moe", "minimax_m2", "kimi_k2")
+    a.scoring_func = _g(text, "scoring_func", default="sigmoid" if _v3_like else "softmax")
     a.n_group = _g(text, "n_group", default=1) or 1
     a.topk_group = _g(text, "topk_group", default=1) or 1
     a.routed_scaling_factor = float(_g(text, "routed_scaling_factor", default=1.0))
-    a.router_bias = _g(text, "topk_method", default="") == "noaux_tc"
+    # DeepSeek-V3 and its descendants always carry `e_score_correction_bias` (and rank expert groups
+    # by the sum of their two best biased scores); older configs say so with topk_method
+    a.router_bias = _g(text, "topk_method", default="") == "noaux_tc" or _v3_like
     # MLA
     a.q_lora_rank = _g(text, "q_lora_rank", default=0) or 0
     a.kv_lora_rank = _g(text, "kv_lora_rank", default=0) or 0

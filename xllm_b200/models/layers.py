@@ -83,12 +83,16 @@ class Module:
     def load_weights(self, weights: Iterable[Tuple[str, torch.Tensor]], strict=True):
         loaders = dict(self.named_loaders())
         seen = set()
-        for name, w in weights:
-            f = loaders.get(name)
-            if f is None:
-                continue
-            f(w)
-            seen.add(name)
+        # a model whose checkpoints name or pack tensors differently (fused gate_up_proj, w1/w2/w3
+        # experts) defines `remap_weight(name, tensor) -> [(name, tensor), ...]`
+        remap = getattr(self, "remap_weight", None)
+        for name0, w0 in weights:
+            for name, w in (remap(name0, w0) if remap is not None else ((name0, w0),)):
+                f = loaders.get(name)
+                if f is None:
+                    continue
+                f(w)
+                seen.add(name)
         missing = [n for n in loaders if n not in seen]
         if strict and missing:
             raise KeyError(f"weights missing from checkpoint: {missing[:8]} (+{max(0, len(missing) - 8)} more)")
@@ -120,9 +124,10 @@ class Linear(Module):
     """y = x W^T (+ b). `parallel`: None (replicated), 'column' (shard dim 0), 'row' (shard dim 1)."""
 
     def __init__(self, in_f, out_f, bias, dtype, device, ps: ParallelState = None, parallel=None,
-                 reduce=True, gather_output=False):
+                 reduce=True, gather_output=False, fuse_reduce=True):
         super().__init__()
         self.ps = ps or single()
+        self.fuse_reduce = fuse_reduce      # False: a plain all-reduce, for layers that norm the sum by itself
         tp, rank = self.ps.tp_size, self.ps.tp_rank
         self.parallel = parallel if tp > 1 else None
         self.reduce = reduce
@@ -150,7 +155,7 @@ class Linear(Module):
         if self.parallel == "row" and self.ps.tp_rank != 0:
             bias = None  # added once, by rank 0, before the reduction
         if self.parallel == "row" and self.reduce:
-            comm = self.ps.comm
+            comm = self.ps.comm if self.fuse_reduce else None
             if comm is not None and x.is_cuda:
                 # the partial result goes to the symmetric buffer; the cross-rank sum is fused
                 # into the add+RMSNorm that follows (TpComm.allreduce_norm)
@@ -330,7 +335,8 @@ class Attention(Module):
     """GQA self-attention over the paged cache: fused QKV GEMM -> (qk-norm + RoPE + KV write) ->
     paged decode / prefill attention -> row-parallel o_proj."""
 
-    def __init__(self, args, layer_idx, dtype, device, ps: ParallelState = None, rope: RotaryEmbedding = None):
+    def __init__(self, args, layer_idx, dtype, device, ps: ParallelState = None, rope: RotaryEmbedding = None,
+                 fuse_reduce=True):
         super().__init__()
         self.ps = ps or single()
         tp = self.ps.tp_size
@@ -345,7 +351,7 @@ class Attention(Module):
             ["q_proj", "k_proj", "v_proj"], args.attention_bias, dtype, device, self.ps,
             shard_counts=[tp, kv_shards, kv_shards]))
         self.o_proj = self.add_module("o_proj", Linear(args.num_attention_heads * self.d, H, False, dtype, device,
-                                                       self.ps, parallel="row"))
+                                                       self.ps, parallel="row", fuse_reduce=fuse_reduce))
         self.q_norm = self.k_norm = None
         if args.qk_norm:
             self.q_norm = self.add_module("q_norm", RMSNorm(self.d, args.rms_norm_eps, dtype, device))
@@ -361,7 +367,9 @@ class Attention(Module):
             yield n.replace("qkv_proj.", ""), f
 
     def forward(self, x, positions, meta: AttentionMetadata, k_cache, v_cache):
-        qkv = self.qkv(x)
+        return self._attend(self.qkv(x), positions, meta, k_cache, v_cache)
+
+    def _attend(self, qkv, positions, meta: AttentionMetadata, k_cache, v_cache):
         cos_sin = self.rope.cos_sin
         if meta.rope_table is not None:
             cos_sin, positions = meta.rope_table, meta.rope_rows
@@ -390,14 +398,14 @@ class Attention(Module):
 class DenseMLP(Module):
     """SwiGLU MLP: fused gate|up column-parallel GEMM -> silu·mul -> row-parallel down GEMM."""
 
-    def __init__(self, hidden, inter, act, dtype, device, ps: ParallelState = None, reduce=True):
+    def __init__(self, hidden, inter, act, dtype, device, ps: ParallelState = None, reduce=True, fuse_reduce=True):
         super().__init__()
         self.ps = ps or single()
         self.act = act
         self.gate_up = self.add_module("gate_up_proj", MergedColumnLinear(
             hidden, [inter, inter], ["gate_proj", "up_proj"], False, dtype, device, self.ps))
         self.down = self.add_module("down_proj", Linear(inter, hidden, False, dtype, device, self.ps,
-                                                        parallel="row", reduce=reduce))
+                                                        parallel="row", reduce=reduce, fuse_reduce=fuse_reduce))
 
     def named_loaders(self, prefix=""):
         for n, f in super().named_loaders(prefix):

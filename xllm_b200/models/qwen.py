@@ -65,7 +65,10 @@ class DecoderLayer(Module):
 class DenseCausalLM(Module):
     """model.embed_tokens -> N x DecoderLayer -> model.norm -> lm_head."""
 
-    def __init__(self, args, dtype=torch.bfloat16, device="cpu", ps: ParallelState = None, make_mlp=None):
+    fused_tp = True      # False in families whose layers cannot use the fused all-reduce + norm
+
+    def __init__(self, args, dtype=torch.bfloat16, device="cpu", ps: ParallelState = None, make_mlp=None,
+                 layer_cls=None):
         super().__init__()
         self.args = args
         self.ps = ps or single()
@@ -81,7 +84,8 @@ class DenseCausalLM(Module):
         self.layers = []
         for i in range(args.num_hidden_layers):
             mlp = make_mlp(i) if make_mlp is not None else None
-            self.layers.append(layers.add_module(str(i), DecoderLayer(args, i, dtype, device, self.ps, self.rope, mlp)))
+            self.layers.append(layers.add_module(str(i), (layer_cls or DecoderLayer)(args, i, dtype, device, self.ps,
+                                                                                      self.rope, mlp)))
         self.norm = inner.add_module("norm", RMSNorm(args.hidden_size, args.rms_norm_eps, dtype, device))
         self.lm_head = LMHead(args.vocab_size, args.hidden_size, dtype, device, self.ps,
                               tied=self.embed if args.tie_word_embeddings else None)
@@ -108,7 +112,7 @@ class DenseCausalLM(Module):
         residual = None
         for layer, (kc, vc) in zip(self.layers, kv_caches):
             x, residual = layer(x, residual, positions, meta, kc, vc)
-        comm = self.ps.comm
+        comm = self.ps.comm if self.fused_tp else None
         if comm is not None and x.is_cuda:
             return comm.allreduce_norm(x.shape[0], residual, self.norm.weight, self.norm.eps)
         return self.norm(x, residual=residual)
