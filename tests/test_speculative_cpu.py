@@ -99,3 +99,52 @@ def test_mtp_drafter_on_deepseek_matches_plain_greedy():
     llm2.engine.spec.drafter = Oracle()
     got2 = [o.outputs[0].token_ids for o in llm2.generate(prompts, sp)]
     assert got2 == plain and llm2.engine.spec.acceptance_rate > 0.9
+
+
+def test_mtp_chained_drafts_match_plain_greedy():
+    """Three draft tokens per step from one MTP layer chained on its own output: the stream is the
+    plain greedy one, and every proposal is k tokens wide."""
+    from test_deepseek_cpu import _args
+    from xllm_b200.engine.llm_engine import EngineConfig, LLMEngine
+
+    def make(**kw):
+        llm = LLM.__new__(LLM)
+        llm.engine = LLMEngine(EngineConfig(model="d", device="cpu", dtype="float32", num_blocks=96, enable_graph=False,
+                                            max_tokens_per_batch=24, enable_schedule_overlap=False, **kw), model_args=_args())
+        llm.tokenizer = None
+        return llm
+
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 500, (n,), generator=g).tolist() for n in (15, 16, 33)]   # 16: a block boundary
+    sp = SamplingParams(max_tokens=12, temperature=0.0, ignore_eos=True)
+    plain = [o.outputs[0].token_ids for o in make().generate(prompts, sp)]
+    llm = make(num_speculative_tokens=3, speculative_method="mtp")
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert got == plain
+    d = llm.engine.spec.drafter
+    assert d.k == 3 and all(len(v) == 3 for v in d.draft.values())
+
+
+def test_eagle3_head_drafts_and_stream_is_unchanged():
+    """EAGLE-3 head on a tiny dense model: the target exposes three auxiliary hidden states, the head
+    drafts two tokens per step over its draft vocabulary (mapped through d2t), and the verified stream
+    equals plain greedy decoding."""
+    def make(**kw):
+        return LLM("tiny", devices="cpu", dtype="float32", block_size=16, num_blocks=96, max_seqs_per_batch=8,
+                   max_tokens_per_batch=64, enable_graph=False, enable_schedule_overlap=False, **kw)
+
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (7, 30, 70)]
+    sp = SamplingParams(max_tokens=10, temperature=0.0, ignore_eos=True)
+    plain = [o.outputs[0].token_ids for o in make().generate(prompts, sp)]
+    llm = make(num_speculative_tokens=2, speculative_method="eagle3")
+    eng = llm.engine
+    H = eng.args.hidden_size
+    eng.eagle3.d2t.copy_(torch.full_like(eng.eagle3.d2t, 3))       # draft id d stands for target id d + 3
+    eng.eagle3.d2t[-3:] = 0
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert got == plain
+    assert eng.model.last_aux.shape[-1] == 3 * H
+    assert eng.spec.steps > 0 and all(len(v) == 2 for v in eng.spec.drafter.draft.values())
+    ids = torch.tensor([0, 5, 100])
+    assert eng.eagle3.to_target_ids(ids).tolist() == [3, 8, 103]

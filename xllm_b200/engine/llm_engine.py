@@ -160,6 +160,14 @@ class LLMEngine:
                 from ..models.deepseek import MTPDraft
                 self.mtp = MTPDraft(self.args, self.model, self.dtype, self.device, self.ps)
                 self.mtp.init_random(seed=cfg.seed + 17)   # replaced by load_weights() for real checkpoints
+            elif cfg.speculative_method == "eagle3":
+                from ..models.eagle3 import Eagle3Draft, aux_layer_ids
+                self.model.aux_layers = aux_layer_ids(self.args.num_hidden_layers)
+                self.eagle3 = Eagle3Draft(self.args, self.model, self.dtype, self.device, self.ps)
+                self.eagle3.init_random(seed=cfg.seed + 19)
+                if cfg.draft_model and os.path.isdir(cfg.draft_model):
+                    from ..utils.loader import iterate_weights
+                    self.eagle3.load_weights(iterate_weights(cfg.draft_model), strict=False)
             self.spec = SpecDecoder(self, make_drafter(cfg.speculative_method, cfg.num_speculative_tokens, self),
                                     cfg.num_speculative_tokens)
         self.steps = 0

@@ -82,35 +82,71 @@ class MTPDrafter:
     target layer, addressed through the same block tables, and is run over exactly the rows the
     target has verified: every prompt chunk and unspeculated decode row (`after_execute`), and the
     accepted rows of a verification pass (`observe`).  The prediction made at the last verified
-    position of a sequence is its draft for the next step."""
+    position of a sequence is its draft for the next step.
+
+    More than one draft token per step (k > 1) chains the layer on itself: draft j + 1 comes from the
+    layer's own output at draft j and the embedding of draft j, one single-token pass per extra draft
+    over all sequences at once (the reference chains its MTP / EAGLE-3 draft passes the same way).
+    Draft KV written past a sequence's last allocated block lands in the padding block, which costs
+    acceptance at block boundaries, never correctness: the target verifies every draft.
+
+    The same driver serves an EAGLE-3 head (`models.eagle3.Eagle3Draft`): it reads the three
+    auxiliary hidden states the target keeps (`model.last_aux`) instead of the final one and maps its
+    draft-vocabulary ids to target ids."""
 
     name = "mtp"
 
-    def __init__(self, engine, k: int = 1):
-        assert k == 1, "one MTP layer drafts one token per step"
-        self.k = 1
+    def __init__(self, engine, k: int = 1, head=None):
+        self.k = int(k)
         self.engine = engine
-        self.mtp = engine.mtp
+        self.mtp = head if head is not None else engine.mtp
+        self.takes_aux = bool(getattr(self.mtp, "takes_aux", False))
         k0, v0 = engine.runner.kv_caches[0]
         self.kv = (torch.zeros_like(k0), torch.zeros_like(v0))
         self.draft = {}
         engine.runner.keep_hidden = True
 
     def propose(self, batch, n_rows: int, **_) -> np.ndarray:
-        out = np.zeros((n_rows, 1), dtype=np.int64)
+        out = np.zeros((n_rows, self.k), dtype=np.int64)
         for i in range(n_rows):
             d = self.draft.get(batch.request_id(i))
-            out[i, 0] = int(batch.history(i, 1)[0]) if d is None else d
+            out[i, :] = int(batch.history(i, 1)[0]) if d is None else d
         return out
 
-    def _run(self, next_tokens, hidden, positions, meta, last_rows, request_ids):
+    def _ids(self, hidden_rows):
+        ids = self.mtp.logits(hidden_rows).argmax(-1)
+        return self.mtp.to_target_ids(ids) if hasattr(self.mtp, "to_target_ids") else ids
+
+    def _run(self, next_tokens, hidden, positions, meta, last_rows, request_ids, pos_last=None, block_tables=None):
         h = self.mtp.forward(next_tokens, hidden, positions, meta, self.kv[0], self.kv[1])
         if len(last_rows) == 0:
             return
-        rows = torch.as_tensor(last_rows, dtype=torch.long, device=h.device)
-        ids = self.mtp.logits(h[rows]).argmax(-1).cpu().tolist()
-        for rid, t in zip(request_ids, ids):
-            self.draft[rid] = int(t)
+        dev = h.device
+        rows = torch.as_tensor(last_rows, dtype=torch.long, device=dev)
+        hr = h[rows]
+        ids = self._ids(hr)
+        drafts = [ids]
+        if self.k > 1:
+            bs = self.engine.cfg.block_size
+            n = len(last_rows)
+            bt = np.ascontiguousarray(np.asarray(block_tables)[:, :]).astype(np.int32)
+            bt_dev = torch.from_numpy(bt).to(dev)
+            p0 = np.asarray(pos_last, dtype=np.int64)
+            cu = torch.arange(0, n + 1, dtype=torch.int32, device=dev)
+            for j in range(1, self.k):
+                pj = p0 + j
+                blk = np.where(pj // bs < bt.shape[1], bt[np.arange(n), np.minimum(pj // bs, bt.shape[1] - 1)], 0)
+                slots = (blk.astype(np.int64) * bs + pj % bs).astype(np.int32)
+                m = AttentionMetadata(
+                    n_decode=0, n_prefill=n, slots=torch.from_numpy(slots).to(dev), block_table=bt_dev,
+                    kv_lens=torch.from_numpy((pj + 1).astype(np.int32)).to(dev), cu_q=cu, max_q_len=1,
+                    max_kv_len=int(pj.max()) + 1)
+                hr = self.mtp.forward(ids, hr, torch.from_numpy(pj).to(dev), m, self.kv[0], self.kv[1])
+                ids = self._ids(hr)
+                drafts.append(ids)
+        table = torch.stack(drafts, dim=1).cpu().tolist()
+        for rid, t in zip(request_ids, table):
+            self.draft[rid] = [int(v) for v in t]
 
     def after_execute(self, batch, sampled_ids):
         """After a normal (unspeculated) step: run the layer over all of its rows."""
@@ -118,13 +154,15 @@ class MTPDrafter:
         hidden, meta, positions = runner.last_hidden, runner.last_meta, runner.last_positions
         if hidden is None:
             return
+        if self.takes_aux:
+            hidden = runner.model.last_aux
         cu = np.asarray(batch.cu_q)
         pos_h = np.asarray(batch.positions)
         nseq = batch.n_decode + batch.n_prefill
         sample_seq = np.asarray(batch.sample_seq)
         sampled = {int(sample_seq[r]): int(sampled_ids[r]) for r in range(len(sample_seq))}
         nxt = np.zeros(int(cu[nseq]), dtype=np.int64)
-        last_rows, rids = [], []
+        last_rows, rids, seqs = [], [], []
         for i in range(nseq):
             a, b = int(cu[i]), int(cu[i + 1])
             hist = batch.history(i, 0)
@@ -135,7 +173,10 @@ class MTPDrafter:
                 nxt[b - 1] = sampled[i]
                 last_rows.append(b - 1)
                 rids.append(batch.request_id(i))
-        self._run(torch.from_numpy(nxt).to(hidden.device), hidden[: len(nxt)], positions[: len(nxt)], meta, last_rows, rids)
+                seqs.append(i)
+        self._run(torch.from_numpy(nxt).to(hidden.device), hidden[: len(nxt)], positions[: len(nxt)], meta, last_rows, rids,
+                  pos_last=[int(pos_h[r]) for r in last_rows],
+                  block_tables=np.asarray(batch.block_tables)[seqs] if seqs else None)
 
     def observe(self, batch, n_rows, hidden_rows, counts, tokens=None, kv0=None, block_tables=None):
         """After a verification pass: hidden_rows [B, 2, H]; row j < counts[i] of sequence i is
@@ -163,7 +204,7 @@ class MTPDrafter:
             cu_q=torch.tensor(cu, dtype=torch.int32, device=dev), max_q_len=int(max(counts)),
             max_kv_len=int(max(kv0)) + 1)
         self._run(torch.tensor(nxt, dtype=torch.int64, device=dev), hid, torch.tensor(pos, dtype=torch.int64, device=dev),
-                  meta, last_rows, rids)
+                  meta, last_rows, rids, pos_last=[pos[r] for r in last_rows], block_tables=block_tables[:n_rows])
 
     def forget(self, request_id):
         self.draft.pop(request_id, None)
@@ -252,7 +293,8 @@ class SpecDecoder:
         counts_h = counts.cpu().numpy().astype(np.int32)
         out_h = out.cpu().numpy()
         flat = np.concatenate([out_h[i, : counts_h[i]] for i in range(B)]).astype(np.int64)
-        self.drafter.observe(batch, B, hidden.view(B, k + 1, -1), counts_h, tokens=out_h, kv0=kv0, block_tables=bt)
+        seen = self.runner.model.last_aux if getattr(self.drafter, "takes_aux", False) else hidden
+        self.drafter.observe(batch, B, seen.view(B, k + 1, -1), counts_h, tokens=out_h, kv0=kv0, block_tables=bt)
         self.proposed += B * k
         self.accepted += int(counts_h.sum()) - B
         self.steps += 1
@@ -264,4 +306,6 @@ def make_drafter(kind: str, k: int, engine=None, **kw):
         return NgramDrafter(k, **kw)
     if kind == "mtp":
         return MTPDrafter(engine, k)
+    if kind == "eagle3":
+        return MTPDrafter(engine, k, head=engine.eagle3)
     raise ValueError(f"unknown drafter {kind!r}")

@@ -110,8 +110,14 @@ class DenseCausalLM(Module):
             x = x.clone() if x.data_ptr() == self.embed.weight.data_ptr() else x
             x[embeds[0]] = embeds[1].to(x.dtype)
         residual = None
-        for layer, (kc, vc) in zip(self.layers, kv_caches):
+        aux_ids = getattr(self, "aux_layers", None)        # layers whose outputs a draft head wants to see
+        aux = {}
+        for i, (layer, (kc, vc)) in enumerate(zip(self.layers, kv_caches)):
             x, residual = layer(x, residual, positions, meta, kc, vc)
+            if aux_ids and i in aux_ids:
+                aux[i] = x + residual                      # the layer's output: the branch joins the residual lazily
+        if aux_ids:
+            self.last_aux = torch.cat([aux[i] for i in aux_ids], dim=-1)
         comm = self.ps.comm if self.fused_tp else None
         if comm is not None and x.is_cuda:
             return comm.allreduce_norm(x.shape[0], residual, self.norm.weight, self.norm.eps)
