@@ -101,3 +101,34 @@ def test_vlm_on_gpu_matches_cpu_tokens():
         vlm.image_token_id = IMG
         outs[dev] = vlm.generate_mm(reqs, SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True))[0]
     assert len(outs["cuda:0"]) == 5 and outs["cuda:0"][:2] == outs["cpu"][:2], outs
+
+
+def test_vmm_pool_maps_device_memory_and_keeps_addresses():
+    """The page pool on the real driver: map on demand, compute on the mapped tensor, give the pages
+    back, map again at the same address, let a second range reuse the pages."""
+    from xllm_b200.utils.xtensor import VmmPool
+    pool = VmmPool(device=0, page_bytes=2 << 20, max_pages=8)
+    assert not pool.fake and pool.p.driver == "cuda"
+    pb = pool.page_bytes
+    r = pool.range(8 * pb)
+    r.ensure(3 * pb)
+    t = r.tensor((3 * pb // 2,), torch.bfloat16)
+    assert t.is_cuda and t.data_ptr() == r.ptr
+    t.fill_(1.0)
+    assert float(t.float().sum()) == t.numel()
+    y = torch.ones(4, 8, device="cuda", dtype=torch.bfloat16) @ r.tensor((8, 16), torch.bfloat16)
+    assert float(y.float().sum()) == 4 * 8 * 16
+    torch.cuda.synchronize()
+    addr = r.ptr
+    r.release_all()
+    assert pool.pages_in_use == 0 and pool.pages_free == 3
+    other = pool.range(4 * pb)
+    other.ensure(2 * pb)                                # reuses two of the pages
+    assert pool.pages_created == 3
+    r.ensure(pb)
+    assert r.ptr == addr and pool.pages_in_use == 3
+    r.tensor((16,), torch.float32).zero_()
+    torch.cuda.synchronize()
+    other.release_all()
+    r.release_all()
+    assert pool.trim() == 3

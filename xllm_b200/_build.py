@@ -46,7 +46,7 @@ NVCC_FLAGS = [
 ]
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-pthread",
              "-I", str(CSRC / "runtime"), "-I", str(CSRC / "frontend"), "-I", str(CSRC / "server"),
-             "-Wall", "-Wno-sign-compare", "-I", str(CSRC)]
+             "-Wall", "-Wno-sign-compare", "-I", str(CSRC), "-I", "/usr/local/cuda/include"]
 
 KERNEL_LIB = LIBDIR / "libxllm_kernels.so"
 
@@ -216,7 +216,7 @@ def _build_runtime(force, verbose) -> Path:
     want = _sha(srcs + hdrs, " ".join(flags))
     if todo or force or not out.exists() or not link_stamp.exists() \
             or link_stamp.read_text() != want:
-        _link_atomic([CXX, "-shared"], out, objs, ["-pthread", "-lrt"], verbose)
+        _link_atomic([CXX, "-shared"], out, objs, ["-pthread", "-lrt", "-ldl"], verbose)
         link_stamp.write_text(want)
     return out
 
