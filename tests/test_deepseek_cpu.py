@@ -97,3 +97,35 @@ def test_fp8_block_checkpoint_stream_is_dequantised():
     got = dict(dequant_fp8_stream(stream))
     assert set(got) == {"a.weight", "b.weight"} and got["a.weight"].dtype == torch.bfloat16
     assert (got["a.weight"].float() - w).abs().max() < 0.03
+
+
+def test_latent_cache_form_matches_materialised_form():
+    """The same weights through both MLA forms, with chunked prefill, a shared prompt prefix served
+    from the prefix cache and several sequences decoding together: identical token streams, and a
+    cache row of kv_lora_rank + rope values per token instead of per-head K and V."""
+    args = _args()
+
+    def make(**kw):
+        llm = LLM.__new__(LLM)
+        llm.engine = LLMEngine(EngineConfig(model="d", device="cpu", dtype="float32", num_blocks=96, enable_graph=False,
+                                            max_tokens_per_batch=24, **kw), model_args=args)
+        llm.tokenizer = None
+        return llm
+
+    g = torch.Generator().manual_seed(4)
+    shared = torch.randint(0, 500, (32,), generator=g).tolist()
+    prompts = [shared + torch.randint(0, 500, (n,), generator=g).tolist() for n in (5, 30)] + \
+              [torch.randint(0, 500, (n,), generator=g).tolist() for n in (11, 50)]
+    sp = SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)
+    a = make()
+    b = make(mla_latent_cache=True)
+    for (n, t), (_, u) in zip(a.engine.model.named_params(), b.engine.model.named_params()):
+        u.copy_(t)
+    want = [o.outputs[0].token_ids for o in a.generate(prompts, sp)]
+    got = [o.outputs[0].token_ids for o in b.generate(prompts, sp)]
+    assert got == want
+    again = [o.outputs[0].token_ids for o in b.generate(prompts[:2], sp)]       # now from the prefix cache
+    assert again == want[:2]
+    ka, kb = a.engine.runner.kv_caches[0][0], b.engine.runner.kv_caches[0][0]
+    assert kb.shape[1] == 1 and kb.shape[3] == args.kv_lora_rank + args.qk_rope_head_dim
+    assert kb[0].numel() * 1 < ka[0].numel() * 2

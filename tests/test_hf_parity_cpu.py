@@ -28,7 +28,7 @@ def _case(fam):
     if fam == "qwen3_moe":
         return t.Qwen3MoeConfig(**COMMON, head_dim=16, moe_intermediate_size=32, num_experts=8, num_experts_per_tok=2,
                                 norm_topk_prob=True), t.Qwen3MoeForCausalLM
-    if fam == "deepseek_v3":
+    if fam in ("deepseek_v3", "deepseek_v3_latent"):
         return t.DeepseekV3Config(**COMMON, moe_intermediate_size=32, n_routed_experts=8, num_experts_per_tok=2,
                                   n_shared_experts=1, first_k_dense_replace=1, n_group=2, topk_group=1, q_lora_rank=32,
                                   kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
@@ -46,7 +46,8 @@ def _case(fam):
     raise KeyError(fam)
 
 
-FAMILIES = ["llama", "mistral", "qwen2", "qwen3", "qwen3_moe", "deepseek_v3", "glm4", "glm4_moe", "minimax_m2"]
+FAMILIES = ["llama", "mistral", "qwen2", "qwen3", "qwen3_moe", "deepseek_v3", "deepseek_v3_latent", "glm4", "glm4_moe",
+            "minimax_m2"]
 
 
 @pytest.mark.parametrize("fam", FAMILIES)
@@ -67,7 +68,10 @@ def test_family_matches_huggingface(fam, tmp_path):
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (9, 21, 33)]
     llm = LLM(str(tmp_path), devices="cpu", dtype="float32", block_size=16, num_blocks=64, max_seqs_per_batch=8,
-              max_tokens_per_batch=256, enable_graph=False)
+              max_tokens_per_batch=256, enable_graph=False, mla_latent_cache=fam.endswith("_latent"))
+    if fam.endswith("_latent"):                   # one shared row of kv_lora_rank + rope values per token
+        k0, v0 = llm.engine.runner.kv_caches[0]
+        assert k0.shape[1:] == (1, 16, 16 + 8) and v0.data_ptr() == k0.data_ptr()
     outs = llm.generate(prompts, SamplingParams(max_tokens=10, temperature=0.0, ignore_eos=True))
     for p, o in zip(prompts, outs):
         with torch.no_grad():

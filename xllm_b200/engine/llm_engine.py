@@ -59,6 +59,7 @@ class EngineConfig:
     host_kv_blocks: int = 0             # > 0: keep evicted prefix-cache blocks in host memory (second tier)
     speculative_method: str = "ngram"   # drafter: "ngram" (suffix / prompt lookup, no draft model)
     draft_model: str = ""
+    mla_latent_cache: bool = False      # MLA models: cache [c_kv | k_pe] rows (576 values per token) instead of per-head K/V
     activation_reserve_bytes: int = 0   # 0: estimated from max_tokens_per_batch
 
 
@@ -85,6 +86,9 @@ class LLMEngine:
             self.args = load_model_args(cfg.model)
         else:
             self.args = preset(cfg.model)
+        if cfg.mla_latent_cache and self.args.kv_lora_rank:
+            import dataclasses
+            self.args = dataclasses.replace(self.args, mla_latent_cache=True)
         if cfg.dtype == "auto":
             self.dtype = torch.bfloat16 if self.device.type == "cuda" else _DTYPES.get(self.args.dtype, torch.float32)
             if self.device.type == "cpu" and self.dtype == torch.bfloat16:
@@ -114,12 +118,15 @@ class LLMEngine:
         max_len = cfg.max_model_len or min(self.args.max_position_embeddings, 32768)
         self.max_model_len = max_len
         nkv = self.model.num_kv_heads_local
-        per_block = ModelRunner.kv_bytes_per_block(self.args, nkv, cfg.block_size, self.dtype)
+        per_block = ModelRunner.kv_bytes_per_block(self.args, nkv, cfg.block_size, self.dtype,
+                                                   head_dim=getattr(self.model, "head_dim", None),
+                                                   planes=int(getattr(self.model, "kv_planes", 2)))
         num_blocks = cfg.num_blocks or self._estimate_blocks(per_block)
         self.num_blocks = num_blocks
         self.runner = ModelRunner(self.model, cfg.block_size, num_blocks, cfg.max_seqs_per_batch,
                                   cfg.max_tokens_per_batch, max_len, self.device, self.dtype,
-                                  enable_graph=cfg.enable_graph, graph_buckets=cfg.graph_buckets)
+                                  enable_graph=cfg.enable_graph and bool(getattr(self.model, "supports_graph", True)),
+                                  graph_buckets=cfg.graph_buckets)
         self.runner.overlap = cfg.enable_schedule_overlap
         # ---- scheduler
         sc = rt.SchedulerConfig()

@@ -119,15 +119,16 @@ class ModelRunner:
     def _alloc_kv(self):
         m = self.model
         L = self.args.num_hidden_layers
-        shape = (L, 2, self.num_blocks, m.num_kv_heads_local, self.block_size, m.head_dim)
+        planes = int(getattr(m, "kv_planes", 2))
+        shape = (L, planes, self.num_blocks, m.num_kv_heads_local, self.block_size, m.head_dim)
         kv = torch.zeros(shape, dtype=self.dtype, device=self.device)
         self.kv_tensor = kv
-        return [(kv[i, 0], kv[i, 1]) for i in range(L)]
+        return [(kv[i, 0], kv[i, planes - 1]) for i in range(L)]
 
     @staticmethod
-    def kv_bytes_per_block(args, nkv_local, block_size, dtype):
+    def kv_bytes_per_block(args, nkv_local, block_size, dtype, head_dim=None, planes=2):
         esz = torch.empty((), dtype=dtype).element_size()
-        return args.num_hidden_layers * 2 * nkv_local * block_size * args.head_dim * esz
+        return args.num_hidden_layers * planes * nkv_local * block_size * (head_dim or args.head_dim) * esz
 
     @staticmethod
     def _capacity(T, S, NS, bt):

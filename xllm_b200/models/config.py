@@ -59,6 +59,7 @@ class ModelArgs:
     qk_nope_head_dim: int = 0
     qk_rope_head_dim: int = 0
     v_head_dim: int = 0
+    mla_latent_cache: bool = False   # paged cache of [c_kv | k_pe] rows shared by all heads instead of per-head K/V
     # multi-token prediction
     num_nextn_predict_layers: int = 0
     # quantisation (from `quantization_config`)

@@ -3,12 +3,20 @@ shared experts, and the multi-token-prediction (MTP) draft layer.
 
 Parity: the reference has DeepSeek only for non-CUDA back ends (xllm/models/llm/deepseek_v2.h,
 deepseek_v3.h; MLA blueprint xllm/core/layers/dcu/deepseek_v2_attention.cpp:242-433;
-deepseek_mtp.h).  MLA here runs in its materialised form: the latent c_kv is expanded through
-kv_b_proj into per-head K (nope | rope) and V, heads are padded to 256 and laid out
-[rope | nope | pad] so that the fused rope/KV-write kernel and the paged attention kernels of the
-dense models are reused unchanged (dot products do not depend on the order of head dimensions as
-long as Q and K agree).  The latent-cache ("absorbed") decode kernel is not built yet; the price of
-this form is KV-cache size, not correctness.
+deepseek_mtp.h).  MLA has two forms here.
+
+Materialised (default): the latent c_kv is expanded through kv_b_proj into per-head K (nope | rope)
+and V, heads are padded to 256 and laid out [rope | nope | pad] so that the fused rope/KV-write
+kernel and the paged attention kernels of the dense models are reused unchanged (dot products do
+not depend on the order of head dimensions as long as Q and K agree).  Its price is KV-cache size.
+
+Latent (`ModelArgs.mla_latent_cache`): the paged cache holds one row of kv_lora_rank + rope
+values per token, shared by all heads ([normed c_kv | rotated k_pe], 576 values for DeepSeek-V3
+against 128 heads x 512 in the other form).  Queries are absorbed into the latent space
+(q_nope W_UK), attention is multi-query over the latent rows, and the result is expanded through
+W_UV.  This form runs on batched matrix products of the tensor library (a gather of the context
+rows, two batched GEMMs and a masked softmax per group of rows); a fused tcgen05 decode kernel over
+the latent cache is not built.
 """
 from __future__ import annotations
 
@@ -65,8 +73,76 @@ class MLAAttention(Module):
         # on this rank the cache sees `nh` KV heads of PAD_D
         self.nq = self.nkv = self.nh
         self.d = PAD_D
+        self.latent = bool(getattr(args, "mla_latent_cache", False))
+        if self.latent:
+            self.nkv, self.d = 1, self.kv_lora + self.rope_d
+
+    # ------------------------------------------------------------------ latent-cache form
+    def _rope(self, v, positions):
+        """Rotary embedding on adjacent pairs of the last dimension; v [T, heads, rope_d]."""
+        half = self.rope_d // 2
+        cs = self.rope.cos_sin[positions.long()].float()
+        cos, sin = cs[:, None, :half], cs[:, None, half:]
+        vf = v.float()
+        x1, x2 = vf[..., 0::2], vf[..., 1::2]
+        return torch.stack([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).flatten(-2).to(v.dtype)
+
+    def _forward_latent(self, x, positions, meta: AttentionMetadata, cache):
+        T, nh, L, r = x.shape[0], self.nh, self.kv_lora, self.rope_d
+        if self.q_lora:
+            q = self.q_b_proj(self.q_a_layernorm(self.q_a_proj(x)))
+        else:
+            q = self.q_proj(x)
+        q = q.view(T, nh, self.qk_d)
+        kv_a = self.kv_a_proj(x)
+        c = self.kv_a_layernorm(kv_a[:, :L].contiguous())
+        k_pe = self._rope(kv_a[:, None, L:], positions)[:, 0]
+        rows = cache.view(-1, L + r)                          # one row per token slot (a single shared "head")
+        valid = meta.slots >= 0
+        rows.index_copy_(0, meta.slots[valid].long(), torch.cat([c, k_pe], dim=-1)[valid].to(rows.dtype))
+        w = self.kv_b_proj.weight.view(nh, self.nope + self.vd, L)
+        w_uk, w_uv = w[:, :self.nope], w[:, self.nope:]        # [nh, nope, L], [nh, vd, L]
+        q_cat = torch.cat([torch.einsum("thn,hnl->thl", q[..., :self.nope], w_uk),
+                           self._rope(q[..., self.nope:], positions)], dim=-1)          # [T, nh, L + r]
+        o_lat = torch.empty((T, nh, L), dtype=x.dtype, device=x.device)
+        page = cache.shape[2]
+        host = getattr(meta, "_host_lens", None)
+        if host is None:
+            host = (meta.cu_q.tolist() if meta.cu_q is not None else None, meta.kv_lens.tolist())
+            meta._host_lens = host
+        cu, kv_lens = host
+        nd = meta.n_decode
+        ar = torch.arange(page, device=x.device)
+
+        def context(tables, n_tok):                           # tables [B, nb] -> latent rows [B, nb * page, L + r]
+            nb = (n_tok + page - 1) // page
+            idx = (tables[:, :nb].long()[:, :, None] * page + ar).flatten(1)
+            return rows[idx]
+
+        if nd > 0:                                            # one query token per sequence: padded batch
+            smax = max(kv_lens[:nd])
+            ctx = context(meta.block_table[:nd], smax)
+            s = torch.einsum("bhd,bsd->bhs", q_cat[:nd].float(), ctx.float()) * self.scale
+            dead = torch.arange(ctx.shape[1], device=x.device)[None, :] >= meta.kv_lens[:nd, None]
+            p = torch.softmax(s.masked_fill(dead[:, None, :], float("-inf")), dim=-1)
+            o_lat[:nd] = torch.einsum("bhs,bsl->bhl", p, ctx[..., :L].float()).to(x.dtype)
+        for i in range(meta.n_prefill):                       # prompt chunks: per sequence, queries in slices
+            a, b, n_kv = cu[nd + i], cu[nd + i + 1], kv_lens[nd + i]
+            ctx = context(meta.block_table[nd + i: nd + i + 1], n_kv)[0, :n_kv].float()
+            first = n_kv - (b - a)                            # position of the chunk's first query
+            for q0 in range(a, b, 256):
+                q1 = min(b, q0 + 256)
+                s = torch.einsum("qhd,sd->hqs", q_cat[q0:q1].float(), ctx) * self.scale
+                qpos = first + torch.arange(q0 - a, q1 - a, device=x.device)
+                dead = torch.arange(n_kv, device=x.device)[None, :] > qpos[:, None]
+                p = torch.softmax(s.masked_fill(dead[None], float("-inf")), dim=-1)
+                o_lat[q0:q1] = torch.einsum("hqs,sl->qhl", p, ctx[:, :L]).to(x.dtype)
+        out = torch.einsum("thl,hvl->thv", o_lat, w_uv)
+        return self.o_proj(out.reshape(T, nh * self.vd))
 
     def forward(self, x, positions, meta: AttentionMetadata, k_cache, v_cache):
+        if self.latent:
+            return self._forward_latent(x, positions, meta, k_cache)
         T = x.shape[0]
         nh = self.nh
         if self.q_lora:
@@ -138,11 +214,20 @@ class DeepseekCausalLM(DenseCausalLM):
 
     @property
     def num_kv_heads_local(self):
-        return self.layers[0].self_attn.nh
+        return self.layers[0].self_attn.nkv
 
     @property
     def head_dim(self):
-        return PAD_D
+        return self.layers[0].self_attn.d
+
+    @property
+    def kv_planes(self):
+        """2 = separate K and V caches; 1 = one latent cache per layer (the V handle aliases it)."""
+        return 1 if self.layers[0].self_attn.latent else 2
+
+    @property
+    def supports_graph(self):
+        return not self.layers[0].self_attn.latent     # the latent form sizes its gathers per batch
 
 
 class MTPDraft(Module):
