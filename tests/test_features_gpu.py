@@ -132,3 +132,27 @@ def test_vmm_pool_maps_device_memory_and_keeps_addresses():
     other.release_all()
     r.release_all()
     assert pool.trim() == 3
+
+
+def test_mla_latent_cache_on_gpu_matches_materialised_form():
+    from test_deepseek_cpu import _args
+    from xllm_b200.engine.llm_engine import EngineConfig, LLMEngine
+    args = _args()
+
+    def make(**kw):
+        llm = LLM.__new__(LLM)
+        llm.engine = LLMEngine(EngineConfig(model="d", device="cuda:0", dtype="bfloat16", num_blocks=128, enable_graph=False,
+                                            max_tokens_per_batch=64, **kw), model_args=args)
+        llm.tokenizer = None
+        return llm
+
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 500, (n,), generator=g).tolist() for n in (12, 70, 33)]
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    a, b = make(), make(mla_latent_cache=True)
+    for (_, t), (_, u) in zip(a.engine.model.named_params(), b.engine.model.named_params()):
+        u.copy_(t)
+    want = [o.outputs[0].token_ids for o in a.generate(prompts, sp)]
+    got = [o.outputs[0].token_ids for o in b.generate(prompts, sp)]
+    assert [w[:2] for w in want] == [x[:2] for x in got], (want, got)      # bf16: later near ties may differ
+    assert b.engine.runner.kv_caches[0][0].shape[1] == 1

@@ -83,3 +83,54 @@ def test_family_matches_huggingface(fam, tmp_path):
     with torch.no_grad():
         ref = hf(torch.tensor([seq])).logits[0]
     assert float((ours - ref).abs().max()) < 1e-4
+
+
+@pytest.mark.parametrize("fam", ["qwen2_vl", "qwen2_5_vl"])
+def test_vision_language_model_matches_huggingface(fam, tmp_path):
+    """Vision tower, merger, prompt expansion, 3-axis rotary positions and the decoder against
+    HuggingFace, from a saved checkpoint directory and a random image."""
+    import numpy as np
+    from xllm_b200.api.vlm import VLM
+    from xllm_b200.multimodal import Qwen2VLImageProcessor
+    t = transformers
+    IMG, VSTART, VEND = 500, 501, 502
+    text = dict(vocab_size=512, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                intermediate_size=128, max_position_embeddings=512, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]})
+    torch.manual_seed(0)
+    if fam == "qwen2_vl":
+        vis = dict(depth=2, embed_dim=32, hidden_size=64, num_heads=2, mlp_ratio=2, patch_size=14, spatial_merge_size=2,
+                   temporal_patch_size=2, in_channels=3)
+        cfg = t.Qwen2VLConfig(text_config=text, vision_config=vis, image_token_id=IMG, vision_start_token_id=VSTART,
+                              vision_end_token_id=VEND, video_token_id=503)
+        hf = t.Qwen2VLForConditionalGeneration(cfg)
+    else:
+        vis = dict(depth=2, hidden_size=32, out_hidden_size=64, intermediate_size=48, num_heads=2, patch_size=14,
+                   spatial_merge_size=2, temporal_patch_size=2, in_channels=3, window_size=56, fullatt_block_indexes=[1])
+        cfg = t.Qwen2_5_VLConfig(text_config=text, vision_config=vis, image_token_id=IMG, vision_start_token_id=VSTART,
+                                 vision_end_token_id=VEND, video_token_id=503)
+        hf = t.Qwen2_5_VLForConditionalGeneration(cfg)
+    hf = hf.float().eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n and p.dim() == 1 and not n.endswith("bias"):
+                p.copy_(1 + 0.1 * torch.randn_like(p))
+            elif n.endswith("bias"):
+                p.copy_(0.1 * torch.randn_like(p))
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    vlm = VLM(str(tmp_path), devices="cpu", dtype="float32", block_size=16, num_blocks=64, max_seqs_per_batch=8,
+              max_tokens_per_batch=64, enable_graph=False)
+    vlm.processor = Qwen2VLImageProcessor(14, 2, 2, min_pixels=56 * 56, max_pixels=140 * 140)
+    img = (np.random.default_rng(1).random((120, 150, 3)) * 255).astype(np.uint8)
+    prompt = [11, 12, VSTART, IMG, VEND, 13, 14, 15]
+    ids, mm = vlm.prepare(prompt, [img])
+    pv, grid = vlm.processor([img])
+    with torch.no_grad():
+        ref = hf.generate(input_ids=torch.tensor([ids]), pixel_values=pv, image_grid_thw=grid, max_new_tokens=8,
+                          do_sample=False, eos_token_id=None, pad_token_id=0)[0, len(ids):].tolist()
+        hv = hf.model.visual(pv, grid_thw=grid)
+        hv = hv.pooler_output if hasattr(hv, "pooler_output") else hv
+    assert float((hv - mm.embeds).abs().max()) < 1e-4
+    got = vlm.generate_mm([dict(prompt_token_ids=prompt, images=[img])],
+                          SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))[0]
+    assert got == ref

@@ -110,7 +110,12 @@ class LLMEngine:
                 weights = iterate_weights(cfg.model)
                 if self.args.quant_method == "fp8":
                     weights = dequant_fp8_stream(weights)
-                self.model.load_weights(weights, strict=False)
+                missing = self.model.load_weights(weights, strict=False)
+                # a checkpoint that lacks tensors the model needs would otherwise run on zeros
+                missing = [n for n in missing if not n.endswith("e_score_correction_bias")]
+                if missing and os.environ.get("XLLM_ALLOW_MISSING_WEIGHTS", "0") != "1":
+                    raise KeyError(f"checkpoint {cfg.model} lacks {len(missing)} tensors the model needs, e.g. "
+                                   f"{missing[:6]} (set XLLM_ALLOW_MISSING_WEIGHTS=1 to load anyway)")
             else:
                 self.model.init_random(seed=cfg.seed)
         self.load_seconds = time.time() - t0

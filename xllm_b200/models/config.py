@@ -170,7 +170,8 @@ def model_args_from_dict(cfg: Dict[str, Any]) -> ModelArgs:
     a.vision_config = cfg.get("vision_config")
     a.image_token_id = _g(cfg, "image_token_id", default=-1)
     a.vision_start_token_id = _g(cfg, "vision_start_token_id", default=-1)
-    rs = cfg.get("rope_scaling") or (cfg.get("text_config") or {}).get("rope_scaling") or {}
+    rs = cfg.get("rope_scaling") or (cfg.get("text_config") or {}).get("rope_scaling") or \
+        (rp if isinstance(rp, dict) else None) or {}
     a.mrope_section = list(rs.get("mrope_section") or [])
     a.video_token_id = _g(cfg, "video_token_id", default=-1)
     return a

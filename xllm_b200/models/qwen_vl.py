@@ -24,22 +24,40 @@ def _rot_half(x):
     return torch.cat([-x2, x1], dim=-1)
 
 
+def _rms(x, w, eps=1e-6):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
 class VisionBlock(Module):
-    def __init__(self, dim, heads, mlp_dim, dtype, device, act="quick_gelu"):
+    """`gated` selects the Qwen2.5-VL block: RMSNorm without bias and a SwiGLU MLP (gate/up/down with
+    biases) instead of LayerNorm and fc1 / quick-GELU / fc2."""
+
+    def __init__(self, dim, heads, mlp_dim, dtype, device, act="quick_gelu", gated=False):
         super().__init__()
-        self.heads, self.act = heads, act
+        self.heads, self.act, self.gated = heads, act, gated
         mk = lambda *s: torch.zeros(*s, dtype=dtype, device=device)
-        for name, shape in (("norm1.weight", (dim,)), ("norm1.bias", (dim,)), ("norm2.weight", (dim,)), ("norm2.bias", (dim,)),
-                            ("attn.qkv.weight", (3 * dim, dim)), ("attn.qkv.bias", (3 * dim,)),
-                            ("attn.proj.weight", (dim, dim)), ("attn.proj.bias", (dim,)),
-                            ("mlp.fc1.weight", (mlp_dim, dim)), ("mlp.fc1.bias", (mlp_dim,)),
-                            ("mlp.fc2.weight", (dim, mlp_dim)), ("mlp.fc2.bias", (dim,))):
+        shapes = [("norm1.weight", (dim,)), ("norm2.weight", (dim,)),
+                  ("attn.qkv.weight", (3 * dim, dim)), ("attn.qkv.bias", (3 * dim,)),
+                  ("attn.proj.weight", (dim, dim)), ("attn.proj.bias", (dim,))]
+        if gated:
+            shapes += [("mlp.gate_proj.weight", (mlp_dim, dim)), ("mlp.gate_proj.bias", (mlp_dim,)),
+                       ("mlp.up_proj.weight", (mlp_dim, dim)), ("mlp.up_proj.bias", (mlp_dim,)),
+                       ("mlp.down_proj.weight", (dim, mlp_dim)), ("mlp.down_proj.bias", (dim,))]
+        else:
+            shapes += [("norm1.bias", (dim,)), ("norm2.bias", (dim,)),
+                       ("mlp.fc1.weight", (mlp_dim, dim)), ("mlp.fc1.bias", (mlp_dim,)),
+                       ("mlp.fc2.weight", (dim, mlp_dim)), ("mlp.fc2.bias", (dim,))]
+        for name, shape in shapes:
             self.add_param(name, mk(*shape))
         self.p = self._params
 
     def forward(self, x, cos, sin, cu):
         p = self.p
-        h = F.layer_norm(x, x.shape[-1:], p["norm1.weight"], p["norm1.bias"], 1e-6)
+        if self.gated:
+            h = _rms(x, p["norm1.weight"])
+        else:
+            h = F.layer_norm(x, x.shape[-1:], p["norm1.weight"], p["norm1.bias"], 1e-6)
         T, D = h.shape
         q, k, v = F.linear(h, p["attn.qkv.weight"], p["attn.qkv.bias"]).view(T, 3, self.heads, D // self.heads).unbind(1)
         q = q * cos + _rot_half(q) * sin
@@ -50,6 +68,11 @@ class VisionBlock(Module):
                                                v[a:b].transpose(0, 1)[None])[0]
             outs.append(o.transpose(0, 1).reshape(b - a, D))
         x = x + F.linear(torch.cat(outs), p["attn.proj.weight"], p["attn.proj.bias"])
+        if self.gated:
+            h = _rms(x, p["norm2.weight"])
+            g = F.silu(F.linear(h, p["mlp.gate_proj.weight"], p["mlp.gate_proj.bias"]))
+            u = F.linear(h, p["mlp.up_proj.weight"], p["mlp.up_proj.bias"])
+            return x + F.linear(g * u, p["mlp.down_proj.weight"], p["mlp.down_proj.bias"])
         h = F.layer_norm(x, x.shape[-1:], p["norm2.weight"], p["norm2.bias"], 1e-6)
         h = F.linear(h, p["mlp.fc1.weight"], p["mlp.fc1.bias"])
         h = h * torch.sigmoid(1.702 * h) if self.act == "quick_gelu" else F.gelu(h)
@@ -61,14 +84,19 @@ class VisionBlock(Module):
 class VisionTower(Module):
     def __init__(self, vc: dict, out_hidden: int, dtype, device):
         super().__init__()
-        self.dim = vc.get("embed_dim", vc.get("hidden_size", 1280))
+        # Qwen2.5-VL: gated blocks, windowed attention except in `fullatt_block_indexes`, `hidden_size` is the
+        # tower width and `out_hidden_size` the decoder width (Qwen2-VL: `embed_dim` and `hidden_size`)
+        self.v25 = "fullatt_block_indexes" in vc or "out_hidden_size" in vc
+        self.dim = vc.get("hidden_size", 1280) if self.v25 else vc.get("embed_dim", vc.get("hidden_size", 1280))
+        self.full_blocks = set(vc.get("fullatt_block_indexes") or [])
+        self.window = int(vc.get("window_size", 112))
         self.heads = vc.get("num_heads", 16)
         self.patch = vc.get("patch_size", 14)
         self.merge = vc.get("spatial_merge_size", 2)
         self.tp = vc.get("temporal_patch_size", 2)
         in_ch = vc.get("in_chans", vc.get("in_channels", 3))
         depth = vc.get("depth", 32)
-        mlp_dim = int(self.dim * vc.get("mlp_ratio", 4))
+        mlp_dim = int(vc["intermediate_size"]) if self.v25 else int(self.dim * vc.get("mlp_ratio", 4))
         mk = lambda *s: torch.zeros(*s, dtype=dtype, device=device)
         # Conv3d(kernel = stride = patch) over non-overlapping patches is a linear map of the patch
         self.add_param("patch_embed.proj.weight", mk(self.dim, in_ch * self.tp * self.patch * self.patch),
@@ -77,12 +105,35 @@ class VisionTower(Module):
         blocks = Module()
         self.add_module("blocks", blocks)
         self.blocks = [blocks.add_module(str(i), VisionBlock(self.dim, self.heads, mlp_dim, dtype, device,
-                                                             vc.get("hidden_act", "quick_gelu"))) for i in range(depth)]
+                                                             vc.get("hidden_act", "quick_gelu"), gated=self.v25))
+                       for i in range(depth)]
         m2 = self.merge * self.merge
-        for name, shape in (("merger.ln_q.weight", (self.dim,)), ("merger.ln_q.bias", (self.dim,)),
+        for name, shape in (("merger.ln_q.weight", (self.dim,)),) + ((() if self.v25 else (("merger.ln_q.bias", (self.dim,)),)) + (
                             ("merger.mlp.0.weight", (self.dim * m2, self.dim * m2)), ("merger.mlp.0.bias", (self.dim * m2,)),
-                            ("merger.mlp.2.weight", (out_hidden, self.dim * m2)), ("merger.mlp.2.bias", (out_hidden,))):
+                            ("merger.mlp.2.weight", (out_hidden, self.dim * m2)), ("merger.mlp.2.bias", (out_hidden,)))):
             self.add_param(name, mk(*shape))
+
+    def window_index(self, grid_thw):
+        """Order of the merged units grouped by attention window, and the window boundaries in
+        patches (Qwen2.5-VL): windows of `window_size` pixels tile each frame, ragged at the edges."""
+        m = self.merge
+        ws = max(1, self.window // m // self.patch)
+        order, cu, base = [], [0], 0
+        for t, h, w in grid_thw.tolist():
+            gh, gw = h // m, w // m
+            idx = torch.arange(t * gh * gw).reshape(t, gh, gw)
+            ph, pw = ws - gh % ws, ws - gw % ws
+            nh, nw = (gh + ph) // ws, (gw + pw) // ws
+            pad = F.pad(idx, (0, pw, 0, ph), value=-100).reshape(t, nh, ws, nw, ws).permute(0, 1, 3, 2, 4)
+            pad = pad.reshape(t, nh * nw, ws, ws)
+            lens = (pad != -100).sum([2, 3]).reshape(-1)
+            flat = pad.reshape(-1)
+            order.append(flat[flat != -100] + base)
+            for n in lens.tolist():
+                if n:
+                    cu.append(cu[-1] + n * m * m)
+            base += t * gh * gw
+        return torch.cat(order), cu
 
     def rot_pos_emb(self, grid_thw, device):
         """2-D rotary angles per patch, in the merge-window order the processor emits patches in."""
@@ -111,12 +162,23 @@ class VisionTower(Module):
         cu = [0]
         for s in sizes:
             cu.append(cu[-1] + s)
-        for blk in self.blocks:
-            x = blk(x, cos, sin, cu)
-        x = F.layer_norm(x, x.shape[-1:], p["merger.ln_q.weight"], p["merger.ln_q.bias"], 1e-6)
-        x = x.view(-1, self.dim * self.merge * self.merge)
+        m2 = self.merge * self.merge
+        if self.v25:
+            order, cu_win = self.window_index(grid_thw)
+            order = order.to(x.device)
+            regroup = lambda z: z.reshape(z.shape[0] // m2, m2, *z.shape[1:])[order].reshape(z.shape)
+            x, cos, sin = regroup(x), regroup(cos), regroup(sin)
+            for i, blk in enumerate(self.blocks):
+                x = blk(x, cos, sin, cu if i in self.full_blocks else cu_win)
+            x = _rms(x, p["merger.ln_q.weight"])
+        else:
+            for blk in self.blocks:
+                x = blk(x, cos, sin, cu)
+            x = F.layer_norm(x, x.shape[-1:], p["merger.ln_q.weight"], p["merger.ln_q.bias"], 1e-6)
+        x = x.view(-1, self.dim * m2)
         x = F.gelu(F.linear(x, p["merger.mlp.0.weight"], p["merger.mlp.0.bias"]))
-        return F.linear(x, p["merger.mlp.2.weight"], p["merger.mlp.2.bias"])
+        x = F.linear(x, p["merger.mlp.2.weight"], p["merger.mlp.2.bias"])
+        return x[torch.argsort(order)] if self.v25 else x
 
     __call__ = forward
 
@@ -130,6 +192,16 @@ class Qwen2VLForConditionalGeneration(DenseCausalLM):
 
     def encode_images(self, pixel_values, grid_thw):
         return self.visual(pixel_values.to(self.device), grid_thw)
+
+    @staticmethod
+    def remap_weight(name, w):
+        # checkpoints name the tower `visual.*` or `model.visual.*`, the decoder `model.layers.*` or
+        # `model.language_model.layers.*`, depending on the library version that wrote them
+        if name.startswith("model.visual."):
+            name = name[len("model."):]
+        elif name.startswith("model.language_model."):
+            name = "model." + name[len("model.language_model."):]
+        return [(name, w)]
 
 
 @register_model("qwen2_vl", "qwen2_5_vl", "Qwen2VLForConditionalGeneration", "Qwen2_5_VLForConditionalGeneration")
