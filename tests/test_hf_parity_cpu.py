@@ -134,3 +134,39 @@ def test_vision_language_model_matches_huggingface(fam, tmp_path):
     got = vlm.generate_mm([dict(prompt_token_ids=prompt, images=[img])],
                           SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))[0]
     assert got == ref
+
+
+def test_qwen3_next_hybrid_matches_huggingface(tmp_path):
+    """Gated-delta-net layers (convolution tail + recurrent state per request), gated full attention,
+    zero-centred norms and the gated shared expert against HuggingFace; prompts are prefilled in
+    chunks so that the states carry over between steps, and several requests decode together."""
+    t = transformers
+    if not hasattr(t, "Qwen3NextForCausalLM"):
+        pytest.skip("no Qwen3-Next in this transformers build")
+    cfg = t.Qwen3NextConfig(vocab_size=512, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                            head_dim=32, intermediate_size=128, max_position_embeddings=512, rms_norm_eps=1e-6,
+                            tie_word_embeddings=False, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=16,
+                            linear_value_head_dim=16, linear_conv_kernel_dim=4, num_experts=8, num_experts_per_tok=2,
+                            moe_intermediate_size=32, shared_expert_intermediate_size=48, norm_topk_prob=True,
+                            decoder_sparse_step=1, mlp_only_layers=[], full_attention_interval=4)
+    torch.manual_seed(0)
+    hf = t.Qwen3NextForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("layernorm.weight") or n.endswith("model.norm.weight") or n.endswith("_norm.weight"):
+                p.copy_(0.1 * torch.randn_like(p))
+            elif n.endswith("linear_attn.norm.weight"):
+                p.copy_(1 + 0.1 * torch.randn_like(p))
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (9, 40, 23)]
+    llm = LLM(str(tmp_path), devices="cpu", dtype="float32", block_size=16, num_blocks=64, max_seqs_per_batch=8,
+              max_tokens_per_batch=24, enable_graph=False)
+    assert llm.engine.model.needs_state
+    outs = llm.generate(prompts, SamplingParams(max_tokens=10, temperature=0.0, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        with torch.no_grad():
+            ref = hf.generate(torch.tensor([p]), max_new_tokens=10, do_sample=False, eos_token_id=None,
+                              pad_token_id=0)[0, len(p):].tolist()
+        assert o.outputs[0].token_ids == ref
+    assert not llm.engine.model.state.owner               # every slot was given back

@@ -13,6 +13,7 @@ import time
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional
 
+import numpy as np
 import torch
 
 from .. import _build  # noqa: F401  (keeps the build helper importable from the package)
@@ -133,6 +134,9 @@ class LLMEngine:
                                   enable_graph=cfg.enable_graph and bool(getattr(self.model, "supports_graph", True)),
                                   graph_buckets=cfg.graph_buckets)
         self.runner.overlap = cfg.enable_schedule_overlap
+        if getattr(self.model, "needs_state", False):
+            self.model.alloc_state(cfg.max_seqs_per_batch + 1)
+            self.runner.meta_hook = self._state_hook
         # ---- scheduler
         sc = rt.SchedulerConfig()
         sc.max_tokens_per_batch = cfg.max_tokens_per_batch
@@ -141,7 +145,8 @@ class LLMEngine:
         sc.max_seqs_per_batch = cfg.max_seqs_per_batch
         sc.enable_chunked_prefill = cfg.enable_chunked_prefill
         sc.max_tokens_per_chunk_for_prefill = cfg.max_tokens_per_chunk_for_prefill
-        sc.enable_prefix_cache = cfg.enable_prefix_cache
+        # linear-attention models carry per-sequence state that cached prompt tokens would not update
+        sc.enable_prefix_cache = cfg.enable_prefix_cache and not getattr(self.model, "needs_state", False)
         sc.block_size = cfg.block_size
         sc.num_blocks = num_blocks
         sc.policy = cfg.policy
@@ -263,6 +268,22 @@ class LLMEngine:
         self.grammar = GrammarFilter(token_text, top_n, self.args.eos_token_id if eos_token_id is None else eos_token_id)
         self.runner.logits_hook = self._grammar_hook
 
+    # ------------------------------------------------------------------ linear-attention state slots
+    def _state_hook(self, batch, meta):
+        """Gives every sequence of the batch its state slot and marks the ones that start at
+        position 0 (new, or recomputed after a preemption) so that their state is reset."""
+        st = self.model.state
+        n = batch.n_decode + batch.n_prefill
+        cu, pos = np.asarray(batch.cu_q), np.asarray(batch.positions)
+        slots, fresh, bounds = [], [], []
+        for i in range(n):
+            a, b = int(cu[i]), int(cu[i + 1])
+            slots.append(st.slot_of(batch.request_id(i)))
+            fresh.append(int(pos[a]) == 0)
+            bounds.append((a, b))
+        meta.state_slots = torch.tensor(slots, dtype=torch.long, device=self.device)
+        meta.state_fresh, meta.seq_bounds = fresh, bounds
+
     # ------------------------------------------------------------------ multimodal inputs
     def _mm_hook(self, batch):
         """Per-step inputs of multimodal requests: the image embeddings of the placeholder rows in
@@ -365,6 +386,10 @@ class LLMEngine:
             else:
                 events = self.scheduler.take_pending_events()
         self._grammar_advance(events)
+        if getattr(self.model, "needs_state", False):
+            for ev in events:
+                if ev.request_finished:
+                    self.model.state.release(ev.request_id)
         if self.mm:
             for ev in events:
                 if ev.request_finished:

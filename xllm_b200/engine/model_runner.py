@@ -101,6 +101,7 @@ class ModelRunner:
         self.graph_replays = 0
         self.logits_hook = None
         self.mm_hook = None          # multimodal requests: (batch) -> None | (embeds, rope_table, rope_rows)
+        self.meta_hook = None        # (batch, meta) -> None: per-sequence state slots of linear-attention models
         self.keep_hidden = False     # speculative decoding with a draft layer needs the step's hidden states
         self.last_hidden = self.last_meta = self.last_positions = None
         self.graph_launches_per_replay: Dict[int, int] = {}
@@ -264,6 +265,8 @@ class ModelRunner:
             if self.overlap and self.prev_ids is not None:
                 ops.resolve_placeholders(tokens, self.prev_ids)
             meta = self._meta_from(buf, off, nd, npf, batch.max_q_len, batch.max_kv_len, bt_stride)
+            if self.meta_hook is not None:
+                self.meta_hook(batch, meta)
             if mm is not None:
                 embeds, meta.rope_table, meta.rope_rows = mm
                 hidden = self.model.forward(tokens, positions, meta, self.kv_caches, embeds=embeds)

@@ -167,6 +167,10 @@ def model_args_from_dict(cfg: Dict[str, Any]) -> ModelArgs:
     if q:
         a.quant_method = q.get("quant_method", "")
         a.quant_block = list(q.get("weight_block_size") or [])
+    for key in ("layer_types", "full_attention_interval", "linear_num_value_heads", "linear_num_key_heads",
+                "linear_key_head_dim", "linear_value_head_dim", "linear_conv_kernel_dim"):
+        if text.get(key) is not None:
+            a.extra[key] = text[key]
     a.vision_config = cfg.get("vision_config")
     a.image_token_id = _g(cfg, "image_token_id", default=-1)
     a.vision_start_token_id = _g(cfg, "vision_start_token_id", default=-1)

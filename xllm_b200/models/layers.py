@@ -369,14 +369,13 @@ class Attention(Module):
     def forward(self, x, positions, meta: AttentionMetadata, k_cache, v_cache):
         return self._attend(self.qkv(x), positions, meta, k_cache, v_cache)
 
-    def _attend(self, qkv, positions, meta: AttentionMetadata, k_cache, v_cache):
+    def _attend(self, qkv, positions, meta: AttentionMetadata, k_cache, v_cache, gate=None):
         cos_sin = self.rope.cos_sin
         if meta.rope_table is not None:
             cos_sin, positions = meta.rope_table, meta.rope_rows
         q = ops.rope_kv_write(qkv, self.nq, self.nkv, self.d, positions, cos_sin, self.rope.rot_dim,
                               slots=meta.slots, k_cache=k_cache, v_cache=v_cache,
-                              q_norm_w=self.q_norm.weight if self.q_norm else None,
-                              k_norm_w=self.k_norm.weight if self.k_norm else None, eps=self.eps,
+                              q_norm_w=self._norm_w(self.q_norm), k_norm_w=self._norm_w(self.k_norm), eps=self.eps,
                               interleaved=self.rope.interleaved)
         T = q.shape[0]
         out = torch.empty((T, self.nq, self.d), dtype=q.dtype, device=q.device)
@@ -390,7 +389,16 @@ class Attention(Module):
             ops.paged_prefill_attention(q, k_cache, v_cache, meta.block_table[nd:], meta.cu_q[nd:],
                                         meta.kv_lens[nd:], meta.max_q_len, self.scale, causal=True,
                                         window=self.window, out=out)
-        return self.o_proj(out.view(T, self.nq * self.d))
+        out = out.view(T, self.nq * self.d)
+        if gate is not None:                               # per-element output gate (Qwen3-Next)
+            out = out * torch.sigmoid(gate.float()).to(out.dtype)
+        return self.o_proj(out)
+
+    @staticmethod
+    def _norm_w(norm):
+        if norm is None:
+            return None
+        return norm.weight + 1.0 if norm.gemma else norm.weight       # zero-centred weights
 
     __call__ = forward
 

@@ -66,6 +66,9 @@ class SparseMoeBlock(Module):
         if args.n_shared_experts > 0:
             si = args.shared_expert_intermediate_size or args.moe_intermediate_size * args.n_shared_experts
             self.shared = self.add_module("shared_experts", DenseMLP(H, si, args.hidden_act, dtype, device, self.ps, reduce=False))
+        self.shared_gate = None
+        if self.shared is not None and args.extra.get("shared_expert_gate"):
+            self.shared_gate = self.add_module("shared_gate", Linear(H, 1, False, dtype, device, self.ps))
         self._ws = None
 
     def forward(self, x):
@@ -78,6 +81,8 @@ class SparseMoeBlock(Module):
             # With EP every rank would add the full shared output, so only the rank that owns
             # expert 0 contributes it.
             shared_out = ops.linear(ops.act_and_mul(self.shared.gate_up(x), a.hidden_act), self.shared.down.weight)
+            if self.shared_gate is not None:               # Qwen2-MoE / Qwen3-Next: sigmoid-gated shared expert
+                shared_out = shared_out * torch.sigmoid(self.shared_gate(x).float()).to(shared_out.dtype)
             if self.ep > 1 and self.e_begin != 0 and self.shared.ps.tp_size == 1 and self.ps.dp_size == 1:
                 shared_out = None
         if self.ep > 1 and self.ps.dp_size > 1:
