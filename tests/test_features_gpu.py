@@ -156,3 +156,33 @@ def test_mla_latent_cache_on_gpu_matches_materialised_form():
     got = [o.outputs[0].token_ids for o in b.generate(prompts, sp)]
     assert [w[:2] for w in want] == [x[:2] for x in got], (want, got)      # bf16: later near ties may differ
     assert b.engine.runner.kv_caches[0][0].shape[1] == 1
+
+
+def test_qwen3_next_hybrid_on_gpu_matches_cpu_tokens():
+    """Linear-attention state slots, gated attention and the MoE on the GPU against the CPU engine
+    with the same weights (bf16 against fp32: the first tokens must agree)."""
+    from xllm_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from xllm_b200.models import ModelArgs
+    args = ModelArgs(model_type="qwen3_next", vocab_size=1000, hidden_size=256, num_hidden_layers=4, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=64, intermediate_size=512, qk_norm=True, partial_rotary_factor=0.25,
+                     rope_theta=10000.0, max_position_embeddings=512, tie_word_embeddings=False, num_experts=8,
+                     num_experts_per_tok=2, moe_intermediate_size=128, shared_expert_intermediate_size=128, norm_topk_prob=True,
+                     extra=dict(linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=32,
+                                linear_value_head_dim=32, linear_conv_kernel_dim=4, full_attention_interval=4))
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (9, 50, 21)]
+    sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
+    outs, params = {}, None
+    for dev, dt in (("cpu", "float32"), ("cuda:0", "bfloat16")):
+        llm = LLM.__new__(LLM)
+        llm.engine = LLMEngine(EngineConfig(model="n", device=dev, dtype=dt, num_blocks=64, enable_graph=False,
+                                            max_tokens_per_batch=32), model_args=args)
+        llm.tokenizer = None
+        if params is None:
+            llm.engine.model.init_random(std=0.05, seed=5)
+            params = dict(llm.engine.model.named_params())
+        else:
+            for n, t in llm.engine.model.named_params():
+                t.copy_(params[n].to(t.dtype))
+        outs[dev] = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert [o[:2] for o in outs["cuda:0"]] == [o[:2] for o in outs["cpu"]], outs
