@@ -216,3 +216,28 @@ def test_paged_prefill_attention_tcgen05_and_legacy(nq, nkv, page, impl, monkeyp
     r0 = int(cu[2])
     _close(y2[r0:], yr[r0:], 2e-2)
     assert torch.count_nonzero(y2[:r0]) == 0
+
+
+@pytest.mark.parametrize("B,nv,dk,dv", [(3, 4, 32, 32), (17, 8, 128, 128), (2, 2, 64, 96)])
+def test_gdn_decode_step_matches_reference(B, nv, dk, dv):
+    """Gated-delta-rule state update against the same arithmetic in fp32 tensor ops; the states of
+    the slots that are not addressed must stay untouched."""
+    from xllm_b200.ops import gdn
+    g0 = torch.Generator(device="cuda").manual_seed(B)
+    n_slots = B + 3
+    state = torch.randn(n_slots, nv, dk, dv, device="cuda", generator=g0) * 0.3
+    slots = torch.randperm(n_slots, device="cuda")[:B]
+    q = torch.randn(B, nv, dk, device="cuda", generator=g0) * 0.2
+    k = torch.nn.functional.normalize(torch.randn(B, nv, dk, device="cuda", generator=g0), dim=-1)
+    v = torch.randn(B, nv, dv, device="cuda", generator=g0)
+    g = -torch.rand(B, nv, device="cuda", generator=g0)
+    beta = torch.rand(B, nv, device="cuda", generator=g0)
+    want_S, want_o = gdn.decode_step_reference(state[slots], q, k, v, g, beta)
+    before = state.clone()
+    out = gdn.decode_step(state, slots, q, k, v, g, beta)
+    torch.cuda.synchronize()
+    assert torch.allclose(out, want_o, atol=2e-4, rtol=2e-4)
+    assert torch.allclose(state[slots], want_S, atol=2e-4, rtol=2e-4)
+    rest = torch.ones(n_slots, dtype=torch.bool, device="cuda")
+    rest[slots] = False
+    assert torch.equal(state[rest], before[rest])

@@ -1,0 +1,64 @@
+// Gated delta rule, one decode token per sequence (linear-attention layers of Qwen3-Next / Qwen3.5):
+//
+//   S <- S * exp(g);  delta = (v - S^T k) * beta;  S <- S + k (x) delta;  o = S^T q
+//
+// S is the per-request, per-head recurrent state [d_k, d_v] in fp32, addressed through a slot index.
+// One CTA per (head, sequence), one thread per state column: a thread reads its column once from
+// HBM for S^T k and once more (from L1/L2) while it rewrites it and accumulates o, so the state
+// crosses HBM once in each direction -- the step is bound by that traffic.
+//
+// Parity: the reference runs this update through Triton FLA kernels on its Python executor
+// (xllm/python/.../kernels_cuda, fused_recurrent_gated_delta_rule); there is no CUDA C++ version.
+#include "common.cuh"
+
+namespace xllm {
+
+__global__ void gdn_decode_kernel(float* __restrict__ state, const int64_t* __restrict__ slots,
+                                  const float* __restrict__ q, const float* __restrict__ k,
+                                  const float* __restrict__ v, const float* __restrict__ g,
+                                  const float* __restrict__ beta, float* __restrict__ out, int nv, int dk, int dv) {
+  extern __shared__ float sm[];
+  float* ks = sm;
+  float* qs = sm + dk;
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int64_t row = (int64_t)b * nv + h;
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+    ks[i] = k[row * dk + i];
+    qs[i] = q[row * dk + i];
+  }
+  __syncthreads();
+  const float decay = __expf(g[row]);
+  const float bt = beta[row];
+  float* S = state + ((slots[b] * nv + h) * (int64_t)dk) * dv;
+  for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+    float kv = 0.f;
+    for (int i = 0; i < dk; ++i) kv += S[(int64_t)i * dv + j] * ks[i];
+    const float delta = (v[row * dv + j] - kv * decay) * bt;
+    float o = 0.f;
+    for (int i = 0; i < dk; ++i) {
+      const float s = S[(int64_t)i * dv + j] * decay + ks[i] * delta;
+      S[(int64_t)i * dv + j] = s;
+      o += s * qs[i];
+    }
+    out[row * dv + j] = o;
+  }
+}
+
+}  // namespace xllm
+
+// state [n_slots, nv, dk, dv] fp32; slots [B] int64; q, k [B, nv, dk]; v, out [B, nv, dv]; g, beta [B, nv] (all fp32).
+XLLM_API int xllm_gdn_decode_step(void* state, const void* slots, const void* q, const void* k, const void* v,
+                                  const void* g, const void* beta, void* out, int B, int nv, int dk, int dv,
+                                  void* stream) {
+  using namespace xllm;
+  if (B == 0) return 0;
+  if (dk <= 0 || dv <= 0 || dk > 4096) return (int)cudaErrorInvalidValue;
+  int threads = ((dv + 31) / 32) * 32;
+  if (threads > 256) threads = 256;
+  launch_pdl(gdn_decode_kernel, dim3(nv, B), dim3(threads), (size_t)(2 * dk * sizeof(float)), (cudaStream_t)stream,
+             (float*)state, (const int64_t*)slots, (const float*)q, (const float*)k, (const float*)v, (const float*)g,
+             (const float*)beta, (float*)out, nv, dk, dv);
+  return XLLM_LAUNCH_CHECK();
+}

@@ -22,6 +22,7 @@ import dataclasses
 import torch
 import torch.nn.functional as F
 
+from ..ops import gdn as gdn_ops
 from .layers import Attention, DenseMLP, Linear, MergedColumnLinear, Module, RMSNorm
 from .qwen import DecoderLayer, DenseCausalLM
 from .qwen_moe import SparseMoeBlock
@@ -116,9 +117,7 @@ class GatedDeltaNet(Module):
             y = F.silu((full.float() * self.conv_w.float()).sum(-1)).to(x.dtype)
             conv[s] = full[:, :, 1:]
             qh, kh, vh = heads(y)
-            S, o = self._step(rec[s], qh, kh, vh, g[:nd], beta[:nd])
-            rec[s] = S
-            out[:nd] = o
+            gdn_ops.decode_step(rec, s, qh, kh, vh, g[:nd], beta[:nd], out=out[:nd])
         for i in range(nd, len(bounds)):                   # prompt chunks
             a0, b0 = bounds[i]
             s = int(slots[i])
