@@ -136,3 +136,23 @@ def test_rerank_and_sample_routes(server):
         assert len(lp) == 3 and lp[0] >= lp[1] >= lp[2] and lp[0] <= 0
     st, _ = _post(server.port, "/v1/sample", {"prompt": "x", "selector": {"type": "regex", "value": "x"}})
     assert st == 400
+
+
+def test_image_generation_route(server):
+    import base64
+    import struct
+    import zlib
+    st, data = _post(server.port, "/v1/images/generations", {"prompt": "a red square", "n": 2, "size": "32x24", "steps": 6})
+    data = json.loads(data)
+    assert st == 200 and len(data["data"]) == 2
+    png = base64.b64decode(data["data"][0]["b64_json"])
+    assert png[:8] == b"\x89PNG\r\n\x1a\n"
+    w, h = struct.unpack(">II", png[16:24])
+    assert (w, h) == (32, 24)
+    n = struct.unpack(">I", png[33:37])[0]                      # the IDAT chunk follows the 25-byte IHDR chunk
+    assert png[37:41] == b"IDAT" and len(zlib.decompress(png[41:41 + n])) == h * (1 + 3 * w)
+    st, again = _post(server.port, "/v1/images/generations", {"prompt": "a red square", "size": "32x24", "steps": 6})
+    again = json.loads(again)
+    assert again["data"][0]["b64_json"] == data["data"][0]["b64_json"]      # the prompt seeds the noise
+    st, err = _post(server.port, "/v1/images/generations", {"n": 1})
+    assert st == 400

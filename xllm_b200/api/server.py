@@ -136,6 +136,8 @@ class ApiServer:
             return self._rerank(req, body)
         if path == "/v1/sample":
             return self._sample(req, body)
+        if path == "/v1/images/generations":
+            return self._images(req, body)
         if path == "/pause":
             self.engine.pause(str(body.get("mode", "KEEP")).upper())
             return self._json(req.id, 200, {"status": "paused"})
@@ -261,6 +263,17 @@ class ApiServer:
         n_tok = sum(len(x) for x in ids)
         self._json(req.id, 200, {"object": "list", "data": data, "model": self.model_name,
                                  "usage": {"prompt_tokens": n_tok, "total_tokens": n_tok}})
+
+    def _images(self, req, body):
+        """Text-to-image through the diffusion pipeline (`dit/pipeline.py`), created on first use."""
+        if getattr(self, "image_pipeline", None) is None:
+            from ..dit.pipeline import ImagePipeline
+            self.image_pipeline = ImagePipeline()
+        try:
+            out = self.image_pipeline.openai_response(body)
+        except ValueError as e:
+            return self._error(req.id, 400, str(e))
+        self._json(req.id, 200, out)
 
     def _rerank(self, req, body):
         from .embedding import rerank_scores
