@@ -268,6 +268,6 @@ class MTPDraft(Module):
         return self.lm_head(hidden_rows)
 
 
-@register_model("deepseek_v2", "deepseek_v3", "deepseek_v32", "DeepseekV2ForCausalLM", "DeepseekV3ForCausalLM")
+@register_model("deepseek_v2", "deepseek_v3", "deepseek_v32", "kimi_k2", "DeepseekV2ForCausalLM", "DeepseekV3ForCausalLM")
 def build_deepseek(args, dtype, device, ps):
     return DeepseekCausalLM(args, dtype, device, ps)
