@@ -321,7 +321,8 @@ class LLMEngine:
                 rows.extend(a + (m.positions[j] - p0) for j in range(lo, hi))
                 vals.append(m.embeds[lo:hi])
         dev = self.runner.device
-        table = mrope_table(pos3.to(dev), self.args.rotary_dim, self.args.rope_theta, self.model.mrope_section)
+        table = mrope_table(pos3.to(dev), self.args.rotary_dim, self.args.rope_theta, self.model.mrope_section,
+                            interleaved=bool(getattr(self.model, "mrope_interleaved", False)))
         embeds = None
         if rows:
             embeds = (torch.tensor(rows, dtype=torch.long, device=dev), torch.cat(vals).to(dev))

@@ -106,14 +106,20 @@ class DenseCausalLM(Module):
         `embeds` = (rows, values): input embeddings that replace the token embedding of those rows
         (image tokens of a multimodal prompt).  Returns the final-norm hidden states [T, H]."""
         x = self.embed(tokens)
+        deep = None
         if embeds is not None:
             x = x.clone() if x.data_ptr() == self.embed.weight.data_ptr() else x
-            x[embeds[0]] = embeds[1].to(x.dtype)
+            H = x.shape[-1]
+            x[embeds[0]] = embeds[1][:, :H].to(x.dtype)
+            if embeds[1].shape[-1] > H:                    # "deepstack": further visual features join after the first layers
+                deep = embeds[1][:, H:].to(x.dtype).view(embeds[1].shape[0], -1, H)
         residual = None
         aux_ids = getattr(self, "aux_layers", None)        # layers whose outputs a draft head wants to see
         aux = {}
         for i, (layer, (kc, vc)) in enumerate(zip(self.layers, kv_caches)):
             x, residual = layer(x, residual, positions, meta, kc, vc)
+            if deep is not None and i < deep.shape[1]:
+                x[embeds[0]] += deep[:, i]                  # the branch output joins the residual later: same sum
             if aux_ids and i in aux_ids:
                 aux[i] = x + residual                      # the layer's output: the branch joins the residual lazily
         if aux_ids:

@@ -207,3 +207,117 @@ class Qwen2VLForConditionalGeneration(DenseCausalLM):
 @register_model("qwen2_vl", "qwen2_5_vl", "Qwen2VLForConditionalGeneration", "Qwen2_5_VLForConditionalGeneration")
 def build_qwen2_vl(args, dtype, device, ps):
     return Qwen2VLForConditionalGeneration(args, dtype, device, ps)
+
+
+# ----------------------------------------------------------------------------------------- Qwen3-VL
+class VisionTowerV3(Module):
+    """Qwen3-VL tower: LayerNorm blocks with a tanh-GELU MLP, a learned position table interpolated
+    bilinearly to the image grid, 2-D rotary attention inside each frame, a merger, and "deepstack"
+    mergers that read the states after chosen blocks; their outputs are added to the decoder's
+    hidden states at the image rows after its first layers.  forward returns
+    [N / merge^2, out * (1 + n_deepstack)]: the image embeddings followed by the deepstack features."""
+
+    def __init__(self, vc: dict, dtype, device):
+        super().__init__()
+        self.dim, self.heads = vc["hidden_size"], vc["num_heads"]
+        self.out = vc["out_hidden_size"]
+        self.patch, self.merge, self.tp = vc.get("patch_size", 16), vc.get("spatial_merge_size", 2), vc.get("temporal_patch_size", 2)
+        self.deep_idx = list(vc.get("deepstack_visual_indexes") or [])
+        self.side = int(round(vc.get("num_position_embeddings", 2304) ** 0.5))
+        self.act = vc.get("hidden_act", "gelu_pytorch_tanh")
+        in_ch, inter, m2 = vc.get("in_channels", 3), vc["intermediate_size"], self.merge ** 2
+        mk = lambda *s: torch.zeros(*s, dtype=dtype, device=device)
+        D = self.dim
+        shapes = [("patch_embed.proj.bias", (D,)), ("pos_embed.weight", (self.side ** 2, D))]
+        for i in range(vc["depth"]):
+            b = f"blocks.{i}."
+            shapes += [(b + "norm1.weight", (D,)), (b + "norm1.bias", (D,)), (b + "norm2.weight", (D,)), (b + "norm2.bias", (D,)),
+                       (b + "attn.qkv.weight", (3 * D, D)), (b + "attn.qkv.bias", (3 * D,)),
+                       (b + "attn.proj.weight", (D, D)), (b + "attn.proj.bias", (D,)),
+                       (b + "mlp.linear_fc1.weight", (inter, D)), (b + "mlp.linear_fc1.bias", (inter,)),
+                       (b + "mlp.linear_fc2.weight", (D, inter)), (b + "mlp.linear_fc2.bias", (D,))]
+        for pre, nd in [("merger.", D)] + [(f"deepstack_merger_list.{k}.", D * m2) for k in range(len(self.deep_idx))]:
+            shapes += [(pre + "norm.weight", (nd,)), (pre + "norm.bias", (nd,)),
+                       (pre + "linear_fc1.weight", (D * m2, D * m2)), (pre + "linear_fc1.bias", (D * m2,)),
+                       (pre + "linear_fc2.weight", (self.out, D * m2)), (pre + "linear_fc2.bias", (self.out,))]
+        self.depth = vc["depth"]
+        w = mk(D, in_ch * self.tp * self.patch * self.patch)
+        self.add_param("patch_embed.proj.weight", w, {"patch_embed.proj.weight": lambda x, t=w: t.copy_(x.reshape(t.shape).to(t.dtype))})
+        for name, shape in shapes:
+            self.add_param(name, mk(*shape))
+
+    def _pos_embed(self, grid_thw, device):
+        p, m, n = self._params["pos_embed.weight"], self.merge, self.side
+        outs = []
+        for t, h, w in grid_thw.tolist():
+            hi, wi = torch.linspace(0, n - 1, h), torch.linspace(0, n - 1, w)
+            h0, w0 = hi.int(), wi.int()
+            h1, w1 = (h0 + 1).clip(max=n - 1), (w0 + 1).clip(max=n - 1)
+            dh, dw = (hi - h0)[:, None], (wi - w0)[None, :]
+            emb = 0
+            for hh, ww, wt in ((h0, w0, (1 - dh) * (1 - dw)), (h0, w1, (1 - dh) * dw), (h1, w0, dh * (1 - dw)), (h1, w1, dh * dw)):
+                idx = (hh.long()[:, None] * n + ww.long()[None, :]).flatten().to(device)
+                emb = emb + p[idx] * wt.flatten().to(device=device, dtype=p.dtype)[:, None]
+            emb = emb.repeat(t, 1).view(t, h // m, m, w // m, m, -1).permute(0, 1, 3, 2, 4, 5).flatten(0, 4)
+            outs.append(emb)
+        return torch.cat(outs)
+
+    def _merge(self, pre, x, post_norm):
+        p, D, m2 = self._params, self.dim, self.merge ** 2
+        if post_norm:
+            x = F.layer_norm(x.view(-1, D * m2), (D * m2,), p[pre + "norm.weight"], p[pre + "norm.bias"], 1e-6)
+        else:
+            x = F.layer_norm(x, (D,), p[pre + "norm.weight"], p[pre + "norm.bias"], 1e-6).view(-1, D * m2)
+        x = F.gelu(F.linear(x, p[pre + "linear_fc1.weight"], p[pre + "linear_fc1.bias"]))
+        return F.linear(x, p[pre + "linear_fc2.weight"], p[pre + "linear_fc2.bias"])
+
+    rot_pos_emb = VisionTower.rot_pos_emb
+
+    def forward(self, pixel_values, grid_thw):
+        p, D = self._params, self.dim
+        x = F.linear(pixel_values.to(p["patch_embed.proj.weight"].dtype), p["patch_embed.proj.weight"], p["patch_embed.proj.bias"])
+        x = x + self._pos_embed(grid_thw, x.device)
+        cos, sin = self.rot_pos_emb(grid_thw, x.device)
+        cos, sin = cos.to(x.dtype), sin.to(x.dtype)
+        cu = [0]
+        for t, h, w in grid_thw.tolist():                  # attention stays inside a frame
+            for _ in range(t):
+                cu.append(cu[-1] + h * w)
+        deep = []
+        for i in range(self.depth):
+            b = f"blocks.{i}."
+            h_ = F.layer_norm(x, (D,), p[b + "norm1.weight"], p[b + "norm1.bias"], 1e-6)
+            T = h_.shape[0]
+            q, k, v = F.linear(h_, p[b + "attn.qkv.weight"], p[b + "attn.qkv.bias"]).view(T, 3, self.heads, D // self.heads).unbind(1)
+            q = q * cos + _rot_half(q) * sin
+            k = k * cos + _rot_half(k) * sin
+            outs = []
+            for a0, b0 in zip(cu[:-1], cu[1:]):
+                o = F.scaled_dot_product_attention(q[a0:b0].transpose(0, 1)[None], k[a0:b0].transpose(0, 1)[None],
+                                                   v[a0:b0].transpose(0, 1)[None])[0]
+                outs.append(o.transpose(0, 1).reshape(b0 - a0, D))
+            x = x + F.linear(torch.cat(outs), p[b + "attn.proj.weight"], p[b + "attn.proj.bias"])
+            h_ = F.layer_norm(x, (D,), p[b + "norm2.weight"], p[b + "norm2.bias"], 1e-6)
+            h_ = F.gelu(F.linear(h_, p[b + "mlp.linear_fc1.weight"], p[b + "mlp.linear_fc1.bias"]),
+                        approximate="tanh" if "tanh" in self.act else "none")
+            x = x + F.linear(h_, p[b + "mlp.linear_fc2.weight"], p[b + "mlp.linear_fc2.bias"])
+            if i in self.deep_idx:
+                deep.append(self._merge(f"deepstack_merger_list.{self.deep_idx.index(i)}.", x, True))
+        return torch.cat([self._merge("merger.", x, False)] + deep, dim=-1)
+
+    __call__ = forward
+
+
+class Qwen3VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
+    mrope_interleaved = True
+
+    def __init__(self, args, dtype=torch.bfloat16, device="cpu", ps=None):
+        DenseCausalLM.__init__(self, args, dtype, device, ps or single())
+        self.visual = self.add_module("visual", VisionTowerV3(args.vision_config or {}, dtype, device))
+        half = args.rotary_dim // 2
+        self.mrope_section = list(args.mrope_section) or [half - 2 * (half * 3 // 8), half * 3 // 8, half * 3 // 8]
+
+
+@register_model("qwen3_vl", "Qwen3VLForConditionalGeneration")
+def build_qwen3_vl(args, dtype, device, ps):
+    return Qwen3VLForConditionalGeneration(args, dtype, device, ps)

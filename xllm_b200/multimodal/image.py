@@ -134,13 +134,21 @@ class MMInput:
     hash_key: int = 0                          # discriminator for the prefix cache (content hash of the images)
 
 
-def mrope_table(pos3: torch.Tensor, rot_dim: int, theta: float, sections: Sequence[int]) -> torch.Tensor:
+def mrope_table(pos3: torch.Tensor, rot_dim: int, theta: float, sections: Sequence[int],
+                interleaved: bool = False) -> torch.Tensor:
     """cos|sin rows [T, rot_dim] for 3-D positions pos3 [3, T]: frequency j uses the axis whose
-    section contains j (sections count rotary pairs: sum = rot_dim / 2)."""
+    section contains j (sections count rotary pairs: sum = rot_dim / 2).  `interleaved` (Qwen3-VL)
+    deals the axes out in turn instead, t h w t h w ..., the temporal axis keeping what is left."""
     half = rot_dim // 2
     assert sum(sections) == half
     inv = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float64, device=pos3.device) * 2.0 / rot_dim))
-    axis = torch.repeat_interleave(torch.arange(3, device=pos3.device), torch.tensor(list(sections), device=pos3.device))
+    if interleaved:
+        axis = torch.zeros(half, dtype=torch.long, device=pos3.device)
+        for ax, off in ((1, 1), (2, 2)):
+            axis[off:sections[ax] * 3:3] = ax
+    else:
+        axis = torch.repeat_interleave(torch.arange(3, device=pos3.device),
+                                       torch.tensor(list(sections), device=pos3.device))
     p = pos3.to(torch.float64)[axis]                      # [half, T]
     ang = (p * inv[:, None]).T                            # [T, half]
     return torch.cat([ang.cos(), ang.sin()], dim=-1).float()
