@@ -217,3 +217,32 @@ def test_qwen3_vl_matches_huggingface(tmp_path):
     got = vlm.generate_mm([dict(prompt_token_ids=prompt, images=[img])],
                           SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))[0]
     assert got == ref
+
+
+def test_qwen3_5_text_matches_huggingface(tmp_path):
+    """Qwen3.5 text decoder: the gated-delta-net layers with four separate input projections and a
+    dense MLP, every fourth layer gated full attention."""
+    t = transformers
+    if not hasattr(t, "Qwen3_5ForCausalLM"):
+        pytest.skip("no Qwen3.5 in this transformers build")
+    cfg = t.Qwen3_5TextConfig(vocab_size=512, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                              head_dim=32, intermediate_size=128, max_position_embeddings=512, rms_norm_eps=1e-6,
+                              tie_word_embeddings=False, linear_num_value_heads=4, linear_num_key_heads=2,
+                              linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4)
+    torch.manual_seed(0)
+    hf = t.Qwen3_5ForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("layernorm.weight") or n.endswith("model.norm.weight") or n.endswith("_norm.weight"):
+                p.copy_(0.1 * torch.randn_like(p))
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (9, 40, 23)]
+    llm = LLM(str(tmp_path), devices="cpu", dtype="float32", block_size=16, num_blocks=64, max_seqs_per_batch=8,
+              max_tokens_per_batch=24, enable_graph=False)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=10, temperature=0.0, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        with torch.no_grad():
+            ref = hf.generate(torch.tensor([p]), max_new_tokens=10, do_sample=False, eos_token_id=None,
+                              pad_token_id=0)[0, len(p):].tolist()
+        assert o.outputs[0].token_ids == ref

@@ -68,8 +68,17 @@ class GatedDeltaNet(Module):
         self.lin_idx = lin_idx
         self.eps = args.rms_norm_eps
         H = args.hidden_size
-        self.in_proj_qkvz = self.add_module("in_proj_qkvz", Linear(H, 2 * self.key_dim + 2 * self.value_dim, False, dtype, device))
-        self.in_proj_ba = self.add_module("in_proj_ba", Linear(H, 2 * self.nv, False, dtype, device))
+        # Qwen3-Next packs q|k|v|z per key head in one projection (and b|a in another); Qwen3.5 has four
+        # plain projections: [all q | all k | all v], z, b, a
+        self.split_proj = bool(e.get("split_proj"))
+        if self.split_proj:
+            self.in_proj_qkv = self.add_module("in_proj_qkv", Linear(H, self.conv_dim, False, dtype, device))
+            self.in_proj_z = self.add_module("in_proj_z", Linear(H, self.value_dim, False, dtype, device))
+            self.in_proj_b = self.add_module("in_proj_b", Linear(H, self.nv, False, dtype, device))
+            self.in_proj_a = self.add_module("in_proj_a", Linear(H, self.nv, False, dtype, device))
+        else:
+            self.in_proj_qkvz = self.add_module("in_proj_qkvz", Linear(H, 2 * self.key_dim + 2 * self.value_dim, False, dtype, device))
+            self.in_proj_ba = self.add_module("in_proj_ba", Linear(H, 2 * self.nv, False, dtype, device))
         self.conv_w = torch.zeros(self.conv_dim, self.K, dtype=dtype, device=device)
         self.add_param("conv1d.weight", self.conv_w, {"conv1d.weight": lambda w, t=self.conv_w: t.copy_(w.reshape(t.shape).to(t.dtype))})
         self.dt_bias = self.add_param("dt_bias", torch.ones(self.nv, dtype=dtype, device=device))
@@ -87,12 +96,17 @@ class GatedDeltaNet(Module):
     def forward(self, x, meta, state: LinearStateCache):
         T = x.shape[0]
         nk, nv, dk, dv, r = self.nk, self.nv, self.dk, self.dv, self.nv // self.nk
-        qkvz = self.in_proj_qkvz(x).view(T, nk, 2 * dk + 2 * r * dv)
-        ba = self.in_proj_ba(x).view(T, nk, 2 * r)
-        q, k, v, z = torch.split(qkvz, [dk, dk, r * dv, r * dv], dim=-1)
-        b, a = torch.split(ba, [r, r], dim=-1)
-        z = z.reshape(T, nv, dv)
-        mixed = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=-1)      # [T, conv_dim]
+        if self.split_proj:
+            mixed = self.in_proj_qkv(x)
+            z = self.in_proj_z(x).view(T, nv, dv)
+            b, a = self.in_proj_b(x), self.in_proj_a(x)
+        else:
+            qkvz = self.in_proj_qkvz(x).view(T, nk, 2 * dk + 2 * r * dv)
+            ba = self.in_proj_ba(x).view(T, nk, 2 * r)
+            q, k, v, z = torch.split(qkvz, [dk, dk, r * dv, r * dv], dim=-1)
+            b, a = torch.split(ba, [r, r], dim=-1)
+            z = z.reshape(T, nv, dv)
+            mixed = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=-1)  # [T, conv_dim]
         beta = torch.sigmoid(b.reshape(T, nv).float())
         g = -self.A_log.float().exp() * F.softplus(a.reshape(T, nv).float() + self.dt_bias.float())
         conv, rec = state.conv[self.lin_idx], state.rec[self.lin_idx]
@@ -206,6 +220,7 @@ class Qwen3NextCausalLM(DenseCausalLM):
             iv = int(e.get("full_attention_interval", 4))
             e["layer_types"] = ["full_attention" if (i + 1) % iv == 0 else "linear_attention" for i in range(n)]
         e["shared_expert_gate"] = True
+        e["split_proj"] = args.model_type.lower().startswith("qwen3_5")
         a = dataclasses.replace(args, extra=e, qk_norm=True,
                                 n_shared_experts=1 if args.shared_expert_intermediate_size else 0)
 
@@ -243,12 +258,15 @@ class Qwen3NextCausalLM(DenseCausalLM):
 
     @staticmethod
     def remap_weight(name, w):
+        if name.startswith("model.language_model."):        # checkpoints written from the vision-language wrapper
+            name = "model." + name[len("model.language_model."):]
         name = name.replace(".mlp.shared_expert.", ".mlp.shared_experts.")
         if name.endswith(".mlp.shared_expert_gate.weight"):
             name = name.replace(".mlp.shared_expert_gate.", ".mlp.shared_gate.")
         return [(name, w)]
 
 
-@register_model("qwen3_next", "qwen3_5", "qwen3_5_moe", "Qwen3NextForCausalLM")
+@register_model("qwen3_next", "qwen3_5_text", "qwen3_5_moe_text", "Qwen3NextForCausalLM", "Qwen3_5ForCausalLM",
+                "Qwen3_5MoeForCausalLM")
 def build_qwen3_next(args, dtype, device, ps):
     return Qwen3NextCausalLM(args, dtype, device, ps)
