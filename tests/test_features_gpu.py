@@ -172,7 +172,8 @@ def test_qwen3_next_hybrid_on_gpu_matches_cpu_tokens():
     g = torch.Generator().manual_seed(3)
     prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (9, 50, 21)]
     sp = SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True)
-    outs, params = {}, None
+    from xllm_b200.api.embedding import hidden_states
+    outs, params, logits = {}, None, {}
     for dev, dt in (("cpu", "float32"), ("cuda:0", "bfloat16")):
         llm = LLM.__new__(LLM)
         llm.engine = LLMEngine(EngineConfig(model="n", device=dev, dtype=dt, num_blocks=64, enable_graph=False,
@@ -185,4 +186,19 @@ def test_qwen3_next_hybrid_on_gpu_matches_cpu_tokens():
             for n, t in llm.engine.model.named_params():
                 t.copy_(params[n].to(t.dtype))
         outs[dev] = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
-    assert [o[:2] for o in outs["cuda:0"]] == [o[:2] for o in outs["cpu"]], outs
+        # teacher-forced logits over prompt + the CPU continuation, one pass
+        logits[dev] = [llm.engine.model.logits(hidden_states(llm.engine, p + c)).float().cpu()
+                       for p, c in zip(prompts, outs["cpu"])]
+    # bf16 against fp32 on nearly flat logits: first tokens agree, logits agree closely over whole sequences
+    assert [o[:1] for o in outs["cuda:0"]] == [o[:1] for o in outs["cpu"]], outs
+    for a, b in zip(logits["cpu"], logits["cuda:0"]):
+        assert float((a - b).abs().mean() / a.std()) < 0.08
+    # and on the GPU itself the decode path (state kernel, paged decode attention) must reproduce what
+    # the one-pass prefill predicts at the same positions
+    hit = tot = 0
+    for p, c, lg in zip(prompts, outs["cuda:0"], logits["cuda:0"]):
+        if c == outs["cpu"][prompts.index(p)]:
+            pred = lg[len(p) - 1: len(p) - 1 + len(c)].argmax(-1).tolist()
+            hit += sum(int(x == y) for x, y in zip(pred, c))
+            tot += len(c)
+    assert tot >= 10 and hit >= 0.8 * tot, (hit, tot, outs)
