@@ -165,8 +165,7 @@ def test_qwen3_next_hybrid_on_gpu_matches_cpu_tokens():
     from xllm_b200.models import ModelArgs
     args = ModelArgs(model_type="qwen3_next", vocab_size=1000, hidden_size=256, num_hidden_layers=4, num_attention_heads=4,
                      num_key_value_heads=2, head_dim=64, intermediate_size=512, qk_norm=True, partial_rotary_factor=0.25,
-                     rope_theta=10000.0, max_position_embeddings=512, tie_word_embeddings=False, num_experts=8,
-                     num_experts_per_tok=2, moe_intermediate_size=128, shared_expert_intermediate_size=128, norm_topk_prob=True,
+                     rope_theta=10000.0, max_position_embeddings=512, tie_word_embeddings=False,   # dense MLPs: no routing ties
                      extra=dict(linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=32,
                                 linear_value_head_dim=32, linear_conv_kernel_dim=4, full_attention_interval=4))
     g = torch.Generator().manual_seed(3)
