@@ -241,3 +241,51 @@ def test_gdn_decode_step_matches_reference(B, nv, dk, dv):
     rest = torch.ones(n_slots, dtype=torch.bool, device="cuda")
     rest[slots] = False
     assert torch.equal(state[rest], before[rest])
+
+
+def test_kernels_do_not_write_outside_their_outputs():
+    """Canary rows before and after every output buffer: odd token counts (not multiples of any tile
+    size) through norm, activation, gather, GEMM and the state kernel leave the guard rows untouched."""
+    from xllm_b200 import ops
+    from xllm_b200.ops import gdn
+    dev = "cuda"
+    g0 = torch.Generator(device=dev).manual_seed(0)
+
+    def guarded(rows, cols, dtype=torch.bfloat16, pad=3):
+        buf = torch.full((rows + 2 * pad, cols), 777.0, dtype=dtype, device=dev)
+        return buf, buf[pad:pad + rows]
+
+    def intact(buf, rows, pad=3):
+        return bool((buf[:pad] == 777.0).all()) and bool((buf[pad + rows:] == 777.0).all())
+
+    for T in (1, 5, 131):
+        H = 512
+        x = torch.randn(T, H, device=dev, dtype=torch.bfloat16, generator=g0)
+        w = torch.ones(H, device=dev, dtype=torch.bfloat16)
+        buf, out = guarded(T, H)
+        ops.rmsnorm(x, w, 1e-6, out=out)
+        assert intact(buf, T) and torch.isfinite(out.float()).all()
+        buf, out = guarded(T, H // 2)
+        ops.act_and_mul(x, "silu", out=out)
+        assert intact(buf, T)
+        idx = torch.randint(0, T, (T,), device=dev, generator=g0)
+        buf, out = guarded(T, H)
+        ops.gather_rows(x, idx, out=out)
+        assert intact(buf, T) and torch.equal(out, x[idx])
+        wt = torch.randn(384, H, device=dev, dtype=torch.bfloat16, generator=g0) * 0.05
+        buf, out = guarded(T, 384)
+        ops.linear(x, wt, out=out)
+        torch.cuda.synchronize()
+        assert intact(buf, T)
+        assert torch.allclose(out.float(), x.float() @ wt.float().T, atol=0.08, rtol=0.05)
+    B, nv, dk, dv = 5, 3, 32, 48
+    state = torch.zeros(B + 2, nv, dk, dv, device=dev)
+    state[0] = 777.0
+    state[-1] = 777.0
+    slots = torch.arange(1, B + 1, device=dev)
+    f = lambda *s: torch.randn(*s, device=dev, generator=g0)
+    buf, out = guarded(B * nv, dv, torch.float32)
+    gdn.decode_step(state, slots, f(B, nv, dk), f(B, nv, dk), f(B, nv, dv), -torch.rand(B, nv, device=dev, generator=g0),
+                    torch.rand(B, nv, device=dev, generator=g0), out=out.view(B, nv, dv))
+    torch.cuda.synchronize()
+    assert intact(buf, B * nv) and bool((state[0] == 777.0).all()) and bool((state[-1] == 777.0).all())

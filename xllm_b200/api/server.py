@@ -14,6 +14,7 @@ requests, step the engine, turn output events into response chunks.
 from __future__ import annotations
 
 import json
+import os
 import time
 import uuid
 from dataclasses import dataclass, field
@@ -66,6 +67,17 @@ class ApiServer:
         self.unhealthy_reason = ""
         self.profiler = None
         self._stop = False
+        from ..engine.fault import DeviceWatchdog
+        self.watchdog = DeviceWatchdog.for_engine(engine, self._set_unhealthy)
+        self._next_watch = 0.0
+        self.watch_interval_s = 3.0
+        from ..utils.tracing import TraceLog
+        self.trace = TraceLog(os.environ.get("XLLM_TRACE_LOG", ""))
+
+    def _set_unhealthy(self, reason: str):
+        """/health answers 503 with the reason from now on; an orchestrator is expected to recycle the instance."""
+        self.healthy = False
+        self.unhealthy_reason = reason
 
     # ------------------------------------------------------------------ plumbing
     def _json(self, http_id, status, obj):
@@ -95,6 +107,10 @@ class ApiServer:
             if self.http.is_disconnected(call.http_id):
                 self.engine.abort(rid)
                 self.calls.pop(rid, None)
+        now = time.time()
+        if now >= self._next_watch:            # expired bounded waits in kernels -> unhealthy
+            self._next_watch = now + self.watch_interval_s
+            self.watchdog.check()
         if self.engine.has_unfinished():
             for ev in self.engine.step():
                 self._on_event(ev)
@@ -157,20 +173,19 @@ class ApiServer:
         return self._error(req.id, 404, f"unknown route {path}")
 
     def _profile(self, req, start, body):
-        import torch
+        from ..utils.tracing import Profiler
         if start:
             if self.profiler is None:
-                acts = [torch.profiler.ProfilerActivity.CPU]
-                if torch.cuda.is_available():
-                    acts.append(torch.profiler.ProfilerActivity.CUDA)
-                self.profiler = torch.profiler.profile(activities=acts)
-                self.profiler.__enter__()
-            return self._json(req.id, 200, {"status": "profiling"})
+                backend = str(body.get("profile_backend") or os.environ.get("XLLM_PROFILE_BACKEND", "torch"))
+                try:
+                    self.profiler = Profiler(backend, self.engine.ps.rank)
+                except ValueError as e:
+                    return self._error(req.id, 400, str(e))
+                self.profiler.start()
+            return self._json(req.id, 200, {"status": "profiling", "backend": self.profiler.backend})
         path = ""
         if self.profiler is not None:
-            self.profiler.__exit__(None, None, None)
-            path = f"{body.get('profile_dir', '.')}/xllm_rank{self.engine.ps.rank}_{int(time.time())}.pt.trace.json"
-            self.profiler.export_chrome_trace(path)
+            path = self.profiler.stop(str(body.get("profile_dir", ".")))
             self.profiler = None
         return self._json(req.id, 200, {"status": "stopped", "trace": path})
 
@@ -398,6 +413,7 @@ class ApiServer:
             if call.t_first == 0.0:
                 call.t_first = now
                 _rt.metric_histogram_observe("time_to_first_token_latency_milliseconds", (now - call.t_arrival) * 1e3)
+                self.trace.event(ev.request_id, "first_token", ttft_ms=round((now - call.t_arrival) * 1e3, 3))
             call.token_ids[i].append(ev.token)
             if ev.has_logprob:
                 call.logprobs[i].append(ev.logprob)

@@ -187,6 +187,8 @@ class LLMEngine:
                     self.eagle3.load_weights(iterate_weights(cfg.draft_model), strict=False)
             self.spec = SpecDecoder(self, make_drafter(cfg.speculative_method, cfg.num_speculative_tokens, self),
                                     cfg.num_speculative_tokens)
+        from .fault import FaultPlan
+        self.fault = FaultPlan.from_env(self.ps.rank)      # host-side fault hooks (XLLM_FAULT), None when unset
         self.steps = 0
         self.step_log: List[tuple] = []
         self.record_steps = False
@@ -361,6 +363,8 @@ class LLMEngine:
     def step(self):
         """One scheduler iteration. Returns the list of OutputEvent produced by it."""
         events = []
+        if self.fault is not None:
+            self.fault.before_step(self.steps)
         batches = self.scheduler.schedule()
         batch = batches[0] if batches else None
         if self.ps.dp_size > 1 and self.ps.ep_size > 1:

@@ -200,6 +200,8 @@ def sample(logits, temperature=None, top_k=None, top_p=None, seed=0, offset=0, w
            generator=None, out_ids=None):
     """Returns (ids int64 [B], logprob fp32 [B] | None)."""
     if not logits.is_cuda:
+        if generator is None:       # the same (seed, offset) gives the same draw, as on the device
+            generator = torch.Generator().manual_seed((int(seed) * 1000003 + int(offset)) & 0x7FFFFFFFFFFFFFFF)
         return reference.sample(logits, temperature, top_k, top_p, generator, want_logprob)
     B, V = logits.shape
     assert logits.stride(-1) == 1
