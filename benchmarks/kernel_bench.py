@@ -168,6 +168,27 @@ def small_rows(results, hbm, tf, tag):
     print(f"sample greedy B=256 {t*1e3:8.3f} ms {b/t/1e9:7.0f} GB/s")
 
 
+def gdn_rows(results, hbm, tf, tag):
+    """Gated-delta-rule decode step (Qwen3-Next geometry: 32 value heads, 128 x 128 state per head).
+    The state is read and written once: 2 x B x 32 x 64 KB per call, far larger than L2."""
+    from xllm_b200.ops import gdn
+    nv, dk, dv = 32, 128, 128
+    for B in (64, 256):
+        state = torch.randn(B, nv, dk, dv, device="cuda") * 0.1
+        slots = torch.arange(B, device="cuda")
+        q = torch.randn(B, nv, dk, device="cuda") * 0.1
+        k = torch.nn.functional.normalize(torch.randn(B, nv, dk, device="cuda"), dim=-1)
+        v = torch.randn(B, nv, dv, device="cuda")
+        g = -torch.rand(B, nv, device="cuda")
+        beta = torch.rand(B, nv, device="cuda")
+        out = torch.empty(B, nv, dv, device="cuda")
+        t = bench(lambda: gdn.decode_step(state, slots, q, k, v, g, beta, out=out))
+        b = 2.0 * state.numel() * 4
+        results.append(dict(kernel="gdn_decode_step", shape=f"B={B} nv={nv} dk={dk} dv={dv}", ms=t * 1e3, gbs=b / t / 1e9,
+                            frac_of_roofline=b / t / 1e9 / hbm, peaks=tag))
+        print(f"gdn_decode_step B={B:<4} {t*1e3:8.3f} ms {b/t/1e9:7.0f} GB/s  {b/t/1e9/hbm:5.2f} of {tag} copy bandwidth")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--what", default="gemm,decode,prefill,small")
@@ -176,7 +197,7 @@ def main():
     hbm, tf, tag = peaks()
     results = []
     for w in a.what.split(","):
-        {"gemm": gemm_rows, "decode": decode_rows, "prefill": prefill_rows, "small": small_rows}[w](results, hbm, tf, tag)
+        {"gemm": gemm_rows, "decode": decode_rows, "prefill": prefill_rows, "small": small_rows, "gdn": gdn_rows}[w](results, hbm, tf, tag)
     if a.json:
         with open(a.json, "w") as f:
             json.dump(results, f, indent=1)

@@ -218,7 +218,8 @@ def test_paged_prefill_attention_tcgen05_and_legacy(nq, nkv, page, impl, monkeyp
     assert torch.count_nonzero(y2[:r0]) == 0
 
 
-@pytest.mark.parametrize("B,nv,dk,dv", [(3, 4, 32, 32), (17, 8, 128, 128), (2, 2, 64, 96)])
+@pytest.mark.parametrize("B,nv,dk,dv", [(3, 4, 32, 32), (17, 8, 128, 128), (2, 2, 64, 96), (4, 2, 256, 64), (3, 2, 256, 128),
+                                         (2, 3, 48, 40)])
 def test_gdn_decode_step_matches_reference(B, nv, dk, dv):
     """Gated-delta-rule state update against the same arithmetic in fp32 tensor ops; the states of
     the slots that are not addressed must stay untouched."""

@@ -46,6 +46,61 @@ __global__ void gdn_decode_kernel(float* __restrict__ state, const int64_t* __re
   }
 }
 
+// The same update with the state column held in registers: four row groups per CTA (threadIdx.y), each
+// thread keeps R = dk / 4 rows of its column, so that the state is read from HBM exactly once, all of a
+// thread's loads are in flight together, and the two column sums (S^T k and S^T q) are completed
+// through shared memory.
+constexpr int gdn_reg_max_threads(int R) { return R >= 64 ? 256 : (R >= 32 ? 512 : (R >= 16 ? 768 : 1024)); }
+
+template <int R>
+__global__ void __launch_bounds__(gdn_reg_max_threads(R)) gdn_decode_reg_kernel(float* __restrict__ state, const int64_t* __restrict__ slots,
+                                      const float* __restrict__ q, const float* __restrict__ k,
+                                      const float* __restrict__ v, const float* __restrict__ g,
+                                      const float* __restrict__ beta, float* __restrict__ out, int nv, int dv) {
+  constexpr int dk = 4 * R;
+  extern __shared__ float sm[];
+  float* ks = sm;
+  float* qs = sm + dk;
+  float* red = sm + 2 * dk;                         // [4][blockDim.x]
+  const int h = blockIdx.x, b = blockIdx.y;
+  // a CTA owns blockDim.x columns of the state (the columns are independent of one another)
+  const int tx = threadIdx.x, gy = threadIdx.y, dvp = blockDim.x;
+  const int j = blockIdx.z * dvp + tx;
+  const int64_t row = (int64_t)b * nv + h;
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int i = gy * dvp + tx; i < dk; i += 4 * dvp) {
+    ks[i] = k[row * dk + i];
+    qs[i] = q[row * dk + i];
+  }
+  const float decay = __expf(g[row]);
+  const float bt = beta[row];
+  const bool live = j < dv;
+  float* S = state + ((slots[b] * nv + h) * (int64_t)dk + gy * R) * dv + j;
+  float s[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) s[r] = live ? S[(int64_t)r * dv] : 0.f;
+  __syncthreads();
+  float part = 0.f;
+#pragma unroll
+  for (int r = 0; r < R; ++r) part += s[r] * ks[gy * R + r];
+  red[gy * dvp + tx] = part;
+  __syncthreads();
+  const float kv = (red[tx] + red[dvp + tx] + red[2 * dvp + tx] + red[3 * dvp + tx]) * decay;
+  const float delta = ((live ? v[row * dv + j] : 0.f) - kv) * bt;
+  float o = 0.f;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    s[r] = s[r] * decay + ks[gy * R + r] * delta;
+    if (live) S[(int64_t)r * dv] = s[r];
+    o += s[r] * qs[gy * R + r];
+  }
+  __syncthreads();
+  red[gy * dvp + tx] = o;
+  __syncthreads();
+  if (gy == 0 && live) out[row * dv + j] = red[tx] + red[dvp + tx] + red[2 * dvp + tx] + red[3 * dvp + tx];
+}
+
 }  // namespace xllm
 
 // state [n_slots, nv, dk, dv] fp32; slots [B] int64; q, k [B, nv, dk]; v, out [B, nv, dv]; g, beta [B, nv] (all fp32).
@@ -55,7 +110,29 @@ XLLM_API int xllm_gdn_decode_step(void* state, const void* slots, const void* q,
   using namespace xllm;
   if (B == 0) return 0;
   if (dk <= 0 || dv <= 0 || dk > 4096) return (int)cudaErrorInvalidValue;
-  int threads = ((dv + 31) / 32) * 32;
+  const int dvp = ((dv + 31) / 32) * 32;
+  if (dk == 32 || dk == 64 || dk == 128 || dk == 256) {   // register-resident state columns
+    // 64 columns per CTA (32 for the largest state rows): 256 threads, so that two or more CTAs share an SM
+    const int cols = dk == 256 ? 32 : (dvp < 64 ? dvp : 64);
+    const dim3 grid(nv, B, (dv + cols - 1) / cols), block(cols, 4);
+    const size_t smem = (size_t)(2 * dk + 4 * cols) * sizeof(float);
+    cudaStream_t st = (cudaStream_t)stream;
+#define XLLM_GDN_CASE(RR)                                                                                       \
+  case RR:                                                                                                      \
+    launch_pdl(gdn_decode_reg_kernel<RR>, grid, block, smem, st, (float*)state, (const int64_t*)slots,          \
+               (const float*)q, (const float*)k, (const float*)v, (const float*)g, (const float*)beta,          \
+               (float*)out, nv, dv);                                                                            \
+    return XLLM_LAUNCH_CHECK();
+    switch (dk / 4) {
+      XLLM_GDN_CASE(8)
+      XLLM_GDN_CASE(16)
+      XLLM_GDN_CASE(32)
+      XLLM_GDN_CASE(64)
+      default: break;
+    }
+#undef XLLM_GDN_CASE
+  }
+  int threads = dvp;
   if (threads > 256) threads = 256;
   launch_pdl(gdn_decode_kernel, dim3(nv, B), dim3(threads), (size_t)(2 * dk * sizeof(float)), (cudaStream_t)stream,
              (float*)state, (const int64_t*)slots, (const float*)q, (const float*)k, (const float*)v, (const float*)g,
