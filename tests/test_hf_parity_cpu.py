@@ -219,18 +219,25 @@ def test_qwen3_vl_matches_huggingface(tmp_path):
     assert got == ref
 
 
-def test_qwen3_5_text_matches_huggingface(tmp_path):
-    """Qwen3.5 text decoder: the gated-delta-net layers with four separate input projections and a
-    dense MLP, every fourth layer gated full attention."""
+@pytest.mark.parametrize("moe", [False, True])
+def test_qwen3_5_text_matches_huggingface(moe, tmp_path):
+    """Qwen3.5 text decoder: the gated-delta-net layers with four separate input projections, a dense
+    MLP or the MoE with a gated shared expert, every fourth layer gated full attention."""
     t = transformers
-    if not hasattr(t, "Qwen3_5ForCausalLM"):
+    if not hasattr(t, "Qwen3_5ForCausalLM") or not hasattr(t, "Qwen3_5MoeForCausalLM"):
         pytest.skip("no Qwen3.5 in this transformers build")
-    cfg = t.Qwen3_5TextConfig(vocab_size=512, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
-                              head_dim=32, intermediate_size=128, max_position_embeddings=512, rms_norm_eps=1e-6,
-                              tie_word_embeddings=False, linear_num_value_heads=4, linear_num_key_heads=2,
-                              linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4)
+    common = dict(vocab_size=512, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                  head_dim=32, max_position_embeddings=512, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                  linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=16, linear_value_head_dim=16,
+                  linear_conv_kernel_dim=4)
     torch.manual_seed(0)
-    hf = t.Qwen3_5ForCausalLM(cfg).float().eval()
+    if moe:
+        cfg = t.Qwen3_5MoeTextConfig(**common, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32,
+                                     shared_expert_intermediate_size=48)
+        hf = t.Qwen3_5MoeForCausalLM(cfg).float().eval()
+    else:
+        cfg = t.Qwen3_5TextConfig(**common, intermediate_size=128)
+        hf = t.Qwen3_5ForCausalLM(cfg).float().eval()
     with torch.no_grad():
         for n, p in hf.named_parameters():
             if n.endswith("layernorm.weight") or n.endswith("model.norm.weight") or n.endswith("_norm.weight"):
