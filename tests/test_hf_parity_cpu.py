@@ -172,9 +172,11 @@ def test_qwen3_next_hybrid_matches_huggingface(tmp_path):
     assert not llm.engine.model.state.owner               # every slot was given back
 
 
-def test_qwen3_vl_matches_huggingface(tmp_path):
+@pytest.mark.parametrize("moe", [False, True])
+def test_qwen3_vl_matches_huggingface(moe, tmp_path):
     """Qwen3-VL: interpolated position table, deepstack features added after the first decoder
-    layers, interleaved 3-axis rotary embedding, q/k norms."""
+    layers, interleaved 3-axis rotary embedding, q/k norms; with the dense or the MoE decoder (whose
+    checkpoints keep a layer's experts in two fused tensors)."""
     import numpy as np
     from xllm_b200.api.vlm import VLM
     from xllm_b200.multimodal import Qwen2VLImageProcessor
@@ -187,10 +189,18 @@ def test_qwen3_vl_matches_huggingface(tmp_path):
                 rope_scaling={"rope_type": "default", "mrope_section": [2, 3, 3], "mrope_interleaved": True})
     vis = dict(depth=3, hidden_size=32, out_hidden_size=64, intermediate_size=48, num_heads=2, patch_size=16, spatial_merge_size=2,
                temporal_patch_size=2, in_channels=3, num_position_embeddings=36, deepstack_visual_indexes=[0, 2])
-    cfg = t.Qwen3VLConfig(text_config=text, vision_config=vis, image_token_id=IMG, vision_start_token_id=VSTART,
-                          vision_end_token_id=VEND, video_token_id=503)
     torch.manual_seed(0)
-    hf = t.Qwen3VLForConditionalGeneration(cfg).float().eval()
+    if moe:
+        if not hasattr(t, "Qwen3VLMoeForConditionalGeneration"):
+            pytest.skip("no Qwen3-VL-MoE in this transformers build")
+        text.update(num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32, decoder_sparse_step=1, mlp_only_layers=[])
+        cfg = t.Qwen3VLMoeConfig(text_config=text, vision_config=vis, image_token_id=IMG, vision_start_token_id=VSTART,
+                                 vision_end_token_id=VEND, video_token_id=503)
+        hf = t.Qwen3VLMoeForConditionalGeneration(cfg).float().eval()
+    else:
+        cfg = t.Qwen3VLConfig(text_config=text, vision_config=vis, image_token_id=IMG, vision_start_token_id=VSTART,
+                              vision_end_token_id=VEND, video_token_id=503)
+        hf = t.Qwen3VLForConditionalGeneration(cfg).float().eval()
     with torch.no_grad():
         for n, p in hf.named_parameters():
             if "norm" in n and p.dim() == 1 and not n.endswith("bias"):

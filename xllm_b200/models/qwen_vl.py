@@ -321,3 +321,41 @@ class Qwen3VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
 @register_model("qwen3_vl", "Qwen3VLForConditionalGeneration")
 def build_qwen3_vl(args, dtype, device, ps):
     return Qwen3VLForConditionalGeneration(args, dtype, device, ps)
+
+
+class Qwen3VLMoeForConditionalGeneration(Qwen3VLForConditionalGeneration):
+    """Qwen3-VL with the Qwen3-MoE decoder.  Its checkpoints keep the experts of a layer in two fused
+    tensors, `experts.gate_up_proj` [E, 2I, H] (or [E, H, 2I] in the original release) and
+    `experts.down_proj` [E, H, I] (or [E, I, H]); they are split into per-expert tensors on load."""
+
+    def __init__(self, args, dtype=torch.bfloat16, device="cpu", ps=None):
+        from .qwen_moe import _make_mlp
+        DenseCausalLM.__init__(self, args, dtype, device, ps or single(), make_mlp=_make_mlp(args, dtype, device, ps or single()))
+        self.visual = self.add_module("visual", VisionTowerV3(args.vision_config or {}, dtype, device))
+        half = args.rotary_dim // 2
+        self.mrope_section = list(args.mrope_section) or [half - 2 * (half * 3 // 8), half * 3 // 8, half * 3 // 8]
+
+    def remap_weight(self, name, w):
+        out = []
+        for n, t in Qwen2VLForConditionalGeneration.remap_weight(name, w):
+            H, I = self.args.hidden_size, self.args.moe_intermediate_size
+            if n.endswith(".mlp.experts.gate_up_proj"):
+                base = n[: -len("gate_up_proj")]
+                if t.shape[1] != 2 * I:
+                    t = t.transpose(1, 2)                  # [E, H, 2I] -> [E, 2I, H]
+                for e in range(t.shape[0]):
+                    out += [(f"{base}{e}.gate_proj.weight", t[e, :I]), (f"{base}{e}.up_proj.weight", t[e, I:])]
+            elif n.endswith(".mlp.experts.down_proj"):
+                base = n[: -len("down_proj")]
+                if t.shape[1] != H:
+                    t = t.transpose(1, 2)                  # [E, I, H] -> [E, H, I]
+                for e in range(t.shape[0]):
+                    out.append((f"{base}{e}.down_proj.weight", t[e]))
+            else:
+                out.append((n, t))
+        return out
+
+
+@register_model("qwen3_vl_moe", "Qwen3VLMoeForConditionalGeneration")
+def build_qwen3_vl_moe(args, dtype, device, ps):
+    return Qwen3VLMoeForConditionalGeneration(args, dtype, device, ps)
