@@ -263,3 +263,42 @@ def test_qwen3_5_text_matches_huggingface(moe, tmp_path):
             ref = hf.generate(torch.tensor([p]), max_new_tokens=10, do_sample=False, eos_token_id=None,
                               pad_token_id=0)[0, len(p):].tolist()
         assert o.outputs[0].token_ids == ref
+
+
+def test_qwen3_5_vision_language_matches_huggingface(tmp_path):
+    """Qwen3.5 with images: hybrid decoder (state slots) + vision tower + interleaved M-RoPE on the
+    full-attention layers, prompt prefilled in two chunks."""
+    import numpy as np
+    from xllm_b200.api.vlm import VLM
+    from xllm_b200.multimodal import Qwen2VLImageProcessor
+    t = transformers
+    if not hasattr(t, "Qwen3_5ForConditionalGeneration"):
+        pytest.skip("no Qwen3.5 in this transformers build")
+    IMG, VSTART, VEND = 500, 501, 502
+    text = dict(vocab_size=512, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                intermediate_size=128, max_position_embeddings=512, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=16, linear_value_head_dim=16,
+                linear_conv_kernel_dim=4,
+                rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.25,
+                                 "mrope_section": [2, 3, 3], "mrope_interleaved": True})
+    vis = dict(depth=2, hidden_size=32, out_hidden_size=64, intermediate_size=48, num_heads=2, patch_size=16, spatial_merge_size=2,
+               temporal_patch_size=2, in_channels=3, num_position_embeddings=36)
+    cfg = t.Qwen3_5Config(text_config=text, vision_config=vis, image_token_id=IMG, vision_start_token_id=VSTART,
+                          vision_end_token_id=VEND, video_token_id=503)
+    torch.manual_seed(0)
+    hf = t.Qwen3_5ForConditionalGeneration(cfg).float().eval()
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    vlm = VLM(str(tmp_path), devices="cpu", dtype="float32", block_size=16, num_blocks=64, max_seqs_per_batch=8,
+              max_tokens_per_batch=16, enable_graph=False)
+    vlm.processor = Qwen2VLImageProcessor(16, 2, 2, min_pixels=64 * 64, max_pixels=160 * 160)
+    img = (np.random.default_rng(1).random((120, 150, 3)) * 255).astype(np.uint8)
+    prompt = [11, 12, VSTART, IMG, VEND, 13, 14, 15]
+    ids, mm = vlm.prepare(prompt, [img])
+    pv, grid = vlm.processor([img])
+    with torch.no_grad():
+        kinds = torch.tensor([[1 if i == IMG else 0 for i in ids]])
+        ref = hf.generate(input_ids=torch.tensor([ids]), pixel_values=pv, image_grid_thw=grid, mm_token_type_ids=kinds,
+                          max_new_tokens=8, do_sample=False, eos_token_id=None, pad_token_id=0)[0, len(ids):].tolist()
+    got = vlm.generate_mm([dict(prompt_token_ids=prompt, images=[img])],
+                          SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))[0]
+    assert got == ref

@@ -258,7 +258,8 @@ class Qwen3NextCausalLM(DenseCausalLM):
 
     @staticmethod
     def remap_weight(name, w):
-        if name.startswith("model.language_model."):        # checkpoints written from the vision-language wrapper
+        # checkpoints written from the vision-language wrapper nest the decoder under one or more `language_model.`
+        while name.startswith("model.language_model."):
             name = "model." + name[len("model.language_model."):]
         name = name.replace(".mlp.shared_expert.", ".mlp.shared_experts.")
         if name.endswith(".mlp.shared_expert_gate.weight"):
@@ -270,3 +271,33 @@ class Qwen3NextCausalLM(DenseCausalLM):
                 "Qwen3_5MoeForCausalLM")
 def build_qwen3_next(args, dtype, device, ps):
     return Qwen3NextCausalLM(args, dtype, device, ps)
+
+
+class Qwen3_5ForConditionalGeneration(Qwen3NextCausalLM):
+    """Qwen3.5 with its vision tower (the Qwen3-VL tower without deepstack mergers); the decoder's full
+    attention layers take the interleaved 3-axis rotary table, the linear layers need no positions."""
+    mrope_interleaved = True
+
+    def __init__(self, args, dtype=torch.bfloat16, device="cpu", ps=None):
+        super().__init__(args, dtype, device, ps)
+        from .qwen_vl import VisionTowerV3
+        self.visual = self.add_module("visual", VisionTowerV3(args.vision_config or {}, dtype, device))
+        half = self.args.rotary_dim // 2
+        self.mrope_section = list(args.mrope_section) or [half - 2 * (half // 3), half // 3, half // 3]
+
+    def encode_images(self, pixel_values, grid_thw):
+        return self.visual(pixel_values.to(self.device), grid_thw)
+
+    @staticmethod
+    def remap_weight(name, w):
+        out = []
+        for n, t in Qwen3NextCausalLM.remap_weight(name, w):
+            out.append((n[len("model."):] if n.startswith("model.visual.") else n, t))
+        return out
+
+
+@register_model("qwen3_5", "qwen3_5_moe", "Qwen3_5ForConditionalGeneration", "Qwen3_5MoeForConditionalGeneration")
+def build_qwen3_5_vl(args, dtype, device, ps):
+    if not args.vision_config:
+        return Qwen3NextCausalLM(args, dtype, device, ps)
+    return Qwen3_5ForConditionalGeneration(args, dtype, device, ps)
