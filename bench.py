@@ -1,21 +1,36 @@
 #!/usr/bin/env python
-"""Headline serving benchmark: output tokens/s of a Qwen3-8B-shaped bf16 decoder under the closed-loop
-load named in BASELINE.json (1024 synthetic requests, input 1024, output 512 with ignore_eos, 256
-concurrent, paged KV with block 16, CUDA graphs for decode) at TP = --gpus.
+"""Serving benchmark: output tokens/s, p50 TTFT and p50 TPOT of the closed-loop workloads of
+BASELINE.json on N GPUs of one node.
 
-    python bench.py --gpus 1                      # whole workload (default)
-    python bench.py --gpus 1 --steps 200 --warmup 5
+    python bench.py --gpus 1                        # config 2, whole workload (1024 requests)
+    python bench.py --gpus 1 --steps 20 --warmup 5  # config 2, K steps of the steady state
+    python bench.py --gpus 8 --config 3 --steps 20  # Qwen3-32B shape, chunked 2048-token prefill
+    python bench.py --gpus 8 --config 4 --steps 20  # Qwen3-30B-A3B shape, EP + DP attention
 
-A "step" is one engine iteration (one scheduled batch -> one forward pass -> one sampled token per
-scheduled sequence).  Without --steps the whole 1024-request workload is timed and `steps` reports
-how many engine steps it took; with --steps K exactly the first K engine steps of the workload
-are timed.  Timing is CUDA events around the step loop, bracketed by barrier + synchronize, max over
-ranks.  The `e2e` block repeats the workload through the public API (`LLM.generate`) and times it
-with the host clock; every step of both runs copies its inputs from pinned host memory and reads
-the sampled tokens back.
+Workload (config 2): Qwen3-8B-shaped bf16 decoder, random-init weights, 1024 requests of uniform
+random token ids, input 1024 / output 512 with ignore_eos, at most 256 requests in flight (a closed
+loop: a finished request admits the next one), paged KV with block 16, CUDA graphs, TP = --gpus.
+The scheduler mixes decode rows and prompt chunks in one step (decode_first: every running sequence
+decodes, the rest of the token budget goes to prompt chunks), so a step costs one launch of one graph.
 
-`--impl reference` is the arm for the unmodified upstream engine; it cannot be installed offline
- so that arm prints its `unavailable` line.
+A "step" is one engine iteration: one scheduled batch -> one forward pass -> one sampled token per
+scheduled sequence.  Without --steps the whole workload is timed from a cold queue.  With --steps K
+exactly K steps of the workload's STEADY STATE are timed: a closed loop with requests of one length
+settles into a regime where, per step, every one of the 256 sequences decodes and 256/512 = 1/2 of a
+request finishes and is replaced, i.e. one 512-token prompt chunk per step.  The set-up (untimed)
+builds that regime directly: 256 sequences whose remaining output lengths are staggered 2, 4, ... 512
+(their prompts carry the tokens "generated so far", so KV lengths are those of requests in mid
+flight).  Then W warm-up steps and K timed steps run it; finished requests are replaced by fresh
+1024-token requests inside the window.  Timing is CUDA events around the step loop, bracketed by
+barrier + synchronize, max over ranks.  TTFT / TPOT are host clock: submission -> first token
+on the host, and the mean gap between a request's tokens.
+
+The `e2e` block runs the same kind of requests (same shape, same concurrency, full output length)
+through the public API (`LLM.generate`) on the host clock; every step of both runs copies its inputs
+from pinned host memory and reads the sampled tokens back.
+
+`--impl reference` is the arm for the unmodified upstream engine; it cannot be installed offline,
+so that arm prints its `unavailable` line.
 """
 from __future__ import annotations
 
@@ -32,6 +47,16 @@ REF_UNAVAILABLE = ("reference cannot be installed offline: its setup.py rejects 
                    "commands and every third_party submodule (brpc, cutlass, Mooncake, ...) is empty; "
                    "the build also needs vcpkg, Rust crates and FlashInfer AOT modules from the network")
 
+# name -> (model preset, input_len, output_len, concurrency, requests, prompt chunk, parallelism)
+CONFIGS = {
+    "2": dict(model="qwen3-8b", input_len=1024, output_len=512, concurrency=256, requests=1024, chunk=512,
+              parallelism="tp"),
+    "3": dict(model="qwen3-32b", input_len=4096, output_len=256, concurrency=64, requests=256, chunk=2048,
+              parallelism="tp"),
+    "4": dict(model="qwen3-30b-a3b", input_len=2048, output_len=512, concurrency=512, requests=1024, chunk=2048,
+              parallelism="ep"),
+}
+
 
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
@@ -40,7 +65,7 @@ class ClockSampler:
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index=0, period_ms=200):
+    def __init__(self, gpu_index=0, period_ms=100):
         self.rows = []
         self.proc = None
         self.gpu = gpu_index
@@ -95,14 +120,42 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def make_requests(n, input_len, vocab, seed):
+def make_requests(n, length, vocab, seed):
     import torch
     g = torch.Generator().manual_seed(seed)
     # token ids live in pinned host memory: the engine's per-step H2D copy starts from them
-    ids = torch.randint(0, vocab, (n, input_len), generator=g, dtype=torch.int64)
+    ids = torch.randint(0, vocab, (n, length), generator=g, dtype=torch.int64)
     if torch.cuda.is_available():
         ids = ids.pin_memory()
     return ids
+
+
+def p50(xs):
+    xs = [x for x in xs if x is not None]
+    return statistics.median(xs) if xs else None
+
+
+class Tracker:
+    """Host-side request timing: submission, first token, last token, token count."""
+
+    def __init__(self):
+        self.t_submit, self.t_first, self.t_last, self.n_tok = {}, {}, {}, {}
+
+    def submit(self, rid, now):
+        self.t_submit[rid] = now
+
+    def token(self, rid, now):
+        if rid not in self.t_first:
+            self.t_first[rid] = now
+            self.n_tok[rid] = 0
+        self.t_last[rid] = now
+        self.n_tok[rid] += 1
+
+    def ttft_ms(self, since=0.0):
+        return p50([(self.t_first[r] - t) * 1e3 for r, t in self.t_submit.items() if r in self.t_first and t >= since])
+
+    def tpot_ms(self):
+        return p50([(self.t_last[r] - self.t_first[r]) * 1e3 / (n - 1) for r, n in self.n_tok.items() if n > 1])
 
 
 def run(args):
@@ -112,79 +165,138 @@ def run(args):
     from xllm_b200 import LLM, SamplingParams, ops
     from xllm_b200.parallel.state import init_parallel
 
+    cfg = CONFIGS[args.config]
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    ps = init_parallel() if world > 1 else None
+    ep = cfg["parallelism"] == "ep" and world > 1
+    ps = None
+    if world > 1:
+        ps = init_parallel(dp_size=world, ep_size=world) if ep else init_parallel()
     rank = ps.rank if ps else 0
     dev = ps.device if ps else torch.device("cuda", 0)
     torch.cuda.set_device(dev)
 
-    max_len = args.input_len + args.output_len + 16
-    llm = LLM(args.model, devices=str(dev), dtype="bfloat16", block_size=args.block_size,
-              max_seqs_per_batch=args.concurrency, max_tokens_per_batch=args.max_tokens_per_batch,
-              max_model_len=max_len, enable_prefix_cache=False, enable_chunked_prefill=True,
-              enable_schedule_overlap=not args.no_overlap, enable_graph=not args.no_graph,
-              policy="prefill_first", random_weights=True, parallel_state=ps,
-              max_memory_utilization=args.max_memory_utilization, num_blocks=args.num_blocks)
+    in_len, out_len = args.input_len or cfg["input_len"], args.output_len or cfg["output_len"]
+    conc_total = args.concurrency or cfg["concurrency"]
+    n_req_total = args.requests or cfg["requests"]
+    chunk = args.chunk or cfg["chunk"]
+    # with data-parallel attention every rank serves its own share of the requests
+    conc = conc_total // world if ep else conc_total
+    n_req = n_req_total // world if ep else n_req_total
+    budget = args.max_tokens_per_batch or (conc + chunk)
+    max_len = in_len + out_len + 16
+    llm = LLM(args.model or cfg["model"], devices=str(dev), dtype="bfloat16", block_size=args.block_size,
+              max_seqs_per_batch=conc, max_tokens_per_batch=max(budget, 4096 if args.steps > 0 else budget),
+              max_tokens_per_chunk_for_prefill=chunk, max_model_len=max_len, enable_prefix_cache=False,
+              enable_chunked_prefill=True, enable_schedule_overlap=not args.no_overlap,
+              enable_graph=not args.no_graph, policy="decode_first", random_weights=True, parallel_state=ps,
+              max_memory_utilization=args.max_memory_utilization, num_blocks=args.num_blocks,
+              dp_size=world if ep else 1, ep_size=world if ep else 1)
     eng = llm.engine
     vocab = eng.args.vocab_size
+    sched = eng.scheduler
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def submit(prefix, ids_pinned, out_len):
-        for i in range(ids_pinned.shape[0]):
-            eng.add_request(f"{prefix}-{i}", ids_pinned[i].tolist(), temperature=0.0, max_tokens=out_len,
-                            ignore_eos=True, offline=True)
+    def unfinished():
+        return eng.dp_has_unfinished() if ep else eng.has_unfinished()
 
-    # ---------------------------------------------------------------- warm-up (untimed)
-    eng.runner.warmup([b for b in eng.runner.buckets if b in (args.concurrency,)] or None)
-    warm = make_requests(min(8, args.concurrency), min(args.input_len, 256), vocab, 1)
-    submit("warm", warm, max(2, args.warmup))
-    wsteps = 0
-    while eng.has_unfinished():
-        eng.step()
-        wsteps += 1
-    eng.drain()
-    while wsteps < args.warmup:  # at least W warm-up steps
-        submit(f"warm{wsteps}", warm[:1], 2)
-        while eng.has_unfinished():
-            eng.step()
-            wsteps += 1
-    barrier()
+    track = Tracker()
+    counters = {"tokens": 0, "in_flight": 0, "cursor": 0}
 
-    # ---------------------------------------------------------------- timed run (device clock)
-    reqs = make_requests(args.requests, args.input_len, vocab, 0)
-    total_target = args.steps if args.steps > 0 else 1 << 60
-    out_tokens = 0
-    cursor = 0
-    in_flight = 0
+    def add(rid, ids, max_tokens):
+        eng.add_request(rid, ids, temperature=0.0, max_tokens=max_tokens, ignore_eos=True, offline=True)
+        track.submit(rid, time.perf_counter())
+        counters["in_flight"] += 1
+
+    def step():
+        evs = eng.step()
+        now = time.perf_counter()
+        for ev in evs:
+            if ev.token >= 0:
+                counters["tokens"] += 1
+                track.token(ev.request_id, now)
+            if ev.request_finished:
+                counters["in_flight"] -= 1
+        return evs
+
+    reqs = make_requests(n_req, in_len, vocab, 100 + rank)
 
     def submit_more():
-        nonlocal cursor, in_flight
-        while cursor < args.requests and in_flight < args.concurrency:
-            eng.add_request(f"r-{cursor}", reqs[cursor].tolist(), temperature=0.0, max_tokens=args.output_len,
-                            ignore_eos=True, offline=True)
-            cursor += 1
-            in_flight += 1
+        while counters["cursor"] < n_req and counters["in_flight"] < conc:
+            i = counters["cursor"]
+            add(f"r-{i}", reqs[i].tolist(), out_len)
+            counters["cursor"] += 1
 
+    # ---------------------------------------------------------------- set-up (untimed)
+    window = args.steps > 0
+    wsteps = 0
+    if window:
+        # the steady state, built directly: sequence j has out_len - r_j tokens behind it and r_j to go
+        sched.reconfigure("prefill_first", max(budget, 4096), conc, 0)
+        rem = [max(1, (j + 1) * out_len // conc) for j in range(conc)]
+        cohort = make_requests(conc, in_len + out_len, vocab, 7 + rank)
+        for j in range(conc):
+            add(f"c-{j}", cohort[j, : in_len + out_len - rem[j]].tolist(), rem[j] + 1)
+        while sched.num_waiting > 0 or sched.num_prefilling > 0:
+            step()
+        for ev in eng.drain():
+            if ev.request_finished:
+                counters["in_flight"] -= 1
+        sched.reconfigure("decode_first", budget, conc, chunk)
+        counters["tokens"] = 0
+    else:
+        # graphs and kernels warm, nothing of the workload started
+        warm = make_requests(min(8, conc), min(in_len, 256), vocab, 1)
+        for i in range(warm.shape[0]):
+            add(f"w-{i}", warm[i].tolist(), max(4, args.warmup))
+        while unfinished():
+            step()
+            wsteps += 1
+        eng.drain()
+        eng.runner.warmup([conc], prefill_tokens=[t for t in eng.runner.prefill_buckets if t >= min(chunk, budget - conc)][:1])
+        counters["tokens"] = 0
+        counters["in_flight"] = 0
+    barrier()
+    if window:
+        submit_more()
+        while wsteps < args.warmup:       # W steps of the regime that is timed (captures its graphs)
+            step()
+            submit_more()
+            wsteps += 1
+        barrier()
+
+    # the window starts with nothing in flight: tokens of earlier steps are accounted before it
+    now = time.perf_counter()
+    for ev in eng.drain():
+        if ev.token >= 0:
+            counters["tokens"] += 1
+            track.token(ev.request_id, now)
+        if ev.request_finished:
+            counters["in_flight"] -= 1
+    if window:
+        track.__init__()              # TTFT / TPOT of the window only
+    if args.profile:
+        profile_steps(eng, step, submit_more, args.profile, rank)
+
+    # ---------------------------------------------------------------- timed run (device clock)
     sampler = ClockSampler(dev.index or 0)
-    launches0, replays0 = ops.launches(), eng.runner.graph_replays
+    launches0, glaunch0, replays0 = ops.launches(), eng.runner.graph_launches, eng.runner.graph_replays
     h2d0, d2h0 = eng.runner.h2d_bytes, eng.runner.d2h_bytes
+    tok0 = counters["tokens"]
+    t_window = time.perf_counter()
     barrier()
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     steps = 0
+    total_target = args.steps if window else 1 << 60
     submit_more()
-    while steps < total_target and (eng.has_unfinished() or cursor < args.requests):
-        for ev in eng.step():
-            if ev.token >= 0:
-                out_tokens += 1
-            if ev.request_finished:
-                in_flight -= 1
+    while steps < total_target and (unfinished() or counters["cursor"] < n_req):
+        step()
         steps += 1
         submit_more()
     e1.record()
@@ -192,37 +304,46 @@ def run(args):
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
     # tokens of the step still in flight (overlap mode) belong to the timed region as well
+    now = time.perf_counter()
     for ev in eng.drain():
         if ev.token >= 0:
-            out_tokens += 1
-    replays = eng.runner.graph_replays - replays0
-    per_replay = max(eng.runner.graph_launches_per_replay.values()) if eng.runner.graph_launches_per_replay else 0
-    gpu_launches = (ops.launches() - launches0) + replays * per_replay
+            counters["tokens"] += 1
+            track.token(ev.request_id, now)
+    out_tokens = counters["tokens"] - tok0
+    graph_replays = eng.runner.graph_replays - replays0
+    gpu_launches = (ops.launches() - launches0) + (eng.runner.graph_launches - glaunch0)
     h2d_step = (eng.runner.h2d_bytes - h2d0) / max(steps, 1)
     d2h_step = (eng.runner.d2h_bytes - d2h0) / max(steps, 1)
+    ttft, tpot = track.ttft_ms(since=t_window if window else 0.0), track.tpot_ms()
     if world > 1:
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+        if ep:      # every rank produced its own tokens
+            t = torch.tensor([float(out_tokens)], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+            out_tokens = int(t.item())
     value = out_tokens / (ms / 1e3)
 
     # abort whatever the K-step window left unfinished, then the end-to-end run
     if eng.has_unfinished():
-        for i in range(cursor):
+        for j in range(conc):
+            eng.abort(f"c-{j}")
+        for i in range(counters["cursor"]):
             eng.abort(f"r-{i}")
-        while eng.has_unfinished():
-            eng.step()
+    while unfinished():
+        eng.step()
+    eng.drain()
     e2e = None
     if not args.no_e2e:
-        n_e2e = args.requests if args.steps <= 0 else min(args.requests, args.concurrency)
-        reqs2 = make_requests(n_e2e, args.input_len, vocab, 2)
+        n_e2e = n_req if not window else conc
+        reqs2 = make_requests(n_e2e, in_len, vocab, 200 + rank)
         prompts = [reqs2[i] for i in range(n_e2e)]  # pinned host tensors handed to the public API
-        sp = SamplingParams(max_tokens=args.output_len if args.steps <= 0 else max(4, min(args.output_len, args.steps // 2)),
-                            temperature=0.0, ignore_eos=True)
+        sp = SamplingParams(max_tokens=out_len, temperature=0.0, ignore_eos=True)
         h2d0, d2h0, s0 = eng.runner.h2d_bytes, eng.runner.d2h_bytes, eng.steps
         barrier()
         t0 = time.perf_counter()
-        outs = llm.generate(prompts, sp, max_concurrency=args.concurrency)
+        outs = llm.generate(prompts, sp, max_concurrency=conc)
         barrier()
         dt = time.perf_counter() - t0
         gen = sum(o.usage.num_generated_tokens for o in outs)
@@ -230,28 +351,40 @@ def run(args):
             t = torch.tensor([dt], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dt = float(t.item())
+            if ep:
+                t = torch.tensor([float(gen)], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.SUM)
+                gen = int(t.item())
         nst = max(eng.steps - s0, 1)
-        e2e = {"value": gen / dt, "unit": "output tok/s", "requests": n_e2e,
-               "output_len": sp.max_tokens, "seconds": dt, "steps": nst,
+        e2e = {"value": gen / dt, "unit": "output tok/s", "requests": n_e2e * (world if ep else 1),
+               "output_len": out_len, "seconds": dt, "steps": nst,
+               "ttft_p50_ms": p50([m["ttft_ms"] for m in (o.metrics for o in outs) if m]),
+               "tpot_p50_ms": p50([m["tpot_ms"] for m in (o.metrics for o in outs) if m]),
                "h2d_bytes_per_step": (eng.runner.h2d_bytes - h2d0) / nst,
                "d2h_bytes_per_step": (eng.runner.d2h_bytes - d2h0) / nst}
 
     if rank == 0:
+        name = args.model or cfg["model"]
+        par = (f"ep{world}+dp{world}" if ep else f"tp{world}")
         line = {
             "metric": "output tok/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": steps,
-            "warmup": wsteps, "ms_per_step": ms / max(steps, 1), "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "impl": "xllm_b200",
-            "config": {"model": f"{args.model} (random-init, Qwen3-8B shape)" if args.model == "qwen3-8b" else args.model,
-                       "requests": args.requests, "input_len": args.input_len, "output_len": args.output_len,
-                       "concurrency": args.concurrency, "global_batch": args.concurrency,
-                       "seq_len": args.input_len + args.output_len, "block_size": args.block_size,
-                       "parallelism": f"tp{world}", "cuda_graphs": not args.no_graph,
-                       "schedule_overlap": not args.no_overlap,
-                       "window": "whole workload" if args.steps <= 0 else f"first {steps} engine steps",
-                       "l2": "inputs larger than L2: every step streams the 16 GB weights / the KV cache",
+            "warmup": wsteps if not window else args.warmup, "ms_per_step": ms / max(steps, 1),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "impl": "xllm_b200", "ttft_p50_ms": ttft, "tpot_p50_ms": tpot,
+            "config": {"name": f"BASELINE.json config #{args.config}",
+                       "model": f"{name} (random-init weights of that architecture)",
+                       "requests": n_req_total, "input_len": in_len, "output_len": out_len,
+                       "concurrency": conc_total, "global_batch": conc_total, "seq_len": in_len + out_len,
+                       "block_size": args.block_size, "parallelism": par, "cuda_graphs": not args.no_graph,
+                       "schedule_overlap": not args.no_overlap, "policy": "decode_first",
+                       "tokens_per_step_budget": budget, "prefill_chunk": chunk,
+                       "window": ("whole workload from a cold queue" if not window else
+                                  f"{steps} steps of the steady state of the closed loop: every step decodes the "
+                                  f"{conc_total} running sequences and prefills one {chunk}-token prompt chunk"),
+                       "l2": "inputs larger than L2: every step streams the weights and the KV cache of all running "
+                             "sequences (tens of GB)",
                        "output_tokens": out_tokens, "kv_blocks": eng.num_blocks},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": int(gpu_launches),
+            "clocks": clocks, "e2e": e2e, "gpu_launches": int(gpu_launches), "graph_replays": int(graph_replays),
             "h2d_bytes_per_step": h2d_step, "d2h_bytes_per_step": d2h_step,
         }
         print(json.dumps(line), flush=True)
@@ -265,24 +398,55 @@ def run(args):
         os._exit(0)
 
 
+def profile_steps(eng, step, submit_more, n, rank):
+    """Per-kernel device time of n steps of the regime about to be timed (CUPTI activity records through
+    the PyTorch profiler), printed to stderr by rank 0.  Runs before the timed region, never inside it."""
+    import collections
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(n):
+            step()
+            submit_more()
+        torch.cuda.synchronize()
+    eng.drain()
+    per = collections.defaultdict(lambda: [0.0, 0])
+    total = 0.0
+    for ev in prof.events():
+        dt = getattr(ev, "device_time", 0) or getattr(ev, "cuda_time", 0)
+        if dt and ev.device_type is not None and "cuda" in str(ev.device_type).lower():
+            per[ev.name][0] += dt
+            per[ev.name][1] += 1
+            total += dt
+    if rank == 0:
+        print(f"profile: {n} steps, device busy {total / 1e3 / n:.2f} ms/step", file=sys.stderr)
+        for name, (us, k) in sorted(per.items(), key=lambda kv: -kv[1][0])[:24]:
+            print(f"{us / 1e3 / n:8.3f} ms/step {100 * us / total:5.1f}%  n/step {k / n:7.1f}  avg {us / k:8.1f} us  "
+                  f"{name[:100]}", file=sys.stderr)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=0, help="engine steps to time; 0 = the whole workload")
+    ap.add_argument("--steps", type=int, default=0, help="steady-state engine steps to time; 0 = the whole workload")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="xllm_b200", choices=["xllm_b200", "ours", "reference"])
-    ap.add_argument("--model", default="qwen3-8b")
-    ap.add_argument("--requests", type=int, default=1024)
-    ap.add_argument("--input-len", type=int, default=1024)
-    ap.add_argument("--output-len", type=int, default=512)
-    ap.add_argument("--concurrency", type=int, default=256)
+    ap.add_argument("--config", default="2", choices=sorted(CONFIGS), help="BASELINE.json config number")
+    ap.add_argument("--model", default="")
+    ap.add_argument("--requests", type=int, default=0)
+    ap.add_argument("--input-len", type=int, default=0)
+    ap.add_argument("--output-len", type=int, default=0)
+    ap.add_argument("--concurrency", type=int, default=0)
+    ap.add_argument("--chunk", type=int, default=0, help="prompt tokens per chunk")
     ap.add_argument("--block-size", type=int, default=16)
-    ap.add_argument("--max-tokens-per-batch", type=int, default=16384)
+    ap.add_argument("--max-tokens-per-batch", type=int, default=0)
     ap.add_argument("--max-memory-utilization", type=float, default=0.9)
     ap.add_argument("--num-blocks", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--profile", type=int, default=0, help="print a per-kernel breakdown of this many steps first")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

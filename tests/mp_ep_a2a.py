@@ -70,13 +70,9 @@ def main():
 
     ta, tr = timeit(a2a), timeit(replicate)
     assert comm.error_status() == 0
-    dist.barrier()
-    if r == 0:
-        print(f"EP_A2A_OK world={W} E={E} T/rank={T}: a2a {ta * 1e3:.1f} us, replicate+all-reduce {tr * 1e3:.1f} us", flush=True)
-    torch.cuda.synchronize()
-    sys.stdout.flush()
-    os._exit(0)
+    return f"EP_A2A_OK world={W} E={E} T/rank={T}: a2a {ta * 1e3:.1f} us, replicate+all-reduce {tr * 1e3:.1f} us"
 
 
 if __name__ == "__main__":
-    main()
+    from mp_common import guarded
+    guarded(main)

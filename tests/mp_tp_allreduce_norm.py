@@ -55,11 +55,9 @@ def main():
     dist.all_reduce(tot)
     assert torch.allclose(y.float(), tot, atol=0.06, rtol=0.02)
     assert comm.error_status() == 0
-    dist.barrier()
-    if ps.rank == 0:
-        print("ALLREDUCE_NORM_OK multimem=%d world=%d" % (int(comm.mc_base != 0), ps.world_size), flush=True)
-    dist.destroy_process_group()
+    return "ALLREDUCE_NORM_OK multimem=%d world=%d" % (int(comm.mc_base != 0), ps.world_size)
 
 
 if __name__ == "__main__":
-    main()
+    from mp_common import guarded
+    guarded(main)

@@ -89,11 +89,9 @@ def main():
     assert rel < 0.1 and same >= 0.8, (rel, same, prefix)
     assert sum(prefix) >= 4 * len(prompts), (prefix, base, got)
     assert ps.comm.error_status() == 0
-    dist.barrier()
-    if ps.rank == 0:
-        print("TP_ENGINE_OK", "moe-ep-a2a" if moe else "dense", flush=True)
-    dist.destroy_process_group()
+    return "TP_ENGINE_OK " + ("moe-ep-a2a" if moe else "dense")
 
 
 if __name__ == "__main__":
-    main()
+    from mp_common import guarded
+    guarded(main)

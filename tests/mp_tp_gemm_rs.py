@@ -94,18 +94,13 @@ def main():
     tf, tb = timeit(fused), timeit(baseline)
     tg, tbar = timeit(gemm_only), timeit(barrier_fused)
     assert comm.error_status() == 0
-    dist.barrier()
-    if r == 0:
-        flops = 2.0 * T * H * K
-        link_bytes = (W - 1) / W * T * H * 2 * 2  # scatter of partials out + gather of normalised rows in
-        print(f"GEMM_RS_OK world={W} T={T} K={K}: fused {tf * 1e3:.1f} us, cublas+nccl+norm {tb * 1e3:.1f} us "
+    flops = 2.0 * T * H * K
+    link_bytes = (W - 1) / W * T * H * 2 * 2  # scatter of partials out + gather of normalised rows in
+    return (f"GEMM_RS_OK world={W} T={T} K={K}: fused {tf * 1e3:.1f} us, cublas+nccl+norm {tb * 1e3:.1f} us "
               f"local gemm alone {tg * 1e3:.1f} us, gemm + barrier all-reduce+norm kernel {tbar * 1e3:.1f} us "
-              f"(gemm alone at 1.6 PF: {flops / 1.6e15 * 1e6:.1f} us, link at 770 GB/s: {link_bytes / 770e9 * 1e6:.1f} us)",
-              flush=True)
-    torch.cuda.synchronize()
-    sys.stdout.flush()
-    os._exit(0)
+              f"(gemm alone at 1.6 PF: {flops / 1.6e15 * 1e6:.1f} us, link at 770 GB/s: {link_bytes / 770e9 * 1e6:.1f} us)")
 
 
 if __name__ == "__main__":
-    main()
+    from mp_common import guarded
+    guarded(main)

@@ -87,3 +87,48 @@ def _hf_names(model):
             yield base + "up_proj.weight", u
         else:
             yield n, t
+
+
+def test_mixed_step_graphs_and_in_graph_sampling():
+    """Steps that carry prompt chunks replay a graph of a padded shape (decode bucket x prompt-token
+    bucket) with the sampler inside; the tokens equal those of the eager engine, greedy and sampled."""
+    prompts = _prompts(n=10, seed=3)
+    for sp in (SamplingParams(max_tokens=20, temperature=0.0, ignore_eos=True),
+               SamplingParams(max_tokens=20, temperature=0.8, top_k=40, top_p=0.9, seed=11, ignore_eos=True, logprobs=True)):
+        base_llm = _llm(enable_graph=False, policy="decode_first", max_tokens_per_batch=144)
+        base = base_llm.generate(prompts, sp, max_concurrency=6)
+        llm = _llm(enable_graph=True, policy="decode_first", max_tokens_per_batch=144, enable_schedule_overlap=True)
+        got = llm.generate(prompts, sp, max_concurrency=6)
+        r = llm.engine.runner
+        mixed = [k for k in r.graphs if k[1] > 0]
+        assert mixed, "no step with prompt chunks was replayed from a graph"
+        assert all(k[3] == ("greedy" if sp.temperature == 0 else "sample") for k in r.graphs)
+        agree = sum(a.outputs[0].token_ids == b.outputs[0].token_ids for a, b in zip(base, got))
+        if sp.temperature == 0:
+            assert agree >= len(prompts) - 2, agree
+        else:
+            # a sampled stream forks as soon as a different GEMM tiling moves a probability across the
+            # drawn number; the first token (same prompt, same random stream) must agree, and the graph
+            # engine must reproduce itself exactly
+            first = sum(a.outputs[0].token_ids[0] == b.outputs[0].token_ids[0] for a, b in zip(base, got))
+            assert first >= len(prompts) - 2, first
+            llm2 = _llm(enable_graph=True, policy="decode_first", max_tokens_per_batch=144, enable_schedule_overlap=True)
+            again = llm2.generate(prompts, sp, max_concurrency=6)
+            assert [o.outputs[0].token_ids for o in again] == [o.outputs[0].token_ids for o in got]
+        if sp.logprobs:
+            for a, b in zip(base, got):
+                if a.outputs[0].token_ids == b.outputs[0].token_ids:
+                    assert torch.allclose(torch.tensor(a.outputs[0].logprobs), torch.tensor(b.outputs[0].logprobs), atol=0.15)
+
+
+def test_top_logprobs_and_penalties_use_the_logits_graph():
+    sp = SamplingParams(max_tokens=6, temperature=0.7, seed=3, logprobs=True, top_logprobs=4, repetition_penalty=1.1,
+                        ignore_eos=True)
+    llm = _llm(enable_graph=True)
+    outs = llm.generate(_prompts(n=3, seed=5), sp)
+    assert all(k[3] == "logits" for k in llm.engine.runner.graphs)
+    for o in outs:
+        so = o.outputs[0]
+        assert len(so.top_logprobs) == len(so.token_ids) == 6
+        for alts in so.top_logprobs:
+            assert len(alts) == 4 and all(alts[i][1] >= alts[i + 1][1] for i in range(3))

@@ -290,3 +290,73 @@ def test_kernels_do_not_write_outside_their_outputs():
                     torch.rand(B, nv, device=dev, generator=g0), out=out.view(B, nv, dv))
     torch.cuda.synchronize()
     assert intact(buf, B * nv) and bool((state[0] == 777.0).all()) and bool((state[-1] == 777.0).all())
+
+
+@pytest.mark.parametrize("tokens,hidden", [(3, 256), (129, 2048), (40, 4096), (9, 7168), (2, 16384)])
+def test_rmsnorm_row_groups(tokens, hidden):
+    """Every thread-group width of the row kernels (32 / 64 / 128 / 256 threads per row), token counts
+    that do not fill the last CTA, strided input, and rows the kernel must not touch."""
+    torch.manual_seed(3)
+    big = torch.randn(tokens + 2, hidden + 64, device=DEV, dtype=torch.bfloat16)
+    x = big[1:-1, :hidden]                                   # row stride != hidden
+    w = (torch.randn(hidden, device=DEV) * 0.1 + 1).to(torch.bfloat16)
+    out = torch.full((tokens + 2, hidden), 7.0, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(tokens, hidden, device=DEV, dtype=torch.bfloat16)
+    res0 = res.clone()
+    ops.rmsnorm(x, w, 1e-6, residual=res, out=out[1:-1])
+    yr, rr = ref.rmsnorm(x, w, 1e-6, residual=res0)
+    _close(res, rr, 1e-2)
+    _close(out[1:-1], yr, 3e-2)
+    assert bool((out[0] == 7).all()) and bool((out[-1] == 7).all())   # canary rows
+
+
+@pytest.mark.parametrize("tokens,hidden", [(5, 512), (70, 4096), (3, 7168)])
+def test_rmsnorm_group_fp8(tokens, hidden):
+    """RMSNorm whose output is e4m3 with one scale per (row, 128 columns)."""
+    from xllm_b200.ops import fp8 as fp8_ops
+    torch.manual_seed(4)
+    x = torch.randn(tokens, hidden, device=DEV, dtype=torch.bfloat16) * 3
+    w = (torch.randn(hidden, device=DEV) * 0.1 + 1).to(torch.bfloat16)
+    res = torch.randn_like(x)
+    res0 = res.clone()
+    q, sc = fp8_ops.rmsnorm_group_quant(x, w, 1e-6, residual=res)
+    yr, rr = ref.rmsnorm(x, w, 1e-6, residual=res0)
+    _close(res, rr, 1e-2)
+    assert q.dtype == torch.float8_e4m3fn and sc.shape == (tokens, hidden // 128)
+    deq = q.float().view(tokens, hidden // 128, 128) * sc[:, :, None]
+    want = yr.float().view(tokens, hidden // 128, 128)
+    # e4m3 has 3 mantissa bits: half an ulp is 1/16 of the value, plus the bf16 rounding of the norm
+    assert bool(((deq - want).abs() <= 0.07 * want.abs() + sc[:, :, None] * 0.6 + 2e-2).all())
+    amax = want.abs().amax(-1)
+    assert torch.allclose(sc, amax / 448.0, rtol=2e-2, atol=1e-6)
+
+
+def test_top_logprobs_and_per_row_streams():
+    torch.manual_seed(5)
+    B, V, n = 9, 5003, 5
+    logits = torch.randn(B, V, device=DEV, dtype=torch.float32) * 2
+    logits[0, 17] = logits[0, 4000] = 9.0                    # a tie: the lower index comes first
+    ids, lp = ops.top_logprobs(logits, n)
+    want_lp, want_ids = torch.log_softmax(logits, -1).topk(n, -1)
+    assert torch.allclose(lp, want_lp, atol=1e-4)
+    assert ids[0, 0].item() == 17 and ids[0, 1].item() == 4000
+    assert torch.equal(ids[1:].long(), want_ids[1:])
+    idb, lpb = ops.top_logprobs(logits.to(torch.bfloat16), n)
+    assert torch.allclose(lpb, torch.log_softmax(logits.to(torch.bfloat16).float(), -1).topk(n, -1)[0], atol=1e-3)
+    # a row's draw depends on its own (seed, offset) only: not on its row index nor on its neighbours
+    temp = torch.full((B,), 0.9, device=DEV)
+    topk = torch.full((B,), 50, device=DEV, dtype=torch.int32)
+    topp = torch.full((B,), 0.95, device=DEV)
+    seeds = torch.arange(100, 100 + B, device=DEV, dtype=torch.int64)
+    offs = torch.arange(B, device=DEV, dtype=torch.int32)
+    a, la = ops.sample(logits, temp, topk, topp, seeds=seeds, offsets=offs, want_logprob=True)
+    perm = torch.randperm(B, device=DEV)
+    b, _ = ops.sample(logits[perm].contiguous(), temp, topk, topp, seeds=seeds[perm].contiguous(),
+                      offsets=offs[perm].contiguous())
+    assert torch.equal(a[perm], b)
+    c, _ = ops.sample(logits, temp, topk, topp, seeds=seeds, offsets=offs + 1)
+    assert not torch.equal(a, c)
+    # samples come from the filtered distribution
+    probs = ref.filtered_distribution(logits.cpu(), temp.cpu(), topk.cpu(), topp.cpu())
+    assert bool((probs[torch.arange(B), a.cpu()] > 0).all())
+    assert torch.allclose(la.cpu(), torch.log(probs[torch.arange(B), a.cpu()]), atol=2e-3)

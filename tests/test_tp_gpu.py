@@ -38,6 +38,18 @@ def test_fused_allreduce_norm(multimem):
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("multimem", ["1", "0"])
+def test_oneshot_allreduce_norm_argmax_gather(multimem):
+    """One-shot fused all-reduce (+residual +RMSNorm), sharded arg-max and logits gather; eager and graph."""
+    env = {"XLLM_TP_MULTIMEM": multimem}
+    if multimem == "0":
+        env["XLLM_TP_ONESHOT_TOKENS_P2P"] = "2048"     # exercise the peer-load form at every size
+    out = _run("mp_tp_oneshot.py", min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2, env)
+    assert "ONESHOT_OK" in out
+    print(out[out.index("ONESHOT_OK"):].splitlines()[0])
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("multimem", ["1", "0"])
 def test_fused_gemm_reduce_scatter_norm(multimem):
     """tcgen05 GEMM whose epilogue pushes tiles to the owner ranks + owner-side reduce/norm/all-gather."""
     out = _run("mp_tp_gemm_rs.py", min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2, {"XLLM_TP_MULTIMEM": multimem})

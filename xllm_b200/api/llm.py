@@ -52,6 +52,8 @@ class SequenceOutput:
     token_ids: List[int] = field(default_factory=list)
     finish_reason: Optional[str] = None
     logprobs: Optional[List[float]] = None
+    # per generated token, when the request asked for top_logprobs: [(token id, logprob), ...] best first
+    top_logprobs: Optional[List[List[tuple]]] = None
 
 
 @dataclass
@@ -71,6 +73,9 @@ class RequestOutput:
     finished: bool = False
     cancelled: bool = False
     usage: Usage = field(default_factory=Usage)
+    # host-clock timing of the request: ttft_ms (submission -> first token), tpot_ms (mean gap between
+    # tokens), e2e_ms; filled by generate()
+    metrics: Dict[str, float] = field(default_factory=dict)
 
 
 class LLM:
@@ -150,6 +155,10 @@ class LLM:
         eng = self.engine
         in_flight = 0
         cursor = 0
+        import time as _time
+        t_sub: Dict[str, float] = {}
+        t_first: Dict[str, float] = {}
+        t_last: Dict[str, float] = {}
 
         def submit_some():
             nonlocal cursor, in_flight
@@ -171,16 +180,25 @@ class LLM:
                     by_id[rid].cancelled = True
                 else:
                     in_flight += 1
+                    t_sub[rid] = _time.perf_counter()
 
         submit_some()
         while eng.has_unfinished() or cursor < n:
-            for e in eng.step():
+            evs = eng.step()
+            now = _time.perf_counter()
+            for e in evs:
                 ro = by_id.get(e.request_id)
                 if ro is None:
                     continue
                 so = ro.outputs[e.seq_index]
                 if e.token >= 0:
+                    t_first.setdefault(e.request_id, now)
+                    t_last[e.request_id] = now
                     so.token_ids.append(e.token)
+                    if e.top_ids:
+                        if so.top_logprobs is None:
+                            so.top_logprobs = []
+                        so.top_logprobs.append(list(zip(e.top_ids, e.top_logprobs)))
                     if e.has_logprob:
                         if so.logprobs is None:
                             so.logprobs = []
@@ -202,6 +220,11 @@ class LLM:
                 so.text = self._decode(so.token_ids, sp.skip_special_tokens)
             ro.usage.num_generated_tokens = gen
             ro.usage.num_total_tokens = gen + ro.usage.num_prompt_tokens
+            rid = ro.request_id
+            if rid in t_first:
+                ro.metrics = {"ttft_ms": (t_first[rid] - t_sub[rid]) * 1e3,
+                              "e2e_ms": (t_last[rid] - t_sub[rid]) * 1e3,
+                              "tpot_ms": (t_last[rid] - t_first[rid]) * 1e3 / (gen - 1) if gen > 1 else None}
         return outs
 
     # ------------------------------------------------------------------ control

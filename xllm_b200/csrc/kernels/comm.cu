@@ -31,14 +31,18 @@
 // residual shard, applies RMSNorm and broadcasts the normalised rows to every rank's `out`
 // (`multimem.st` or peer stores), then runs the closing flag exchange.  There is no opening
 // barrier: an arrival from a peer already proves that the peer's earlier kernels have finished.
-#include "common.cuh"
+#include "rowops.cuh"
+#include <algorithm>
 
 namespace xllm {
 
 constexpr int kCommThreads = 256;
 constexpr int kCommMaxVec = 8;
 constexpr int kMaxRanks = 16;
-constexpr long long kFlagBudgetCycles = 4000000000LL;
+// Budget of every flag wait, in SM clock cycles (about two seconds by default).  It is a launch
+// parameter: the launchers copy this host value into the kernel parameters, and
+// xllm_comm_set_wait_budget() changes it (tests make a wait run out with a short budget).
+static long long g_wait_budget_cycles = 4000000000LL;
 
 struct TpNormParams {
   void* const* peer_bufs;     // [world] base pointers of the symmetric buffer on every rank
@@ -52,6 +56,7 @@ struct TpNormParams {
   int* err;                   // error word
   int T, H, rank, world, mode;  // mode 0: out = sum ; 1: out = rmsnorm(sum + residual) * w
   float eps;
+  long long budget;           // cycles a flag wait may take before the error word is set
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -74,7 +79,7 @@ __device__ __forceinline__ void exchange_flags(const TpNormParams& p, uint32_t e
     const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.signal_pads[p.rank]) + p.sig_off + peer;
     const long long t0 = clock64();
     while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
-      if (clock64() - t0 > kFlagBudgetCycles) {
+      if (clock64() - t0 > p.budget) {
         atomicExch(p.err, 1 + peer);
         break;
       }
@@ -118,7 +123,7 @@ __global__ void __launch_bounds__(kCommThreads) tp_allreduce_norm_kernel(TpNormP
     if (threadIdx.x == 0) {
       const long long t0 = clock64();
       while (state[1] != e0 + 1) {
-        if (clock64() - t0 > kFlagBudgetCycles) {
+        if (clock64() - t0 > p.budget) {
           atomicExch(p.err, 100);
           break;
         }
@@ -264,7 +269,7 @@ __global__ void __launch_bounds__(kCommThreads) tp_inbox_norm_kernel(TpNormParam
   if (threadIdx.x == 0) {
     const long long t0 = clock64();
     while (ld_acquire_sys(counter) < expected) {
-      if (clock64() - t0 > kFlagBudgetCycles) {
+      if (clock64() - t0 > p.budget) {
         atomicExch(p.err, 200);
         break;
       }
@@ -341,6 +346,336 @@ __global__ void __launch_bounds__(kCommThreads) tp_inbox_norm_kernel(TpNormParam
   pdl_launch_dependents();
 }
 
+
+// ------------------------------------------------------------------------------------------------
+//   xllm_tp_oneshot_norm : one-shot form of the fused all-reduce for messages of a few MB.
+//
+// Every rank reduces ALL rows itself: with the buffer bound to an NVSwitch multicast object one
+// `multimem.ld_reduce` per 16 bytes returns the sum over the ranks (the switch adds the replicas, so
+// the bytes that enter this GPU are those of one copy of the message); without it the rank reads the
+// row from every peer.  Residual add, RMSNorm and the store are local: the residual stream is
+// replicated, nothing is broadcast and there is no closing barrier.
+//   signal   CTA 0 stores the call's epoch into this rank's slot of every peer's signal pad
+//   wait     EVERY CTA polls the `world` slots of its own pad (local memory) until they reach the
+//            epoch - no CTA waits for another CTA of the grid, so the grid need not be co-resident
+//   reduce   rows are spread over thread groups (rowops.cuh): several rows per CTA
+// What makes the missing closing barrier safe: the caller alternates between two partial buffers
+// (`x_off` of consecutive calls differ).  A rank can only pass the wait of call n+1 after every rank
+// has entered call n+1, i.e. finished reading in call n; so when a rank overwrites the buffer of call
+// n (for call n+2) nobody reads it any more.
+struct TpOneShotParams {
+  void* const* peer_bufs;
+  void* const* signal_pads;
+  uint64_t mc_base;
+  int64_t x_off;              // byte offset of this call's partial buffer in the symmetric buffer
+  int64_t sig_off;            // uint32 offset of the flag slots [world] in the signal pad
+  uint32_t* state;            // local: [0] epoch of the last finished call, [1] CTA arrival counter
+  const bf16* residual_in;    // [T, H] or null (treated as zero)
+  bf16* residual_out;         // [T, H] or null; may alias residual_in
+  const bf16* weight;         // [H] or null: no normalisation, out = sum (+ residual)
+  bf16* out;                  // [T, H] local
+  int* err;
+  int T, H, rank, world;
+  float eps;
+  long long budget;
+};
+
+__device__ __forceinline__ bool wait_flags(void* const* signal_pads, int64_t sig_off, int rank, int world,
+                                           uint32_t epoch, long long budget, int* err, int code) {
+  bool ok = true;
+  if (threadIdx.x < world) {
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(signal_pads[rank]) + sig_off + threadIdx.x;
+    const long long t0 = clock64();
+    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+      if (clock64() - t0 > budget) {
+        atomicExch(err, code + (int)threadIdx.x);
+        ok = false;
+        break;
+      }
+    }
+  }
+  return ok;
+}
+
+template <int TPR>
+__global__ void __launch_bounds__(kRowThreads) tp_oneshot_norm_kernel(TpOneShotParams p) {
+  __shared__ float red[8];
+  constexpr int R = kRowThreads / TPR;
+  const int t = threadIdx.x % TPR;
+  const int nvec = p.H >> 3;
+  pdl_wait();
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.state) + 1u;
+  if (blockIdx.x == 0 && threadIdx.x < p.world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(p.signal_pads[threadIdx.x]) + p.sig_off + p.rank, epoch);
+  }
+  wait_flags(p.signal_pads, p.sig_off, p.rank, p.world, epoch, p.budget, p.err, 300);
+  __syncthreads();
+  for (int64_t row0 = (int64_t)blockIdx.x * R; row0 < p.T; row0 += (int64_t)gridDim.x * R) {
+    const int64_t row = row0 + threadIdx.x / TPR;
+    const bool active = row < p.T;
+    const int64_t row_byte = row * p.H * 2;
+    float vals[kRowMaxVec][8];
+    float ss = 0.f;
+    if (p.mc_base != 0) {
+      // all loads of the row in flight before the first use
+      uint4 raw[kRowMaxVec];
+#pragma unroll
+      for (int i = 0; i < kRowMaxVec; ++i) {
+        const int v = t + i * TPR;
+        if (active && v < nvec) raw[i] = multimem_ld_reduce_bf16x8(p.mc_base + p.x_off + row_byte + (int64_t)v * 16);
+      }
+#pragma unroll
+      for (int i = 0; i < kRowMaxVec; ++i) {
+        const int v = t + i * TPR;
+        if (active && v < nvec) unpack8(*reinterpret_cast<const bf16x8*>(&raw[i]), vals[i]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < kRowMaxVec; ++i) {
+        const int v = t + i * TPR;
+        if (active && v < nvec) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) vals[i][j] = 0.f;
+          for (int k = 0; k < p.world; ++k) {
+            // fixed order (rank 0 first) so that every rank adds the same numbers in the same order
+            const uint4 u = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.peer_bufs[k]) +
+                                                                  p.x_off + row_byte + (int64_t)v * 16));
+            float f[8];
+            unpack8(*reinterpret_cast<const bf16x8*>(&u), f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) vals[i][j] += f[j];
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kRowMaxVec; ++i) {
+      const int v = t + i * TPR;
+      if (active && v < nvec) {
+        if (p.residual_in != nullptr) {
+          float r[8];
+          unpack8(reinterpret_cast<const bf16x8*>(p.residual_in + row * p.H)[v], r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) vals[i][j] += r[j];
+        }
+        const bf16x8 nr = pack8(vals[i]);  // the residual stream is bf16: round once
+        if (p.residual_out != nullptr) reinterpret_cast<bf16x8*>(p.residual_out + row * p.H)[v] = nr;
+        unpack8(nr, vals[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+      }
+    }
+    float inv = 1.f;
+    if (p.weight != nullptr) {
+      ss = group_sum<TPR>(ss, red);
+      inv = rsqrtf(ss / (float)p.H + p.eps);
+    }
+#pragma unroll
+    for (int i = 0; i < kRowMaxVec; ++i) {
+      const int v = t + i * TPR;
+      if (active && v < nvec) {
+        float o[8];
+        if (p.weight != nullptr) {
+          float w[8];
+          unpack8(reinterpret_cast<const bf16x8*>(p.weight)[v], w);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * inv * w[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = vals[i][j];
+        }
+        reinterpret_cast<bf16x8*>(p.out + row * p.H)[v] = pack8(o);
+      }
+    }
+  }
+  // the last CTA to finish publishes the epoch for the next call of this communicator
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned prev = atomicAdd(p.state + 1, 1u);
+    if (prev == gridDim.x - 1) {
+      p.state[1] = 0u;
+      *reinterpret_cast<volatile uint32_t*>(p.state) = epoch;
+      __threadfence();
+    }
+  }
+  pdl_launch_dependents();
+}
+
+// ------------------------------------------------------------------------------------------------
+//   xllm_tp_argmax : greedy sampling over vocabulary-sharded logits without gathering them.
+//
+// One CTA per row finds the maximum of the local shard and stores (value, global index) into slot
+// [parity][rank][row] of EVERY rank's pair area (plain peer stores, 8 bytes per row and peer).  The
+// last CTA to finish runs the flag exchange (bounded) and then picks, for every row, the best pair
+// over the ranks (ties: lowest index), so all ranks write identical ids.  parity = epoch & 1: a rank
+// can be at most one call ahead of a peer that still reads the previous call's pairs.
+struct TpArgmaxParams {
+  const bf16* logits;         // [B, Vs] local shard
+  int64_t row_stride;
+  void* const* peer_bufs;
+  void* const* signal_pads;
+  int64_t pair_off;           // byte offset of the pair area [2][world][max_rows] x 8 bytes
+  int64_t sig_off;
+  uint32_t* state;            // [0] epoch, [1] CTA arrival counter
+  int64_t* out_ids;           // [B]
+  int* err;
+  int B, Vs, vocab_start, max_rows, rank, world;
+  long long budget;
+};
+
+__global__ void __launch_bounds__(256) tp_argmax_kernel(TpArgmaxParams p) {
+  __shared__ float redv[32];
+  __shared__ int redi[32];
+  __shared__ int s_last;
+  const int row = blockIdx.x;
+  pdl_wait();
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.state) + 1u;
+  const int parity = (int)(epoch & 1u);
+  const bf16* x = p.logits + (int64_t)row * p.row_stride;
+  float mx = -INFINITY;
+  int arg = 0x7fffffff;
+  // 8 values per 16-byte load where the row allows it
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+  const int nvec = vec_ok ? (p.Vs >> 3) : 0;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float f[8];
+    unpack8(reinterpret_cast<const bf16x8*>(x)[v], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (f[j] > mx) { mx = f[j]; arg = v * 8 + j; }
+  }
+  for (int i = nvec * 8 + threadIdx.x; i < p.Vs; i += blockDim.x) {
+    const float f = __bfloat162float(x[i]);
+    if (f > mx || (f == mx && i < arg)) { mx = f; arg = i; }
+  }
+  // block arg-max, ties to the lowest index
+  {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, mx, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ov > mx || (ov == mx && oi < arg)) { mx = ov; arg = oi; }
+    }
+    if (lane == 0) { redv[wid] = mx; redi[wid] = arg; }
+    __syncthreads();
+    const int nw = blockDim.x >> 5;
+    mx = lane < nw ? redv[lane] : -INFINITY;
+    arg = lane < nw ? redi[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, mx, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ov > mx || (ov == mx && oi < arg)) { mx = ov; arg = oi; }
+    }
+  }
+  if (threadIdx.x < p.world) {
+    const int64_t slot = ((int64_t)parity * p.world + p.rank) * p.max_rows + row;
+    int2 pr;
+    pr.x = __float_as_int(mx);
+    pr.y = arg == 0x7fffffff ? 0x7fffffff : arg + p.vocab_start;
+    *reinterpret_cast<int2*>(reinterpret_cast<uint8_t*>(p.peer_bufs[threadIdx.x]) + p.pair_off + slot * 8) = pr;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned prev = atomicAdd(p.state + 1, 1u);
+    s_last = prev == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  // every CTA of this rank has stored its pairs: tell the peers, wait for theirs
+  if (threadIdx.x < p.world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(p.signal_pads[threadIdx.x]) + p.sig_off + p.rank, epoch);
+  }
+  wait_flags(p.signal_pads, p.sig_off, p.rank, p.world, epoch, p.budget, p.err, 400);
+  __syncthreads();
+  const uint8_t* mine = reinterpret_cast<const uint8_t*>(p.peer_bufs[p.rank]) + p.pair_off;
+  for (int r = threadIdx.x; r < p.B; r += blockDim.x) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int k = 0; k < p.world; ++k) {
+      const int64_t slot = ((int64_t)parity * p.world + k) * p.max_rows + r;
+      const int2 pr = __ldcg(reinterpret_cast<const int2*>(mine + slot * 8));
+      const float v = __int_as_float(pr.x);
+      if (v > bv || (v == bv && pr.y < bi)) { bv = v; bi = pr.y; }
+    }
+    p.out_ids[r] = bi == 0x7fffffff ? 0 : bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    p.state[1] = 0u;
+    *reinterpret_cast<volatile uint32_t*>(p.state) = epoch;
+    __threadfence();
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+//   xllm_tp_gather_cols : all-gather of column shards (vocabulary-sharded logits -> full rows).
+//
+// Every rank copies its [B, Vs] shard into columns [rank * Vs, (rank + 1) * Vs) of the [B, V_pad]
+// area of EVERY rank (16-byte peer stores, or one `multimem.st` when a multicast mapping exists).  The
+// last CTA to finish runs the flag exchange, so completion of the kernel on a rank means that all
+// shards have landed in that rank's area.
+struct TpGatherParams {
+  const bf16* src;            // [B, Vs] local shard
+  int64_t src_stride;
+  void* const* peer_bufs;
+  void* const* signal_pads;
+  uint64_t mc_base;
+  int64_t dst_off;            // byte offset of the gathered area in the symmetric buffer
+  int64_t dst_stride;         // elements per gathered row (>= world * Vs)
+  int64_t sig_off;
+  uint32_t* state;
+  int* err;
+  int B, Vs, rank, world;
+  long long budget;
+};
+
+__global__ void __launch_bounds__(256) tp_gather_cols_kernel(TpGatherParams p) {
+  __shared__ int s_last;
+  pdl_wait();
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.state) + 1u;
+  const int nvec = p.Vs >> 3;
+  const int64_t total = (int64_t)p.B * nvec;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / nvec;
+    const int v = (int)(i - r * nvec);
+    const uint4 u = *reinterpret_cast<const uint4*>(p.src + r * p.src_stride + (int64_t)v * 8);
+    const int64_t off = p.dst_off + (r * p.dst_stride + (int64_t)p.rank * p.Vs + (int64_t)v * 8) * 2;
+    if (p.mc_base != 0) {
+      multimem_st_16(p.mc_base + off, u);
+    } else {
+      for (int k = 0; k < p.world; ++k) {
+        const int peer = (p.rank + k) % p.world;
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.peer_bufs[peer]) + off) = u;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned prev = atomicAdd(p.state + 1, 1u);
+    s_last = prev == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (threadIdx.x < p.world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(p.signal_pads[threadIdx.x]) + p.sig_off + p.rank, epoch);
+  }
+  wait_flags(p.signal_pads, p.sig_off, p.rank, p.world, epoch, p.budget, p.err, 500);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    p.state[1] = 0u;
+    *reinterpret_cast<volatile uint32_t*>(p.state) = epoch;
+    __threadfence();
+  }
+}
+
 }  // namespace xllm
 
 // Number of uint32 flag slots one call site needs in the signal pad.
@@ -363,7 +698,7 @@ XLLM_API int xllm_tp_allreduce_norm(const void* peer_bufs, const void* signal_pa
   p.peer_bufs = (void* const*)peer_bufs; p.signal_pads = (void* const*)signal_pads; p.mc_base = mc_base;
   p.x_off = x_off; p.out_off = out_off; p.sig_off = sig_off; p.epochs = (uint32_t*)epochs;
   p.residual = (bf16*)residual; p.weight = (const bf16*)weight; p.err = (int*)err; p.T = T; p.H = H;
-  p.rank = rank; p.world = world; p.mode = mode; p.eps = eps;
+  p.rank = rank; p.world = world; p.mode = mode; p.eps = eps; p.budget = g_wait_budget_cycles;
   tp_allreduce_norm_kernel<<<n_ctas, kCommThreads, 0, (cudaStream_t)stream>>>(p);
   return XLLM_LAUNCH_CHECK();
 }
@@ -386,7 +721,86 @@ XLLM_API int xllm_tp_inbox_norm(const void* peer_bufs, const void* signal_pads, 
   p.peer_bufs = (void* const*)peer_bufs; p.signal_pads = (void* const*)signal_pads; p.mc_base = mc_base;
   p.x_off = x_off; p.out_off = out_off; p.sig_off = sig_off; p.epochs = (uint32_t*)epochs;
   p.residual = (bf16*)residual; p.weight = (const bf16*)weight; p.err = (int*)err; p.T = T; p.H = H;
-  p.rank = rank; p.world = world; p.mode = mode; p.eps = eps;
+  p.rank = rank; p.world = world; p.mode = mode; p.eps = eps; p.budget = g_wait_budget_cycles;
   tp_inbox_norm_kernel<<<n_ctas, kCommThreads, 0, (cudaStream_t)stream>>>(p, counter_idx, expected);
+  return XLLM_LAUNCH_CHECK();
+}
+
+// Cycles a flag wait of the kernels of this file may take before it gives up and sets the error
+// word (default 4e9, about two seconds).  Returns the previous value.
+XLLM_API long long xllm_comm_set_wait_budget(long long cycles) {
+  const long long old = xllm::g_wait_budget_cycles;
+  if (cycles > 0) xllm::g_wait_budget_cycles = cycles;
+  return old;
+}
+
+// One-shot fused all-reduce (see the kernel's header comment).  x is [T, H] bf16 at byte offset x_off
+// of the symmetric buffer on every rank; consecutive calls on one communicator must use different
+// x_off.  out / residual_in / residual_out are local [T, H] tensors (residual_in and weight may be
+// null, residual_out may be null or alias residual_in).  sig_off: uint32 index of `world` flag slots
+// reserved for this kernel in the signal pad; state: 2 zero-initialised device uint32 owned by the
+// communicator.  n_ctas: any positive number (CTAs do not wait for one another).
+XLLM_API int xllm_tp_oneshot_norm(const void* peer_bufs, const void* signal_pads, uint64_t mc_base, int64_t x_off,
+                                  int64_t sig_off, void* state, const void* residual_in, void* residual_out,
+                                  const void* weight, void* out, void* err, int T, int H, int rank, int world,
+                                  float eps, int n_ctas, void* stream) {
+  using namespace xllm;
+  if (T == 0) return 0;
+  const int tpr = row_group_threads(H);
+  if (H % 8 != 0 || tpr == 0 || world > kMaxRanks || (x_off & 15) || n_ctas < 1) return (int)cudaErrorInvalidValue;
+  TpOneShotParams p;
+  p.peer_bufs = (void* const*)peer_bufs; p.signal_pads = (void* const*)signal_pads; p.mc_base = mc_base;
+  p.x_off = x_off; p.sig_off = sig_off; p.state = (uint32_t*)state; p.residual_in = (const bf16*)residual_in;
+  p.residual_out = (bf16*)residual_out; p.weight = (const bf16*)weight; p.out = (bf16*)out; p.err = (int*)err;
+  p.T = T; p.H = H; p.rank = rank; p.world = world; p.eps = eps; p.budget = g_wait_budget_cycles;
+  const int rows = kRowThreads / tpr;
+  const dim3 grid((unsigned)std::min<int64_t>(n_ctas, ((int64_t)T + rows - 1) / rows)), block(kRowThreads);
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (tpr) {
+    case 32: launch_pdl(tp_oneshot_norm_kernel<32>, grid, block, 0, s, p); break;
+    case 64: launch_pdl(tp_oneshot_norm_kernel<64>, grid, block, 0, s, p); break;
+    case 128: launch_pdl(tp_oneshot_norm_kernel<128>, grid, block, 0, s, p); break;
+    default: launch_pdl(tp_oneshot_norm_kernel<256>, grid, block, 0, s, p); break;
+  }
+  return XLLM_LAUNCH_CHECK();
+}
+
+// Greedy sampling over vocabulary shards: out_ids[r] = argmax over all ranks' shards of row r (ties:
+// lowest index), identical on every rank.  logits: local [B, Vs] bf16 (only the first Vs columns of a
+// row are looked at: pass the number of real vocabulary rows of the shard); the pair area needs
+// 2 * world * max_rows * 8 bytes at byte offset pair_off of the symmetric buffer; B <= max_rows.
+XLLM_API int xllm_tp_argmax(const void* logits, int64_t row_stride, const void* peer_bufs, const void* signal_pads,
+                            int64_t pair_off, int64_t sig_off, void* state, void* out_ids, void* err, int B, int Vs,
+                            int vocab_start, int max_rows, int rank, int world, void* stream) {
+  using namespace xllm;
+  if (B == 0) return 0;
+  if (B > max_rows || world > kMaxRanks || (pair_off & 7) || Vs < 0) return (int)cudaErrorInvalidValue;
+  TpArgmaxParams p;
+  p.logits = (const bf16*)logits; p.row_stride = row_stride; p.peer_bufs = (void* const*)peer_bufs;
+  p.signal_pads = (void* const*)signal_pads; p.pair_off = pair_off; p.sig_off = sig_off; p.state = (uint32_t*)state;
+  p.out_ids = (int64_t*)out_ids; p.err = (int*)err; p.B = B; p.Vs = Vs; p.vocab_start = vocab_start;
+  p.max_rows = max_rows; p.rank = rank; p.world = world; p.budget = g_wait_budget_cycles;
+  launch_pdl(tp_argmax_kernel, dim3(B), dim3(256), 0, (cudaStream_t)stream, p);
+  return XLLM_LAUNCH_CHECK();
+}
+
+// All-gather of column shards into every rank's [B, dst_stride] area at byte offset dst_off of the
+// symmetric buffer (see the kernel's header comment).  Vs % 8 == 0, src rows 16-byte aligned,
+// dst_off and dst_stride * 2 multiples of 16.
+XLLM_API int xllm_tp_gather_cols(const void* src, int64_t src_stride, const void* peer_bufs, const void* signal_pads,
+                                 uint64_t mc_base, int64_t dst_off, int64_t dst_stride, int64_t sig_off, void* state,
+                                 void* err, int B, int Vs, int rank, int world, void* stream) {
+  using namespace xllm;
+  if (B == 0) return 0;
+  if (Vs % 8 != 0 || (dst_off & 15) || (dst_stride % 8) || (src_stride % 8) || world > kMaxRanks)
+    return (int)cudaErrorInvalidValue;
+  TpGatherParams p;
+  p.src = (const bf16*)src; p.src_stride = src_stride; p.peer_bufs = (void* const*)peer_bufs;
+  p.signal_pads = (void* const*)signal_pads; p.mc_base = mc_base; p.dst_off = dst_off; p.dst_stride = dst_stride;
+  p.sig_off = sig_off; p.state = (uint32_t*)state; p.err = (int*)err; p.B = B; p.Vs = Vs; p.rank = rank;
+  p.world = world; p.budget = g_wait_budget_cycles;
+  const int64_t total = (int64_t)B * (Vs / 8);
+  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(296, (total + 255) / 256));
+  launch_pdl(tp_gather_cols_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, p);
   return XLLM_LAUNCH_CHECK();
 }

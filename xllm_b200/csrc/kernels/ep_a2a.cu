@@ -27,7 +27,9 @@ namespace xllm {
 constexpr int kEpMaxRanks = 16;
 constexpr int kEpMaxExperts = 512;
 constexpr int kEpTile = 128;
-constexpr long long kEpFlagBudget = 4000000000LL;
+// Budget of a flag wait in SM cycles (about two seconds by default); a launch parameter copied from
+// this host value, which xllm_ep_set_wait_budget() changes.
+static long long g_ep_wait_budget = 4000000000LL;
 
 struct EpParams {
   void* const* peer_bufs;    // [world] symmetric buffer bases
@@ -39,6 +41,7 @@ struct EpParams {
   uint32_t* epochs;          // [0] epoch of the last completed exchange
   int* err;
   int rank, world, E, E_local, H, cap_rows;
+  long long budget;
 };
 
 __device__ __forceinline__ void ep_st_release(uint32_t* p, uint32_t v) {
@@ -62,7 +65,7 @@ __device__ __forceinline__ void ep_exchange(const EpParams& p) {
     const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.signal_pads[p.rank]) + p.sig_off + peer;
     const long long t0 = clock64();
     while ((int32_t)(ep_ld_acquire(mine) - e) < 0) {
-      if (clock64() - t0 > kEpFlagBudget) {
+      if (clock64() - t0 > p.budget) {
         atomicExch(p.err, 1 + peer);
         break;
       }
@@ -191,6 +194,7 @@ static EpParams make_ep(const void* peer_bufs, const void* signal_pads, int64_t 
   p.peer_bufs = (void* const*)peer_bufs; p.signal_pads = (void* const*)signal_pads; p.cnt_off = cnt_off;
   p.recvx_off = recvx_off; p.recvy_off = recvy_off; p.sig_off = sig_off; p.epochs = (uint32_t*)epochs;
   p.err = (int*)err; p.rank = rank; p.world = world; p.E = E; p.E_local = E / world; p.H = H; p.cap_rows = cap_rows;
+  p.budget = g_ep_wait_budget;
   return p;
 }
 
@@ -252,4 +256,12 @@ XLLM_API int xllm_ep_combine(EP_COMMON_ARGS, void* out, const void* where, const
   ep_combine_kernel<<<T, 128, 0, (cudaStream_t)stream>>>(EP_MAKE, (bf16*)out, (const int32_t*)where, (const float*)w,
                                                         (const bf16*)shared_out, T, K);
   return XLLM_LAUNCH_CHECK();
+}
+
+// Cycles a flag wait of the expert-parallel kernels may take before it gives up and sets the error
+// word (default 4e9, about two seconds).  Returns the previous value.
+XLLM_API long long xllm_ep_set_wait_budget(long long cycles) {
+  const long long old = xllm::g_ep_wait_budget;
+  if (cycles > 0) xllm::g_ep_wait_budget = cycles;
+  return old;
 }

@@ -34,6 +34,10 @@ struct SampleParams {
   float* out_logprob;        // [B] or null
   int V;
   unsigned long long seed, offset;
+  // per-row random streams: seed of the row's sequence and how many draws it has made (tokens
+  // generated so far).  Null: the batch-level (seed, offset) with the row as the subsequence.
+  const unsigned long long* seeds;
+  const int32_t* offsets;
 };
 
 __device__ __forceinline__ void block_argmax(float& v, int& idx, float* redv, int* redi) {
@@ -148,7 +152,10 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
   }
   const float excl = wprefix + incl - local;
   curandStatePhilox4_32_10_t st;
-  curand_init(p.seed, (unsigned long long)row, p.offset, &st);
+  if (p.seeds != nullptr)
+    curand_init(p.seeds[row], 0ull, p.offsets ? (unsigned long long)p.offsets[row] : 0ull, &st);
+  else
+    curand_init(p.seed, (unsigned long long)row, p.offset, &st);
   const float u = curand_uniform(&st);  // (0, 1]
   const float target = u * total;
   // the owner is the first thread whose inclusive prefix reaches the target
@@ -174,6 +181,46 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
       const float e = exp2f((ldf<T>(x, c) - mx) * sc);
       p.out_logprob[row] = logf(e / total);
     }
+  }
+}
+
+// The n most likely tokens of every row with their log-probabilities under softmax(logits)
+// (Sampler::forward's top_logprobs, xllm/core/framework/sampling/sampler.cpp:166-169; the reference
+// sorts with torch.topk).  One CTA per row: max and normaliser in two passes, then n arg-max
+// passes, each restricted to the elements that come after the previous pick in the order
+// (value descending, index ascending).  n is small (<= 20 in the OpenAI API) and the row is in L2.
+template <typename T>
+__global__ void __launch_bounds__(kSampleThreads) top_logprobs_kernel(const T* logits, int64_t row_stride, int V, int n,
+                                                                      int32_t* out_ids, float* out_lp) {
+  __shared__ float red[32];
+  __shared__ float redv[32];
+  __shared__ int redi[32];
+  const int row = blockIdx.x;
+  const T* x = logits + (int64_t)row * row_stride;
+  pdl_wait();
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += kSampleThreads) mx = fmaxf(mx, ldf<T>(x, i));
+  mx = block_max(mx, red);
+  float z = 0.f;
+  for (int i = threadIdx.x; i < V; i += kSampleThreads) z += __expf(ldf<T>(x, i) - mx);
+  const float logz = logf(block_sum(z, red));
+  float pv = INFINITY;
+  int pi = -1;
+  for (int k = 0; k < n; ++k) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += kSampleThreads) {
+      const float v = ldf<T>(x, i);
+      const bool after = (v < pv) || (v == pv && i > pi);
+      if (after && (v > bv || (v == bv && i < bi))) { bv = v; bi = i; }
+    }
+    block_argmax(bv, bi, redv, redi);
+    if (threadIdx.x == 0) {
+      out_ids[(int64_t)row * n + k] = bi == 0x7fffffff ? -1 : bi;
+      out_lp[(int64_t)row * n + k] = bi == 0x7fffffff ? -INFINITY : bv - mx - logz;
+    }
+    pv = bv;
+    pi = bi;
   }
 }
 
@@ -212,9 +259,47 @@ XLLM_API int xllm_sample(const void* logits, int64_t row_stride, int dtype, int 
   p.logits = logits; p.row_stride = row_stride; p.temperature = (const float*)temperature;
   p.top_k = (const int32_t*)top_k; p.top_p = (const float*)top_p; p.out_ids = (int64_t*)out_ids;
   p.out_logprob = (float*)out_logprob; p.V = vocab; p.seed = seed; p.offset = offset;
+  p.seeds = nullptr; p.offsets = nullptr;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == 0) launch_pdl(sample_kernel<bf16>, dim3(batch), dim3(kSampleThreads), 0, s, p);
   else launch_pdl(sample_kernel<float>, dim3(batch), dim3(kSampleThreads), 0, s, p);
+  return XLLM_LAUNCH_CHECK();
+}
+
+// Same sampler with one random stream per row: seeds [batch] u64 (the row's sequence seed) and
+// offsets [batch] i32 (draws that sequence has made so far), both device arrays, so the launch does
+// not depend on host values and can be replayed from a CUDA graph.
+XLLM_API int xllm_sample_rows(const void* logits, int64_t row_stride, int dtype, int batch, int vocab,
+                              const void* temperature, const void* top_k, const void* top_p, void* out_ids,
+                              void* out_logprob, const void* seeds, const void* offsets, void* stream) {
+  using namespace xllm;
+  if (batch == 0) return 0;
+  if (seeds == nullptr) return (int)cudaErrorInvalidValue;
+  SampleParams p;
+  p.logits = logits; p.row_stride = row_stride; p.temperature = (const float*)temperature;
+  p.top_k = (const int32_t*)top_k; p.top_p = (const float*)top_p; p.out_ids = (int64_t*)out_ids;
+  p.out_logprob = (float*)out_logprob; p.V = vocab; p.seed = 0; p.offset = 0;
+  p.seeds = (const unsigned long long*)seeds; p.offsets = (const int32_t*)offsets;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == 0) launch_pdl(sample_kernel<bf16>, dim3(batch), dim3(kSampleThreads), 0, s, p);
+  else launch_pdl(sample_kernel<float>, dim3(batch), dim3(kSampleThreads), 0, s, p);
+  return XLLM_LAUNCH_CHECK();
+}
+
+// out_ids [batch, n] int32 and out_lp [batch, n] fp32: the n most likely tokens of every row and
+// their log-probabilities under softmax(logits), most likely first (ties: lowest index).
+XLLM_API int xllm_top_logprobs(const void* logits, int64_t row_stride, int dtype, int batch, int vocab, int n,
+                               void* out_ids, void* out_lp, void* stream) {
+  using namespace xllm;
+  if (batch == 0 || n == 0) return 0;
+  if (n < 0 || n > vocab) return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == 0)
+    launch_pdl(top_logprobs_kernel<bf16>, dim3(batch), dim3(kSampleThreads), 0, s, (const bf16*)logits, row_stride,
+               vocab, n, (int32_t*)out_ids, (float*)out_lp);
+  else
+    launch_pdl(top_logprobs_kernel<float>, dim3(batch), dim3(kSampleThreads), 0, s, (const float*)logits, row_stride,
+               vocab, n, (int32_t*)out_ids, (float*)out_lp);
   return XLLM_LAUNCH_CHECK();
 }
 

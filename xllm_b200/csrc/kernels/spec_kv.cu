@@ -26,6 +26,10 @@ struct VerifyParams {
   int32_t* out_len;           // [B] tokens emitted (accepted drafts + 1)
   int K, V;
   unsigned long long seed, offset;
+  // per-row random streams (null: batch-level seed with the row as sub-stream): the seed of the
+  // row's sequence and the number of tokens it has generated; a step draws at most 2 (K + 1) numbers
+  const unsigned long long* seeds;
+  const int32_t* offsets;
 };
 
 __global__ void __launch_bounds__(256) spec_verify_kernel(VerifyParams p) {
@@ -40,7 +44,12 @@ __global__ void __launch_bounds__(256) spec_verify_kernel(VerifyParams p) {
   const float* Q = p.draft_probs ? p.draft_probs + (int64_t)b * K * V : nullptr;
   const bool greedy = p.greedy ? p.greedy[b] != 0 : false;
   curandStatePhilox4_32_10_t st;
-  if (threadIdx.x == 0) curand_init(p.seed, (unsigned long long)b, p.offset, &st);
+  if (threadIdx.x == 0) {
+    if (p.seeds != nullptr)
+      curand_init(p.seeds[b], 1ull, (unsigned long long)(p.offsets ? p.offsets[b] : 0) * (2ull * (p.K + 1)), &st);
+    else
+      curand_init(p.seed, (unsigned long long)b, p.offset, &st);
+  }
   int n_out = 0;
   for (int i = 0; i <= K; ++i) {
     const float* pi = P + (int64_t)i * V;
@@ -210,6 +219,23 @@ XLLM_API int xllm_spec_verify(const void* draft_ids, const void* target_probs, c
   p.draft_ids = (const int64_t*)draft_ids; p.target_probs = (const float*)target_probs;
   p.draft_probs = (const float*)draft_probs; p.greedy = (const uint8_t*)greedy; p.out_tokens = (int64_t*)out_tokens;
   p.out_len = (int32_t*)out_len; p.K = K; p.V = V; p.seed = seed; p.offset = offset;
+  p.seeds = nullptr; p.offsets = nullptr;
+  spec_verify_kernel<<<B, 256, 0, (cudaStream_t)stream>>>(p);
+  return XLLM_LAUNCH_CHECK();
+}
+
+// Same with one random stream per row: seeds [B] u64, offsets [B] i32 (tokens generated so far).
+XLLM_API int xllm_spec_verify_rows(const void* draft_ids, const void* target_probs, const void* draft_probs,
+                                   const void* greedy, void* out_tokens, void* out_len, int B, int K, int V,
+                                   const void* seeds, const void* offsets, void* stream) {
+  using namespace xllm;
+  if (B == 0) return 0;
+  if (seeds == nullptr) return (int)cudaErrorInvalidValue;
+  VerifyParams p;
+  p.draft_ids = (const int64_t*)draft_ids; p.target_probs = (const float*)target_probs;
+  p.draft_probs = (const float*)draft_probs; p.greedy = (const uint8_t*)greedy; p.out_tokens = (int64_t*)out_tokens;
+  p.out_len = (int32_t*)out_len; p.K = K; p.V = V; p.seed = 0; p.offset = 0;
+  p.seeds = (const unsigned long long*)seeds; p.offsets = (const int32_t*)offsets;
   spec_verify_kernel<<<B, 256, 0, (cudaStream_t)stream>>>(p);
   return XLLM_LAUNCH_CHECK();
 }

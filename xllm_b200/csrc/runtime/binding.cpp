@@ -80,6 +80,29 @@ PYBIND11_MODULE(_rt, m) {
     return out;
   }, py::arg("tokens"), py::arg("block_size"), py::arg("extra") = 0);
 
+  // Byte offsets of the packed per-step input buffer for T token rows, S sequences and NS sample
+  // rows (the layout Batch.fill_packed writes; same return convention).
+  m.def("packed_layout", [](int64_t T, int64_t S, int64_t NS, int64_t bt_stride) {
+    auto al = [](int64_t x) { return (x + 15) & ~(int64_t)15; };
+    std::vector<int64_t> off(17);
+    int64_t o = 0;
+    off[0] = o; o = al(o + T * 8);
+    off[1] = o; o = al(o + T * 8);
+    off[2] = o; o = al(o + NS * 8);
+    off[3] = o; o = al(o + T * 4);
+    off[4] = o; o = al(o + S * 4);
+    off[5] = o; o = al(o + (S + 1) * 4);
+    off[6] = o; o = al(o + S * 4);
+    off[7] = o; o = al(o + NS * 4);
+    off[8] = o; o = al(o + NS * 4);
+    off[9] = o; o = al(o + NS * 4);
+    off[10] = o; o = al(o + S * bt_stride * 4);
+    off[15] = o; o = al(o + NS * 8);
+    off[16] = o; o = al(o + NS * 4);
+    off[11] = o; off[12] = T; off[13] = S; off[14] = NS;
+    return off;
+  });
+
   py::class_<SamplingParams>(m, "SamplingParams")
       .def(py::init<>())
       .def_readwrite("temperature", &SamplingParams::temperature)
@@ -119,6 +142,7 @@ PYBIND11_MODULE(_rt, m) {
       .def_readwrite("dp_size", &SchedulerConfig::dp_size)
       .def_readwrite("num_speculative_tokens", &SchedulerConfig::num_speculative_tokens)
       .def_readwrite("max_decode_batch", &SchedulerConfig::max_decode_batch)
+      .def_readwrite("max_running_seqs", &SchedulerConfig::max_running_seqs)
       .def_readwrite("hold_finished_blocks", &SchedulerConfig::hold_finished_blocks);
 
   py::enum_<PauseMode>(m, "PauseMode")
@@ -138,6 +162,7 @@ PYBIND11_MODULE(_rt, m) {
       .def_readonly("any_penalty", &Batch::any_penalty)
       .def_readonly("any_logprobs", &Batch::any_logprobs)
       .def_readonly("all_greedy", &Batch::all_greedy)
+      .def_readonly("max_top_logprobs", &Batch::max_top_logprobs)
       .def_property_readonly("n_seqs", &Batch::n_seqs)
       .def_property_readonly("n_samples", [](const Batch& b) { return (int64_t)b.sample_rows.size(); })
       .def_property_readonly("tokens", [](const Batch& b) { return to_np(b.tokens); })
@@ -163,6 +188,7 @@ PYBIND11_MODULE(_rt, m) {
       .def_property_readonly("presence_penalty", [](const Batch& b) { return to_np(b.pres_pen); })
       .def_property_readonly("repetition_penalty", [](const Batch& b) { return to_np(b.rep_pen); })
       .def_property_readonly("seeds", [](const Batch& b) { return to_np(b.seeds); })
+      .def_property_readonly("sample_offsets", [](const Batch& b) { return to_np(b.sample_offsets); })
       .def_property_readonly("seq_ids", [](const Batch& b) { return to_np(b.seq_ids); })
       // the last `max_n` tokens (prompt + generated) of sequence `i` of the batch (all when max_n <= 0)
       .def("history",
@@ -182,8 +208,13 @@ PYBIND11_MODULE(_rt, m) {
       //   block_table i32[S, bt_stride]
       // With pad_seqs > n_seqs (decode-only batches replayed from a CUDA graph) T = S = NS =
       // pad_seqs and the padding rows are inert: token 0, slot -1, kv_len 0, greedy.
+      // followed by seeds u64[NS] | sample_offsets i32[NS].
+      // With pad_prefill_tokens / pad_prefill_seqs > 0 (steps with prompt chunks replayed from a CUDA
+      // graph) the layout is fixed: pad_seqs decode rows, then pad_prefill_tokens prompt-chunk rows;
+      // pad_seqs + pad_prefill_seqs sequences; padding sequences have q_len 0 and kv_len 0.
       // Returns [off_tokens, off_positions, off_sample_rows, off_slots, off_kv_lens, off_cu_q,
-      //          off_q_lens, off_top_k, off_temperature, off_top_p, off_bt, total_bytes, T, S, NS].
+      //          off_q_lens, off_top_k, off_temperature, off_top_p, off_bt, total_bytes, T, S, NS,
+      //          off_seeds, off_sample_offsets].
       // Unique token ids and their counts over each sampled sequence (prompt + generated), padded
       // with -1 / 0 to the widest row; None when the batch has no penalties.
       .def("penalty_tokens",
@@ -211,16 +242,28 @@ PYBIND11_MODULE(_rt, m) {
              return py::make_tuple(ids, cnt);
            })
       .def("fill_packed",
-           [](const Batch& b, uintptr_t ptr, int64_t capacity, int32_t bt_stride, int32_t pad_seqs) {
-             int64_t T = b.n_tokens, S = b.n_seqs(), NS = (int64_t)b.sample_rows.size();
-             const int64_t rT = T, rS = S, rNS = NS;
-             if (pad_seqs > S) {
-               if (b.n_prefill != 0) throw std::runtime_error("padding is for decode-only batches");
-               T = S = NS = pad_seqs;
+           [](const Batch& b, uintptr_t ptr, int64_t capacity, int32_t bt_stride, int32_t pad_seqs,
+              int32_t pad_prefill_tokens, int32_t pad_prefill_seqs) {
+             // real sizes
+             const int64_t nd = b.n_decode, npf = b.n_prefill;
+             const int64_t rT = b.n_tokens, rS = b.n_seqs(), rNS = (int64_t)b.sample_rows.size();
+             const int64_t ptok = rT - nd;  // prompt-chunk token rows
+             // padded layout: decode rows [0, D), prompt-chunk rows [D, D + Q), sequences D + P
+             const bool mixed = pad_prefill_tokens > 0 || pad_prefill_seqs > 0;
+             int64_t D = nd, Q = ptok, P = npf;
+             if (mixed) {
+               D = std::max<int64_t>(pad_seqs, 0);
+               Q = pad_prefill_tokens;
+               P = pad_prefill_seqs;
+               if (nd > D || ptok > Q || npf > P) throw std::runtime_error("batch does not fit the padded layout");
+             } else if (pad_seqs > rS) {
+               if (npf != 0) throw std::runtime_error("decode padding needs a decode-only batch");
+               D = pad_seqs;
              }
+             const int64_t T = D + Q, S = D + P, NS = (mixed || D > nd) ? S : rNS;
              if (bt_stride < b.max_blocks) throw std::runtime_error("block table stride too small");
              auto al = [](int64_t x) { return (x + 15) & ~(int64_t)15; };
-             std::vector<int64_t> off(15);
+             std::vector<int64_t> off(17);
              int64_t o = 0;
              off[0] = o; o = al(o + T * 8);
              off[1] = o; o = al(o + T * 8);
@@ -233,6 +276,8 @@ PYBIND11_MODULE(_rt, m) {
              off[8] = o; o = al(o + NS * 4);
              off[9] = o; o = al(o + NS * 4);
              off[10] = o; o = al(o + S * (int64_t)bt_stride * 4);
+             off[15] = o; o = al(o + NS * 8);
+             off[16] = o; o = al(o + NS * 4);
              off[11] = o; off[12] = T; off[13] = S; off[14] = NS;
              if (o > capacity) throw std::runtime_error("staging buffer too small");
              uint8_t* base = reinterpret_cast<uint8_t*>(ptr);
@@ -247,28 +292,52 @@ PYBIND11_MODULE(_rt, m) {
              float* temp = (float*)(base + off[8]);
              float* topp = (float*)(base + off[9]);
              int32_t* bt = (int32_t*)(base + off[10]);
-             std::memcpy(tok, b.tokens.data(), rT * 8);
-             std::memcpy(pos, b.positions.data(), rT * 8);
-             std::memcpy(srow, b.sample_rows.data(), rNS * 8);
-             std::memcpy(slots, b.slots.data(), rT * 4);
-             std::memcpy(kvl, b.kv_lens.data(), rS * 4);
-             std::memcpy(cuq, b.cu_q.data(), (rS + 1) * 4);
-             std::memcpy(ql, b.q_lens.data(), rS * 4);
-             std::memcpy(topk, b.top_k.data(), rNS * 4);
-             std::memcpy(temp, b.temperature.data(), rNS * 4);
-             std::memcpy(topp, b.top_p.data(), rNS * 4);
-             for (int64_t i = rT; i < T; ++i) { tok[i] = 0; pos[i] = 0; slots[i] = -1; }
-             for (int64_t i = rS; i < S; ++i) { kvl[i] = 0; ql[i] = 1; cuq[i + 1] = cuq[i] + 1; }
-             for (int64_t i = rNS; i < NS; ++i) { srow[i] = i; topk[i] = 0; temp[i] = 0.f; topp[i] = 1.f; }
-             for (int64_t i = 0; i < rS; ++i) {
-               std::memcpy(bt + i * bt_stride, b.block_tables.data() + i * b.max_blocks, b.max_blocks * 4);
-               if (bt_stride > b.max_blocks)
-                 std::memset(bt + i * bt_stride + b.max_blocks, 0, (size_t)(bt_stride - b.max_blocks) * 4);
+             uint64_t* seeds = (uint64_t*)(base + off[15]);
+             int32_t* soff = (int32_t*)(base + off[16]);
+             // token rows
+             std::memcpy(tok, b.tokens.data(), nd * 8);
+             std::memcpy(pos, b.positions.data(), nd * 8);
+             std::memcpy(slots, b.slots.data(), nd * 4);
+             for (int64_t i = nd; i < D; ++i) { tok[i] = 0; pos[i] = 0; slots[i] = -1; }
+             std::memcpy(tok + D, b.tokens.data() + nd, ptok * 8);
+             std::memcpy(pos + D, b.positions.data() + nd, ptok * 8);
+             std::memcpy(slots + D, b.slots.data() + nd, ptok * 4);
+             for (int64_t i = D + ptok; i < T; ++i) { tok[i] = 0; pos[i] = 0; slots[i] = -1; }
+             // sequences
+             std::memcpy(kvl, b.kv_lens.data(), nd * 4);
+             std::memcpy(ql, b.q_lens.data(), nd * 4);
+             for (int64_t i = 0; i <= nd; ++i) cuq[i] = b.cu_q[i];
+             for (int64_t i = nd; i < D; ++i) { kvl[i] = 0; ql[i] = 1; cuq[i + 1] = cuq[i] + 1; }
+             const int32_t shift = (int32_t)(D - nd);   // how far the prompt-chunk rows moved
+             for (int64_t j = 0; j < npf; ++j) {
+               kvl[D + j] = b.kv_lens[nd + j];
+               ql[D + j] = b.q_lens[nd + j];
+               cuq[D + j + 1] = b.cu_q[nd + j + 1] + shift;
              }
-             if (S > rS) std::memset(bt + rS * bt_stride, 0, (size_t)(S - rS) * bt_stride * 4);
+             for (int64_t j = npf; j < P; ++j) { kvl[D + j] = 0; ql[D + j] = 0; cuq[D + j + 1] = cuq[D + j]; }
+             // sample rows keep their order (decode rows, then the prompt chunks that end a prompt);
+             // padding entries sample row 0 greedily and are ignored by the caller
+             for (int64_t r = 0; r < rNS; ++r) {
+               const int64_t row = b.sample_rows[r];
+               srow[r] = row >= nd ? row + shift : row;
+               topk[r] = b.top_k[r]; temp[r] = b.temperature[r]; topp[r] = b.top_p[r];
+               seeds[r] = b.seeds[r]; soff[r] = b.sample_offsets[r];
+             }
+             for (int64_t r = rNS; r < NS; ++r) {
+               srow[r] = mixed ? 0 : r; topk[r] = 0; temp[r] = 0.f; topp[r] = 1.f; seeds[r] = 0; soff[r] = 0;
+             }
+             // block tables
+             for (int64_t i = 0; i < rS; ++i) {
+               int32_t* dst = bt + (i < nd ? i : i + shift) * (int64_t)bt_stride;
+               std::memcpy(dst, b.block_tables.data() + i * b.max_blocks, b.max_blocks * 4);
+               if (bt_stride > b.max_blocks) std::memset(dst + b.max_blocks, 0, (size_t)(bt_stride - b.max_blocks) * 4);
+             }
+             for (int64_t i = nd; i < D; ++i) std::memset(bt + i * (int64_t)bt_stride, 0, (size_t)bt_stride * 4);
+             for (int64_t j = npf; j < P; ++j) std::memset(bt + (D + j) * (int64_t)bt_stride, 0, (size_t)bt_stride * 4);
              return off;
            },
-           py::arg("ptr"), py::arg("capacity"), py::arg("bt_stride"), py::arg("pad_seqs") = 0);
+           py::arg("ptr"), py::arg("capacity"), py::arg("bt_stride"), py::arg("pad_seqs") = 0,
+           py::arg("pad_prefill_tokens") = 0, py::arg("pad_prefill_seqs") = 0);
 
   py::class_<OutputEvent>(m, "OutputEvent")
       .def_readonly("request_id", &OutputEvent::request_id)
@@ -281,7 +350,10 @@ PYBIND11_MODULE(_rt, m) {
       .def_readonly("num_prompt_tokens", &OutputEvent::num_prompt_tokens)
       .def_readonly("num_generated", &OutputEvent::num_generated)
       .def_readonly("prefix_hit_tokens", &OutputEvent::prefix_hit_tokens)
-      .def_readonly("request_finished", &OutputEvent::request_finished);
+      .def_readonly("request_finished", &OutputEvent::request_finished)
+      .def_readonly("seq_id", &OutputEvent::seq_id)
+      .def_readonly("top_ids", &OutputEvent::top_ids)
+      .def_readonly("top_logprobs", &OutputEvent::top_logprobs);
 
   py::class_<Scheduler>(m, "Scheduler")
       .def(py::init<const SchedulerConfig&>())
@@ -323,7 +395,17 @@ PYBIND11_MODULE(_rt, m) {
              return s.process_output_multi(batch_id, toks.data(), counts.data(), (int64_t)counts.size(), lp);
            },
            py::arg("batch_id"), py::arg("tokens"), py::arg("counts"), py::arg("logprobs") = py::none())
+      .def("set_top_logprobs",
+           [](Scheduler& s, int64_t batch_id, py::array_t<int32_t, py::array::c_style | py::array::forcecast> ids,
+              py::array_t<float, py::array::c_style | py::array::forcecast> lps) {
+             if (ids.ndim() != 2 || lps.ndim() != 2 || ids.shape(0) != lps.shape(0) || ids.shape(1) != lps.shape(1))
+               throw std::invalid_argument("set_top_logprobs: ids and logprobs must both be [rows, n]");
+             s.set_top_logprobs(batch_id, ids.data(), lps.data(), (int64_t)ids.shape(0), (int32_t)ids.shape(1));
+           })
       .def("take_pending_events", &Scheduler::take_pending_events)
+      .def("take_preempted", &Scheduler::take_preempted)
+      .def("reconfigure", &Scheduler::reconfigure, py::arg("policy") = "", py::arg("max_tokens_per_batch") = 0,
+           py::arg("max_seqs_per_batch") = 0, py::arg("max_tokens_per_chunk_for_prefill") = 0)
       .def("pause", &Scheduler::pause)
       .def("resume", &Scheduler::resume)
       .def("is_drained", &Scheduler::is_drained)
@@ -332,6 +414,7 @@ PYBIND11_MODULE(_rt, m) {
       .def("has_unfinished", &Scheduler::has_unfinished)
       .def_property_readonly("num_waiting", &Scheduler::num_waiting)
       .def_property_readonly("num_running", &Scheduler::num_running)
+      .def_property_readonly("num_prefilling", &Scheduler::num_prefilling)
       .def_property_readonly("num_requests", &Scheduler::num_requests)
       .def_property_readonly("num_preemptions", &Scheduler::num_preemptions)
       .def("block_manager", [](Scheduler& s, int dp) -> BlockManager& { return s.block_manager(dp); },

@@ -50,6 +50,10 @@ struct SchedulerConfig {
   int32_t dp_size = 1;
   int32_t num_speculative_tokens = 0;  // extra KV slots reserved per decode step
   int32_t max_decode_batch = 0;        // 0: max_seqs_per_batch
+  // Cap on sequences that hold KV / state at the same time (running queue), 0 = no cap.  The
+  // per-step sequence budget does not bound it: with prefill_first the running set grows over
+  // successive steps.  Models with per-sequence state slots size their pool by this number.
+  int32_t max_running_seqs = 0;
   // PD disaggregation, prefill side: a sequence that finishes keeps its KV blocks until
   // release_held() so that they can be pushed to the decode instance first.
   bool hold_finished_blocks = false;
@@ -72,9 +76,11 @@ struct Batch {
   std::vector<int32_t> sample_seq;            // index into seqs for each sample row
   std::vector<float> temperature, top_p, freq_pen, pres_pen, rep_pen;
   std::vector<int32_t> top_k;
-  std::vector<uint64_t> seeds;
+  std::vector<uint64_t> seeds;                // per sample row: the sequence's own random stream
+  std::vector<int32_t> sample_offsets;        // per sample row: tokens the sequence has generated so far
   std::vector<int64_t> seq_ids;
   bool any_penalty = false, any_logprobs = false, all_greedy = true;
+  int32_t max_top_logprobs = 0;               // widest `top_logprobs` request among the sample rows
   std::vector<Sequence*> seqs;  // not exposed
   int32_t n_seqs() const { return n_decode + n_prefill; }
   bool empty() const { return n_tokens == 0; }
@@ -90,6 +96,10 @@ struct OutputEvent {
   std::string finish_reason;
   int32_t num_prompt_tokens = 0, num_generated = 0, prefix_hit_tokens = 0;
   bool request_finished = false;
+  int64_t seq_id = -1;
+  // the most likely alternatives at this position (requests with top_logprobs > 0), best first
+  std::vector<int32_t> top_ids;
+  std::vector<float> top_logprobs;
 };
 
 class Scheduler {
@@ -101,6 +111,16 @@ class Scheduler {
   }
 
   const SchedulerConfig& config() const { return cfg_; }
+
+  // Change the batching policy and the per-step budgets of a live scheduler (takes effect at the
+  // next schedule()); values <= 0 and an empty policy keep the current setting.
+  void reconfigure(const std::string& policy, int32_t max_tokens_per_batch, int32_t max_seqs_per_batch,
+                   int32_t max_tokens_per_chunk_for_prefill) {
+    if (!policy.empty()) cfg_.policy = policy;
+    if (max_tokens_per_batch > 0) cfg_.max_tokens_per_batch = max_tokens_per_batch;
+    if (max_seqs_per_batch > 0) cfg_.max_seqs_per_batch = max_seqs_per_batch;
+    if (max_tokens_per_chunk_for_prefill != 0) cfg_.max_tokens_per_chunk_for_prefill = max_tokens_per_chunk_for_prefill;
+  }
   BlockManager& block_manager(int dp = 0) { return *bm_[dp]; }
 
   // ---------------------------------------------------------------- intake
@@ -288,6 +308,11 @@ class Scheduler {
           finish_seq(s, fr);
         }
         ev.push_back(make_event(s, tok, want_lp ? logprobs[base + j] : 0.f, want_lp));
+        if (want_lp && b.top_n > 0 && counts == nullptr && (r + 1) * b.top_n <= (int64_t)b.top_ids.size()) {
+          const int32_t k = std::min<int32_t>(b.top_n, s->request->sampling.top_logprobs);
+          ev.back().top_ids.assign(b.top_ids.begin() + r * b.top_n, b.top_ids.begin() + r * b.top_n + k);
+          ev.back().top_logprobs.assign(b.top_lps.begin() + r * b.top_n, b.top_lps.begin() + r * b.top_n + k);
+        }
         if (s->request->all_finished()) ev.back().request_finished = true;
         if (s->finished()) break;
       }
@@ -303,6 +328,25 @@ class Scheduler {
     done.erase(std::unique(done.begin(), done.end()), done.end());
     for (Request* r : done) maybe_erase_request(r);
     return ev;
+  }
+
+  // Alternatives for the sample rows of a batch still in flight: ids / logprobs are [n_rows, n]
+  // (best first); the next process_output of that batch attaches the first `top_logprobs` of each
+  // row to its event.  One token per row only (no speculative rows).
+  void set_top_logprobs(int64_t batch_id, const int32_t* ids, const float* lps, int64_t n_rows, int32_t n) {
+    auto it = in_flight_batches_.find(batch_id);
+    if (it == in_flight_batches_.end() || n <= 0) return;
+    it->second.top_n = n;
+    it->second.top_ids.assign(ids, ids + n_rows * n);
+    it->second.top_lps.assign(lps, lps + n_rows * n);
+  }
+
+  // Sequence ids preempted since the last call (their KV - and any per-sequence state - is gone and
+  // will be rebuilt from position 0).
+  std::vector<int64_t> take_preempted() {
+    std::vector<int64_t> out;
+    out.swap(preempted_ids_);
+    return out;
   }
 
   std::vector<OutputEvent> take_pending_events() {
@@ -344,6 +388,12 @@ class Scheduler {
   bool has_unfinished() const { return !waiting_.empty() || !running_.empty() || !in_flight_batches_.empty(); }
   int64_t num_waiting() const { return (int64_t)waiting_.size(); }
   int64_t num_running() const { return (int64_t)running_.size(); }
+  // running sequences whose prompt is not in the cache yet (a chunk may be in flight)
+  int64_t num_prefilling() const {
+    int64_t n = 0;
+    for (const Sequence* s : running_) n += s->stage == SeqStage::PREFILL ? 1 : 0;
+    return n;
+  }
   int64_t num_requests() const { return (int64_t)requests_.size(); }
   int64_t num_preemptions() const { return preemptions_; }
 
@@ -353,6 +403,9 @@ class Scheduler {
     std::vector<Sequence*> seqs;
     std::vector<int32_t> q_lens, sample_seq;
     int32_t n_decode = 0;
+    int32_t top_n = 0;
+    std::vector<int32_t> top_ids;
+    std::vector<float> top_lps;
   };
   // ---------------------------------------------------------------- queues
   bool before(const Sequence* a, const Sequence* b) const {
@@ -450,6 +503,7 @@ class Scheduler {
     s->kv_computed = 0;
     s->preempt_count++;
     preemptions_++;
+    preempted_ids_.push_back(s->seq_id);
     enqueue_waiting(s, /*front=*/true);
   }
 
@@ -457,6 +511,7 @@ class Scheduler {
     OutputEvent e;
     e.request_id = s->request->request_id;
     e.seq_index = s->index;
+    e.seq_id = s->seq_id;
     e.token = tok;
     e.logprob = lp;
     e.has_logprob = has_lp;
@@ -586,6 +641,7 @@ class Scheduler {
       }
       if (admit_blocked_) return;
       while (!waiting_.empty() && tok_budget > 0 && seq_budget > 0) {
+        if (cfg_.max_running_seqs > 0 && (int32_t)running_.size() >= cfg_.max_running_seqs) break;
         Sequence* s = waiting_.front();
         const int target_dp = cfg_.dp_size == 1 ? 0 : pick_dp_rank();
         if (target_dp != dp) break;  // this request goes to another rank's batch
@@ -717,9 +773,14 @@ class Scheduler {
         b.freq_pen.push_back(sp.frequency_penalty);
         b.pres_pen.push_back(sp.presence_penalty);
         b.rep_pen.push_back(sp.repetition_penalty);
-        b.seeds.push_back(sp.seed);
+        // one random stream per sequence (parallel samples of a request must not draw the same
+        // numbers), advanced by the number of tokens generated so far: a sample depends neither on
+        // the row a sequence happens to occupy nor on who shares the batch
+        b.seeds.push_back(sp.seed + 0x9E3779B97F4A7C15ull * (uint64_t)s->index);
+        b.sample_offsets.push_back(s->num_generated() + s->pending_samples);
         b.any_penalty |= sp.has_penalty();
         b.any_logprobs |= sp.logprobs;
+        if (sp.logprobs) b.max_top_logprobs = std::max(b.max_top_logprobs, sp.top_logprobs);
         b.all_greedy &= !(sp.temperature > 0.f);
         s->pending_samples++;
       }
@@ -745,6 +806,7 @@ class Scheduler {
   std::map<int64_t, InFlight> in_flight_batches_;
   std::map<int, std::unordered_map<Sequence*, int32_t>> last_sample_row_;
   std::vector<OutputEvent> pending_events_;
+  std::vector<int64_t> preempted_ids_;
   int64_t next_seq_id_ = 0, next_batch_id_ = 0, preemptions_ = 0;
   bool paused_ = false, admit_blocked_ = false, pause_mode_active_ = false;
   PauseMode pause_mode_ = PauseMode::KEEP;

@@ -32,6 +32,7 @@ class FaultPlan:
     raise_step: Optional[int] = None
     slow_ms: float = 0.0
     drop_prob: float = 0.0
+    refused: bool = False
     rng: random.Random = field(default_factory=lambda: random.Random(0))
 
     @staticmethod
@@ -59,9 +60,24 @@ class FaultPlan:
         spec = os.environ.get("XLLM_FAULT", "")
         return FaultPlan.parse(spec, rank) if spec else None
 
-    def before_step(self, step: int, sleep: Callable[[float], None] = time.sleep):
+    def before_step(self, step: int, sleep: Callable[[float], None] = time.sleep, multicast_bound: bool = False):
+        """`multicast_bound`: this rank's memory is bound to an NVLink multicast object (a fused
+        communicator with a multimem mapping, NVLS).  A rank must not leave while that is so - the
+        other ranks' multimem accesses would fault - so the hooks that end the rank are refused: they
+        log once and the step goes on.  Run such experiments with XLLM_TP_MULTIMEM=0 and
+        NCCL_NVLS_ENABLE=0."""
         if self.slow_ms > 0:
             sleep(self.slow_ms / 1e3)
+        leaving = (self.exit_step is not None and step >= self.exit_step) or \
+                  (self.raise_step is not None and step == self.raise_step)
+        if leaving and multicast_bound:
+            if not self.refused:
+                self.refused = True
+                import logging
+                logging.getLogger("xllm_b200.fault").warning(
+                    "XLLM_FAULT worker_exit / raise refused at step %d: this rank's memory is bound to an NVLink "
+                    "multicast object; set XLLM_TP_MULTIMEM=0 and NCCL_NVLS_ENABLE=0 to use these hooks", step)
+            return
         if self.exit_step is not None and step >= self.exit_step:
             raise SystemExit(f"XLLM_FAULT: worker_exit at step {step}")
         if self.raise_step is not None and step == self.raise_step:

@@ -62,6 +62,18 @@ class EngineConfig:
     draft_model: str = ""
     mla_latent_cache: bool = False      # MLA models: cache [c_kv | k_pe] rows (576 values per token) instead of per-head K/V
     activation_reserve_bytes: int = 0   # 0: estimated from max_tokens_per_batch
+    max_running_seqs: int = 0           # cap on sequences holding KV / state at once; 0: no cap (state models: max_seqs_per_batch + 1)
+
+
+_U64 = (1 << 64) - 1
+
+
+def _mix64(a: int, b: int) -> int:
+    """splitmix64 of (a, b): a well-spread 64-bit value for per-request random streams."""
+    z = (a * 0x9E3779B97F4A7C15 + b * 0xBF58476D1CE4E5B9 + 0x94D049BB133111EB) & _U64
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _U64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _U64
+    return z ^ (z >> 31)
 
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float16": torch.float16,
@@ -99,7 +111,10 @@ class LLMEngine:
         # ---- fused tensor-parallel communicator (symmetric memory), before the model is built
         if self.ps.tp_size > 1 and self.device.type == "cuda" and self.ps.comm is None:
             from ..parallel import symm
-            symm.attach(self.ps, max(cfg.max_tokens_per_batch, cfg.max_seqs_per_batch), self.args.hidden_size)
+            tp = self.ps.tp_size
+            shard = (self.args.vocab_size + tp - 1) // tp
+            symm.attach(self.ps, max(cfg.max_tokens_per_batch, cfg.max_seqs_per_batch), self.args.hidden_size,
+                        vocab_shard=shard if shard % 8 == 0 else 0, max_sample_rows=min(cfg.max_seqs_per_batch, 1024))
         # ---- model
         t0 = time.time()
         if model is not None:
@@ -135,7 +150,10 @@ class LLMEngine:
                                   graph_buckets=cfg.graph_buckets)
         self.runner.overlap = cfg.enable_schedule_overlap
         if getattr(self.model, "needs_state", False):
-            self.model.alloc_state(cfg.max_seqs_per_batch + 1)
+            # one state slot per sequence that can hold KV at the same time; the scheduler admits no
+            # more than that (max_running_seqs below), so a slot is always free when one is needed
+            self.state_slots = cfg.max_running_seqs or (cfg.max_seqs_per_batch + 1)
+            self.model.alloc_state(self.state_slots)
             self.runner.meta_hook = self._state_hook
         # ---- scheduler
         sc = rt.SchedulerConfig()
@@ -154,9 +172,11 @@ class LLMEngine:
         sc.enable_schedule_overlap = cfg.enable_schedule_overlap
         sc.dp_size = 1  # one scheduler instance per DP replica
         sc.num_speculative_tokens = cfg.num_speculative_tokens
+        sc.max_running_seqs = getattr(self, "state_slots", 0) or cfg.max_running_seqs
         sc.hold_finished_blocks = hold_finished_blocks   # PD disaggregation, prefill side
         self.scheduler = rt.Scheduler(sc)
         self._pending: Optional[StepOutput] = None
+        self._req_counter = 0
         self.grammar = None
         self.asleep = 0
         self._host_weights = None
@@ -235,7 +255,10 @@ class LLMEngine:
         sp.repetition_penalty = float(repetition_penalty)
         sp.logprobs = bool(logprobs)
         sp.top_logprobs = int(top_logprobs)
-        sp.seed = int(seed if seed is not None else self.cfg.seed)
+        # without an explicit seed every request gets its own random stream, derived from the
+        # engine seed and the arrival order (the same on every tensor-parallel rank)
+        self._req_counter += 1
+        sp.seed = int(seed) & _U64 if seed is not None else _mix64(self.cfg.seed, self._req_counter)
         st = rt.StoppingParams()
         st.max_tokens = int(max_tokens)
         st.max_context_len = int(self.max_model_len)
@@ -277,10 +300,11 @@ class LLMEngine:
         st = self.model.state
         n = batch.n_decode + batch.n_prefill
         cu, pos = np.asarray(batch.cu_q), np.asarray(batch.positions)
+        seq_ids = np.asarray(batch.seq_ids)
         slots, fresh, bounds = [], [], []
         for i in range(n):
             a, b = int(cu[i]), int(cu[i + 1])
-            slots.append(st.slot_of(batch.request_id(i)))
+            slots.append(st.slot_of(int(seq_ids[i])))
             fresh.append(int(pos[a]) == 0)
             bounds.append((a, b))
         meta.state_slots = torch.tensor(slots, dtype=torch.long, device=self.device)
@@ -358,13 +382,18 @@ class LLMEngine:
     # ------------------------------------------------------------------ stepping
     def _finish(self, out: StepOutput):
         ids, lp = out.wait()
+        top = out.top_host()
+        if top is not None:
+            self.scheduler.set_top_logprobs(out.batch_id, top[0], top[1])
         return self.scheduler.process_output(out.batch_id, ids, lp)
 
     def step(self):
         """One scheduler iteration. Returns the list of OutputEvent produced by it."""
         events = []
         if self.fault is not None:
-            self.fault.before_step(self.steps)
+            comm = getattr(self.ps, "comm", None)
+            nvls = self.ps.world_size > 1 and self.device.type == "cuda" and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0"
+            self.fault.before_step(self.steps, multicast_bound=bool(getattr(comm, "mc_base", 0)) or nvls)
         batches = self.scheduler.schedule()
         batch = batches[0] if batches else None
         if self.ps.dp_size > 1 and self.ps.ep_size > 1:
@@ -377,7 +406,8 @@ class LLMEngine:
                 events = self._finish(self._pending)
             self._pending = new
         else:
-            if batch is not None and self.spec is not None and batch.n_prefill == 0 and batch.n_decode > 0:
+            if batch is not None and self.spec is not None and batch.n_prefill == 0 and batch.n_decode > 0 \
+                    and self.spec.can_verify(batch, self.runner):
                 flat, counts, lp = self.spec.step(batch)
                 events = self.scheduler.process_output_multi(batch.batch_id, flat, counts, lp)
             elif batch is not None:
@@ -393,8 +423,10 @@ class LLMEngine:
         self._grammar_advance(events)
         if getattr(self.model, "needs_state", False):
             for ev in events:
-                if ev.request_finished:
-                    self.model.state.release(ev.request_id)
+                if ev.finished and ev.seq_id >= 0:
+                    self.model.state.release(int(ev.seq_id))
+            for sid in self.scheduler.take_preempted():
+                self.model.state.release(int(sid))     # the state is rebuilt from position 0 anyway
         if self.mm:
             for ev in events:
                 if ev.request_finished:
@@ -483,7 +515,8 @@ class LLMEngine:
         self._kv_shapes = [(k.shape, v.shape, k.dtype, k.device) for k, v in r.kv_caches]
         r.graphs.clear()
         r.graph_in.clear()
-        r.graph_logits.clear()
+        r.graph_out.clear()
+        r.graph_off.clear()
         r.graph_pool = None
         for i in range(len(r.kv_caches)):
             r.kv_caches[i] = None

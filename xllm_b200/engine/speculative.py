@@ -30,6 +30,8 @@ from typing import Optional
 import numpy as np
 import torch
 
+from ..ops import reference
+
 from .. import ops
 from ..models.layers import AttentionMetadata
 from ..ops import spec as spec_ops
@@ -278,27 +280,48 @@ class SpecDecoder:
         temperature = np.asarray(batch.temperature)[:B]
         greedy = temperature <= 0
         d_dev = torch.from_numpy(drafts).to(dev)
+        lp = None
         if greedy.all():
             tgt = logits.argmax(-1)                                           # [B, k+1]
             agree = (tgt[:, :k] == d_dev).to(torch.int32)
             n_acc = torch.cumprod(agree, dim=1).sum(1)                        # accepted drafts per row
             counts = (n_acc + 1).to(torch.int32)
             out = tgt                                                         # tokens 0..n_acc are the target's own
+            if batch.any_logprobs:
+                lp = torch.log_softmax(logits, dim=-1).gather(-1, out.unsqueeze(-1)).squeeze(-1)
         else:
-            t = torch.from_numpy(np.where(greedy, 1.0, temperature).astype(np.float32)).to(dev)
-            probs = torch.softmax(logits / t.view(B, 1, 1), dim=-1).contiguous()
-            out, counts = spec_ops.verify(d_dev, probs, None, torch.from_numpy(greedy).to(dev),
-                                          seed=int(batch.seeds[0]), offset=self.runner.sample_offset)
-            self.runner.sample_offset += 4
+            # the verified distribution is the one the sampler would have drawn from: temperature,
+            # then the top-k / top-p filter, renormalised (the reference's rejection sampler works on
+            # the filtered target distribution too: sampling/rejection_sampler.cpp:65-360)
+            rep = lambda a, dt: torch.from_numpy(np.repeat(np.asarray(a)[:B], k + 1).astype(dt)).to(dev)
+            probs = reference.filtered_distribution(logits.view(B * (k + 1), -1), rep(temperature, np.float32),
+                                                    rep(batch.top_k, np.int32), rep(batch.top_p, np.float32))
+            probs = probs.float().view(B, k + 1, -1).contiguous()
+            seeds = torch.from_numpy(np.asarray(batch.seeds)[:B].astype(np.uint64).view(np.int64)).to(dev)
+            offs = torch.from_numpy(np.asarray(batch.sample_offsets)[:B].astype(np.int32)).to(dev)
+            out, counts = spec_ops.verify(d_dev, probs, None, torch.from_numpy(greedy).to(dev), seeds=seeds, offsets=offs)
+            if batch.any_logprobs:
+                lp = torch.log(probs.gather(-1, out.clamp_min(0).unsqueeze(-1)).squeeze(-1).clamp_min(1e-30))
         counts_h = counts.cpu().numpy().astype(np.int32)
         out_h = out.cpu().numpy()
         flat = np.concatenate([out_h[i, : counts_h[i]] for i in range(B)]).astype(np.int64)
+        lp_flat = None
+        if lp is not None:
+            lp_h = lp.float().cpu().numpy()
+            lp_flat = np.concatenate([lp_h[i, : counts_h[i]] for i in range(B)]).astype(np.float32)
         seen = self.runner.model.last_aux if getattr(self.drafter, "takes_aux", False) else hidden
         self.drafter.observe(batch, B, seen.view(B, k + 1, -1), counts_h, tokens=out_h, kv0=kv0, block_tables=bt)
         self.proposed += B * k
         self.accepted += int(counts_h.sum()) - B
         self.steps += 1
-        return flat, counts_h, None
+        return flat, counts_h, lp_flat
+
+    @staticmethod
+    def can_verify(batch, runner) -> bool:
+        """Whether one verification pass can honour every request of the batch.  Penalties depend on
+        the tokens drafted so far, grammar masks on the automaton state after each of them, and
+        top_logprobs needs the host in the loop: such batches take the ordinary one-token step."""
+        return not (batch.any_penalty or runner.logits_hook is not None or batch.max_top_logprobs > 0)
 
 
 def make_drafter(kind: str, k: int, engine=None, **kw):

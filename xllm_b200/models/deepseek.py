@@ -186,6 +186,7 @@ class DeepseekDecoderLayer(DecoderLayer):
 
 
 class DeepseekCausalLM(DenseCausalLM):
+    supports_prefill_graph = False
     def __init__(self, args, dtype=torch.bfloat16, device="cpu", ps=None):
         Module.__init__(self)
         self.args = args
@@ -255,13 +256,17 @@ class MTPDraft(Module):
         self.norm = self.add_module("shared_head.norm", RMSNorm(H, args.rms_norm_eps, dtype, device))
 
     def forward(self, tokens, prev_hidden, positions, meta, k_cache, v_cache):
+        comm = self.ps.comm
+        if comm is not None and tokens.is_cuda:
+            comm.begin_forward(tokens.shape[0])
         e = self.enorm(self.embed(tokens))
         h = self.hnorm(prev_hidden)
         x = self.eh_proj(torch.cat([e, h], dim=-1))
         y, residual = self.layer(x, None, positions, meta, k_cache, v_cache)
-        comm = self.ps.comm
         if comm is not None and x.is_cuda:
-            return comm.allreduce_norm(x.shape[0], residual, self.norm.weight, self.norm.eps)
+            h = comm.allreduce_norm(x.shape[0], residual, self.norm.weight, self.norm.eps)
+            comm.end_forward()
+            return h
         return self.norm(y, residual=residual)
 
     def logits(self, hidden_rows):

@@ -38,6 +38,9 @@ class AttentionMetadata:
     # position-indexed cache (row i of the table belongs to token row i)
     rope_table: Optional[torch.Tensor] = None
     rope_rows: Optional[torch.Tensor] = None
+    # the step has a fixed padded shape (CUDA-graph replay): token rows that belong to no sequence
+    # exist, and whatever a kernel leaves unwritten for them must still be finite
+    padded: bool = False
 
     @property
     def n_seqs(self):
@@ -378,7 +381,7 @@ class Attention(Module):
                               q_norm_w=self._norm_w(self.q_norm), k_norm_w=self._norm_w(self.k_norm), eps=self.eps,
                               interleaved=self.rope.interleaved)
         T = q.shape[0]
-        out = torch.empty((T, self.nq, self.d), dtype=q.dtype, device=q.device)
+        out = (torch.zeros if meta.padded else torch.empty)((T, self.nq, self.d), dtype=q.dtype, device=q.device)
         nd = meta.n_decode
         if nd > 0:
             ops.paged_decode_attention(q[:nd], k_cache, v_cache, meta.block_table[:nd], meta.kv_lens[:nd],

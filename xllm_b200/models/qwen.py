@@ -43,14 +43,12 @@ class DecoderLayer(Module):
     def _forward_tp_fused(self, comm, x, residual, positions, meta, k_cache, v_cache):
         """Tensor-parallel path with the reductions fused into the norms: row-parallel GEMMs leave
         their partial sums in the symmetric buffer, `allreduce_norm` sums them across ranks, adds the
-        residual and normalises.  The residual stream is sharded by token rows: each rank keeps (and
-        updates) only the rows it reduces."""
+        residual and normalises.  In the two-shot form the residual stream is sharded by token rows
+        (each rank keeps and updates only the rows it reduces); in the one-shot form it is replicated."""
         T = x.shape[0]
         eps = self.input_layernorm.eps
         if residual is None:
-            b, e, S = comm.shard(T)
-            residual = torch.zeros((S, x.shape[1]), dtype=x.dtype, device=x.device)
-            residual[: e - b].copy_(x[b:e])
+            residual = comm.new_residual(x)
             h = self.input_layernorm(x)
         else:
             h = comm.allreduce_norm(T, residual, self.input_layernorm.weight, eps)
@@ -66,6 +64,7 @@ class DenseCausalLM(Module):
     """model.embed_tokens -> N x DecoderLayer -> model.norm -> lm_head."""
 
     fused_tp = True      # False in families whose layers cannot use the fused all-reduce + norm
+    supports_prefill_graph = True   # steps with prompt chunks may be captured (padded shapes are safe)
 
     def __init__(self, args, dtype=torch.bfloat16, device="cpu", ps: ParallelState = None, make_mlp=None,
                  layer_cls=None):
@@ -105,6 +104,9 @@ class DenseCausalLM(Module):
         """tokens/positions: [T] int64.  kv_caches: list of (k_cache, v_cache) per layer.
         `embeds` = (rows, values): input embeddings that replace the token embedding of those rows
         (image tokens of a multimodal prompt).  Returns the final-norm hidden states [T, H]."""
+        comm = self.ps.comm if self.fused_tp else None
+        if comm is not None and tokens.is_cuda:
+            comm.begin_forward(tokens.shape[0])
         x = self.embed(tokens)
         deep = None
         if embeds is not None:
@@ -124,9 +126,10 @@ class DenseCausalLM(Module):
                 aux[i] = x + residual                      # the layer's output: the branch joins the residual lazily
         if aux_ids:
             self.last_aux = torch.cat([aux[i] for i in aux_ids], dim=-1)
-        comm = self.ps.comm if self.fused_tp else None
         if comm is not None and x.is_cuda:
-            return comm.allreduce_norm(x.shape[0], residual, self.norm.weight, self.norm.eps)
+            h = comm.allreduce_norm(x.shape[0], residual, self.norm.weight, self.norm.eps)
+            comm.end_forward()
+            return h
         return self.norm(x, residual=residual)
 
     def logits(self, hidden_rows):

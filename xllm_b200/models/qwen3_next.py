@@ -32,7 +32,9 @@ from ..parallel.state import single
 
 class LinearStateCache:
     """Convolution tails and recurrent states of every linear-attention layer, one slot per running
-    request."""
+    sequence (keyed by the scheduler's sequence id: parallel samples of one request have their own
+    state).  The scheduler admits at most `slots` sequences at a time and slots return on finish and
+    on preemption, so `slot_of` finds a free slot whenever it needs one."""
 
     def __init__(self, n_layers, slots, conv_dim, kernel, nv, dk, dv, device, dtype):
         self.conv = torch.zeros(n_layers, slots, conv_dim, kernel - 1, dtype=dtype, device=device)
@@ -44,7 +46,7 @@ class LinearStateCache:
         s = self.owner.get(request_id)
         if s is None:
             if not self.free:
-                raise RuntimeError("no free linear-state slot: more running requests than max_seqs_per_batch")
+                raise RuntimeError("no free linear-state slot: the scheduler admitted more sequences than the pool holds")
             s = self.owner[request_id] = self.free.pop()
         return s
 

@@ -197,9 +197,27 @@ def paged_prefill_attention(q, k_cache, v_cache, block_table, cu_q, kv_lens, max
 
 # ----------------------------------------------------------------------------- sampling
 def sample(logits, temperature=None, top_k=None, top_p=None, seed=0, offset=0, want_logprob=False,
-           generator=None, out_ids=None):
-    """Returns (ids int64 [B], logprob fp32 [B] | None)."""
+           generator=None, out_ids=None, seeds=None, offsets=None, out_logprob=None):
+    """Returns (ids int64 [B], logprob fp32 [B] | None).
+
+    `seeds` (uint64/int64 [B]) and `offsets` (int32 [B]) give every row its own random stream: the seed
+    of the row's sequence and the number of draws it has made so far.  Without them the batch-level
+    (`seed`, `offset`) pair is used with the row index as the sub-stream."""
     if not logits.is_cuda:
+        if seeds is not None and generator is None:
+            ids = torch.empty(logits.shape[0], dtype=torch.int64)
+            lp = torch.empty(logits.shape[0], dtype=torch.float32) if want_logprob else None
+            for r in range(logits.shape[0]):
+                g = torch.Generator().manual_seed((int(seeds[r]) * 1000003 + int(offsets[r] if offsets is not None else 0))
+                                                  & 0x7FFFFFFFFFFFFFFF)
+                sl = slice(r, r + 1)
+                i, l = reference.sample(logits[sl], None if temperature is None else temperature[sl],
+                                        None if top_k is None else top_k[sl], None if top_p is None else top_p[sl],
+                                        g, want_logprob)
+                ids[r] = i[0]
+                if want_logprob:
+                    lp[r] = l[0]
+            return ids, lp
         if generator is None:       # the same (seed, offset) gives the same draw, as on the device
             generator = torch.Generator().manual_seed((int(seed) * 1000003 + int(offset)) & 0x7FFFFFFFFFFFFFFF)
         return reference.sample(logits, temperature, top_k, top_p, generator, want_logprob)
@@ -210,12 +228,39 @@ def sample(logits, temperature=None, top_k=None, top_p=None, seed=0, offset=0, w
         logits = logits.float()
     if out_ids is None:
         out_ids = torch.empty(B, dtype=torch.int64, device=logits.device)
-    lp = torch.empty(B, dtype=torch.float32, device=logits.device) if want_logprob else None
-    check(_lib_().xllm_sample(ptr(logits), logits.stride(0), dt, B, V, ptr(temperature), ptr(top_k),
-                              ptr(top_p), ptr(out_ids), ptr(lp), int(seed), int(offset), stream()),
-          "sample")
+    lp = out_logprob
+    if lp is None and want_logprob:
+        lp = torch.empty(B, dtype=torch.float32, device=logits.device)
+    if seeds is not None:
+        check(_lib_().xllm_sample_rows(ptr(logits), logits.stride(0), dt, B, V, ptr(temperature), ptr(top_k),
+                                       ptr(top_p), ptr(out_ids), ptr(lp), ptr(seeds), ptr(offsets), stream()),
+              "sample_rows")
+    else:
+        check(_lib_().xllm_sample(ptr(logits), logits.stride(0), dt, B, V, ptr(temperature), ptr(top_k),
+                                  ptr(top_p), ptr(out_ids), ptr(lp), int(seed), int(offset), stream()),
+              "sample")
     _count()
     return out_ids, lp
+
+
+def top_logprobs(logits, n):
+    """The n most likely tokens of every row and their log-probabilities under softmax(logits):
+    (ids int32 [B, n], logprobs fp32 [B, n]), most likely first."""
+    if not logits.is_cuda:
+        lp = torch.log_softmax(logits.float(), dim=-1)
+        v, i = lp.topk(n, dim=-1)
+        return i.to(torch.int32), v
+    B, V = logits.shape
+    assert logits.stride(-1) == 1
+    dt = 0 if logits.dtype == torch.bfloat16 else 1
+    if dt == 1 and logits.dtype != torch.float32:
+        logits = logits.float()
+    ids = torch.empty((B, n), dtype=torch.int32, device=logits.device)
+    lp = torch.empty((B, n), dtype=torch.float32, device=logits.device)
+    check(_lib_().xllm_top_logprobs(ptr(logits), logits.stride(0), dt, B, V, int(n), ptr(ids), ptr(lp), stream()),
+          "top_logprobs")
+    _count()
+    return ids, lp
 
 
 def apply_penalties(logits, ids, counts, freq=None, presence=None, repetition=None):

@@ -69,6 +69,9 @@ def _declare(lib):
         "xllm_paged_prefill_attn_tc": [P, L, P, L, L, P, P, L, P, I, P, P, I, I, I, I, I, F, I, P],
         "xllm_fmha_error_status": [],
         "xllm_sample": [P, L, I, I, I, P, P, P, P, P, U64, U64, P],
+        "xllm_sample_rows": [P, L, I, I, I, P, P, P, P, P, P, P, P],
+        "xllm_top_logprobs": [P, L, I, I, I, I, P, P, P],
+        "xllm_rmsnorm_group_fp8": [P, P, P, P, P, I, I, F, L, I, P],
         "xllm_apply_penalties": [P, L, I, I, I, P, P, I, P, P, P, P],
         "xllm_embedding": [P, P, P, L, I, L, L, P],
         "xllm_gather_rows": [P, P, P, L, L, L, P],

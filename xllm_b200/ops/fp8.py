@@ -78,6 +78,29 @@ def quant_group128(x):
     return q, s
 
 
+def rmsnorm_group_quant(x, w, eps=1e-6, residual=None, gemma=False):
+    """rmsnorm(x (+ residual)) * w written as e4m3 with one scale per (row, 128 columns): the norm and
+    the activation quantisation of a block-scaled fp8 linear in one pass over the row.  `residual`,
+    when given, is updated in place.  Returns (q [T, H] e4m3, scales [T, H / 128] fp32)."""
+    if not x.is_cuda:
+        from . import reference
+        y, new_res = reference.rmsnorm(x, w, eps, residual, gemma)
+        if residual is not None:
+            residual.copy_(new_res)
+        return quant_group128_ref(y.to(torch.bfloat16))
+    T, H = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and H % 128 == 0
+    if residual is not None:
+        assert residual.is_contiguous()
+    q = torch.empty(T, H, dtype=FP8, device=x.device)
+    s = torch.empty(T, H // 128, dtype=torch.float32, device=x.device)
+    check(_lib.load().xllm_rmsnorm_group_fp8(ptr(q), ptr(s), ptr(x), ptr(residual), ptr(w), T, H, float(eps),
+                                             x.stride(0), int(gemma), stream()), "rmsnorm_group_fp8")
+    from . import _count
+    _count()
+    return q, s
+
+
 def dequant_block128(q, scales, out=None):
     if not q.is_cuda:
         return dequant_block128_ref(q, scales)

@@ -10,6 +10,7 @@ from . import _lib
 from ._lib import I, P, U64, check, ptr, stream
 
 _lib.register_signature("xllm_spec_verify", [P, P, P, P, P, P, I, I, I, U64, U64, P])
+_lib.register_signature("xllm_spec_verify_rows", [P, P, P, P, P, P, I, I, I, P, P, P])
 
 
 def verify_reference(draft_ids, target_probs, draft_probs=None, greedy=None, generator=None):
@@ -49,8 +50,23 @@ def verify_reference(draft_ids, target_probs, draft_probs=None, greedy=None, gen
     return out, lens
 
 
-def verify(draft_ids, target_probs, draft_probs=None, greedy=None, seed=0, offset=0, generator=None):
+def verify(draft_ids, target_probs, draft_probs=None, greedy=None, seed=0, offset=0, generator=None, seeds=None,
+           offsets=None):
+    """`seeds` / `offsets` ([B] int64 / int32): one random stream per row (the row's sequence seed and
+    the tokens it has generated so far) instead of the batch-level (`seed`, `offset`)."""
     if not target_probs.is_cuda:
+        if seeds is not None and generator is None:
+            B, K = draft_ids.shape
+            out = torch.full((B, K + 1), -1, dtype=torch.int64)
+            lens = torch.zeros(B, dtype=torch.int32)
+            for b in range(B):
+                g = torch.Generator().manual_seed((int(seeds[b]) * 1000003 + 7919 * int(offsets[b] if offsets is not None else 0))
+                                                  & 0x7FFFFFFFFFFFFFFF)
+                o, l = verify_reference(draft_ids[b:b + 1], target_probs[b:b + 1],
+                                        None if draft_probs is None else draft_probs[b:b + 1],
+                                        None if greedy is None else greedy[b:b + 1], g)
+                out[b], lens[b] = o[0], l[0]
+            return out, lens
         return verify_reference(draft_ids, target_probs, draft_probs, greedy, generator)
     B, K = draft_ids.shape
     V = target_probs.shape[-1]
@@ -58,6 +74,12 @@ def verify(draft_ids, target_probs, draft_probs=None, greedy=None, seed=0, offse
     out = torch.empty(B, K + 1, dtype=torch.int64, device=target_probs.device)
     lens = torch.empty(B, dtype=torch.int32, device=target_probs.device)
     g8 = greedy.to(torch.uint8) if greedy is not None else None
+    if seeds is not None:
+        check(_lib.load().xllm_spec_verify_rows(ptr(draft_ids), ptr(target_probs), ptr(draft_probs), ptr(g8), ptr(out),
+                                                ptr(lens), B, K, V, ptr(seeds), ptr(offsets), stream()), "spec_verify")
+        from . import _count
+        _count()
+        return out, lens
     check(_lib.load().xllm_spec_verify(ptr(draft_ids), ptr(target_probs), ptr(draft_probs), ptr(g8), ptr(out), ptr(lens),
                                        B, K, V, int(seed), int(offset), stream()), "spec_verify")
     from . import _count
