@@ -36,6 +36,8 @@ def guarded(body):
         dist.barrier(group=g)
         dist.destroy_process_group()
     if err is not None:
+        # on stdout as well: the launcher's own report fills the tail of stderr
+        print(f"[rank {rank}] FAILED\n{err}", flush=True)
         sys.stderr.write(f"[rank {rank}] FAILED\n{err}\n")
         sys.stderr.flush()
     if all_ok and rank == 0 and msg:

@@ -21,7 +21,7 @@ def _run(script, nproc, extra_env=None, timeout=300):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", "29571", os.path.join(ROOT, "tests", script)]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, r.stdout[-6000:] + r.stderr[-2000:]
     return r.stdout
 
 

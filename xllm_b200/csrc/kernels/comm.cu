@@ -405,16 +405,27 @@ __global__ void __launch_bounds__(kRowThreads) tp_oneshot_norm_kernel(TpOneShotP
   const int nvec = p.H >> 3;
   pdl_wait();
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.state) + 1u;
-  if (blockIdx.x == 0 && threadIdx.x < p.world) {
-    __threadfence_system();
+  if (blockIdx.x == 0 && threadIdx.x < p.world)   // the release store orders the earlier kernels' writes before the flag
     st_release_sys(reinterpret_cast<uint32_t*>(p.signal_pads[threadIdx.x]) + p.sig_off + p.rank, epoch);
-  }
-  wait_flags(p.signal_pads, p.sig_off, p.rank, p.world, epoch, p.budget, p.err, 300);
-  __syncthreads();
+  bool waited = false;
   for (int64_t row0 = (int64_t)blockIdx.x * R; row0 < p.T; row0 += (int64_t)gridDim.x * R) {
     const int64_t row = row0 + threadIdx.x / TPR;
     const bool active = row < p.T;
     const int64_t row_byte = row * p.H * 2;
+    // what is local goes first: the residual rows are in flight while the flags travel
+    uint4 rres[kRowMaxVec];
+    if (p.residual_in != nullptr) {
+#pragma unroll
+      for (int i = 0; i < kRowMaxVec; ++i) {
+        const int v = t + i * TPR;
+        if (active && v < nvec) rres[i] = __ldg(reinterpret_cast<const uint4*>(p.residual_in + row * p.H) + v);
+      }
+    }
+    if (!waited) {
+      wait_flags(p.signal_pads, p.sig_off, p.rank, p.world, epoch, p.budget, p.err, 300);
+      __syncthreads();
+      waited = true;
+    }
     float vals[kRowMaxVec][8];
     float ss = 0.f;
     if (p.mc_base != 0) {
@@ -431,20 +442,24 @@ __global__ void __launch_bounds__(kRowThreads) tp_oneshot_norm_kernel(TpOneShotP
         if (active && v < nvec) unpack8(*reinterpret_cast<const bf16x8*>(&raw[i]), vals[i]);
       }
     } else {
+      for (int k = 0; k < p.world; ++k) {
+        // fixed order (rank 0 first) so that every rank adds the same numbers in the same order
+        uint4 raw[kRowMaxVec];
 #pragma unroll
-      for (int i = 0; i < kRowMaxVec; ++i) {
-        const int v = t + i * TPR;
-        if (active && v < nvec) {
+        for (int i = 0; i < kRowMaxVec; ++i) {
+          const int v = t + i * TPR;
+          if (active && v < nvec)
+            raw[i] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.peer_bufs[k]) + p.x_off +
+                                                           row_byte + (int64_t)v * 16));
+        }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) vals[i][j] = 0.f;
-          for (int k = 0; k < p.world; ++k) {
-            // fixed order (rank 0 first) so that every rank adds the same numbers in the same order
-            const uint4 u = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.peer_bufs[k]) +
-                                                                  p.x_off + row_byte + (int64_t)v * 16));
+        for (int i = 0; i < kRowMaxVec; ++i) {
+          const int v = t + i * TPR;
+          if (active && v < nvec) {
             float f[8];
-            unpack8(*reinterpret_cast<const bf16x8*>(&u), f);
+            unpack8(*reinterpret_cast<const bf16x8*>(&raw[i]), f);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) vals[i][j] += f[j];
+            for (int j = 0; j < 8; ++j) vals[i][j] = (k == 0 ? 0.f : vals[i][j]) + f[j];
           }
         }
       }
@@ -455,7 +470,7 @@ __global__ void __launch_bounds__(kRowThreads) tp_oneshot_norm_kernel(TpOneShotP
       if (active && v < nvec) {
         if (p.residual_in != nullptr) {
           float r[8];
-          unpack8(reinterpret_cast<const bf16x8*>(p.residual_in + row * p.H)[v], r);
+          unpack8(*reinterpret_cast<const bf16x8*>(&rres[i]), r);
 #pragma unroll
           for (int j = 0; j < 8; ++j) vals[i][j] += r[j];
         }

@@ -1212,8 +1212,9 @@ XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* b
     for (int p = 0; p < 2; ++p) {
       if (pair >= 0 && p != pair) continue;
       if (p == 1 && M <= kBM) continue;
-      for (int tn = 64; tn <= 256; tn <<= 1) {
+      for (int tn : {64, 128, 192, 256}) {
         if (tile_n != 0 && tn != tile_n) continue;
+        if (tn == 192 && w_packed) continue;
         const int rows = p ? 2 * kBM : kBM, units = p ? sms / 2 : sms;
         const long tiles = (long)((M + rows - 1) / rows) * ((N + tn - 1) / tn);
         const long waves = (tiles + units - 1) / units;

@@ -36,16 +36,27 @@ rmsnorm_kernel(bf16* __restrict__ out, uint8_t* __restrict__ out_q, float* __res
   const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
   pdl_wait();
   pdl_launch_dependents();  // dependents may be scheduled now; they block in their own pdl_wait()
+  // every load of the row is issued before the first store: a store to the residual would otherwise
+  // fence the loads behind it (the compiler cannot prove that x and residual do not overlap)
+  uint4 rx[kRowMaxVec], rr_in[kRowMaxVec];
+#pragma unroll
+  for (int i = 0; i < kRowMaxVec; ++i) {
+    const int v = t + i * TPR;
+    if (active && v < nvec) {
+      rx[i] = *reinterpret_cast<const uint4*>(xr + v);
+      if (rr) rr_in[i] = *reinterpret_cast<const uint4*>(rr + v);
+    }
+  }
   float vals[kRowMaxVec][8];
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < kRowMaxVec; ++i) {
     const int v = t + i * TPR;
     if (active && v < nvec) {
-      unpack8(xr[v], vals[i]);
+      unpack8(*reinterpret_cast<const bf16x8*>(&rx[i]), vals[i]);
       if (rr) {
         float r[8];
-        unpack8(rr[v], r);
+        unpack8(*reinterpret_cast<const bf16x8*>(&rr_in[i]), r);
 #pragma unroll
         for (int j = 0; j < 8; ++j) vals[i][j] += r[j];
         // the residual stream is kept in bf16: round once here so that the norm sees

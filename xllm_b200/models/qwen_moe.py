@@ -195,4 +195,8 @@ def _make_mlp(args, dtype, device, ps):
 
 @register_model("qwen3_moe", "qwen2_moe", "Qwen3MoeForCausalLM", "Qwen2MoeForCausalLM")
 def build_qwen_moe(args, dtype, device, ps):
-    return DenseCausalLM(args, dtype, device, ps, make_mlp=_make_mlp(args, dtype, device, ps))
+    m = DenseCausalLM(args, dtype, device, ps, make_mlp=_make_mlp(args, dtype, device, ps))
+    # with expert parallelism prompt chunks go through the all-to-all kernels, which are not captured:
+    # only decode-only steps replay graphs
+    m.supports_prefill_graph = not (ps is not None and ps.ep_size > 1)
+    return m
