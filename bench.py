@@ -11,13 +11,17 @@ Workload (config 2): Qwen3-8B-shaped bf16 decoder, random-init weights, 1024 req
 random token ids, input 1024 / output 512 with ignore_eos, at most 256 requests in flight (a closed
 loop: a finished request admits the next one), paged KV with block 16, CUDA graphs, TP = --gpus.
 The scheduler mixes decode rows and prompt chunks in one step (decode_first: every running sequence
-decodes, the rest of the token budget goes to prompt chunks), so a step costs one launch of one graph.
+decodes, the rest of the token budget goes to prompt chunks), so a step costs one launch of one graph;
+prompt work is batched: it is held back until 2048 prompt tokens are pending, because one 2048-token
+chunk every fourth step runs its GEMMs at the compute-bound rate while a 512-token chunk in every step
+does not.
 
 A "step" is one engine iteration: one scheduled batch -> one forward pass -> one sampled token per
 scheduled sequence.  Without --steps the whole workload is timed from a cold queue.  With --steps K
 exactly K steps of the workload's STEADY STATE are timed: a closed loop with requests of one length
 settles into a regime where, per step, every one of the 256 sequences decodes and 256/512 = 1/2 of a
-request finishes and is replaced, i.e. one 512-token prompt chunk per step.  The set-up (untimed)
+request finishes and is replaced, i.e. 512 prompt tokens per step on average (two 1024-token prompts
+every fourth step).  The set-up (untimed)
 builds that regime directly: 256 sequences whose remaining output lengths are staggered 2, 4, ... 512
 (their prompts carry the tokens "generated so far", so KV lengths are those of requests in mid
 flight).  Then W warm-up steps and K timed steps run it; finished requests are replaced by fresh
@@ -49,7 +53,7 @@ REF_UNAVAILABLE = ("reference cannot be installed offline: its setup.py rejects 
 
 # name -> (model preset, input_len, output_len, concurrency, requests, prompt chunk, parallelism)
 CONFIGS = {
-    "2": dict(model="qwen3-8b", input_len=1024, output_len=512, concurrency=256, requests=1024, chunk=512,
+    "2": dict(model="qwen3-8b", input_len=1024, output_len=512, concurrency=256, requests=1024, chunk=2048,
               parallelism="tp"),
     "3": dict(model="qwen3-32b", input_len=4096, output_len=256, concurrency=64, requests=256, chunk=2048,
               parallelism="tp"),
@@ -183,6 +187,7 @@ def run(args):
     conc = conc_total // world if ep else conc_total
     n_req = n_req_total // world if ep else n_req_total
     budget = args.max_tokens_per_batch or (conc + chunk)
+    min_prefill = chunk if args.prefill_batch < 0 else args.prefill_batch
     max_len = in_len + out_len + 16
     llm = LLM(args.model or cfg["model"], devices=str(dev), dtype="bfloat16", block_size=args.block_size,
               max_seqs_per_batch=conc, max_tokens_per_batch=max(budget, 4096 if args.steps > 0 else budget),
@@ -190,7 +195,8 @@ def run(args):
               enable_chunked_prefill=True, enable_schedule_overlap=not args.no_overlap,
               enable_graph=not args.no_graph, policy="decode_first", random_weights=True, parallel_state=ps,
               max_memory_utilization=args.max_memory_utilization, num_blocks=args.num_blocks,
-              dp_size=world if ep else 1, ep_size=world if ep else 1)
+              dp_size=world if ep else 1, ep_size=world if ep else 1, min_prefill_tokens=min_prefill,
+              max_prefill_wait_steps=16)
     eng = llm.engine
     vocab = eng.args.vocab_size
     sched = eng.scheduler
@@ -246,6 +252,8 @@ def run(args):
             if ev.request_finished:
                 counters["in_flight"] -= 1
         sched.reconfigure("decode_first", budget, conc, chunk)
+        # both shapes of the regime are captured before any step is timed
+        eng.runner.warmup([conc], prefill_tokens=[t for t in eng.runner.prefill_buckets if t >= min(chunk, budget - conc)][:1])
         counters["tokens"] = 0
     else:
         # graphs and kernels warm, nothing of the workload started
@@ -377,10 +385,11 @@ def run(args):
                        "concurrency": conc_total, "global_batch": conc_total, "seq_len": in_len + out_len,
                        "block_size": args.block_size, "parallelism": par, "cuda_graphs": not args.no_graph,
                        "schedule_overlap": not args.no_overlap, "policy": "decode_first",
-                       "tokens_per_step_budget": budget, "prefill_chunk": chunk,
+                       "tokens_per_step_budget": budget, "prefill_chunk": chunk, "min_prefill_tokens": min_prefill,
                        "window": ("whole workload from a cold queue" if not window else
                                   f"{steps} steps of the steady state of the closed loop: every step decodes the "
-                                  f"{conc_total} running sequences and prefills one {chunk}-token prompt chunk"),
+                                  f"running sequences (up to {conc_total}); finished requests are replaced, their prompts "
+                                  f"prefilled in chunks of up to {chunk} tokens once {min_prefill} prompt tokens are pending"),
                        "l2": "inputs larger than L2: every step streams the weights and the KV cache of all running "
                              "sequences (tens of GB)",
                        "output_tokens": out_tokens, "kv_blocks": eng.num_blocks},
@@ -438,7 +447,9 @@ def main():
     ap.add_argument("--input-len", type=int, default=0)
     ap.add_argument("--output-len", type=int, default=0)
     ap.add_argument("--concurrency", type=int, default=0)
-    ap.add_argument("--chunk", type=int, default=0, help="prompt tokens per chunk")
+    ap.add_argument("--chunk", type=int, default=0, help="prompt tokens per step (and per chunk)")
+    ap.add_argument("--prefill-batch", type=int, default=-1,
+                    help="hold prompt work back until this many prompt tokens are pending (-1: --chunk, 0: never hold)")
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--max-tokens-per-batch", type=int, default=0)
     ap.add_argument("--max-memory-utilization", type=float, default=0.9)

@@ -156,3 +156,42 @@ def test_image_generation_route(server):
     assert again["data"][0]["b64_json"] == data["data"][0]["b64_json"]      # the prompt seeds the noise
     st, err = _post(server.port, "/v1/images/generations", {"n": 1})
     assert st == 400
+
+
+def _raw(port, payload: bytes, read=True, timeout=10):
+    import socket
+    s = socket.create_connection(("127.0.0.1", port), timeout=timeout)
+    s.sendall(payload)
+    data = b""
+    if read:
+        try:
+            while True:
+                chunk = s.recv(65536)
+                if not chunk:
+                    break
+                data += chunk
+        except socket.timeout:
+            pass
+    s.close()
+    return data
+
+
+def test_malformed_requests_close_their_connection_only(server):
+    """A bad Content-Length, an oversized body announcement, a garbled request line and a megabyte
+    without an end of headers are each answered (or dropped) and closed; the serving thread lives on."""
+    port = server.port
+    r = _raw(port, b"POST /v1/completions HTTP/1.1\r\nHost: x\r\nContent-Length: abc\r\n\r\n")
+    assert r.startswith(b"HTTP/1.1 400") and b"Connection: close" in r
+    r = _raw(port, b"POST /v1/completions HTTP/1.1\r\nContent-Length: 99999999999999999999999\r\n\r\n")
+    assert r.startswith(b"HTTP/1.1 400")
+    r = _raw(port, b"POST /v1/completions HTTP/1.1\r\nContent-Length: 999999999999\r\n\r\n" + b"x" * 100000)
+    assert r.startswith(b"HTTP/1.1 413")          # answered and closed although the body kept coming
+    r = _raw(port, b"GARBAGE\r\n\r\n")
+    assert r.startswith(b"HTTP/1.1 400")
+    r = _raw(port, b"A" * (1 << 20) + b"B" * 4096)
+    assert r.startswith(b"HTTP/1.1 400") or r == b""
+    # still serving
+    c = http.client.HTTPConnection("127.0.0.1", port, timeout=30)
+    c.request("GET", "/health")
+    assert c.getresponse().status == 200
+    c.close()

@@ -76,3 +76,15 @@ def embed_token_lists(engine, token_lists: List[List[int]], normalize: bool = Tr
             v = v / v.norm().clamp_min(1e-12)
         out.append(v.cpu().tolist())
     return out
+
+
+class Embedding:
+    """Offline embedding entry point (xllm/pybind/embedding.py:28): `Embedding(model, ...).embed(prompts)`."""
+
+    def __init__(self, model: str = "tiny", **kw):
+        from .llm import LLM
+        kw.setdefault("enable_graph", False)
+        self.llm = LLM(model, **kw)
+
+    def embed(self, prompts, pooling_params=None):
+        return self.llm.embed(prompts, pooling_params)

@@ -37,6 +37,16 @@ class SamplingParams:
     echo: bool = False
 
 
+RequestParams = SamplingParams       # the reference's name for the per-request parameter bag (xllm_export.RequestParams)
+
+
+@dataclass
+class PoolingParams:
+    """Parameters of an embedding request (xllm/pybind/params.py PoolingParams)."""
+    normalize: bool = True
+    is_embeddings: bool = True
+
+
 @dataclass
 class BeamSearchParams:
     beam_width: int = 4
@@ -76,6 +86,25 @@ class RequestOutput:
     # host-clock timing of the request: ttft_ms (submission -> first token), tpot_ms (mean gap between
     # tokens), e2e_ms; filled by generate()
     metrics: Dict[str, float] = field(default_factory=dict)
+
+
+@dataclass
+class EmbeddingOutputs:
+    embedding: List[float] = field(default_factory=list)
+
+    @property
+    def embeddings(self):
+        return self.embedding
+
+
+@dataclass
+class EmbeddingOutput:
+    """Result of `LLM.embed` for one prompt (xllm/pybind/llm.py:64-80)."""
+    prompt: Optional[str]
+    outputs: EmbeddingOutputs
+    usage: Usage
+    request_output: Optional[RequestOutput] = None
+    status: Optional[object] = None
 
 
 class LLM:
@@ -241,6 +270,58 @@ class LLM:
                 for r in res:
                     r.text = self.tokenizer.decode(r.token_ids)
             outs.append(res)
+        return outs
+
+    def embed(self, prompts, pooling_params: Union[PoolingParams, List[PoolingParams], None] = None) -> List[EmbeddingOutput]:
+        """Pooled embedding (final-norm hidden state of the last token, L2-normalised unless the
+        pooling parameters say otherwise) of every prompt: xllm/pybind/llm.py:386-406."""
+        from .embedding import embed_token_lists
+        if isinstance(prompts, (str, torch.Tensor)) or (prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        pps = pooling_params if isinstance(pooling_params, list) else [pooling_params or PoolingParams()] * len(prompts)
+        outs = []
+        for p, pp in zip(prompts, pps):
+            ids = self._encode(p)
+            vec = embed_token_lists(self.engine, [ids], normalize=pp.normalize)[0]
+            ro = RequestOutput(f"embed-{next(LLM._ids)}", p if isinstance(p, str) else None, ids, finished=True)
+            ro.usage = Usage(len(ids), 0, len(ids), 0)
+            outs.append(EmbeddingOutput(ro.prompt, EmbeddingOutputs(vec), ro.usage, ro))
+        return outs
+
+    def sample(self, prompts, selector, logprobs: int = 5) -> List[RequestOutput]:
+        """For every occurrence of the `selector` token in a prompt, the `logprobs` most likely tokens
+        to follow it (one forward pass per prompt, nothing is generated): xllm/pybind/llm.py:452-519.
+        `selector` is a special-token string (needs a tokenizer), a {"type": "literal", "value": ...}
+        dict, a token id, or one of those per prompt.  Each occurrence becomes one SequenceOutput
+        whose `top_logprobs[0]` lists (token id, logprob) pairs, most likely first."""
+        from .embedding import next_token_logprobs
+        if isinstance(prompts, (str, torch.Tensor)) or (prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        sels = selector if isinstance(selector, (list, tuple)) else [selector] * len(prompts)
+        if len(sels) != len(prompts):
+            raise ValueError("selector count must match prompts count")
+        outs = []
+        for p, sel in zip(prompts, sels):
+            ids = self._encode(p)
+            if isinstance(sel, dict):
+                if sel.get("type", "literal") != "literal" or not sel.get("value"):
+                    raise ValueError("selector must be {'type': 'literal', 'value': <token>}")
+                sel = sel["value"]
+            if isinstance(sel, str):
+                sid = self._encode(sel)
+                if len(sid) != 1:
+                    raise ValueError("selector.value must be a stable single special token")
+                sel = sid[0]
+            slots = [i for i, t in enumerate(ids) if t == int(sel)]
+            ro = RequestOutput(f"sample-{next(LLM._ids)}", p if isinstance(p, str) else None, ids, finished=True)
+            ro.usage = Usage(len(ids), 0, len(ids), 0)
+            if slots:
+                for j, alts in enumerate(next_token_logprobs(self.engine, ids, slots, logprobs)):
+                    so = SequenceOutput(j, token_ids=[alts[0][0]], finish_reason="length", logprobs=[alts[0][1]],
+                                        top_logprobs=[alts])
+                    so.text = self._decode(so.token_ids)
+                    ro.outputs.append(so)
+            outs.append(ro)
         return outs
 
     def sleep(self, level: int = 1):

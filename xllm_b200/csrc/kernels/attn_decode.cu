@@ -17,6 +17,7 @@
 // Scratch: when splits > 1 the normalised partial outputs and their log2-sum-exp go to
 // caller-provided fp32 workspaces and `xllm_attn_merge` combines them.
 #include "attn_common.cuh"
+#include <atomic>
 
 namespace xllm {
 
@@ -253,14 +254,14 @@ __global__ void attn_merge_kernel(bf16* __restrict__ out, const float* __restric
 template <int D, int STAGES>
 static int launch_decode(const DecodeParams& p, int batch, cudaStream_t s) {
   constexpr int SMEM = 4 * STAGES * 2 * 16 * D * 2;
-  static bool attr_done[64] = {};
+  static std::atomic<bool> attr_done[64] = {};   // first calls from several host threads may coincide
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!attr_done[dev & 63]) {
+  if (!attr_done[dev & 63].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<D, STAGES>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
-    attr_done[dev & 63] = true;
+    attr_done[dev & 63].store(true, std::memory_order_release);
   }
   const int qtiles = (p.group + 15) / 16;
   dim3 grid(p.nkv * qtiles, batch, p.splits);
@@ -320,6 +321,7 @@ XLLM_API int xllm_attn_merge(void* out, const void* o_part, const void* lse_part
 // Allocation-free variant (declared in no_alloc.h, which states who needs it and the contract).
 // The split-KV partials live in this file-scope array instead of a caller-provided workspace.
 #include "no_alloc.h"
+#include <atomic>
 #include <cstdio>
 
 namespace xllm {
@@ -327,7 +329,9 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[XLLM_NO_ALLOC_S
 // Device address of the array, per device.  In host code `g_noalloc_scratch` is only a handle of
 // the symbol — passing it to a kernel would hand the GPU a host address — so the address is
 // resolved once per device with cudaGetSymbolAddress and cached here.
-static float* g_noalloc_ptr[64] = {};
+// Published with release / read with acquire: two host threads may make their first call on a device
+// at the same time; both would store the same address.
+static std::atomic<float*> g_noalloc_ptr[64] = {};
 static thread_local char g_noalloc_msg[192] = "";
 }  // namespace xllm
 
@@ -340,7 +344,14 @@ XLLM_API int xllm_paged_decode_attn_noalloc(void* out, const void* q, int64_t q_
   using namespace xllm;
   g_noalloc_msg[0] = 0;
   if (batch == 0) return 0;
-  if (nkv <= 0 || nq % nkv != 0 || page_size % 16 != 0 || splits < 1) return (int)cudaErrorInvalidValue;
+  // every argument is checked before the first CUDA call
+  if (batch < 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || page_size % 16 != 0 || splits < 1 ||
+      (d != 64 && d != 128 && d != 256)) {
+    snprintf(g_noalloc_msg, sizeof(g_noalloc_msg),
+             "bad argument: batch %d, heads %d / %d, head_dim %d (64, 128 or 256), page %d, splits %d", batch, nq, nkv,
+             d, page_size, splits);
+    return (int)cudaErrorInvalidValue;
+  }
   const long long need = splits > 1 ? (long long)batch * nq * splits * (d + 1) * 4 : 0;
   if (need > (long long)XLLM_NO_ALLOC_SCRATCH_BYTES) {
     snprintf(g_noalloc_msg, sizeof(g_noalloc_msg),
@@ -354,15 +365,18 @@ XLLM_API int xllm_paged_decode_attn_noalloc(void* out, const void* q, int64_t q_
     snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "no current CUDA device (or device index >= 64)");
     return XLLM_NO_ALLOC_SETUP_FAILED;
   }
-  if (g_noalloc_ptr[dev] == nullptr) {
-    // set-up, once per device, with that device current
+  float* scratch = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
+    // set-up, once per device, with that device current.  With CUDA's lazy module loading this is
+    // also the moment the driver loads the kernel image and gives the array its device memory.
     void* p = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (e != cudaSuccess || p == nullptr) {
       snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
       return XLLM_NO_ALLOC_SETUP_FAILED;
     }
-    g_noalloc_ptr[dev] = static_cast<float*>(p);
+    scratch = static_cast<float*>(p);
+    g_noalloc_ptr[dev].store(scratch, std::memory_order_release);
   }
   DecodeParams p;
   p.q = (const bf16*)q; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
@@ -370,7 +384,7 @@ XLLM_API int xllm_paged_decode_attn_noalloc(void* out, const void* q, int64_t q_
   p.out = (bf16*)out; p.q_stride = q_stride; p.bt_stride = bt_stride; p.nq = nq; p.nkv = nkv;
   p.group = nq / nkv; p.page_size = page_size; p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f;
-  p.o_part = splits > 1 ? g_noalloc_ptr[dev] : nullptr;
+  p.o_part = splits > 1 ? scratch : nullptr;
   p.lse_part = p.o_part ? p.o_part + (int64_t)batch * nq * splits * d : nullptr;
   cudaStream_t s = (cudaStream_t)stream;
   int rc;

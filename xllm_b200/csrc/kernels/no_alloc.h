@@ -10,9 +10,15 @@
 //
 // What it does: the same paged GQA decode attention as xllm_paged_decode_attn, but the partial
 // outputs and log-sum-exps of the KV splits are kept in a fixed array that lives inside the
-// library image (file scope, `static __device__`).  Every GPU that loads the library holds that
-// array (XLLM_NO_ALLOC_SCRATCH_BYTES, 8 MiB) until the process exits.  The caller still passes
-// every input and the output.
+// library image (file scope, `static __device__`).  Every GPU on which the library's kernels are
+// loaded holds that array (XLLM_NO_ALLOC_SCRATCH_BYTES, 8 MiB) until the process exits.  The caller
+// still passes every input and the output.
+//
+// When the memory is taken: CUDA loads modules lazily by default, so the array (and the kernel
+// image) get their device memory when the library is first USED on a device, not when the shared
+// object is opened.  A host that freezes its memory budget, or that must not see driver-side
+// allocation later, makes one call of this entry point per device at start-up (or runs with
+// CUDA_MODULE_LOADING=EAGER); from then on calls neither allocate nor load anything.
 //
 // Contract:
 //   * nothing is allocated or freed, by this call or by anything it calls;
@@ -20,8 +26,11 @@
 //     XLLM_NO_ALLOC_SCRATCH_BYTES is refused with XLLM_NO_ALLOC_TOO_LARGE and the reason can be
 //     read with xllm_no_alloc_last_error();
 //   * the first call on a device looks up the device address of the array (one
-//     cudaGetSymbolAddress, with that device current).  Make that first call outside of any
-//     stream capture;
+//     cudaGetSymbolAddress, with that device current), sets the kernel's shared-memory attribute
+//     and triggers the driver's module load.  Make that first call at start-up, outside of any
+//     stream capture and before a memory budget is frozen.  It is safe from several host threads
+//     at once;
+//   * arguments are validated before any CUDA call: head_dim must be 64, 128 or 256, batch > 0;
 //   * all calls on a device share the one array, which keeps whatever the previous call left in
 //     it.  The kernels overwrite every slot they later read, so nothing has to be cleared between
 //     calls — but two calls that overlap in time on the same GPU (different streams) race on it.

@@ -143,6 +143,8 @@ PYBIND11_MODULE(_rt, m) {
       .def_readwrite("num_speculative_tokens", &SchedulerConfig::num_speculative_tokens)
       .def_readwrite("max_decode_batch", &SchedulerConfig::max_decode_batch)
       .def_readwrite("max_running_seqs", &SchedulerConfig::max_running_seqs)
+      .def_readwrite("min_prefill_tokens", &SchedulerConfig::min_prefill_tokens)
+      .def_readwrite("max_prefill_wait_steps", &SchedulerConfig::max_prefill_wait_steps)
       .def_readwrite("hold_finished_blocks", &SchedulerConfig::hold_finished_blocks);
 
   py::enum_<PauseMode>(m, "PauseMode")
@@ -404,6 +406,8 @@ PYBIND11_MODULE(_rt, m) {
            })
       .def("take_pending_events", &Scheduler::take_pending_events)
       .def("take_preempted", &Scheduler::take_preempted)
+      .def("set_prefill_batching", &Scheduler::set_prefill_batching, py::arg("min_prefill_tokens"),
+           py::arg("max_prefill_wait_steps") = 0)
       .def("reconfigure", &Scheduler::reconfigure, py::arg("policy") = "", py::arg("max_tokens_per_batch") = 0,
            py::arg("max_seqs_per_batch") = 0, py::arg("max_tokens_per_chunk_for_prefill") = 0)
       .def("pause", &Scheduler::pause)

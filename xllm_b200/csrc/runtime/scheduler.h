@@ -54,6 +54,13 @@ struct SchedulerConfig {
   // per-step sequence budget does not bound it: with prefill_first the running set grows over
   // successive steps.  Models with per-sequence state slots size their pool by this number.
   int32_t max_running_seqs = 0;
+  // Prompt batching for the mixing policies (decode_first / unified): while sequences are decoding,
+  // prompt chunks are only scheduled once at least `min_prefill_tokens` prompt tokens are pending,
+  // or after `max_prefill_wait_steps` steps of holding them back.  Large prompt batches run the
+  // GEMMs at their compute-bound rate; a trickle of small chunks makes every step pay for a
+  // mid-size GEMM.  0 = schedule prompt work as soon as it exists.
+  int32_t min_prefill_tokens = 0;
+  int32_t max_prefill_wait_steps = 8;
   // PD disaggregation, prefill side: a sequence that finishes keeps its KV blocks until
   // release_held() so that they can be pushed to the decode instance first.
   bool hold_finished_blocks = false;
@@ -120,6 +127,10 @@ class Scheduler {
     if (max_tokens_per_batch > 0) cfg_.max_tokens_per_batch = max_tokens_per_batch;
     if (max_seqs_per_batch > 0) cfg_.max_seqs_per_batch = max_seqs_per_batch;
     if (max_tokens_per_chunk_for_prefill != 0) cfg_.max_tokens_per_chunk_for_prefill = max_tokens_per_chunk_for_prefill;
+  }
+  void set_prefill_batching(int32_t min_prefill_tokens, int32_t max_prefill_wait_steps) {
+    cfg_.min_prefill_tokens = min_prefill_tokens;
+    if (max_prefill_wait_steps > 0) cfg_.max_prefill_wait_steps = max_prefill_wait_steps;
   }
   BlockManager& block_manager(int dp = 0) { return *bm_[dp]; }
 
@@ -704,6 +715,22 @@ class Scheduler {
       if (prefills.empty()) try_decode();
     } else {
       try_decode();
+      if (cfg_.min_prefill_tokens > 0 && prompt_work && !decodes.empty()) {
+        // hold small amounts of prompt work back while the step has decode rows anyway
+        int64_t pending = 0;
+        for (Sequence* s : run)
+          if (s->stage == SeqStage::PREFILL && s->in_flight == 0) pending += s->num_tokens() - s->kv_computed;
+        if (!admit_blocked_)
+          for (Sequence* s : waiting_) {
+            pending += s->num_tokens();
+            if (pending >= cfg_.min_prefill_tokens) break;
+          }
+        if (pending < cfg_.min_prefill_tokens && prefill_held_steps_ < cfg_.max_prefill_wait_steps) {
+          ++prefill_held_steps_;
+          return build_batch(dp, decodes, prefills);
+        }
+      }
+      prefill_held_steps_ = 0;
       if (cfg_.policy == "unified") {
         // prompt work ordered by deadline (earliest first), the configured order otherwise
         std::stable_sort(waiting_.begin(), waiting_.end(), [&](Sequence* a, Sequence* b) {
@@ -808,6 +835,7 @@ class Scheduler {
   std::vector<OutputEvent> pending_events_;
   std::vector<int64_t> preempted_ids_;
   int64_t next_seq_id_ = 0, next_batch_id_ = 0, preemptions_ = 0;
+  int32_t prefill_held_steps_ = 0;
   bool paused_ = false, admit_blocked_ = false, pause_mode_active_ = false;
   PauseMode pause_mode_ = PauseMode::KEEP;
 };

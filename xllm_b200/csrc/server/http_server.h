@@ -193,24 +193,48 @@ class HttpServer {
     }
   }
 
+  // Full-string, range-checked decimal parse of a Content-Length value (no exceptions).
+  static bool parse_length(const std::string& v, size_t* out) {
+    size_t b = 0, e = v.size();
+    while (b < e && (v[b] == ' ' || v[b] == '\t')) ++b;
+    while (e > b && (v[e - 1] == ' ' || v[e - 1] == '\t' || v[e - 1] == '\r')) --e;
+    if (b == e || e - b > 18) return false;
+    size_t n = 0;
+    for (size_t i = b; i < e; ++i) {
+      if (v[i] < '0' || v[i] > '9') return false;
+      n = n * 10 + (size_t)(v[i] - '0');
+    }
+    *out = n;
+    return true;
+  }
+
+  // Answer `status` and close: the reply is queued, input is dropped from now on, and the caller
+  // flushes (flush() closes the connection once the reply is out).  mu_ is held by the caller.
+  void reject(Conn& c, int status) {
+    c.out += status_line(status) + "Content-Length: 0\r\nConnection: close\r\n\r\n";
+    c.close_after = true;
+    c.in.clear();
+  }
+
   // Parse as many complete requests as the buffer holds (one at a time per connection: the next
   // request of a keep-alive connection is parsed after the current one was answered).
-  void try_parse(int fd) {
+  // Returns true when the connection has something to send (a rejection) and must be flushed.
+  bool try_parse(int fd) {
     std::unique_lock<std::mutex> lk(mu_);
     auto it = conns_.find(fd);
-    if (it == conns_.end()) return;
+    if (it == conns_.end()) return false;
     Conn& c = it->second;
-    if (c.active_req != 0) return;
+    if (c.active_req != 0 || c.close_after) return false;
     const size_t he = c.in.find("\r\n\r\n");
     if (he == std::string::npos) {
-      if (c.in.size() > (1u << 20)) c.close_after = true;
-      return;
+      if (c.in.size() > (1u << 20)) { reject(c, 400); return true; }   // no end of headers within 1 MiB
+      return false;
     }
     HttpRequest req;
     size_t line_end = c.in.find("\r\n");
     const std::string first = c.in.substr(0, line_end);
     const size_t s1 = first.find(' '), s2 = first.rfind(' ');
-    if (s1 == std::string::npos || s2 == s1) { c.close_after = true; return; }
+    if (s1 == std::string::npos || s2 == s1) { reject(c, 400); return true; }
     req.method = first.substr(0, s1);
     std::string target = first.substr(s1 + 1, s2 - s1 - 1);
     const size_t q = target.find('?');
@@ -225,17 +249,16 @@ class HttpServer {
       if (colon != std::string::npos) {
         std::string k = line.substr(0, colon), v = line.substr(colon + 1);
         while (!v.empty() && v.front() == ' ') v.erase(0, 1);
-        if (strcasecmp(k.c_str(), "content-length") == 0) content_length = (size_t)std::stoull(v);
+        if (strcasecmp(k.c_str(), "content-length") == 0 && !parse_length(v, &content_length)) {
+          reject(c, 400);
+          return true;
+        }
         req.headers.emplace_back(std::move(k), std::move(v));
       }
       pos = e + 2;
     }
-    if (content_length > max_body_) {
-      c.out += status_line(413) + "Content-Length: 0\r\nConnection: close\r\n\r\n";
-      c.close_after = true;
-      return;
-    }
-    if (c.in.size() < he + 4 + content_length) return;  // body still arriving
+    if (content_length > max_body_) { reject(c, 413); return true; }
+    if (c.in.size() < he + 4 + content_length) return false;  // body still arriving
     req.body = c.in.substr(he + 4, content_length);
     c.in.erase(0, he + 4 + content_length);
     req.id = next_id_++;
@@ -244,6 +267,7 @@ class HttpServer {
     inbox_.push_back(std::move(req));
     lk.unlock();
     cv_.notify_all();
+    return false;
   }
 
   void flush(int fd) {
@@ -272,6 +296,21 @@ class HttpServer {
       const int n = epoll_wait(epfd_, evs.data(), (int)evs.size(), 200);
       for (int i = 0; i < n; ++i) {
         const int fd = evs[i].data.fd;
+        // nothing a single connection sends may end the serving thread: an exception raised while
+        // its event is handled closes that connection only
+        try {
+          handle_event(fd, evs[i].events);
+        } catch (...) {
+          if (fd != listen_fd_ && fd != wake_fd_) close_conn(fd);
+        }
+      }
+      drain_outbox();
+    }
+  }
+
+  void handle_event(int fd, uint32_t events) {
+    {
+      {
         if (fd == listen_fd_) {
           while (true) {
             const int cfd = ::accept4(listen_fd_, nullptr, nullptr, SOCK_NONBLOCK);
@@ -281,15 +320,15 @@ class HttpServer {
             { std::lock_guard<std::mutex> lk(mu_); conns_[cfd]; }
             add_fd(cfd, EPOLLIN);
           }
-          continue;
+          return;
         }
         if (fd == wake_fd_) {
           uint64_t v;
           while (::read(wake_fd_, &v, sizeof(v)) > 0) {}
-          continue;
+          return;
         }
-        if (evs[i].events & (EPOLLHUP | EPOLLERR)) { close_conn(fd); continue; }
-        if (evs[i].events & EPOLLIN) {
+        if (events & (EPOLLHUP | EPOLLERR)) { close_conn(fd); return; }
+        if (events & EPOLLIN) {
           char buf[65536];
           bool closed = false;
           while (true) {
@@ -297,19 +336,25 @@ class HttpServer {
             if (r > 0) {
               std::lock_guard<std::mutex> lk(mu_);
               auto it = conns_.find(fd);
-              if (it != conns_.end()) it->second.in.append(buf, (size_t)r);
+              // a connection that is being closed takes no more input (its buffer must not grow)
+              if (it != conns_.end() && !it->second.close_after) it->second.in.append(buf, (size_t)r);
               continue;
             }
             if (r == 0) closed = true;
             else if (errno != EAGAIN && errno != EWOULDBLOCK) closed = true;
             break;
           }
-          if (closed) { close_conn(fd); continue; }
-          try_parse(fd);
+          if (closed) { close_conn(fd); return; }
+          if (try_parse(fd)) flush(fd);
         }
-        if (evs[i].events & EPOLLOUT) flush(fd);
+        if (events & EPOLLOUT) flush(fd);
       }
-      // move queued responses into their connections
+    }
+  }
+
+  // move queued responses into their connections
+  void drain_outbox() {
+    {
       std::vector<int> touched;
       {
         std::lock_guard<std::mutex> lk(mu_);
@@ -327,7 +372,7 @@ class HttpServer {
       }
       for (int fd : touched) {
         flush(fd);
-        try_parse(fd);  // a pipelined request may already be buffered
+        if (try_parse(fd)) flush(fd);  // a pipelined request may already be buffered
       }
     }
   }

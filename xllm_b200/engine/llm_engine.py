@@ -62,6 +62,8 @@ class EngineConfig:
     draft_model: str = ""
     mla_latent_cache: bool = False      # MLA models: cache [c_kv | k_pe] rows (576 values per token) instead of per-head K/V
     activation_reserve_bytes: int = 0   # 0: estimated from max_tokens_per_batch
+    min_prefill_tokens: int = 0         # mixing policies: hold prompt chunks back until this many prompt tokens are pending
+    max_prefill_wait_steps: int = 8     # ... or this many steps have passed
     max_running_seqs: int = 0           # cap on sequences holding KV / state at once; 0: no cap (state models: max_seqs_per_batch + 1)
 
 
@@ -143,6 +145,13 @@ class LLMEngine:
                                                    head_dim=getattr(self.model, "head_dim", None),
                                                    planes=int(getattr(self.model, "kv_planes", 2)))
         num_blocks = cfg.num_blocks or self._estimate_blocks(per_block)
+        if self.ps.world_size > 1 and self.ps.tp_size > 1:
+            # every tensor-parallel rank runs the same scheduler: they must agree on the size of the
+            # cache, so the smallest estimate wins (free memory differs by a few MB between GPUs)
+            import torch.distributed as dist
+            t = torch.tensor([num_blocks], dtype=torch.int64, device=self.device if self.device.type == "cuda" else "cpu")
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.ps.tp_group)
+            num_blocks = int(t.item())
         self.num_blocks = num_blocks
         self.runner = ModelRunner(self.model, cfg.block_size, num_blocks, cfg.max_seqs_per_batch,
                                   cfg.max_tokens_per_batch, max_len, self.device, self.dtype,
@@ -172,6 +181,8 @@ class LLMEngine:
         sc.enable_schedule_overlap = cfg.enable_schedule_overlap
         sc.dp_size = 1  # one scheduler instance per DP replica
         sc.num_speculative_tokens = cfg.num_speculative_tokens
+        sc.min_prefill_tokens = cfg.min_prefill_tokens
+        sc.max_prefill_wait_steps = cfg.max_prefill_wait_steps
         sc.max_running_seqs = getattr(self, "state_slots", 0) or cfg.max_running_seqs
         sc.hold_finished_blocks = hold_finished_blocks   # PD disaggregation, prefill side
         self.scheduler = rt.Scheduler(sc)

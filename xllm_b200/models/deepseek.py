@@ -273,6 +273,8 @@ class MTPDraft(Module):
         return self.lm_head(hidden_rows)
 
 
-@register_model("deepseek_v2", "deepseek_v3", "deepseek_v32", "kimi_k2", "DeepseekV2ForCausalLM", "DeepseekV3ForCausalLM")
+# DeepSeek-V3.2 is not registered: its sparse attention (the DSA indexer) is not implemented, and running
+# such a checkpoint with dense attention would silently compute something else.
+@register_model("deepseek_v2", "deepseek_v3", "kimi_k2", "DeepseekV2ForCausalLM", "DeepseekV3ForCausalLM")
 def build_deepseek(args, dtype, device, ps):
     return DeepseekCausalLM(args, dtype, device, ps)
