@@ -29,8 +29,8 @@ flight).  Then W warm-up steps and K timed steps run it; finished requests are r
 barrier + synchronize, max over ranks.  TTFT / TPOT are host clock: submission -> first token
 on the host, and the mean gap between a request's tokens.
 
-The `e2e` block runs the same kind of requests (same shape, same concurrency, full output length)
-through the public API (`LLM.generate`) on the host clock; every step of both runs copies its inputs
+The `e2e` block runs the whole workload (all requests, same shape, same concurrency, full output
+length, from a cold queue) through the public API (`LLM.generate`) on the host clock; every step of both runs copies its inputs
 from pinned host memory and reads the sampled tokens back.
 
 `--impl reference` is the arm for the unmodified upstream engine; it cannot be installed offline,
@@ -344,7 +344,7 @@ def run(args):
     eng.drain()
     e2e = None
     if not args.no_e2e:
-        n_e2e = n_req if not window else conc
+        n_e2e = n_req if args.e2e_requests <= 0 else min(n_req, args.e2e_requests)
         reqs2 = make_requests(n_e2e, in_len, vocab, 200 + rank)
         prompts = [reqs2[i] for i in range(n_e2e)]  # pinned host tensors handed to the public API
         sp = SamplingParams(max_tokens=out_len, temperature=0.0, ignore_eos=True)
@@ -457,6 +457,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-requests", type=int, default=0, help="requests of the end-to-end run (0: the whole workload)")
     ap.add_argument("--profile", type=int, default=0, help="print a per-kernel breakdown of this many steps first")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -40,7 +40,7 @@ def test_fused_allreduce_norm(multimem):
 @pytest.mark.parametrize("multimem", ["1", "0"])
 def test_oneshot_allreduce_norm_argmax_gather(multimem):
     """One-shot fused all-reduce (+residual +RMSNorm), sharded arg-max and logits gather; eager and graph."""
-    env = {"XLLM_TP_MULTIMEM": multimem}
+    env = {"XLLM_TP_MULTIMEM": multimem, "XLLM_TP_ONESHOT_TOKENS": "4096"}   # the one-shot form at every size tested
     if multimem == "0":
         env["XLLM_TP_ONESHOT_TOKENS_P2P"] = "2048"     # exercise the peer-load form at every size
     out = _run("mp_tp_oneshot.py", min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2, env)

@@ -17,9 +17,11 @@
 //   epilogue   + residual shard (kept only by the owner, updated in place), RMSNorm, * weight
 //   broadcast  the normalised rows go to every rank's `out`: one `multimem.st`, or a store per peer
 //   barrier 2  every rank's `out` is complete; partial buffers may be overwritten
-// A barrier is a flag exchange through the symmetric signal pad done by one CTA per rank (a growing
-// epoch stored into slot [my rank] of every peer, then a wait on the own slots); the other CTAs of
-// the grid synchronise with that CTA through device-local flags.  Every wait is bounded;
+// A barrier is a flag exchange through the symmetric signal pad: a growing epoch stored into slot
+// [my rank] of every peer by one CTA, then a wait on the own slots.  For the opening barrier EVERY CTA
+// polls the own slots (local memory), so no CTA waits for another CTA of its grid and the grid may be
+// of any size; the closing one is run by the last CTA to finish.  Rows are spread over thread groups
+// (rowops.cuh), several rows per CTA.  Every wait is bounded;
 // when the budget runs out the kernel sets an error word and carries on (results are then
 // undefined, the GPU stays healthy and the host can see the error).  Epoch counters live in device
 // memory and are advanced by the kernel itself, so the launch can be replayed from a CUDA graph.
@@ -100,129 +102,6 @@ __device__ __forceinline__ void multimem_st_16(uint64_t mc_addr, uint4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
                "r"(v.z), "r"(v.w)
                : "memory");
-}
-
-__global__ void __launch_bounds__(kCommThreads) tp_allreduce_norm_kernel(TpNormParams p) {
-  __shared__ float red[32];
-  __shared__ int s_last;
-  volatile uint32_t* state = p.epochs;
-  const uint32_t e0 = state[0];
-  const int S = (p.T + p.world - 1) / p.world;
-  const int row_begin = p.rank * S;
-  const int row_end = min(row_begin + S, p.T);
-  const int nvec = p.H >> 3;
-  pdl_wait();
-  // ---- barrier 1: CTA 0 talks to the peers, the other CTAs wait for its local "go"
-  if (blockIdx.x == 0) {
-    exchange_flags(p, e0 + 1);
-    if (threadIdx.x == 0) {
-      __threadfence();
-      state[1] = e0 + 1;
-    }
-  } else {
-    if (threadIdx.x == 0) {
-      const long long t0 = clock64();
-      while (state[1] != e0 + 1) {
-        if (clock64() - t0 > p.budget) {
-          atomicExch(p.err, 100);
-          break;
-        }
-      }
-      __threadfence();
-    }
-    __syncthreads();
-  }
-
-  for (int row = row_begin + blockIdx.x; row < row_end; row += gridDim.x) {
-    float vals[kCommMaxVec][8];
-    float ss = 0.f;
-    const int64_t row_byte = (int64_t)row * p.H * 2;
-#pragma unroll
-    for (int i = 0; i < kCommMaxVec; ++i) {
-      const int v = threadIdx.x + i * kCommThreads;
-      if (v < nvec) {
-        const int64_t off = p.x_off + row_byte + (int64_t)v * 16;
-        if (p.mc_base != 0) {
-          const uint4 u = multimem_ld_reduce_bf16x8(p.mc_base + off);
-          unpack8(*reinterpret_cast<const bf16x8*>(&u), vals[i]);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) vals[i][j] = 0.f;
-          for (int k = 0; k < p.world; ++k) {
-            const int peer = (p.rank + k) % p.world;  // start at home, spread the link load
-            const bf16x8 u = *reinterpret_cast<const bf16x8*>(reinterpret_cast<const uint8_t*>(p.peer_bufs[peer]) + off);
-            float f[8];
-            unpack8(u, f);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) vals[i][j] += f[j];
-          }
-        }
-        if (p.mode == 1) {
-          bf16x8* rr = reinterpret_cast<bf16x8*>(p.residual + (int64_t)(row - row_begin) * p.H) + v;
-          float r[8];
-          unpack8(*rr, r);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) vals[i][j] += r[j];
-          const bf16x8 nr = pack8(vals[i]);  // the residual stream is bf16: round once
-          *rr = nr;
-          unpack8(nr, vals[i]);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
-        }
-      }
-    }
-    float inv = 1.f;
-    if (p.mode == 1) {
-      ss = block_sum(ss, red);
-      inv = rsqrtf(ss / (float)p.H + p.eps);
-    }
-#pragma unroll
-    for (int i = 0; i < kCommMaxVec; ++i) {
-      const int v = threadIdx.x + i * kCommThreads;
-      if (v < nvec) {
-        float o[8];
-        if (p.mode == 1) {
-          float w[8];
-          unpack8(reinterpret_cast<const bf16x8*>(p.weight)[v], w);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * inv * w[j];
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = vals[i][j];
-        }
-        const bf16x8 ob = pack8(o);
-        const uint4 u = *reinterpret_cast<const uint4*>(&ob);
-        const int64_t off = p.out_off + row_byte + (int64_t)v * 16;
-        if (p.mc_base != 0) {
-          multimem_st_16(p.mc_base + off, u);
-        } else {
-          for (int k = 0; k < p.world; ++k) {
-            const int peer = (p.rank + k) % p.world;
-            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.peer_bufs[peer]) + off) = u;
-          }
-        }
-      }
-    }
-  }
-  // ---- barrier 2: the last CTA to finish tells the peers and waits for theirs, so that the
-  // completion of this kernel means `out` is complete on this rank
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    const unsigned prev = atomicAdd(const_cast<uint32_t*>(&state[2]), 1u);
-    s_last = prev == gridDim.x - 1;
-    __threadfence();
-  }
-  __syncthreads();
-  if (s_last) {
-    exchange_flags(p, e0 + 2);
-    if (threadIdx.x == 0) {
-      state[2] = 0;
-      state[0] = e0 + 2;
-      __threadfence();
-    }
-  }
-  pdl_launch_dependents();
 }
 
 // Closing exchange shared by both kernels: the last CTA to finish tells the peers and waits for
@@ -519,6 +398,155 @@ __global__ void __launch_bounds__(kRowThreads) tp_oneshot_norm_kernel(TpOneShotP
 }
 
 // ------------------------------------------------------------------------------------------------
+//   two-shot kernel of xllm_tp_allreduce_norm (algorithm in the header of this file)
+template <int TPR>
+__global__ void __launch_bounds__(kRowThreads) tp_twoshot_norm_kernel(TpNormParams p) {
+  __shared__ float red[8];
+  __shared__ int s_last;
+  constexpr int R = kRowThreads / TPR;
+  const int t = threadIdx.x % TPR;
+  const int nvec = p.H >> 3;
+  const int S = (p.T + p.world - 1) / p.world;
+  const int row_begin = p.rank * S;
+  const int row_end = min(row_begin + S, p.T);
+  pdl_wait();
+  const uint32_t e0 = *reinterpret_cast<volatile uint32_t*>(p.epochs);
+  if (blockIdx.x == 0 && threadIdx.x < p.world)
+    st_release_sys(reinterpret_cast<uint32_t*>(p.signal_pads[threadIdx.x]) + p.sig_off + p.rank, e0 + 1);
+  bool waited = false;
+  for (int64_t row0 = row_begin + (int64_t)blockIdx.x * R; row0 < row_end; row0 += (int64_t)gridDim.x * R) {
+    const int64_t row = row0 + threadIdx.x / TPR;
+    const bool active = row < row_end;
+    const int64_t row_byte = row * p.H * 2;
+    uint4 rres[kRowMaxVec];
+    if (p.mode == 1) {
+#pragma unroll
+      for (int i = 0; i < kRowMaxVec; ++i) {
+        const int v = t + i * TPR;
+        if (active && v < nvec) rres[i] = *(reinterpret_cast<const uint4*>(p.residual + (row - row_begin) * p.H) + v);
+      }
+    }
+    if (!waited) {
+      wait_flags(p.signal_pads, p.sig_off, p.rank, p.world, e0 + 1, p.budget, p.err, 1);
+      __syncthreads();
+      waited = true;
+    }
+    float vals[kRowMaxVec][8];
+    float ss = 0.f;
+    if (p.mc_base != 0) {
+      uint4 raw[kRowMaxVec];
+#pragma unroll
+      for (int i = 0; i < kRowMaxVec; ++i) {
+        const int v = t + i * TPR;
+        if (active && v < nvec) raw[i] = multimem_ld_reduce_bf16x8(p.mc_base + p.x_off + row_byte + (int64_t)v * 16);
+      }
+#pragma unroll
+      for (int i = 0; i < kRowMaxVec; ++i) {
+        const int v = t + i * TPR;
+        if (active && v < nvec) unpack8(*reinterpret_cast<const bf16x8*>(&raw[i]), vals[i]);
+      }
+    } else {
+      for (int k = 0; k < p.world; ++k) {
+        const int peer = (p.rank + k) % p.world;  // start at home, spread the link load
+        uint4 raw[kRowMaxVec];
+#pragma unroll
+        for (int i = 0; i < kRowMaxVec; ++i) {
+          const int v = t + i * TPR;
+          if (active && v < nvec)
+            raw[i] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.peer_bufs[peer]) +
+                                                           p.x_off + row_byte + (int64_t)v * 16));
+        }
+#pragma unroll
+        for (int i = 0; i < kRowMaxVec; ++i) {
+          const int v = t + i * TPR;
+          if (active && v < nvec) {
+            float f[8];
+            unpack8(*reinterpret_cast<const bf16x8*>(&raw[i]), f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) vals[i][j] = (k == 0 ? 0.f : vals[i][j]) + f[j];
+          }
+        }
+      }
+    }
+    if (p.mode == 1) {
+#pragma unroll
+      for (int i = 0; i < kRowMaxVec; ++i) {
+        const int v = t + i * TPR;
+        if (active && v < nvec) {
+          float r[8];
+          unpack8(*reinterpret_cast<const bf16x8*>(&rres[i]), r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) vals[i][j] += r[j];
+          const bf16x8 nr = pack8(vals[i]);  // the residual stream is bf16: round once
+          reinterpret_cast<bf16x8*>(p.residual + (row - row_begin) * p.H)[v] = nr;
+          unpack8(nr, vals[i]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+        }
+      }
+    }
+    float inv = 1.f;
+    if (p.mode == 1) {
+      ss = group_sum<TPR>(ss, red);
+      inv = rsqrtf(ss / (float)p.H + p.eps);
+    }
+#pragma unroll
+    for (int i = 0; i < kRowMaxVec; ++i) {
+      const int v = t + i * TPR;
+      if (active && v < nvec) {
+        float o[8];
+        if (p.mode == 1) {
+          float w[8];
+          unpack8(reinterpret_cast<const bf16x8*>(p.weight)[v], w);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * inv * w[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = vals[i][j];
+        }
+        const bf16x8 ob = pack8(o);
+        const uint4 u = *reinterpret_cast<const uint4*>(&ob);
+        const int64_t off = p.out_off + row_byte + (int64_t)v * 16;
+        if (p.mc_base != 0) {
+          multimem_st_16(p.mc_base + off, u);
+        } else {
+          for (int k = 0; k < p.world; ++k) {
+            const int peer = (p.rank + k) % p.world;
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.peer_bufs[peer]) + off) = u;
+          }
+        }
+      }
+    }
+  }
+  if (!waited) {   // a CTA without rows still may not run ahead of the opening barrier
+    wait_flags(p.signal_pads, p.sig_off, p.rank, p.world, e0 + 1, p.budget, p.err, 1);
+  }
+  // closing barrier: the last CTA to finish tells the peers that this rank's rows have been
+  // broadcast and waits for theirs, so that completion of the kernel means `out` is complete here
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned prev = atomicAdd(p.epochs + 2, 1u);
+    s_last = prev == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x < p.world) {
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<uint32_t*>(p.signal_pads[threadIdx.x]) + p.sig_off + p.rank, e0 + 2);
+    }
+    wait_flags(p.signal_pads, p.sig_off, p.rank, p.world, e0 + 2, p.budget, p.err, 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      p.epochs[2] = 0u;
+      *reinterpret_cast<volatile uint32_t*>(p.epochs) = e0 + 2;
+      __threadfence();
+    }
+  }
+  pdl_launch_dependents();
+}
+
+// ------------------------------------------------------------------------------------------------
 //   xllm_tp_argmax : greedy sampling over vocabulary-sharded logits without gathering them.
 //
 // One CTA per row finds the maximum of the local shard and stores (value, global index) into slot
@@ -699,7 +727,8 @@ XLLM_API int64_t xllm_tp_signal_slots(int world) { return (int64_t)world; }
 // peer_bufs / signal_pads: device arrays of `world` pointers.  x and out are [T, H] bf16 at byte
 // offsets x_off / out_off of the symmetric buffer (16-byte aligned, H % 8 == 0, H <= 16384).
 // residual: local [ceil(T/world), H] shard (mode 1).  epochs: 4 zero-initialised device uint32
-// (epoch, go flag, arrival counter), owned by this communicator; n_ctas <= 296 (all CTAs must be co-resident).  err: device int, set non-zero if a flag wait ran out.
+// (epoch, unused, arrival counter), owned by this communicator; n_ctas: any positive number (CTAs do not
+// wait for one another).  err: device int, set non-zero if a flag wait ran out.
 XLLM_API int xllm_tp_allreduce_norm(const void* peer_bufs, const void* signal_pads, uint64_t mc_base,
                                     int64_t x_off, int64_t out_off, int64_t sig_off, void* epochs,
                                     void* residual, const void* weight, void* err, int T, int H, int rank,
@@ -714,7 +743,18 @@ XLLM_API int xllm_tp_allreduce_norm(const void* peer_bufs, const void* signal_pa
   p.x_off = x_off; p.out_off = out_off; p.sig_off = sig_off; p.epochs = (uint32_t*)epochs;
   p.residual = (bf16*)residual; p.weight = (const bf16*)weight; p.err = (int*)err; p.T = T; p.H = H;
   p.rank = rank; p.world = world; p.mode = mode; p.eps = eps; p.budget = g_wait_budget_cycles;
-  tp_allreduce_norm_kernel<<<n_ctas, kCommThreads, 0, (cudaStream_t)stream>>>(p);
+  const int tpr = row_group_threads(H);
+  if (tpr == 0 || n_ctas < 1) return (int)cudaErrorInvalidValue;
+  const int rows = kRowThreads / tpr;
+  const int S = (T + world - 1) / world;
+  const dim3 grid((unsigned)std::max<int64_t>(1, std::min<int64_t>(n_ctas, ((int64_t)S + rows - 1) / rows))), block(kRowThreads);
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (tpr) {
+    case 32: launch_pdl(tp_twoshot_norm_kernel<32>, grid, block, 0, s, p); break;
+    case 64: launch_pdl(tp_twoshot_norm_kernel<64>, grid, block, 0, s, p); break;
+    case 128: launch_pdl(tp_twoshot_norm_kernel<128>, grid, block, 0, s, p); break;
+    default: launch_pdl(tp_twoshot_norm_kernel<256>, grid, block, 0, s, p); break;
+  }
   return XLLM_LAUNCH_CHECK();
 }
 

@@ -60,7 +60,13 @@ class TpComm:
         self.device = ps.device
         row_bytes = hidden * 2
         al = lambda n: (n + 255) & ~255
-        self.oneshot_tokens = min(self.max_tokens, int(os.environ.get("XLLM_TP_ONESHOT_TOKENS", "2048")))
+        # One-shot or two-shot?  One-shot has one flag exchange (~10 us) but every rank pulls the whole
+        # message through the switch, so each GPU serves `world` readers; two-shot has two exchanges and
+        # moves (1 + 1/world) messages per GPU.  They cost the same at about
+        # 10 us x 600 GB/s / (world - 1 - 1/world) bytes: 12 MB at 2 ranks, 2.2 MB at 4, 0.9 MB at 8.
+        even = 6e6 / max(self.world - 1.0 - 1.0 / self.world, 0.25)
+        auto = max(16, int(even / row_bytes))
+        self.oneshot_tokens = min(self.max_tokens, int(os.environ.get("XLLM_TP_ONESHOT_TOKENS", str(auto))))
         self.x_off = 0
         self.x1_off = al(self.max_tokens * row_bytes)
         self.out_off = al(self.x1_off + self.oneshot_tokens * row_bytes)
@@ -140,12 +146,18 @@ class TpComm:
             return (self.x1 if self._parity else self.x)[:T]
         return self.x[:T]
 
+    def _mc(self, T):
+        """Multicast address for a reduction of T rows, or 0 for plain peer loads.  With two ranks a
+        peer load fetches one remote copy, which measures faster than `multimem.ld_reduce` from 128
+        rows on (41 us against 59 us at 2048 x 4096); with more ranks the in-switch reduction wins
+        because a rank would otherwise fetch world - 1 copies."""
+        return 0 if (self.world == 2 and T >= 128) else self.mc_base
+
     def _oneshot(self, T, residual_in, residual_out, weight, eps, out=None):
         if out is None:
             out = torch.empty((T, self.hidden), dtype=torch.bfloat16, device=self.device)
         x_off = self.x1_off if self._parity else self.x_off
-        # a few rows per CTA and all CTAs resident at once: the call is latency-bound
-        check(_lib.load().xllm_tp_oneshot_norm(self.peer_ptrs, self.signal_ptrs, self.mc_base, x_off, self.sig_oneshot,
+        check(_lib.load().xllm_tp_oneshot_norm(self.peer_ptrs, self.signal_ptrs, self._mc(T), x_off, self.sig_oneshot,
                                                ptr(self.state_oneshot), ptr(residual_in), ptr(residual_out),
                                                ptr(weight), ptr(out), ptr(self.err), T, self.hidden, self.rank,
                                                self.world, float(eps), 296, stream()), "tp_oneshot_norm")
@@ -174,7 +186,7 @@ class TpComm:
             from ..ops import _count
             _count()
             return self.out[:T]
-        check(_lib.load().xllm_tp_allreduce_norm(self.peer_ptrs, self.signal_ptrs, self.mc_base, self.x_off,
+        check(_lib.load().xllm_tp_allreduce_norm(self.peer_ptrs, self.signal_ptrs, self._mc(T), self.x_off,
                                                  self.out_off, self.sig_off, ptr(self.state), ptr(residual),
                                                  ptr(weight), ptr(self.err), T, self.hidden, self.rank,
                                                  self.world, mode, eps, n_ctas, stream()), "tp_allreduce_norm")
