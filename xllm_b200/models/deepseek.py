@@ -88,6 +88,10 @@ class MLAAttention(Module):
         return torch.stack([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).flatten(-2).to(v.dtype)
 
     def _forward_latent(self, x, positions, meta: AttentionMetadata, cache):
+        """Absorbed form over the latent cache: q_abs = q_nope . W_UK, attention against rows
+        [c_kv | k_pe] (one shared "head" of 576), out = (P . c_kv) . W_UV.  The cache write, both rotary
+        embeddings and the attention are kernels of ops.mla; nothing is read back to the host."""
+        from ..ops import mla as mla_ops
         T, nh, L, r = x.shape[0], self.nh, self.kv_lora, self.rope_d
         if self.q_lora:
             q = self.q_b_proj(self.q_a_layernorm(self.q_a_proj(x)))
@@ -95,48 +99,23 @@ class MLAAttention(Module):
             q = self.q_proj(x)
         q = q.view(T, nh, self.qk_d)
         kv_a = self.kv_a_proj(x)
-        c = self.kv_a_layernorm(kv_a[:, :L].contiguous())
-        k_pe = self._rope(kv_a[:, None, L:], positions)[:, 0]
-        rows = cache.view(-1, L + r)                          # one row per token slot (a single shared "head")
-        valid = meta.slots >= 0
-        rows.index_copy_(0, meta.slots[valid].long(), torch.cat([c, k_pe], dim=-1)[valid].to(rows.dtype))
         w = self.kv_b_proj.weight.view(nh, self.nope + self.vd, L)
         w_uk, w_uv = w[:, :self.nope], w[:, self.nope:]        # [nh, nope, L], [nh, vd, L]
-        q_cat = torch.cat([torch.einsum("thn,hnl->thl", q[..., :self.nope], w_uk),
-                           self._rope(q[..., self.nope:], positions)], dim=-1)          # [T, nh, L + r]
+        q_cat = torch.empty((T, nh, L + r), dtype=x.dtype, device=x.device)
+        q_cat[..., :L] = torch.einsum("thn,hnl->thl", q[..., :self.nope], w_uk)
+        mla_ops.cache_write(kv_a, self.kv_a_layernorm.weight, self.kv_a_layernorm.eps, self.rope.cos_sin, positions,
+                            meta.slots, cache, q[..., self.nope:], q_cat)
         o_lat = torch.empty((T, nh, L), dtype=x.dtype, device=x.device)
-        page = cache.shape[2]
-        host = getattr(meta, "_host_lens", None)
-        if host is None:
-            host = (meta.cu_q.tolist() if meta.cu_q is not None else None, meta.kv_lens.tolist())
-            meta._host_lens = host
-        cu, kv_lens = host
         nd = meta.n_decode
-        ar = torch.arange(page, device=x.device)
-
-        def context(tables, n_tok):                           # tables [B, nb] -> latent rows [B, nb * page, L + r]
-            nb = (n_tok + page - 1) // page
-            idx = (tables[:, :nb].long()[:, :, None] * page + ar).flatten(1)
-            return rows[idx]
-
-        if nd > 0:                                            # one query token per sequence: padded batch
-            smax = max(kv_lens[:nd])
-            ctx = context(meta.block_table[:nd], smax)
-            s = torch.einsum("bhd,bsd->bhs", q_cat[:nd].float(), ctx.float()) * self.scale
-            dead = torch.arange(ctx.shape[1], device=x.device)[None, :] >= meta.kv_lens[:nd, None]
-            p = torch.softmax(s.masked_fill(dead[:, None, :], float("-inf")), dim=-1)
-            o_lat[:nd] = torch.einsum("bhs,bsl->bhl", p, ctx[..., :L].float()).to(x.dtype)
-        for i in range(meta.n_prefill):                       # prompt chunks: per sequence, queries in slices
-            a, b, n_kv = cu[nd + i], cu[nd + i + 1], kv_lens[nd + i]
-            ctx = context(meta.block_table[nd + i: nd + i + 1], n_kv)[0, :n_kv].float()
-            first = n_kv - (b - a)                            # position of the chunk's first query
-            for q0 in range(a, b, 256):
-                q1 = min(b, q0 + 256)
-                s = torch.einsum("qhd,sd->hqs", q_cat[q0:q1].float(), ctx) * self.scale
-                qpos = first + torch.arange(q0 - a, q1 - a, device=x.device)
-                dead = torch.arange(n_kv, device=x.device)[None, :] > qpos[:, None]
-                p = torch.softmax(s.masked_fill(dead[None], float("-inf")), dim=-1)
-                o_lat[q0:q1] = torch.einsum("hqs,sl->qhl", p, ctx[:, :L]).to(x.dtype)
+        if nd > 0:                                            # one query token per sequence
+            mla_ops.decode(q_cat[:nd], cache, meta.block_table, self.scale, seq_lens=meta.kv_lens[:nd], out=o_lat[:nd],
+                           latent=L)
+        if meta.n_prefill > 0 and T > nd:
+            # every token of a prompt chunk is a query row that sees the cache up to its own position
+            tok = torch.arange(nd, T, device=x.device, dtype=torch.int32)
+            seq = torch.bucketize(tok, meta.cu_q[nd + 1:].contiguous(), right=True).clamp_(max=meta.n_prefill - 1)
+            mla_ops.decode(q_cat[nd:], cache, meta.block_table, self.scale, positions=positions[nd:],
+                           bt_rows=(seq + nd).to(torch.int32), out=o_lat[nd:], latent=L)
         out = torch.einsum("thl,hvl->thv", o_lat, w_uv)
         return self.o_proj(out.reshape(T, nh * self.vd))
 
@@ -226,9 +205,7 @@ class DeepseekCausalLM(DenseCausalLM):
         """2 = separate K and V caches; 1 = one latent cache per layer (the V handle aliases it)."""
         return 1 if self.layers[0].self_attn.latent else 2
 
-    @property
-    def supports_graph(self):
-        return not self.layers[0].self_attn.latent     # the latent form sizes its gathers per batch
+    supports_graph = True
 
 
 class MTPDraft(Module):
