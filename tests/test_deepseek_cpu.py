@@ -129,3 +129,83 @@ def test_latent_cache_form_matches_materialised_form():
     ka, kb = a.engine.runner.kv_caches[0][0], b.engine.runner.kv_caches[0][0]
     assert kb.shape[1] == 1 and kb.shape[3] == args.kv_lora_rank + args.qk_rope_head_dim
     assert kb[0].numel() * 1 < ka[0].numel() * 2
+
+
+def test_fp8_checkpoint_runs_in_fp8_layers_and_matches_dequantised(tmp_path):
+    """A block-scaled e4m3 checkpoint (128 x 128 weight blocks) loaded twice: into layers that keep the
+    e4m3 weights and their scales (fp8 execution) and dequantised to the wide type at load.  Same
+    tokens, logits equal up to rounding."""
+    import dataclasses
+    import json
+
+    from xllm_b200 import LLM, SamplingParams
+    from xllm_b200.models import ModelArgs, create_model
+    from xllm_b200.ops import fp8
+    from xllm_b200.utils.loader import save_file
+    args = ModelArgs(model_type="deepseek_v3", vocab_size=512, hidden_size=256, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=4, head_dim=48, intermediate_size=256, num_experts=4,
+                     num_experts_per_tok=2, moe_intermediate_size=128, n_shared_experts=1, first_k_dense_replace=1,
+                     scoring_func="sigmoid", n_group=2, topk_group=1, routed_scaling_factor=2.5, router_bias=True,
+                     q_lora_rank=128, kv_lora_rank=128, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
+                     qk_norm=False, rope_theta=10000.0, max_position_embeddings=512, dtype="float32")
+    src = create_model(args, torch.float32, "cpu")
+    src.init_random(seed=5)
+    tensors = {}
+    for name, t in _checkpoint_names(src):
+        quantise = "proj" in name and name.endswith(".weight") and t.dim() == 2 and t.shape[1] % 128 == 0
+        if quantise:
+            q, sc = fp8.quant_block128_ref(t)
+            tensors[name] = q
+            tensors[name + "_scale_inv"] = sc
+        else:
+            tensors[name] = t
+    d = tmp_path / "ckpt"
+    d.mkdir()
+    save_file(tensors, str(d / "model.safetensors"))
+    cfg = {"model_type": "deepseek_v3", "architectures": ["DeepseekV3ForCausalLM"], "vocab_size": 512, "hidden_size": 256,
+           "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 4, "intermediate_size": 256,
+           "n_routed_experts": 4, "num_experts_per_tok": 2, "moe_intermediate_size": 128, "n_shared_experts": 1,
+           "first_k_dense_replace": 1, "scoring_func": "sigmoid", "n_group": 2, "topk_group": 1,
+           "routed_scaling_factor": 2.5, "topk_method": "noaux_tc", "norm_topk_prob": True, "q_lora_rank": 128,
+           "kv_lora_rank": 128, "qk_nope_head_dim": 32, "qk_rope_head_dim": 16, "v_head_dim": 32, "rope_theta": 10000.0,
+           "max_position_embeddings": 512, "rms_norm_eps": 1e-6, "torch_dtype": "float32", "eos_token_id": 1,
+           "quantization_config": {"quant_method": "fp8", "fmt": "e4m3", "weight_block_size": [128, 128]}}
+    (d / "config.json").write_text(json.dumps(cfg))
+    prompts = [[5, 9, 33, 120, 7, 7, 250], [400, 3, 18]]
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    outs = {}
+    for mode in (True, False):
+        llm = LLM(str(d), devices="cpu", dtype="float32", enable_graph=False, num_blocks=64, max_seqs_per_batch=4,
+                  max_tokens_per_batch=64, fp8_execution=mode, tokenizer=_NoTokenizer())
+        kinds = {t.dtype for _, t in llm.engine.model.named_params()}
+        assert (torch.float8_e4m3fn in kinds) == mode
+        outs[mode] = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert outs[True] == outs[False], outs
+
+
+class _NoTokenizer:
+    def decode(self, ids, skip_special=True):
+        return ""
+
+
+def _checkpoint_names(model):
+    """Parameters under checkpoint names: fused projections and stacked experts split back."""
+    a = model.args
+    for n, t in model.named_params():
+        if n.endswith("gate_up_proj.weight"):
+            g, u = t.chunk(2)
+            base = n[: -len("gate_up_proj.weight")]
+            yield base + "gate_proj.weight", g
+            yield base + "up_proj.weight", u
+        elif n.endswith("experts.gate_up"):
+            base = n[: -len("gate_up")]
+            for e in range(t.shape[0]):
+                g, u = t[e].chunk(2)
+                yield f"{base}{e}.gate_proj.weight", g
+                yield f"{base}{e}.up_proj.weight", u
+        elif n.endswith("experts.down"):
+            base = n[: -len("down")]
+            for e in range(t.shape[0]):
+                yield f"{base}{e}.down_proj.weight", t[e]
+        else:
+            yield n, t

@@ -1135,6 +1135,260 @@ static int launch_gemm_pair(const void* a, const void* w, void* c, const void* b
   return XLLM_LAUNCH_CHECK();
 }
 
+// ===================================================================================== block-scaled fp8
+// C[M,N] (bf16) = sum over 128-wide K blocks kb of
+//     (A_q[:, kb] . W_q[:, kb]^T) * a_scale[m, kb] * w_scale[n / 128, kb]
+// with A_q, W_q e4m3: the format of DeepSeek-V3-style checkpoints (weights quantised in 128 x 128
+// blocks, activations per token in groups of 128).  The reference has no such kernel on CUDA: its
+// CUTLASS sm100 scaled_mm refuses block scales
+// (xllm/core/kernels/cuda/cutlass_w8a8/scaled_mm_c3x_sm100.cu:34-44).
+//
+// The scales differ from one K block to the next, so the products of different K blocks cannot be
+// summed inside the tensor core's accumulator.  Each K block (4 x tcgen05.mma kind::f8f6f4, K = 32) is
+// accumulated FRESH into one of two 128-column TMEM buffers; the four epilogue warps read a buffer back
+// (tcgen05.ld), multiply by the block's scales and add into fp32 registers (one output row of 128
+// columns per thread) while the MMA warp already fills the other buffer.  One tile is 128 x 128, so
+// the weight scale is one number per (tile, K block) and the activation scale one per (row, K block).
+// Grouped form (MoE experts): `tile_expert[row tile]` names the expert of each 128-row tile (-1:
+// skip); expert e's weights start e * expert_rows rows into W and its scale rows e * expert_rows / 128
+// rows into w_scale.
+constexpr int kFbStages = 6;
+struct FbSmem {
+  static constexpr int A_BYTES = kBM * 128;        // 128 rows x 128 bytes (one K block of e4m3)
+  static constexpr int B_BYTES = 128 * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFF = kFbStages * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFF + (2 * kFbStages + 4) * 8 + 16 + 1024;
+};
+
+__global__ void __launch_bounds__(192, 1)
+gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                      bf16* __restrict__ c, int64_t ldc, const float* __restrict__ a_scale,
+                      const float* __restrict__ w_scale, int M, int N, int K, int a_box_rows,
+                      const int32_t* __restrict__ tile_expert, int expert_rows, int* __restrict__ err_word) {
+  using S = FbSmem;
+  constexpr int BN = 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + S::BAR_OFF;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kFbStages + s); };
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * kFbStages + a); };
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * kFbStages + 2 + a); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::BAR_OFF + (2 * kFbStages + 4) * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + BN - 1) / BN;
+  const int total_tiles = m_tiles * n_tiles;
+  const int k_blocks = K / 128;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kFbStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                 "r"(256));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  pdl_wait();
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int armed = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % m_tiles) * kBM;
+      int n0 = (tile / m_tiles) * BN;
+      if (tile_expert != nullptr) {
+        const int e = tile_expert[tile % m_tiles];
+        if (e < 0) continue;
+        n0 += e * expert_rows;
+      }
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        if (!mbar_wait_warp(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
+        const uint32_t a_dst = sbase + stage * S::STAGE_BYTES;
+        if (elect_one()) {
+          mbar_expect_tx(full_bar(stage), S::B_BYTES + a_box_rows * 128);
+          tma_load_2d(a_dst, &tma_a, kb * 128, m0, full_bar(stage));
+          tma_load_2d(a_dst + S::A_BYTES, &tma_b, kb * 128, n0, full_bar(stage));
+        }
+        __syncwarp();
+        ++armed;
+        if (++stage == kFbStages) { stage = 0; phase ^= 1; }
+      }
+    }
+    if (!ok) {
+      const int pending = armed < kFbStages ? armed : kFbStages;
+      for (int i = 0; i < pending; ++i) {
+        int s = stage - 1 - i;
+        uint32_t ph = phase;
+        if (s < 0) { s += kFbStages; ph ^= 1; }
+        const long long t0 = clock64();
+        while (!mbar_try(full_bar(s), ph) && clock64() - t0 < 20000000LL) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t idesc = umma_idesc_e4m3(BN);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    uint32_t g = 0;  // K blocks issued so far: block g uses accumulator g & 1 for the (g >> 1)-th time
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      if (tile_expert != nullptr && tile_expert[tile % m_tiles] < 0) continue;
+      for (int kb = 0; kb < k_blocks; ++kb, ++g) {
+        const int acc = g & 1;
+        if (!mbar_wait_warp(tempty_bar(acc), ((g >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_addr = sbase + stage * S::STAGE_BYTES;
+        if (elect_one()) {
+          const uint64_t adesc = umma_smem_desc(a_addr);
+          const uint64_t bdesc = umma_smem_desc(a_addr + S::A_BYTES);
+          const uint32_t d_tmem = tmem_base + acc * BN;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_fp8(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, k != 0);
+          umma_commit(empty_bar(stage));   // the ring slot is free once these MMAs have read it
+          umma_commit(tfull_bar(acc));     // ... and the block's product is complete in TMEM
+        }
+        __syncwarp();
+        if (++stage == kFbStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------- promote + store (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    bool ok = true;
+    uint32_t g = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      int e = 0;
+      if (tile_expert != nullptr) {
+        e = tile_expert[tile % m_tiles];
+        if (e < 0) continue;
+      }
+      const int m0 = (tile % m_tiles) * kBM, n0 = (tile / m_tiles) * BN;
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < M;
+      const float* as = a_scale + (int64_t)(row_ok ? row : 0) * k_blocks;
+      const float* ws = w_scale + ((int64_t)(e * expert_rows + n0) / 128) * k_blocks;
+      float accum[BN];
+#pragma unroll
+      for (int i = 0; i < BN; ++i) accum[i] = 0.f;
+      float sc_next = row_ok ? as[0] * ws[0] : 0.f;
+      for (int kb = 0; kb < k_blocks; ++kb, ++g) {
+        const int acc = g & 1;
+        const float sc = sc_next;
+        if (kb + 1 < k_blocks) sc_next = row_ok ? as[kb + 1] * ws[kb + 1] : 0.f;   // in flight during the wait
+        if (!mbar_wait(tfull_bar(acc), (g >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll
+        for (int ch = 0; ch < BN / 32; ++ch) {
+          uint32_t r[32];
+          tmem_ld32(taddr + ch * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) accum[ch * 32 + i] = fmaf(__uint_as_float(r[i]), sc, accum[ch * 32 + i]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+      }
+      if (ok && row_ok) {
+        bf16* dst = c + (int64_t)row * ldc + n0;
+#pragma unroll
+        for (int j = 0; j < BN / 8; ++j) {
+          if (n0 + j * 8 < N) reinterpret_cast<bf16x8*>(dst)[j] = pack8(accum + j * 8);   // N % 8 == 0
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && err_word != nullptr) atomicExch(err_word, 1);
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256));
+  }
+}
+
+static int launch_fp8_block(const void* a, const void* w, void* c, const void* a_scale, const void* w_scale, int M,
+                            int N, int K, int64_t lda, int64_t ldw, int64_t ldc, const int32_t* tile_expert,
+                            int n_experts, cudaStream_t s) {
+  using S = FbSmem;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static bool attr_done[64] = {};
+  if (!attr_done[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    attr_done[dev & 63] = true;
+  }
+  if (g_err_word[dev & 63] == nullptr) {
+    if (cudaMalloc(&g_err_word[dev & 63], sizeof(int)) != cudaSuccess) return (int)cudaErrorMemoryAllocation;
+    cudaMemset(g_err_word[dev & 63], 0, sizeof(int));
+  }
+  CUtensorMap ta, tb;
+  const int a_box = M >= kBM ? kBM : ((M + 7) & ~7);
+  if (!make_tmap(&ta, a, M, K, lda, a_box, true, true) ||
+      !make_tmap(&tb, w, (int64_t)N * n_experts, K, ldw, 128, true, true))
+    return (int)cudaErrorInvalidValue;
+  const int tiles = ((M + kBM - 1) / kBM) * ((N + 127) / 128);
+  const int grid = tiles < 148 ? tiles : 148;
+  launch_pdl(gemm_fp8_block_kernel, dim3(grid), dim3(192), (size_t)S::TOTAL, s, ta, tb, (bf16*)c, ldc,
+             (const float*)a_scale, (const float*)w_scale, M, N, K, a_box, tile_expert, N, g_err_word[dev & 63]);
+  return XLLM_LAUNCH_CHECK();
+}
+
+}  // namespace xllm
+
+// Block-scaled fp8 GEMM: C[M,N] (bf16, row stride ldc) = sum_kb (A_q[:, kb] . W_q[:, kb]^T) * a_scale[m, kb] *
+// w_scale[n / 128, kb].  A_q [M, K] and W_q [N, K] are e4m3 (row strides lda / ldw bytes); a_scale [M, K / 128]
+// and w_scale [ceil(N / 128), K / 128] are fp32, row-major.  K % 128 == 0, N % 8 == 0, 16-byte aligned
+// bases, lda / ldw % 16 == 0, ldc % 8 == 0.
+XLLM_API int xllm_gemm_fp8_block(const void* a, const void* w, void* c, const void* a_scale, const void* w_scale, int M,
+                                 int N, int K, int64_t lda, int64_t ldw, int64_t ldc, void* stream) {
+  using namespace xllm;
+  if (M == 0 || N == 0) return 0;
+  if (K % 128 || K == 0 || N % 8 || lda % 16 || ldw % 16 || ldc % 8 || (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15))
+    return (int)cudaErrorInvalidValue;
+  return launch_fp8_block(a, w, c, a_scale, w_scale, M, N, K, lda, ldw, ldc, nullptr, 1, (cudaStream_t)stream);
+}
+
+// Grouped form for MoE experts: the rows of A are sorted by expert and padded so that every 128-row
+// tile belongs to one expert, tile_expert[row tile] (device int32, -1 = unused tile).  W_q is
+// [n_experts * N, K], w_scale [n_experts * ceil(N / 128), K / 128]; N % 128 == 0.
+XLLM_API int xllm_gemm_fp8_block_grouped(const void* a, const void* w, void* c, const void* a_scale,
+                                         const void* w_scale, const void* tile_expert, int n_experts, int M, int N,
+                                         int K, int64_t lda, int64_t ldw, int64_t ldc, void* stream) {
+  using namespace xllm;
+  if (M == 0 || N == 0) return 0;
+  if (K % 128 || K == 0 || N % 128 || lda % 16 || ldw % 16 || ldc % 8 || tile_expert == nullptr ||
+      (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15))
+    return (int)cudaErrorInvalidValue;
+  return launch_fp8_block(a, w, c, a_scale, w_scale, M, N, K, lda, ldw, ldc, (const int32_t*)tile_expert, n_experts,
+                          (cudaStream_t)stream);
+}
+
+namespace xllm {
 }  // namespace xllm
 
 // C[M,N] = A[M,K] · W[N,K]^T (+ bias).  bf16 row-major, leading dimensions in elements.

@@ -62,6 +62,7 @@ class EngineConfig:
     draft_model: str = ""
     mla_latent_cache: bool = False      # MLA models: cache [c_kv | k_pe] rows (576 values per token) instead of per-head K/V
     activation_reserve_bytes: int = 0   # 0: estimated from max_tokens_per_batch
+    fp8_execution: Optional[bool] = None  # block-scaled fp8 checkpoints: None / True = run the fp8 GEMMs, False = dequantise at load
     min_prefill_tokens: int = 0         # mixing policies: hold prompt chunks back until this many prompt tokens are pending
     max_prefill_wait_steps: int = 8     # ... or this many steps have passed
     max_running_seqs: int = 0           # cap on sequences holding KV / state at once; 0: no cap (state models: max_seqs_per_batch + 1)
@@ -104,6 +105,10 @@ class LLMEngine:
         if cfg.mla_latent_cache and self.args.kv_lora_rank:
             import dataclasses
             self.args = dataclasses.replace(self.args, mla_latent_cache=True)
+        if self.args.quant_method == "fp8" and list(self.args.quant_block or [128, 128]) == [128, 128] \
+                and cfg.fp8_execution is not False:
+            import dataclasses
+            self.args = dataclasses.replace(self.args, fp8_execution=True)
         if cfg.dtype == "auto":
             self.dtype = torch.bfloat16 if self.device.type == "cuda" else _DTYPES.get(self.args.dtype, torch.float32)
             if self.device.type == "cpu" and self.dtype == torch.bfloat16:
@@ -127,10 +132,16 @@ class LLMEngine:
                 from ..utils.loader import dequant_fp8_stream, iterate_weights
                 weights = iterate_weights(cfg.model)
                 if self.args.quant_method == "fp8":
-                    weights = dequant_fp8_stream(weights)
+                    # layers that execute in fp8 take the e4m3 tensors and their block scales as they are;
+                    # everything else (embeddings, router, kv_b_proj, ...) is dequantised while streaming
+                    keep = {n[: -len("_scale_inv")] for n, _ in self.model.named_loaders() if n.endswith("weight_scale_inv")}
+                    weights = dequant_fp8_stream(weights, keep, self.dtype)
                 missing = self.model.load_weights(weights, strict=False)
                 # a checkpoint that lacks tensors the model needs would otherwise run on zeros
                 missing = [n for n in missing if not n.endswith("e_score_correction_bias")]
+                # a weight that arrived in a wide type was quantised by its loader, which also set the scales
+                gone = set(missing)
+                missing = [n for n in missing if not (n.endswith("weight_scale_inv") and n[: -len("_scale_inv")] not in gone)]
                 if missing and os.environ.get("XLLM_ALLOW_MISSING_WEIGHTS", "0") != "1":
                     raise KeyError(f"checkpoint {cfg.model} lacks {len(missing)} tensors the model needs, e.g. "
                                    f"{missing[:6]} (set XLLM_ALLOW_MISSING_WEIGHTS=1 to load anyway)")

@@ -65,6 +65,8 @@ class ModelArgs:
     # quantisation (from `quantization_config`)
     quant_method: str = ""
     quant_block: List[int] = field(default_factory=list)
+    # run block-scaled fp8 checkpoints on the fp8 GEMM (weights stay e4m3) instead of dequantising at load
+    fp8_execution: bool = False
     # VLM
     vision_config: Optional[Dict[str, Any]] = None
     image_token_id: int = -1

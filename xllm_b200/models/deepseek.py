@@ -49,20 +49,22 @@ class MLAAttention(Module):
         self.qk_d = self.nope + self.rope_d
         H = a.hidden_size
         self.q_lora = a.q_lora_rank
+        qn = "fp8_block" if getattr(a, "fp8_execution", False) else None
         if self.q_lora:
-            self.q_a_proj = self.add_module("q_a_proj", Linear(H, self.q_lora, False, dtype, device, self.ps))
+            self.q_a_proj = self.add_module("q_a_proj", Linear(H, self.q_lora, False, dtype, device, self.ps, quant=qn))
             self.q_a_layernorm = self.add_module("q_a_layernorm", RMSNorm(self.q_lora, a.rms_norm_eps, dtype, device))
             self.q_b_proj = self.add_module("q_b_proj", Linear(self.q_lora, a.num_attention_heads * self.qk_d, False, dtype,
-                                                               device, self.ps, parallel="column"))
+                                                               device, self.ps, parallel="column", quant=qn))
         else:
             self.q_proj = self.add_module("q_proj", Linear(H, a.num_attention_heads * self.qk_d, False, dtype, device,
-                                                           self.ps, parallel="column"))
-        self.kv_a_proj = self.add_module("kv_a_proj_with_mqa", Linear(H, a.kv_lora_rank + self.rope_d, False, dtype, device, self.ps))
+                                                           self.ps, parallel="column", quant=qn))
+        self.kv_a_proj = self.add_module("kv_a_proj_with_mqa", Linear(H, a.kv_lora_rank + self.rope_d, False, dtype, device,
+                                                                      self.ps, quant=qn))
         self.kv_a_layernorm = self.add_module("kv_a_layernorm", RMSNorm(a.kv_lora_rank, a.rms_norm_eps, dtype, device))
         self.kv_b_proj = self.add_module("kv_b_proj", Linear(a.kv_lora_rank, a.num_attention_heads * (self.nope + self.vd), False,
                                                              dtype, device, self.ps, parallel="column"))
         self.o_proj = self.add_module("o_proj", Linear(a.num_attention_heads * self.vd, H, False, dtype, device, self.ps,
-                                                       parallel="row"))
+                                                       parallel="row", quant=qn))
         self.kv_lora = a.kv_lora_rank
         self.rope = rope
         self.scale = 1.0 / math.sqrt(self.qk_d)
@@ -184,7 +186,8 @@ class DeepseekCausalLM(DenseCausalLM):
             if args.is_moe_layer(i):
                 mlp = SparseMoeBlock(args, dtype, device, self.ps)
             else:
-                mlp = DenseMLP(args.hidden_size, args.intermediate_size, args.hidden_act, dtype, device, self.ps)
+                mlp = DenseMLP(args.hidden_size, args.intermediate_size, args.hidden_act, dtype, device, self.ps,
+                               quant="fp8_block" if getattr(args, "fp8_execution", False) else None)
             self.layers.append(layers.add_module(str(i), DeepseekDecoderLayer(args, i, dtype, device, self.ps, self.rope, mlp)))
         self.norm = inner.add_module("norm", RMSNorm(args.hidden_size, args.rms_norm_eps, dtype, device))
         self.lm_head = LMHead(args.vocab_size, args.hidden_size, dtype, device, self.ps,

@@ -105,7 +105,17 @@ class Module:
     def init_random(self, std=0.02, seed=0):
         """Deterministic N(0, std) weights; norm weights are set to 1."""
         for i, (name, t) in enumerate(self.named_params()):
-            if t.dtype in (torch.float8_e4m3fn, torch.uint8, torch.int32, torch.int64):
+            if t.dtype == torch.float8_e4m3fn:
+                # an e4m3 weight and its block scales: q ~ N(0, 96) (well inside +-448), scale = std / 96
+                g = torch.Generator(device=t.device)
+                g.manual_seed(seed * 1000003 + i)
+                w = torch.empty(t.shape, dtype=torch.float32, device=t.device).normal_(0.0, 96.0, generator=g)
+                t.copy_(w.clamp_(-448, 448).to(t.dtype))
+                continue
+            if name.endswith("weight_scale_inv") or name.endswith("_scale"):
+                t.fill_(std / 96.0)
+                continue
+            if t.dtype in (torch.uint8, torch.int32, torch.int64):
                 continue
             if name.endswith("norm.weight") or name.endswith("layernorm.weight") or ".norm." in name \
                     or name.endswith("_norm.weight"):
@@ -123,11 +133,67 @@ def _shard(w, dim, rank, size):
     return w.narrow(dim, rank * n, n)
 
 
+FP8 = torch.float8_e4m3fn
+
+
+def _to_fp8_blocks(w):
+    """A bf16 / fp32 weight quantised to e4m3 in 128 x 128 blocks: (q, scales)."""
+    from ..ops import fp8 as fp8_ops
+    return fp8_ops.quant_block128_ref(w.float())
+
+
+def _fp8_linear(x, w_q, w_scale, bias=None, out=None):
+    """x @ dequant(w_q, w_scale)^T: the block-scaled tcgen05 GEMM on CUDA (activations quantised per
+    token in groups of 128), the dequantised product on CPU."""
+    from ..ops import fp8 as fp8_ops
+    if x.is_cuda:
+        y = fp8_ops.linear_block_fp8(x, w_q, w_scale, out=out)
+    else:
+        w = fp8_ops.dequant_block128_ref(w_q, w_scale, torch.float32)
+        y = (x.float() @ w.T).to(x.dtype)
+        if out is not None:
+            out.copy_(y)
+            y = out
+    if bias is not None:
+        y = y + bias
+    return y
+
+
+class _Fp8Weight:
+    """Storage and loaders of one block-scaled fp8 weight [rows, cols] (+ scales [rows / 128, cols / 128]).
+    `parts`: list of (source name, row offset, rows, shard fn) for fused weights; a source tensor may
+    arrive as e4m3 (then its `weight_scale_inv` follows or precedes it) or in a wider type (quantised
+    here)."""
+
+    def __init__(self, rows, cols, device):
+        self.q = torch.zeros(rows, cols, dtype=FP8, device=device)
+        self.scale = torch.ones((rows + 127) // 128, (cols + 127) // 128, dtype=torch.float32, device=device)
+
+    def loaders(self, name, row0, rows, shard_w, shard_s):
+        """-> {name.weight: fn, name.weight_scale_inv: fn} writing rows [row0, row0 + rows)."""
+        q, scale = self.q, self.scale
+
+        def lw(w):
+            w = shard_w(w)
+            if w.dtype == FP8:
+                q[row0:row0 + rows].copy_(w)
+            else:
+                wq, ws = _to_fp8_blocks(w)
+                q[row0:row0 + rows].copy_(wq)
+                scale[row0 // 128: row0 // 128 + ws.shape[0]].copy_(ws)
+
+        def ls(sc):
+            sc = shard_s(sc.float())
+            scale[row0 // 128: row0 // 128 + sc.shape[0]].copy_(sc)
+
+        return {f"{name}weight": lw, f"{name}weight_scale_inv": ls}
+
+
 class Linear(Module):
     """y = x W^T (+ b). `parallel`: None (replicated), 'column' (shard dim 0), 'row' (shard dim 1)."""
 
     def __init__(self, in_f, out_f, bias, dtype, device, ps: ParallelState = None, parallel=None,
-                 reduce=True, gather_output=False, fuse_reduce=True):
+                 reduce=True, gather_output=False, fuse_reduce=True, quant=None):
         super().__init__()
         self.ps = ps or single()
         self.fuse_reduce = fuse_reduce      # False: a plain all-reduce, for layers that norm the sum by itself
@@ -137,13 +203,25 @@ class Linear(Module):
         self.gather_output = gather_output
         out_l = out_f // tp if self.parallel == "column" else out_f
         in_l = in_f // tp if self.parallel == "row" else in_f
-        self.weight = torch.empty(out_l, in_l, dtype=dtype, device=device)
         dim = {"column": 0, "row": 1}.get(self.parallel)
+        # quant == "fp8_block": the weight stays e4m3 with 128 x 128 block scales and the product runs on
+        # the block-scaled GEMM (needs in_l % 128 == 0; shards must fall on block boundaries)
+        self.fp8 = None
+        if quant == "fp8_block" and in_l % 128 == 0 and (dim is None or (out_l % 128 == 0 and in_l % 128 == 0)):
+            self.fp8 = _Fp8Weight(out_l, in_l, device)
+            self.weight = self.fp8.q
+            sh_w = (lambda w: _shard(w, dim, rank, tp)) if dim is not None else (lambda w: w)
+            sh_s = (lambda sc: _shard(sc, dim, rank, tp)) if dim is not None else (lambda sc: sc)
+            self._params["weight"] = self.fp8.q
+            self._params["weight_scale_inv"] = self.fp8.scale
+            self._loaders.update(self.fp8.loaders("", 0, out_l, sh_w, sh_s))
+        else:
+            self.weight = torch.empty(out_l, in_l, dtype=dtype, device=device)
 
-        def load_w(w, t=self.weight):
-            t.copy_((_shard(w, dim, rank, tp) if dim is not None else w).to(t.dtype))
+            def load_w(w, t=self.weight):
+                t.copy_((_shard(w, dim, rank, tp) if dim is not None else w).to(t.dtype))
 
-        self.add_param("weight", self.weight, {"weight": load_w})
+            self.add_param("weight", self.weight, {"weight": load_w})
         self.bias = None
         if bias:
             self.bias = torch.zeros(out_l, dtype=dtype, device=device)
@@ -163,12 +241,17 @@ class Linear(Module):
                 # the partial result goes to the symmetric buffer; the cross-rank sum is fused
                 # into the add+RMSNorm that follows (TpComm.allreduce_norm)
                 T = x.shape[0]
+                if self.fp8 is not None:
+                    return _fp8_linear(x, self.fp8.q, self.fp8.scale, bias, out=comm.partial_buffer(T))
                 if comm.push_supported(x, self.weight, bias):
                     # prefill-size batches: the GEMM's epilogue pushes each tile to the rank that
                     # reduces those rows (GEMM -> reduce-scatter in one kernel, TpComm.push_gemm)
                     return comm.push_gemm(x, self.weight)
                 return ops.linear(x, self.weight, bias, out=comm.partial_buffer(T))
-        y = ops.linear(x, self.weight, bias)
+        if self.fp8 is not None:
+            y = _fp8_linear(x, self.fp8.q, self.fp8.scale, bias)
+        else:
+            y = ops.linear(x, self.weight, bias)
         if self.parallel == "row" and self.reduce:
             y = self.ps.all_reduce(y)
         elif self.parallel == "column" and self.gather_output:
@@ -185,13 +268,28 @@ class MergedColumnLinear(Module):
     (KV heads when n_kv_heads < tp)."""
 
     def __init__(self, in_f, sizes: List[int], names: List[str], bias, dtype, device,
-                 ps: ParallelState = None, shard_counts: Optional[List[int]] = None):
+                 ps: ParallelState = None, shard_counts: Optional[List[int]] = None, quant=None):
         super().__init__()
         self.ps = ps or single()
         tp, rank = self.ps.tp_size, self.ps.tp_rank
         counts = shard_counts or [tp] * len(sizes)
         self.local_sizes = [s // c for s, c in zip(sizes, counts)]
         total = sum(self.local_sizes)
+        self.fp8 = None
+        if quant == "fp8_block" and in_f % 128 == 0 and all(n % 128 == 0 for n in self.local_sizes) and not bias:
+            self.fp8 = _Fp8Weight(total, in_f, device)
+            self.weight = self.fp8.q
+            self.bias = None
+            off = 0
+            for name, cnt, loc in zip(names, counts, self.local_sizes):
+                idx = rank * cnt // tp
+                self._loaders.update(self.fp8.loaders(f"{name}.", off, loc,
+                                                      lambda w, i=idx, n=loc: w.narrow(0, i * n, n),
+                                                      lambda sc, i=idx, n=loc: sc.narrow(0, i * n // 128, n // 128)))
+                off += loc
+            self._params["weight"] = self.fp8.q
+            self._params["weight_scale_inv"] = self.fp8.scale
+            return
         self.weight = torch.empty(total, in_f, dtype=dtype, device=device)
         self.bias = torch.zeros(total, dtype=dtype, device=device) if bias else None
         loaders = {}
@@ -215,6 +313,8 @@ class MergedColumnLinear(Module):
         self._loaders.update(loaders)
 
     def forward(self, x):
+        if self.fp8 is not None:
+            return _fp8_linear(x, self.fp8.q, self.fp8.scale)
         return ops.linear(x, self.weight, self.bias)
 
     __call__ = forward
@@ -409,14 +509,16 @@ class Attention(Module):
 class DenseMLP(Module):
     """SwiGLU MLP: fused gate|up column-parallel GEMM -> silu·mul -> row-parallel down GEMM."""
 
-    def __init__(self, hidden, inter, act, dtype, device, ps: ParallelState = None, reduce=True, fuse_reduce=True):
+    def __init__(self, hidden, inter, act, dtype, device, ps: ParallelState = None, reduce=True, fuse_reduce=True,
+                 quant=None):
         super().__init__()
         self.ps = ps or single()
         self.act = act
         self.gate_up = self.add_module("gate_up_proj", MergedColumnLinear(
-            hidden, [inter, inter], ["gate_proj", "up_proj"], False, dtype, device, self.ps))
+            hidden, [inter, inter], ["gate_proj", "up_proj"], False, dtype, device, self.ps, quant=quant))
         self.down = self.add_module("down_proj", Linear(inter, hidden, False, dtype, device, self.ps,
-                                                        parallel="row", reduce=reduce, fuse_reduce=fuse_reduce))
+                                                        parallel="row", reduce=reduce, fuse_reduce=fuse_reduce,
+                                                        quant=quant))
 
     def named_loaders(self, prefix=""):
         for n, f in super().named_loaders(prefix):

@@ -38,12 +38,49 @@ class SparseMoeBlock(Module):
             self.i_local, i_rank, i_parts = I // tp, self.ps.tp_rank, tp
         self.top_k = args.num_experts_per_tok
         self.gate = self.add_module("gate", Linear(H, E, False, dtype, device, self.ps))  # replicated router
-        self.w_gate_up = torch.empty(self.e_local, 2 * self.i_local, H, dtype=dtype, device=device)
-        self.w_down = torch.empty(self.e_local, H, self.i_local, dtype=dtype, device=device)
-        self._params["experts.gate_up"] = self.w_gate_up
-        self._params["experts.down"] = self.w_down
         il = self.i_local
-        for e in range(self.e_local):
+        # block-scaled fp8 experts: e4m3 weights + 128 x 128 scales, grouped block-scaled GEMMs
+        self.fp8 = bool(getattr(args, "fp8_execution", False)) and il % 128 == 0 and H % 128 == 0
+        if self.fp8:
+            from .layers import FP8, _to_fp8_blocks
+            self.w_gate_up = torch.zeros(self.e_local, 2 * il, H, dtype=FP8, device=device)
+            self.w_down = torch.zeros(self.e_local, H, il, dtype=FP8, device=device)
+            self.s_gate_up = torch.ones(self.e_local, 2 * il // 128, H // 128, dtype=torch.float32, device=device)
+            self.s_down = torch.ones(self.e_local, H // 128, il // 128, dtype=torch.float32, device=device)
+            self._params["experts.gate_up"] = self.w_gate_up
+            self._params["experts.down"] = self.w_down
+            self._params["experts.gate_up_scale"] = self.s_gate_up
+            self._params["experts.down_scale"] = self.s_down
+
+            def put(wt, st, e, r0, rows, w, dim):
+                """rows [r0, r0 + rows) of expert e from checkpoint tensor w (sharded along `dim`)."""
+                w = w.narrow(dim, i_rank * il, il)
+                if w.dtype == FP8:
+                    wt[e, r0:r0 + rows].copy_(w)
+                else:
+                    q, sc = _to_fp8_blocks(w)
+                    wt[e, r0:r0 + rows].copy_(q)
+                    st[e, r0 // 128: r0 // 128 + sc.shape[0]].copy_(sc)
+
+            def put_s(st, e, r0, sc, dim):
+                sc = sc.float().narrow(dim, i_rank * il // 128, il // 128)
+                st[e, r0 // 128: r0 // 128 + sc.shape[0]].copy_(sc)
+
+            for e in range(self.e_local):
+                ge = e + self.e_begin
+                L_ = self._loaders
+                L_[f"experts.{ge}.gate_proj.weight"] = lambda w, e=e: put(self.w_gate_up, self.s_gate_up, e, 0, il, w, 0)
+                L_[f"experts.{ge}.up_proj.weight"] = lambda w, e=e: put(self.w_gate_up, self.s_gate_up, e, il, il, w, 0)
+                L_[f"experts.{ge}.down_proj.weight"] = lambda w, e=e: put(self.w_down, self.s_down, e, 0, H, w, 1)
+                L_[f"experts.{ge}.gate_proj.weight_scale_inv"] = lambda sc, e=e: put_s(self.s_gate_up, e, 0, sc, 0)
+                L_[f"experts.{ge}.up_proj.weight_scale_inv"] = lambda sc, e=e: put_s(self.s_gate_up, e, il, sc, 0)
+                L_[f"experts.{ge}.down_proj.weight_scale_inv"] = lambda sc, e=e: put_s(self.s_down, e, 0, sc, 1)
+        else:
+            self.w_gate_up = torch.empty(self.e_local, 2 * self.i_local, H, dtype=dtype, device=device)
+            self.w_down = torch.empty(self.e_local, H, self.i_local, dtype=dtype, device=device)
+            self._params["experts.gate_up"] = self.w_gate_up
+            self._params["experts.down"] = self.w_down
+        for e in range(self.e_local if not self.fp8 else 0):
             ge = e + self.e_begin
 
             def lg(w, e=e):
@@ -65,7 +102,9 @@ class SparseMoeBlock(Module):
         self.shared = None
         if args.n_shared_experts > 0:
             si = args.shared_expert_intermediate_size or args.moe_intermediate_size * args.n_shared_experts
-            self.shared = self.add_module("shared_experts", DenseMLP(H, si, args.hidden_act, dtype, device, self.ps, reduce=False))
+            self.shared = self.add_module("shared_experts", DenseMLP(
+                H, si, args.hidden_act, dtype, device, self.ps, reduce=False,
+                quant="fp8_block" if getattr(args, "fp8_execution", False) else None))
         self.shared_gate = None
         if self.shared is not None and args.extra.get("shared_expert_gate"):
             self.shared_gate = self.add_module("shared_gate", Linear(H, 1, False, dtype, device, self.ps))
@@ -80,7 +119,12 @@ class SparseMoeBlock(Module):
             # the shared expert is TP-sharded like a dense MLP: its partial joins the routed partial.
             # With EP every rank would add the full shared output, so only the rank that owns
             # expert 0 contributes it.
-            shared_out = ops.linear(ops.act_and_mul(self.shared.gate_up(x), a.hidden_act), self.shared.down.weight)
+            hs = ops.act_and_mul(self.shared.gate_up(x), a.hidden_act)
+            if self.shared.down.fp8 is not None:
+                from .layers import _fp8_linear
+                shared_out = _fp8_linear(hs, self.shared.down.fp8.q, self.shared.down.fp8.scale)
+            else:
+                shared_out = ops.linear(hs, self.shared.down.weight)
             if self.shared_gate is not None:               # Qwen2-MoE / Qwen3-Next: sigmoid-gated shared expert
                 shared_out = shared_out * torch.sigmoid(self.shared_gate(x).float()).to(shared_out.dtype)
             if self.ep > 1 and self.e_begin != 0 and self.shared.ps.tp_size == 1 and self.ps.dp_size == 1:
@@ -96,7 +140,8 @@ class SparseMoeBlock(Module):
                                             self.i_local, x.device, x.dtype)
         y = moe_ops.fused_moe(x, logits, self.w_gate_up, self.w_down, self.top_k, a.scoring_func, self.bias,
                               a.n_group, a.topk_group, a.norm_topk_prob, a.routed_scaling_factor, self.e_begin,
-                              a.num_experts, shared_out, self._ws, out)
+                              a.num_experts, shared_out, self._ws, out,
+                              w_scales=(self.s_gate_up, self.s_down) if self.fp8 else None)
         if out is None and self.ps.tp_size > 1:
             y = self.ps.all_reduce(y)
         return y
@@ -107,7 +152,7 @@ class SparseMoeBlock(Module):
     # all-reduce + norm that follows assembles the full activation without summing duplicates.
     def _use_a2a(self, x, comm) -> bool:
         import os
-        return (self.ep > 1 and x.is_cuda and comm is not None and self.ep == self.ps.tp_size
+        return (self.ep > 1 and not self.fp8 and x.is_cuda and comm is not None and self.ep == self.ps.tp_size
                 and os.environ.get("XLLM_EP_MODE", "a2a") == "a2a" and not torch.cuda.is_current_stream_capturing())
 
     def _forward_a2a(self, x, logits, shared_out, comm, out):

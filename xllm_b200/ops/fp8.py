@@ -16,6 +16,8 @@ _lib.register_signature("xllm_gemm_fp8", [P, P, P, P, P, P, I, I, I, I, I, L, L,
 _lib.register_signature("xllm_quant_fp8_per_token", [P, P, P, P, L, I, L, P])
 _lib.register_signature("xllm_quant_fp8_group128", [P, P, P, L, I, L, P])
 _lib.register_signature("xllm_dequant_fp8_block128", [P, P, P, L, I, P])
+_lib.register_signature("xllm_gemm_fp8_block", [P, P, P, P, P, I, I, I, L, L, L, P])
+_lib.register_signature("xllm_gemm_fp8_block_grouped", [P, P, P, P, P, P, I, I, I, I, L, L, L, P])
 
 FP8 = torch.float8_e4m3fn
 FP8_MAX = 448.0
@@ -129,3 +131,60 @@ def scaled_mm(a_q, w_q, a_scale, w_scale, bias=None, out=None):
     from . import _count
     _count()
     return out
+
+
+# ------------------------------------------------------------------ block-scaled GEMM (1 x 128 activations, 128 x 128 weights)
+def block_scaled_mm_ref(a_q, a_scale, w_q, w_scale):
+    """fp32 reference: dequantise both operands block by block, multiply."""
+    M, K = a_q.shape
+    N = w_q.shape[0]
+    a = a_q.float() * a_scale.float().repeat_interleave(128, 1)[:, :K]
+    w = w_q.float() * w_scale.float().repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)[:, :K]
+    return (a @ w.T).to(torch.bfloat16)
+
+
+def block_scaled_mm(a_q, a_scale, w_q, w_scale, out=None):
+    """bf16 C[M, N] = sum_kb (a_q[:, kb] @ w_q[:, kb]^T) * a_scale[:, kb, None] * w_scale[n // 128, kb]:
+    a_q [M, K] / w_q [N, K] e4m3, a_scale [M, K / 128], w_scale [ceil(N / 128), K / 128] fp32."""
+    if not a_q.is_cuda:
+        y = block_scaled_mm_ref(a_q, a_scale, w_q, w_scale)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    M, K = a_q.shape
+    N = w_q.shape[0]
+    assert a_q.dtype == FP8 and w_q.dtype == FP8 and a_q.stride(1) == 1 and w_q.stride(1) == 1
+    assert a_scale.dtype == torch.float32 and a_scale.is_contiguous() and a_scale.shape == (M, K // 128)
+    assert w_scale.dtype == torch.float32 and w_scale.is_contiguous() and w_scale.shape == ((N + 127) // 128, K // 128)
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a_q.device)
+    check(_lib.load().xllm_gemm_fp8_block(ptr(a_q), ptr(w_q), ptr(out), ptr(a_scale), ptr(w_scale), M, N, K,
+                                          a_q.stride(0), w_q.stride(0), out.stride(0), stream()), "gemm_fp8_block")
+    from . import _count
+    _count()
+    return out
+
+
+def block_scaled_mm_grouped(a_q, a_scale, w_q, w_scale, tile_expert, out):
+    """Grouped form: rows of a_q are sorted by expert in 128-row tiles, tile_expert [rows / 128] int32
+    (-1: unused); w_q [E, N, K] e4m3, w_scale [E, N / 128, K / 128]; out [rows, N] bf16."""
+    E, N, K = w_q.shape
+    rows = a_q.shape[0]
+    assert a_q.dtype == FP8 and w_q.dtype == FP8 and w_q.is_contiguous() and w_scale.is_contiguous()
+    assert a_scale.shape == (rows, K // 128) and a_scale.is_contiguous() and N % 128 == 0
+    check(_lib.load().xllm_gemm_fp8_block_grouped(ptr(a_q), ptr(w_q), ptr(out), ptr(a_scale), ptr(w_scale),
+                                                  ptr(tile_expert), E, rows, N, K, a_q.stride(0), K, out.stride(0),
+                                                  stream()), "gemm_fp8_block_grouped")
+    from . import _count
+    _count()
+    return out
+
+
+def linear_block_fp8(x, w_q, w_scale, out=None):
+    """y = x @ dequant(w_q, w_scale)^T with the activation quantised on the fly in 1 x 128 groups."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    a_q, a_s = quant_group128(x2 if x2.stride(-1) == 1 else x2.contiguous())
+    y = block_scaled_mm(a_q, a_s, w_q, w_scale, out=out)
+    return y.reshape(*lead, w_q.shape[0])

@@ -81,9 +81,16 @@ class MoeWorkspace:
 
 def fused_moe(x, logits, w_gate_up, w_down, top_k, scoring="softmax", bias=None, n_group=1, topk_group=1,
               renorm=True, scale=1.0, expert_begin=0, n_experts=None, shared_out=None, ws: MoeWorkspace = None,
-              out=None):
-    """x [T,H], logits [T,E]; w_gate_up [E_local, 2I, H], w_down [E_local, H, I] -> [T,H]."""
+              out=None, w_scales=None):
+    """x [T,H], logits [T,E]; w_gate_up [E_local, 2I, H], w_down [E_local, H, I] -> [T,H].
+    `w_scales` = (s_gate_up [E_local, 2I/128, H/128], s_down [E_local, H/128, I/128]): the weights are e4m3
+    with 128 x 128 block scales and both grouped GEMMs run block-scaled in fp8 (the rows are quantised
+    per token in groups of 128 before each of them)."""
     if not x.is_cuda:
+        if w_scales is not None:
+            from . import fp8
+            w_gate_up = torch.stack([fp8.dequant_block128_ref(w_gate_up[e], w_scales[0][e], x.dtype) for e in range(w_gate_up.shape[0])])
+            w_down = torch.stack([fp8.dequant_block128_ref(w_down[e], w_scales[1][e], x.dtype) for e in range(w_down.shape[0])])
         return fused_moe_reference(x, logits, w_gate_up, w_down, top_k, scoring, bias, n_group, topk_group, renorm,
                                    scale, expert_begin, shared_out)
     from . import _count, act_and_mul
@@ -105,11 +112,19 @@ def fused_moe(x, logits, w_gate_up, w_down, top_k, scoring="softmax", bias=None,
                                expert_begin, s), "moe_offsets")
     check(lib.xllm_moe_permute(ptr(ws.xp), ptr(ws.rows_of), ptr(x), ptr(ws.topk_ids), ptr(ws.slot), ptr(ws.offsets),
                                T, top_k, H, s), "moe_permute")
-    check(lib.xllm_gemm_bf16_grouped(ptr(ws.xp), ptr(w_gate_up), ptr(ws.h), ptr(ws.tile_expert), ws.rows, I2, H,
-                                     E_local, H, I2, s), "moe_gemm1")
-    act_and_mul(ws.h, "silu", out=ws.a)
-    check(lib.xllm_gemm_bf16_grouped(ptr(ws.a), ptr(w_down), ptr(ws.y), ptr(ws.tile_expert), ws.rows, H, inter,
-                                     E_local, inter, H, s), "moe_gemm2")
+    if w_scales is not None:
+        from . import fp8
+        xq, xs = fp8.quant_group128(ws.xp)
+        fp8.block_scaled_mm_grouped(xq, xs, w_gate_up, w_scales[0], ws.tile_expert, ws.h)
+        act_and_mul(ws.h, "silu", out=ws.a)
+        aq, as_ = fp8.quant_group128(ws.a)
+        fp8.block_scaled_mm_grouped(aq, as_, w_down, w_scales[1], ws.tile_expert, ws.y)
+    else:
+        check(lib.xllm_gemm_bf16_grouped(ptr(ws.xp), ptr(w_gate_up), ptr(ws.h), ptr(ws.tile_expert), ws.rows, I2, H,
+                                         E_local, H, I2, s), "moe_gemm1")
+        act_and_mul(ws.h, "silu", out=ws.a)
+        check(lib.xllm_gemm_bf16_grouped(ptr(ws.a), ptr(w_down), ptr(ws.y), ptr(ws.tile_expert), ws.rows, H, inter,
+                                         E_local, inter, H, s), "moe_gemm2")
     if out is None:
         out = torch.empty_like(x)
     check(lib.xllm_moe_finalize(ptr(out), ptr(ws.y), ptr(ws.rows_of), ptr(ws.topk_w), ptr(shared_out), T, top_k, H, s),

@@ -82,24 +82,29 @@ def save_file(tensors: Dict[str, torch.Tensor], path: str, metadata: Dict[str, s
             f.write(b)
 
 
-def dequant_fp8_stream(weights):
+def dequant_fp8_stream(weights, keep_fp8=None, dtype=torch.bfloat16):
     """Pair every block-scaled fp8 tensor `X.weight` with its `X.weight_scale_inv` (128 x 128 blocks,
-    DeepSeek-V3 checkpoints) and yield the bf16 weight; everything else passes through."""
+    DeepSeek-V3 checkpoints) and yield the bf16 weight; everything else passes through.  Weights named in
+    `keep_fp8` (a set of `X.weight` names: layers that execute in fp8) pass through untouched, scales
+    included.  `dtype`: type of the dequantised tensors (the model's compute type)."""
     from ..ops import fp8
     pending_w, pending_s = {}, {}
+    keep_fp8 = keep_fp8 or ()
     for name, t in weights:
-        if name.endswith(".weight_scale_inv"):
+        if name in keep_fp8 or (name.endswith("_scale_inv") and name[: -len("_scale_inv")] in keep_fp8):
+            yield name, t
+        elif name.endswith(".weight_scale_inv"):
             base = name[: -len("_scale_inv")]
             if base in pending_w:
-                yield base, fp8.dequant_block128_ref(pending_w.pop(base), t.float())
+                yield base, fp8.dequant_block128_ref(pending_w.pop(base), t.float(), dtype)
             else:
                 pending_s[base] = t
         elif t.dtype == torch.float8_e4m3fn:
             if name in pending_s:
-                yield name, fp8.dequant_block128_ref(t, pending_s.pop(name).float())
+                yield name, fp8.dequant_block128_ref(t, pending_s.pop(name).float(), dtype)
             else:
                 pending_w[name] = t
         else:
             yield name, t
     for name, t in pending_w.items():  # fp8 tensors without scales: plain cast
-        yield name, t.to(torch.bfloat16)
+        yield name, t.to(dtype)
