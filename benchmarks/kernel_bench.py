@@ -189,6 +189,51 @@ def gdn_rows(results, hbm, tf, tag):
         print(f"gdn_decode_step B={B:<4} {t*1e3:8.3f} ms {b/t/1e9:7.0f} GB/s  {b/t/1e9/hbm:5.2f} of {tag} copy bandwidth")
 
 
+def mla_rows(results, hbm, tf, tag):
+    """Absorbed MLA decode over the latent cache: every cached token is 1152 bytes, read once per
+    group of 16 heads; 128 heads (TP 1) re-read it from L2."""
+    from xllm_b200.ops import mla
+    page = 16
+    for N, nh, ctx in ((256, 16, 2048), (64, 16, 8192), (256, 128, 2048), (16, 128, 8192)):
+        nb = N * (ctx // page) + 1
+        cache = torch.randn(nb, 1, page, 576, device="cuda", dtype=torch.bfloat16)
+        bt = (torch.randperm(nb - 1, device="cuda")[: N * (ctx // page)] + 1).view(N, -1).to(torch.int32)
+        q = torch.randn(N, nh, 576, device="cuda", dtype=torch.bfloat16) * 0.3
+        sl = torch.full((N,), ctx, device="cuda", dtype=torch.int32)
+        out = torch.empty(N, nh, 512, device="cuda", dtype=torch.bfloat16)
+        t = bench(lambda: mla.decode(q, cache, bt, 0.07, seq_lens=sl, out=out))
+        b = N * ctx * 1152.0
+        fl = 2.0 * N * nh * ctx * (576 + 512)
+        results.append(dict(kernel="mla_decode_kernel", shape=f"rows={N} heads={nh} ctx={ctx}", ms=t * 1e3, gbs=b / t / 1e9,
+                            tflops=fl / t / 1e12, frac_of_roofline=max(b / (hbm * 1e9), fl / (tf * 1e12)) / t, peaks=tag))
+        print(f"mla_decode rows={N:<4} heads={nh:<4} ctx={ctx:<5} {t*1e3:8.3f} ms {b/t/1e9:7.0f} GB/s {fl/t/1e12:7.1f} TF/s")
+
+
+def fp8_rows(results, hbm, tf, tag):
+    """Block-scaled fp8 GEMM (1 x 128 activation scales, 128 x 128 weight scales) on DeepSeek-V3 shapes,
+    with the bf16 tcgen05 GEMM, the per-tensor fp8 GEMM and cuBLAS bf16 on the same shapes."""
+    from xllm_b200.ops import fp8
+    for M, N, K, name in ((4096, 7168, 7168, "square"), (4096, 4096, 7168, "gate_up/8"), (4096, 7168, 2048, "down expert"),
+                          (256, 7168, 7168, "decode"), (256, 24576, 1536, "q_b")):
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+        a_q, a_s = fp8.quant_group128(x)
+        w_q, w_s = fp8.quant_block128_ref(w)
+        a_t, s_t = fp8.quant_per_token(x)
+        ws1 = torch.ones(1, device="cuda")
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        t_blk = bench(lambda: fp8.block_scaled_mm(a_q, a_s, w_q, w_s, out=out))
+        t_pt = bench(lambda: fp8.scaled_mm(a_t, w_q, s_t, ws1, out=out))
+        t_bf = bench(lambda: gemm_tcgen05.gemm_nt(x, w, out=out))
+        t_lib = bench(lambda: torch.nn.functional.linear(x, w))
+        fl = 2.0 * M * N * K
+        results.append(dict(kernel="gemm_fp8_block_kernel", shape=f"{name} M={M} N={N} K={K}", ms=t_blk * 1e3,
+                            tflops=fl / t_blk / 1e12, per_tensor_fp8_ms=t_pt * 1e3, bf16_ms=t_bf * 1e3, cublas_bf16_ms=t_lib * 1e3,
+                            peaks=tag))
+        print(f"fp8 block {name:<12} M={M:<5} N={N:<6} K={K:<5} {t_blk*1e3:7.3f} ms {fl/t_blk/1e12:7.1f} TF/s | per-tensor fp8 "
+              f"{t_pt*1e3:7.3f} ms | bf16 tcgen05 {t_bf*1e3:7.3f} ms | cuBLAS bf16 {t_lib*1e3:7.3f} ms")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--what", default="gemm,decode,prefill,small")
@@ -197,7 +242,8 @@ def main():
     hbm, tf, tag = peaks()
     results = []
     for w in a.what.split(","):
-        {"gemm": gemm_rows, "decode": decode_rows, "prefill": prefill_rows, "small": small_rows, "gdn": gdn_rows}[w](results, hbm, tf, tag)
+        {"gemm": gemm_rows, "decode": decode_rows, "prefill": prefill_rows, "small": small_rows, "gdn": gdn_rows, "mla": mla_rows,
+         "fp8": fp8_rows}[w](results, hbm, tf, tag)
     if a.json:
         with open(a.json, "w") as f:
             json.dump(results, f, indent=1)

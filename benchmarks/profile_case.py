@@ -8,6 +8,14 @@ hundred MB on the device, a handful of launches).
     python benchmarks/profile_case.py --kernel prefill    # paged prefill attention, 4 x 2048
     python benchmarks/profile_case.py --kernel norm       # fused add + RMSNorm, 16384 x 4096
     python benchmarks/profile_case.py --kernel moe        # grouped GEMM of the MoE layer
+    python benchmarks/profile_case.py --kernel mla        # absorbed MLA decode, 64 rows x 16 heads, ctx 4096
+    python benchmarks/profile_case.py --kernel fp8_block  # block-scaled fp8 GEMM, 4096 x 7168 x 7168
+    python benchmarks/profile_case.py --kernel rope       # qk-norm + RoPE + paged KV write, 8192 tokens
+    python benchmarks/profile_case.py --kernel act        # SiLU-mul, 8192 x 24576
+    python benchmarks/profile_case.py --kernel sample     # sampler, 256 rows x 151936
+    python benchmarks/profile_case.py --kernel quant      # 1 x 128 group quantisation, 8192 x 7168
+    python benchmarks/profile_case.py --kernel gdn        # gated-delta-rule decode step
+    python benchmarks/profile_case.py --kernel route      # MoE routing, 8192 tokens x 256 experts
 """
 import argparse
 import math
@@ -70,6 +78,70 @@ def main():
         w2 = torch.randn(E, H, I, device=dev, dtype=torch.bfloat16) * 0.05
         ws = moe.MoeWorkspace(T, K, E, E, H, I, dev)
         fn = lambda: moe.fused_moe(x, logits, w1, w2, K, ws=ws)
+    elif a.kernel == "mla":
+        from xllm_b200.ops import mla
+        N, nh, ctx, page = 64, 16, 4096, 16
+        nb = N * (ctx // page) + 1
+        cache = torch.randn(nb, 1, page, 576, device=dev, dtype=torch.bfloat16)
+        bt = (torch.randperm(nb - 1, device=dev)[: N * (ctx // page)] + 1).view(N, -1).to(torch.int32)
+        q = torch.randn(N, nh, 576, device=dev, dtype=torch.bfloat16) * 0.3
+        sl = torch.full((N,), ctx, device=dev, dtype=torch.int32)
+        out = torch.empty(N, nh, 512, device=dev, dtype=torch.bfloat16)
+        fn = lambda: mla.decode(q, cache, bt, 0.07, seq_lens=sl, splits=4, out=out)
+    elif a.kernel == "fp8_block":
+        from xllm_b200.ops import fp8
+        M, N, K = 4096, 7168, 7168
+        a_q, a_s = fp8.quant_group128(torch.randn(M, K, device=dev, dtype=torch.bfloat16))
+        w_q, w_s = fp8.quant_block128_ref(torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.05)
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        fn = lambda: fp8.block_scaled_mm(a_q, a_s, w_q, w_s, out=out)
+    elif a.kernel == "rope":
+        from xllm_b200.ops import reference as ref
+        T, nq, nkv, d, page = 8192, 32, 8, 128, 16
+        qkv = torch.randn(T, (nq + 2 * nkv) * d, device=dev, dtype=torch.bfloat16)
+        pos = torch.arange(T, device=dev) % 4096
+        cs = ref.build_cos_sin_cache(d, 4096, 1e6, None, dev)
+        w = torch.ones(d, device=dev, dtype=torch.bfloat16)
+        kc = torch.zeros(T // page + 1, nkv, page, d, device=dev, dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        slots = torch.arange(T, device=dev, dtype=torch.int32)
+        fn = lambda: ops.rope_kv_write(qkv, nq, nkv, d, pos, cs, d, slots, kc, vc, w, w, 1e-6)
+    elif a.kernel == "act":
+        x = torch.randn(8192, 2 * 12288, device=dev, dtype=torch.bfloat16)
+        out = torch.empty(8192, 12288, device=dev, dtype=torch.bfloat16)
+        fn = lambda: ops.act_and_mul(x, "silu", out=out)
+    elif a.kernel == "sample":
+        B, V = 256, 151936
+        logits = torch.randn(B, V, device=dev, dtype=torch.bfloat16)
+        t = torch.full((B,), 0.8, device=dev)
+        k = torch.full((B,), 50, device=dev, dtype=torch.int32)
+        pp = torch.full((B,), 0.9, device=dev)
+        seeds = torch.arange(B, device=dev, dtype=torch.int64)
+        offs = torch.zeros(B, device=dev, dtype=torch.int32)
+        fn = lambda: ops.sample(logits, t, k, pp, seeds=seeds, offsets=offs, want_logprob=True)
+    elif a.kernel == "quant":
+        from xllm_b200.ops import fp8
+        x = torch.randn(8192, 7168, device=dev, dtype=torch.bfloat16)
+        fn = lambda: fp8.quant_group128(x)
+    elif a.kernel == "gdn":
+        from xllm_b200.ops import gdn
+        B, nv, dk, dv = 256, 32, 128, 128
+        state = torch.zeros(B, nv, dk, dv, device=dev, dtype=torch.float32)
+        slots = torch.arange(B, device=dev, dtype=torch.int64)
+        q, k = torch.randn(B, nv, dk, device=dev), torch.randn(B, nv, dk, device=dev) * 0.1
+        v = torch.randn(B, nv, dv, device=dev)
+        g, beta = -torch.rand(B, nv, device=dev), torch.rand(B, nv, device=dev)
+        fn = lambda: gdn.decode_step(state, slots, q, k, v, g, beta)
+    elif a.kernel == "route":
+        from xllm_b200.ops import _lib
+        T, E, K = 8192, 256, 8
+        logits = torch.randn(T, E, device=dev)
+        bias = torch.zeros(E, device=dev)
+        ws = moe.MoeWorkspace(T, K, E, E, 128, 128, dev)
+        lib = _lib.load()
+        fn = lambda: lib.xllm_moe_route(logits.data_ptr(), 1, bias.data_ptr(), ws.topk_ids.data_ptr(), ws.topk_w.data_ptr(),
+                                        ws.counts.data_ptr(), ws.slot.data_ptr(), T, E, K, 8, 4, 1, 1, 2.5, 0, E,
+                                        torch.cuda.current_stream().cuda_stream)
     else:
         raise SystemExit(f"unknown kernel {a.kernel}")
     for _ in range(a.iters):

@@ -1146,8 +1146,8 @@ static int launch_gemm_pair(const void* a, const void* w, void* c, const void* b
 // The scales differ from one K block to the next, so the products of different K blocks cannot be
 // summed inside the tensor core's accumulator.  Each K block (4 x tcgen05.mma kind::f8f6f4, K = 32) is
 // accumulated FRESH into one of two 128-column TMEM buffers; the four epilogue warps read a buffer back
-// (tcgen05.ld), multiply by the block's scales and add into fp32 registers (one output row of 128
-// columns per thread) while the MMA warp already fills the other buffer.  One tile is 128 x 128, so
+// (tcgen05.ld), multiply by the block's scales and add into fp32 registers (eight warps: one output row
+// and 64 of the 128 columns per thread) while the MMA warp already fills the other buffer.  One tile is 128 x 128, so
 // the weight scale is one number per (tile, K block) and the activation scale one per (row, K block).
 // Grouped form (MoE experts): `tile_expert[row tile]` names the expert of each 128-row tile (-1:
 // skip); expert e's weights start e * expert_rows rows into W and its scale rows e * expert_rows / 128
@@ -1161,7 +1161,7 @@ struct FbSmem {
   static constexpr int TOTAL = BAR_OFF + (2 * kFbStages + 4) * 8 + 16 + 1024;
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                       bf16* __restrict__ c, int64_t ldc, const float* __restrict__ a_scale,
                       const float* __restrict__ w_scale, int M, int N, int K, int a_box_rows,
@@ -1191,7 +1191,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);
+      mbar_init(tempty_bar(a), 8);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -1274,8 +1274,9 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       }
     }
   } else {
-    // -------------------------------------------------------------------- promote + store (warps 2..5)
-    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    // -------------------------------------------------------------------- promote + store (warps 2..9)
+    const int q = warp & 3;            // TMEM lane quarter this warp may access
+    const int ch0 = ((warp - 2) >> 2) * (BN / 2);   // its half of the tile's columns
     bool ok = true;
     uint32_t g = 0;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -1289,9 +1290,9 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       const bool row_ok = row < M;
       const float* as = a_scale + (int64_t)(row_ok ? row : 0) * k_blocks;
       const float* ws = w_scale + ((int64_t)(e * expert_rows + n0) / 128) * k_blocks;
-      float accum[BN];
+      float accum[BN / 2];
 #pragma unroll
-      for (int i = 0; i < BN; ++i) accum[i] = 0.f;
+      for (int i = 0; i < BN / 2; ++i) accum[i] = 0.f;
       float sc_next = row_ok ? as[0] * ws[0] : 0.f;
       for (int kb = 0; kb < k_blocks; ++kb, ++g) {
         const int acc = g & 1;
@@ -1299,24 +1300,25 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         if (kb + 1 < k_blocks) sc_next = row_ok ? as[kb + 1] * ws[kb + 1] : 0.f;   // in flight during the wait
         if (!mbar_wait(tfull_bar(acc), (g >> 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-#pragma unroll
-        for (int ch = 0; ch < BN / 32; ++ch) {
-          uint32_t r[32];
-          tmem_ld32(taddr + ch * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) accum[ch * 32 + i] = fmaf(__uint_as_float(r[i]), sc, accum[ch * 32 + i]);
-        }
+        const uint32_t taddr = tmem_base + acc * BN + ch0 + ((uint32_t)(q * 32) << 16);
+        uint32_t r0[32], r1[32];
+        tmem_ld32(taddr, r0);
+        tmem_ld32(taddr + 32, r1);
+        tmem_ld_wait();
+        // the buffer has been read: hand it back before the arithmetic
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(acc));
+#pragma unroll
+        for (int i = 0; i < 32; ++i) accum[i] = fmaf(__uint_as_float(r0[i]), sc, accum[i]);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) accum[32 + i] = fmaf(__uint_as_float(r1[i]), sc, accum[32 + i]);
       }
       if (ok && row_ok) {
-        bf16* dst = c + (int64_t)row * ldc + n0;
+        bf16* dst = c + (int64_t)row * ldc + n0 + ch0;
 #pragma unroll
-        for (int j = 0; j < BN / 8; ++j) {
-          if (n0 + j * 8 < N) reinterpret_cast<bf16x8*>(dst)[j] = pack8(accum + j * 8);   // N % 8 == 0
+        for (int j = 0; j < BN / 16; ++j) {
+          if (n0 + ch0 + j * 8 < N) reinterpret_cast<bf16x8*>(dst)[j] = pack8(accum + j * 8);   // N % 8 == 0
         }
       }
     }
@@ -1353,7 +1355,7 @@ static int launch_fp8_block(const void* a, const void* w, void* c, const void* a
     return (int)cudaErrorInvalidValue;
   const int tiles = ((M + kBM - 1) / kBM) * ((N + 127) / 128);
   const int grid = tiles < 148 ? tiles : 148;
-  launch_pdl(gemm_fp8_block_kernel, dim3(grid), dim3(192), (size_t)S::TOTAL, s, ta, tb, (bf16*)c, ldc,
+  launch_pdl(gemm_fp8_block_kernel, dim3(grid), dim3(320), (size_t)S::TOTAL, s, ta, tb, (bf16*)c, ldc,
              (const float*)a_scale, (const float*)w_scale, M, N, K, a_box, tile_expert, N, g_err_word[dev & 63]);
   return XLLM_LAUNCH_CHECK();
 }
