@@ -17,11 +17,14 @@ __device__ __forceinline__ float act_gelu_tanh(float x) {
 template <int ACT>
 __global__ void __launch_bounds__(256)
 act_and_mul_kernel(bf16* __restrict__ out, const bf16* __restrict__ x, int64_t tokens, int d,
-                   int64_t x_stride) {
+                   int64_t x_stride, const int32_t* __restrict__ n_rows_dev) {
   const int vec_per_row = d >> 3;
-  const int64_t total = tokens * vec_per_row;
   pdl_wait();
   pdl_launch_dependents();  // dependents may be scheduled now; they block in their own pdl_wait()
+  // the number of rows that hold data may live on the device (expert-parallel receive buffers: the
+  // launch is sized for the capacity, the work for what arrived)
+  if (n_rows_dev != nullptr) tokens = min(tokens, (int64_t)*n_rows_dev);
+  const int64_t total = tokens * vec_per_row;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t t = i / vec_per_row;
@@ -51,8 +54,25 @@ XLLM_API int xllm_act_and_mul(void* out, const void* x, int64_t tokens, int d, i
   int grid = (int)((total + 255) / 256);
   if (grid > 148 * 16) grid = 148 * 16;
   cudaStream_t s = (cudaStream_t)stream;
-  if (act == 0) launch_pdl(act_and_mul_kernel<0>, dim3(grid), dim3(256), 0, s, (bf16*)out, (const bf16*)x, tokens, d, x_stride);
-  else if (act == 1) launch_pdl(act_and_mul_kernel<1>, dim3(grid), dim3(256), 0, s, (bf16*)out, (const bf16*)x, tokens, d, x_stride);
-  else launch_pdl(act_and_mul_kernel<2>, dim3(grid), dim3(256), 0, s, (bf16*)out, (const bf16*)x, tokens, d, x_stride);
+  const int32_t* none = nullptr;
+  if (act == 0) launch_pdl(act_and_mul_kernel<0>, dim3(grid), dim3(256), 0, s, (bf16*)out, (const bf16*)x, tokens, d, x_stride, none);
+  else if (act == 1) launch_pdl(act_and_mul_kernel<1>, dim3(grid), dim3(256), 0, s, (bf16*)out, (const bf16*)x, tokens, d, x_stride, none);
+  else launch_pdl(act_and_mul_kernel<2>, dim3(grid), dim3(256), 0, s, (bf16*)out, (const bf16*)x, tokens, d, x_stride, none);
+  return XLLM_LAUNCH_CHECK();
+}
+
+// Same over the first min(max_tokens, *n_rows) rows, n_rows a device int32: for buffers sized for a
+// capacity of which only a prefix is in use (the count is not known on the host).
+XLLM_API int xllm_act_and_mul_rows(void* out, const void* x, int64_t max_tokens, const void* n_rows, int d,
+                                   int64_t x_stride, int act, void* stream) {
+  using namespace xllm;
+  if (max_tokens == 0) return 0;
+  if (d % 8 != 0 || n_rows == nullptr) return (int)cudaErrorInvalidValue;
+  const int grid = 148 * 8;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int32_t* nr = (const int32_t*)n_rows;
+  if (act == 0) launch_pdl(act_and_mul_kernel<0>, dim3(grid), dim3(256), 0, s, (bf16*)out, (const bf16*)x, max_tokens, d, x_stride, nr);
+  else if (act == 1) launch_pdl(act_and_mul_kernel<1>, dim3(grid), dim3(256), 0, s, (bf16*)out, (const bf16*)x, max_tokens, d, x_stride, nr);
+  else launch_pdl(act_and_mul_kernel<2>, dim3(grid), dim3(256), 0, s, (bf16*)out, (const bf16*)x, max_tokens, d, x_stride, nr);
   return XLLM_LAUNCH_CHECK();
 }

@@ -94,8 +94,9 @@ __global__ void ep_publish_counts_kernel(EpParams p, int32_t* __restrict__ count
 // send_off[e]   : first row, in the owner's receive buffer, of this rank's tokens of expert e
 // tile_expert[i]: local expert of row tile i of this rank's receive buffer (-1 = unused)
 // meta[0] = rows used in the local receive buffer (multiple of 128)
-__global__ void ep_layout_kernel(EpParams p, int32_t* __restrict__ send_off, int32_t* __restrict__ tile_expert,
-                                 int32_t* __restrict__ meta, int max_tiles) {
+__device__ __forceinline__ void ep_layout_dev(const EpParams& p, int32_t* __restrict__ send_off,
+                                              int32_t* __restrict__ tile_expert, int32_t* __restrict__ meta,
+                                              int max_tiles) {
   __shared__ int s_tot[kEpMaxExperts], s_before[kEpMaxExperts], s_base[kEpMaxExperts + kEpMaxRanks];
   const int32_t* C = reinterpret_cast<const int32_t*>(reinterpret_cast<const uint8_t*>(p.peer_bufs[p.rank]) + p.cnt_off);
   for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
@@ -140,10 +141,31 @@ __global__ void ep_layout_kernel(EpParams p, int32_t* __restrict__ send_off, int
   for (int i = meta[1] + threadIdx.x; i < max_tiles; i += blockDim.x) tile_expert[i] = -1;
 }
 
+__global__ void ep_layout_kernel(EpParams p, int32_t* __restrict__ send_off, int32_t* __restrict__ tile_expert,
+                                 int32_t* __restrict__ meta, int max_tiles) {
+  ep_layout_dev(p, send_off, tile_expert, meta, max_tiles);
+}
+
+// publish_counts + layout in one launch (one CTA): the counts go to every peer, the flag exchange
+// makes every peer's counts visible here, the layout follows from them.
+__global__ void ep_counts_layout_kernel(EpParams p, int32_t* __restrict__ counts, int32_t* __restrict__ send_off,
+                                        int32_t* __restrict__ tile_expert, int32_t* __restrict__ meta, int max_tiles) {
+  for (int i = threadIdx.x; i < p.E * p.world; i += blockDim.x) {
+    const int peer = i / p.E, e = i - peer * p.E;
+    int32_t* dst = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(p.peer_bufs[peer]) + p.cnt_off);
+    dst[p.rank * p.E + e] = counts[e];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < p.E; e += blockDim.x) counts[e] = 0;  // ready for the next routing pass
+  ep_exchange(p);
+  ep_layout_dev(p, send_off, tile_expert, meta, max_tiles);
+}
+
 __global__ void __launch_bounds__(128)
 ep_dispatch_kernel(EpParams p, const bf16* __restrict__ x, const int32_t* __restrict__ topk_ids,
                    const int32_t* __restrict__ slot, const int32_t* __restrict__ send_off,
-                   int32_t* __restrict__ where, int T, int K) {
+                   int32_t* __restrict__ where, int T, int K, int close) {
+  __shared__ int s_last;
   const int pair = blockIdx.x;
   const int t = pair / K;
   const int e = topk_ids[pair];
@@ -154,18 +176,50 @@ ep_dispatch_kernel(EpParams p, const bf16* __restrict__ x, const int32_t* __rest
       where[pair] = -1;
       atomicExch(p.err, 301);
     }
-    return;
+  } else {
+    if (threadIdx.x == 0) where[pair] = d * p.cap_rows + row;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)t * p.H);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.peer_bufs[d]) + p.recvx_off + (int64_t)row * p.H * 2);
+    for (int v = threadIdx.x; v < (p.H >> 3); v += blockDim.x) dst[v] = src[v];
   }
-  if (threadIdx.x == 0) where[pair] = d * p.cap_rows + row;
-  const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)t * p.H);
-  uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.peer_bufs[d]) + p.recvx_off + (int64_t)row * p.H * 2);
-  for (int v = threadIdx.x; v < (p.H >> 3); v += blockDim.x) dst[v] = src[v];
+  if (!close) return;
+  // closing exchange by the last CTA to finish: when this kernel has completed on a rank, the rows of
+  // every rank have landed in its receive buffer
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    s_last = atomicAdd(p.epochs + 1, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x == 0) p.epochs[1] = 0u;
+    ep_exchange(p);
+  }
 }
 
 __global__ void __launch_bounds__(128)
 ep_combine_kernel(EpParams p, bf16* __restrict__ out, const int32_t* __restrict__ where, const float* __restrict__ w,
-                  const bf16* __restrict__ shared_out, int T, int K) {
+                  const bf16* __restrict__ shared_out, int T, int K, int open) {
   const int t = blockIdx.x;
+  uint32_t e_open = 0;
+  if (open) {
+    // opening exchange: every rank's expert outputs are complete before anybody reads them.  CTA 0
+    // signals, every CTA polls its own (local) flag slots; the last CTA to finish publishes the epoch.
+    e_open = *reinterpret_cast<volatile uint32_t*>(p.epochs) + 1u;
+    if (blockIdx.x == 0 && threadIdx.x < p.world)
+      ep_st_release(reinterpret_cast<uint32_t*>(p.signal_pads[threadIdx.x]) + p.sig_off + p.rank, e_open);
+    if (threadIdx.x < p.world) {
+      const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.signal_pads[p.rank]) + p.sig_off + threadIdx.x;
+      const long long t0 = clock64();
+      while ((int32_t)(ep_ld_acquire(mine) - e_open) < 0) {
+        if (clock64() - t0 > p.budget) {
+          atomicExch(p.err, 1 + (int)threadIdx.x);
+          break;
+        }
+      }
+    }
+    __syncthreads();
+  }
   for (int v = threadIdx.x; v < (p.H >> 3); v += blockDim.x) {
     float acc[8];
 #pragma unroll
@@ -184,6 +238,17 @@ ep_combine_kernel(EpParams p, bf16* __restrict__ out, const int32_t* __restrict_
       for (int j = 0; j < 8; ++j) acc[j] += wk * f[j];
     }
     reinterpret_cast<bf16x8*>(out + (int64_t)t * p.H)[v] = pack8(acc);
+  }
+  if (open) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(p.epochs + 1, 1u) == gridDim.x - 1) {
+        p.epochs[1] = 0u;
+        *reinterpret_cast<volatile uint32_t*>(p.epochs) = e_open;
+        __threadfence();
+      }
+    }
   }
 }
 
@@ -243,7 +308,50 @@ XLLM_API int xllm_ep_dispatch(EP_COMMON_ARGS, const void* x, const void* topk_id
   if (T * K == 0) return 0;
   ep_dispatch_kernel<<<T * K, 128, 0, (cudaStream_t)stream>>>(EP_MAKE, (const bf16*)x, (const int32_t*)topk_ids,
                                                              (const int32_t*)slot, (const int32_t*)send_off,
-                                                             (int32_t*)where, T, K);
+                                                             (int32_t*)where, T, K, 0);
+  return XLLM_LAUNCH_CHECK();
+}
+
+// Fused forms (fewer launches and flag exchanges per MoE layer):
+//   xllm_ep_counts_layout  = publish_counts + layout                       (one exchange)
+//   xllm_ep_dispatch_sync  = dispatch, then the exchange that says "all rows have landed"
+//   xllm_ep_combine_sync   = the exchange that says "all expert outputs are complete", then combine
+// With these a layer needs three exchanges and no closing barrier: a rank can only pass the dispatch
+// exchange of the next layer after every rank has finished this layer's combine, so the receive and
+// output buffers are free again by the time anybody writes them.
+XLLM_API int xllm_ep_counts_layout(EP_COMMON_ARGS, void* counts, void* send_off, void* tile_expert, void* meta,
+                                   int max_tiles, void* stream) {
+  using namespace xllm;
+  if (int rc = ep_check(world, E, H)) return rc;
+  ep_counts_layout_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(EP_MAKE, (int32_t*)counts, (int32_t*)send_off,
+                                                              (int32_t*)tile_expert, (int32_t*)meta, max_tiles);
+  return XLLM_LAUNCH_CHECK();
+}
+
+XLLM_API int xllm_ep_dispatch_sync(EP_COMMON_ARGS, const void* x, const void* topk_ids, const void* slot,
+                                   const void* send_off, void* where, int T, int K, void* stream) {
+  using namespace xllm;
+  if (int rc = ep_check(world, E, H)) return rc;
+  if (T * K == 0) {   // nothing to send: only the exchange
+    ep_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(EP_MAKE);
+    return XLLM_LAUNCH_CHECK();
+  }
+  ep_dispatch_kernel<<<T * K, 128, 0, (cudaStream_t)stream>>>(EP_MAKE, (const bf16*)x, (const int32_t*)topk_ids,
+                                                             (const int32_t*)slot, (const int32_t*)send_off,
+                                                             (int32_t*)where, T, K, 1);
+  return XLLM_LAUNCH_CHECK();
+}
+
+XLLM_API int xllm_ep_combine_sync(EP_COMMON_ARGS, void* out, const void* where, const void* w, const void* shared_out,
+                                  int T, int K, void* stream) {
+  using namespace xllm;
+  if (int rc = ep_check(world, E, H)) return rc;
+  if (T == 0) {
+    ep_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(EP_MAKE);
+    return XLLM_LAUNCH_CHECK();
+  }
+  ep_combine_kernel<<<T, 128, 0, (cudaStream_t)stream>>>(EP_MAKE, (bf16*)out, (const int32_t*)where, (const float*)w,
+                                                        (const bf16*)shared_out, T, K, 1);
   return XLLM_LAUNCH_CHECK();
 }
 
@@ -254,7 +362,7 @@ XLLM_API int xllm_ep_combine(EP_COMMON_ARGS, void* out, const void* where, const
   if (int rc = ep_check(world, E, H)) return rc;
   if (T == 0) return 0;
   ep_combine_kernel<<<T, 128, 0, (cudaStream_t)stream>>>(EP_MAKE, (bf16*)out, (const int32_t*)where, (const float*)w,
-                                                        (const bf16*)shared_out, T, K);
+                                                        (const bf16*)shared_out, T, K, 0);
   return XLLM_LAUNCH_CHECK();
 }
 

@@ -1145,7 +1145,9 @@ static int launch_gemm_pair(const void* a, const void* w, void* c, const void* b
 //
 // The scales differ from one K block to the next, so the products of different K blocks cannot be
 // summed inside the tensor core's accumulator.  Each K block (4 x tcgen05.mma kind::f8f6f4, K = 32) is
-// accumulated FRESH into one of two 128-column TMEM buffers; the four epilogue warps read a buffer back
+// accumulated FRESH into one of four 128-column TMEM buffers (all 512 columns: with two, the round trip
+// MMA -> commit -> tcgen05.ld -> release of a buffer, ~1000 cycles, is longer than the ~260 cycles of a
+// K block's MMAs and the tensor pipe idles half the time); the four epilogue warps read a buffer back
 // (tcgen05.ld), multiply by the block's scales and add into fp32 registers (eight warps: one output row
 // and 64 of the 128 columns per thread) while the MMA warp already fills the other buffer.  One tile is 128 x 128, so
 // the weight scale is one number per (tile, K block) and the activation scale one per (row, K block).
@@ -1153,12 +1155,13 @@ static int launch_gemm_pair(const void* a, const void* w, void* c, const void* b
 // skip); expert e's weights start e * expert_rows rows into W and its scale rows e * expert_rows / 128
 // rows into w_scale.
 constexpr int kFbStages = 6;
+constexpr int kFbAcc = 4;        // TMEM accumulators of 128 columns
 struct FbSmem {
   static constexpr int A_BYTES = kBM * 128;        // 128 rows x 128 bytes (one K block of e4m3)
   static constexpr int B_BYTES = 128 * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFF = kFbStages * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFF + (2 * kFbStages + 4) * 8 + 16 + 1024;
+  static constexpr int TOTAL = BAR_OFF + (2 * kFbStages + 2 * kFbAcc) * 8 + 16 + 1024;
 };
 
 __global__ void __launch_bounds__(320, 1)
@@ -1175,8 +1178,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (kFbStages + s); };
   auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * kFbStages + a); };
-  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * kFbStages + 2 + a); };
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::BAR_OFF + (2 * kFbStages + 4) * 8);
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * kFbStages + kFbAcc + a); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::BAR_OFF + (2 * kFbStages + 2 * kFbAcc) * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1189,7 +1192,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < kFbAcc; ++a) {
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), 8);
     }
@@ -1198,7 +1201,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
-                 "r"(256));
+                 "r"(512));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   tc_fence_before();
@@ -1251,12 +1254,12 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    uint32_t g = 0;  // K blocks issued so far: block g uses accumulator g & 1 for the (g >> 1)-th time
+    uint32_t g = 0;  // K blocks issued so far: block g uses accumulator g % 4 for the (g / 4)-th time
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       if (tile_expert != nullptr && tile_expert[tile % m_tiles] < 0) continue;
       for (int kb = 0; kb < k_blocks; ++kb, ++g) {
-        const int acc = g & 1;
-        if (!mbar_wait_warp(tempty_bar(acc), ((g >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        const int acc = g & (kFbAcc - 1);
+        if (!mbar_wait_warp(tempty_bar(acc), ((g / kFbAcc) & 1) ^ 1, abort_flag)) { ok = false; break; }
         if (!mbar_wait_warp(full_bar(stage), phase, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t a_addr = sbase + stage * S::STAGE_BYTES;
@@ -1295,10 +1298,10 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       for (int i = 0; i < BN / 2; ++i) accum[i] = 0.f;
       float sc_next = row_ok ? as[0] * ws[0] : 0.f;
       for (int kb = 0; kb < k_blocks; ++kb, ++g) {
-        const int acc = g & 1;
+        const int acc = g & (kFbAcc - 1);
         const float sc = sc_next;
         if (kb + 1 < k_blocks) sc_next = row_ok ? as[kb + 1] * ws[kb + 1] : 0.f;   // in flight during the wait
-        if (!mbar_wait(tfull_bar(acc), (g >> 1) & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(tfull_bar(acc), (g / kFbAcc) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t taddr = tmem_base + acc * BN + ch0 + ((uint32_t)(q * 32) << 16);
         uint32_t r0[32], r1[32];
@@ -1328,7 +1331,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   if (threadIdx.x == 0 && *abort_flag && err_word != nullptr) atomicExch(err_word, 1);
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
   }
 }
 

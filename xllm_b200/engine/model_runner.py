@@ -25,6 +25,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Optional
 
+import os
+
 import numpy as np
 import torch
 
@@ -231,7 +233,8 @@ class ModelRunner:
         if npf == 0:
             Bp = self._bucket(nd)
             return None if Bp is None else (Bp, 0, 0, mode)
-        if npf > self.prefill_graph_seqs or not getattr(self.model, "supports_prefill_graph", True):
+        if npf > self.prefill_graph_seqs or not getattr(self.model, "supports_prefill_graph", True) \
+                or os.environ.get("XLLM_PREFILL_GRAPH", "1") == "0":
             return None
         ptok = batch.n_tokens - nd
         Tq = next((t for t in self.prefill_buckets if t >= ptok), None)

@@ -153,7 +153,8 @@ class SparseMoeBlock(Module):
     def _use_a2a(self, x, comm) -> bool:
         import os
         return (self.ep > 1 and not self.fp8 and x.is_cuda and comm is not None and self.ep == self.ps.tp_size
-                and os.environ.get("XLLM_EP_MODE", "a2a") == "a2a" and not torch.cuda.is_current_stream_capturing())
+                and os.environ.get("XLLM_EP_MODE", "a2a") == "a2a"
+                and (getattr(self.ps, "ep_comm", None) is not None or not torch.cuda.is_current_stream_capturing()))
 
     def _forward_a2a(self, x, logits, shared_out, comm, out):
         a = self.args
@@ -190,7 +191,8 @@ class SparseMoeBlock(Module):
         ps = self.ps
         group = ps.moe_ep_group or ps.world_group
         T = x.shape[0]
-        if x.is_cuda and os.environ.get("XLLM_EP_MODE", "a2a") == "a2a" and not torch.cuda.is_current_stream_capturing():
+        if x.is_cuda and os.environ.get("XLLM_EP_MODE", "a2a") == "a2a" and \
+                (getattr(ps, "ep_comm", None) is not None or not torch.cuda.is_current_stream_capturing()):
             ep = getattr(ps, "ep_comm", None)
             if ep is None:
                 from ..parallel.ep import EpComm
@@ -241,7 +243,4 @@ def _make_mlp(args, dtype, device, ps):
 @register_model("qwen3_moe", "qwen2_moe", "Qwen3MoeForCausalLM", "Qwen2MoeForCausalLM")
 def build_qwen_moe(args, dtype, device, ps):
     m = DenseCausalLM(args, dtype, device, ps, make_mlp=_make_mlp(args, dtype, device, ps))
-    # with expert parallelism prompt chunks go through the all-to-all kernels, which are not captured:
-    # only decode-only steps replay graphs
-    m.supports_prefill_graph = not (ps is not None and ps.ep_size > 1)
     return m

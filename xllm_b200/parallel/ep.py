@@ -24,6 +24,10 @@ _lib.register_signature("xllm_ep_publish_counts", _EP + [P, P])
 _lib.register_signature("xllm_ep_layout", _EP + [P, P, P, I, P])
 _lib.register_signature("xllm_ep_dispatch", _EP + [P, P, P, P, P, I, I, P])
 _lib.register_signature("xllm_ep_combine", _EP + [P, P, P, P, I, I, P])
+_lib.register_signature("xllm_ep_counts_layout", _EP + [P, P, P, P, I, P])
+_lib.register_signature("xllm_ep_dispatch_sync", _EP + [P, P, P, P, P, I, I, P])
+_lib.register_signature("xllm_ep_combine_sync", _EP + [P, P, P, P, I, I, P])
+_lib.register_signature("xllm_act_and_mul_rows", [P, P, L, P, I, L, I, P])
 
 
 class EpComm:
@@ -78,7 +82,7 @@ class EpComm:
             scale=1.0, shared_out=None, out=None):
         """x [T, H] = this rank's tokens, logits [T, E]; w_gate_up [E_local, 2I, H] and w_down
         [E_local, H, I] = this rank's experts.  Returns the MoE output of this rank's tokens."""
-        from ..ops import _count, act_and_mul
+        from ..ops import _count
         lib = _lib.load()
         T = x.shape[0]
         assert T <= self.max_local_tokens and x.shape[1] == self.H
@@ -96,23 +100,26 @@ class EpComm:
         check(lib.xllm_moe_route(ptr(logits), int(lf), ptr(bias), ptr(self.topk_ids), ptr(self.topk_w), ptr(self.counts),
                                  ptr(self.slot), T, self.E, self.K, n_group, topk_group, 0 if scoring == "softmax" else 1,
                                  int(renorm), float(scale), 0, self.E, s), "moe_route")
-        check(lib.xllm_ep_publish_counts(*c, ptr(self.counts), s), "ep_publish_counts")
-        check(lib.xllm_ep_layout(*c, ptr(self.send_off), ptr(self.tile_expert), ptr(self.meta), self.max_tiles, s), "ep_layout")
-        check(lib.xllm_ep_dispatch(*c, ptr(x), ptr(self.topk_ids), ptr(self.slot), ptr(self.send_off), ptr(self.where),
-                                   T, self.K, s), "ep_dispatch")
-        check(lib.xllm_ep_barrier(*c, s), "ep_barrier")          # every rank's rows have landed
+        # counts to every peer + layout of the receive buffers (exchange 1)
+        check(lib.xllm_ep_counts_layout(*c, ptr(self.counts), ptr(self.send_off), ptr(self.tile_expert), ptr(self.meta),
+                                        self.max_tiles, s), "ep_counts_layout")
+        # rows to their experts' owners; the kernel ends when every rank's rows have landed (exchange 2)
+        check(lib.xllm_ep_dispatch_sync(*c, ptr(x), ptr(self.topk_ids), ptr(self.slot), ptr(self.send_off),
+                                        ptr(self.where), T, self.K, s), "ep_dispatch")
         check(lib.xllm_gemm_bf16_grouped(ptr(self.recv_x), ptr(w_gate_up), ptr(self.h), ptr(self.tile_expert), self.cap,
                                          I2, self.H, self.e_local, self.H, I2, s), "ep_gemm1")
-        act_and_mul(self.h, "silu", out=self.a)
+        # the activation only touches the rows that arrived (meta[0], known on the device)
+        check(lib.xllm_act_and_mul_rows(ptr(self.a), ptr(self.h), self.cap, ptr(self.meta), inter, I2, 0, s), "ep_act")
         check(lib.xllm_gemm_bf16_grouped(ptr(self.a), ptr(w_down), ptr(self.recv_y), ptr(self.tile_expert), self.cap,
                                          self.H, inter, self.e_local, inter, self.H, s), "ep_gemm2")
-        check(lib.xllm_ep_barrier(*c, s), "ep_barrier")          # every rank's expert outputs are complete
         if out is None:
             out = torch.empty_like(x)
-        check(lib.xllm_ep_combine(*c, ptr(out), ptr(self.where), ptr(self.topk_w), ptr(shared_out), T, self.K, s),
+        # waits for every rank's expert outputs (exchange 3), then gathers and weights this rank's rows.
+        # No closing barrier: nobody can overwrite a buffer before the next layer's exchanges, which
+        # every rank only enters after this combine.
+        check(lib.xllm_ep_combine_sync(*c, ptr(out), ptr(self.where), ptr(self.topk_w), ptr(shared_out), T, self.K, s),
               "ep_combine")
-        check(lib.xllm_ep_barrier(*c, s), "ep_barrier")          # peers are done reading recv_y
-        _count(10)
+        _count(7)
         return out
 
     def error_status(self) -> int:
