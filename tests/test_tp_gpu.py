@@ -79,3 +79,12 @@ def test_moe_engine_with_expert_parallel_all_to_all():
     replicate path; tokens must match the single-GPU engine."""
     out = _run("mp_tp_engine.py", 2, {"MODEL": "moe"})
     assert "TP_ENGINE_OK moe-ep-a2a" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_pd_disaggregation_two_processes_peer_push():
+    """Prefill instance on GPU 0, decode instance on GPU 1, separate processes: KV pushed per layer
+    from inside the prefill forward, control messages over a socket, tokens equal one engine's."""
+    out = _run("mp_pd.py", 2, timeout=600)
+    assert "PD_OK" in out
+    print(out[out.index("PD_OK"):].splitlines()[0])

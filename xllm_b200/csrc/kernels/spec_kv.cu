@@ -208,6 +208,25 @@ __global__ void kv_wait_kernel(const uint32_t* flag, uint32_t value, int* status
   }
 }
 
+// The same for n flags at once (one per layer): thread i waits for flags[i]; status[0] = 0 when all
+// arrived, else 1 + the index of a flag that did not arrive within the budget.
+__global__ void kv_wait_many_kernel(const uint32_t* flags, int n, uint32_t value, int* status, long long budget_cycles) {
+  __shared__ int s_bad;
+  if (threadIdx.x == 0) s_bad = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const long long t0 = clock64();
+    uint32_t v;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + i) : "memory");
+      if ((int32_t)(v - value) >= 0) break;
+      if (clock64() - t0 > budget_cycles) { atomicMax(&s_bad, i + 1); break; }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *status = s_bad;
+}
+
 }  // namespace xllm
 
 XLLM_API int xllm_spec_verify(const void* draft_ids, const void* target_probs, const void* draft_probs,
@@ -262,5 +281,13 @@ XLLM_API int xllm_kv_push(const void* src, void* dst, const void* pairs, int n_p
 XLLM_API int xllm_kv_wait(const void* flag, uint32_t value, void* status, long long budget_cycles, void* stream) {
   using namespace xllm;
   kv_wait_kernel<<<1, 1, 0, (cudaStream_t)stream>>>((const uint32_t*)flag, value, (int*)status, budget_cycles);
+  return XLLM_LAUNCH_CHECK();
+}
+
+XLLM_API int xllm_kv_wait_many(const void* flags, int n, uint32_t value, void* status, long long budget_cycles,
+                               void* stream) {
+  using namespace xllm;
+  if (n <= 0) return (int)cudaErrorInvalidValue;
+  kv_wait_many_kernel<<<1, 128, 0, (cudaStream_t)stream>>>((const uint32_t*)flags, n, value, (int*)status, budget_cycles);
   return XLLM_LAUNCH_CHECK();
 }

@@ -367,6 +367,13 @@ PYBIND11_MODULE(_rt, m) {
       .def("adopt_prefilled", &Scheduler::adopt_prefilled, py::arg("request_id"), py::arg("tokens"),
            py::arg("num_prompt_tokens"), py::arg("sampling"), py::arg("stopping"), py::arg("priority") = 0,
            py::arg("offline") = false, py::arg("stream") = false)
+      .def("reserve_blocks", &Scheduler::reserve_blocks, py::arg("request_id"), py::arg("n_tokens"))
+      .def("cancel_reserved", &Scheduler::cancel_reserved)
+      .def("num_reserved", &Scheduler::num_reserved)
+      .def("reserved_ids", &Scheduler::reserved_ids)
+      .def("adopt_reserved", &Scheduler::adopt_reserved, py::arg("request_id"), py::arg("tokens"),
+           py::arg("num_prompt_tokens"), py::arg("sampling"), py::arg("stopping"), py::arg("priority") = 0,
+           py::arg("offline") = false, py::arg("stream") = false)
       .def("held_blocks", &Scheduler::held_blocks)
       .def("release_held", &Scheduler::release_held)
       .def("schedule", &Scheduler::schedule, py::call_guard<py::gil_scoped_release>())

@@ -211,6 +211,68 @@ class Scheduler {
     return blocks;
   }
 
+  // PD disaggregation, decode side, in two phases (the prompt's KV is pushed into the reserved
+  // blocks WHILE the prefill instance computes it, so the blocks must exist before the tokens do):
+  // reserve_blocks() sets blocks aside for `n_tokens` (+ one decode step), adopt_reserved() turns
+  // the reservation into a running sequence once the first token has arrived, cancel_reserved()
+  // gives the blocks back (prefill side gone, request aborted).
+  std::vector<int32_t> reserve_blocks(const std::string& id, int32_t n_tokens) {
+    std::vector<int32_t> none;
+    if (n_tokens < 1 || reserved_.count(id) || requests_.count(id)) return none;
+    BlockManager& bm = *bm_[0];
+    const int32_t need = (n_tokens + 2 + cfg_.num_speculative_tokens + cfg_.block_size - 1) / cfg_.block_size;
+    std::vector<int32_t> blocks = bm.allocate(need);
+    if ((int32_t)blocks.size() < need) return none;
+    reserved_.emplace(id, blocks);
+    return blocks;
+  }
+  bool cancel_reserved(const std::string& id) {
+    auto it = reserved_.find(id);
+    if (it == reserved_.end()) return false;
+    bm_[0]->free_blocks(it->second);
+    reserved_.erase(it);
+    return true;
+  }
+  int32_t num_reserved() const { return (int32_t)reserved_.size(); }
+  std::vector<std::string> reserved_ids() const {
+    std::vector<std::string> out;
+    for (auto& kv : reserved_) out.push_back(kv.first);
+    return out;
+  }
+  bool adopt_reserved(const std::string& id, const std::vector<int32_t>& tokens, int32_t num_prompt_tokens,
+                      const SamplingParams& sp, const StoppingParams& st, int32_t priority, bool offline,
+                      bool stream) {
+    auto it = reserved_.find(id);
+    if (it == reserved_.end() || requests_.count(id) || (int32_t)tokens.size() < 2 || num_prompt_tokens < 1 ||
+        num_prompt_tokens >= (int32_t)tokens.size())
+      return false;
+    const int32_t need = ((int32_t)tokens.size() + 1 + cfg_.num_speculative_tokens + cfg_.block_size - 1) / cfg_.block_size;
+    if ((int32_t)it->second.size() < need) return false;
+    auto req = std::make_unique<Request>();
+    req->request_id = id;
+    req->sampling = sp;
+    req->stopping = st;
+    req->priority = priority;
+    req->offline = offline;
+    req->stream = stream;
+    req->arrival_time = now_seconds();
+    auto s = std::make_unique<Sequence>();
+    s->seq_id = next_seq_id_++;
+    s->request = req.get();
+    s->tokens = tokens;
+    s->num_prompt_tokens = num_prompt_tokens;
+    s->kv_computed = (int32_t)tokens.size() - 1;
+    s->blocks = it->second;
+    s->stage = SeqStage::DECODE;
+    s->first_token_time = req->arrival_time;
+    Sequence* sp_ = s.get();
+    req->seqs.push_back(std::move(s));
+    requests_.emplace(id, std::move(req));
+    running_.push_back(sp_);
+    reserved_.erase(it);
+    return true;
+  }
+
   // Blocks of a finished sequence that hold_finished_blocks kept alive (empty if none).
   std::vector<int32_t> held_blocks(const std::string& id) const {
     auto it = held_.find(id);
@@ -410,6 +472,7 @@ class Scheduler {
 
  private:
   std::unordered_map<std::string, std::vector<int32_t>> held_;
+  std::unordered_map<std::string, std::vector<int32_t>> reserved_;  // decode side of PD: blocks awaiting a prefill
   struct InFlight {
     std::vector<Sequence*> seqs;
     std::vector<int32_t> q_lens, sample_seq;

@@ -85,7 +85,7 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float16": torch.
 
 class LLMEngine:
     def __init__(self, cfg: EngineConfig, ps: Optional[ParallelState] = None, model=None,
-                 model_args: Optional[ModelArgs] = None, hold_finished_blocks: bool = False):
+                 model_args: Optional[ModelArgs] = None, hold_finished_blocks: bool = False, kv_allocator=None):
         self.cfg = cfg
         self.ps = ps or single()
         rt = _rt()
@@ -167,7 +167,7 @@ class LLMEngine:
         self.runner = ModelRunner(self.model, cfg.block_size, num_blocks, cfg.max_seqs_per_batch,
                                   cfg.max_tokens_per_batch, max_len, self.device, self.dtype,
                                   enable_graph=cfg.enable_graph and bool(getattr(self.model, "supports_graph", True)),
-                                  graph_buckets=cfg.graph_buckets)
+                                  graph_buckets=cfg.graph_buckets, kv_allocator=kv_allocator)
         self.runner.overlap = cfg.enable_schedule_overlap
         if getattr(self.model, "needs_state", False):
             # one state slot per sequence that can hold KV at the same time; the scheduler admits no

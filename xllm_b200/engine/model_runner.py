@@ -89,7 +89,8 @@ class ModelRunner:
     def __init__(self, model, block_size: int, num_blocks: int, max_seqs: int, max_tokens: int,
                  max_model_len: int, device, dtype, enable_graph: bool = True,
                  graph_buckets: Optional[List[int]] = None, n_staging: int = 2,
-                 prefill_graph_tokens: Optional[List[int]] = None, prefill_graph_seqs: int = 4):
+                 prefill_graph_tokens: Optional[List[int]] = None, prefill_graph_seqs: int = 4,
+                 kv_allocator=None):
         from .. import _rt
         self._rt = _rt
         self.model = model
@@ -104,6 +105,7 @@ class ModelRunner:
         self.cuda = self.device.type == "cuda"
         self.enable_graph = enable_graph and self.cuda
         self.bt_cols = (max_model_len + block_size - 1) // block_size
+        self.kv_allocator = kv_allocator     # (n_bytes) -> uint8 tensor, e.g. a slice of peer-mapped memory
         self.kv_caches = self._alloc_kv()
         cap = self._capacity(self.max_tokens, self.max_seqs, self.max_seqs, self.bt_cols)
         self.staging = [_Staging(cap, self.device, self.cuda) for _ in range(n_staging)]
@@ -145,7 +147,15 @@ class ModelRunner:
         L = self.args.num_hidden_layers
         planes = int(getattr(m, "kv_planes", 2))
         shape = (L, planes, self.num_blocks, m.num_kv_heads_local, self.block_size, m.head_dim)
-        kv = torch.zeros(shape, dtype=self.dtype, device=self.device)
+        if self.kv_allocator is not None:
+            n = 1
+            for d in shape:
+                n *= d
+            raw = self.kv_allocator(n * torch.empty((), dtype=self.dtype).element_size())
+            kv = raw.view(self.dtype).view(shape)
+            kv.zero_()
+        else:
+            kv = torch.zeros(shape, dtype=self.dtype, device=self.device)
         self.kv_tensor = kv
         return [(kv[i, 0], kv[i, planes - 1]) for i in range(L)]
 

@@ -14,7 +14,7 @@ import torch.distributed as dist
 
 def _bcast(obj, ps):
     box = [obj]
-    dist.broadcast_object_list(box, src=0, group=ps.world_group)
+    dist.broadcast_object_list(box, src=getattr(ps, "leader", 0), group=ps.world_group)
     return box[0]
 
 

@@ -41,6 +41,10 @@ class AttentionMetadata:
     # the step has a fixed padded shape (CUDA-graph replay): token rows that belong to no sequence
     # exist, and whatever a kernel leaves unwritten for them must still be finite
     padded: bool = False
+    # called with a layer's K cache right after the layer has written its new KV rows (prefill side
+    # of a disaggregated pair: the layer's blocks are pushed to the decode instance while the next
+    # layer computes)
+    kv_hook: Optional[Callable] = None
 
     @property
     def n_seqs(self):
@@ -480,6 +484,8 @@ class Attention(Module):
                               slots=meta.slots, k_cache=k_cache, v_cache=v_cache,
                               q_norm_w=self._norm_w(self.q_norm), k_norm_w=self._norm_w(self.k_norm), eps=self.eps,
                               interleaved=self.rope.interleaved)
+        if meta.kv_hook is not None:
+            meta.kv_hook(k_cache)
         T = q.shape[0]
         out = (torch.zeros if meta.padded else torch.empty)((T, self.nq, self.d), dtype=q.dtype, device=q.device)
         nd = meta.n_decode

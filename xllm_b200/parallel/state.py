@@ -68,6 +68,13 @@ class ParallelState:
     cp_group: Optional[object] = None
     tp_ranks: List[int] = field(default_factory=lambda: [0])
     comm: Optional[object] = None  # fused-kernel communicator (symmetric memory), set by symm.attach
+    # a job may hold several independent serving instances (prefill / decode pairs): `rank` and
+    # `world_size` above are those of THIS instance, the job-wide ones are below
+    instance: int = 0
+    n_instances: int = 1
+    global_rank: int = 0
+    job_group: Optional[object] = None
+    leader: int = 0                # job rank of this instance's rank 0 (source of in-instance broadcasts)
 
     @property
     def tp_size(self) -> int:
@@ -143,18 +150,24 @@ def single() -> ParallelState:
 
 
 def init_parallel(dp_size: int = 1, ep_size: int = 1, cp_size: int = 1, backend: Optional[str] = None,
-                  timeout_s: float = 600.0) -> ParallelState:
-    """Join the job described by RANK / WORLD_SIZE / LOCAL_RANK / MASTER_ADDR / MASTER_PORT."""
+                  timeout_s: float = 600.0, instances: int = 1) -> ParallelState:
+    """Join the job described by RANK / WORLD_SIZE / LOCAL_RANK / MASTER_ADDR / MASTER_PORT.
+    With `instances` > 1 the job's ranks are cut into that many equal, contiguous slices and every
+    slice becomes an independent instance (its own world / TP / DP / EP groups): the prefill and
+    decode halves of a disaggregated deployment started by one launcher."""
     import datetime
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    job_world = int(os.environ.get("WORLD_SIZE", "1"))
+    job_rank = int(os.environ.get("RANK", "0"))
+    assert job_world % instances == 0, (job_world, instances)
+    world = job_world // instances
+    inst, rank = divmod(job_rank, world)
+    local = int(os.environ.get("LOCAL_RANK", str(job_rank)))
     use_cuda = torch.cuda.is_available()
     device = torch.device("cuda", local) if use_cuda else torch.device("cpu")
     if use_cuda:
         torch.cuda.set_device(device)
-    if world == 1:
+    if job_world == 1:
         return ParallelState(device=device)
     if backend is None:
         backend = "nccl" if use_cuda else "gloo"
@@ -164,20 +177,31 @@ def init_parallel(dp_size: int = 1, ep_size: int = 1, cp_size: int = 1, backend:
         kw = {}
         if backend == "nccl":
             kw["device_id"] = device
-        dist.init_process_group(backend=backend, rank=rank, world_size=world,
+        dist.init_process_group(backend=backend, rank=job_rank, world_size=job_world,
                                 timeout=datetime.timedelta(seconds=timeout_s), **kw)
     assert world % (dp_size * cp_size) == 0 and world % ep_size == 0
     st = ParallelState(rank=rank, world_size=world, dp_size=dp_size, ep_size=ep_size, cp_size=cp_size,
-                       device=device)
-    st.world_group = dist.group.WORLD
+                       device=device, instance=inst, n_instances=instances, global_rank=job_rank,
+                       job_group=dist.group.WORLD, leader=inst * world)
 
     def make(groups):
-        mine = None
-        for ranks in groups:
-            g = dist.new_group(ranks) if len(ranks) > 1 else None
-            if rank in ranks:
-                mine = (g, ranks)
+        # `groups` are rank lists of ONE instance; every process of the job creates the groups of
+        # every instance (group creation is collective over the job) and keeps its own
+        mine = (None, [rank])
+        for j in range(instances):
+            for ranks in groups:
+                job_ranks = [j * world + r for r in ranks]
+                g = dist.new_group(job_ranks) if len(job_ranks) > 1 else None
+                if job_rank in job_ranks:
+                    mine = (g, ranks)
         return mine
+
+    if instances == 1:
+        st.world_group = dist.group.WORLD
+    else:
+        st.world_group, _ = make([list(range(world))])
+    if world == 1:
+        return st
 
     if cp_size > 1:
         tp_groups, cp_groups = cp_rank_layout(world, dp_size, cp_size)
