@@ -435,12 +435,45 @@ def profile_steps(eng, step, submit_more, n, rank):
                   f"{name[:100]}", file=sys.stderr)
 
 
+def run_library(args):
+    """The same workload through the all-library engine of the image (vLLM: cuBLAS + NCCL +
+    FlashAttention/FlashInfer + CUDA graphs), whole workload, end to end.  Prints one JSON line with
+    "impl": "library"; it is never the reference arm.  Under a multi-rank launcher only rank 0 runs
+    it (the library spawns its own workers on the GPUs of the node)."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT", "TORCHELASTIC_RUN_ID",
+              "GROUP_RANK", "ROLE_RANK", "LOCAL_WORLD_SIZE", "ROLE_WORLD_SIZE", "GROUP_WORLD_SIZE"):
+        os.environ.pop(k, None)
+    cfg = CONFIGS[args.config]
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+    line = {"impl": "library", "metric": "output_tokens_per_s", "unit": "tokens/s", "n_gpus": args.gpus,
+            "higher_is_better": True, "dtype": "bf16", "data": "synthetic token ids, random-init weights",
+            "config": {"model": args.model or cfg["model"], "input_len": args.input_len or cfg["input_len"],
+                       "output_len": args.output_len or cfg["output_len"],
+                       "concurrency": args.concurrency or cfg["concurrency"],
+                       "requests": args.requests or cfg["requests"], "window": "whole workload, wall clock around generate()"}}
+    try:
+        import library_vllm
+        c = line["config"]
+        r = library_vllm.run(c["model"], args.gpus, c["input_len"], c["output_len"], c["concurrency"], c["requests"],
+                             args.chunk or cfg["chunk"], warmup_requests=min(64, c["concurrency"]),
+                             expert_parallel=cfg["parallelism"] == "ep", attention_backend=args.library_attention)
+        line.update(value=round(r["value"], 1), seconds=round(r["seconds"], 2), library=r["library"],
+                    attention_backend=r["attention_backend"], init_seconds=round(r["init_seconds"], 1))
+    except BaseException as e:  # noqa: BLE001 - the arm reports why it could not run
+        line["unavailable"] = f"{type(e).__name__}: {str(e)[:300]}"
+    print(json.dumps(line), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=0, help="steady-state engine steps to time; 0 = the whole workload")
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="xllm_b200", choices=["xllm_b200", "ours", "reference"])
+    ap.add_argument("--impl", default="xllm_b200", choices=["xllm_b200", "ours", "reference", "library"])
+    ap.add_argument("--library-attention", default="", help="library arm: attention backend name handed to vLLM")
     ap.add_argument("--config", default="2", choices=sorted(CONFIGS), help="BASELINE.json config number")
     ap.add_argument("--model", default="")
     ap.add_argument("--requests", type=int, default=0)
@@ -464,6 +497,8 @@ def main():
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REF_UNAVAILABLE}), flush=True)
         return 0
+    if args.impl == "library":
+        return run_library(args)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus > 1 and world == 1:
         # convenience: re-launch under torchrun when started as a plain script

@@ -90,6 +90,28 @@ def test_paged_decode_attention(nq, nkv, d, page, splits):
     _close(y, yr, 2e-2)
 
 
+@pytest.mark.parametrize("d,page,splits,window", [(128, 16, 1, 48), (128, 16, 4, 200), (64, 32, 2, 33), (128, 64, 3, 1)])
+def test_paged_decode_attention_sliding_window(d, page, splits, window):
+    """Only the last `window` positions count; pages entirely before the window are never read
+    (their table entries point at a block full of NaN)."""
+    lens = [1, 17, 200, 555, 64, 1023]
+    nq, nkv = 8, 2
+    B = len(lens)
+    kc, vc, bt = _paged_setup(B, nq, nkv, d, page, lens, seed=9)
+    q = torch.randn(B, nq, d, device=DEV, dtype=torch.bfloat16)
+    sl = torch.tensor(lens, device=DEV, dtype=torch.int32)
+    scale = 1 / math.sqrt(d)
+    yr = ref.paged_decode_attention(q, kc, vc, bt, sl, scale, window)
+    kc[0] = float("nan")
+    vc[0] = float("nan")
+    for b, n in enumerate(lens):
+        dead = max(0, n - window) // page           # pages that end at or before the window start
+        bt[b, :dead] = 0
+    y = ops.paged_decode_attention(q, kc, vc, bt, sl, scale, splits=splits, window=window)
+    assert torch.isfinite(y.float()).all()
+    _close(y, yr, 2e-2)
+
+
 def test_paged_decode_padding_rows_are_zero():
     kc, vc, bt = _paged_setup(3, 8, 2, 128, 16, [40, 40, 40])
     q = torch.randn(3, 8, 128, device=DEV, dtype=torch.bfloat16)

@@ -22,7 +22,9 @@ P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 
 def _lib():
     from xllm_b200.ops import _lib as loader
-    lib = ctypes.CDLL(str(loader.lib_path())) if loader.lib_path().exists() else loader.load()
+    if not loader.lib_path().exists():
+        loader.load()                                  # builds the library in-tree
+    lib = ctypes.CDLL(str(loader.lib_path()))          # a plain handle: the entry point is C ABI, no Python layer
     lib.xllm_paged_decode_attn_noalloc.argtypes = [P, P, L, P, P, P, I, P, I, I, I, I, I, F, I, P]
     lib.xllm_paged_decode_attn_noalloc.restype = I
     lib.xllm_paged_decode_attn.argtypes = [P, P, L, P, P, P, I, P, I, I, I, I, I, F, I, P, P]

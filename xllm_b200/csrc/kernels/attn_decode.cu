@@ -32,6 +32,7 @@ struct DecodeParams {
   float* lse_part;             // [B, nq, splits]   (log2 domain)
   int64_t q_stride;            // elements between sequences in q
   int bt_stride, nq, nkv, group, page_size, splits;
+  int window;                  // 0 = attend to the whole sequence
   float scale_log2;
 };
 
@@ -50,9 +51,13 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(DecodeParams p) {
   pdl_wait();
   pdl_launch_dependents();  // dependents may be scheduled now; they block in their own pdl_wait()
   const int seq_len = p.seq_lens[b];
+  // sliding window: only the last `window` positions take part; tiles before them are never
+  // touched (their cache blocks may have been given back already)
+  const int win_start = p.window > 0 ? max(0, seq_len - p.window) : 0;
+  const int tile_first = win_start >> 4;
   const int tiles_total = (seq_len + 15) >> 4;
-  const int tps = (tiles_total + p.splits - 1) / p.splits;
-  const int t_begin = split * tps;
+  const int tps = (tiles_total - tile_first + p.splits - 1) / p.splits;
+  const int t_begin = tile_first + split * tps;
   const int t_end = min(t_begin + tps, tiles_total);
   const int my_n = (t_end - t_begin - warp + 3) >> 2;  // tiles of this warp (may be <= 0)
   const int rows_valid = min(16, p.group - qt * 16);
@@ -91,7 +96,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(DecodeParams p) {
       for (int j = 0; j < (16 * CH) / 32; ++j) {
         const int id = lane + j * 32;
         const int r = id / CH, c = id - r * CH;
-        const bool valid = tok0 + r < seq_len;
+        const bool valid = tok0 + r < seq_len && tok0 + r >= win_start;
         const int64_t go = valid ? (int64_t)r * D + c * 8 : 0;
         cp_async16(ks + swz<CH>(r, c), kb + go, valid);
         cp_async16(vs + swz<CH>(r, c), vb + go, valid);
@@ -136,7 +141,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(DecodeParams p) {
       for (int j = 0; j < 4; ++j) {
         const int tok = tok0 + nt * 8 + (lane & 3) * 2 + (j & 1);
         float v = s[nt][j] * p.scale_log2;
-        if (tok >= seq_len) v = -INFINITY;
+        if (tok >= seq_len || tok < win_start) v = -INFINITY;
         s[nt][j] = v;
         if (j < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
       }
@@ -279,20 +284,20 @@ XLLM_API int64_t xllm_decode_attn_workspace_bytes(int batch, int nq, int d, int 
 
 // q:[B,nq,D] (q_stride elements between sequences), caches [n_blocks, nkv, page, D], out:[B,nq,D] dense.
 // workspace: fp32 scratch of xllm_decode_attn_workspace_bytes() bytes when splits > 1 (else may be null).
-XLLM_API int xllm_paged_decode_attn(void* out, const void* q, int64_t q_stride, const void* k_cache,
-                                    const void* v_cache, const void* block_table, int bt_stride,
-                                    const void* seq_lens, int batch, int nq, int nkv, int d,
-                                    int page_size, float scale, int splits, void* workspace,
-                                    void* stream) {
+static int decode_attn_impl(void* out, const void* q, int64_t q_stride, const void* k_cache,
+                            const void* v_cache, const void* block_table, int bt_stride,
+                            const void* seq_lens, int batch, int nq, int nkv, int d,
+                            int page_size, float scale, int splits, void* workspace, int window,
+                            void* stream) {
   using namespace xllm;
   if (batch == 0) return 0;
-  if (nq % nkv != 0 || page_size % 16 != 0 || splits < 1) return (int)cudaErrorInvalidValue;
+  if (nq % nkv != 0 || page_size % 16 != 0 || splits < 1 || window < 0) return (int)cudaErrorInvalidValue;
   if (splits > 1 && workspace == nullptr) return (int)cudaErrorInvalidValue;
   DecodeParams p;
   p.q = (const bf16*)q; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
   p.block_table = (const int32_t*)block_table; p.seq_lens = (const int32_t*)seq_lens;
   p.out = (bf16*)out; p.q_stride = q_stride; p.bt_stride = bt_stride; p.nq = nq; p.nkv = nkv;
-  p.group = nq / nkv; p.page_size = page_size; p.splits = splits;
+  p.group = nq / nkv; p.page_size = page_size; p.splits = splits; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.o_part = (float*)workspace;
   p.lse_part = p.o_part ? p.o_part + (int64_t)batch * nq * splits * d : nullptr;
@@ -305,6 +310,26 @@ XLLM_API int xllm_paged_decode_attn(void* out, const void* q, int64_t q_stride, 
   if (rc != 0 || splits == 1) return rc;
   launch_pdl(attn_merge_kernel, dim3(batch * nq), dim3(d < 128 ? d : 128), 0, s, p.out, p.o_part, p.lse_part, splits, d);
   return XLLM_LAUNCH_CHECK();
+}
+
+XLLM_API int xllm_paged_decode_attn(void* out, const void* q, int64_t q_stride, const void* k_cache,
+                                    const void* v_cache, const void* block_table, int bt_stride,
+                                    const void* seq_lens, int batch, int nq, int nkv, int d,
+                                    int page_size, float scale, int splits, void* workspace,
+                                    void* stream) {
+  return decode_attn_impl(out, q, q_stride, k_cache, v_cache, block_table, bt_stride, seq_lens, batch, nq, nkv, d,
+                          page_size, scale, splits, workspace, 0, stream);
+}
+
+// The same with a sliding window: every query attends to its last `window` positions only, and the
+// block-table entries of pages entirely before the window are never read.
+XLLM_API int xllm_paged_decode_attn_window(void* out, const void* q, int64_t q_stride, const void* k_cache,
+                                           const void* v_cache, const void* block_table, int bt_stride,
+                                           const void* seq_lens, int batch, int nq, int nkv, int d,
+                                           int page_size, float scale, int splits, void* workspace,
+                                           int window, void* stream) {
+  return decode_attn_impl(out, q, q_stride, k_cache, v_cache, block_table, bt_stride, seq_lens, batch, nq, nkv, d,
+                          page_size, scale, splits, workspace, window, stream);
 }
 
 // Standalone merge of `splits` normalised partials (also used by context-parallel decode).
@@ -382,7 +407,7 @@ XLLM_API int xllm_paged_decode_attn_noalloc(void* out, const void* q, int64_t q_
   p.q = (const bf16*)q; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
   p.block_table = (const int32_t*)block_table; p.seq_lens = (const int32_t*)seq_lens;
   p.out = (bf16*)out; p.q_stride = q_stride; p.bt_stride = bt_stride; p.nq = nq; p.nkv = nkv;
-  p.group = nq / nkv; p.page_size = page_size; p.splits = splits;
+  p.group = nq / nkv; p.page_size = page_size; p.splits = splits; p.window = 0;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.o_part = splits > 1 ? scratch : nullptr;
   p.lse_part = p.o_part ? p.o_part + (int64_t)batch * nq * splits * d : nullptr;

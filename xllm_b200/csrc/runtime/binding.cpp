@@ -145,7 +145,9 @@ PYBIND11_MODULE(_rt, m) {
       .def_readwrite("max_running_seqs", &SchedulerConfig::max_running_seqs)
       .def_readwrite("min_prefill_tokens", &SchedulerConfig::min_prefill_tokens)
       .def_readwrite("max_prefill_wait_steps", &SchedulerConfig::max_prefill_wait_steps)
-      .def_readwrite("hold_finished_blocks", &SchedulerConfig::hold_finished_blocks);
+      .def_readwrite("hold_finished_blocks", &SchedulerConfig::hold_finished_blocks)
+      .def_readwrite("admission", &SchedulerConfig::admission)
+      .def_readwrite("sliding_window", &SchedulerConfig::sliding_window);
 
   py::enum_<PauseMode>(m, "PauseMode")
       .value("KEEP", PauseMode::KEEP)
@@ -428,6 +430,8 @@ PYBIND11_MODULE(_rt, m) {
       .def_property_readonly("num_prefilling", &Scheduler::num_prefilling)
       .def_property_readonly("num_requests", &Scheduler::num_requests)
       .def_property_readonly("num_preemptions", &Scheduler::num_preemptions)
+      .def_property_readonly("num_window_released_blocks", &Scheduler::num_window_released_blocks)
+      .def_property_readonly("num_admission_refusals", &Scheduler::num_admission_refusals)
       .def("block_manager", [](Scheduler& s, int dp) -> BlockManager& { return s.block_manager(dp); },
            py::arg("dp") = 0, py::return_value_policy::reference_internal)
       .def("block_stats", [](Scheduler& s, int dp) { return s.block_manager(dp).stats(); }, py::arg("dp") = 0)

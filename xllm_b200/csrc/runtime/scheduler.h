@@ -43,6 +43,18 @@ struct SchedulerConfig {
   int32_t block_size = 128;
   int32_t num_blocks = 0;  // per DP rank
   std::string policy = "prefill_first";
+  // Admission rule on top of the batching policy:
+  //   ""              admit while blocks last; a running sequence that cannot grow preempts others
+  //   "zero_eviction" admit a request only when a simulation of every running sequence up to its
+  //                   max_tokens shows that the pool never runs short, so nothing is ever preempted
+  //                   (xllm/core/scheduler/zero_eviction_scheduler.cpp:200-237)
+  //   "fixed_steps"   waves: requests are admitted only when nothing is running, then the whole wave
+  //                   runs its (short, fixed) number of steps to the end; generative recommendation
+  //                   (xllm/core/scheduler/fixed_steps_scheduler.h:49)
+  std::string admission = "";
+  // Sliding-window attention in every layer: KV blocks that lie entirely before the window of the
+  // next query are given back while the sequence runs (0 = full attention)
+  int32_t sliding_window = 0;
   std::string priority_strategy = "fcfs";
   double prefill_scheduling_memory_usage_threshold = 0.95;
   bool enable_schedule_overlap = false;
@@ -469,10 +481,14 @@ class Scheduler {
   }
   int64_t num_requests() const { return (int64_t)requests_.size(); }
   int64_t num_preemptions() const { return preemptions_; }
+  int64_t num_window_released_blocks() const { return window_released_blocks_; }
+  int64_t num_admission_refusals() const { return admission_refusals_; }
 
  private:
   std::unordered_map<std::string, std::vector<int32_t>> held_;
-  std::unordered_map<std::string, std::vector<int32_t>> reserved_;  // decode side of PD: blocks awaiting a prefill
+  std::unordered_map<std::string, std::vector<int32_t>> reserved_;
+  int64_t window_released_blocks_ = 0;
+  int64_t admission_refusals_ = 0;  // decode side of PD: blocks awaiting a prefill
   struct InFlight {
     std::vector<Sequence*> seqs;
     std::vector<int32_t> q_lens, sample_seq;
@@ -529,13 +545,64 @@ class Scheduler {
 
   void publish_blocks(Sequence* s) {
     BlockManager& bm = *bm_[s->dp_rank];
-    if (!bm.prefix_cache_enabled()) return;
-    const int32_t full = std::min<int32_t>(s->kv_computed, s->num_tokens()) / cfg_.block_size;
-    if (full > s->cached_blocks) {
-      bm.cache_blocks(s->tokens.data(), (int64_t)full * cfg_.block_size, s->blocks, s->cached_blocks,
-                      s->extra_hash_key);
-      s->cached_blocks = full;
+    if (bm.prefix_cache_enabled()) {
+      const int32_t full = std::min<int32_t>(s->kv_computed, s->num_tokens()) / cfg_.block_size;
+      if (full > s->cached_blocks) {
+        bm.cache_blocks(s->tokens.data(), (int64_t)full * cfg_.block_size, s->blocks, s->cached_blocks,
+                        s->extra_hash_key);
+        s->cached_blocks = full;
+      }
     }
+    release_out_of_window(s);
+  }
+
+  // Sliding window: the next query (position >= kv_computed) attends to positions > its own minus
+  // the window, so blocks that end at or before kv_computed - window are dead.  Their table entries
+  // become the padding block (0), which the windowed attention kernels never read.
+  void release_out_of_window(Sequence* s) {
+    if (cfg_.sliding_window <= 0 || s->in_flight > 0) return;
+    const int32_t dead = (s->kv_computed - cfg_.sliding_window + 1) / cfg_.block_size;
+    if (dead <= s->window_released) return;
+    std::vector<int32_t> give;
+    for (int32_t i = s->window_released; i < dead && i < (int32_t)s->blocks.size(); ++i) {
+      if (s->blocks[i] > 0) give.push_back(s->blocks[i]);
+      s->blocks[i] = 0;
+    }
+    s->window_released = dead;
+    window_released_blocks_ += (int64_t)give.size();
+    bm_[s->dp_rank]->free_blocks(give);
+  }
+
+  // zero_eviction / fixed_steps: would the pool of rank `dp` hold every running sequence plus
+  // `cand` all the way to their stopping lengths?  Sequences are sorted by remaining steps; the
+  // demand peaks right before one of them finishes, so only those moments are checked.
+  bool fits_without_eviction(const Sequence* cand, int dp) const {
+    struct Item { int64_t len, remaining; };
+    std::vector<Item> items;
+    int64_t held = 0;
+    auto add = [&](const Sequence* q) {
+      const int64_t len = q->num_tokens();
+      int64_t rem = (int64_t)q->request->stopping.max_tokens - q->num_generated();
+      if (q->request->stopping.max_context_len > 0)
+        rem = std::min<int64_t>(rem, (int64_t)q->request->stopping.max_context_len - len);
+      items.push_back({len, std::max<int64_t>(rem, 0)});
+    };
+    for (const Sequence* q : running_) {
+      if (q->dp_rank != dp || q->finished()) continue;
+      add(q);
+      for (int32_t b : q->blocks) held += b > 0;
+    }
+    add(cand);
+    std::sort(items.begin(), items.end(), [](const Item& a, const Item& b) { return a.remaining < b.remaining; });
+    const int64_t bs = cfg_.block_size, extra = 1 + cfg_.num_speculative_tokens;
+    const int64_t capacity = bm_[dp]->num_free_blocks() + held;
+    for (size_t k = 0; k < items.size(); ++k) {
+      const int64_t t = items[k].remaining;
+      int64_t demand = 0;
+      for (size_t i = k; i < items.size(); ++i) demand += (items[i].len + t + extra + bs - 1) / bs;
+      if (demand > capacity) return false;
+    }
+    return true;
   }
 
   void release_blocks(Sequence* s) {
@@ -550,6 +617,7 @@ class Scheduler {
     bm_[s->dp_rank]->free_blocks(s->blocks);
     s->blocks.clear();
     s->cached_blocks = 0;
+    s->window_released = 0;
   }
 
   void finish_seq(Sequence* s, FinishReason fr) {
@@ -717,6 +785,19 @@ class Scheduler {
       while (!waiting_.empty() && tok_budget > 0 && seq_budget > 0) {
         if (cfg_.max_running_seqs > 0 && (int32_t)running_.size() >= cfg_.max_running_seqs) break;
         Sequence* s = waiting_.front();
+        if (cfg_.admission == "fixed_steps" && !run.empty()) break;   // a wave is running: the next one waits
+        if (!cfg_.admission.empty() && !fits_without_eviction(s, dp)) {
+          if (running_.empty() && in_flight_batches_.empty()) {
+            // alone it still does not fit up to its stopping length: it never will
+            waiting_.pop_front();
+            finish_seq(s, FinishReason::LENGTH);
+            pending_events_.push_back(make_event(s, -1, 0.f, false));
+            pending_events_.back().request_finished = s->request->all_finished();
+            continue;
+          }
+          ++admission_refusals_;
+          break;
+        }
         const int target_dp = cfg_.dp_size == 1 ? 0 : pick_dp_rank();
         if (target_dp != dp) break;  // this request goes to another rank's batch
         if (!cfg_.enable_chunked_prefill && s->num_tokens() > tok_budget &&

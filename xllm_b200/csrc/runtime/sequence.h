@@ -74,6 +74,7 @@ struct Sequence {
   std::vector<float> logprobs;   // per generated token (when requested)
   double first_token_time = 0, last_token_time = 0, finish_time = 0;
   int32_t preempt_count = 0;
+  int32_t window_released = 0;   // leading blocks given back because they fell out of the sliding window
   int32_t in_flight = 0;         // batches containing this sequence that the device has not returned yet
   int32_t pending_samples = 0;   // of those, how many will append a token
   uint64_t extra_hash_key = 0;   // e.g. multimodal / LoRA discriminator for the prefix cache

@@ -21,6 +21,7 @@ import ctypes
 
 _lib.register_signature("xllm_kv_push", [P, P, P, I, L, L, L, I, I, I, P, ctypes.c_uint32, P, P])
 _lib.register_signature("xllm_kv_wait", [P, ctypes.c_uint32, P, ctypes.c_longlong, P])
+_lib.register_signature("xllm_kv_wait_many", [P, I, ctypes.c_uint32, P, ctypes.c_longlong, P])
 
 
 def plan_head_slices(src_tp: int, src_rank: int, dst_tp: int, n_kv_heads: int) -> List[Tuple[int, int, int, int]]:

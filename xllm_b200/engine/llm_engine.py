@@ -66,6 +66,7 @@ class EngineConfig:
     min_prefill_tokens: int = 0         # mixing policies: hold prompt chunks back until this many prompt tokens are pending
     max_prefill_wait_steps: int = 8     # ... or this many steps have passed
     max_running_seqs: int = 0           # cap on sequences holding KV / state at once; 0: no cap (state models: max_seqs_per_batch + 1)
+    scheduler_type: str = "continuous"  # "continuous" | "zero_eviction" (never preempts: admits by simulation) | "fixed_steps" (waves)
 
 
 _U64 = (1 << 64) - 1
@@ -188,6 +189,12 @@ class LLMEngine:
         sc.block_size = cfg.block_size
         sc.num_blocks = num_blocks
         sc.policy = cfg.policy
+        if cfg.scheduler_type not in ("continuous", "zero_eviction", "fixed_steps"):
+            raise ValueError(f"unknown scheduler_type {cfg.scheduler_type!r}")
+        sc.admission = "" if cfg.scheduler_type == "continuous" else cfg.scheduler_type
+        # sliding-window models (the window in every layer) give dead blocks back while they run
+        if int(getattr(self.args, "sliding_window", 0) or 0) > 0 and not getattr(self.model, "mixed_window_layers", False):
+            sc.sliding_window = int(self.args.sliding_window)
         sc.priority_strategy = cfg.priority_strategy
         sc.enable_schedule_overlap = cfg.enable_schedule_overlap
         sc.dp_size = 1  # one scheduler instance per DP replica

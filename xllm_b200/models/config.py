@@ -132,7 +132,11 @@ def model_args_from_dict(cfg: Dict[str, Any]) -> ModelArgs:
         a.partial_rotary_factor = float(text["rotary_dim"]) / a.head_dim
     a.max_position_embeddings = _g(text, "max_position_embeddings", default=32768)
     a.tie_word_embeddings = bool(_g(cfg, "tie_word_embeddings", default=_g(text, "tie_word_embeddings", default=False)))
-    a.sliding_window = int(_g(text, "sliding_window", default=0) or 0) if _g(text, "use_sliding_window", default=False) else 0
+    # Qwen-style configs carry a window plus a switch; Mistral-style configs carry only the window
+    use_window = _g(text, "use_sliding_window", default=None)
+    if use_window is None:
+        use_window = mt in ("mistral", "mixtral")
+    a.sliding_window = int(_g(text, "sliding_window", default=0) or 0) if use_window else 0
     a.bos_token_id = _g(text, "bos_token_id", default=-1)
     a.eos_token_id, a.stop_token_ids = _eos_list(_g(text, "eos_token_id", default=_g(cfg, "eos_token_id")))
     a.dtype = _g(text, "torch_dtype", "dtype", default=_g(cfg, "torch_dtype", "dtype", default="bfloat16"))

@@ -492,7 +492,7 @@ class Attention(Module):
         if nd > 0:
             ops.paged_decode_attention(q[:nd], k_cache, v_cache, meta.block_table[:nd], meta.kv_lens[:nd],
                                        self.scale, splits=meta.decode_splits,
-                                       workspace=meta.decode_workspace, out=out[:nd])
+                                       workspace=meta.decode_workspace, out=out[:nd], window=self.window)
         if meta.n_prefill > 0:
             # cu_q holds absolute token rows, so the full q / out tensors are passed
             ops.paged_prefill_attention(q, k_cache, v_cache, meta.block_table[nd:], meta.cu_q[nd:],

@@ -132,10 +132,12 @@ def decode_workspace(batch, nq, d, splits, device):
 
 
 def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, scale, splits=None,
-                           workspace=None, out=None):
-    """q: [B, nq, d] (one query token per sequence) -> [B, nq, d]."""
+                           workspace=None, out=None, window=0):
+    """q: [B, nq, d] (one query token per sequence) -> [B, nq, d].  `window` > 0: every query sees
+    its last `window` positions only (pages before them are not read)."""
+    window = int(window or 0)
     if not q.is_cuda:
-        y = reference.paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, scale)
+        y = reference.paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, scale, window)
         if out is not None:
             out.copy_(y)
             return out
@@ -150,10 +152,16 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, scale, sp
     if out is None:
         out = torch.empty((B, nq, d), dtype=q.dtype, device=q.device)
     assert q.stride(-1) == 1 and q.stride(1) == d
-    check(_lib_().xllm_paged_decode_attn(ptr(out), ptr(q), q.stride(0), ptr(k_cache), ptr(v_cache),
-                                         ptr(block_table), block_table.stride(0), ptr(seq_lens), B,
-                                         nq, nkv, d, page, scale, splits, ptr(workspace), stream()),
-          "paged_decode_attn")
+    if window > 0:
+        check(_lib_().xllm_paged_decode_attn_window(ptr(out), ptr(q), q.stride(0), ptr(k_cache), ptr(v_cache),
+                                                    ptr(block_table), block_table.stride(0), ptr(seq_lens), B,
+                                                    nq, nkv, d, page, scale, splits, ptr(workspace), window, stream()),
+              "paged_decode_attn_window")
+    else:
+        check(_lib_().xllm_paged_decode_attn(ptr(out), ptr(q), q.stride(0), ptr(k_cache), ptr(v_cache),
+                                             ptr(block_table), block_table.stride(0), ptr(seq_lens), B,
+                                             nq, nkv, d, page, scale, splits, ptr(workspace), stream()),
+              "paged_decode_attn")
     _count(2 if splits > 1 else 1)
     return out
 

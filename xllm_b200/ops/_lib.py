@@ -44,10 +44,36 @@ def load(build_if_missing: bool = True):
                 raise KernelLibraryMissing(f"cannot build {_LIB_PATH}: {e}") from e
     if not _LIB_PATH.exists():
         raise KernelLibraryMissing(f"{_LIB_PATH} not found; run `python -m xllm_b200._build`")
-    lib = ctypes.CDLL(str(_LIB_PATH))
+    lib = _CheckedLibrary(ctypes.CDLL(str(_LIB_PATH)))
     _declare(lib)
     _LIB = lib
     return lib
+
+
+class _CheckedLibrary:
+    """The kernel library behind a gate: an entry point can only be called after its argument types
+    were declared.  Without a declaration ctypes would pass Python integers as 32-bit C ints, i.e.
+    device pointers cut in half, and the kernel would write through them."""
+
+    def __init__(self, cdll):
+        object.__setattr__(self, "_cdll", cdll)
+        object.__setattr__(self, "_declared", set())
+
+    def declare(self, name, argtypes, restype):
+        fn = getattr(self._cdll, name, None)
+        if fn is None:
+            return False
+        fn.argtypes = argtypes
+        fn.restype = restype
+        self._declared.add(name)
+        return True
+
+    def __getattr__(self, name):
+        fn = getattr(self._cdll, name)          # AttributeError when the symbol does not exist
+        if name not in self._declared:
+            raise RuntimeError(f"{name}: argument types were never declared (ops/_lib.register_signature); "
+                               "refusing to call it with default integer conversion")
+        return fn
 
 
 P = ctypes.c_void_p
@@ -64,6 +90,7 @@ def _declare(lib):
         "xllm_act_and_mul": [P, P, L, I, L, I, P],
         "xllm_rope_kv": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P],
         "xllm_paged_decode_attn": [P, P, L, P, P, P, I, P, I, I, I, I, I, F, I, P, P],
+        "xllm_paged_decode_attn_window": [P, P, L, P, P, P, I, P, I, I, I, I, I, F, I, P, I, P],
         "xllm_attn_merge": [P, P, P, L, I, I, P],
         "xllm_paged_prefill_attn": [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P],
         "xllm_paged_prefill_attn_tc": [P, L, P, L, L, P, P, L, P, I, P, P, I, I, I, I, I, F, I, P],
@@ -80,14 +107,8 @@ def _declare(lib):
         "xllm_resolve_placeholders": [P, P, L, L, P],
     }
     for name, args in sig.items():
-        fn = getattr(lib, name, None)
-        if fn is None:
-            continue
-        fn.argtypes = args
-        fn.restype = I
-    if hasattr(lib, "xllm_decode_attn_workspace_bytes"):
-        lib.xllm_decode_attn_workspace_bytes.argtypes = [I, I, I, I]
-        lib.xllm_decode_attn_workspace_bytes.restype = L
+        lib.declare(name, args, I)
+    lib.declare("xllm_decode_attn_workspace_bytes", [I, I, I, I], L)
     _declare_optional(lib)
 
 
@@ -103,10 +124,7 @@ def register_signature(name, argtypes, restype=I):
 
 def _declare_optional(lib):
     for name, args, res in _OPTIONAL:
-        fn = getattr(lib, name, None)
-        if fn is not None:
-            fn.argtypes = args
-            fn.restype = res
+        lib.declare(name, args, res)
 
 
 def ptr(t):

@@ -180,11 +180,11 @@ def paged_attention(q, k_cache, v_cache, block_table, cu_q, kv_lens, scale, caus
     return out
 
 
-def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, scale):
+def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, scale, window=0):
     """q: [B, nq, d] one token per sequence."""
     B = q.shape[0]
     cu = torch.arange(B + 1, dtype=torch.int32, device=q.device)
-    return paged_attention(q, k_cache, v_cache, block_table, cu, seq_lens, scale, causal=True)
+    return paged_attention(q, k_cache, v_cache, block_table, cu, seq_lens, scale, causal=True, window=window)
 
 
 def apply_penalties(logits, ids, counts, freq, presence, repetition):
