@@ -195,3 +195,59 @@ def test_malformed_requests_close_their_connection_only(server):
     c.request("GET", "/health")
     assert c.getresponse().status == 200
     c.close()
+
+
+def test_native_response_pool_matches_python_formatting_under_concurrency(tmp_path):
+    """The same requests through the C++ response pool and through the Python formatter give the
+    same bodies; 24 streaming clients at once keep their chunks in order."""
+    tok = _tokenizer(tmp_path)
+    outs = {}
+    for name, threads in (("native", 3), ("python", 0)):
+        eng = LLMEngine(EngineConfig(model="tiny", device="cpu", dtype="float32", num_blocks=256, enable_graph=False,
+                                     max_seqs_per_batch=32, max_tokens_per_batch=256))
+        srv = ApiServer(eng, tok, model_name="tiny", host="127.0.0.1", port=0, response_threads=threads,
+                        request_threads=3 if threads else 0)
+        assert (srv.rp is not None) == (threads > 0)
+        t = threading.Thread(target=srv.serve_forever, args=(5,), daemon=True)
+        t.start()
+        res = [None] * 24
+
+        def client(i):
+            if i % 2:
+                body = {"messages": [{"role": "user", "content": f"hello world {i}"}], "max_tokens": 12, "temperature": 0,
+                        "ignore_eos": True, "stream": i % 4 == 1, "stop": ["zzzz"]}
+                res[i] = _post(srv.port, "/v1/chat/completions", body)
+            else:
+                body = {"prompt": [7 + i, 8, 9, 10 + i], "max_tokens": 12, "temperature": 0, "ignore_eos": True,
+                        "stream": i % 4 == 0, "stream_options": {"include_usage": True}}
+                res[i] = _post(srv.port, "/v1/completions", body)
+
+        ts = [threading.Thread(target=client, args=(i,)) for i in range(24)]
+        [x.start() for x in ts]
+        [x.join(timeout=120) for x in ts]
+        if threads:
+            assert srv.rp.drain(5000)
+            assert srv.rp.processed >= 24 * 12 and srv.rp.pending == 0
+            time.sleep(0.05)                      # one more loop turn collects the finished calls
+            assert not srv.calls
+        srv.shutdown()
+        t.join(timeout=5)
+        texts = []
+        for i, (st, data) in enumerate(res):
+            assert st == 200, data
+            if data.startswith("data: "):
+                ev = [json.loads(l[6:]) for l in data.split("\n") if l.startswith("data: ") and l != "data: [DONE]"]
+                assert data.rstrip().endswith("data: [DONE]")
+                if i % 2:
+                    texts.append("".join(e["choices"][0]["delta"].get("content", "") for e in ev if e["choices"]))
+                    assert ev[0]["choices"][0]["delta"].get("role") == "assistant"
+                    assert ev[-1]["choices"][0]["finish_reason"] == "length"
+                else:
+                    texts.append("".join(e["choices"][0]["text"] for e in ev if e["choices"]))
+                    assert ev[-1]["usage"]["completion_tokens"] == 12
+            else:
+                obj = json.loads(data)
+                texts.append(obj["choices"][0]["message"]["content"] if i % 2 else obj["choices"][0]["text"])
+                assert obj["usage"]["completion_tokens"] == 12 and obj["choices"][0]["finish_reason"] == "length"
+        outs[name] = texts
+    assert outs["native"] == outs["python"]

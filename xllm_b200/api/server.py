@@ -8,15 +8,26 @@ Tool-call and reasoning parsing of chat responses uses the C++ stream parsers; r
 `max_concurrent_requests` rate limiting and client-disconnect aborts follow
 chat_service_impl.cpp:702-860 / continuous_scheduler.cpp:964-1018.
 
-Transport is the C++ epoll server (`_rt.HttpServer`); this module is one loop: take new HTTP
-requests, step the engine, turn output events into response chunks.
+Transport is the C++ epoll server (`_rt.HttpServer`).  Three stages run concurrently, as in the
+reference's master (request thread pool, llm_master.cpp:216-303) and response processor
+(async_response_processor.cpp:86-376):
+  * request pool (Python threads): JSON parsing, chat template, tokenisation (the C++ tokenizer
+    releases the interpreter lock) -> a queue of admitted-to-be requests,
+  * engine loop (this thread): drains that queue, steps the engine, hands ALL output events of a step
+    to the response stage in one call,
+  * response pool (C++ threads, `_rt.ResponseProcessor`): incremental detokenisation, stop strings,
+    SSE / JSON formatting and the socket hand-off, without the interpreter.  Calls that need more
+    than text (tool-call / reasoning parsers, logprobs, the Anthropic format) are formatted by the
+    engine loop in Python instead.
 """
 from __future__ import annotations
 
 import json
 import os
+import queue
 import time
 import uuid
+from concurrent.futures import ThreadPoolExecutor
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
@@ -49,16 +60,29 @@ class _Call:
     t_arrival: float = 0.0
     t_first: float = 0.0
     started: bool = False
+    native: int = 0                # handle in the C++ response processor (0: formatted in Python)
 
 
 class ApiServer:
     def __init__(self, engine: LLMEngine, tokenizer, model_name: str = "xllm_b200", host: str = "", port: int = 8010,
-                 max_concurrent_requests: int = 200, tool_call_parser: str = "", reasoning_parser: str = ""):
+                 max_concurrent_requests: int = 200, tool_call_parser: str = "", reasoning_parser: str = "",
+                 request_threads: int = 4, response_threads: int = 4):
         self.engine = engine
         self.tok = tokenizer
         self.model_name = model_name
         self.http = _rt.HttpServer()
         self.port = self.http.start(host, port)
+        # request stage: a pool of threads that parse, template and tokenise; results queue up for the engine loop
+        self.request_pool = ThreadPoolExecutor(max(1, request_threads), thread_name_prefix="xllm-req") \
+            if request_threads > 0 else None
+        self._ready: "queue.SimpleQueue" = queue.SimpleQueue()
+        self._preparing = 0
+        # response stage: native worker threads (needs the C++ tokenizer, or none at all)
+        self.rp = None
+        impl = getattr(tokenizer, "impl", None)
+        if response_threads > 0 and (tokenizer is None or isinstance(impl, _rt.BpeTokenizer)):
+            self.rp = _rt.ResponseProcessor(self.http, impl, response_threads)
+        self._native_by_rid: Dict[str, int] = {}
         self.max_concurrent = max_concurrent_requests
         self.tool_kind = tool_call_parser
         self.reason_kind = reasoning_parser
@@ -93,34 +117,99 @@ class ApiServer:
     def serve_forever(self, idle_poll_ms: int = 50):
         while not self._stop:
             self.run_once(idle_poll_ms)
+        if self.rp is not None:
+            self.rp.drain(2000)
+            self.rp.stop()
+        if self.request_pool is not None:
+            self.request_pool.shutdown(wait=False)
         self.http.stop()
 
+    GENERATION_PATHS = ("/v1/completions", "/v1/chat/completions", "/v1/messages")
+
+    def _prepare(self, req):
+        """Request stage (pool thread): everything up to the point where the engine is needed."""
+        try:
+            self._route(req, prepared=True)
+        except Exception as e:  # a malformed request must never take a thread down
+            self._error(req.id, 500, f"{type(e).__name__}: {e}", "internal_error")
+        finally:
+            self._ready.put(None)          # one marker per prepared request: wakes the accounting below
+
     def run_once(self, idle_poll_ms: int = 0):
-        busy = self.engine.has_unfinished()
+        busy = self.engine.has_unfinished() or self._preparing > 0
         for req in self.http.poll(0 if busy else idle_poll_ms):
             try:
-                self._route(req)
+                path = req.path.rstrip("/") or "/"
+                if self.request_pool is not None and req.method == "POST" and path in self.GENERATION_PATHS:
+                    self._preparing += 1
+                    self.request_pool.submit(self._prepare, req)
+                else:
+                    self._route(req)
             except Exception as e:  # a malformed request must never take the loop down
+                self._error(req.id, 500, f"{type(e).__name__}: {e}", "internal_error")
+        # requests the pool has finished preparing: the engine is only ever touched by this thread
+        while True:
+            try:
+                item = self._ready.get_nowait()
+            except queue.Empty:
+                break
+            if item is None:
+                self._preparing -= 1
+                continue
+            req, call, ids, sampling, stops = item
+            try:
+                self._admit(req, call, ids, sampling, stops)
+            except Exception as e:
                 self._error(req.id, 500, f"{type(e).__name__}: {e}", "internal_error")
         # client went away: abort its request (frees its KV blocks at once)
         for rid, call in list(self.calls.items()):
             if self.http.is_disconnected(call.http_id):
                 self.engine.abort(rid)
                 self.calls.pop(rid, None)
+                if call.native:
+                    self._native_by_rid.pop(rid, None)
+                    self.rp.push([call.native], [0], [-1], [4], [""])
         now = time.time()
         if now >= self._next_watch:            # expired bounded waits in kernels -> unhealthy
             self._next_watch = now + self.watch_interval_s
             self.watchdog.check()
         if self.engine.has_unfinished():
-            for ev in self.engine.step():
-                self._on_event(ev)
+            self._dispatch(self.engine.step())
+        if self.rp is not None:
+            for d in self.rp.take_done():
+                self.calls.pop(d.request_id, None)
+                self._native_by_rid.pop(d.request_id, None)
+                self.trace.event(d.request_id, "finished", generated=int(d.generated), ttft_ms=round(d.ttft_ms, 3),
+                                 e2e_ms=round(d.e2e_ms, 3))
         s = self.engine.scheduler
         _rt.metric_gauge_set("num_running_requests", float(s.num_running))
         _rt.metric_gauge_set("num_waiting_requests", float(s.num_waiting))
         _rt.metric_gauge_set("kv_cache_utilization", float(s.kv_utilization(0)))
 
+    def _dispatch(self, events):
+        """Output events of one step: those of natively formatted calls go to the response pool in
+        one call, the others are formatted here."""
+        if not self._native_by_rid:
+            for ev in events:
+                self._on_event(ev)
+            return
+        h, si, tk, fl, rs = [], [], [], [], []
+        for ev in events:
+            handle = self._native_by_rid.get(ev.request_id)
+            if handle is None:
+                self._on_event(ev)
+                continue
+            aborted = ev.finish_reason == "abort" and ev.finished
+            h.append(handle)
+            si.append(int(ev.seq_index))
+            tk.append(int(ev.token))
+            fl.append((1 if ev.finished else 0) | (2 if ev.request_finished else 0) | (4 if aborted else 0))
+            rs.append(ev.finish_reason if ev.finished else "")
+        if h:
+            self.rp.push(h, si, tk, fl, rs)
+
     # ------------------------------------------------------------------ routing
-    def _route(self, req):
+    def _route(self, req, prepared: bool = False):
         path, method = req.path.rstrip("/") or "/", req.method
         _rt.metric_counter_add("server_request_in_total")
         if path == "/health":
@@ -205,6 +294,15 @@ class ApiServer:
                     logprobs=bool(lp) if not isinstance(lp, int) else lp > 0,
                     stop_token_ids=body.get("stop_token_ids")), (stop or [])
 
+    def _submit(self, req, call: _Call, prompt_ids, sampling, stops):
+        """End of the request stage: straight into the engine when called by the engine loop, through
+        the ready queue when called by a pool thread."""
+        import threading
+        if self.request_pool is not None and threading.current_thread().name.startswith("xllm-req"):
+            self._ready.put((req, call, prompt_ids, sampling, stops))
+        else:
+            self._admit(req, call, prompt_ids, sampling, stops)
+
     def _admit(self, req, call: _Call, prompt_ids, sampling, stops):
         if self.max_concurrent and len(self.calls) >= self.max_concurrent:
             return self._error(req.id, 429, "too many concurrent requests", "rate_limit_error")
@@ -214,8 +312,10 @@ class ApiServer:
         call.prompt_tokens = len(prompt_ids)
         call.t_arrival = time.time()
         call.want_logprobs = sampling["logprobs"]
+        native = (self.rp is not None and call.kind in ("completion", "chat") and not call.want_logprobs
+                  and not (call.kind == "chat" and (self.reason_kind or self.tool_kind)))
         for _ in range(n):
-            call.decoders.append(self.tok.incremental_decoder(stops, True) if self.tok else None)
+            call.decoders.append(self.tok.incremental_decoder(stops, True) if self.tok and not native else None)
             call.texts.append("")
             call.token_ids.append([])
             call.finish.append(None)
@@ -228,6 +328,16 @@ class ApiServer:
         if not ok:
             return self._error(req.id, 400, "prompt is empty or longer than the model's context window")
         self.calls[call.request_id] = call
+        if native:
+            spec = _rt.RespCallSpec()
+            spec.http_id, spec.request_id, spec.model = call.http_id, call.request_id, call.model
+            spec.kind = 0 if call.kind == "completion" else 1
+            spec.stream, spec.include_usage, spec.n = call.stream, call.include_usage, n
+            spec.prompt_tokens, spec.created, spec.echo_text = call.prompt_tokens, call.created, call.echo_text
+            spec.stops = list(stops)
+            spec.t_arrival = time.monotonic()
+            call.native = self.rp.open(spec)
+            self._native_by_rid[call.request_id] = call.native
         _rt.metric_counter_add("server_request_total_ok", 0)
 
     def _completion(self, req, body):
@@ -246,7 +356,7 @@ class ApiServer:
         call = _Call(req.id, rid, "completion", bool(body.get("stream")), body.get("model") or self.model_name,
                      int(time.time()), n=int(body.get("n", 1)), echo_text=text if body.get("echo") else "",
                      include_usage=bool((body.get("stream_options") or {}).get("include_usage")))
-        self._admit(req, call, ids, sampling, stops)
+        self._submit(req, call, ids, sampling, stops)
 
     def _chat(self, req, body, kind):
         if self.tok is None:
@@ -266,7 +376,7 @@ class ApiServer:
         call = _Call(req.id, rid, kind, bool(body.get("stream")), body.get("model") or self.model_name,
                      int(time.time()), n=int(body.get("n", 1)),
                      include_usage=bool((body.get("stream_options") or {}).get("include_usage")))
-        self._admit(req, call, ids, sampling, stops)
+        self._submit(req, call, ids, sampling, stops)
 
     def _embeddings(self, req, body):
         inp = body.get("input", "")

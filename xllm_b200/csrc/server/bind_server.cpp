@@ -4,6 +4,7 @@
 
 #include "http_server.h"
 #include "metrics.h"
+#include "response_processor.h"
 
 namespace py = pybind11;
 using namespace xllm;
@@ -31,6 +32,66 @@ void bind_server(py::module_& m) {
       .def("is_disconnected", &HttpServer::is_disconnected)
       .def("num_connections", &HttpServer::num_connections)
       .def_property_readonly("port", &HttpServer::port);
+
+  py::class_<RespCallSpec>(m, "RespCallSpec")
+      .def(py::init<>())
+      .def_readwrite("http_id", &RespCallSpec::http_id)
+      .def_readwrite("request_id", &RespCallSpec::request_id)
+      .def_readwrite("model", &RespCallSpec::model)
+      .def_readwrite("kind", &RespCallSpec::kind)
+      .def_readwrite("stream", &RespCallSpec::stream)
+      .def_readwrite("include_usage", &RespCallSpec::include_usage)
+      .def_readwrite("return_token_ids", &RespCallSpec::return_token_ids)
+      .def_readwrite("n", &RespCallSpec::n)
+      .def_readwrite("prompt_tokens", &RespCallSpec::prompt_tokens)
+      .def_readwrite("created", &RespCallSpec::created)
+      .def_readwrite("echo_text", &RespCallSpec::echo_text)
+      .def_readwrite("stops", &RespCallSpec::stops)
+      .def_readwrite("skip_special", &RespCallSpec::skip_special)
+      .def_readwrite("t_arrival", &RespCallSpec::t_arrival);
+
+  py::class_<RespDone>(m, "RespDone")
+      .def_readonly("request_id", &RespDone::request_id)
+      .def_readonly("http_id", &RespDone::http_id)
+      .def_readonly("generated", &RespDone::generated)
+      .def_readonly("prompt_tokens", &RespDone::prompt_tokens)
+      .def_readonly("aborted", &RespDone::aborted)
+      .def_readonly("ttft_ms", &RespDone::ttft_ms)
+      .def_readonly("e2e_ms", &RespDone::e2e_ms);
+
+  py::class_<ResponseProcessor>(m, "ResponseProcessor")
+      .def(py::init([](HttpServer* http, py::object tok, int n_threads) {
+             std::shared_ptr<BpeTokenizer> t;
+             if (!tok.is_none()) t = tok.cast<std::shared_ptr<BpeTokenizer>>();
+             return new ResponseProcessor(http, std::move(t), n_threads);
+           }),
+           py::arg("http"), py::arg("tokenizer"), py::arg("n_threads") = 4, py::keep_alive<1, 2>())
+      .def("open", &ResponseProcessor::open)
+      // events of one engine step as parallel lists: handles, sequence indices, tokens, flags
+      // (bit 0 finished, bit 1 request_finished, bit 2 aborted), finish reasons
+      .def("push",
+           [](ResponseProcessor& rp, const std::vector<int64_t>& calls, const std::vector<int32_t>& seq,
+              const std::vector<int32_t>& tokens, const std::vector<int32_t>& flags,
+              const std::vector<std::string>& reasons) {
+             std::vector<RespEvent> ev(calls.size());
+             for (size_t i = 0; i < calls.size(); ++i) {
+               ev[i].call = calls[i];
+               ev[i].seq_index = seq[i];
+               ev[i].token = tokens[i];
+               ev[i].finished = flags[i] & 1;
+               ev[i].request_finished = flags[i] & 2;
+               ev[i].aborted = flags[i] & 4;
+               if (i < reasons.size()) ev[i].finish_reason = reasons[i];
+             }
+             py::gil_scoped_release rel;
+             rp.push(std::move(ev));
+           })
+      .def("take_done", &ResponseProcessor::take_done)
+      .def("drain", &ResponseProcessor::drain, py::arg("timeout_ms") = 5000, py::call_guard<py::gil_scoped_release>())
+      .def("stop", &ResponseProcessor::stop, py::call_guard<py::gil_scoped_release>())
+      .def_property_readonly("pending", &ResponseProcessor::pending)
+      .def_property_readonly("processed", &ResponseProcessor::processed)
+      .def_property_readonly("num_threads", &ResponseProcessor::num_threads);
 
   m.def("metric_counter_add", [](const std::string& n, double v) { Metrics::instance().counter_add(n, v); },
         py::arg("name"), py::arg("value") = 1.0);

@@ -107,7 +107,9 @@ class ModelRunner:
         self.bt_cols = (max_model_len + block_size - 1) // block_size
         self.kv_allocator = kv_allocator     # (n_bytes) -> uint8 tensor, e.g. a slice of peer-mapped memory
         self.kv_caches = self._alloc_kv()
-        cap = self._capacity(self.max_tokens, self.max_seqs, self.max_seqs, self.bt_cols)
+        # a padded mixed step has up to `prefill_graph_seqs` prompt-chunk sequences besides a full decode bucket
+        extra = max(1, int(prefill_graph_seqs))
+        cap = self._capacity(self.max_tokens + extra, self.max_seqs + extra, self.max_seqs + extra, self.bt_cols)
         self.staging = [_Staging(cap, self.device, self.cuda) for _ in range(n_staging)]
         for s in self.staging:
             s.ids_host = torch.empty(self.max_seqs, dtype=torch.int64, pin_memory=self.cuda)
