@@ -1,0 +1,263 @@
+// Selection kernels of beam search and generative recommendation.
+//
+//   log_softmax      : row-wise log-softmax of logits (bf16 / fp32 in, fp32 out)
+//   radix_topk       : the k largest entries of every row by radix selection, sorted, optionally as
+//                      log-probabilities (the row's log-normaliser is subtracted)
+//   beam_step        : one beam-search step for B requests x W beams: the W best of the W x k
+//                      candidates (cumulative score of the parent + candidate log-probability),
+//                      with their parents and tokens
+//
+// Parity: xllm/core/kernels/cuda/air_log_softmax_last_dim.cu:35-250 (log-softmax),
+// topk_last_dim.cuh:1556-1986 (radix top-k over the last dimension), rec_beam_search.cu:503-1063
+// (beam step of the recommendation models) and beam_search.cu.
+//
+// Radix selection works on a 56-bit composite key: [order-preserving image of the fp32 value : 32]
+// [0xFFFFFF - index : 24].  Keys are unique, so "the k largest" is a well-defined set and ties in
+// the value go to the lowest index, like a stable sort; seven 8-bit passes find the k-th key, one
+// more pass gathers the k winners, a bitonic network in shared memory orders them.  Rows are
+// re-read from L2 (a 152k-entry bf16 row is 300 KB).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "common.cuh"
+
+namespace xllm {
+
+constexpr int kTopkThreads = 1024;
+constexpr int kTopkMax = 1024;
+
+template <typename T> __device__ __forceinline__ float beam_ld(const T* x, int64_t i);
+template <> __device__ __forceinline__ float beam_ld<float>(const float* x, int64_t i) { return x[i]; }
+template <> __device__ __forceinline__ float beam_ld<bf16>(const bf16* x, int64_t i) { return __bfloat162float(x[i]); }
+
+__device__ __forceinline__ uint32_t float_key(float f) {
+  if (f != f) f = -INFINITY;                       // NaN sorts last
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+__device__ __forceinline__ uint64_t make_key(float v, int i) {
+  return ((uint64_t)float_key(v) << 24) | (uint64_t)(0xFFFFFFu - (uint32_t)i);
+}
+
+__device__ __forceinline__ float topk_block_max(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  v = (threadIdx.x & 31) < (blockDim.x >> 5) ? red[threadIdx.x & 31] : -INFINITY;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  return v;
+}
+__device__ __forceinline__ float topk_block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  v = (threadIdx.x & 31) < (blockDim.x >> 5) ? red[threadIdx.x & 31] : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  return v;
+}
+
+// ------------------------------------------------------------------------------------------ log-softmax
+template <typename T>
+__global__ void __launch_bounds__(kTopkThreads) log_softmax_kernel(const T* __restrict__ x, int64_t row_stride, int V,
+                                                                   float* __restrict__ out) {
+  __shared__ float red[32];
+  const T* r = x + (int64_t)blockIdx.x * row_stride;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, beam_ld<T>(r, i));
+  mx = topk_block_max(mx, red);
+  float z = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) z += __expf(beam_ld<T>(r, i) - mx);
+  const float lse = mx + logf(topk_block_sum(z, red));
+  float* o = out + (int64_t)blockIdx.x * V;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) o[i] = beam_ld<T>(r, i) - lse;
+}
+
+// ------------------------------------------------------------------------------------------ selection core
+// Value of candidate i of this row; Loader::n() entries.
+template <typename T>
+struct RowLoader {
+  const T* x;
+  int V;
+  __device__ __forceinline__ int n() const { return V; }
+  __device__ __forceinline__ float operator()(int i) const { return beam_ld<T>(x, i); }
+};
+// W beams x k candidates: score = cum[w] + lp[w][j]; finished parents (cum = -inf) drop out by themselves
+struct BeamLoader {
+  const float* lp;    // [W * k]
+  const float* cum;   // [W]
+  int W, k;
+  __device__ __forceinline__ int n() const { return W * k; }
+  __device__ __forceinline__ float operator()(int i) const { return lp[i] + cum[i / k]; }
+};
+
+// Leaves the k largest keys of the row, sorted descending, in s_keys[0..k).  k <= kTopkMax, k <= n.
+template <typename Loader>
+__device__ void radix_select_sorted(const Loader& ld, int k, uint64_t* s_keys, uint32_t* s_hist, uint64_t* s_prefix,
+                                    int* s_int) {
+  const int n = ld.n();
+  uint64_t prefix = 0;
+  int remaining = k;
+  for (int pass = 6; pass >= 0; --pass) {
+    const int shift = pass * 8;
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) s_hist[i] = 0;
+    __syncthreads();
+    const uint64_t hi_mask = pass == 6 ? 0ull : (~0ull << (shift + 8));
+    for (int base = 0; base < n; base += blockDim.x) {
+      const int i = base + threadIdx.x;
+      int digit = -1;
+      if (i < n) {
+        const uint64_t key = make_key(ld(i), i);
+        if ((key & hi_mask) == prefix) digit = (int)((key >> shift) & 255u);
+      }
+      // one shared atomic per distinct digit of the warp
+      const unsigned peers = __match_any_sync(0xffffffffu, digit);
+      if (digit >= 0 && (int)(__ffs(peers) - 1) == (int)(threadIdx.x & 31)) atomicAdd(&s_hist[digit], (uint32_t)__popc(peers));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int acc = 0, d = 255;
+      for (; d > 0; --d) {
+        if (acc + (int)s_hist[d] >= remaining) break;
+        acc += (int)s_hist[d];
+      }
+      s_int[0] = remaining - acc;
+      *s_prefix = prefix | ((uint64_t)d << shift);
+    }
+    __syncthreads();
+    prefix = *s_prefix;
+    remaining = s_int[0];
+    __syncthreads();
+  }
+  // prefix is now the k-th largest key: gather everything >= it (exactly k keys)
+  int p2 = 1;
+  while (p2 < k) p2 <<= 1;
+  for (int i = threadIdx.x; i < p2; i += blockDim.x) s_keys[i] = 0ull;
+  if (threadIdx.x == 0) s_int[1] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const uint64_t key = make_key(ld(i), i);
+    if (key >= prefix) {
+      const int slot = atomicAdd(&s_int[1], 1);
+      if (slot < p2) s_keys[slot] = key;
+    }
+  }
+  __syncthreads();
+  // bitonic sort, descending
+  for (int size = 2; size <= p2; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = threadIdx.x; t < (p2 >> 1); t += blockDim.x) {
+        const int lo = 2 * t - (t & (stride - 1));
+        const int hi = lo + stride;
+        const bool desc = (lo & size) == 0;
+        const uint64_t a = s_keys[lo], b = s_keys[hi];
+        if ((a < b) == desc) { s_keys[lo] = b; s_keys[hi] = a; }
+      }
+      __syncthreads();
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kTopkThreads) radix_topk_kernel(const T* __restrict__ x, int64_t row_stride, int V, int k,
+                                                                  int normalize, float* __restrict__ out_vals,
+                                                                  int32_t* __restrict__ out_ids) {
+  __shared__ uint64_t s_keys[kTopkMax];
+  __shared__ uint32_t s_hist[256];
+  __shared__ uint64_t s_prefix;
+  __shared__ int s_int[2];
+  __shared__ float red[32];
+  const T* r = x + (int64_t)blockIdx.x * row_stride;
+  float lse = 0.f;
+  if (normalize) {
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, beam_ld<T>(r, i));
+    mx = topk_block_max(mx, red);
+    float z = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) z += __expf(beam_ld<T>(r, i) - mx);
+    lse = mx + logf(topk_block_sum(z, red));
+  }
+  RowLoader<T> ld{r, V};
+  radix_select_sorted(ld, k, s_keys, s_hist, &s_prefix, s_int);
+  for (int i = threadIdx.x; i < k; i += blockDim.x) {
+    const uint64_t key = s_keys[i];
+    out_ids[(int64_t)blockIdx.x * k + i] = (int32_t)(0xFFFFFFu - (uint32_t)(key & 0xFFFFFFu));
+    out_vals[(int64_t)blockIdx.x * k + i] = key_float((uint32_t)(key >> 24)) - lse;
+  }
+}
+
+// One CTA per request.  cand_lp / cand_ids: [B, W, k]; cum: [B, W]; outputs [B, W].
+__global__ void __launch_bounds__(kTopkThreads) beam_step_kernel(const float* __restrict__ cand_lp,
+                                                                 const int32_t* __restrict__ cand_ids,
+                                                                 const float* __restrict__ cum, int W, int k, int n_out,
+                                                                 int32_t* __restrict__ out_token,
+                                                                 int32_t* __restrict__ out_parent,
+                                                                 float* __restrict__ out_score) {
+  __shared__ uint64_t s_keys[kTopkMax];
+  __shared__ uint32_t s_hist[256];
+  __shared__ uint64_t s_prefix;
+  __shared__ int s_int[2];
+  const int b = blockIdx.x;
+  BeamLoader ld{cand_lp + (int64_t)b * W * k, cum + (int64_t)b * W, W, k};
+  radix_select_sorted(ld, n_out, s_keys, s_hist, &s_prefix, s_int);
+  for (int i = threadIdx.x; i < n_out; i += blockDim.x) {
+    const uint64_t key = s_keys[i];
+    const int idx = (int)(0xFFFFFFu - (uint32_t)(key & 0xFFFFFFu));
+    out_parent[(int64_t)b * n_out + i] = idx / k;
+    out_token[(int64_t)b * n_out + i] = cand_ids[(int64_t)b * W * k + idx];
+    out_score[(int64_t)b * n_out + i] = key_float((uint32_t)(key >> 24));
+  }
+}
+
+}  // namespace xllm
+
+// dtype: 0 bf16, 1 fp32.  out: fp32 [rows, V] dense.
+XLLM_API int xllm_log_softmax(const void* x, int64_t row_stride, int dtype, int rows, int V, void* out, void* stream) {
+  using namespace xllm;
+  if (rows == 0) return 0;
+  if (V <= 0) return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == 0) log_softmax_kernel<bf16><<<rows, kTopkThreads, 0, s>>>((const bf16*)x, row_stride, V, (float*)out);
+  else log_softmax_kernel<float><<<rows, kTopkThreads, 0, s>>>((const float*)x, row_stride, V, (float*)out);
+  return XLLM_LAUNCH_CHECK();
+}
+
+// The k largest entries of every row, sorted descending (ties: lowest index first).  normalize != 0:
+// values are log-probabilities of the row.  1 <= k <= min(V, 1024), V < 2^24.
+XLLM_API int xllm_radix_topk(const void* x, int64_t row_stride, int dtype, int rows, int V, int k, int normalize,
+                             void* out_vals, void* out_ids, void* stream) {
+  using namespace xllm;
+  if (rows == 0) return 0;
+  if (k < 1 || k > kTopkMax || k > V || V >= (1 << 24)) return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == 0)
+    radix_topk_kernel<bf16><<<rows, kTopkThreads, 0, s>>>((const bf16*)x, row_stride, V, k, normalize, (float*)out_vals,
+                                                           (int32_t*)out_ids);
+  else
+    radix_topk_kernel<float><<<rows, kTopkThreads, 0, s>>>((const float*)x, row_stride, V, k, normalize, (float*)out_vals,
+                                                            (int32_t*)out_ids);
+  return XLLM_LAUNCH_CHECK();
+}
+
+// The n_out best of W x k candidates per request.  n_out <= min(W * k, 1024).
+XLLM_API int xllm_beam_step(const void* cand_lp, const void* cand_ids, const void* cum, int B, int W, int k, int n_out,
+                            void* out_token, void* out_parent, void* out_score, void* stream) {
+  using namespace xllm;
+  if (B == 0) return 0;
+  if (W < 1 || k < 1 || n_out < 1 || n_out > kTopkMax || n_out > W * k || (int64_t)W * k >= (1 << 24))
+    return (int)cudaErrorInvalidValue;
+  beam_step_kernel<<<B, kTopkThreads, 0, (cudaStream_t)stream>>>((const float*)cand_lp, (const int32_t*)cand_ids,
+                                                                 (const float*)cum, W, k, n_out, (int32_t*)out_token,
+                                                                 (int32_t*)out_parent, (float*)out_score);
+  return XLLM_LAUNCH_CHECK();
+}

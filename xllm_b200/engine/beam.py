@@ -92,13 +92,19 @@ def beam_search(engine, prompt_token_ids, beam_width: int = 4, max_tokens: int =
         h = model.forward(torch.tensor(tokens, dtype=torch.int64, device=dev),
                           torch.tensor(positions, dtype=torch.int64, device=dev), meta, kv)
         last = torch.tensor([c - 1 for c in cu[1:]], dtype=torch.long, device=dev)
-        return torch.log_softmax(model.logits(h[last]).float(), dim=-1)
+        return model.logits(h[last])           # raw logits: the selection kernels normalise the rows they keep
 
     # ---- prompt once
     blocks = [pool.new() for _ in range((L + bs - 1) // bs)]
     slots = [blocks[p // bs] * bs + p % bs for p in range(L)]
-    logp = forward(prompt, list(range(L)), slots, [blocks], [L], [L])[0]
-    top = torch.topk(logp, min(2 * W, logp.numel()))
+    from ..ops import select
+    logits = forward(prompt, list(range(L)), slots, [blocks], [L], [L])[:1]
+    if logits.dtype not in (torch.bfloat16, torch.float32):
+        logits = logits.float()
+    V = logits.shape[1]
+    n_cand = min(2 * W, V)
+    tv, ti = select.topk(logits, n_cand, normalize=True)
+    top_vals, top_ids = tv[0].tolist(), ti[0].tolist()
     beams: List[Beam] = []
     done: List[BeamOutput] = []
 
@@ -126,8 +132,7 @@ def beam_search(engine, prompt_token_ids, beam_width: int = 4, max_tokens: int =
             tbl.append(pool.new())
         return tbl
 
-    for j in range(top.indices.numel()):
-        tok, sc = int(top.indices[j]), float(top.values[j])
+    for tok, sc in zip(top_ids, top_vals):
         if tok == eos and not ignore_eos:
             done.append(BeamOutput([tok], sc, norm(sc, 1), "stop"))
             continue
@@ -143,15 +148,16 @@ def beam_search(engine, prompt_token_ids, beam_width: int = 4, max_tokens: int =
         toks = [b.tokens[-1] for b in beams]
         pos = [n_ctx - 1] * len(beams)
         slots = [b.blocks[(n_ctx - 1) // bs] * bs + (n_ctx - 1) % bs for b in beams]
-        logp = forward(toks, pos, slots, [b.blocks for b in beams], [n_ctx] * len(beams), [1] * len(beams))
-        cand = torch.tensor([b.score for b in beams], device=logp.device)[:, None] + logp
-        top = torch.topk(cand.flatten(), min(2 * W, cand.numel()))
-        V = logp.shape[1]
+        logits = forward(toks, pos, slots, [b.blocks for b in beams], [n_ctx] * len(beams), [1] * len(beams))
+        if logits.dtype not in (torch.bfloat16, torch.float32):
+            logits = logits.float()
+        cum = torch.tensor([b.score for b in beams], dtype=torch.float32, device=logits.device)
+        # every beam's 2W best continuations, then the 2W best of all of them: one device->host read
+        t_tok, t_par, t_sc = select.beam_topk(logits, cum, min(2 * W, logits.numel()))
+        t_tok, t_par, t_sc = t_tok.tolist(), t_par.tolist(), t_sc.tolist()
         new: List[Beam] = []
         used_parent = set()
-        for j in range(top.indices.numel()):
-            idx, sc = int(top.indices[j]), float(top.values[j])
-            p, tok = idx // V, idx % V
+        for tok, p, sc in zip(t_tok, t_par, t_sc):
             seq = beams[p].tokens + [tok]
             if tok == eos and not ignore_eos:
                 done.append(BeamOutput(seq, sc, norm(sc, len(seq)), "stop"))
