@@ -266,6 +266,31 @@ def test_gdn_decode_step_matches_reference(B, nv, dk, dv):
     assert torch.equal(state[rest], before[rest])
 
 
+@pytest.mark.parametrize("n,nv,dk,dv,fresh", [(1, 4, 128, 128, True), (37, 8, 128, 128, False), (300, 4, 64, 96, True),
+                                               (64, 2, 256, 128, False), (129, 3, 32, 40, False)])
+def test_gdn_prefill_matches_the_token_by_token_recurrence(n, nv, dk, dv, fresh):
+    """A prompt chunk through the fused-recurrent kernel equals n single-token updates; only the
+    addressed slot changes; a fresh sequence ignores what the slot held."""
+    from xllm_b200.ops import gdn
+    g0 = torch.Generator(device="cuda").manual_seed(n)
+    state = torch.randn(5, nv, dk, dv, device="cuda", generator=g0) * 0.3
+    slot = 3
+    q = torch.randn(n, nv, dk, device="cuda", generator=g0) * 0.2
+    k = torch.nn.functional.normalize(torch.randn(n, nv, dk, device="cuda", generator=g0), dim=-1)
+    v = torch.randn(n, nv, dv, device="cuda", generator=g0)
+    g = -torch.rand(n, nv, device="cuda", generator=g0) * 0.5
+    beta = torch.rand(n, nv, device="cuda", generator=g0)
+    S0 = torch.zeros_like(state[slot]) if fresh else state[slot].clone()
+    want_S, want_o = gdn.prefill_reference(S0, q, k, v, g, beta)
+    before = state.clone()
+    out = gdn.prefill(state, slot, fresh, q, k, v, g, beta)
+    torch.cuda.synchronize()
+    assert torch.allclose(out, want_o, atol=1e-3, rtol=1e-3)
+    assert torch.allclose(state[slot], want_S, atol=1e-3, rtol=1e-3)
+    rest = [i for i in range(5) if i != slot]
+    assert torch.equal(state[rest], before[rest])
+
+
 def test_kernels_do_not_write_outside_their_outputs():
     """Canary rows before and after every output buffer: odd token counts (not multiples of any tile
     size) through norm, activation, gather, GEMM and the state kernel leave the guard rows untouched."""

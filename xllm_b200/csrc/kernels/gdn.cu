@@ -101,7 +101,100 @@ __global__ void __launch_bounds__(gdn_reg_max_threads(R)) gdn_decode_reg_kernel(
   if (gy == 0 && live) out[row * dv + j] = red[tx] + red[dvp + tx] + red[2 * dvp + tx] + red[3 * dvp + tx];
 }
 
+// Prompt chunks: the same recurrence over the n tokens of ONE sequence without leaving the kernel.
+// A CTA owns blockDim.x state columns of one head (four row groups, R rows of the column per thread,
+// as above) and walks the tokens in order; k_t and q_t of the next token are staged in shared memory
+// while the current one is reduced.  The state is read from HBM once (or starts at zero for a new
+// sequence) and written once; per token the CTA moves 2 dk + 1 inputs and one output per column.
+// The reference reaches this through FLA's chunked Triton kernels
+// (xllm/python/kernels_cuda/triton/gdn_prefill.py); this is the fused-recurrent form of the same rule.
+template <int R>
+__global__ void __launch_bounds__(gdn_reg_max_threads(R)) gdn_prefill_reg_kernel(
+    float* __restrict__ state, int64_t slot, int fresh, const float* __restrict__ q, const float* __restrict__ k,
+    const float* __restrict__ v, const float* __restrict__ g, const float* __restrict__ beta, float* __restrict__ out,
+    int n, int nv, int dv) {
+  constexpr int dk = 4 * R;
+  extern __shared__ float sm[];
+  float* kq = sm;                                   // [2 buffers][k: dk | q: dk]
+  float* red_a = sm + 4 * dk;                       // [4][blockDim.x]
+  float* red_b = red_a + 4 * blockDim.x;            // [4][blockDim.x]
+  const int h = blockIdx.x;
+  const int tx = threadIdx.x, gy = threadIdx.y, dvp = blockDim.x;
+  const int j = blockIdx.y * dvp + tx;
+  const bool live = j < dv;
+  const int tid = gy * dvp + tx, nthreads = 4 * dvp;
+  float* S = state + ((slot * nv + h) * (int64_t)dk + gy * R) * dv + j;
+  float s[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) s[r] = (live && !fresh) ? S[(int64_t)r * dv] : 0.f;
+  auto stage = [&](int t, int buf) {
+    const int64_t row = (int64_t)t * nv + h;
+    float* dst = kq + buf * 2 * dk;
+    for (int i = tid; i < 2 * dk; i += nthreads) dst[i] = i < dk ? k[row * dk + i] : q[row * dk + (i - dk)];
+  };
+  stage(0, 0);
+  __syncthreads();
+  for (int t = 0; t < n; ++t) {
+    const int buf = t & 1;
+    const float* ks = kq + buf * 2 * dk;
+    const float* qs = ks + dk;
+    const int64_t row = (int64_t)t * nv + h;
+    if (t + 1 < n) stage(t + 1, buf ^ 1);           // visible after the next barrier
+    const float decay = __expf(g[row]);
+    const float bt = beta[row];
+    float part = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r) part += s[r] * ks[gy * R + r];
+    red_a[gy * dvp + tx] = part;
+    __syncthreads();
+    const float kv = (red_a[tx] + red_a[dvp + tx] + red_a[2 * dvp + tx] + red_a[3 * dvp + tx]) * decay;
+    const float delta = ((live ? v[row * dv + j] : 0.f) - kv) * bt;
+    float o = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      s[r] = s[r] * decay + ks[gy * R + r] * delta;
+      o += s[r] * qs[gy * R + r];
+    }
+    red_b[gy * dvp + tx] = o;
+    __syncthreads();
+    if (gy == 0 && live) out[row * dv + j] = red_b[tx] + red_b[dvp + tx] + red_b[2 * dvp + tx] + red_b[3 * dvp + tx];
+  }
+  if (live) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) S[(int64_t)r * dv] = s[r];
+  }
+}
+
 }  // namespace xllm
+
+// Prompt chunk of one sequence: q, k [n, nv, dk]; v, out [n, nv, dv]; g, beta [n, nv] (fp32); the
+// state of slot `slot` is advanced over the n tokens (from zero when `fresh`).  dk in {32, 64, 128, 256}.
+XLLM_API int xllm_gdn_prefill(void* state, int64_t slot, int fresh, const void* q, const void* k, const void* v,
+                              const void* g, const void* beta, void* out, int n, int nv, int dk, int dv, void* stream) {
+  using namespace xllm;
+  if (n == 0) return 0;
+  if (!(dk == 32 || dk == 64 || dk == 128 || dk == 256) || dv <= 0) return (int)cudaErrorInvalidValue;
+  const int dvp = ((dv + 31) / 32) * 32;
+  const int cols = dk == 256 ? 32 : (dvp < 64 ? dvp : 64);
+  const dim3 grid(nv, (dv + cols - 1) / cols), block(cols, 4);
+  const size_t smem = (size_t)(4 * dk + 8 * cols) * sizeof(float);
+  cudaStream_t st = (cudaStream_t)stream;
+#define XLLM_GDN_PF_CASE(RR)                                                                                      \
+  case RR:                                                                                                        \
+    gdn_prefill_reg_kernel<RR><<<grid, block, smem, st>>>((float*)state, slot, fresh, (const float*)q,            \
+                                                          (const float*)k, (const float*)v, (const float*)g,      \
+                                                          (const float*)beta, (float*)out, n, nv, dv);            \
+    return XLLM_LAUNCH_CHECK();
+  switch (dk / 4) {
+    XLLM_GDN_PF_CASE(8)
+    XLLM_GDN_PF_CASE(16)
+    XLLM_GDN_PF_CASE(32)
+    XLLM_GDN_PF_CASE(64)
+    default: break;
+  }
+#undef XLLM_GDN_PF_CASE
+  return (int)cudaErrorInvalidValue;
+}
 
 // state [n_slots, nv, dk, dv] fp32; slots [B] int64; q, k [B, nv, dk]; v, out [B, nv, dv]; g, beta [B, nv] (all fp32).
 XLLM_API int xllm_gdn_decode_step(void* state, const void* slots, const void* q, const void* k, const void* v,

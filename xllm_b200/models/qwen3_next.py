@@ -143,12 +143,8 @@ class GatedDeltaNet(Module):
             y = F.silu((win.float() * self.conv_w.float()).sum(-1)).to(x.dtype)
             conv[s] = full[-(self.K - 1):].T
             qh, kh, vh = heads(y)
-            S = torch.zeros_like(rec[s]) if fresh[i] else rec[s].clone()
-            S = S[None]
-            for t in range(b0 - a0):
-                S, o = self._step(S, qh[t:t + 1], kh[t:t + 1], vh[t:t + 1], g[a0 + t:a0 + t + 1], beta[a0 + t:a0 + t + 1])
-                out[a0 + t] = o[0]
-            rec[s] = S[0]
+            # the whole chunk in one kernel on CUDA (the state stays in registers across the tokens)
+            gdn_ops.prefill(rec, s, bool(fresh[i]), qh, kh, vh, g[a0:b0], beta[a0:b0], out=out[a0:b0])
         # gated RMSNorm over each value head, then the output projection
         o = out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + self.eps)
         o = (self.norm_w * o.to(x.dtype)) * F.silu(z.float())
