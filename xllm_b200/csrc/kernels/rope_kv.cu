@@ -29,97 +29,124 @@ struct RopeKvParams {
   float eps;
 };
 
+// One CTA per token.  A thread owns the same 8-element slot of up to kRopeHeadsPerThread heads (the
+// heads of one token share the position, hence the cos / sin values, which are read once per thread);
+// all of a thread's 16-byte loads are issued before anything is computed, so that a CTA has its whole
+// token row (12 KB for 48 heads of 128) in flight at once.
+constexpr int kRopeHeadsPerThread = 4;
+
 __global__ void __launch_bounds__(256) rope_kv_kernel(RopeKvParams p) {
   const int tph = p.d >> 3;  // threads per head (each owns 8 contiguous elements)
-  const int heads_per_block = blockDim.x / tph;
+  const int heads_per_pass = blockDim.x / tph;
   const int total_heads = p.nq + 2 * p.nkv;
   const int local = threadIdx.x / tph;
   const int g = threadIdx.x - local * tph;
-  const int64_t gh = (int64_t)blockIdx.x * heads_per_block + local;
-  const bool active = gh < (int64_t)p.tokens * total_heads;
+  const int64_t t = blockIdx.x;
+  const int e0 = g * 8;
   pdl_wait();
   pdl_launch_dependents();  // dependents may be scheduled now; they block in their own pdl_wait()
-  const int64_t t = active ? gh / total_heads : 0;
-  const int h = active ? (int)(gh - t * total_heads) : 0;
-  const int e0 = g * 8;
 
-  float x[8];
-  if (active) {
-    const bf16x8* src = reinterpret_cast<const bf16x8*>(p.qkv + t * p.qkv_stride + (int64_t)h * p.d);
-    unpack8(src[g], x);
-  } else {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) x[j] = 0.f;
-  }
-  const bool is_q = h < p.nq;
-  const bool is_k = !is_q && h < p.nq + p.nkv;
-  const bf16* nw = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
-
-  // per-head RMSNorm (segmented reduce across the tph lanes of this head)
-  float ss = 0.f;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
-  for (int o = tph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  if (nw != nullptr) {
-    const float inv = rsqrtf(ss / (float)p.d + p.eps);
-    float w[8];
-    unpack8(reinterpret_cast<const bf16x8*>(nw)[g], w);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      // match the usual bf16 module: normalise, round to bf16, scale by the bf16 weight
-      x[j] = __bfloat162float(__float2bfloat16(x[j] * inv)) * w[j];
-    }
-  }
-
-  // RoPE on q and k
-  if (p.cos_sin != nullptr) {
-    const int half = p.rot >> 1;
-    const int64_t pos = active ? p.positions[t] : 0;
-    const float* cs = p.cos_sin + pos * p.rot;
+  // cos / sin of this thread's slot (shared by all its heads)
+  const int half = p.rot >> 1;
+  const bool rotates = p.cos_sin != nullptr && e0 < p.rot;
+  float c[8], sn[8];
+  if (rotates) {
+    const float* cs = p.cos_sin + p.positions[t] * p.rot;
     if (p.interleaved) {
-      if (active && !(!is_q && !is_k) && e0 < p.rot) {
-#pragma unroll
-        for (int j = 0; j < 8; j += 2) {
-          const int pi = (e0 + j) >> 1;
-          const float c = cs[pi], s = cs[half + pi];
-          const float a = x[j], b = x[j + 1];
-          x[j] = a * c - b * s;
-          x[j + 1] = b * c + a * s;
-        }
-      }
+      const int pi = e0 >> 1;
+      const float4 c4 = *reinterpret_cast<const float4*>(cs + pi);
+      const float4 s4 = *reinterpret_cast<const float4*>(cs + half + pi);
+      c[0] = c4.x; c[1] = c4.y; c[2] = c4.z; c[3] = c4.w;
+      sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
     } else {
-      const int half_lanes = half >> 3;
-      float other[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) other[j] = __shfl_xor_sync(0xffffffffu, x[j], half_lanes);
-      if (active && (is_q || is_k) && e0 < p.rot) {
-        const bool first = e0 < half;
-        const int ci = first ? e0 : e0 - half;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float c = cs[ci + j], s = cs[half + ci + j];
-          x[j] = first ? (x[j] * c - other[j] * s) : (x[j] * c + other[j] * s);
-        }
-      }
+      const int ci = e0 < half ? e0 : e0 - half;
+      const float4 ca = *reinterpret_cast<const float4*>(cs + ci), cb = *reinterpret_cast<const float4*>(cs + ci + 4);
+      const float4 sa = *reinterpret_cast<const float4*>(cs + half + ci), sb = *reinterpret_cast<const float4*>(cs + half + ci + 4);
+      c[0] = ca.x; c[1] = ca.y; c[2] = ca.z; c[3] = ca.w; c[4] = cb.x; c[5] = cb.y; c[6] = cb.z; c[7] = cb.w;
+      sn[0] = sa.x; sn[1] = sa.y; sn[2] = sa.z; sn[3] = sa.w; sn[4] = sb.x; sn[5] = sb.y; sn[6] = sb.z; sn[7] = sb.w;
     }
   }
-  if (!active) return;
-  const bf16x8 o = pack8(x);
-  if (is_q) {
-    reinterpret_cast<bf16x8*>(p.q_out + (t * p.nq + h) * (int64_t)p.d)[g] = o;
-    return;
-  }
-  const int kvh = is_k ? h - p.nq : h - p.nq - p.nkv;
-  bf16* dense = is_k ? p.k_out : p.v_out;
-  if (dense) reinterpret_cast<bf16x8*>(dense + (t * p.nkv + kvh) * (int64_t)p.d)[g] = o;
-  bf16* cache = is_k ? p.k_cache : p.v_cache;
-  if (cache && p.slots) {
-    const int slot = p.slots[t];
-    if (slot >= 0) {
-      const int64_t blk = slot / p.block_size;
-      const int off = slot - (int)blk * p.block_size;
-      bf16* dst = cache + (((blk * p.nkv + kvh) * p.block_size) + off) * (int64_t)p.d;
-      reinterpret_cast<bf16x8*>(dst)[g] = o;
+  const int slot = (p.slots != nullptr) ? p.slots[t] : -1;
+  const bf16* row = p.qkv + t * p.qkv_stride;
+
+  for (int h0 = 0; h0 < total_heads; h0 += heads_per_pass * kRopeHeadsPerThread) {
+    bf16x8 raw[kRopeHeadsPerThread];
+#pragma unroll
+    for (int u = 0; u < kRopeHeadsPerThread; ++u) {
+      const int h = h0 + u * heads_per_pass + local;
+      if (h < total_heads) raw[u] = reinterpret_cast<const bf16x8*>(row + (int64_t)h * p.d)[g];
+    }
+#pragma unroll
+    for (int u = 0; u < kRopeHeadsPerThread; ++u) {
+      const int h = h0 + u * heads_per_pass + local;
+      // whole heads are active or not together, so the shuffles below always see their partners
+      const bool active = h < total_heads;
+      float x[8];
+      if (active) {
+        unpack8(raw[u], x);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = 0.f;
+      }
+      const bool is_q = h < p.nq;
+      const bool is_k = !is_q && h < p.nq + p.nkv;
+      const bf16* nw = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
+      // per-head RMSNorm (segmented reduce across the tph lanes of this head)
+      if (p.q_norm_w != nullptr || p.k_norm_w != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
+        for (int o = tph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (active && nw != nullptr) {
+          const float inv = rsqrtf(ss / (float)p.d + p.eps);
+          float w[8];
+          unpack8(reinterpret_cast<const bf16x8*>(nw)[g], w);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            // match the usual bf16 module: normalise, round to bf16, scale by the bf16 weight
+            x[j] = __bfloat162float(__float2bfloat16(x[j] * inv)) * w[j];
+          }
+        }
+      }
+      // RoPE on q and k
+      if (p.cos_sin != nullptr) {
+        if (p.interleaved) {
+          if (active && (is_q || is_k) && rotates) {
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+              const float a = x[j], b = x[j + 1];
+              x[j] = a * c[j >> 1] - b * sn[j >> 1];
+              x[j + 1] = b * c[j >> 1] + a * sn[j >> 1];
+            }
+          }
+        } else {
+          const int half_lanes = half >> 3;
+          float other[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) other[j] = __shfl_xor_sync(0xffffffffu, x[j], half_lanes);
+          if (active && (is_q || is_k) && rotates) {
+            const bool first = e0 < half;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = first ? (x[j] * c[j] - other[j] * sn[j]) : (x[j] * c[j] + other[j] * sn[j]);
+          }
+        }
+      }
+      if (!active) continue;
+      const bf16x8 o = pack8(x);
+      if (is_q) {
+        reinterpret_cast<bf16x8*>(p.q_out + (t * p.nq + h) * (int64_t)p.d)[g] = o;
+        continue;
+      }
+      const int kvh = is_k ? h - p.nq : h - p.nq - p.nkv;
+      bf16* dense = is_k ? p.k_out : p.v_out;
+      if (dense) reinterpret_cast<bf16x8*>(dense + (t * p.nkv + kvh) * (int64_t)p.d)[g] = o;
+      bf16* cache = is_k ? p.k_cache : p.v_cache;
+      if (cache && slot >= 0) {
+        const int64_t blk = slot / p.block_size;
+        const int off = slot - (int)blk * p.block_size;
+        bf16* dst = cache + (((blk * p.nkv + kvh) * p.block_size) + off) * (int64_t)p.d;
+        reinterpret_cast<bf16x8*>(dst)[g] = o;
+      }
     }
   }
 }
@@ -146,9 +173,8 @@ XLLM_API int xllm_rope_kv(const void* qkv, int64_t qkv_stride, void* q_out, void
   p.cos_sin = (const float*)cos_sin; p.positions = (const int64_t*)positions;
   p.slots = (const int32_t*)slots; p.tokens = tokens; p.nq = nq; p.nkv = nkv; p.d = d; p.rot = rot;
   p.block_size = block_size; p.interleaved = interleaved; p.eps = eps;
-  const int heads_per_block = 256 / tph;
-  const int64_t total = (int64_t)tokens * (nq + 2 * nkv);
-  const int grid = (int)((total + heads_per_block - 1) / heads_per_block);
-  launch_pdl(rope_kv_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, p);
+  // float4 loads of the cos / sin rows: `rot` floats per position, 8-element slots
+  if (cos_sin && (rot % 8 != 0 || ((uintptr_t)cos_sin & 15))) return (int)cudaErrorInvalidValue;
+  launch_pdl(rope_kv_kernel, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, p);
   return XLLM_LAUNCH_CHECK();
 }
