@@ -94,10 +94,9 @@ def test_argmax_and_gather_world_of_one():
 
 
 def _short_budget(fn_name, cycles=600_000):
-    lib = _lib()
-    f = getattr(lib, fn_name)
-    f.argtypes = [ctypes.c_longlong]
-    f.restype = ctypes.c_longlong
+    import xllm_b200.parallel.ep  # noqa: F401 - declares the setters' signatures
+    import xllm_b200.parallel.symm  # noqa: F401
+    f = getattr(_lib(), fn_name)
     return f, f(cycles)
 
 

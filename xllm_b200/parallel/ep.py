@@ -28,6 +28,7 @@ _lib.register_signature("xllm_ep_counts_layout", _EP + [P, P, P, P, I, P])
 _lib.register_signature("xllm_ep_dispatch_sync", _EP + [P, P, P, P, P, I, I, P])
 _lib.register_signature("xllm_ep_combine_sync", _EP + [P, P, P, P, I, I, P])
 _lib.register_signature("xllm_act_and_mul_rows", [P, P, L, P, I, L, I, P])
+_lib.register_signature("xllm_ep_set_wait_budget", [ctypes.c_longlong], ctypes.c_longlong)
 
 
 class EpComm:
