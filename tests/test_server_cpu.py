@@ -251,3 +251,91 @@ def test_native_response_pool_matches_python_formatting_under_concurrency(tmp_pa
                 assert obj["usage"]["completion_tokens"] == 12 and obj["choices"][0]["finish_reason"] == "length"
         outs[name] = texts
     assert outs["native"] == outs["python"]
+
+
+def _spawn_server(tmp_path, **kw):
+    eng = LLMEngine(EngineConfig(model="tiny", device="cpu", dtype="float32", num_blocks=128, enable_graph=False,
+                                 max_seqs_per_batch=8, max_tokens_per_batch=256, enable_prefix_cache=False))
+    srv = ApiServer(eng, _tokenizer(tmp_path), model_name="tiny", host="127.0.0.1", port=0, **kw)
+    t = threading.Thread(target=srv.serve_forever, args=(5,), daemon=True)
+    t.start()
+    return srv, t
+
+
+def test_fork_master_serves_a_second_model_and_sleeps_it(tmp_path):
+    srv, t = _spawn_server(tmp_path)
+    try:
+        body = {"prompt": [5, 6, 7, 8, 9], "max_tokens": 6, "temperature": 0, "ignore_eos": True}
+        st, data = _post(srv.port, "/v1/completions", body)
+        base = json.loads(data)["choices"][0]
+        st, data = _post(srv.port, "/fork_master", {"model_id": "second", "model": "tiny", "num_blocks": 64})
+        assert st == 200 and json.loads(data)["state"] == "READY", data
+        assert json.loads(_post(srv.port, "/fork_master", {"model_id": "second"})[1])["ok"]      # idempotent
+        c = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=10)
+        c.request("GET", "/v1/models")
+        assert [m["id"] for m in json.loads(c.getresponse().read())["data"]] == ["tiny", "second"]
+        c.close()
+        st, data = _post(srv.port, "/v1/completions", dict(body, model="second"))
+        got = json.loads(data)
+        assert st == 200 and got["model"] == "second" and got["usage"]["completion_tokens"] == 6
+        # the fork has no tokenizer (a preset, not a directory): it answers with token ids
+        assert got["choices"][0]["finish_reason"] == "length" and len(got["choices"][0]["token_ids"]) == 6
+        assert srv.forks["second"].engine is not srv.engine
+        assert _post(srv.port, "/sleep", {"model_id": "second", "level": 1})[0] == 200
+        assert srv.forks["second"].engine.asleep and not srv.engine.asleep
+        c = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=10)
+        c.request("GET", "/v2/repository/index")
+        assert [m["state"] for m in json.loads(c.getresponse().read())] == ["READY", "SLEEPING"]
+        c.close()
+        assert _post(srv.port, "/wakeup", {"model_id": "second"})[0] == 200
+        st, data = _post(srv.port, "/v1/completions", dict(body, model="second"))
+        assert st == 200 and json.loads(data)["choices"][0]["token_ids"] == got["choices"][0]["token_ids"]
+        st, data = _post(srv.port, "/v1/completions", body)                                   # the first model is untouched
+        assert json.loads(data)["choices"][0]["text"] == base["text"]
+    finally:
+        srv.shutdown()
+        t.join(timeout=5)
+
+
+def test_link_p2p_pairs_two_servers_as_prefill_and_decode(tmp_path):
+    p_srv, pt = _spawn_server(tmp_path)
+    d_srv, dt = _spawn_server(tmp_path)
+    try:
+        bodies = [{"prompt": list(range(3 + i, 40 + 3 * i)), "max_tokens": 9, "temperature": 0, "ignore_eos": True,
+                   "stream": bool(i % 2)} for i in range(4)]
+
+        def text(resp):
+            st, data = resp
+            assert st == 200, data
+            if data.startswith("data: "):
+                ev = [json.loads(l[6:]) for l in data.split("\n") if l.startswith("data: ") and l != "data: [DONE]"]
+                return "".join(e["choices"][0]["text"] for e in ev if e["choices"])
+            return json.loads(data)["choices"][0]["text"]
+
+        want = [text(_post(p_srv.port, "/v1/completions", b)) for b in bodies]
+        st, data = _post(d_srv.port, "/link_p2p", {"role": "decode", "port": 0})
+        assert st == 200
+        port = json.loads(data)["port"]
+        st, data = _post(p_srv.port, "/link_p2p", {"role": "prefill", "host": "127.0.0.1", "port": port})
+        assert st == 200, data
+        assert _post(p_srv.port, "/link_p2p", {"role": "prefill", "port": port})[0] == 409
+        got = [None] * 4
+        ts = [threading.Thread(target=lambda i=i: got.__setitem__(i, text(_post(p_srv.port, "/v1/completions", bodies[i]))))
+              for i in range(4)]
+        [x.start() for x in ts]
+        [x.join(timeout=120) for x in ts]
+        assert got == want
+        assert p_srv.pd_prefill.handed_over == 4 and d_srv.pd_decode.adopted == 4
+        assert _post(p_srv.port, "/unlink_p2p", {})[0] == 200 and p_srv.pd_prefill is None
+        for _ in range(200):
+            if d_srv.pd_decode is None:
+                break
+            time.sleep(0.01)
+        assert d_srv.pd_decode is None
+        assert text(_post(p_srv.port, "/v1/completions", bodies[0])) == want[0]                # a plain instance again
+        assert p_srv.engine.scheduler.block_stats(0).num_used == 0 and d_srv.engine.scheduler.block_stats(0).num_used == 0
+    finally:
+        p_srv.shutdown()
+        d_srv.shutdown()
+        pt.join(timeout=5)
+        dt.join(timeout=5)

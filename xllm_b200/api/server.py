@@ -66,12 +66,21 @@ class _Call:
 class ApiServer:
     def __init__(self, engine: LLMEngine, tokenizer, model_name: str = "xllm_b200", host: str = "", port: int = 8010,
                  max_concurrent_requests: int = 200, tool_call_parser: str = "", reasoning_parser: str = "",
-                 request_threads: int = 4, response_threads: int = 4):
+                 request_threads: int = 4, response_threads: int = 4, parent: "ApiServer" = None):
         self.engine = engine
         self.tok = tokenizer
         self.model_name = model_name
-        self.http = _rt.HttpServer()
-        self.port = self.http.start(host, port)
+        # a forked master (another model served by the same process) shares its parent's transport
+        self.parent = parent
+        if parent is None:
+            self.http = _rt.HttpServer()
+            self.port = self.http.start(host, port)
+        else:
+            self.http, self.port = parent.http, parent.port
+        self.forks: Dict[str, "ApiServer"] = {}
+        self.pd_prefill = None      # engine/pd_service.PrefillService once linked as the prefill side
+        self.pd_decode = None       # engine/pd_service.DecodeService once linked as the decode side
+        self._pd_listen = None
         # request stage: a pool of threads that parse, template and tokenise; results queue up for the engine loop
         self.request_pool = ThreadPoolExecutor(max(1, request_threads), thread_name_prefix="xllm-req") \
             if request_threads > 0 else None
@@ -133,10 +142,15 @@ class ApiServer:
         except Exception as e:  # a malformed request must never take a thread down
             self._error(req.id, 500, f"{type(e).__name__}: {e}", "internal_error")
         finally:
-            self._ready.put(None)          # one marker per prepared request: wakes the accounting below
+            self._ready.put(None)          # one marker per prepared request (this server counts them)
+
+    def _busy(self) -> bool:
+        return (self.engine.has_unfinished() or self._preparing > 0 or
+                (self.pd_prefill is not None and self.pd_prefill.has_unfinished()) or
+                any(f._busy() for f in self.forks.values()))
 
     def run_once(self, idle_poll_ms: int = 0):
-        busy = self.engine.has_unfinished() or self._preparing > 0
+        busy = self._busy()
         for req in self.http.poll(0 if busy else idle_poll_ms):
             try:
                 path = req.path.rstrip("/") or "/"
@@ -147,6 +161,12 @@ class ApiServer:
                     self._route(req)
             except Exception as e:  # a malformed request must never take the loop down
                 self._error(req.id, 500, f"{type(e).__name__}: {e}", "internal_error")
+        self._after_poll()
+        for f in list(self.forks.values()):
+            f._after_poll()
+
+    def _after_poll(self):
+        """Everything of an iteration that belongs to ONE served model: admit, abort, step, respond."""
         # requests the pool has finished preparing: the engine is only ever touched by this thread
         while True:
             try:
@@ -154,7 +174,7 @@ class ApiServer:
             except queue.Empty:
                 break
             if item is None:
-                self._preparing -= 1
+                (self.parent or self)._preparing -= 1
                 continue
             req, call, ids, sampling, stops = item
             try:
@@ -164,7 +184,7 @@ class ApiServer:
         # client went away: abort its request (frees its KV blocks at once)
         for rid, call in list(self.calls.items()):
             if self.http.is_disconnected(call.http_id):
-                self.engine.abort(rid)
+                (self.pd_prefill or self.engine).abort(rid)
                 self.calls.pop(rid, None)
                 if call.native:
                     self._native_by_rid.pop(rid, None)
@@ -173,18 +193,34 @@ class ApiServer:
         if now >= self._next_watch:            # expired bounded waits in kernels -> unhealthy
             self._next_watch = now + self.watch_interval_s
             self.watchdog.check()
-        if self.engine.has_unfinished():
+        if self._pd_listen is not None:
+            self._pd_accept()
+        if self.pd_prefill is not None:
+            if self.pd_prefill.has_unfinished():
+                self._dispatch(self.pd_prefill.step())
+        elif self.pd_decode is not None:
+            self._dispatch(self.pd_decode.step())
+            if self.pd_decode.stopped and not self.engine.has_unfinished():
+                self.pd_decode = None          # the peer said bye or went away: plain instance again
+        elif self.engine.has_unfinished():
             self._dispatch(self.engine.step())
-        if self.rp is not None:
-            for d in self.rp.take_done():
-                self.calls.pop(d.request_id, None)
-                self._native_by_rid.pop(d.request_id, None)
-                self.trace.event(d.request_id, "finished", generated=int(d.generated), ttft_ms=round(d.ttft_ms, 3),
-                                 e2e_ms=round(d.e2e_ms, 3))
+        self._collect_done()
         s = self.engine.scheduler
         _rt.metric_gauge_set("num_running_requests", float(s.num_running))
         _rt.metric_gauge_set("num_waiting_requests", float(s.num_waiting))
         _rt.metric_gauge_set("kv_cache_utilization", float(s.kv_utilization(0)))
+
+    def _collect_done(self, wait_ms: int = 0):
+        """Forget the calls the response pool has completed."""
+        if self.rp is None:
+            return
+        if wait_ms:
+            self.rp.drain(wait_ms)
+        for d in self.rp.take_done():
+            self.calls.pop(d.request_id, None)
+            self._native_by_rid.pop(d.request_id, None)
+            self.trace.event(d.request_id, "finished", generated=int(d.generated), ttft_ms=round(d.ttft_ms, 3),
+                             e2e_ms=round(d.e2e_ms, 3))
 
     def _dispatch(self, events):
         """Output events of one step: those of natively formatted calls go to the response pool in
@@ -220,7 +256,12 @@ class ApiServer:
             return self.http.respond(req.id, 200, "text/plain; version=0.0.4", _rt.metrics_text())
         if path in ("/v1/models", "/models"):
             return self._json(req.id, 200, {"object": "list", "data": [
-                {"id": self.model_name, "object": "model", "created": int(time.time()), "owned_by": "xllm_b200"}]})
+                {"id": m.model_name, "object": "model", "created": int(time.time()), "owned_by": "xllm_b200"}
+                for m in [self] + list(self.forks.values())]})
+        if path == "/v2/repository/index":
+            return self._json(req.id, 200, [
+                {"name": m.model_name, "version": "1", "state": "SLEEPING" if m.engine.asleep else "READY"}
+                for m in [self] + list(self.forks.values())])
         if method != "POST":
             return self._error(req.id, 405 if path.startswith("/v1") else 404, f"{method} {path} not supported")
         body = {}
@@ -229,12 +270,23 @@ class ApiServer:
                 body = json.loads(req.body)
             except json.JSONDecodeError as e:
                 return self._error(req.id, 400, f"invalid JSON body: {e}")
+        # another model served by this process (fork_master): same routes, its own engine
+        target = self.forks.get(str(body.get("model") or body.get("model_id") or ""))
+        if target is not None and path in self.GENERATION_PATHS + ("/v1/embeddings", "/v1/rerank", "/v1/sample",
+                                                                   "/sleep", "/wakeup", "/pause", "/resume"):
+            return target._route(req, prepared)
         if path == "/v1/completions":
             return self._completion(req, body)
         if path == "/v1/chat/completions":
             return self._chat(req, body, "chat")
         if path == "/v1/messages":
             return self._chat(req, body, "anthropic")
+        if path == "/fork_master":
+            return self._fork_master(req, body)
+        if path == "/link_p2p":
+            return self._link_p2p(req, body)
+        if path == "/unlink_p2p":
+            return self._unlink_p2p(req, body)
         if path == "/v1/embeddings":
             return self._embeddings(req, body)
         if path == "/v1/rerank":
@@ -250,8 +302,12 @@ class ApiServer:
             self.engine.resume()
             return self._json(req.id, 200, {"status": "running"})
         if path == "/sleep":      # releases the KV cache (level 1) and the weights too (level 2)
-            self.engine.sleep(int(body.get("level", 1)))
-            return self._json(req.id, 200, {"status": "sleeping", "level": int(body.get("level", 1))})
+            level = int(body.get("level", body.get("master_status", 1)) or 1)
+            self._collect_done(wait_ms=200)
+            if self.calls:        # the reference's rule: a master only sleeps with no request in flight
+                return self._error(req.id, 409, f"{len(self.calls)} requests in flight", "conflict")
+            self.engine.sleep(level)
+            return self._json(req.id, 200, {"status": "sleeping", "level": level})
         if path == "/wakeup":
             self.engine.wake_up()
             return self._json(req.id, 200, {"status": "running"})
@@ -260,6 +316,100 @@ class ApiServer:
         if path == "/stop_profile":
             return self._profile(req, False, body)
         return self._error(req.id, 404, f"unknown route {path}")
+
+    # ------------------------------------------------------------------ more masters, instance links
+    def _fork_master(self, req, body):
+        """Serve another model from this process (the reference's `fork_master`,
+        api_service.cpp:1046-1118): its own engine, scheduler and KV cache on the same device, the
+        same transport; requests reach it through their `model` field.  `master_status` 1 / 2 starts
+        it asleep (KV cache released / weights on the host as well) until `/wakeup`."""
+        mid = str(body.get("model_id") or body.get("model") or "")
+        if not mid:
+            return self._error(req.id, 400, "`model_id` is required")
+        if mid == self.model_name or mid in self.forks:
+            return self._json(req.id, 200, {"ok": True, "message": f"master for model {mid} already exists"})
+        import dataclasses
+        from ..engine.llm_engine import EngineConfig, LLMEngine
+        base = self.engine.cfg
+        allowed = {f.name for f in dataclasses.fields(EngineConfig)}
+        kw = {k: v for k, v in body.items() if k in allowed and k not in ("model", "device")}
+        cfg = dataclasses.replace(base, model=str(body.get("model_path") or body.get("model") or mid), **kw)
+        try:
+            eng = LLMEngine(cfg)
+        except Exception as e:
+            return self._error(req.id, 400, f"failed to fork master {mid}: {type(e).__name__}: {e}")
+        tok = None
+        if os.path.isdir(cfg.model):
+            try:
+                from ..utils.tokenizer import load_tokenizer
+                tok = load_tokenizer(cfg.model)
+            except Exception:
+                tok = None
+        fork = ApiServer(eng, tok, model_name=mid, max_concurrent_requests=self.max_concurrent,
+                         tool_call_parser=self.tool_kind, reasoning_parser=self.reason_kind,
+                         request_threads=0, response_threads=self.rp.num_threads if self.rp else 0, parent=self)
+        fork.request_pool = self.request_pool
+        self.forks[mid] = fork
+        status = int(body.get("master_status", 0) or 0)
+        if status in (1, 2):
+            eng.sleep(status)
+        return self._json(req.id, 200, {"ok": True, "model_id": mid, "state": "SLEEPING" if eng.asleep else "READY"})
+
+    def _link_p2p(self, req, body):
+        """Pair this instance with another one for prefill/decode disaggregation (the reference's
+        `link_p2p`): role "decode" listens on `port` and adopts what the peer prefills; role "prefill"
+        connects to a decode instance at `host:port` and from then on hands every request over after
+        its first token.  KV travels on the same connection (`SocketCopy`) unless a peer-memory link
+        was installed through `attach_pd`."""
+        from ..engine.pd_service import Channel, PrefillService, SocketCopy
+        role = str(body.get("role", "prefill"))
+        host, port = str(body.get("host", "127.0.0.1")), int(body.get("port", 0))
+        if self.pd_prefill is not None or self.pd_decode is not None or self._pd_listen is not None:
+            return self._error(req.id, 409, "already linked", "conflict")
+        if role == "decode":
+            srv = Channel.listen(host, port)
+            srv.setblocking(False)
+            self._pd_listen = srv
+            return self._json(req.id, 200, {"ok": True, "role": "decode", "port": srv.getsockname()[1]})
+        self._collect_done(wait_ms=200)
+        if self.calls:
+            return self._error(req.id, 409, "requests in flight", "conflict")
+        try:
+            ch = Channel.connect(host, port, timeout=float(body.get("timeout", 10.0)))
+            self.engine.scheduler.set_hold_finished_blocks(True)
+            self.pd_prefill = PrefillService(self.engine, ch, SocketCopy(self.engine.runner),
+                                             hello_timeout=float(body.get("timeout", 10.0)))
+        except Exception as e:
+            self.engine.scheduler.set_hold_finished_blocks(False)
+            self.pd_prefill = None
+            return self._error(req.id, 502, f"cannot link to {host}:{port}: {type(e).__name__}: {e}", "bad_gateway")
+        return self._json(req.id, 200, {"ok": True, "role": "prefill", "peer": f"{host}:{port}"})
+
+    def _pd_accept(self):
+        from ..engine.pd_service import Channel, DecodeService, SocketCopy
+        try:
+            conn, _ = self._pd_listen.accept()
+        except (BlockingIOError, OSError):
+            return
+        self._pd_listen.close()
+        self._pd_listen = None
+        self.pd_decode = DecodeService(self.engine, Channel(conn), SocketCopy(self.engine.runner))
+
+    def _unlink_p2p(self, req, body):
+        if self.pd_prefill is not None:
+            if self.pd_prefill.has_unfinished():
+                return self._error(req.id, 409, "requests in flight", "conflict")
+            self.pd_prefill.close()
+            self.pd_prefill.ch.close()
+            self.engine.runner.meta_hook = None
+            self.engine.scheduler.set_hold_finished_blocks(False)
+            self.pd_prefill = None
+        if self._pd_listen is not None:
+            self._pd_listen.close()
+            self._pd_listen = None
+        if self.pd_decode is not None:
+            self.pd_decode.ch.close()       # the service reclaims on its next step
+        return self._json(req.id, 200, {"ok": True})
 
     def _profile(self, req, start, body):
         from ..utils.tracing import Profiler
@@ -324,7 +474,11 @@ class ApiServer:
             call.reasoning_text.append("")
             call.tools.append(_rt.ToolCallParser(self.tool_kind) if self.tool_kind and call.kind != "completion" else None)
             call.tool_calls.append([])
-        ok = self.engine.add_request(call.request_id, prompt_ids, n=n, stream=call.stream, **sampling)
+        if self.pd_prefill is not None and n == 1:
+            ok = self.pd_prefill.add_request(call.request_id, prompt_ids, **{k: v for k, v in sampling.items()
+                                                                            if k not in ("logprobs",)})
+        else:
+            ok = self.engine.add_request(call.request_id, prompt_ids, n=n, stream=call.stream, **sampling)
         if not ok:
             return self._error(req.id, 400, "prompt is empty or longer than the model's context window")
         self.calls[call.request_id] = call

@@ -376,6 +376,7 @@ PYBIND11_MODULE(_rt, m) {
       .def("adopt_reserved", &Scheduler::adopt_reserved, py::arg("request_id"), py::arg("tokens"),
            py::arg("num_prompt_tokens"), py::arg("sampling"), py::arg("stopping"), py::arg("priority") = 0,
            py::arg("offline") = false, py::arg("stream") = false)
+      .def("set_hold_finished_blocks", &Scheduler::set_hold_finished_blocks)
       .def("held_blocks", &Scheduler::held_blocks)
       .def("release_held", &Scheduler::release_held)
       .def("schedule", &Scheduler::schedule, py::call_guard<py::gil_scoped_release>())

@@ -285,6 +285,8 @@ class Scheduler {
     return true;
   }
 
+  // Prefill side of a disaggregated pair: finished prompts keep their blocks until released.
+  void set_hold_finished_blocks(bool on) { cfg_.hold_finished_blocks = on; }
   // Blocks of a finished sequence that hold_finished_blocks kept alive (empty if none).
   std::vector<int32_t> held_blocks(const std::string& id) const {
     auto it = held_.find(id);

@@ -300,6 +300,9 @@ class RemoteEvent:
         self.request_finished = self.finished
         self.finish_reason = m.get("reason", "")
         self.index = 0
+        self.seq_index = 0
+        self.has_logprob = False
+        self.num_prompt_tokens = 0
         self.seq_id = -1
 
 
