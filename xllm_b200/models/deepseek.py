@@ -208,7 +208,12 @@ class DeepseekCausalLM(DenseCausalLM):
         """2 = separate K and V caches; 1 = one latent cache per layer (the V handle aliases it)."""
         return 1 if self.layers[0].self_attn.latent else 2
 
-    supports_graph = True
+    @property
+    def supports_graph(self):
+        """The latent-cache kernels exist for DeepSeek's widths (512 + 64); other widths run the
+        tensor-op form, which reads lengths on the host and therefore cannot be captured."""
+        att = self.layers[0].self_attn
+        return not att.latent or (self.args.kv_lora_rank == 512 and self.args.qk_rope_head_dim == 64)
 
 
 class MTPDraft(Module):

@@ -30,7 +30,9 @@ def cache_write(kv_a, norm_w, eps, cos_sin, positions, slots, cache, q_rope, q_c
     """cache row of every token's slot = [rmsnorm(kv_a[:, :512]) * w | rope(kv_a[:, 512:])];
     q_cat[..., 512:] = rope(q_rope) for every head.  cache: any tensor whose memory is rows of 576."""
     T = kv_a.shape[0]
-    if not kv_a.is_cuda:
+    # the kernels are built for DeepSeek's widths (512 + 64); anything else (tiny test models) takes
+    # the tensor-op form, on whatever device it lives
+    if not kv_a.is_cuda or norm_w.shape[0] != LATENT or kv_a.shape[1] != LATENT + ROT:
         from . import reference
         lat = norm_w.shape[0]                      # the reference takes any latent / rotary width
         c, _ = reference.rmsnorm(kv_a[:, :lat].contiguous(), norm_w, eps)
@@ -43,9 +45,6 @@ def cache_write(kv_a, norm_w, eps, cos_sin, positions, slots, cache, q_rope, q_c
         if q_cat is not None:
             q_cat[..., lat:] = rope_pairs(q_rope, cs)
         return
-    if norm_w.shape[0] != LATENT or kv_a.shape[1] != LATENT + ROT:
-        raise ValueError(f"the MLA kernels are built for a {LATENT}-wide latent and {ROT} rotary values, "
-                         f"got {norm_w.shape[0]} + {kv_a.shape[1] - norm_w.shape[0]}")
     assert kv_a.dtype == torch.bfloat16 and kv_a.stride(1) == 1 and kv_a.shape[1] == LATENT + ROT
     assert cos_sin.dtype == torch.float32 and cos_sin.shape[1] == ROT and cache.is_contiguous()
     nh = 0
@@ -84,7 +83,7 @@ def decode(q_cat, cache, block_table, scale, seq_lens=None, positions=None, bt_r
     [n_blocks, (1,) page, 576].  Row n sees seq_lens[n] tokens (or positions[n] + 1) of the sequence whose
     block-table row is bt_rows[n] (default n)."""
     N, nh, _ = q_cat.shape
-    if not q_cat.is_cuda:
+    if not q_cat.is_cuda or latent != LATENT or q_cat.shape[2] != LATENT + ROT:
         lens = seq_lens if seq_lens is not None else positions + 1
         y = decode_reference(q_cat, cache, block_table, lens, bt_rows, scale, latent)
         if out is not None:
