@@ -48,10 +48,13 @@ from .disagg import _FirstToken
 
 # ------------------------------------------------------------------------------------------ framing
 class Channel:
-    """Length-prefixed msgpack frames over a connected TCP socket; `poll` never blocks."""
+    """Length-prefixed frames over a connected TCP socket; `poll` never blocks.  A frame body is a
+    protobuf message behind a type byte (`xllm_b200.proto.encode`; codec "protobuf", the default) or a
+    msgpack map (codec "msgpack"); both ends must use the same codec."""
 
-    def __init__(self, sock: socket.socket):
+    def __init__(self, sock: socket.socket, codec: str = "protobuf"):
         self.sock = sock
+        self.codec = codec
         sock.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
         sock.setblocking(True)
         self._rx = bytearray()
@@ -87,7 +90,11 @@ class Channel:
     def send(self, msg: dict) -> bool:
         if self.closed:
             return False
-        body = msgpack.packb(msg, use_bin_type=True)
+        if self.codec == "protobuf":
+            from .. import proto
+            body = proto.encode(msg)
+        else:
+            body = msgpack.packb(msg, use_bin_type=True)
         try:
             self.sock.sendall(struct.pack("<I", len(body)) + body)
             self.sent += 1
@@ -119,7 +126,12 @@ class Channel:
                 (n,) = struct.unpack_from("<I", self._rx, 0)
                 if len(self._rx) < 4 + n:
                     break
-                out.append(msgpack.unpackb(bytes(self._rx[4:4 + n]), raw=False))
+                frame = bytes(self._rx[4:4 + n])
+                if self.codec == "protobuf":
+                    from .. import proto
+                    out.append(proto.decode(frame))
+                else:
+                    out.append(msgpack.unpackb(frame, raw=False))
                 del self._rx[:4 + n]
                 self.received += 1
         return out
