@@ -44,9 +44,11 @@ def log_softmax(x: torch.Tensor) -> torch.Tensor:
 def topk_reference(x: torch.Tensor, k: int, normalize: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """Values descending, ties to the lowest index (a stable sort)."""
     v = x.float()
+    # the order is that of the logits themselves (subtracting the normaliser can round two different
+    # logits to the same log-probability)
+    order = torch.sort(v, dim=-1, descending=True, stable=True).indices[:, :k]
     if normalize:
         v = torch.log_softmax(v, dim=-1)
-    order = torch.sort(v, dim=-1, descending=True, stable=True).indices[:, :k]
     return v.gather(1, order), order.to(torch.int32)
 
 
