@@ -78,3 +78,40 @@ int main(void) {
     assert r.returncode == 0, r.stdout + r.stderr
     res = json.loads(r.stdout.split("RESULT ", 1)[1])
     assert len(res[0]["token_ids"]) == 4
+
+
+def test_cpp_wrapper_from_a_cpp_program(tmp_path):
+    """The header-only C++ class over the C API: Initialize / Completions / Call / Sleep / WakeUp."""
+    src = tmp_path / "host.cc"
+    src.write_text(r'''
+#include <iostream>
+#include "xllm.hpp"
+int main() {
+  xllm_b200::LLM llm;
+  if (!llm.Initialize("tiny", R"({"devices": "cpu", "dtype": "float32", "num_blocks": 64, "enable_graph": false})")) {
+    std::cout << "init failed: " << xllm_b200::LLM::LastError() << "\n";
+    return 1;
+  }
+  const std::string sp = R"({"max_tokens": 4, "temperature": 0.0, "ignore_eos": true})";
+  std::string a = llm.Completions("[[1, 2, 3, 4, 5]]", sp);
+  llm.Sleep(1);
+  llm.WakeUp();
+  std::string b = llm.Completions("[[1, 2, 3, 4, 5]]", sp);
+  std::string beams = llm.Call("beam_search", R"({"prompt": [1, 2, 3, 4, 5], "beam_width": 2, "max_tokens": 3})");
+  bool threw = false;
+  try { llm.Call("no_such_method", "{}"); } catch (const std::exception& e) { threw = true; }
+  std::cout << "RESULT " << a << "\nAGAIN " << b << "\nBEAMS " << beams << "\nTHREW " << threw << "\n";
+  return 0;
+}
+''')
+    lib = _build.build_c_api()
+    exe = tmp_path / "host_cc"
+    inc = os.path.join(ROOT, "xllm_b200", "csrc", "c_api")
+    subprocess.run(["g++", "-std=c++17", str(src), "-I", inc, "-o", str(exe), str(lib), f"-Wl,-rpath,{lib.parent}",
+                    f"-Wl,-rpath,{sysconfig.get_config_var('LIBDIR')}"], check=True)
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.pathsep.join(p for p in sys.path if p))
+    r = subprocess.run([str(exe)], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    lines = {l.split(" ", 1)[0]: l.split(" ", 1)[1] for l in r.stdout.splitlines() if " " in l}
+    assert json.loads(lines["RESULT"]) == json.loads(lines["AGAIN"]) and len(json.loads(lines["RESULT"])[0]["token_ids"]) == 4
+    assert len(json.loads(lines["BEAMS"])) == 2 and lines["THREW"] == "1"

@@ -36,6 +36,14 @@ XLLM_C_API void xllm_llm_destroy(xllm_llm* llm);
  *   {"token_ids": [...], "text": "...", "finish_reason": "...", "prompt_tokens": n}  */
 XLLM_C_API char* xllm_llm_generate(xllm_llm* llm, const char* prompts_json, const char* sampling_json);
 
+/* Every other method of the offline API by name; args_json holds its keyword arguments, the result is
+ * a JSON document:
+ *   "chat"           {"messages": [{"role": ..., "content": ...}, ...], "sampling": {...}}  -> same objects as generate
+ *   "embed"          {"prompts": [...]}                                -> [[float, ...], ...]
+ *   "beam_search"    {"prompt": [...ids] | "text", "beam_width": 4, "max_tokens": 16} -> [{"token_ids", "score"}, ...]
+ *   "sleep"          {"level": 1 | 2}     "wake_up" {}     "stats" {}   -> {"ok": true} / counters  */
+XLLM_C_API char* xllm_llm_call(xllm_llm* llm, const char* method, const char* args_json);
+
 /* Engine counters as a JSON object (steps, KV utilisation, prefix hits, ...). */
 XLLM_C_API char* xllm_llm_stats(xllm_llm* llm);
 

@@ -136,6 +136,26 @@ char* xllm_llm_stats(xllm_llm* llm) {
   return dup_result(r);
 }
 
+char* xllm_llm_call(xllm_llm* llm, const char* method, const char* args_json) {
+  if (llm == nullptr || method == nullptr) {
+    g_error = "null argument";
+    return nullptr;
+  }
+  Gil gil;
+  PyObject* f = bridge("call");
+  if (f == nullptr) {
+    take_error("cannot import xllm_b200.api.c_bridge");
+    return nullptr;
+  }
+  PyObject* r = PyObject_CallFunction(f, "Oss", llm->handle, method, args_json ? args_json : "{}");
+  Py_DECREF(f);
+  if (r == nullptr) {
+    take_error("xllm_llm_call failed");
+    return nullptr;
+  }
+  return dup_result(r);
+}
+
 void xllm_free_string(char* s) { free(s); }
 const char* xllm_last_error(void) { return g_error.c_str(); }
 
