@@ -106,6 +106,10 @@ class ApiServer:
         self.watch_interval_s = 3.0
         from ..utils.tracing import TraceLog
         self.trace = TraceLog(os.environ.get("XLLM_TRACE_LOG", ""))
+        from ..utils import metrics_catalog
+        if parent is None:
+            metrics_catalog.register_all()
+        self.metrics = metrics_catalog.EnginePublisher(engine)
 
     def _set_unhealthy(self, reason: str):
         """/health answers 503 with the reason from now on; an orchestrator is expected to recycle the instance."""
@@ -118,6 +122,12 @@ class ApiServer:
 
     def _error(self, http_id, status, message, typ="invalid_request_error"):
         _rt.metric_counter_add("server_request_total_fail")
+        _rt.metric_counter_add({400: "request_status_total_invalid_argument", 401: "request_status_total_unauthenticated",
+                                404: "request_status_total_unimplemented", 405: "request_status_total_unimplemented",
+                                429: "request_status_total_resource_exhausted", 503: "request_status_total_unavailable"}
+                               .get(status, "request_status_total_unknown"))
+        if status == 429:
+            _rt.metric_counter_add("server_request_total_limit")
         self._json(http_id, status, {"error": {"message": message, "type": typ, "code": status}})
 
     def shutdown(self):
@@ -205,10 +215,7 @@ class ApiServer:
         elif self.engine.has_unfinished():
             self._dispatch(self.engine.step())
         self._collect_done()
-        s = self.engine.scheduler
-        _rt.metric_gauge_set("num_running_requests", float(s.num_running))
-        _rt.metric_gauge_set("num_waiting_requests", float(s.num_waiting))
-        _rt.metric_gauge_set("kv_cache_utilization", float(s.kv_utilization(0)))
+        self.metrics.tick(len(self.calls))
 
     def _collect_done(self, wait_ms: int = 0):
         """Forget the calls the response pool has completed."""
@@ -504,7 +511,9 @@ class ApiServer:
                 prompt = prompt[0] if prompt else ""
             if self.tok is None:
                 return self._error(req.id, 400, "this server has no tokenizer: send token ids as `prompt`")
+            t0 = time.perf_counter()
             ids, text = self.tok.encode(prompt), prompt
+            _rt.metric_counter_add("tokenization_latency_seconds", time.perf_counter() - t0)
         sampling, stops = self._sampling(body, 16)
         rid = req.header("x-request-id") or f"cmpl-{uuid.uuid4().hex}"
         call = _Call(req.id, rid, "completion", bool(body.get("stream")), body.get("model") or self.model_name,
@@ -522,9 +531,13 @@ class ApiServer:
         if not messages:
             return self._error(req.id, 400, "`messages` must not be empty")
         kwargs = dict(body.get("chat_template_kwargs") or {})
+        t0 = time.perf_counter()
         prompt = self.tok.apply_chat_template(messages, tools=body.get("tools"), add_generation_prompt=True,
                                               enable_thinking=bool(kwargs.get("enable_thinking", True)))
+        t1 = time.perf_counter()
         ids = self.tok.encode(prompt)
+        _rt.metric_counter_add("chat_template_latency_seconds", t1 - t0)
+        _rt.metric_counter_add("tokenization_latency_seconds", time.perf_counter() - t1)
         sampling, stops = self._sampling(body)
         rid = req.header("x-request-id") or (f"msg_{uuid.uuid4().hex}" if kind == "anthropic" else f"chatcmpl-{uuid.uuid4().hex}")
         call = _Call(req.id, rid, kind, bool(body.get("stream")), body.get("model") or self.model_name,

@@ -285,6 +285,9 @@ class ResponseProcessor {
     const double now = now_s();
     Metrics& m = Metrics::instance();
     m.counter_add(aborted ? "server_request_total_fail" : "server_request_total_ok", 1.0);
+    m.counter_add(aborted ? "request_status_total_cancelled" : "request_status_total_ok", 1.0);
+    m.histogram_observe("num_generated_tokens_per_request", (double)gen);
+    m.histogram_observe("num_prompt_tokens_per_request", (double)c.spec.prompt_tokens);
     m.counter_add("num_generated_tokens_total", (double)gen);
     m.counter_add("num_prompt_tokens_total", (double)c.spec.prompt_tokens);
     m.histogram_observe("end_2_end_latency_milliseconds", (now - c.spec.t_arrival) * 1e3);
