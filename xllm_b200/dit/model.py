@@ -27,12 +27,18 @@ class DiTBlock(torch.nn.Module):
         self.fc2 = torch.nn.Linear(4 * dim, dim)
         self.ada = torch.nn.Linear(dim, 6 * dim)
 
-    def forward(self, x, c):
+    def forward(self, x, c, st=None):
+        """x: [B, T, D] (with sequence parallelism: this rank's T/sp tokens; attention then goes through
+        the Ulysses all-to-all, parallel/dit_parallel.py)."""
         s1, b1, g1, s2, b2, g2 = self.ada(F.silu(c))[:, None].chunk(6, dim=-1)
         h = F.layer_norm(x, x.shape[-1:]) * (1 + s1) + b1
         B, T, D = h.shape
         q, k, v = self.qkv(h).view(B, T, 3, self.heads, D // self.heads).permute(2, 0, 3, 1, 4)
-        a = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, T, D)
+        if st is not None and st.sp_size > 1:
+            from ..parallel.dit_parallel import ulysses_attention
+            a = ulysses_attention(q.contiguous(), k.contiguous(), v.contiguous(), st).transpose(1, 2).reshape(B, T, D)
+        else:
+            a = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, T, D)
         x = x + g1 * self.proj(a)
         h = F.layer_norm(x, x.shape[-1:]) * (1 + s2) + b2
         return x + g2 * self.fc2(F.gelu(self.fc1(h), approximate="tanh"))
@@ -47,6 +53,7 @@ class TinyDiT(torch.nn.Module):
         self.t_mlp = torch.nn.Sequential(torch.nn.Linear(dim, dim), torch.nn.SiLU(), torch.nn.Linear(dim, dim))
         self.blocks = torch.nn.ModuleList([DiTBlock(dim, heads) for _ in range(depth)])
         self.out = torch.nn.Linear(dim, in_ch * patch * patch)
+        self.cond = torch.nn.Linear(dim, dim)      # conditioning vector (e.g. a pooled text embedding) -> modulation
         self.dim = dim
 
     def patchify(self, x):
@@ -59,28 +66,53 @@ class TinyDiT(torch.nn.Module):
         p, C, n = self.patch, self.in_ch, self.size // self.patch
         return y.view(B, n, n, C, p, p).permute(0, 3, 1, 4, 2, 5).reshape(B, C, n * p, n * p)
 
-    def forward(self, x, t, cache=None, step=0):
+    def forward(self, x, t, cache=None, step=0, cond=None, st=None):
+        """cond: [B, dim] conditioning vectors or None (the unconditional branch).  st: a
+        DitParallelState; with sp_size > 1 the token sequence is sharded over the sp group between the
+        patch embedding and the output projection."""
         c = self.t_mlp(timestep_embedding(t, self.dim))
+        if cond is not None:
+            c = c + self.cond(cond)
         h = self.embed(self.patchify(x)) + self.pos
-        first = lambda z: self.blocks[0](z, c)
+        sp = st is not None and st.sp_size > 1
+        if sp:
+            from ..parallel.dit_parallel import gather_sequence, shard_sequence
+            h = shard_sequence(h, st, dim=1)
+        first = lambda z: self.blocks[0](z, c, st)
 
         def rest(z):
             for b in self.blocks[1:]:
-                z = b(z, c)
+                z = b(z, c, st)
             return z
 
         h = cache.run(step, h, first, rest) if cache is not None else rest(first(h))
+        if sp:
+            h = gather_sequence(h, st, dim=1)
         return self.unpatchify(self.out(h))
 
     @torch.no_grad()
-    def sample(self, noise, steps=20, cache=None):
-        """Euler integration of the predicted velocity from t = 1 to t = 0."""
+    def sample(self, noise, steps=20, cache=None, cond=None, guidance_scale=1.0, st=None):
+        """Euler integration of the predicted velocity from t = 1 to t = 0.  With a conditioning vector
+        and guidance_scale != 1 every step evaluates the conditional and the unconditional branch
+        (classifier-free guidance): on one rank as a batch of two, with a CFG group of two ranks one
+        branch per rank and an all-gather of the two predictions."""
         x = noise
         ts = torch.linspace(1.0, 0.0, steps + 1)
         if cache is not None:
             cache.reset()
+        guided = cond is not None and guidance_scale != 1.0
+        cfg_parallel = guided and st is not None and st.cfg_size == 2
         for i in range(steps):
             t = ts[i].expand(x.shape[0]) * 1000
-            v = self.forward(x, t, cache, i)
+            if not guided:
+                v = self.forward(x, t, cache, i, cond=cond, st=st)
+            elif cfg_parallel:
+                from ..parallel.dit_parallel import cfg_combine
+                mine = cond if st.cfg_rank == 0 else None
+                v = cfg_combine(self.forward(x, t, cache, i, cond=mine, st=st), st, guidance_scale)
+            else:
+                vc = self.forward(x, t, None, i, cond=cond, st=st)
+                vu = self.forward(x, t, None, i, cond=None, st=st)
+                v = vu + guidance_scale * (vc - vu)
             x = x + (ts[i + 1] - ts[i]) * v
         return x

@@ -52,16 +52,25 @@ class ImagePipeline:
         g = torch.Generator().manual_seed(seed + 1)
         self.to_rgb = torch.randn(3, self.model.in_ch, generator=g) * 0.5          # latent channels -> RGB
 
+    def prompt_embedding(self, prompt: str, n: int) -> torch.Tensor:
+        """A fixed pseudo-embedding of the prompt (this build has no text encoder): the conditioning
+        vector of the guided branch."""
+        seed = int.from_bytes(hashlib.blake2b(("cond:" + prompt).encode(), digest_size=4).digest(), "little")
+        g = torch.Generator().manual_seed(seed)
+        return torch.randn(1, self.model.dim, generator=g).expand(n, -1).to(self.device)
+
     @torch.no_grad()
     def generate(self, prompt: str, n: int = 1, size: str = "64x64", steps: Optional[int] = None,
-                 seed: Optional[int] = None) -> List[np.ndarray]:
+                 seed: Optional[int] = None, guidance_scale: float = 1.0, parallel=None) -> List[np.ndarray]:
         w, h = (int(v) for v in size.lower().split("x"))
         if seed is None:                       # the same prompt gives the same image
             seed = int.from_bytes(hashlib.blake2b(prompt.encode(), digest_size=4).digest(), "little")
         g = torch.Generator().manual_seed(int(seed))
         noise = torch.randn(n, self.model.in_ch, self.latent_size, self.latent_size, generator=g).to(self.device)
         cache = make_cache(self.cache_kind) if self.cache_kind and self.cache_kind != "none" else None
-        lat = self.model.sample(noise, steps=steps or self.steps, cache=cache).float().cpu()
+        cond = self.prompt_embedding(prompt, n) if guidance_scale != 1.0 else None
+        lat = self.model.sample(noise, steps=steps or self.steps, cache=cache, cond=cond, guidance_scale=guidance_scale,
+                                st=parallel).float().cpu()
         rgb = torch.einsum("oc,bchw->bohw", self.to_rgb, lat)
         rgb = torch.nn.functional.interpolate(rgb, size=(h, w), mode="nearest")
         rgb = ((rgb.tanh() * 0.5 + 0.5) * 255).round().clamp(0, 255).to(torch.uint8)
@@ -83,6 +92,7 @@ class ImagePipeline:
             raise ValueError("`size` must look like 256x256")
         if not (8 <= w <= 1024 and 8 <= h <= 1024):
             raise ValueError("`size` out of range")
-        imgs = self.generate(prompt, n, size, body.get("num_inference_steps") or body.get("steps"), body.get("seed"))
+        imgs = self.generate(prompt, n, size, body.get("num_inference_steps") or body.get("steps"), body.get("seed"),
+                             guidance_scale=float(body.get("guidance_scale") or 1.0), parallel=getattr(self, "parallel", None))
         return {"created": int(time.time()),
                 "data": [{"b64_json": base64.b64encode(encode_png(im)).decode()} for im in imgs]}
