@@ -88,3 +88,10 @@ def test_pd_disaggregation_two_processes_peer_push():
     out = _run("mp_pd.py", 2, timeout=600)
     assert "PD_OK" in out
     print(out[out.index("PD_OK"):].splitlines()[0])
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_ulysses_all_to_all_over_peer_memory():
+    out = _run("mp_ulysses_a2a.py", min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2)
+    assert "ULYSSES_A2A_OK" in out
+    print(out[out.index("ULYSSES_A2A_OK"):].splitlines()[0])

@@ -719,7 +719,100 @@ __global__ void __launch_bounds__(256) tp_gather_cols_kernel(TpGatherParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------- permuting all-to-all
+// Ulysses sequence parallelism: x [d0, d1, d2, E] on every rank; dimension `scatter` (1 or 2) is cut
+// into `world` parts, part r goes to rank r, and what arrives is laid out along the OTHER of the two
+// dimensions in rank order -- the layout change and the exchange in one pass of peer stores:
+//   mode 0 (scatter d1, gather d2): out [d0, d1 / n, n * d2, E]  (sequence-sharded -> head-sharded)
+//   mode 1 (scatter d2, gather d1): out [d0, n * d1, d2 / n, E]  (head-sharded -> sequence-sharded)
+// E elements of 2 bytes, E % 8 == 0.  The receive area is double-buffered by call parity, so a rank may
+// run ahead into the next call while a peer still reads the previous result; the caller copies the
+// result out before the call after next.
+struct A2aParams {
+  const bf16* x;
+  void* const* peer_bufs;
+  void* const* signal_pads;
+  int64_t recv_off;           // byte offset of the receive area ([2 halves] of half_bytes)
+  int64_t half_bytes;
+  int64_t sig_off;
+  uint32_t* state;            // [0] epoch, [1] arrival counter
+  int* err;
+  int d0, d1, d2, E, mode, rank, world;
+  long long budget;
+};
+
+__global__ void __launch_bounds__(256) a2a_permute_kernel(A2aParams p) {
+  __shared__ int s_last;
+  pdl_wait();
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(p.state) + 1u;
+  const int64_t half = (int64_t)(epoch & 1u) * p.half_bytes;
+  const int ev = p.E >> 3;
+  const int n = p.world;
+  const int64_t total = (int64_t)p.d0 * p.d1 * p.d2 * ev;
+  const int d1s = p.d1 / n, d2s = p.d2 / n;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int v = (int)(i % ev);
+    int64_t r = i / ev;
+    const int i2 = (int)(r % p.d2);
+    r /= p.d2;
+    const int i1 = (int)(r % p.d1);
+    const int i0 = (int)(r / p.d1);
+    int dst;
+    int64_t idx;
+    if (p.mode == 0) {
+      dst = i1 / d1s;
+      idx = (((int64_t)i0 * d1s + (i1 - dst * d1s)) * ((int64_t)n * p.d2) + (int64_t)p.rank * p.d2 + i2) * p.E;
+    } else {
+      dst = i2 / d2s;
+      idx = (((int64_t)i0 * ((int64_t)n * p.d1) + (int64_t)p.rank * p.d1 + i1) * d2s + (i2 - dst * d2s)) * p.E;
+    }
+    const uint4 u = *reinterpret_cast<const uint4*>(p.x + (((int64_t)i0 * p.d1 + i1) * p.d2 + i2) * p.E + (int64_t)v * 8);
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.peer_bufs[dst]) + p.recv_off + half + (idx + (int64_t)v * 8) * 2) = u;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    s_last = atomicAdd(p.state + 1, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (threadIdx.x < p.world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(p.signal_pads[threadIdx.x]) + p.sig_off + p.rank, epoch);
+  }
+  wait_flags(p.signal_pads, p.sig_off, p.rank, p.world, epoch, p.budget, p.err, 600);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    p.state[1] = 0u;
+    *reinterpret_cast<volatile uint32_t*>(p.state) = epoch;
+    __threadfence();
+  }
+}
+
 }  // namespace xllm
+
+// x: local [d0, d1, d2, E] bf16 (16-byte aligned); the result of this call lies at byte offset
+// recv_off + (new epoch & 1) * half_bytes of this rank's symmetric buffer, where the new epoch is
+// state[0] + 1 at launch (the kernel publishes it in state[0]); shapes as described at the kernel.
+XLLM_API int xllm_a2a_permute(const void* x, const void* peer_bufs, const void* signal_pads, int64_t recv_off,
+                              int64_t half_bytes, int64_t sig_off, void* state, void* err, int d0, int d1, int d2, int E,
+                              int mode, int rank, int world, void* stream) {
+  using namespace xllm;
+  if ((int64_t)d0 * d1 * d2 * E == 0) return 0;
+  if (E % 8 != 0 || world > kMaxRanks || world < 1 || (mode != 0 && mode != 1) || (recv_off & 15) || (half_bytes & 15) ||
+      ((uintptr_t)x & 15))
+    return (int)cudaErrorInvalidValue;
+  if ((mode == 0 ? d1 : d2) % world != 0) return (int)cudaErrorInvalidValue;
+  if ((int64_t)d0 * d1 * d2 * E * 2 > half_bytes) return (int)cudaErrorInvalidValue;
+  A2aParams p;
+  p.x = (const bf16*)x; p.peer_bufs = (void* const*)peer_bufs; p.signal_pads = (void* const*)signal_pads;
+  p.recv_off = recv_off; p.half_bytes = half_bytes; p.sig_off = sig_off; p.state = (uint32_t*)state; p.err = (int*)err;
+  p.d0 = d0; p.d1 = d1; p.d2 = d2; p.E = E; p.mode = mode; p.rank = rank; p.world = world; p.budget = g_wait_budget_cycles;
+  const int64_t total = (int64_t)d0 * d1 * d2 * (E / 8);
+  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(592, (total + 255) / 256));
+  launch_pdl(a2a_permute_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, p);
+  return XLLM_LAUNCH_CHECK();
+}
 
 // Number of uint32 flag slots one call site needs in the signal pad.
 XLLM_API int64_t xllm_tp_signal_slots(int world) { return (int64_t)world; }

@@ -131,6 +131,61 @@ def gather_sequence(x: torch.Tensor, st: DitParallelState, dim: int = 1) -> torc
     return torch.cat(parts, dim=dim)
 
 
+class AllToAll:
+    """The Ulysses exchange over peer memory (CUDA): one kernel (`a2a_permute_kernel`, comm.cu) stores
+    every element straight into its place in the destination rank's receive area, in the head-sharded
+    (or sequence-sharded) layout, and one flag exchange completes the call.  Attach to a
+    DitParallelState as `st.a2a`; used by `all_to_all` for bf16 4-D tensors with scatter / gather dims
+    (1, 2) or (2, 1), anything else goes through the process group."""
+
+    def __init__(self, group, rank: int, world: int, device, max_bytes: int):
+        import torch.distributed._symmetric_memory as symm_mem
+        from ..ops import _lib
+        from ..ops._lib import I, L, P
+        _lib.register_signature("xllm_a2a_permute", [P, P, P, L, L, L, P, P, I, I, I, I, I, I, I, P])
+        self.group, self.rank, self.world, self.device = group, rank, world, device
+        self.half = (int(max_bytes) + 255) & ~255
+        self.buf = symm_mem.empty(2 * self.half, dtype=torch.uint8, device=device)
+        self.hdl = symm_mem.rendezvous(self.buf, group)
+        self.peer_ptrs = self.hdl.buffer_ptrs_dev
+        self.signal_ptrs = self.hdl.signal_pad_ptrs_dev
+        self.sig_off = self.hdl.signal_pad_size // 8 + 160       # its own 32-slot group in the upper half of the pad
+        self.state = torch.zeros(2, dtype=torch.int32, device=device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=device)
+        self.calls = 0
+        self.hdl.barrier()
+
+    def __call__(self, x: torch.Tensor, scatter_dim: int, gather_dim: int) -> torch.Tensor:
+        ok = (x.dim() == 4 and x.dtype == torch.bfloat16 and (scatter_dim, gather_dim) in ((1, 2), (2, 1))
+              and x.shape[3] % 8 == 0 and x.numel() * 2 <= self.half)
+        if not ok:
+            parts = [p.contiguous() for p in x.chunk(self.world, dim=scatter_dim)]
+            recv = [torch.empty_like(parts[0]) for _ in range(self.world)]
+            dist.all_to_all(recv, parts, group=self.group)
+            return torch.cat(recv, dim=gather_dim)
+        from ..ops import _count, _lib
+        from ..ops._lib import check, ptr, stream
+        x = x.contiguous()
+        d0, d1, d2, E = x.shape
+        mode = 0 if scatter_dim == 1 else 1
+        check(_lib.load().xllm_a2a_permute(ptr(x), self.peer_ptrs, self.signal_ptrs, 0, self.half, self.sig_off,
+                                           ptr(self.state), ptr(self.err), d0, d1, d2, E, mode, self.rank, self.world,
+                                           stream()), "a2a_permute")
+        _count()
+        self.calls += 1
+        half = (self.calls & 1) * self.half               # the kernel's epoch is the call count
+        shape = (d0, d1 // self.world, d2 * self.world, E) if mode == 0 else (d0, d1 * self.world, d2 // self.world, E)
+        n = d0 * d1 * d2 * E
+        # copy out: the area is reused by the call after next
+        return self.buf[half: half + 2 * n].view(torch.bfloat16).view(shape).clone()
+
+    def error_status(self) -> int:
+        v = int(self.err.item())
+        if v:
+            self.err.zero_()
+        return v
+
+
 # ------------------------------------------------------------------------------------------ CFG parallel
 def cfg_combine(branch_out: torch.Tensor, st: DitParallelState, guidance_scale: float) -> torch.Tensor:
     """Every rank holds the prediction of ITS branch (cfg_rank 0: conditional, 1: unconditional);
