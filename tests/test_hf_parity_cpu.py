@@ -33,6 +33,13 @@ def _case(fam):
                                   n_shared_experts=1, first_k_dense_replace=1, n_group=2, topk_group=1, q_lora_rank=32,
                                   kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
                                   routed_scaling_factor=2.5), t.DeepseekV3ForCausalLM
+    if fam == "glm_moe_dsa":
+        # index_topk far below the prompt lengths: every step takes the sparse path
+        return t.GlmMoeDsaConfig(**dict(COMMON, num_key_value_heads=4), moe_intermediate_size=32, n_routed_experts=8, num_experts_per_tok=2,
+                                 n_shared_experts=1, mlp_layer_types=["dense", "sparse"], n_group=1, topk_group=1,
+                                 q_lora_rank=32, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                                 routed_scaling_factor=2.5, index_topk=6, index_head_dim=16, index_n_heads=4,
+                                 pad_token_id=0), t.GlmMoeDsaForCausalLM
     if fam == "glm4":
         return t.Glm4Config(**COMMON, head_dim=16, partial_rotary_factor=0.5, pad_token_id=0), t.Glm4ForCausalLM
     if fam == "glm4_moe":
@@ -47,7 +54,7 @@ def _case(fam):
 
 
 FAMILIES = ["llama", "mistral", "qwen2", "qwen3", "qwen3_moe", "deepseek_v3", "deepseek_v3_latent", "glm4", "glm4_moe",
-            "minimax_m2"]
+            "minimax_m2", "glm_moe_dsa"]
 
 
 @pytest.mark.parametrize("fam", FAMILIES)
@@ -57,6 +64,10 @@ def test_family_matches_huggingface(fam, tmp_path):
     except (AttributeError, TypeError) as e:      # this transformers build lacks the family
         pytest.skip(str(e))
     torch.manual_seed(0)
+    if fam == "glm_moe_dsa":
+        # the oracle must build its causal mask explicitly: with the fused-attention back end this family's
+        # indexer receives no mask at all and selects (and attends to) future tokens
+        cfg._attn_implementation = "eager"
     hf = cls(cfg).float().eval()
     with torch.no_grad():                         # norms away from 1 and biases away from 0, so that both matter
         for n, p in hf.named_parameters():

@@ -170,6 +170,8 @@ class LLMEngine:
                                   enable_graph=cfg.enable_graph and bool(getattr(self.model, "supports_graph", True)),
                                   graph_buckets=cfg.graph_buckets, kv_allocator=kv_allocator)
         self.runner.overlap = cfg.enable_schedule_overlap
+        if getattr(self.model, "needs_index_cache", False):
+            self.model.alloc_index_cache(num_blocks, cfg.block_size)
         if getattr(self.model, "needs_state", False):
             # one state slot per sequence that can hold KV at the same time; the scheduler admits no
             # more than that (max_running_seqs below), so a slot is always free when one is needed

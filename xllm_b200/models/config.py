@@ -60,6 +60,12 @@ class ModelArgs:
     qk_rope_head_dim: int = 0
     v_head_dim: int = 0
     mla_latent_cache: bool = False   # paged cache of [c_kv | k_pe] rows shared by all heads instead of per-head K/V
+    mla_rope_split_half: bool = False  # checkpoint rotates (x[:d/2], x[d/2:]) pairs; the kernels rotate adjacent pairs
+    # DSA (sparse attention through a lightweight indexer: DeepSeek-V3.2, GLM-5)
+    index_n_heads: int = 0
+    index_head_dim: int = 0
+    index_topk: int = 0
+    indexer_rope_interleave: bool = False
     # multi-token prediction
     num_nextn_predict_layers: int = 0
     # quantisation (from `quantization_config`)
@@ -154,7 +160,11 @@ def model_args_from_dict(cfg: Dict[str, Any]) -> ModelArgs:
     a.first_k_dense_replace = _g(text, "first_k_dense_replace", default=0)
     a.moe_layer_freq = _g(text, "moe_layer_freq", "decoder_sparse_step", default=1)
     a.mlp_only_layers = list(_g(text, "mlp_only_layers", default=[]))
-    _v3_like = base in ("deepseek_v3", "deepseek_v32", "glm4_moe", "minimax_m2", "kimi_k2")
+    _v3_like = base in ("deepseek_v3", "deepseek_v32", "glm4_moe", "glm_moe_dsa", "minimax_m2", "kimi_k2")
+    lt = _g(text, "mlp_layer_types", default=None)      # per-layer "dense" / "sparse" instead of first_k_dense_replace
+    if isinstance(lt, list) and lt:
+        a.mlp_only_layers = [i for i, t in enumerate(lt) if t == "dense"]
+        a.first_k_dense_replace = 0
     a.scoring_func = _g(text, "scoring_func", default="sigmoid" if _v3_like else "softmax")
     a.n_group = _g(text, "n_group", default=1) or 1
     a.topk_group = _g(text, "topk_group", default=1) or 1
@@ -169,6 +179,15 @@ def model_args_from_dict(cfg: Dict[str, Any]) -> ModelArgs:
     a.qk_rope_head_dim = _g(text, "qk_rope_head_dim", default=0)
     a.v_head_dim = _g(text, "v_head_dim", default=0)
     a.num_nextn_predict_layers = _g(text, "num_nextn_predict_layers", default=0)
+    if base in ("deepseek_v32", "glm_moe_dsa"):
+        a.index_n_heads = int(_g(text, "index_n_heads", default=64 if base == "deepseek_v32" else 32))
+        a.index_head_dim = int(_g(text, "index_head_dim", default=128))
+        a.index_topk = int(_g(text, "index_topk", default=2048))
+        # DeepSeek-V3.2 rotates adjacent pairs in attention and halves in the indexer; the GLM
+        # checkpoints (as HuggingFace runs them) rotate halves in both
+        a.mla_rope_split_half = bool(_g(text, "rope_interleave", default=base == "deepseek_v32")) is False
+        a.indexer_rope_interleave = bool(_g(text, "indexer_rope_interleave", default=False))
+        a.mla_latent_cache = True            # sparse selection gathers rows of the latent cache
     q = cfg.get("quantization_config") or text.get("quantization_config")
     if q:
         a.quant_method = q.get("quant_method", "")

@@ -38,6 +38,99 @@ def _yarn_mscale(scale, mscale):
     return 1.0 if scale <= 1 else 0.1 * mscale * math.log(scale) + 1.0
 
 
+def _pairs_from_halves(w: torch.Tensor, start: int, width: int, period: int) -> torch.Tensor:
+    """Reorders output rows of a projection so that a rotary embedding over (x[i], x[i + width/2])
+    pairs becomes one over adjacent pairs: in every block of `period` rows, the `width` rows from
+    `start` on are permuted new[2i] = old[i], new[2i+1] = old[i + width/2].  Dot products between
+    vectors permuted the same way do not change."""
+    half = width // 2
+    perm = torch.empty(width, dtype=torch.long)
+    perm[0::2] = torch.arange(half)
+    perm[1::2] = torch.arange(half) + half
+    out = w.clone()
+    for b in range(0, w.shape[0], period):
+        out[b + start: b + start + width] = w[b + start: b + start + width][perm]
+    return out
+
+
+class DsaIndexer(Module):
+    """The lightweight indexer of DeepSeek sparse attention (DSA): per token one index key of
+    `index_head_dim` values (cached), per query `index_n_heads` index queries; the score of context
+    token t for query s is sum_h w[s,h] * relu(q[s,h] . k[t]) * d^-0.5, and attention only sees the
+    `index_topk` best-scored tokens.  Parity: xllm/models/llm/deepseek_v32.h, glm5.h (the indexer of
+    the reference's NPU layers) and HuggingFace's GlmMoeDsaIndexer, which the tests compare against."""
+
+    def __init__(self, args, dtype, device, rope):
+        super().__init__()
+        a = args
+        self.nh, self.d, self.rope_d, self.topk = a.index_n_heads, a.index_head_dim, a.qk_rope_head_dim, a.index_topk
+        self.rope = rope
+        self.interleave = bool(a.indexer_rope_interleave)
+        self.wq_b = self.add_module("wq_b", Linear(a.q_lora_rank, self.nh * self.d, False, dtype, device, None))
+        self.wk = self.add_module("wk", Linear(a.hidden_size, self.d, False, dtype, device, None))
+        self.k_norm_w = self.add_param("k_norm.weight", torch.ones(self.d, dtype=dtype, device=device))
+        self.k_norm_b = self.add_param("k_norm.bias", torch.zeros(self.d, dtype=dtype, device=device))
+        self.weights_proj = self.add_module("weights_proj", Linear(a.hidden_size, self.nh, False, dtype, device, None))
+        self.cache = None            # [n_slots, d]: index keys of every cached token (alloc_cache)
+
+    def alloc_cache(self, n_slots, dtype, device):
+        self.cache = torch.zeros(n_slots, self.d, dtype=dtype, device=device)
+
+    def _rope(self, v, positions):
+        """v [T, heads, rope_d]"""
+        half = self.rope_d // 2
+        cs = self.rope.cos_sin[positions.long()].float()
+        cos, sin = cs[:, None, :half], cs[:, None, half:]
+        vf = v.float()
+        if self.interleave:
+            x1, x2 = vf[..., 0::2], vf[..., 1::2]
+            return torch.stack([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).flatten(-2)
+        x1, x2 = vf[..., :half], vf[..., half:]
+        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+
+    def forward(self, x, q_resid, positions, meta: AttentionMetadata):
+        """Writes this step's index keys into the cache and returns (sel [T, k] int64 context positions,
+        padded with 0, n_sel [T] int32): the tokens every query row attends to.  k = min(index_topk,
+        longest context of the step)."""
+        T = x.shape[0]
+        q = self.wq_b(q_resid).view(T, self.nh, self.d).float()
+        q = torch.cat([self._rope(q[..., :self.rope_d], positions), q[..., self.rope_d:]], dim=-1)
+        k = torch.nn.functional.layer_norm(self.wk(x).float(), (self.d,), self.k_norm_w.float(), self.k_norm_b.float(), 1e-6)
+        k = torch.cat([self._rope(k[:, None, :self.rope_d], positions)[:, 0], k[:, self.rope_d:]], dim=-1)
+        ok = meta.slots >= 0
+        self.cache.index_copy_(0, meta.slots[ok].long(), k[ok].to(self.cache.dtype))
+        w = self.weights_proj(x).float() * (self.nh ** -0.5) * (self.d ** -0.5)        # [T, nh]
+        bt = meta.block_table.long()
+        P = self._page
+        kmax = min(self.topk, int(meta.max_kv_len) if meta.max_kv_len else int(meta.kv_lens.max()))
+        sel = torch.zeros(T, kmax, dtype=torch.long, device=x.device)
+        n_sel = torch.zeros(T, dtype=torch.int32, device=x.device)
+        cu = meta.cu_q.tolist()
+        lens = meta.kv_lens.tolist()
+        for s_idx in range(meta.n_seqs):
+            r0, r1, L = cu[s_idx], cu[s_idx + 1], lens[s_idx]
+            if r1 <= r0 or L <= 0:
+                continue
+            pos_all = torch.arange(L, device=x.device)
+            slots = bt[s_idx, pos_all // P] * P + pos_all % P
+            keys = self.cache[slots].float()                                              # [L, d]
+            sc = torch.einsum("shd,td->sht", q[r0:r1], keys)
+            sc = (torch.relu(sc) * w[r0:r1, :, None]).sum(1)                              # [rows, L]
+            qpos = positions[r0:r1].long()
+            sc = sc.masked_fill(pos_all[None, :] > qpos[:, None], float("-inf"))
+            kk = min(kmax, L)
+            top = sc.topk(kk, dim=-1)
+            valid = torch.isfinite(top.values)
+            sel[r0:r1, :kk] = torch.where(valid, top.indices, torch.zeros_like(top.indices))
+            n_sel[r0:r1] = valid.sum(-1).to(torch.int32)
+            # selected-but-masked entries (rows whose context is shorter than kk) sort last: compact is implied
+            # because topk returns finite scores first
+        return sel, n_sel
+
+    __call__ = forward
+    _page = 16
+
+
 class MLAAttention(Module):
     def __init__(self, args, layer_idx, dtype, device, ps=None, rope=None):
         super().__init__()
@@ -78,6 +171,22 @@ class MLAAttention(Module):
         self.latent = bool(getattr(args, "mla_latent_cache", False))
         if self.latent:
             self.nkv, self.d = 1, self.kv_lora + self.rope_d
+        self.split_half = bool(getattr(args, "mla_rope_split_half", False))
+        self.indexer = None
+        if getattr(args, "index_topk", 0) > 0:
+            assert self.latent and self.q_lora and tp == 1, "DSA runs on the latent cache, with q_lora, without TP"
+            self.indexer = self.add_module("indexer", DsaIndexer(args, dtype, device, rope))
+
+    def named_loaders(self, prefix=""):
+        """Checkpoints whose rotary embedding pairs (x[i], x[i + d/2]) get the rope rows of their q and
+        k_pe projections reordered at load, so that the adjacent-pair kernels compute the same dot products."""
+        for n, f in super().named_loaders(prefix):
+            if self.split_half and n.endswith(("q_b_proj.weight", "q_proj.weight")):
+                yield n, (lambda w, f=f: f(_pairs_from_halves(w, self.nope, self.rope_d, self.qk_d)))
+            elif self.split_half and n.endswith("kv_a_proj_with_mqa.weight"):
+                yield n, (lambda w, f=f: f(_pairs_from_halves(w, self.kv_lora, self.rope_d, self.kv_lora + self.rope_d)))
+            else:
+                yield n, f
 
     # ------------------------------------------------------------------ latent-cache form
     def _rope(self, v, positions):
@@ -95,8 +204,10 @@ class MLAAttention(Module):
         embeddings and the attention are kernels of ops.mla; nothing is read back to the host."""
         from ..ops import mla as mla_ops
         T, nh, L, r = x.shape[0], self.nh, self.kv_lora, self.rope_d
+        q_resid = None
         if self.q_lora:
-            q = self.q_b_proj(self.q_a_layernorm(self.q_a_proj(x)))
+            q_resid = self.q_a_layernorm(self.q_a_proj(x))
+            q = self.q_b_proj(q_resid)
         else:
             q = self.q_proj(x)
         q = q.view(T, nh, self.qk_d)
@@ -109,6 +220,12 @@ class MLAAttention(Module):
                             meta.slots, cache, q[..., self.nope:], q_cat)
         o_lat = torch.empty((T, nh, L), dtype=x.dtype, device=x.device)
         nd = meta.n_decode
+        if self.indexer is not None:
+            self.indexer._page = cache.shape[-2]
+            sel, n_sel = self.indexer(x, q_resid, positions, meta)
+            self._sparse_attend(q_cat, cache, meta, positions, sel, n_sel, o_lat)
+            out = torch.einsum("thl,hvl->thv", o_lat, w_uv)
+            return self.o_proj(out.reshape(T, nh * self.vd))
         if nd > 0:                                            # one query token per sequence
             mla_ops.decode(q_cat[:nd], cache, meta.block_table, self.scale, seq_lens=meta.kv_lens[:nd], out=o_lat[:nd],
                            latent=L)
@@ -120,6 +237,31 @@ class MLAAttention(Module):
                            bt_rows=(seq + nd).to(torch.int32), out=o_lat[nd:], latent=L)
         out = torch.einsum("thl,hvl->thv", o_lat, w_uv)
         return self.o_proj(out.reshape(T, nh * self.vd))
+
+    def _sparse_attend(self, q_cat, cache, meta, positions, sel, n_sel, o_lat):
+        """Attention of every query row over ITS selected context tokens: their latent rows are gathered
+        into scratch pages (one run of pages per row) and the MLA kernel runs over those, with the
+        number of selected tokens as the row's length.  Rows are processed in groups that keep the
+        scratch under 256 MB."""
+        from ..ops import mla as mla_ops
+        T, k = sel.shape
+        W = cache.shape[-1]
+        page = cache.shape[-2]
+        kpad = (k + page - 1) // page * page
+        rows_cache = cache.view(-1, W)
+        tok = torch.arange(T, device=q_cat.device)
+        seq = torch.bucketize(tok, meta.cu_q[1:].contiguous().long(), right=True).clamp_(max=meta.n_seqs - 1)
+        bt = meta.block_table.long()
+        slots = bt[seq[:, None], sel // page] * page + sel % page                     # [T, k] cache slots
+        group = max(1, (256 << 20) // (kpad * W * cache.element_size()))
+        for a in range(0, T, group):
+            b = min(T, a + group)
+            n = b - a
+            scratch = torch.zeros(n * kpad // page, page, W, dtype=cache.dtype, device=cache.device)
+            scratch.view(n, kpad, W)[:, :k] = rows_cache[slots[a:b]]
+            bt_s = torch.arange(n * kpad // page, dtype=torch.int32, device=cache.device).view(n, kpad // page)
+            mla_ops.decode(q_cat[a:b], scratch, bt_s, self.scale, seq_lens=n_sel[a:b].contiguous(), out=o_lat[a:b],
+                           latent=self.kv_lora)
 
     def forward(self, x, positions, meta: AttentionMetadata, k_cache, v_cache):
         if self.latent:
@@ -211,9 +353,21 @@ class DeepseekCausalLM(DenseCausalLM):
     @property
     def supports_graph(self):
         """The latent-cache kernels exist for DeepSeek's widths (512 + 64); other widths run the
-        tensor-op form, which reads lengths on the host and therefore cannot be captured."""
+        tensor-op form, which reads lengths on the host and therefore cannot be captured.  The DSA
+        indexer sizes its selection from the step's lengths on the host: eager as well."""
         att = self.layers[0].self_attn
+        if att.indexer is not None:
+            return False
         return not att.latent or (self.args.kv_lora_rank == 512 and self.args.qk_rope_head_dim == 64)
+
+    @property
+    def needs_index_cache(self):
+        return self.layers[0].self_attn.indexer is not None
+
+    def alloc_index_cache(self, num_blocks: int, block_size: int):
+        """Index keys of the DSA indexer: one [slots, index_head_dim] tensor per layer beside the KV cache."""
+        for layer in self.layers:
+            layer.self_attn.indexer.alloc_cache(num_blocks * block_size, self.dtype, self.device)
 
 
 class MTPDraft(Module):
@@ -258,8 +412,11 @@ class MTPDraft(Module):
         return self.lm_head(hidden_rows)
 
 
-# DeepSeek-V3.2 is not registered: its sparse attention (the DSA indexer) is not implemented, and running
-# such a checkpoint with dense attention would silently compute something else.
-@register_model("deepseek_v2", "deepseek_v3", "kimi_k2", "DeepseekV2ForCausalLM", "DeepseekV3ForCausalLM")
+# DeepSeek-V3.2 and GLM-5 (`glm_moe_dsa`) are this decoder with the DSA indexer in every attention layer
+# (ModelArgs.index_topk > 0); JoyAI-LLM-Flash is the DeepSeek-V2 decoder under another name
+# (xllm/models/llm/deepseek_v32.h, glm5.h, joyai_llm_flash.h).
+@register_model("deepseek_v2", "deepseek_v3", "kimi_k2", "DeepseekV2ForCausalLM", "DeepseekV3ForCausalLM",
+                "deepseek_v32", "DeepseekV32ForCausalLM", "glm_moe_dsa", "GlmMoeDsaForCausalLM",
+                "joyai_llm_flash", "JoyAILLMFlashForCausalLM")
 def build_deepseek(args, dtype, device, ps):
     return DeepseekCausalLM(args, dtype, device, ps)
