@@ -19,7 +19,7 @@ def test_log_softmax(dtype, rows, V):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("rows,V,k", [(4, 151936, 1), (4, 151936, 20), (3, 32000, 128), (2, 8192, 1024), (5, 777, 777),
+@pytest.mark.parametrize("rows,V,k", [(4, 151936, 1), (4, 151936, 20), (3, 32000, 128), (2, 8192, 1024), (2, 40000, 2048), (5, 777, 777),
                                       (2, 65536, 300)])
 def test_radix_topk_matches_stable_sort(dtype, rows, V, k):
     torch.manual_seed(1)

@@ -26,7 +26,7 @@
 namespace xllm {
 
 constexpr int kTopkThreads = 1024;
-constexpr int kTopkMax = 1024;
+constexpr int kTopkMax = 2048;   // the DSA indexer keeps 2048 context tokens per query
 
 template <typename T> __device__ __forceinline__ float beam_ld(const T* x, int64_t i);
 template <> __device__ __forceinline__ float beam_ld<float>(const float* x, int64_t i) { return x[i]; }
@@ -233,7 +233,7 @@ XLLM_API int xllm_log_softmax(const void* x, int64_t row_stride, int dtype, int 
 }
 
 // The k largest entries of every row, sorted descending (ties: lowest index first).  normalize != 0:
-// values are log-probabilities of the row.  1 <= k <= min(V, 1024), V < 2^24.
+// values are log-probabilities of the row.  1 <= k <= min(V, 2048), V < 2^24.
 XLLM_API int xllm_radix_topk(const void* x, int64_t row_stride, int dtype, int rows, int V, int k, int normalize,
                              void* out_vals, void* out_ids, void* stream) {
   using namespace xllm;
@@ -249,7 +249,7 @@ XLLM_API int xllm_radix_topk(const void* x, int64_t row_stride, int dtype, int r
   return XLLM_LAUNCH_CHECK();
 }
 
-// The n_out best of W x k candidates per request.  n_out <= min(W * k, 1024).
+// The n_out best of W x k candidates per request.  n_out <= min(W * k, 2048).
 XLLM_API int xllm_beam_step(const void* cand_lp, const void* cand_ids, const void* cum, int B, int W, int k, int n_out,
                             void* out_token, void* out_parent, void* out_score, void* stream) {
   using namespace xllm;

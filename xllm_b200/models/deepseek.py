@@ -119,9 +119,15 @@ class DsaIndexer(Module):
             qpos = positions[r0:r1].long()
             sc = sc.masked_fill(pos_all[None, :] > qpos[:, None], float("-inf"))
             kk = min(kmax, L)
-            top = sc.topk(kk, dim=-1)
-            valid = torch.isfinite(top.values)
-            sel[r0:r1, :kk] = torch.where(valid, top.indices, torch.zeros_like(top.indices))
+            if sc.is_cuda:
+                from ..ops import select
+                top_v, top_i = select.topk(sc.contiguous(), kk)          # radix selection kernel
+                top_i = top_i.long()
+            else:
+                top = sc.topk(kk, dim=-1)
+                top_v, top_i = top.values, top.indices
+            valid = torch.isfinite(top_v)
+            sel[r0:r1, :kk] = torch.where(valid, top_i, torch.zeros_like(top_i))
             n_sel[r0:r1] = valid.sum(-1).to(torch.int32)
             # selected-but-masked entries (rows whose context is shorter than kk) sort last: compact is implied
             # because topk returns finite scores first

@@ -17,7 +17,7 @@ _lib.register_signature("xllm_log_softmax", [P, L, I, I, I, P, P])
 _lib.register_signature("xllm_radix_topk", [P, L, I, I, I, I, I, P, P, P])
 _lib.register_signature("xllm_beam_step", [P, P, P, I, I, I, I, P, P, P, P])
 
-MAX_K = 1024
+MAX_K = 2048
 
 
 def _dtype_code(x):
