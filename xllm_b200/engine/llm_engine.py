@@ -224,10 +224,18 @@ class LLMEngine:
                 raise ValueError("speculative decoding needs enable_schedule_overlap=False: the number of tokens "
                                  "a step appends is only known after verification")
             from .speculative import SpecDecoder, make_drafter
+            if getattr(self.model, "needs_state", False):
+                raise ValueError("speculative decoding on a model with recurrent state needs a state rollback for "
+                                 "rejected drafts, which is not implemented; run this model without it")
             if cfg.speculative_method == "mtp":
                 from ..models.deepseek import MTPDraft
                 self.mtp = MTPDraft(self.args, self.model, self.dtype, self.device, self.ps)
-                self.mtp.init_random(seed=cfg.seed + 17)   # replaced by load_weights() for real checkpoints
+                self.mtp.init_random(seed=cfg.seed + 17)
+                src = cfg.draft_model if (cfg.draft_model and os.path.isdir(cfg.draft_model)) else cfg.model
+                if os.path.isdir(src) and not cfg.random_weights:
+                    # the MTP layer ships inside the target's checkpoint (or in a directory exported from it)
+                    from ..utils.loader import iterate_weights
+                    self.mtp_tensors_loaded = self.mtp.load_from_checkpoint(iterate_weights(src), strict=False)
             elif cfg.speculative_method == "eagle3":
                 from ..models.eagle3 import Eagle3Draft, aux_layer_ids
                 self.model.aux_layers = aux_layer_ids(self.args.num_hidden_layers)

@@ -376,42 +376,120 @@ class DeepseekCausalLM(DenseCausalLM):
             layer.self_attn.indexer.alloc_cache(num_blocks * block_size, self.dtype, self.device)
 
 
-class MTPDraft(Module):
-    """One multi-token-prediction layer (DeepSeek-V3 `num_nextn_predict_layers`): the draft for
-    position t+2 is computed from the target's hidden state at t and the embedding of token t+1:
-    h' = layer(eh_proj([enorm(embed(tok)), hnorm(h)])) ; logits = shared_head(norm(h')).
-    Parity: xllm/models/llm/deepseek_mtp.h, runtime/mtp_worker_impl.cpp:1245-1850."""
+# How each family spells its multi-token-prediction layer: module names, order of the two halves of the
+# projection input, where the layer lives in the checkpoint.
+MTP_KINDS = {
+    # DeepSeek-V3 / GLM-4.5 / GLM-5: an extra decoder layer after the last one (deepseek_mtp.h, mtp_model_base.h)
+    "deepseek": dict(enorm="enorm", hnorm="hnorm", proj="eh_proj", order="eh", final="shared_head.norm",
+                     prefix=lambda a: f"model.layers.{a.num_hidden_layers}.", layer_prefix="", mask_first=False),
+    # MiMo: `model.mtp_layers.N.*`, input = [hidden | token] (mimo_mtp.h)
+    "mimo": dict(enorm="token_layernorm", hnorm="hidden_layernorm", proj="input_proj", order="he", final="final_layernorm",
+                 prefix=lambda a: "model.mtp_layers.0.", layer_prefix="", mask_first=True),
+    # Qwen3.5 / Qwen3-Next: `mtp.*` with the layer under `mtp.layers.0.` (qwen3_5_mtp_base.h)
+    "qwen3_5": dict(enorm="pre_fc_norm_embedding", hnorm="pre_fc_norm_hidden", proj="fc", order="eh", final="norm",
+                    prefix=lambda a: "mtp.", layer_prefix="layers.0.", mask_first=False),
+}
 
-    def __init__(self, args, target: DeepseekCausalLM, dtype, device, ps=None, layer_cls=None):
+
+def mtp_kind_of(args) -> str:
+    mt = args.model_type.lower()
+    if mt.startswith("mimo"):
+        return "mimo"
+    if mt.startswith("qwen3_5") or mt.startswith("qwen3_next"):
+        return "qwen3_5"
+    return "deepseek"
+
+
+class MTPDraft(Module):
+    """One multi-token-prediction layer: the draft for position t+2 is computed from the target's
+    hidden state at t and the embedding of token t+1:
+    h' = layer(proj([norm_e(embed(tok)), norm_h(h)])) ; logits = lm_head(final_norm(h')),
+    with the embedding and the lm_head shared with the target.  `kind` selects the family's spelling
+    (MTP_KINDS); the layer itself is the family's decoder layer.
+    Parity: xllm/models/llm/deepseek_mtp.h, mimo_mtp.h, qwen3_5_mtp.h, runtime/mtp_worker_impl.cpp:1245-1850."""
+
+    def __init__(self, args, target, dtype, device, ps=None, layer_cls=None, kind: str = None):
         super().__init__()
         self.args = args
         self.ps = ps or single()
+        self.kind = kind or mtp_kind_of(args)
+        k = self.spec = MTP_KINDS[self.kind]
         self.embed = target.embed          # shared with the target model
         self.lm_head = target.lm_head
         H = args.hidden_size
-        self.enorm = self.add_module("enorm", RMSNorm(H, args.rms_norm_eps, dtype, device))
-        self.hnorm = self.add_module("hnorm", RMSNorm(H, args.rms_norm_eps, dtype, device))
-        self.eh_proj = self.add_module("eh_proj", Linear(2 * H, H, False, dtype, device, self.ps))
-        mlp = SparseMoeBlock(args, dtype, device, self.ps) if args.num_experts > 0 else \
-            DenseMLP(H, args.intermediate_size, args.hidden_act, dtype, device, self.ps)
-        if layer_cls is None:
-            self.layer = self.add_module("layer", DeepseekDecoderLayer(args, 0, dtype, device, self.ps, target.rope, mlp))
+        gemma = self.kind == "qwen3_5"     # zero-centred norm weights
+        self.enorm = self.add_module(k["enorm"], RMSNorm(H, args.rms_norm_eps, dtype, device, gemma=gemma))
+        self.hnorm = self.add_module(k["hnorm"], RMSNorm(H, args.rms_norm_eps, dtype, device, gemma=gemma))
+        self.eh_proj = self.add_module(k["proj"], Linear(2 * H, H, False, dtype, device, self.ps))
+        rope = target.rope
+        if self.kind == "deepseek" and layer_cls is None and args.kv_lora_rank:
+            mlp = SparseMoeBlock(args, dtype, device, self.ps) if args.num_experts > 0 else \
+                DenseMLP(H, args.intermediate_size, args.hidden_act, dtype, device, self.ps)
+            self.layer = self.add_module("layer", DeepseekDecoderLayer(args, 0, dtype, device, self.ps, rope, mlp))
+        elif self.kind == "qwen3_5" and layer_cls is None:
+            from .qwen3_next import NextDecoderLayer
+            a = target.args                 # the target's completed arguments (layer types, projections)
+            full = next(i for i, t in enumerate(a.extra["layer_types"]) if t != "linear_attention")
+            mlp = SparseMoeBlock(a, dtype, device, self.ps) if a.num_experts > 0 else \
+                DenseMLP(H, a.intermediate_size, a.hidden_act, dtype, device, self.ps, fuse_reduce=False)
+            self.layer = self.add_module("layer", NextDecoderLayer(a, full, dtype, device, self.ps, rope, mlp))
+            self.layer.mixer.q_norm.gemma = self.layer.mixer.k_norm.gemma = True
         else:
-            self.layer = self.add_module("layer", layer_cls(args, 0, dtype, device, self.ps, target.rope, mlp))
-        self.norm = self.add_module("shared_head.norm", RMSNorm(H, args.rms_norm_eps, dtype, device))
+            mlp = SparseMoeBlock(args, dtype, device, self.ps) if args.num_experts > 0 else \
+                DenseMLP(H, args.intermediate_size, args.hidden_act, dtype, device, self.ps)
+            cls = layer_cls or DecoderLayer
+            self.layer = self.add_module("layer", cls(args, 0, dtype, device, self.ps, rope, mlp))
+        self.norm = self.add_module(k["final"], RMSNorm(H, args.rms_norm_eps, dtype, device, gemma=gemma))
+
+    def checkpoint_name(self, name: str) -> str:
+        """Name of parameter `name` of this module in the family's checkpoint."""
+        k = self.spec
+        prefix = k["prefix"](self.args)
+        if name.startswith("layer."):
+            return prefix + k["layer_prefix"] + name[len("layer."):]
+        return prefix + name
+
+    def load_from_checkpoint(self, weights, strict: bool = True) -> int:
+        """Picks the MTP tensors out of a checkpoint's (name, tensor) stream; the shared embedding and
+        head copies some checkpoints carry beside them are skipped.  Returns the number of tensors used."""
+        k = self.spec
+        prefix = k["prefix"](self.args)
+        top = {k["enorm"], k["hnorm"], k["proj"], k["final"].split(".")[0]}
+        mapped = []
+        for name, w in weights:
+            if not name.startswith(prefix):
+                continue
+            n = name[len(prefix):]
+            head = n.split(".")[0]
+            if head in ("embed_tokens",) or n.startswith("shared_head.head"):
+                continue
+            if head in top:
+                mapped.append((n, w))
+            elif k["layer_prefix"] and n.startswith(k["layer_prefix"]):
+                mapped.append(("layer." + n[len(k["layer_prefix"]):], w))
+            elif not k["layer_prefix"]:
+                mapped.append(("layer." + n, w))
+        if mapped:
+            self.load_weights(mapped, strict=strict)
+        return len(mapped)
 
     def forward(self, tokens, prev_hidden, positions, meta, k_cache, v_cache):
         comm = self.ps.comm
         if comm is not None and tokens.is_cuda:
             comm.begin_forward(tokens.shape[0])
-        e = self.enorm(self.embed(tokens))
+        emb = self.embed(tokens)
+        if self.spec["mask_first"]:          # the embedding at position 0 has no predecessor state
+            emb = emb.masked_fill((positions == 0)[:, None], 0)
+        e = self.enorm(emb)
         h = self.hnorm(prev_hidden)
-        x = self.eh_proj(torch.cat([e, h], dim=-1))
+        x = self.eh_proj(torch.cat([e, h] if self.spec["order"] == "eh" else [h, e], dim=-1))
         y, residual = self.layer(x, None, positions, meta, k_cache, v_cache)
-        if comm is not None and x.is_cuda:
+        if comm is not None and x.is_cuda and self.kind == "deepseek":
             h = comm.allreduce_norm(x.shape[0], residual, self.norm.weight, self.norm.eps)
             comm.end_forward()
             return h
+        if comm is not None and x.is_cuda:
+            comm.end_forward()
         return self.norm(y, residual=residual)
 
     def logits(self, hidden_rows):
