@@ -9,6 +9,7 @@
 #include <pybind11/stl.h>
 
 #include "block_manager.h"
+#include "block_managers_ext.h"
 #include "scheduler.h"
 #include "sequence.h"
 
@@ -69,6 +70,47 @@ PYBIND11_MODULE(_rt, m) {
       .def_property_readonly("block_size", &BlockManager::block_size)
       .def_property_readonly("num_blocks", &BlockManager::num_blocks)
       .def("stats", &BlockManager::stats);
+
+  py::class_<SlidingWindowBlockManager>(m, "SlidingWindowBlockManager")
+      .def(py::init<int32_t, int32_t, int32_t>(), py::arg("num_blocks"), py::arg("block_size"), py::arg("window"))
+      .def("grow",
+           [](SlidingWindowBlockManager& bm, std::vector<int32_t> table, int32_t n_tokens) {
+             const bool ok = bm.grow(table, n_tokens);
+             return py::make_tuple(ok, table);
+           })
+      .def("release", [](SlidingWindowBlockManager& bm, std::vector<int32_t> table) { bm.release(table); })
+      .def_property_readonly("max_blocks_per_sequence", &SlidingWindowBlockManager::max_blocks_per_sequence)
+      .def_property_readonly("num_free_blocks", &SlidingWindowBlockManager::num_free_blocks)
+      .def_property_readonly("num_used_blocks", &SlidingWindowBlockManager::num_used_blocks)
+      .def_property_readonly("window", &SlidingWindowBlockManager::window);
+
+  py::class_<CompositeBlockManager>(m, "CompositeBlockManager")
+      .def(py::init<>())
+      .def("add_pool", &CompositeBlockManager::add_pool, py::arg("name"), py::arg("num_blocks"), py::arg("block_size"),
+           py::arg("prefix_cache") = false)
+      .def("pool", &CompositeBlockManager::pool, py::return_value_policy::reference_internal)
+      .def("names", &CompositeBlockManager::names)
+      .def("allocate", &CompositeBlockManager::allocate)
+      .def("free", &CompositeBlockManager::free)
+      .def_property_readonly("utilization", &CompositeBlockManager::utilization);
+
+  py::class_<EmbeddingBlockManager>(m, "EmbeddingBlockManager")
+      .def(py::init<int32_t>(), py::arg("max_in_flight"))
+      .def("allocate", &EmbeddingBlockManager::allocate)
+      .def("free", &EmbeddingBlockManager::free)
+      .def_property_readonly("num_in_flight", &EmbeddingBlockManager::num_in_flight)
+      .def_property_readonly("capacity", &EmbeddingBlockManager::capacity);
+
+  py::class_<ConcurrentBlockManager>(m, "ConcurrentBlockManager")
+      .def(py::init<int32_t, int32_t, bool>(), py::arg("num_blocks"), py::arg("block_size"), py::arg("prefix_cache") = true)
+      .def("allocate", &ConcurrentBlockManager::allocate, py::call_guard<py::gil_scoped_release>())
+      .def("free", &ConcurrentBlockManager::free_blocks, py::call_guard<py::gil_scoped_release>())
+      .def("match_prefix", &ConcurrentBlockManager::match_prefix, py::arg("tokens"), py::arg("extra") = 0,
+           py::call_guard<py::gil_scoped_release>())
+      .def("cache_blocks", &ConcurrentBlockManager::cache_blocks, py::arg("tokens"), py::arg("blocks"),
+           py::arg("start_block") = 0, py::arg("extra") = 0, py::call_guard<py::gil_scoped_release>())
+      .def_property_readonly("num_free_blocks", &ConcurrentBlockManager::num_free_blocks)
+      .def_property_readonly("num_used_blocks", &ConcurrentBlockManager::num_used_blocks);
 
   m.def("block_hash_chain", [](const std::vector<int32_t>& toks, int32_t block_size, uint64_t extra) {
     std::vector<std::pair<uint64_t, uint64_t>> out;
