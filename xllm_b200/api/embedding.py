@@ -30,7 +30,7 @@ def hidden_states(engine, ids: List[int]) -> torch.Tensor:
         kv_lens=torch.tensor([T], dtype=torch.int32, device=dev),
         cu_q=torch.tensor([0, T], dtype=torch.int32, device=dev), max_q_len=T, max_kv_len=T)
     if getattr(model, "needs_state", False):        # linear-attention layers: a scratch state slot, reset for this pass
-        meta.state_slots = torch.tensor([model.state.conv.shape[1] - 1], dtype=torch.long, device=dev)
+        meta.state_slots = torch.tensor([model.state.n_slots - 1], dtype=torch.long, device=dev)
         meta.state_fresh, meta.seq_bounds = [True], [(0, T)]
     return model.forward(torch.tensor(ids, dtype=torch.int64, device=dev), torch.arange(T, device=dev), meta, kv)
 

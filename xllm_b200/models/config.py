@@ -179,6 +179,16 @@ def model_args_from_dict(cfg: Dict[str, Any]) -> ModelArgs:
     a.qk_rope_head_dim = _g(text, "qk_rope_head_dim", default=0)
     a.v_head_dim = _g(text, "v_head_dim", default=0)
     a.num_nextn_predict_layers = _g(text, "num_nextn_predict_layers", default=0)
+    if base == "rwkv7":
+        # attention-free: heads of `head_size` channels, a 4x channel-mix unless the config says otherwise
+        a.head_dim = int(_g(text, "head_size", "head_dim", default=64))
+        a.num_attention_heads = int(_g(text, "num_attention_heads", "num_heads", default=a.hidden_size // a.head_dim))
+        a.num_key_value_heads = a.num_attention_heads
+        a.intermediate_size = int(_g(text, "intermediate_size", default=4 * a.hidden_size) or 4 * a.hidden_size)
+        for key in ("layer_norm_eps", "decay_low_rank_dim", "a_low_rank_dim", "v_low_rank_dim", "gate_low_rank_dim",
+                    "group_norm_eps"):
+            if text.get(key) is not None:
+                a.extra[key] = text[key]
     if base in ("deepseek_v32", "glm_moe_dsa"):
         a.index_n_heads = int(_g(text, "index_n_heads", default=64 if base == "deepseek_v32" else 32))
         a.index_head_dim = int(_g(text, "index_head_dim", default=128))

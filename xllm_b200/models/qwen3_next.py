@@ -41,6 +41,7 @@ class LinearStateCache:
         self.rec = torch.zeros(n_layers, slots, nv, dk, dv, dtype=torch.float32, device=device)
         self.free = list(range(slots - 1, -1, -1))
         self.owner = {}
+        self.n_slots = slots
 
     def slot_of(self, request_id):
         s = self.owner.get(request_id)
