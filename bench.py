@@ -396,6 +396,8 @@ def run(args):
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(gpu_launches), "graph_replays": int(graph_replays),
             "h2d_bytes_per_step": h2d_step, "d2h_bytes_per_step": d2h_step,
         }
+        line["vs_library"] = _vs_library(args.config, world, n_req_total, in_len, out_len, conc_total,
+                                         e2e.get("value") if isinstance(e2e, dict) else None)
         print(json.dumps(line), flush=True)
     if world > 1:
         # Every collective of this process finished behind the barrier that closed the last timed
@@ -433,6 +435,24 @@ def profile_steps(eng, step, submit_more, n, rank):
         for name, (us, k) in sorted(per.items(), key=lambda kv: -kv[1][0])[:24]:
             print(f"{us / 1e3 / n:8.3f} ms/step {100 * us / total:5.1f}%  n/step {k / n:7.1f}  avg {us / k:8.1f} us  "
                   f"{name[:100]}", file=sys.stderr)
+
+
+def _vs_library(config, n_gpus, requests, in_len, out_len, conc, e2e_value):
+    """End-to-end value over the LIBRARY arm's measured value for the same workload
+    (baseline/library_results.json, filled from `bench.py --impl library` runs), or None."""
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "library_results.json")
+    if e2e_value is None or not os.path.exists(path):
+        return None
+    try:
+        with open(path) as f:
+            rows = json.load(f)["results"]
+    except (OSError, ValueError, KeyError):
+        return None
+    for r in rows:
+        if (str(r.get("config")) == str(config) and r.get("n_gpus") == n_gpus and r.get("requests") == requests
+                and r.get("input_len") == in_len and r.get("output_len") == out_len and r.get("concurrency") == conc):
+            return round(float(e2e_value) / float(r["value"]), 4)
+    return None
 
 
 def run_library(args):
