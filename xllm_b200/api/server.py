@@ -192,13 +192,17 @@ class ApiServer:
             except Exception as e:
                 self._error(req.id, 500, f"{type(e).__name__}: {e}", "internal_error")
         # client went away: abort its request (frees its KV blocks at once)
-        for rid, call in list(self.calls.items()):
-            if self.http.is_disconnected(call.http_id):
-                (self.pd_prefill or self.engine).abort(rid)
-                self.calls.pop(rid, None)
-                if call.native:
-                    self._native_by_rid.pop(rid, None)
-                    self.rp.push([call.native], [0], [-1], [4], [""])
+        self._iter = getattr(self, "_iter", 0) + 1
+        if self.calls and self._iter % 8 == 0:           # every few iterations: one native call for all connections
+            gone = set(self.http.disconnected_among([c.http_id for c in self.calls.values()]))
+            if gone:
+                for rid, call in list(self.calls.items()):
+                    if call.http_id in gone:
+                        (self.pd_prefill or self.engine).abort(rid)
+                        self.calls.pop(rid, None)
+                        if call.native:
+                            self._native_by_rid.pop(rid, None)
+                            self.rp.push([call.native], [0], [-1], [4], [""])
         now = time.time()
         if now >= self._next_watch:            # expired bounded waits in kernels -> unhealthy
             self._next_watch = now + self.watch_interval_s
@@ -236,12 +240,16 @@ class ApiServer:
             for ev in events:
                 self._on_event(ev)
             return
+        if not isinstance(events, list):
+            events = list(events)
         h, si, tk, fl, rs = [], [], [], [], []
-        for ev in events:
+        for i in self.rp.push_events(events, self._native_by_rid):
+            ev = events[i]
             handle = self._native_by_rid.get(ev.request_id)
             if handle is None:
                 self._on_event(ev)
                 continue
+            # an event object of another kind (relayed from a decode instance, a re-labelled first token)
             aborted = ev.finish_reason == "abort" and ev.finished
             h.append(handle)
             si.append(int(ev.seq_index))

@@ -5,6 +5,7 @@
 #include "http_server.h"
 #include "metrics.h"
 #include "response_processor.h"
+#include "../runtime/scheduler.h"
 
 namespace py = pybind11;
 using namespace xllm;
@@ -30,6 +31,13 @@ void bind_server(py::module_& m) {
       .def("stream_send", &HttpServer::stream_send)
       .def("stream_end", &HttpServer::stream_end)
       .def("is_disconnected", &HttpServer::is_disconnected)
+      // the ids among `ids` whose connection is gone (one lock for all of them)
+      .def("disconnected_among", [](HttpServer& s, const std::vector<int64_t>& ids) {
+             std::vector<int64_t> gone;
+             for (int64_t id : ids)
+               if (s.is_disconnected(id)) gone.push_back(id);
+             return gone;
+           })
       .def("num_connections", &HttpServer::num_connections)
       .def_property_readonly("port", &HttpServer::port);
 
@@ -85,6 +93,45 @@ void bind_server(py::module_& m) {
              }
              py::gil_scoped_release rel;
              rp.push(std::move(ev));
+           })
+      // The engine's events as they come out of step(): those whose request id is in `handles` go to the
+      // workers, the indices of the others are returned (the caller formats them itself).  No per-event
+      // attribute access in the interpreter.
+      .def("push_events",
+           [](ResponseProcessor& rp, const py::list& events, const py::dict& handles) {
+             std::vector<RespEvent> ev;
+             std::vector<int64_t> rest;
+             ev.reserve(events.size());
+             int64_t i = 0;
+             for (const py::handle& h : events) {
+               const OutputEvent* e = nullptr;
+               try {
+                 e = &h.cast<const OutputEvent&>();
+               } catch (const py::cast_error&) {
+                 rest.push_back(i++);        // a wrapped event (first token of a disaggregated request, ...)
+                 continue;
+               }
+               py::object key = py::str(e->request_id);
+               if (!handles.contains(key)) {
+                 rest.push_back(i++);
+                 continue;
+               }
+               RespEvent r;
+               r.call = handles[key].cast<int64_t>();
+               r.seq_index = e->seq_index;
+               r.token = e->token;
+               r.finished = e->finished;
+               r.request_finished = e->request_finished;
+               r.aborted = e->finished && e->finish_reason == "abort";
+               if (e->finished) r.finish_reason = e->finish_reason;
+               ev.push_back(std::move(r));
+               ++i;
+             }
+             if (!ev.empty()) {
+               py::gil_scoped_release rel;
+               rp.push(std::move(ev));
+             }
+             return rest;
            })
       .def("take_done", &ResponseProcessor::take_done)
       .def("drain", &ResponseProcessor::drain, py::arg("timeout_ms") = 5000, py::call_guard<py::gil_scoped_release>())
