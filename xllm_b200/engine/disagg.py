@@ -158,6 +158,10 @@ class _FirstToken:
         self.finish_reason = ""
 
     def __getattr__(self, name):
+        # private and protocol names stay with the wrapper: forwarding them lets a binding layer that
+        # probes objects by attribute mistake the wrapper for the event it wraps
+        if name.startswith("_"):
+            raise AttributeError(name)
         return getattr(self._ev, name)
 
 
