@@ -95,3 +95,10 @@ def test_ulysses_all_to_all_over_peer_memory():
     out = _run("mp_ulysses_a2a.py", min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2)
     assert "ULYSSES_A2A_OK" in out
     print(out[out.index("ULYSSES_A2A_OK"):].splitlines()[0])
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_expert_replacement_moves_weights_between_gpus():
+    out = _run("mp_eplb.py", min(_ngpu(), 8) if _ngpu() in (2, 4, 8) else 2)
+    assert "EPLB_OK" in out
+    print(out[out.index("EPLB_OK"):].splitlines()[0])

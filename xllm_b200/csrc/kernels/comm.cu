@@ -814,6 +814,24 @@ XLLM_API int xllm_a2a_permute(const void* x, const void* peer_bufs, const void* 
   return XLLM_LAUNCH_CHECK();
 }
 
+// Plain copy of `nbytes` (multiple of 16, both pointers 16-byte aligned); either side may be peer-mapped
+// memory.  Used to pull expert weights from the rank that holds them (expert re-placement).
+namespace xllm {
+__global__ void __launch_bounds__(256) peer_copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+}  // namespace xllm
+
+XLLM_API int xllm_peer_copy(void* dst, const void* src, int64_t nbytes, void* stream) {
+  using namespace xllm;
+  if (nbytes == 0) return 0;
+  if ((nbytes & 15) || ((uintptr_t)dst & 15) || ((uintptr_t)src & 15)) return (int)cudaErrorInvalidValue;
+  const int64_t n = nbytes >> 4;
+  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(1184, (n + 255) / 256));
+  peer_copy_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((uint4*)dst, (const uint4*)src, n);
+  return XLLM_LAUNCH_CHECK();
+}
+
 // Number of uint32 flag slots one call site needs in the signal pad.
 XLLM_API int64_t xllm_tp_signal_slots(int world) { return (int64_t)world; }
 

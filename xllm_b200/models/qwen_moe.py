@@ -146,6 +146,23 @@ class SparseMoeBlock(Module):
             y = self.ps.all_reduce(y)
         return y
 
+    # ---- expert load balancing (parallel/eplb_gpu.py): with a store attached the layer counts the tokens
+    # every expert receives and its weights can move between the ranks
+    expert_store = None
+
+    def _load(self):
+        return self.expert_store.load if self.expert_store is not None else None
+
+    def enable_eplb(self):
+        """Collective over the expert-parallel group: moves this layer's expert weights into a
+        double-buffered symmetric store.  Returns the store (`rebalance()` re-places the experts)."""
+        from ..parallel.eplb_gpu import ExpertStore
+        ps = self.ps
+        group = ps.moe_ep_group if ps.dp_size > 1 or ps.moe_ep_group is not None else ps.tp_group
+        rank = ps.ep_rank if ps.ep_size > 1 else ps.tp_rank
+        self.expert_store = ExpertStore(self, group or ps.world_group, rank, self.ep)
+        return self.expert_store
+
     # ---- expert parallelism by all-to-all (parallel/ep.py): every rank routes the token rows it owns
     # in the sequence-sharded residual stream, tokens visit the owners of their experts and come
     # back; the rows land in this rank's part of the partial buffer (zeros elsewhere), so the fused
@@ -171,7 +188,7 @@ class SparseMoeBlock(Module):
             out.copy_(shared_out)            # TP-sharded shared expert: a partial sum over all rows
         if e > b:
             ep.moe(x[b:e], logits[b:e], self.w_gate_up, self.w_down, a.scoring_func, self.bias, a.n_group, a.topk_group,
-                   a.norm_topk_prob, a.routed_scaling_factor, None, out=self._a2a_rows(e - b, x))
+                   a.norm_topk_prob, a.routed_scaling_factor, None, out=self._a2a_rows(e - b, x), load=self._load())
             out[b:e] += self._rows[: e - b]
         else:
             ep.moe(x[:0], logits[:0], self.w_gate_up, self.w_down, a.scoring_func, self.bias, a.n_group, a.topk_group,
@@ -200,7 +217,7 @@ class SparseMoeBlock(Module):
                             max_local_tokens=int(getattr(ps, "max_tokens_per_batch", 8192)))
                 ps.ep_comm = ep
             return ep.moe(x, logits, self.w_gate_up, self.w_down, a.scoring_func, self.bias, a.n_group, a.topk_group,
-                          a.norm_topk_prob, a.routed_scaling_factor, shared_out)
+                          a.norm_topk_prob, a.routed_scaling_factor, shared_out, load=self._load())
         W = ps.ep_size
         counts = torch.zeros(W, dtype=torch.int64, device=x.device)
         counts[ps.ep_rank] = T

@@ -80,7 +80,7 @@ class EpComm:
         check(_lib.load().xllm_ep_barrier(*self._common(), stream()), "ep_barrier")
 
     def moe(self, x, logits, w_gate_up, w_down, scoring="softmax", bias=None, n_group=1, topk_group=1, renorm=True,
-            scale=1.0, shared_out=None, out=None):
+            scale=1.0, shared_out=None, out=None, load=None):
         """x [T, H] = this rank's tokens, logits [T, E]; w_gate_up [E_local, 2I, H] and w_down
         [E_local, H, I] = this rank's experts.  Returns the MoE output of this rank's tokens."""
         from ..ops import _count
@@ -101,6 +101,8 @@ class EpComm:
         check(lib.xllm_moe_route(ptr(logits), int(lf), ptr(bias), ptr(self.topk_ids), ptr(self.topk_w), ptr(self.counts),
                                  ptr(self.slot), T, self.E, self.K, n_group, topk_group, 0 if scoring == "softmax" else 1,
                                  int(renorm), float(scale), 0, self.E, s), "moe_route")
+        if load is not None:                      # expert load statistics: this rank's tokens per (physical) expert
+            load += self.counts
         # counts to every peer + layout of the receive buffers (exchange 1)
         check(lib.xllm_ep_counts_layout(*c, ptr(self.counts), ptr(self.send_off), ptr(self.tile_expert), ptr(self.meta),
                                         self.max_tiles, s), "ep_counts_layout")
