@@ -16,7 +16,7 @@ def main():
     mode = os.environ.get("QUIT_MODE", "leave")
     dist.init_process_group("gloo", rank=rank, world_size=world, init_method=os.environ["INIT"])
     store = dist.TCPStore("127.0.0.1", int(os.environ["HB_PORT"]), world, rank == 0, wait_for_workers=False)
-    mon = HeartbeatMonitor(KV(store), rank, world, timeout_s=1.0)
+    mon = HeartbeatMonitor(KV(store), rank, world, timeout_s=2.0)   # generous: a loaded test host must not look like a dead rank
     alive = list(range(world))
     group = dist.group.WORLD
     total = 0
@@ -28,7 +28,7 @@ def main():
             # a rank leaves only between steps: nothing of its own is in flight
             os._exit(0)
         # give the quitter's announcement (or silence) time to show up, then look before launching
-        deadline = time.time() + (0.3 if mode == "leave" else 1.6)
+        deadline = time.time() + (0.3 if mode == "leave" else 3.0)
         while step >= 3 and time.time() < deadline:
             mon.beat(step)                    # a live rank keeps beating while it waits
             time.sleep(0.05)
