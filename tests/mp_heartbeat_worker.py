@@ -44,6 +44,14 @@ def main():
         else:
             total += len(alive)
     print(f"RANK{rank} total={total} alive={alive}", flush=True)
+    # rank 0 hosts the store: it leaves last, or the others' final beats meet a closed socket
+    store.set(f"done{rank}", "1")
+    if rank == 0:
+        import datetime
+        try:
+            store.wait([f"done{r}" for r in alive], datetime.timedelta(seconds=20))
+        except Exception:
+            pass
     os._exit(0)
 
 
