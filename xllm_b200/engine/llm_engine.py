@@ -67,6 +67,12 @@ class EngineConfig:
     max_prefill_wait_steps: int = 8     # ... or this many steps have passed
     max_running_seqs: int = 0           # cap on sequences holding KV / state at once; 0: no cap (state models: max_seqs_per_batch + 1)
     scheduler_type: str = "continuous"  # "continuous" | "zero_eviction" (never preempts: admits by simulation) | "fixed_steps" (waves)
+    # latency-aware budgets: profile the model at start-up and cap the tokens of a step so that a step
+    # stays under `max_global_ttft_ms` (prompt work) and the decode batch so that it stays under `max_global_tpot_ms`
+    enable_profile_token_budget: bool = False
+    max_global_ttft_ms: float = 0.0
+    max_global_tpot_ms: float = 0.0
+    profile_max_prompt_length: int = 2048
 
 
 _U64 = (1 << 64) - 1
@@ -246,11 +252,41 @@ class LLMEngine:
                     self.eagle3.load_weights(iterate_weights(cfg.draft_model), strict=False)
             self.spec = SpecDecoder(self, make_drafter(cfg.speculative_method, cfg.num_speculative_tokens, self),
                                     cfg.num_speculative_tokens)
+        self.profile_manager = None
+        self.profiled_budget = None
+        if cfg.enable_profile_token_budget and (cfg.max_global_ttft_ms > 0 or cfg.max_global_tpot_ms > 0):
+            self._apply_profiled_budgets()
         from .fault import FaultPlan
         self.fault = FaultPlan.from_env(self.ps.rank)      # host-side fault hooks (XLLM_FAULT), None when unset
         self.steps = 0
         self.step_log: List[tuple] = []
         self.record_steps = False
+
+    # ------------------------------------------------------------------ latency-aware budgets
+    def _apply_profiled_budgets(self):
+        """Times prompt and decode steps of this engine (ProfileManager), fits the step-time predictors
+        and reconfigures the scheduler: tokens per step from the TTFT target, sequences per step from
+        the TPOT target (xllm/core/scheduler/profile/profile_manager.cpp, the flags
+        enable_profile_token_budget / max_global_ttft_ms / max_global_tpot_ms)."""
+        from .profile_manager import ProfileManager
+        cfg = self.cfg
+        pm = ProfileManager.for_engine(self, repeats=2)
+        top = max(128, min(cfg.profile_max_prompt_length, cfg.max_tokens_per_batch))
+        sizes = sorted({max(16, top // 8), max(32, top // 4), max(64, top // 2), top})
+        batches = sorted({1, max(2, cfg.max_seqs_per_batch // 8), max(4, cfg.max_seqs_per_batch // 2), cfg.max_seqs_per_batch})
+        ctx = max(64, min(self.max_model_len // 2, 2048))
+        pm.profile(prefill_tokens=sizes, decode_batches=batches, contexts=(ctx // 4, ctx))
+        tokens = seqs = 0
+        if cfg.max_global_ttft_ms > 0:
+            tokens = pm.token_budget(cfg.max_global_ttft_ms / 1e3, hi=cfg.max_tokens_per_batch)
+            tokens = max(tokens, cfg.block_size)                  # a step must be able to make progress
+        if cfg.max_global_tpot_ms > 0:
+            seqs = max(1, min(cfg.max_seqs_per_batch, pm.max_decode_batch(cfg.max_global_tpot_ms / 1e3, ctx,
+                                                                         hi=cfg.max_seqs_per_batch)))
+        self.scheduler.reconfigure("", int(tokens), int(seqs), 0)
+        self.profile_manager = pm
+        self.profiled_budget = {"max_tokens_per_batch": int(tokens) or cfg.max_tokens_per_batch,
+                                "max_seqs_per_batch": int(seqs) or cfg.max_seqs_per_batch}
 
     # ------------------------------------------------------------------ capacity
     def _estimate_blocks(self, per_block: int) -> int:
