@@ -396,6 +396,8 @@ def run(args):
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(gpu_launches), "graph_replays": int(graph_replays),
             "h2d_bytes_per_step": h2d_step, "d2h_bytes_per_step": d2h_step,
         }
+        from xllm_b200.ops import gemm as _gemm
+        line["library_gemm_fallbacks"] = int(sum(_gemm.library_fallbacks().values()))
         line["vs_library"] = _vs_library(args.config, world, n_req_total, in_len, out_len, conc_total,
                                          e2e.get("value") if isinstance(e2e, dict) else None)
         print(json.dumps(line), flush=True)
