@@ -55,3 +55,34 @@ def test_partial_ranges_round_to_pages():
     assert r.mapped_bytes == 0
     with pytest.raises(ValueError):
         r.tensor((6 * pb,), torch.uint8)
+
+
+def test_engine_kv_cache_on_the_shared_page_pool_survives_sleep():
+    """enable_xtensor: the KV cache lives on the device's page pool; sleep returns the pages (another
+    engine can take them), wake-up maps pages again at the same address and generation repeats."""
+    import torch
+    from xllm_b200 import LLM, SamplingParams
+    from xllm_b200.engine.llm_engine import EngineConfig, LLMEngine
+    from xllm_b200.utils.xtensor import shared_pool
+    pool = shared_pool("cpu")
+    kw = dict(model="tiny", device="cpu", dtype="float32", num_blocks=64, enable_graph=False, max_seqs_per_batch=4,
+              max_tokens_per_batch=128, enable_xtensor=True)
+    free0 = pool.pages_in_use
+    a = LLMEngine(EngineConfig(**kw))
+    used_a = pool.pages_in_use - free0
+    assert used_a > 0 and a._kv_range is not None
+    addr = a.runner.kv_tensor.data_ptr()
+    llm = LLM.__new__(LLM)
+    llm.engine, llm.tokenizer = a, None
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (20, 45)]
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    a.sleep(1)
+    assert pool.pages_in_use == free0                      # every page of the cache went back
+    b = LLMEngine(EngineConfig(**kw))                      # a second model takes pages of the same pool meanwhile
+    assert pool.pages_in_use - free0 == used_a
+    b.sleep(1)
+    a.wake_up()
+    assert a.runner.kv_tensor.data_ptr() == addr and pool.pages_in_use - free0 == used_a
+    assert [o.outputs[0].token_ids for o in llm.generate(prompts, sp)] == want

@@ -69,6 +69,7 @@ class EngineConfig:
     scheduler_type: str = "continuous"  # "continuous" | "zero_eviction" (never preempts: admits by simulation) | "fixed_steps" (waves)
     # latency-aware budgets: profile the model at start-up and cap the tokens of a step so that a step
     # stays under `max_global_ttft_ms` (prompt work) and the decode batch so that it stays under `max_global_tpot_ms`
+    enable_xtensor: bool = False        # KV cache on the device's shared page pool: sleep gives the pages back, addresses (and CUDA graphs) survive
     enable_profile_token_budget: bool = False
     max_global_ttft_ms: float = 0.0
     max_global_tpot_ms: float = 0.0
@@ -171,6 +172,17 @@ class LLMEngine:
             dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.ps.tp_group)
             num_blocks = int(t.item())
         self.num_blocks = num_blocks
+        self._kv_range = None
+        if cfg.enable_xtensor and kv_allocator is None:
+            from ..utils.xtensor import shared_pool
+            pool = shared_pool(self.device)
+
+            def kv_allocator(n_bytes, pool=pool):
+                page = pool.page_bytes
+                self._kv_range = pool.range((n_bytes + page - 1) // page * page)
+                self._kv_range.ensure(n_bytes)
+                self._kv_bytes = n_bytes
+                return self._kv_range.tensor((n_bytes,), torch.uint8)
         self.runner = ModelRunner(self.model, cfg.block_size, num_blocks, cfg.max_seqs_per_batch,
                                   cfg.max_tokens_per_batch, max_len, self.device, self.dtype,
                                   enable_graph=cfg.enable_graph and bool(getattr(self.model, "supports_graph", True)),
@@ -587,6 +599,26 @@ class LLMEngine:
         self.pause("KEEP")
         self.reset_prefix_cache()
         r = self.runner
+        if self._kv_range is not None:
+            # page-pool cache: the physical pages go back to the pool, the tensors keep their addresses,
+            # so the captured graphs stay valid and wake-up only maps pages again
+            if self.device.type == "cuda":
+                torch.cuda.synchronize()
+            self._kv_range.release_all()
+            self._kv_shapes = None
+            self._host_weights = None
+            if level >= 2:
+                self._host_weights = []
+                for name, t in self.model.named_params():
+                    h = torch.empty(t.shape, dtype=t.dtype, pin_memory=t.is_cuda)
+                    h.copy_(t)
+                    self._host_weights.append((t, h, t.shape))
+                    t.set_(torch.empty(0, dtype=t.dtype, device=t.device))
+                if self.device.type == "cuda":
+                    torch.cuda.synchronize()
+                    torch.cuda.empty_cache()
+            self.asleep = level
+            return
         self._kv_shapes = [(k.shape, v.shape, k.dtype, k.device) for k, v in r.kv_caches]
         r.graphs.clear()
         r.graph_in.clear()
@@ -619,6 +651,12 @@ class LLMEngine:
                 t.copy_(h, non_blocking=True)
             self._host_weights = None
         r = self.runner
+        if self._kv_range is not None:
+            self._kv_range.ensure(self._kv_bytes)
+            r.kv_tensor.zero_()
+            self.asleep = 0
+            self.resume()
+            return
         for i, (ks, vs, dt, dev) in enumerate(self._kv_shapes):
             r.kv_caches[i] = (torch.zeros(ks, dtype=dt, device=dev), torch.zeros(vs, dtype=dt, device=dev))
         if getattr(self.spec, "drafter", None) is not None and hasattr(self.spec.drafter, "kv"):

@@ -87,3 +87,21 @@ class VmmPool:
 
     def trim(self) -> int:
         return self.p.trim()
+
+
+_SHARED = {}
+
+
+def shared_pool(device, page_bytes: int = 2 << 20, max_pages: int = 0, fake=None) -> VmmPool:
+    """The page pool of a device, shared by every engine of the process (several models on one GPU
+    take turns on the same physical pages: one sleeps, another wakes up)."""
+    dev = torch.device(device)
+    key = (dev.type, dev.index or 0)
+    if key not in _SHARED:
+        if not max_pages:
+            if dev.type == "cuda" and torch.cuda.is_available():
+                max_pages = int(torch.cuda.get_device_properties(dev).total_memory // page_bytes)
+            else:
+                max_pages = 4096
+        _SHARED[key] = VmmPool(dev.index or 0, page_bytes, max_pages, fake=fake if dev.type == "cuda" else True)
+    return _SHARED[key]
