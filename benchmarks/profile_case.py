@@ -16,6 +16,10 @@ hundred MB on the device, a handful of launches).
     python benchmarks/profile_case.py --kernel quant      # 1 x 128 group quantisation, 8192 x 7168
     python benchmarks/profile_case.py --kernel gdn        # gated-delta-rule decode step
     python benchmarks/profile_case.py --kernel route      # MoE routing, 8192 tokens x 256 experts
+    python benchmarks/profile_case.py --kernel topk       # radix top-k, 1024 rows x 151936, k = 64
+    python benchmarks/profile_case.py --kernel logsoftmax # log-softmax, 1024 rows x 151936
+    python benchmarks/profile_case.py --kernel xattn      # beam attention: 16 requests x 128 beams over 2048-token prompts
+    python benchmarks/profile_case.py --kernel gdn_prefill # gated-delta-rule prompt chunk, 4096 tokens x 32 heads
 """
 import argparse
 import math
@@ -142,6 +146,37 @@ def main():
         fn = lambda: lib.xllm_moe_route(logits.data_ptr(), 1, bias.data_ptr(), ws.topk_ids.data_ptr(), ws.topk_w.data_ptr(),
                                         ws.counts.data_ptr(), ws.slot.data_ptr(), T, E, K, 8, 4, 1, 1, 2.5, 0, E,
                                         torch.cuda.current_stream().cuda_stream)
+    elif a.kernel in ("topk", "logsoftmax"):
+        from xllm_b200.ops import select
+        logits = torch.randn(1024, 151936, device=dev, dtype=torch.bfloat16)
+        fn = (lambda: select.topk(logits, 64)) if a.kernel == "topk" else (lambda: select.log_softmax(logits))
+    elif a.kernel == "xattn":
+        from xllm_b200.ops import xattn
+        R, W, ctx, nq, nkv, d, page, cap = 16, 128, 2048, 32, 8, 128, 16, 2
+        nb = R * (ctx // page) + 1
+        kc = torch.randn(nb, nkv, page, d, device=dev, dtype=torch.bfloat16)
+        vc = torch.randn(nb, nkv, page, d, device=dev, dtype=torch.bfloat16)
+        bt = (torch.randperm(nb - 1, device=dev)[: R * (ctx // page)] + 1).view(R, -1).to(torch.int32)
+        q = torch.randn(R * W, nq, d, device=dev, dtype=torch.bfloat16) * 0.3
+        ku = torch.randn(R * W, nkv, cap, d, device=dev, dtype=torch.bfloat16)
+        vu = torch.randn_like(ku)
+        anc = torch.randint(0, R * W, (cap, R * W), device=dev, dtype=torch.int32)
+        cu = (torch.arange(R + 1, device=dev) * W).to(torch.int32)
+        kl = torch.full((R,), ctx, device=dev, dtype=torch.int32)
+        out = torch.empty_like(q)
+        fn = lambda: xattn.xattention(q, kc, vc, bt, cu, kl, W, ku, vu, anc, 2, 1 / math.sqrt(d), out=out)
+        if os.environ.get("XATTN_COMPARE"):   # the same rows through the paged decode kernel: every beam re-reads the prompt
+            bt_rows = bt.repeat_interleave(W, 0).contiguous()
+            sl = torch.full((R * W,), ctx, device=dev, dtype=torch.int32)
+            fn = lambda: ops.paged_decode_attention(q, kc, vc, bt_rows, sl, 1 / math.sqrt(d), out=out)
+    elif a.kernel == "gdn_prefill":
+        from xllm_b200.ops import gdn
+        n, nv, dk, dv = 4096, 32, 128, 128
+        state = torch.zeros(4, nv, dk, dv, device=dev, dtype=torch.float32)
+        q, k = torch.randn(n, nv, dk, device=dev), torch.randn(n, nv, dk, device=dev) * 0.1
+        v = torch.randn(n, nv, dv, device=dev)
+        g, beta = -torch.rand(n, nv, device=dev), torch.rand(n, nv, device=dev)
+        fn = lambda: gdn.prefill(state, 1, True, q, k, v, g, beta)
     else:
         raise SystemExit(f"unknown kernel {a.kernel}")
     for _ in range(a.iters):

@@ -272,6 +272,21 @@ class LLM:
             outs.append(res)
         return outs
 
+    def recommend(self, prompts, beam_width: int = 32, num_steps: int = 3, num_return: Optional[int] = None,
+                  valid_items=None, prompt_embeds=None):
+        """Generative recommendation: for every prompt (token-id list or string) the `beam_width` most likely
+        items of `num_steps` tokens, best first, optionally restricted to `valid_items` (token tuples).  All
+        prompts run as one batch (engine/rec.py; the reference's rec backend)."""
+        from ..engine.rec import ItemTrie, RecEngine
+        if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        ids = [self._encode(p) if isinstance(p, str) else [int(t) for t in p] for p in prompts]
+        if getattr(self, "_rec", None) is None:
+            self._rec = RecEngine(self.engine)
+        trie = ItemTrie([tuple(i) for i in valid_items], self.engine.args.vocab_size) if valid_items else None
+        return self._rec.generate(ids, beam_width=beam_width, num_steps=num_steps, num_return=num_return, trie=trie,
+                                  prompt_embeds=prompt_embeds)
+
     def embed(self, prompts, pooling_params: Union[PoolingParams, List[PoolingParams], None] = None) -> List[EmbeddingOutput]:
         """Pooled embedding (final-norm hidden state of the last token, L2-normalised unless the
         pooling parameters say otherwise) of every prompt: xllm/pybind/llm.py:386-406."""

@@ -31,6 +31,8 @@ from concurrent.futures import ThreadPoolExecutor
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
+import torch
+
 from .. import _rt
 from ..engine.llm_engine import LLMEngine
 
@@ -66,8 +68,10 @@ class _Call:
 class ApiServer:
     def __init__(self, engine: LLMEngine, tokenizer, model_name: str = "xllm_b200", host: str = "", port: int = 8010,
                  max_concurrent_requests: int = 200, tool_call_parser: str = "", reasoning_parser: str = "",
-                 request_threads: int = 4, response_threads: int = 4, parent: "ApiServer" = None):
+                 request_threads: int = 4, response_threads: int = 4, parent: "ApiServer" = None, backend: str = "llm"):
         self.engine = engine
+        self.backend = backend or "llm"   # "rec": /v1/completions answers with the beam_width best items
+        self.rec_engine = None
         self.tok = tokenizer
         self.model_name = model_name
         # a forked master (another model served by the same process) shares its parent's transport
@@ -509,7 +513,50 @@ class ApiServer:
             self._native_by_rid[call.request_id] = call.native
         _rt.metric_counter_add("server_request_total_ok", 0)
 
+    def _rec_completion(self, req, body):
+        """Generative recommendation (`--backend rec`; xllm/api_service/rec_completion_service_impl.cpp): the
+        prompt is the user's history, every choice is one item of `max_tokens` tokens, best first."""
+        from ..engine.rec import ItemTrie, RecEngine
+        prompt = body.get("prompt", "")
+        if isinstance(prompt, list) and prompt and isinstance(prompt[0], int):
+            ids = [int(t) for t in prompt]
+        elif self.tok is None:
+            return self._error(req.id, 400, "this server has no tokenizer: send token ids as `prompt`")
+        else:
+            ids = self.tok.encode(prompt if isinstance(prompt, str) else (prompt[0] if prompt else ""))
+        if not ids:
+            return self._error(req.id, 400, "`prompt` must not be empty")
+        try:
+            if self.rec_engine is None:
+                self.rec_engine = RecEngine(self.engine)
+            steps = int(body.get("max_tokens") or 3)
+            width = int(body.get("beam_width") or 32)
+            trie = None
+            if body.get("valid_items"):
+                trie = ItemTrie([tuple(int(t) for t in it) for it in body["valid_items"]], self.engine.args.vocab_size)
+            embeds = None
+            if body.get("input_embeds"):
+                e = body["input_embeds"]
+                embeds = [(torch.tensor(e["rows"], dtype=torch.long), torch.tensor(e["values"], dtype=torch.float32))]
+            items = self.rec_engine.generate([ids], beam_width=width, num_steps=steps, num_return=int(body.get("n") or width),
+                                             trie=trie, prompt_embeds=embeds)[0]
+        except (ValueError, KeyError, TypeError) as e:
+            return self._error(req.id, 400, str(e))
+        except RuntimeError as e:
+            return self._error(req.id, 503, str(e))
+        choices = [{"index": i, "text": self.tok.decode(it.token_ids) if self.tok is not None else "",
+                    "token_ids": it.token_ids, "logprobs": {"cumulative_logprob": it.logprob}, "finish_reason": "length"}
+                   for i, it in enumerate(items)]
+        n_out = sum(len(it.token_ids) for it in items)
+        self._json(req.id, 200, {"id": req.header("x-request-id") or f"rec-{uuid.uuid4().hex}", "object": "text_completion",
+                                 "created": int(time.time()), "model": body.get("model") or self.model_name,
+                                 "choices": choices,
+                                 "usage": {"prompt_tokens": len(ids), "completion_tokens": n_out,
+                                           "total_tokens": len(ids) + n_out}})
+
     def _completion(self, req, body):
+        if self.backend == "rec":
+            return self._rec_completion(req, body)
         prompt = body.get("prompt", "")
         if isinstance(prompt, list) and prompt and isinstance(prompt[0], int):
             ids = list(prompt)

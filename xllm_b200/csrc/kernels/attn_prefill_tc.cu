@@ -142,6 +142,7 @@ struct Params {
   int bt_stride, nq, nkv, page, causal;
   float scale_log2;
   int* err;
+  float* lse;                  // optional [total_q, nq]: log2-domain log-sum-exp of every row's scaled scores
 };
 
 __global__ void __launch_bounds__(320, 1)
@@ -410,6 +411,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_consta
     asm volatile("bar.sync 1, 256;" ::: "memory");
     l += lsum[(half ^ 1) * kBM + row];
     const float inv = l > 0.f ? 1.f / l : 0.f;
+    if (p.lse != nullptr && half == 0 && ok && m0 + row < q_len)
+      p.lse[(int64_t)(q_begin + m0 + row) * p.nq + h] = l > 0.f ? m + log2f(l) : -INFINITY;
     uint8_t* stage = smem + Q_OFF;                    // [128 rows][256 bytes], 16-byte units XOR-swizzled by row
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
@@ -474,11 +477,13 @@ static int* g_err[64] = {};
 // Same contract as xllm_paged_prefill_attn for head_dim 128, no sliding window, page_size in
 // {16, 32, 64, 128}: q [total_q, nq, 128] (row stride q_stride elements), caches
 // [n_blocks, nkv, page, 128], cu_q absolute row offsets [batch + 1], kv_lens [batch].
-XLLM_API int xllm_paged_prefill_attn_tc(void* out, int64_t o_stride, const void* q, int64_t q_stride, int64_t total_q,
-                                        const void* k_cache, const void* v_cache, int64_t n_blocks,
-                                        const void* block_table, int bt_stride, const void* cu_q, const void* kv_lens,
-                                        int batch, int max_q_len, int nq, int nkv, int page_size, float scale,
-                                        int causal, void* stream) {
+// `lse` (optional, fp32 [total_q, nq]) receives every row's log-sum-exp in the log2 domain, so that the
+// result can be merged with attention over other keys (xllm_attn_merge, the beam-tail kernel).
+XLLM_API int xllm_paged_prefill_attn_tc_lse(void* out, int64_t o_stride, const void* q, int64_t q_stride, int64_t total_q,
+                                            const void* k_cache, const void* v_cache, int64_t n_blocks,
+                                            const void* block_table, int bt_stride, const void* cu_q,
+                                            const void* kv_lens, int batch, int max_q_len, int nq, int nkv,
+                                            int page_size, float scale, int causal, void* lse, void* stream) {
   using namespace xllm;
   using namespace xllm::fmha;
   if (batch == 0 || max_q_len == 0) return 0;
@@ -506,9 +511,20 @@ XLLM_API int xllm_paged_prefill_attn_tc(void* out, int64_t o_stride, const void*
   p.out = (bf16*)out; p.block_table = (const int32_t*)block_table; p.cu_q = (const int32_t*)cu_q;
   p.kv_lens = (const int32_t*)kv_lens; p.o_stride = o_stride; p.bt_stride = bt_stride; p.nq = nq; p.nkv = nkv;
   p.page = page_size; p.causal = causal; p.scale_log2 = scale * 1.4426950408889634f; p.err = g_err[dev & 63];
+  p.lse = (float*)lse;
   dim3 grid((max_q_len + kBM - 1) / kBM, nq, batch);
   prefill_tc_kernel<<<grid, 320, SMEM_TOTAL, (cudaStream_t)stream>>>(tq, tk, tv, p);
   return XLLM_LAUNCH_CHECK();
+}
+
+XLLM_API int xllm_paged_prefill_attn_tc(void* out, int64_t o_stride, const void* q, int64_t q_stride, int64_t total_q,
+                                        const void* k_cache, const void* v_cache, int64_t n_blocks,
+                                        const void* block_table, int bt_stride, const void* cu_q, const void* kv_lens,
+                                        int batch, int max_q_len, int nq, int nkv, int page_size, float scale,
+                                        int causal, void* stream) {
+  return xllm_paged_prefill_attn_tc_lse(out, o_stride, q, q_stride, total_q, k_cache, v_cache, n_blocks, block_table,
+                                        bt_stride, cu_q, kv_lens, batch, max_q_len, nq, nkv, page_size, scale, causal,
+                                        nullptr, stream);
 }
 
 // 0 = no bounded wait expired in the prefill kernel on this device since the last call.

@@ -241,6 +241,11 @@ def preset(name: str) -> ModelArgs:
                          num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                          intermediate_size=768, rms_norm_eps=1e-6, rope_theta=1e6,
                          tie_word_embeddings=True, max_position_embeddings=4096, dtype="float32")
+    if n == "tiny-hd128":                                   # head_dim of the tensor-core attention kernels
+        return ModelArgs(model_type="qwen3", vocab_size=32000, hidden_size=512, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                         intermediate_size=1024, rms_norm_eps=1e-6, rope_theta=1e6,
+                         tie_word_embeddings=True, max_position_embeddings=4096, dtype="float32")
     if n in ("qwen3-8b",):
         return ModelArgs(model_type="qwen3", vocab_size=151936, hidden_size=4096, num_hidden_layers=36,
                          num_attention_heads=32, num_key_value_heads=8, head_dim=128,

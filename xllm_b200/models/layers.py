@@ -45,6 +45,11 @@ class AttentionMetadata:
     # of a disaggregated pair: the layer's blocks are pushed to the decode instance while the next
     # layer computes)
     kv_hook: Optional[Callable] = None
+    # fixed-step beam generation: every sequence row is a REQUEST whose cu_q rows are its beams; the
+    # new tokens' KV goes to the beams' tail cache (`slots` index it) and attention runs over the shared
+    # prompt pages plus each beam's tail (ops/xattn.py).  Object with tail_of(k_cache) -> (ku, vu), anc,
+    # n_tail, max_rows.
+    xattn: Optional[object] = None
 
     @property
     def n_seqs(self):
@@ -480,6 +485,20 @@ class Attention(Module):
         cos_sin = self.rope.cos_sin
         if meta.rope_table is not None:
             cos_sin, positions = meta.rope_table, meta.rope_rows
+        if meta.xattn is not None:
+            from ..ops import xattn as _xattn
+            xa = meta.xattn
+            ku, vu = xa.tail_of(k_cache)
+            q = ops.rope_kv_write(qkv, self.nq, self.nkv, self.d, positions, cos_sin, self.rope.rot_dim,
+                                  slots=meta.slots, k_cache=ku, v_cache=vu,
+                                  q_norm_w=self._norm_w(self.q_norm), k_norm_w=self._norm_w(self.k_norm), eps=self.eps,
+                                  interleaved=self.rope.interleaved)
+            out = _xattn.xattention(q, k_cache, v_cache, meta.block_table, meta.cu_q, meta.kv_lens, xa.max_rows,
+                                    ku, vu, xa.anc, xa.n_tail, self.scale)
+            out = out.view(q.shape[0], self.nq * self.d)
+            if gate is not None:
+                out = out * torch.sigmoid(gate.float()).to(out.dtype)
+            return self.o_proj(out)
         q = ops.rope_kv_write(qkv, self.nq, self.nkv, self.d, positions, cos_sin, self.rope.rot_dim,
                               slots=meta.slots, k_cache=k_cache, v_cache=v_cache,
                               q_norm_w=self._norm_w(self.q_norm), k_norm_w=self._norm_w(self.k_norm), eps=self.eps,

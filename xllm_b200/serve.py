@@ -75,7 +75,8 @@ def main(argv=None):
         return follow_rank0(engine, ps)
     srv = ApiServer(engine, tok, model_name=name, host=flags.get("host"), port=flags.get_int("port"),
                     max_concurrent_requests=flags.get_int("max_concurrent_requests"),
-                    tool_call_parser=flags.get("tool_call_parser"), reasoning_parser=flags.get("reasoning_parser"))
+                    tool_call_parser=flags.get("tool_call_parser"), reasoning_parser=flags.get("reasoning_parser"),
+                    backend=flags.get("backend") or "llm")
     if ps is not None:
         from .engine.replica import lead_ranks
         lead_ranks(srv, ps)
