@@ -49,7 +49,7 @@ def test_xattention_matches_reference(lens, W, n_tail):
 
 def test_rec_engine_on_device_matches_exhaustive_beam():
     from xllm_b200 import LLM
-    from xllm_b200.engine.rec import ItemTrie, RecEngine, recommend_reference
+    from xllm_b200.engine.rec import ItemTrie, RecEngine, item_logprob_reference, recommend_reference
     from xllm_b200.ops import launches as launch_count
     llm = LLM("tiny-hd128", devices="cuda:0", dtype="bfloat16", block_size=16, num_blocks=256, max_seqs_per_batch=8,
               max_tokens_per_batch=512, enable_graph=False, enable_prefix_cache=False)
@@ -62,10 +62,13 @@ def test_rec_engine_on_device_matches_exhaustive_beam():
     assert launch_count() > n0
     for p, items in zip(prompts, got):
         want = recommend_reference(llm.engine, p, 6, 3)
-        # bf16 scores: the sets agree up to near-ties at the tail of the beam, the best item and its score agree
-        assert items[0].token_ids == want[0].token_ids
-        assert abs(items[0].logprob - want[0].logprob) < 0.15
-        assert len({tuple(i.token_ids) for i in items} & {tuple(w.token_ids) for w in want}) >= 4
+        # a random-init model in bf16 ranks many items within rounding of each other, so the check is on scores:
+        # every returned item's score is the one a dense forward gives it, and the best score is the oracle's
+        assert len(items) == 6 and len({tuple(i.token_ids) for i in items}) == 6
+        for it in items:
+            assert abs(it.logprob - item_logprob_reference(llm.engine, p, it.token_ids)) < 0.1, it
+        assert abs(items[0].logprob - want[0].logprob) < 0.1
+        assert all(items[i].logprob >= items[i + 1].logprob for i in range(5))
     items = [tuple(torch.randint(0, V, (3,), generator=g).tolist()) for _ in range(30)]
     got = rec.generate(prompts[:1], beam_width=8, num_steps=3, trie=ItemTrie(items, V))[0]
     assert len(got) == 8 and all(tuple(i.token_ids) in set(items) for i in got)

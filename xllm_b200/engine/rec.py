@@ -214,35 +214,46 @@ class RecEngine:
         return logits if logits.dtype in (torch.bfloat16, torch.float32) else logits.float()
 
 
-def recommend_reference(engine, prompt: Sequence[int], beam_width: int, num_steps: int,
-                        trie: Optional[ItemTrie] = None) -> List[RecItem]:
-    """Oracle for tests: exhaustive beam expansion by re-running the whole sequence for every beam
-    (no KV reuse, no x-attention), through the same model."""
+def _next_logprobs_dense(engine, tokens):
+    """log-probabilities of the token after `tokens`, by one plain causal forward of the whole sequence."""
     runner = engine.runner
     model, dev = runner.model, runner.device
     bs = engine.cfg.block_size
     bm = engine.scheduler.block_manager(0)
+    n = len(tokens)
+    blocks = bm.allocate((n + bs - 1) // bs)
+    try:
+        slots = [blocks[q // bs] * bs + q % bs for q in range(n)]
+        meta = AttentionMetadata(n_decode=0, n_prefill=1, slots=torch.tensor(slots, dtype=torch.int32, device=dev),
+                                 block_table=torch.tensor([list(blocks)], dtype=torch.int32, device=dev),
+                                 kv_lens=torch.tensor([n], dtype=torch.int32, device=dev),
+                                 cu_q=torch.tensor([0, n], dtype=torch.int32, device=dev), max_q_len=n, max_kv_len=n)
+        h = model.forward(torch.tensor(tokens, dtype=torch.int64, device=dev),
+                          torch.arange(n, dtype=torch.int64, device=dev), meta, runner.kv_caches)
+        return torch.log_softmax(model.logits(h[-1:]).float(), -1)[0]
+    finally:
+        bm.free(blocks)
 
-    def next_logprobs(tokens):
-        n = len(tokens)
-        blocks = bm.allocate((n + bs - 1) // bs)
-        try:
-            slots = [blocks[q // bs] * bs + q % bs for q in range(n)]
-            meta = AttentionMetadata(n_decode=0, n_prefill=1, slots=torch.tensor(slots, dtype=torch.int32, device=dev),
-                                     block_table=torch.tensor([list(blocks)], dtype=torch.int32, device=dev),
-                                     kv_lens=torch.tensor([n], dtype=torch.int32, device=dev),
-                                     cu_q=torch.tensor([0, n], dtype=torch.int32, device=dev), max_q_len=n, max_kv_len=n)
-            h = model.forward(torch.tensor(tokens, dtype=torch.int64, device=dev),
-                              torch.arange(n, dtype=torch.int64, device=dev), meta, runner.kv_caches)
-            return torch.log_softmax(model.logits(h[-1:]).float(), -1)[0]
-        finally:
-            bm.free(blocks)
 
+def item_logprob_reference(engine, prompt: Sequence[int], item: Sequence[int]) -> float:
+    """Oracle for tests: the item's log-probability after the prompt, one dense forward per token."""
+    toks, total = list(prompt), 0.0
+    for t in item:
+        total += float(_next_logprobs_dense(engine, toks)[int(t)])
+        toks.append(int(t))
+    return total
+
+
+def recommend_reference(engine, prompt: Sequence[int], beam_width: int, num_steps: int,
+                        trie: Optional[ItemTrie] = None) -> List[RecItem]:
+    """Oracle for tests: exhaustive beam expansion by re-running the whole sequence for every beam
+    (no KV reuse, no x-attention), through the same model."""
+    dev = engine.runner.device
     beams = [([], 0.0)]
     for s in range(num_steps):
         cand = []
         for toks, sc in beams:
-            lp = next_logprobs(list(prompt) + toks)
+            lp = _next_logprobs_dense(engine, list(prompt) + toks)
             if trie is not None:
                 lp = lp.masked_fill(~trie.allowed([toks], dev)[0], float("-inf"))
             k = min(beam_width, lp.numel())
