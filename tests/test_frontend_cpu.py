@@ -47,6 +47,19 @@ def test_flags_reference_names_defaults_json_override(tmp_path):
     bad.parse_args(["--block_size=24"])
     assert any("model" in m for m in bad.validate()) and any("block_size" in m for m in bad.validate())
     assert "SchedulerConfig" in bad.help()
+    # cross-flag rules of the reference's option check
+    for args, word in ((["--cp_size=2"], "cp_size"), (["--backend=tts"], "backend"), (["--task=classify"], "task"),
+                       (["--backend=rec", "--task=embed"], "rec"), (["--enable_eplb"], "enable_eplb"),
+                       (["--beam_width=4", "--num_speculative_tokens=2", "--draft_model=/d"], "beam_width"),
+                       (["--kv_cache_transfer_mode=COPY"], "kv_cache_transfer_mode"),
+                       (["--max_seqs_per_batch=512", "--max_tokens_per_batch=256"], "max_seqs_per_batch"),
+                       (["--host_blocks_factor=1.5"], "host_blocks_factor")):
+        r = _rt.FlagRegistry()
+        r.parse_args(["--model=/m"] + args)
+        assert any(word in m for m in r.validate()), (args, r.validate())
+    ok = _rt.FlagRegistry()
+    ok.parse_args(["--model=/m", "--backend=rec", "--enable_eplb", "--ep_size=2", "--nnodes=2"])
+    assert ok.validate() == []
 
 
 def test_safetensors_roundtrip(tmp_path):

@@ -172,6 +172,35 @@ class FlagRegistry {
       bad.push_back("--instance_role must be DEFAULT, PREFILL, DECODE or MIX");
     if (get_bool("enable_disagg_pd") && (role.empty() || role == "DEFAULT"))
       bad.push_back("--enable_disagg_pd needs --instance_role PREFILL or DECODE");
+    // rules of the reference's option check (xllm/core/distributed_runtime/master.cpp:100-284, xllm.cpp)
+    const std::string backend = get("backend");
+    if (!backend.empty() && backend != "llm" && backend != "vlm" && backend != "dit" && backend != "rec")
+      bad.push_back("--backend must be llm, vlm, dit or rec");
+    const std::string task = get("task");
+    if (task != "generate" && task != "embed" && task != "mm_embed") bad.push_back("--task must be generate, embed or mm_embed");
+    if (backend == "rec" && task != "generate") bad.push_back("--backend rec serves --task generate only");
+    if (get_double("host_blocks_factor") > 1.0 || get_double("host_blocks_factor") < 0.0)
+      bad.push_back("--host_blocks_factor must be in [0, 1]");
+    if (get_int("cp_size") != 1) bad.push_back("--cp_size: context parallelism of the serving engine is not available on this platform (use 1)");
+    if (get_int("kv_split_size") != 1) bad.push_back("--kv_split_size: decode context parallelism is not available on this platform (use 1)");
+    if (get_int("beam_width") < 1) bad.push_back("--beam_width must be >= 1");
+    if (get_int("beam_width") > 1 && get_int("num_speculative_tokens") > 0)
+      bad.push_back("--beam_width > 1 cannot be combined with speculative decoding");
+    if (get_bool("enable_eplb") && get_int("ep_size") <= 1) bad.push_back("--enable_eplb needs --ep_size > 1");
+    if (get_bool("enable_eplb") && get_int("redundant_experts_num") < 0) bad.push_back("--redundant_experts_num must be >= 0");
+    const std::string mode = get("kv_cache_transfer_mode");
+    if (mode != "PUSH" && mode != "PULL") bad.push_back("--kv_cache_transfer_mode must be PUSH or PULL");
+    const std::string kvd = get("kv_cache_dtype");
+    if (kvd != "auto" && kvd != "bfloat16" && kvd != "float16" && kvd != "fp8" && kvd != "int8")
+      bad.push_back("--kv_cache_dtype must be auto, bfloat16, float16, fp8 or int8");
+    if (get_int("max_tokens_per_chunk_for_prefill") == 0) bad.push_back("--max_tokens_per_chunk_for_prefill must be positive (or -1: the batch budget)");
+    if (get_int("max_seqs_per_batch") > get_int("max_tokens_per_batch"))
+      bad.push_back("--max_seqs_per_batch must not exceed --max_tokens_per_batch (every running sequence needs one token per step)");
+    if (get_int("max_concurrent_requests") < 0) bad.push_back("--max_concurrent_requests must be >= 0");
+    if (get_int("num_request_handling_threads") < 1 || get_int("num_response_handling_threads") < 1)
+      bad.push_back("--num_request_handling_threads and --num_response_handling_threads must be >= 1");
+    if (get_bool("enable_disagg_pd") && get_int("num_speculative_tokens") > 0 && role == "PREFILL")
+      bad.push_back("a PREFILL instance does not speculate: drop --num_speculative_tokens");
     return bad;
   }
 

@@ -104,6 +104,9 @@ class LLMEngine:
                 torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
         else:
             self.device = torch.device(cfg.device)
+        if self.device.type == "cuda":
+            from ..utils.platform import bind_rank_to_device
+            self.numa_cpus = bind_rank_to_device(self.device.index or 0)   # [] on one-node hosts or XLLM_NUMA_BIND=0
         if model_args is not None:
             self.args = model_args
         elif os.path.isdir(cfg.model):

@@ -286,16 +286,18 @@ class ModelRunner:
             ids, lp = self._device_sample(logits, gin, off, NS, mode)
             return logits, ids, lp
 
-        s = torch.cuda.Stream(device=self.device)
-        s.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(s):
-            for _ in range(2):
-                run()
-        torch.cuda.current_stream().wait_stream(s)
-        g = torch.cuda.CUDAGraph()
-        before = ops.launches()
-        with torch.cuda.graph(g, pool=self.graph_pool):
-            out = run()
+        from ..utils.platform import graph_capture
+        with graph_capture():                  # no other thread of the process launches on the device meanwhile
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                for _ in range(2):
+                    run()
+            torch.cuda.current_stream().wait_stream(s)
+            g = torch.cuda.CUDAGraph()
+            before = ops.launches()
+            with torch.cuda.graph(g, pool=self.graph_pool):
+                out = run()
         self.graph_launches_per_replay[key] = ops.launches() - before
         if self.graph_pool is None:
             self.graph_pool = g.pool()
