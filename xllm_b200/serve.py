@@ -80,11 +80,27 @@ def main(argv=None):
     if ps is not None:
         from .engine.replica import lead_ranks
         lead_ranks(srv, ps)
+    etcd = None
+    if flags.get("etcd_addr"):
+        # discovery as in the reference: the instance writes itself under a leased key that a keepalive
+        # thread renews; when the process dies the key expires and the routing layer drops the instance
+        import json as _json
+        from .engine.service_client import EtcdKV
+        role = flags.get("instance_role") or "DEFAULT"
+        ns = flags.get("etcd_namespace").strip("/")
+        key = "/".join(x for x in (ns, "XLLM", role, f"{flags.get('host') or '127.0.0.1'}:{srv.port}") if x)
+        record = _json.dumps({"name": key.rsplit("/", 1)[-1], "type": role, "dp_size": flags.get_int("dp_size"),
+                              "model": name})
+        etcd = EtcdKV(flags.get("etcd_addr").split(",")[0], lease_s=float(flags.get_int("etcd_ttl")))
+        etcd.set(key, record)
+        etcd.start_keepalive(on_lost=lambda: etcd.set(key, record))
     print(f"xllm_b200 serving {name} on port {srv.port}", flush=True)
     try:
         srv.serve_forever()
     except KeyboardInterrupt:
         srv.shutdown()
+    if etcd is not None:
+        etcd.close()
     return 0
 
 
