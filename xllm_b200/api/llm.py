@@ -137,13 +137,43 @@ class LLM:
         for k, v in kwargs.items():
             if hasattr(cfg, k):
                 setattr(cfg, k, v)
-        self.engine = LLMEngine(cfg, ps=parallel_state)
+        self._workers = None
+        import os as _os
+        from ..engine.offline_worker import WorkerGroup, _Shim, parse_devices
+        devs = parse_devices(devices)
+        if len(devs) > 1 and parallel_state is None and "RANK" not in _os.environ:
+            # several devices and no launcher: this process becomes rank 0 and starts the other ranks itself
+            from ..engine.replica import lead_ranks
+            from ..parallel.state import init_parallel
+            self._workers = WorkerGroup(cfg, devs, int(kwargs.get("dp_size", 1)), int(kwargs.get("ep_size", 1)))
+            _os.environ.update(self._workers.env0)
+            if self._workers.visible is not None:
+                _os.environ["CUDA_VISIBLE_DEVICES"] = self._workers.visible
+            cfg.device = "auto"
+            parallel_state = init_parallel(dp_size=int(kwargs.get("dp_size", 1)), ep_size=int(kwargs.get("ep_size", 1)))
+            self.engine = LLMEngine(cfg, ps=parallel_state)
+            self._lead = _Shim(self.engine)
+            lead_ranks(self._lead, parallel_state)
+            import atexit
+            atexit.register(self.close)
+        else:
+            self.engine = LLMEngine(cfg, ps=parallel_state)
         self.tokenizer = tokenizer
         if tokenizer is None:
             import os
             if os.path.isdir(model):
                 from ..utils.tokenizer import load_tokenizer
                 self.tokenizer = load_tokenizer(model)
+
+    def close(self):
+        """Stops the worker ranks this object started (no-op otherwise)."""
+        if self._workers is not None:
+            w, self._workers = self._workers, None
+            try:
+                if w.alive():
+                    self._lead.shutdown()          # broadcasts "stop" to the followers
+            finally:
+                w.wait()
 
     # ------------------------------------------------------------------ helpers
     def _encode(self, p) -> List[int]:

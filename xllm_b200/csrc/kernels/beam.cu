@@ -68,19 +68,51 @@ __device__ __forceinline__ float topk_block_sum(float v, float* red) {
 }
 
 // ------------------------------------------------------------------------------------------ log-softmax
+// f(value, index) for every element of the row, this thread's share: 16-byte loads over the aligned body
+// (each thread takes whole vectors, so a warp reads 512 contiguous bytes per step), scalar head and tail.
+template <typename T, typename F>
+__device__ __forceinline__ void row_for_each(const T* __restrict__ r, int V, F f) {
+  constexpr int PER = 16 / (int)sizeof(T);
+  const int mis = (int)(((uintptr_t)r & 15) / sizeof(T));
+  const int head = mis == 0 ? 0 : min(V, PER - mis);
+  const int nvec = (V - head) / PER;
+  for (int i = threadIdx.x; i < head; i += blockDim.x) f(beam_ld<T>(r, i), i);
+  const uint4* rv = reinterpret_cast<const uint4*>(r + head);
+  for (int j = threadIdx.x; j < nvec; j += blockDim.x) {
+    const uint4 raw = rv[j];
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int t = 0; t < PER; ++t) f(beam_ld<T>(e, t), head + j * PER + t);
+  }
+  for (int i = head + nvec * PER + threadIdx.x; i < V; i += blockDim.x) f(beam_ld<T>(r, i), i);
+}
+
+// log-sum-exp of the row in ONE pass: every thread keeps a running maximum and the sum of exponentials
+// relative to it, the block combines them.
+template <typename T>
+__device__ __forceinline__ float row_lse(const T* __restrict__ r, int V, float* red) {
+  float m = -INFINITY, z = 0.f;
+  row_for_each<T>(r, V, [&](float v, int) {
+    if (v > m) {
+      z = z * __expf(m - v) + 1.f;                // m = -inf: z is 0 and so is the factor
+      m = v;
+    } else if (v > -INFINITY) {
+      z += __expf(v - m);
+    }
+  });
+  const float mx = topk_block_max(m, red);
+  z = (m > -INFINITY) ? z * __expf(m - mx) : 0.f;
+  return mx + logf(topk_block_sum(z, red));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kTopkThreads) log_softmax_kernel(const T* __restrict__ x, int64_t row_stride, int V,
                                                                    float* __restrict__ out) {
   __shared__ float red[32];
   const T* r = x + (int64_t)blockIdx.x * row_stride;
-  float mx = -INFINITY;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, beam_ld<T>(r, i));
-  mx = topk_block_max(mx, red);
-  float z = 0.f;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) z += __expf(beam_ld<T>(r, i) - mx);
-  const float lse = mx + logf(topk_block_sum(z, red));
+  const float lse = row_lse<T>(r, V, red);
   float* o = out + (int64_t)blockIdx.x * V;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) o[i] = beam_ld<T>(r, i) - lse;
+  row_for_each<T>(r, V, [&](float v, int i) { o[i] = v - lse; });   // the second read of the row hits L2
 }
 
 // ------------------------------------------------------------------------------------------ selection core
@@ -101,28 +133,47 @@ struct BeamLoader {
   __device__ __forceinline__ float operator()(int i) const { return lp[i] + cum[i / k]; }
 };
 
+constexpr int kCandMax = 3072;   // candidates kept in shared memory once the selection has narrowed to that few
+
+// Adds one key's digit to the histogram: one shared atomic per distinct digit of the warp.
+__device__ __forceinline__ void hist_add(uint32_t* s_hist, int digit) {
+  const unsigned peers = __match_any_sync(0xffffffffu, digit);
+  if (digit >= 0 && (int)(__ffs(peers) - 1) == (int)(threadIdx.x & 31)) atomicAdd(&s_hist[digit], (uint32_t)__popc(peers));
+}
+
 // Leaves the k largest keys of the row, sorted descending, in s_keys[0..k).  k <= kTopkMax, k <= n.
+//
+// Radix selection from the most significant byte of the 56-bit key down.  The passes read the row from
+// global memory only until the keys that still tie with the prefix number at most kCandMax; one more pass
+// then moves those candidates into shared memory (and the keys already known to be among the k largest
+// straight into s_keys), and the remaining bytes are resolved there.  For bf16 rows that is after two
+// passes (the 16 value bits), so a row is read three times instead of eight.
+// s_int: [0] remaining, [1] winners written, [2] ties with the new prefix, [3] candidates written.
 template <typename Loader>
 __device__ void radix_select_sorted(const Loader& ld, int k, uint64_t* s_keys, uint32_t* s_hist, uint64_t* s_prefix,
-                                    int* s_int) {
+                                    int* s_int, uint64_t* s_cand) {
   const int n = ld.n();
   uint64_t prefix = 0;
   int remaining = k;
+  int n_cand = -1;                                  // < 0: the row is still read from global memory
+  int p2 = 1;
+  while (p2 < k) p2 <<= 1;
+  for (int i = threadIdx.x; i < p2; i += blockDim.x) s_keys[i] = 0ull;
+  if (threadIdx.x == 0) s_int[1] = 0;
   for (int pass = 6; pass >= 0; --pass) {
     const int shift = pass * 8;
     for (int i = threadIdx.x; i < 256; i += blockDim.x) s_hist[i] = 0;
     __syncthreads();
     const uint64_t hi_mask = pass == 6 ? 0ull : (~0ull << (shift + 8));
-    for (int base = 0; base < n; base += blockDim.x) {
+    const int count = n_cand < 0 ? n : n_cand;
+    for (int base = 0; base < count; base += blockDim.x) {
       const int i = base + threadIdx.x;
       int digit = -1;
-      if (i < n) {
-        const uint64_t key = make_key(ld(i), i);
+      if (i < count) {
+        const uint64_t key = n_cand < 0 ? make_key(ld(i), i) : s_cand[i];
         if ((key & hi_mask) == prefix) digit = (int)((key >> shift) & 255u);
       }
-      // one shared atomic per distinct digit of the warp
-      const unsigned peers = __match_any_sync(0xffffffffu, digit);
-      if (digit >= 0 && (int)(__ffs(peers) - 1) == (int)(threadIdx.x & 31)) atomicAdd(&s_hist[digit], (uint32_t)__popc(peers));
+      hist_add(s_hist, digit);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -132,24 +183,48 @@ __device__ void radix_select_sorted(const Loader& ld, int k, uint64_t* s_keys, u
         acc += (int)s_hist[d];
       }
       s_int[0] = remaining - acc;
+      s_int[2] = (int)s_hist[d];
+      s_int[3] = 0;
       *s_prefix = prefix | ((uint64_t)d << shift);
     }
     __syncthreads();
     prefix = *s_prefix;
     remaining = s_int[0];
+    const int ties = s_int[2];
     __syncthreads();
+    if (n_cand < 0 && pass > 0 && ties <= kCandMax) {
+      const uint64_t mask = ~0ull << shift;         // the bytes decided so far
+      for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const uint64_t key = make_key(ld(i), i);
+        const uint64_t top = key & mask;
+        if (top == prefix) {
+          const int slot = atomicAdd(&s_int[3], 1);
+          if (slot < kCandMax) s_cand[slot] = key;
+        } else if (top > prefix) {                  // larger in a decided byte: one of the k largest for certain
+          const int slot = atomicAdd(&s_int[1], 1);
+          if (slot < p2) s_keys[slot] = key;
+        }
+      }
+      __syncthreads();
+      n_cand = min(s_int[3], kCandMax);
+    }
   }
-  // prefix is now the k-th largest key: gather everything >= it (exactly k keys)
-  int p2 = 1;
-  while (p2 < k) p2 <<= 1;
-  for (int i = threadIdx.x; i < p2; i += blockDim.x) s_keys[i] = 0ull;
-  if (threadIdx.x == 0) s_int[1] = 0;
-  __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const uint64_t key = make_key(ld(i), i);
-    if (key >= prefix) {
-      const int slot = atomicAdd(&s_int[1], 1);
-      if (slot < p2) s_keys[slot] = key;
+  // prefix is now the k-th largest key: everything >= it that is not in s_keys yet joins (k keys in all)
+  if (n_cand < 0) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const uint64_t key = make_key(ld(i), i);
+      if (key >= prefix) {
+        const int slot = atomicAdd(&s_int[1], 1);
+        if (slot < p2) s_keys[slot] = key;
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < n_cand; i += blockDim.x) {
+      const uint64_t key = s_cand[i];
+      if (key >= prefix) {
+        const int slot = atomicAdd(&s_int[1], 1);
+        if (slot < p2) s_keys[slot] = key;
+      }
     }
   }
   __syncthreads();
@@ -175,20 +250,16 @@ __global__ void __launch_bounds__(kTopkThreads) radix_topk_kernel(const T* __res
   __shared__ uint64_t s_keys[kTopkMax];
   __shared__ uint32_t s_hist[256];
   __shared__ uint64_t s_prefix;
-  __shared__ int s_int[2];
+  __shared__ int s_int[4];
+  __shared__ uint64_t s_cand[kCandMax];
   __shared__ float red[32];
   const T* r = x + (int64_t)blockIdx.x * row_stride;
   float lse = 0.f;
   if (normalize) {
-    float mx = -INFINITY;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, beam_ld<T>(r, i));
-    mx = topk_block_max(mx, red);
-    float z = 0.f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) z += __expf(beam_ld<T>(r, i) - mx);
-    lse = mx + logf(topk_block_sum(z, red));
+    lse = row_lse<T>(r, V, red);
   }
   RowLoader<T> ld{r, V};
-  radix_select_sorted(ld, k, s_keys, s_hist, &s_prefix, s_int);
+  radix_select_sorted(ld, k, s_keys, s_hist, &s_prefix, s_int, s_cand);
   for (int i = threadIdx.x; i < k; i += blockDim.x) {
     const uint64_t key = s_keys[i];
     out_ids[(int64_t)blockIdx.x * k + i] = (int32_t)(0xFFFFFFu - (uint32_t)(key & 0xFFFFFFu));
@@ -206,10 +277,11 @@ __global__ void __launch_bounds__(kTopkThreads) beam_step_kernel(const float* __
   __shared__ uint64_t s_keys[kTopkMax];
   __shared__ uint32_t s_hist[256];
   __shared__ uint64_t s_prefix;
-  __shared__ int s_int[2];
+  __shared__ int s_int[4];
+  __shared__ uint64_t s_cand[kCandMax];
   const int b = blockIdx.x;
   BeamLoader ld{cand_lp + (int64_t)b * W * k, cum + (int64_t)b * W, W, k};
-  radix_select_sorted(ld, n_out, s_keys, s_hist, &s_prefix, s_int);
+  radix_select_sorted(ld, n_out, s_keys, s_hist, &s_prefix, s_int, s_cand);
   for (int i = threadIdx.x; i < n_out; i += blockDim.x) {
     const uint64_t key = s_keys[i];
     const int idx = (int)(0xFFFFFFu - (uint32_t)(key & 0xFFFFFFu));

@@ -127,28 +127,54 @@ __global__ void __launch_bounds__(gdn_reg_max_threads(R)) gdn_prefill_reg_kernel
   float s[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) s[r] = (live && !fresh) ? S[(int64_t)r * dv] : 0.f;
-  auto stage = [&](int t, int buf) {
+  // Software pipeline over tokens, so that no global load is waited for inside a step: k_t / q_t travel
+  // global -> registers (issued two steps ahead) -> shared memory (stored one step ahead, after the step's
+  // first barrier); v_t, g_t, beta_t are loaded one step ahead into registers.
+  constexpr int KQ = dk >= 64 ? dk / 64 : 1;        // k|q values per thread (blockDim.x >= 32: 2 dk / 128 at most)
+  float kq_next[KQ];
+  auto fetch = [&](int t, float* dst) {             // this thread's share of token t's k | q
     const int64_t row = (int64_t)t * nv + h;
-    float* dst = kq + buf * 2 * dk;
-    for (int i = tid; i < 2 * dk; i += nthreads) dst[i] = i < dk ? k[row * dk + i] : q[row * dk + (i - dk)];
+#pragma unroll
+    for (int e = 0; e < KQ; ++e) {
+      const int i = tid + e * nthreads;
+      dst[e] = i < 2 * dk ? (i < dk ? k[row * dk + i] : q[row * dk + (i - dk)]) : 0.f;
+    }
   };
-  stage(0, 0);
+  auto put = [&](const float* src, int buf) {
+    float* dst = kq + buf * 2 * dk;
+#pragma unroll
+    for (int e = 0; e < KQ; ++e) {
+      const int i = tid + e * nthreads;
+      if (i < 2 * dk) dst[i] = src[e];
+    }
+  };
+  fetch(0, kq_next);
+  put(kq_next, 0);
+  if (n > 1) fetch(1, kq_next);
+  float v_n = live ? v[(int64_t)h * dv + j] : 0.f, g_n = g[h], b_n = beta[h];
   __syncthreads();
   for (int t = 0; t < n; ++t) {
     const int buf = t & 1;
     const float* ks = kq + buf * 2 * dk;
     const float* qs = ks + dk;
     const int64_t row = (int64_t)t * nv + h;
-    if (t + 1 < n) stage(t + 1, buf ^ 1);           // visible after the next barrier
-    const float decay = __expf(g[row]);
-    const float bt = beta[row];
+    const float v_t = v_n, decay = __expf(g_n), bt = b_n;
+    float kq_far[KQ];
+    if (t + 2 < n) fetch(t + 2, kq_far);            // consumed at the end of the NEXT step
+    if (t + 1 < n) {
+      const int64_t nrow = row + nv;
+      v_n = live ? v[nrow * dv + j] : 0.f;
+      g_n = g[nrow];
+      b_n = beta[nrow];
+    }
     float part = 0.f;
 #pragma unroll
     for (int r = 0; r < R; ++r) part += s[r] * ks[gy * R + r];
     red_a[gy * dvp + tx] = part;
     __syncthreads();
+    if (t + 1 < n) put(kq_next, buf ^ 1);           // that buffer was last read in step t-1: all threads are past it
     const float kv = (red_a[tx] + red_a[dvp + tx] + red_a[2 * dvp + tx] + red_a[3 * dvp + tx]) * decay;
-    const float delta = ((live ? v[row * dv + j] : 0.f) - kv) * bt;
+    const float delta = (v_t - kv) * bt;
     float o = 0.f;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -158,6 +184,8 @@ __global__ void __launch_bounds__(gdn_reg_max_threads(R)) gdn_prefill_reg_kernel
     red_b[gy * dvp + tx] = o;
     __syncthreads();
     if (gy == 0 && live) out[row * dv + j] = red_b[tx] + red_b[dvp + tx] + red_b[2 * dvp + tx] + red_b[3 * dvp + tx];
+#pragma unroll
+    for (int e = 0; e < KQ; ++e) kq_next[e] = kq_far[e];
   }
   if (live) {
 #pragma unroll

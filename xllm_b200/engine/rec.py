@@ -176,7 +176,7 @@ class RecEngine:
             tail.n_tail = s
             meta = AttentionMetadata(n_decode=0, n_prefill=R, slots=row_ids * tail.cap + (s - 1), block_table=bt,
                                      kv_lens=kv_lens, cu_q=cu_b, max_q_len=W, max_kv_len=max(lens) + s, xattn=tail)
-            h = model.forward(seqs[:, :, -1].reshape(rows), row_pos + (s - 1), meta, kv)
+            h = model.forward(seqs[:, :, -1].reshape(rows).contiguous(), row_pos + (s - 1), meta, kv)
             logits = self._logits(model, h)                                # [R*W, V]
             lp, ids = self._candidates(logits, k_cand, trie, None if trie is None else seqs.reshape(rows, -1).tolist(),
                                        dev)                                # [R*W, k]

@@ -13,6 +13,8 @@ import torch
 from . import _lib, reference
 from ._lib import check, ptr, stream
 
+from . import _debug  # noqa: E402
+
 _launch_count = 0
 
 
@@ -29,6 +31,16 @@ def _count(n=1):
 
 def _lib_():
     return _lib.load()
+
+
+def _index(t, dtype, name):
+    """Index-like kernel input (token ids, positions, slots, lengths): the kernels read it as a dense
+    array of `dtype` through a raw pointer, so a strided view or another integer width must be copied."""
+    if t is None:
+        return None
+    if t.dtype != dtype:
+        raise TypeError(f"{name}: expected {dtype}, got {t.dtype}")
+    return t if t.is_contiguous() else t.contiguous()
 
 
 def _bf16(t, name):
@@ -92,6 +104,10 @@ def rope_kv_write(qkv, nq, nkv, d, positions, cos_sin, rot, slots=None, k_cache=
 
     Returns q [T, nq, d] (and dense k, v when return_kv)."""
     T = qkv.shape[0]
+    if _debug.enabled():
+        _debug.check_range(positions, 0, cos_sin.shape[0], "rope_kv_write positions")
+        if k_cache is not None and slots is not None:
+            _debug.check_range(slots, 0, k_cache.shape[0] * k_cache.shape[2], "rope_kv_write slots", allow_negative_skip=True)
     if not qkv.is_cuda:
         q, k, v = reference.rope_kv(qkv, nq, nkv, d, positions, cos_sin, rot, q_norm_w, k_norm_w,
                                     eps, interleaved)
@@ -100,6 +116,8 @@ def rope_kv_write(qkv, nq, nkv, d, positions, cos_sin, rot, slots=None, k_cache=
         return (q, k, v) if return_kv else q
     _bf16(qkv, "rope_kv_write")
     assert qkv.stride(-1) == 1
+    positions = _index(positions, torch.int64, "rope_kv_write positions")
+    slots = _index(slots, torch.int32, "rope_kv_write slots")
     if q_out is None:
         q_out = torch.empty((T, nq, d), dtype=qkv.dtype, device=qkv.device)
     k_out = v_out = None
@@ -136,6 +154,7 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, scale, sp
     """q: [B, nq, d] (one query token per sequence) -> [B, nq, d].  `window` > 0: every query sees
     its last `window` positions only (pages before them are not read)."""
     window = int(window or 0)
+    _debug.check_block_table(block_table, seq_lens, k_cache.shape[0], k_cache.shape[2], "paged_decode_attention")
     if not q.is_cuda:
         y = reference.paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, scale, window)
         if out is not None:
@@ -143,6 +162,8 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, scale, sp
             return out
         return y
     _bf16(q, "paged_decode_attention")
+    seq_lens = _index(seq_lens, torch.int32, "paged_decode_attention seq_lens")
+    assert block_table.dtype == torch.int32 and block_table.stride(-1) == 1
     B, nq, d = q.shape
     nkv, page = k_cache.shape[1], k_cache.shape[2]
     if splits is None:
@@ -169,6 +190,9 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, scale, sp
 def paged_prefill_attention(q, k_cache, v_cache, block_table, cu_q, kv_lens, max_q_len, scale,
                             causal=True, window=0, out=None):
     """q: [T, nq, d] ragged by cu_q -> [T, nq, d]; attends to cache positions [0, kv_len)."""
+    if _debug.enabled():
+        _debug.check_block_table(block_table, kv_lens, k_cache.shape[0], k_cache.shape[2], "paged_prefill_attention")
+        _debug.check_range(cu_q, 0, q.shape[0] + 1, "paged_prefill_attention cu_q")
     if not q.is_cuda:
         y = reference.paged_attention(q, k_cache, v_cache, block_table, cu_q, kv_lens, scale,
                                       causal, window)
@@ -178,6 +202,9 @@ def paged_prefill_attention(q, k_cache, v_cache, block_table, cu_q, kv_lens, max
             return out
         return y
     _bf16(q, "paged_prefill_attention")
+    cu_q = _index(cu_q, torch.int32, "paged_prefill_attention cu_q")
+    kv_lens = _index(kv_lens, torch.int32, "paged_prefill_attention kv_lens")
+    assert block_table.dtype == torch.int32 and block_table.stride(-1) == 1
     T, nq, d = q.shape
     nkv, page = k_cache.shape[1], k_cache.shape[2]
     if out is None:
@@ -285,12 +312,14 @@ def apply_penalties(logits, ids, counts, freq=None, presence=None, repetition=No
 
 # ----------------------------------------------------------------------------- data movement
 def embedding(ids, table, vocab_start=0, out=None):
+    _debug.check_range(ids, 0, 1 << 31, "embedding ids")           # a vocabulary shard zero-fills ids of other shards
     if not table.is_cuda:
         loc = ids - vocab_start
         ok = (loc >= 0) & (loc < table.shape[0])
         y = table[loc.clamp(0, table.shape[0] - 1)]
         return y * ok[:, None].to(y.dtype)
     _bf16(table, "embedding")
+    ids = _index(ids, torch.int64, "embedding ids")
     T, H = ids.shape[0], table.shape[1]
     if out is None:
         out = torch.empty((T, H), dtype=table.dtype, device=table.device)
@@ -301,6 +330,7 @@ def embedding(ids, table, vocab_start=0, out=None):
 
 
 def gather_rows(x, idx, out=None):
+    _debug.check_range(idx, 0, x.shape[0], "gather_rows idx")
     if not x.is_cuda:
         return x[idx]
     rows = idx.shape[0]

@@ -69,6 +69,11 @@ def xattention(q, k_cache, v_cache, block_table, cu_q, kv_lens, max_rows, ku, vu
                out=None):
     """q [T, nq, d] (rows of request b: cu_q[b]:cu_q[b+1], at most `max_rows` per request) -> [T, nq, d]."""
     assert 0 <= n_tail <= min(TAIL_MAX, ku.shape[2])
+    from . import _debug
+    if _debug.enabled():
+        _debug.check_block_table(block_table, kv_lens, k_cache.shape[0], k_cache.shape[2], "xattention")
+        _debug.check_range(anc[:n_tail], 0, ku.shape[0], "xattention ancestor rows")
+        _debug.check_range(cu_q, 0, q.shape[0] + 1, "xattention cu_q")
     if not supported(q, k_cache):
         if q.is_cuda:
             from .gemm import _note_fallback
@@ -81,6 +86,8 @@ def xattention(q, k_cache, v_cache, block_table, cu_q, kv_lens, max_rows, ku, vu
     T, nq, d = q.shape
     nkv, page = k_cache.shape[1], k_cache.shape[2]
     assert q.stride(-1) == 1 and q.stride(1) == d
+    assert block_table.dtype == torch.int32 and block_table.stride(-1) == 1
+    cu_q, kv_lens = cu_q.to(torch.int32).contiguous(), kv_lens.to(torch.int32).contiguous()
     if out is None:
         out = torch.empty((T, nq, d), dtype=q.dtype, device=q.device)
     lse = torch.empty((T, nq), dtype=torch.float32, device=q.device)
@@ -90,7 +97,9 @@ def xattention(q, k_cache, v_cache, block_table, cu_q, kv_lens, max_rows, ku, vu
                                              k_cache.shape[0], ptr(block_table), block_table.stride(0), ptr(cu_q),
                                              ptr(kv_lens), B, int(max_rows), nq, nkv, page, scale, 0, ptr(lse), stream()),
           "xattention shared stage")
-    anc = anc if anc.dtype == torch.int32 else anc.to(torch.int32)
+    anc = (anc if anc.dtype == torch.int32 else anc.to(torch.int32))
+    if anc.stride(-1) != 1:
+        anc = anc.contiguous()
     check(lib.xllm_xattn_tail_merge(ptr(out), out.stride(0), ptr(lse), ptr(q), q.stride(0), ptr(ku), ptr(vu), ptr(anc),
                                     anc.stride(0), int(n_tail), T, nq, nkv, d, ku.shape[2], scale, stream()),
           "xattention tail merge")

@@ -113,8 +113,13 @@ class ParallelState:
         if g is None or dist.get_world_size(g) == 1:
             return x
         n = dist.get_world_size(g)
-        out = torch.empty((n,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, x.contiguous(), group=g)
+        x = x.contiguous()
+        if x.dim() == 0:
+            x = x.view(1)
+        # concatenated along dim 0: the one output form every backend takes (gloo refuses the stacked one)
+        flat = torch.empty((n * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(flat, x, group=g)
+        out = flat.view((n,) + tuple(x.shape))
         if dim == 0:
             return out.reshape((n * x.shape[0],) + tuple(x.shape[1:]))
         d = dim % x.dim()
