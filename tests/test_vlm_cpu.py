@@ -108,3 +108,111 @@ def test_vlm_engine_matches_dense_reference():
             seq.append(int(logits[-1].argmax()))
         assert g == seq[len(ids):], (g, seq[len(ids):])
     assert not vlm.engine.mm
+
+
+def test_vlm_engine_with_a_video_and_an_image_matches_dense_reference():
+    VID = 903
+    args = _args()
+    args.video_token_id = VID
+    vlm = VLM.__new__(VLM)
+    vlm.engine = LLMEngine(EngineConfig(model="v", device="cpu", dtype="float32", num_blocks=64, enable_graph=False,
+                                        max_tokens_per_batch=32, enable_schedule_overlap=False), model_args=args)
+    vlm.tokenizer = None
+    model = vlm.engine.model
+    model.init_random(std=0.05, seed=5)
+    vlm.processor = Qwen2VLImageProcessor(14, 2, 2, min_pixels=56 * 56, max_pixels=112 * 112)
+    from xllm_b200.multimodal import Qwen2VLVideoProcessor
+    vlm.video_processor = Qwen2VLVideoProcessor(14, 2, 2, min_pixels=56 * 56, max_pixels=84 * 84)
+    vlm.image_token_id = IMG
+    rng = np.random.default_rng(2)
+    img = (rng.random((56, 84, 3)) * 255).astype(np.uint8)
+    video = torch.from_numpy((rng.random((3, 3, 60, 60)) * 255).astype(np.uint8))     # 3 frames -> padded to 4
+    req = dict(prompt_token_ids=[11, VSTART, VID, VEND, 12, VSTART, IMG, VEND, 13], images=[img], videos=[video])
+    got = vlm.generate_mm([req], SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True))[0]
+    ids, mm = vlm.prepare(req["prompt_token_ids"], [img], [video])
+    n_vid = sum(1 for t in ids if t == VID)
+    n_img = sum(1 for t in ids if t == IMG)
+    assert n_vid == 2 * 2 * 2 and n_img == 2 * 3 and mm.embeds.shape[0] == n_vid + n_img
+    assert ids.index(VID) < ids.index(IMG) and mm.positions == [i for i, t in enumerate(ids) if t in (VID, IMG)]
+    # the video's two frame groups sit at consecutive temporal positions, rows / columns restart per group
+    v0 = ids.index(VID)
+    assert mm.mrope[0, v0:v0 + 8].tolist() == [2] * 4 + [3] * 4 and mm.mrope[1, v0:v0 + 4].tolist() == [2, 2, 3, 3]
+    seq = list(ids)
+    for _ in range(4):
+        L = len(seq)
+        pos3 = torch.cat([mm.mrope, (torch.arange(mm.mrope.shape[1], L) + mm.delta).repeat(3, 1)], dim=1)
+        logits = _dense_reference(model, torch.tensor(seq), torch.tensor(mm.positions), mm.embeds, pos3)
+        seq.append(int(logits[-1].argmax()))
+    assert got == seq[len(ids):]
+
+
+def test_chat_route_takes_image_parts(tmp_path):
+    """`/v1/chat/completions` with an image_url part (a data: URL): the server decodes the image, renders
+    the placeholder through the chat template, runs the vision tower and generates; the same request
+    without the image generates something else, and a text-only model refuses image parts."""
+    import base64
+    import http.client
+    import io
+    import json
+    import threading
+
+    from PIL import Image
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+
+    from xllm_b200 import _rt
+    from xllm_b200.api.server import ApiServer
+    from xllm_b200.utils.tokenizer import TokenizerWrapper
+    tok = Tokenizer(models.BPE())
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+    tok.decoder = decoders.ByteLevel()
+    specials = ["<|im_start|>", "<|im_end|>", "<|endoftext|>", "<|vision_start|>", "<|vision_end|>", "<|image_pad|>",
+                "<|video_pad|>"]
+    trainer = trainers.BpeTrainer(vocab_size=400, special_tokens=specials, initial_alphabet=pre_tokenizers.ByteLevel.alphabet())
+    tok.train_from_iterator(["describe this picture please user assistant system\n" * 5], trainer)
+    path = tmp_path / "tokenizer.json"
+    tok.save(str(path))
+    impl = _rt.BpeTokenizer()
+    impl.load_hf_file(str(path))
+    wrapper = TokenizerWrapper(impl, "", {}, "qwen3")
+    ids = {s: wrapper.encode(s)[0] for s in specials}
+    args = _args()
+    args.image_token_id, args.video_token_id = ids["<|image_pad|>"], ids["<|video_pad|>"]
+    args.vision_start_token_id = ids["<|vision_start|>"]
+    eng = LLMEngine(EngineConfig(model="v", device="cpu", dtype="float32", num_blocks=64, enable_graph=False,
+                                 max_tokens_per_batch=64), model_args=args)
+    eng.model.init_random(std=0.05, seed=3)
+    srv = ApiServer(eng, wrapper, model_name="tiny-vl", host="127.0.0.1", port=0)
+    t = threading.Thread(target=srv.serve_forever, args=(10,), daemon=True)
+    t.start()
+
+    def chat(content):
+        c = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=60)
+        c.request("POST", "/v1/chat/completions", json.dumps({"messages": [{"role": "user", "content": content}],
+                                                              "max_tokens": 6, "temperature": 0, "ignore_eos": True}),
+                  {"Content-Type": "application/json"})
+        r = c.getresponse()
+        out = json.loads(r.read().decode())
+        c.close()
+        return r.status, out
+
+    try:
+        rng = np.random.default_rng(0)
+        buf = io.BytesIO()
+        Image.fromarray((rng.random((56, 84, 3)) * 255).astype(np.uint8)).save(buf, format="PNG")
+        url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+        st, with_img = chat([{"type": "text", "text": "describe this picture"}, {"type": "image_url", "image_url": {"url": url}}])
+        assert st == 200 and with_img["usage"]["completion_tokens"] == 6
+        n_img_tokens = (56 // 14) * (84 // 14) // 4
+        st, text_only = chat("describe this picture")
+        assert st == 200
+        assert with_img["usage"]["prompt_tokens"] == text_only["usage"]["prompt_tokens"] + n_img_tokens + 2
+        st, again = chat([{"type": "text", "text": "describe this picture"}, {"type": "image_url", "image_url": {"url": url}}])
+        assert again["choices"][0]["message"]["content"] == with_img["choices"][0]["message"]["content"]
+        st, bad = chat([{"type": "image_url", "image_url": {"url": "https://example.com/x.png"}}])
+        assert st == 400 and "data:" in bad["error"]["message"]
+        st, bad = chat([{"type": "image_url", "image_url": {"url": "data:image/png;base64,AAAA"}}])
+        assert st == 400
+        assert not eng.mm
+    finally:
+        srv.shutdown()
+        t.join(timeout=5)

@@ -478,6 +478,12 @@ class ApiServer:
         if self.engine.scheduler.paused():
             return self._error(req.id, 503, "the instance is paused", "unavailable")
         n = call.n
+        if "mm_raw" in sampling:
+            images, videos = sampling.pop("mm_raw")
+            try:
+                prompt_ids, sampling["mm"] = self._vlm_prepare(prompt_ids, images, videos)
+            except ValueError as e:
+                return self._error(req.id, 400, str(e))
         call.prompt_tokens = len(prompt_ids)
         call.t_arrival = time.time()
         call.want_logprobs = sampling["logprobs"]
@@ -585,6 +591,10 @@ class ApiServer:
             messages = [{"role": "system", "content": sys_text}] + messages
         if not messages:
             return self._error(req.id, 400, "`messages` must not be empty")
+        try:
+            messages, images, videos = self._media_from_messages(messages)
+        except ValueError as e:
+            return self._error(req.id, 400, str(e))
         kwargs = dict(body.get("chat_template_kwargs") or {})
         t0 = time.perf_counter()
         prompt = self.tok.apply_chat_template(messages, tools=body.get("tools"), add_generation_prompt=True,
@@ -594,11 +604,81 @@ class ApiServer:
         _rt.metric_counter_add("chat_template_latency_seconds", t1 - t0)
         _rt.metric_counter_add("tokenization_latency_seconds", time.perf_counter() - t1)
         sampling, stops = self._sampling(body)
+        if images or videos:
+            sampling["mm_raw"] = (images, videos)          # the vision tower runs on the engine thread (_admit)
         rid = req.header("x-request-id") or (f"msg_{uuid.uuid4().hex}" if kind == "anthropic" else f"chatcmpl-{uuid.uuid4().hex}")
         call = _Call(req.id, rid, kind, bool(body.get("stream")), body.get("model") or self.model_name,
                      int(time.time()), n=int(body.get("n", 1)),
                      include_usage=bool((body.get("stream_options") or {}).get("include_usage")))
         self._submit(req, call, ids, sampling, stops)
+
+    # ---- multimodal chat content (xllm/api_service/mm_service_utils.cpp: image_url / video_url parts)
+    IMAGE_MARK = "<|vision_start|><|image_pad|><|vision_end|>"
+    VIDEO_MARK = "<|vision_start|><|video_pad|><|vision_end|>"
+
+    @staticmethod
+    def _load_media(url: str, kind: str):
+        import base64
+        import io
+        if url.startswith("data:"):
+            head, _, payload = url.partition(",")
+            if ";base64" not in head:
+                raise ValueError("data: URLs must be base64-encoded")
+            raw = base64.b64decode(payload)
+        elif url.startswith("file://") or os.path.exists(url):
+            with open(url[7:] if url.startswith("file://") else url, "rb") as f:
+                raw = f.read()
+        else:
+            raise ValueError(f"cannot fetch {kind} from {url[:40]!r}: only data: URLs and local files are served here")
+        if kind == "image":
+            from PIL import Image
+            try:
+                return Image.open(io.BytesIO(raw)).convert("RGB")
+            except Exception as e:
+                raise ValueError(f"undecodable image: {e}")
+        from ..multimodal.media import decode_video
+        return decode_video(raw)[0]
+
+    def _media_from_messages(self, messages):
+        """Content lists with image_url / video_url parts become text with the model's placeholder marks;
+        returns (messages with string contents, images, videos)."""
+        images, videos, out = [], [], []
+        for m in messages:
+            c = m.get("content")
+            if not isinstance(c, list):
+                out.append(m)
+                continue
+            text = []
+            for part in c:
+                t = part.get("type")
+                if t in ("text", "input_text"):
+                    text.append(part.get("text", ""))
+                elif t in ("image_url", "image"):
+                    src = part.get("image_url") or part.get("image") or {}
+                    images.append(self._load_media(src.get("url") if isinstance(src, dict) else src, "image"))
+                    text.append(self.IMAGE_MARK)
+                elif t in ("video_url", "video"):
+                    src = part.get("video_url") or part.get("video") or {}
+                    videos.append(self._load_media(src.get("url") if isinstance(src, dict) else src, "video"))
+                    text.append(self.VIDEO_MARK)
+                else:
+                    raise ValueError(f"unsupported content part type {t!r}")
+            out.append(dict(m, content="".join(text)))
+        if (images or videos) and not hasattr(self.engine.model, "visual"):
+            raise ValueError("this model takes text only")
+        return out, images, videos
+
+    def _vlm_prepare(self, ids, images, videos):
+        if getattr(self, "_vlm", None) is None:
+            from ..multimodal.image import Qwen2VLImageProcessor
+            from .vlm import VLM
+            v = VLM.__new__(VLM)
+            v.engine, v.tokenizer = self.engine, self.tok
+            vis = self.engine.model.visual
+            v.processor = Qwen2VLImageProcessor(vis.patch, vis.merge, vis.tp)
+            v.image_token_id = self.engine.args.image_token_id
+            self._vlm = v
+        return self._vlm.prepare(ids, images, videos)
 
     def _embeddings(self, req, body):
         inp = body.get("input", "")

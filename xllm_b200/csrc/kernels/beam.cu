@@ -112,7 +112,30 @@ __global__ void __launch_bounds__(kTopkThreads) log_softmax_kernel(const T* __re
   const T* r = x + (int64_t)blockIdx.x * row_stride;
   const float lse = row_lse<T>(r, V, red);
   float* o = out + (int64_t)blockIdx.x * V;
-  row_for_each<T>(r, V, [&](float v, int i) { o[i] = v - lse; });   // the second read of the row hits L2
+  // the second read of the row hits L2; 16-byte loads and, where the output lines up, 16-byte stores
+  constexpr int PER = 16 / (int)sizeof(T);
+  const int mis = (int)(((uintptr_t)r & 15) / sizeof(T));
+  const int head = mis == 0 ? 0 : min(V, PER - mis);
+  const int nvec = (V - head) / PER;
+  for (int i = threadIdx.x; i < head; i += blockDim.x) o[i] = beam_ld<T>(r, i) - lse;
+  const uint4* rv = reinterpret_cast<const uint4*>(r + head);
+  const bool o_aligned = (((uintptr_t)(o + head)) & 15) == 0;
+  for (int j = threadIdx.x; j < nvec; j += blockDim.x) {
+    const uint4 raw = rv[j];
+    const T* e = reinterpret_cast<const T*>(&raw);
+    float f[PER];
+#pragma unroll
+    for (int t = 0; t < PER; ++t) f[t] = beam_ld<T>(e, t) - lse;
+    float* dst = o + head + (int64_t)j * PER;
+    if (o_aligned) {
+#pragma unroll
+      for (int t = 0; t < PER; t += 4) *reinterpret_cast<float4*>(dst + t) = make_float4(f[t], f[t + 1], f[t + 2], f[t + 3]);
+    } else {
+#pragma unroll
+      for (int t = 0; t < PER; ++t) dst[t] = f[t];
+    }
+  }
+  for (int i = head + nvec * PER + threadIdx.x; i < V; i += blockDim.x) o[i] = beam_ld<T>(r, i) - lse;
 }
 
 // ------------------------------------------------------------------------------------------ selection core

@@ -167,21 +167,31 @@ __global__ void __launch_bounds__(gdn_reg_max_threads(R)) gdn_prefill_reg_kernel
       g_n = g[nrow];
       b_n = beta[nrow];
     }
-    float part = 0.f;
+    // this thread's R values of k_t and q_t: 16-byte shared loads (the whole warp reads the same address),
+    // four independent partial sums so that the multiply-adds pipeline
+    float kr[R], qr[R];
 #pragma unroll
-    for (int r = 0; r < R; ++r) part += s[r] * ks[gy * R + r];
-    red_a[gy * dvp + tx] = part;
+    for (int r = 0; r < R; r += 4) {
+      const float4 a = *reinterpret_cast<const float4*>(ks + gy * R + r);
+      const float4 b = *reinterpret_cast<const float4*>(qs + gy * R + r);
+      kr[r] = a.x; kr[r + 1] = a.y; kr[r + 2] = a.z; kr[r + 3] = a.w;
+      qr[r] = b.x; qr[r + 1] = b.y; qr[r + 2] = b.z; qr[r + 3] = b.w;
+    }
+    float p4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < R; ++r) p4[r & 3] += s[r] * kr[r];
+    red_a[gy * dvp + tx] = (p4[0] + p4[1]) + (p4[2] + p4[3]);
     __syncthreads();
     if (t + 1 < n) put(kq_next, buf ^ 1);           // that buffer was last read in step t-1: all threads are past it
     const float kv = (red_a[tx] + red_a[dvp + tx] + red_a[2 * dvp + tx] + red_a[3 * dvp + tx]) * decay;
     const float delta = (v_t - kv) * bt;
-    float o = 0.f;
+    float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      s[r] = s[r] * decay + ks[gy * R + r] * delta;
-      o += s[r] * qs[gy * R + r];
+      s[r] = s[r] * decay + kr[r] * delta;
+      o4[r & 3] += s[r] * qr[r];
     }
-    red_b[gy * dvp + tx] = o;
+    red_b[gy * dvp + tx] = (o4[0] + o4[1]) + (o4[2] + o4[3]);
     __syncthreads();
     if (gy == 0 && live) out[row * dv + j] = red_b[tx] + red_b[dvp + tx] + red_b[2 * dvp + tx] + red_b[3 * dvp + tx];
 #pragma unroll
