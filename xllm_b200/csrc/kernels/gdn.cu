@@ -109,7 +109,8 @@ __global__ void __launch_bounds__(gdn_reg_max_threads(R)) gdn_decode_reg_kernel(
 // The reference reaches this through FLA's chunked Triton kernels
 // (xllm/python/kernels_cuda/triton/gdn_prefill.py); this is the fused-recurrent form of the same rule.
 template <int R>
-__global__ void __launch_bounds__(gdn_reg_max_threads(R)) gdn_prefill_reg_kernel(
+__global__ void __launch_bounds__(256) gdn_prefill_reg_kernel(   // the launcher uses at most 64 x 4 threads
+
     float* __restrict__ state, int64_t slot, int fresh, const float* __restrict__ q, const float* __restrict__ k,
     const float* __restrict__ v, const float* __restrict__ g, const float* __restrict__ beta, float* __restrict__ out,
     int n, int nv, int dv) {
@@ -127,18 +128,27 @@ __global__ void __launch_bounds__(gdn_reg_max_threads(R)) gdn_prefill_reg_kernel
   float s[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) s[r] = (live && !fresh) ? S[(int64_t)r * dv] : 0.f;
-  // Software pipeline over tokens, so that no global load is waited for inside a step: k_t / q_t travel
-  // global -> registers (issued two steps ahead) -> shared memory (stored one step ahead, after the step's
-  // first barrier); v_t, g_t, beta_t are loaded one step ahead into registers.
+  // Software pipeline over tokens, so that no global load is waited for inside a step: the inputs of token
+  // t + D are requested while token t is computed and sit in a ring of D register slots (slot = t mod D, the
+  // token loop is unrolled D times so that the slots are plain registers).  k_t / q_t go from their slot to
+  // shared memory one step before they are used (after that step's first barrier), v_t, g_t, beta_t are
+  // read from their slot directly.
   constexpr int KQ = dk >= 64 ? dk / 64 : 1;        // k|q values per thread (blockDim.x >= 32: 2 dk / 128 at most)
-  float kq_next[KQ];
+  constexpr int D = R >= 64 ? 2 : 8;                // ring depth (the largest state leaves few registers)
+  float kq_r[D][KQ], v_r[D], g_r[D], b_r[D];
   auto fetch = [&](int t, float* dst) {             // this thread's share of token t's k | q
     const int64_t row = (int64_t)t * nv + h;
 #pragma unroll
     for (int e = 0; e < KQ; ++e) {
       const int i = tid + e * nthreads;
-      dst[e] = i < 2 * dk ? (i < dk ? k[row * dk + i] : q[row * dk + (i - dk)]) : 0.f;
+      dst[e] = (t < n && i < 2 * dk) ? (i < dk ? k[row * dk + i] : q[row * dk + (i - dk)]) : 0.f;
     }
+  };
+  auto fetch_vgb = [&](int t, float& vv, float& gg, float& bb) {
+    const int64_t row = (int64_t)t * nv + h;
+    vv = (t < n && live) ? v[row * dv + j] : 0.f;
+    gg = t < n ? g[row] : 0.f;
+    bb = t < n ? beta[row] : 0.f;
   };
   auto put = [&](const float* src, int buf) {
     float* dst = kq + buf * 2 * dk;
@@ -148,54 +158,57 @@ __global__ void __launch_bounds__(gdn_reg_max_threads(R)) gdn_prefill_reg_kernel
       if (i < 2 * dk) dst[i] = src[e];
     }
   };
-  fetch(0, kq_next);
-  put(kq_next, 0);
-  if (n > 1) fetch(1, kq_next);
-  float v_n = live ? v[(int64_t)h * dv + j] : 0.f, g_n = g[h], b_n = beta[h];
+#pragma unroll
+  for (int d = 0; d < D; ++d) {
+    fetch(d, kq_r[d]);
+    fetch_vgb(d, v_r[d], g_r[d], b_r[d]);
+  }
+  put(kq_r[0], 0);
+  fetch(D, kq_r[0]);                                // slot 0 is free again: token D
   __syncthreads();
-  for (int t = 0; t < n; ++t) {
-    const int buf = t & 1;
-    const float* ks = kq + buf * 2 * dk;
-    const float* qs = ks + dk;
-    const int64_t row = (int64_t)t * nv + h;
-    const float v_t = v_n, decay = __expf(g_n), bt = b_n;
-    float kq_far[KQ];
-    if (t + 2 < n) fetch(t + 2, kq_far);            // consumed at the end of the NEXT step
-    if (t + 1 < n) {
-      const int64_t nrow = row + nv;
-      v_n = live ? v[nrow * dv + j] : 0.f;
-      g_n = g[nrow];
-      b_n = beta[nrow];
+  for (int t0 = 0; t0 < n; t0 += D) {
+#pragma unroll
+    for (int u = 0; u < D; ++u) {
+      const int t = t0 + u;
+      if (t >= n) break;                            // uniform over the CTA
+      const int buf = t & 1;
+      const float* ks = kq + buf * 2 * dk;
+      const float* qs = ks + dk;
+      const int64_t row = (int64_t)t * nv + h;
+      const float v_t = v_r[u], decay = __expf(g_r[u]), bt = b_r[u];
+      fetch_vgb(t + D, v_r[u], g_r[u], b_r[u]);
+      // this thread's R values of k_t and q_t: 16-byte shared loads (the whole warp reads the same address),
+      // four independent partial sums so that the multiply-adds pipeline
+      float kr[R], qr[R];
+#pragma unroll
+      for (int r = 0; r < R; r += 4) {
+        const float4 a = *reinterpret_cast<const float4*>(ks + gy * R + r);
+        const float4 b = *reinterpret_cast<const float4*>(qs + gy * R + r);
+        kr[r] = a.x; kr[r + 1] = a.y; kr[r + 2] = a.z; kr[r + 3] = a.w;
+        qr[r] = b.x; qr[r + 1] = b.y; qr[r + 2] = b.z; qr[r + 3] = b.w;
+      }
+      float p4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < R; ++r) p4[r & 3] += s[r] * kr[r];
+      red_a[gy * dvp + tx] = (p4[0] + p4[1]) + (p4[2] + p4[3]);
+      __syncthreads();
+      if (t + 1 < n) {
+        const int nu = (u + 1) % D;                 // static after unrolling
+        put(kq_r[nu], buf ^ 1);                     // that buffer was last read in step t-1: all threads are past it
+        fetch(t + 1 + D, kq_r[nu]);
+      }
+      const float kv = (red_a[tx] + red_a[dvp + tx] + red_a[2 * dvp + tx] + red_a[3 * dvp + tx]) * decay;
+      const float delta = (v_t - kv) * bt;
+      float o4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        s[r] = s[r] * decay + kr[r] * delta;
+        o4[r & 3] += s[r] * qr[r];
+      }
+      red_b[gy * dvp + tx] = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+      __syncthreads();
+      if (gy == 0 && live) out[row * dv + j] = red_b[tx] + red_b[dvp + tx] + red_b[2 * dvp + tx] + red_b[3 * dvp + tx];
     }
-    // this thread's R values of k_t and q_t: 16-byte shared loads (the whole warp reads the same address),
-    // four independent partial sums so that the multiply-adds pipeline
-    float kr[R], qr[R];
-#pragma unroll
-    for (int r = 0; r < R; r += 4) {
-      const float4 a = *reinterpret_cast<const float4*>(ks + gy * R + r);
-      const float4 b = *reinterpret_cast<const float4*>(qs + gy * R + r);
-      kr[r] = a.x; kr[r + 1] = a.y; kr[r + 2] = a.z; kr[r + 3] = a.w;
-      qr[r] = b.x; qr[r + 1] = b.y; qr[r + 2] = b.z; qr[r + 3] = b.w;
-    }
-    float p4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int r = 0; r < R; ++r) p4[r & 3] += s[r] * kr[r];
-    red_a[gy * dvp + tx] = (p4[0] + p4[1]) + (p4[2] + p4[3]);
-    __syncthreads();
-    if (t + 1 < n) put(kq_next, buf ^ 1);           // that buffer was last read in step t-1: all threads are past it
-    const float kv = (red_a[tx] + red_a[dvp + tx] + red_a[2 * dvp + tx] + red_a[3 * dvp + tx]) * decay;
-    const float delta = (v_t - kv) * bt;
-    float o4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      s[r] = s[r] * decay + kr[r] * delta;
-      o4[r & 3] += s[r] * qr[r];
-    }
-    red_b[gy * dvp + tx] = (o4[0] + o4[1]) + (o4[2] + o4[3]);
-    __syncthreads();
-    if (gy == 0 && live) out[row * dv + j] = red_b[tx] + red_b[dvp + tx] + red_b[2 * dvp + tx] + red_b[3 * dvp + tx];
-#pragma unroll
-    for (int e = 0; e < KQ; ++e) kq_next[e] = kq_far[e];
   }
   if (live) {
 #pragma unroll
