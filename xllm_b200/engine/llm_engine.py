@@ -58,6 +58,10 @@ class EngineConfig:
     ep_size: int = 1
     num_speculative_tokens: int = 0
     host_kv_blocks: int = 0             # > 0: keep evicted prefix-cache blocks in host memory (second tier)
+    host_blocks_factor: float = 0.0     # the same as a fraction of the device's block count (the reference's flag)
+    enable_kvcache_store: bool = False  # third tier: blocks the host tier drops go to a store under kvcache_store_path
+    kvcache_store_path: str = ""
+    kvcache_store_bytes: int = 0        # 0: unbounded
     speculative_method: str = "ngram"   # drafter: "ngram" (suffix / prompt lookup, no draft model)
     draft_model: str = ""
     mla_latent_cache: bool = False      # MLA models: cache [c_kv | k_pe] rows (576 values per token) instead of per-head K/V
@@ -235,10 +239,20 @@ class LLMEngine:
         self.dp_steps = self.fake_steps = 0
         self.mm = {}                 # request id -> MMInput of multimodal requests
         self.host_tier = None
+        if cfg.host_kv_blocks <= 0 and cfg.host_blocks_factor > 0:
+            cfg.host_kv_blocks = max(1, int(cfg.host_blocks_factor * self.runner.kv_caches[0][0].shape[0]))
         if cfg.host_kv_blocks > 0 and cfg.enable_prefix_cache:
             from .host_tier import HostKVTier
+            store = None
+            if cfg.enable_kvcache_store and cfg.kvcache_store_path:
+                from .host_tier import DirectoryKVStore
+                k0 = self.runner.kv_caches[0][0]
+                # blocks are only interchangeable between engines with the same model, cache geometry and sharding
+                geometry = (f"{self.args.model_type}-L{len(self.runner.kv_caches)}-{'x'.join(str(d) for d in k0.shape[1:])}-"
+                            f"{str(k0.dtype).split('.')[-1]}-tp{self.ps.tp_size}r{self.ps.tp_rank}")
+                store = DirectoryKVStore(cfg.kvcache_store_path, geometry, cfg.kvcache_store_bytes)
             self.host_tier = HostKVTier(self.runner.kv_caches, cfg.host_kv_blocks, self.scheduler.block_manager(0), rt,
-                                        cfg.block_size)
+                                        cfg.block_size, store=store)
         self.spec = None
         if cfg.num_speculative_tokens > 0:
             if cfg.enable_schedule_overlap:

@@ -13,8 +13,19 @@ import sys
 
 
 def build_engine_config(flags):
+    """The reference's flag names -> `EngineConfig` (xllm/xllm.cpp builds its `Options` the same way)."""
     from .engine.llm_engine import EngineConfig
-    return EngineConfig(
+    algo = (flags.get("speculative_algorithm") or "").lower()
+    n_spec = flags.get_int("num_speculative_tokens")
+    method = {"mtp": "mtp", "eagle3": "eagle3", "suffix": "ngram", "ngram": "ngram", "draft": "draft"}.get(algo, "ngram")
+    if n_spec > 0 and flags.get("draft_model") and algo in ("", "mtp") and not flags.is_set("speculative_algorithm"):
+        method = "draft"
+    scheduler = "continuous"
+    if flags.get_bool("use_zero_evict"):
+        scheduler = "zero_eviction"
+    elif flags.get("backend") == "rec":
+        scheduler = "fixed_steps"
+    cfg = EngineConfig(
         model=flags.get("model") or "tiny", dtype="auto", device=("auto" if flags.get("devices") == "auto" else flags.get("devices")),
         block_size=flags.get_int("block_size"), max_memory_utilization=flags.get_double("max_memory_utilization"),
         max_cache_size=flags.get_int("max_cache_size"), max_seqs_per_batch=flags.get_int("max_seqs_per_batch"),
@@ -24,9 +35,21 @@ def build_engine_config(flags):
         max_tokens_per_chunk_for_prefill=flags.get_int("max_tokens_per_chunk_for_prefill"),
         policy=flags.get("scheduler_policy"), priority_strategy=flags.get("priority_strategy"),
         enable_schedule_overlap=flags.get_bool("enable_schedule_overlap"),
-        enable_graph=flags.get_bool("enable_cuda_graph"), random_weights=flags.get_bool("random_weights"),
+        enable_graph=flags.get_bool("enable_cuda_graph") or flags.get_bool("enable_graph"),
+        random_weights=flags.get_bool("random_weights"),
         dp_size=flags.get_int("dp_size"), ep_size=flags.get_int("ep_size"),
-        num_speculative_tokens=flags.get_int("num_speculative_tokens"), draft_model=flags.get("draft_model"))
+        num_speculative_tokens=n_spec, speculative_method=method, draft_model=flags.get("draft_model"),
+        scheduler_type=scheduler, enable_xtensor=flags.get_bool("enable_xtensor"),
+        enable_profile_token_budget=flags.get_bool("enable_profile_token_budget") or flags.get_bool("enable_latency_aware_schedule"),
+        max_global_ttft_ms=float(flags.get_int("max_global_ttft_ms")), max_global_tpot_ms=float(flags.get_int("max_global_tpot_ms")),
+        host_blocks_factor=flags.get_double("host_blocks_factor"),
+        enable_kvcache_store=flags.get_bool("enable_kvcache_store"),
+        # the store of this build is a directory shared by the instances of a node (a tmpfs or NVMe mount)
+        kvcache_store_path=os.environ.get("XLLM_KVCACHE_STORE_PATH", "") or
+        (flags.get("store_master_server_address") if os.path.isabs(flags.get("store_master_server_address") or "") else ""))
+    if cfg.enable_schedule_overlap and n_spec > 0:
+        cfg.enable_schedule_overlap = False          # as the reference: speculation turns the overlap off
+    return cfg
 
 
 def main(argv=None):
