@@ -51,6 +51,7 @@ def test_two_spawned_ranks_match_one(monkeypatch, tmp_path):
     llm = LLM(model, devices="cpu,cpu", **kw)
     try:
         assert llm.engine.ps.world_size == 2 and llm._workers is not None and llm._workers.alive()
+        assert llm.engine.ps.ctl is not None          # control events travel through shared memory
         two = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
         again = [o.outputs[0].token_ids for o in llm.generate(prompts[:1], sp)]
     finally:

@@ -13,14 +13,28 @@ import torch.distributed as dist
 
 
 def _bcast(obj, ps):
+    ctl = getattr(ps, "ctl", None)
+    if ctl is not None:                                   # ranks of one host: shared-memory ring, no collective
+        if ps.rank == 0:
+            ctl.send(obj)
+            return obj
+        return ctl.recv()
     box = [obj]
     dist.broadcast_object_list(box, src=getattr(ps, "leader", 0), group=ps.world_group)
     return box[0]
 
 
+def _open_control(ps):
+    """Both roles call this once, at the same point: the control channel of the instance."""
+    if not hasattr(ps, "ctl"):
+        from .shm_channel import open_for_group
+        ps.ctl = open_for_group(ps)
+
+
 def lead_ranks(server, ps):
     """Wrap rank 0's engine so that add_request / abort / pause / resume / step are mirrored."""
     eng = server.engine
+    _open_control(ps)
     log = []
     orig_add, orig_abort, orig_pause, orig_resume, orig_step = eng.add_request, eng.abort, eng.pause, eng.resume, eng.step
 
@@ -53,15 +67,23 @@ def lead_ranks(server, ps):
     def shutdown():
         _bcast(("stop", []), ps)
         orig_shutdown()
+        if getattr(ps, "ctl", None) is not None:
+            import time
+            time.sleep(0.2)                               # the followers read the stop before the segment goes
+            ps.ctl.close()
+            ps.ctl = None
 
     server.shutdown = shutdown
 
 
 def follow_rank0(engine, ps) -> int:
     """Loop of a non-zero rank: apply rank 0's control events, then run the same step."""
+    _open_control(ps)
     while True:
         kind, events = _bcast(None, ps)
         if kind == "stop":
+            if getattr(ps, "ctl", None) is not None:
+                ps.ctl.close()
             return 0
         for name, a, kw in events:
             getattr(engine, {"add": "add_request"}.get(name, name))(*a, **kw)

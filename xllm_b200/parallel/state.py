@@ -146,6 +146,79 @@ class ParallelState:
         if self.world_group is not None and self.world_size > 1:
             dist.barrier(group=self.world_group)
 
+    def all_to_all_single(self, x, out_splits=None, in_splits=None, group=None):
+        """Rank r's i-th dim-0 slice goes to rank i (equal slices, or `in_splits` / `out_splits` rows per
+        peer).  Backends without a native all-to-all (gloo) run it as one exchange per peer pair."""
+        g = group if group is not None else self.world_group
+        if g is None or dist.get_world_size(g) == 1:
+            return x
+        n, me = dist.get_world_size(g), dist.get_rank(g)
+        x = x.contiguous()
+        if in_splits is None:
+            in_splits = [x.shape[0] // n] * n
+        if out_splits is None:
+            out_splits = list(in_splits) if len(set(in_splits)) == 1 else None
+            if out_splits is None:
+                counts = torch.tensor(in_splits, dtype=torch.int64, device=x.device)
+                gathered = [torch.empty_like(counts) for _ in range(n)]
+                dist.all_gather(gathered, counts, group=g)
+                out_splits = [int(c[me]) for c in gathered]
+        out = torch.empty((sum(out_splits),) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        if dist.get_backend(g) != "gloo":
+            dist.all_to_all_single(out, x, out_splits, in_splits, group=g)
+            return out
+        ins, outs = list(x.split(in_splits)), list(out.split(out_splits))
+        outs[me].copy_(ins[me])
+        self.batch_send_recv([(ins[p], p) for p in range(n) if p != me], [(outs[p], p) for p in range(n) if p != me], group=g)
+        return out
+
+    def send(self, x, dst: int, group=None, tag: int = 0):
+        g = group if group is not None else self.world_group
+        dist.send(x.contiguous(), dst=dist.get_global_rank(g, dst) if g is not None else dst, group=g, tag=tag)
+
+    def recv(self, x, src: int, group=None, tag: int = 0):
+        g = group if group is not None else self.world_group
+        dist.recv(x, src=dist.get_global_rank(g, src) if g is not None else src, group=g, tag=tag)
+        return x
+
+    def batch_send_recv(self, sends, recvs, group=None, max_wave_bytes: int = 256 << 20):
+        """`sends` / `recvs`: [(tensor, peer rank in the group)].  The transfers are issued in waves of at most
+        `max_wave_bytes` each way (a bound on staging memory; xllm's ProcessGroup::batch_isend_irecv with its
+        p2p wave planning) and every wave is waited for before the next starts."""
+        g = group if group is not None else self.world_group
+        glob = (lambda r: dist.get_global_rank(g, r)) if g is not None else (lambda r: r)
+        for wave in plan_p2p_waves(sends, recvs, max_wave_bytes):
+            ops = [dist.P2POp(dist.isend, t.contiguous(), glob(p), g) for t, p in wave[0]] + \
+                  [dist.P2POp(dist.irecv, t, glob(p), g) for t, p in wave[1]]
+            if ops:
+                for w in dist.batch_isend_irecv(ops):
+                    w.wait()
+
+
+def plan_p2p_waves(sends, recvs, max_wave_bytes: int):
+    """Splits matched send / receive lists into waves whose payload stays under the bound per direction.
+    Entry i of a rank's send list to peer p pairs with entry i of p's receive list from this rank, so both
+    sides must cut at the same places: the cut depends only on the sizes, walked in peer order."""
+    def nbytes(t):
+        return t.numel() * t.element_size()
+
+    def waves(items):
+        out, cur, used = [], [], 0
+        for t, p in sorted(items, key=lambda it: it[1]):
+            b = nbytes(t)
+            if cur and used + b > max_wave_bytes:
+                out.append(cur)
+                cur, used = [], 0
+            cur.append((t, p))
+            used += b
+        if cur:
+            out.append(cur)
+        return out
+
+    ws, wr = waves(sends), waves(recvs)
+    n = max(len(ws), len(wr))
+    return [(ws[i] if i < len(ws) else [], wr[i] if i < len(wr) else []) for i in range(n)]
+
 
 _SINGLE = ParallelState()
 
