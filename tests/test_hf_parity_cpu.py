@@ -313,3 +313,45 @@ def test_qwen3_5_vision_language_matches_huggingface(tmp_path):
     got = vlm.generate_mm([dict(prompt_token_ids=prompt, images=[img])],
                           SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))[0]
     assert got == ref
+
+
+def test_glm4v_matches_huggingface(tmp_path):
+    """GLM-4V: learned position embeddings resampled bicubically per image, RMSNorm / SwiGLU vision blocks,
+    strided-convolution downsample and gated merger, in front of the GLM-4 decoder with contiguous M-RoPE
+    sections over the rotated half of each head; the prompt is prefilled in chunks."""
+    import numpy as np
+    from xllm_b200.api.vlm import VLM
+    from xllm_b200.multimodal import Glm4vImageProcessor
+    t = transformers
+    if not hasattr(t, "Glm4vForConditionalGeneration"):
+        pytest.skip("no GLM-4V in this transformers build")
+    IMG, ISTART, IEND = 500, 501, 502
+    text = dict(vocab_size=512, hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                intermediate_size=128, max_position_embeddings=512, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                attention_bias=True,
+                rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5,
+                                 "mrope_section": [2, 3, 3]})
+    vis = dict(depth=2, hidden_size=32, out_hidden_size=128, intermediate_size=48, num_heads=2, patch_size=14, spatial_merge_size=2,
+               temporal_patch_size=2, in_channels=3, image_size=84, rms_norm_eps=1e-5)
+    cfg = t.Glm4vConfig(text_config=text, vision_config=vis, image_token_id=IMG, video_token_id=503, image_start_token_id=ISTART,
+                        image_end_token_id=IEND, video_start_token_id=504, video_end_token_id=505)
+    torch.manual_seed(0)
+    hf = t.Glm4vForConditionalGeneration(cfg).float().eval()
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    vlm = VLM(str(tmp_path), devices="cpu", dtype="float32", block_size=16, num_blocks=64, max_seqs_per_batch=8,
+              max_tokens_per_batch=16, enable_graph=False, processor=Glm4vImageProcessor(14, 2, 2))
+    img = (np.random.default_rng(3).random((100, 130, 3)) * 255).astype(np.uint8)
+    prompt = [11, 12, ISTART, IMG, IEND, 13, 14, 15]
+    ids, mm = vlm.prepare(prompt, [img])
+    pv, grid = vlm.processor([img])
+    with torch.no_grad():
+        feats = hf.get_image_features(pv, grid)
+        feats = feats.pooler_output if hasattr(feats, "pooler_output") else feats
+        feats = torch.cat(list(feats)) if isinstance(feats, (list, tuple)) else feats
+        assert (mm.embeds - feats).abs().max() < 1e-4                      # the tower alone
+        kinds = torch.tensor([[1 if i == IMG else 0 for i in ids]])
+        ref = hf.generate(input_ids=torch.tensor([ids]), pixel_values=pv, image_grid_thw=grid, mm_token_type_ids=kinds,
+                          max_new_tokens=7, do_sample=False, eos_token_id=None, pad_token_id=0)[0, len(ids):].tolist()
+    got = vlm.generate_mm([dict(prompt_token_ids=prompt, images=[img])],
+                          SamplingParams(max_tokens=7, temperature=0.0, ignore_eos=True))[0]
+    assert got == ref            # (the eighth token is a tie to 8e-4 in this random model)

@@ -216,3 +216,41 @@ def test_chat_route_takes_image_parts(tmp_path):
     finally:
         srv.shutdown()
         t.join(timeout=5)
+
+
+def test_oxygenvlm_runs_the_glm4v_tower_in_front_of_a_qwen3_decoder():
+    """`oxygenvlm`: image request through the engine equals the dense reference; `oxygenvlm_text` is the
+    decoder alone under the same registry."""
+    from xllm_b200.models.registry import create_model
+    from xllm_b200.multimodal import Glm4vImageProcessor
+    args = ModelArgs(model_type="oxygenvlm", vocab_size=1000, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=16, intermediate_size=128, qk_norm=False, attention_bias=True, rope_theta=10000.0,
+                     max_position_embeddings=512, tie_word_embeddings=False, image_token_id=IMG, vision_start_token_id=VSTART,
+                     mrope_section=[2, 3, 3],
+                     vision_config=dict(hidden_size=32, out_hidden_size=64, intermediate_size=48, num_heads=2, depth=2,
+                                        patch_size=14, spatial_merge_size=2, temporal_patch_size=2, in_channels=3,
+                                        image_size=84))
+    vlm = VLM.__new__(VLM)
+    vlm.engine = LLMEngine(EngineConfig(model="o", device="cpu", dtype="float32", num_blocks=64, enable_graph=False,
+                                        max_tokens_per_batch=16), model_args=args)
+    vlm.tokenizer = None
+    model = vlm.engine.model
+    assert type(model).__name__ == "OxygenVLForConditionalGeneration" and type(model.visual).__name__ == "Glm4vVisionTower"
+    model.init_random(std=0.05, seed=4)
+    vlm.processor = Glm4vImageProcessor(14, 2, 2)
+    vlm.image_token_id = IMG
+    img = (np.random.default_rng(5).random((70, 98, 3)) * 255).astype(np.uint8)
+    req = dict(prompt_token_ids=[11, VSTART, IMG, VEND, 12, 13], images=[img])
+    got = vlm.generate_mm([req], SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True))[0]
+    ids, mm = vlm.prepare(req["prompt_token_ids"], [img])
+    assert mm.embeds.shape == (sum(1 for t in ids if t == IMG), 64) and torch.isfinite(mm.embeds).all()
+    seq = list(ids)
+    for _ in range(4):
+        L = len(seq)
+        pos3 = torch.cat([mm.mrope, (torch.arange(mm.mrope.shape[1], L) + mm.delta).repeat(3, 1)], dim=1)
+        logits = _dense_reference(model, torch.tensor(seq), torch.tensor(mm.positions), mm.embeds, pos3)
+        seq.append(int(logits[-1].argmax()))
+    assert got == seq[len(ids):]
+    text_args = ModelArgs(**{**args.__dict__, "model_type": "oxygenvlm_text", "vision_config": None})
+    text = create_model(text_args, torch.float32, "cpu")
+    assert not hasattr(text, "visual") and text.mrope_section == [2, 3, 3]

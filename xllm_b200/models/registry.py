@@ -25,7 +25,7 @@ def supported_models():
 
 def _import_all():
     from . import qwen  # noqa: F401
-    for mod in ("qwen_moe", "deepseek", "qwen_vl", "families", "qwen3_next", "rwkv7"):
+    for mod in ("qwen_moe", "deepseek", "qwen_vl", "families", "qwen3_next", "rwkv7", "glm4v"):
         try:
             __import__(f"{__package__}.{mod}")
         except ModuleNotFoundError as e:

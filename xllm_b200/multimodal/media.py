@@ -198,6 +198,9 @@ class Glm4vImageProcessor:
         return pixels, torch.tensor([o[1] for o in outs], dtype=torch.int64).view(-1, 3)
 
 
+Glm4vImageProcessor.tokens_per_image = lambda self, grid_thw: [int(t * h * w) // (self.m * self.m) for t, h, w in grid_thw.tolist()]
+
+
 class ClipImageProcessor:
     """Shortest side to `size` (bicubic), centre crop `crop` x `crop`, CLIP normalisation -> [N, 3, crop, crop]."""
 
