@@ -135,12 +135,23 @@ def rope_kv_write(qkv, nq, nkv, d, positions, cos_sin, rot, slots=None, k_cache=
 
 # ----------------------------------------------------------------------------- attention
 def decode_splits(batch, nkv, group, max_kv_len=None, n_sm=148):
-    """Split-KV factor: enough CTAs to cover ~2 per SM, never more than one split per 256 tokens."""
+    """Split-KV factor.  Without a context length: enough CTAs to cover ~2 per SM.  With one: the factor in
+    1..16 that minimises (waves of CTAs over 2 resident per SM) x (tokens per split + a fixed cost for the
+    split's set-up and its share of the merge), never less than 256 tokens per split — so that 128 CTAs of
+    16k tokens become 2 x 8k in one wave instead of 3 x 5.5k in two."""
     ctas = batch * nkv * ((group + 15) // 16)
-    s = max(1, min(16, (2 * n_sm + ctas - 1) // ctas))
-    if max_kv_len is not None:
-        s = max(1, min(s, (max_kv_len + 255) // 256))
-    return s
+    if max_kv_len is None:
+        return max(1, min(16, (2 * n_sm + ctas - 1) // ctas))
+    slots = 2 * n_sm
+    best, best_cost = 1, None
+    for s in range(1, 17):
+        if s > 1 and max_kv_len // s < 256:
+            break
+        waves = (ctas * s + slots - 1) // slots
+        cost = waves * ((max_kv_len + s - 1) // s + (192 if s > 1 else 0))
+        if best_cost is None or cost < best_cost * 0.97:      # a larger factor must pay for its merge
+            best, best_cost = s, cost
+    return best
 
 
 def decode_workspace(batch, nq, d, splits, device):
