@@ -56,10 +56,15 @@ def main():
     prompts = [torch.randint(0, 32000, (int(L),), generator=g).tolist() for L in (40, 150, 9, 77)]
     sp = SamplingParams(max_tokens=16, temperature=0.0, ignore_eos=True)
 
+    eagle = os.environ.get("SPEC", "") == "eagle3"
+
     def make(ps_, model):
         cfg = EngineConfig(model="t", device=str(ps.device), dtype="bfloat16", block_size=16, num_blocks=256,
                            max_seqs_per_batch=8, max_tokens_per_batch=512, max_model_len=512,
                            enable_graph=True)
+        if eagle and ps_.tp_size > 1:
+            # the target reduces through the process group (replicated activations), the head is whole on every rank
+            cfg.num_speculative_tokens, cfg.speculative_method, cfg.enable_graph = 2, "eagle3", False
         llm = LLM.__new__(LLM)
         llm.engine = LLMEngine(cfg, ps=ps_, model=model, model_args=args)
         llm.tokenizer = None
@@ -68,7 +73,8 @@ def main():
     base_llm = make(single(), full)
     base = [o.outputs[0].token_ids for o in base_llm.generate(prompts, sp)]
     from xllm_b200.parallel import symm
-    symm.attach(ps, 512, args.hidden_size)
+    if not eagle:
+        symm.attach(ps, 512, args.hidden_size)
     tp_model = create_model(args, torch.bfloat16, ps.device, ps)
     tp_model.load_weights(weights, strict=True)
     tp_llm = make(ps, tp_model)
@@ -89,6 +95,10 @@ def main():
         print(f"TP_ENGINE_METRICS common_prefix={prefix} rel_logit_err={rel:.4f} argmax_agreement={same:.3f}", flush=True)
     assert rel < 0.1 and same >= 0.8, (rel, same, prefix)
     assert sum(prefix) >= 4 * len(prompts), (prefix, base, got)
+    if eagle:
+        eng = tp_llm.engine
+        assert ps.comm is None and eng.eagle3.ps.tp_size == 1 and eng.spec.drafter.kv[0].shape[1] == args.num_key_value_heads
+        return "TP_ENGINE_OK eagle3-replicated-head"
     assert ps.comm.error_status() == 0
     return "TP_ENGINE_OK " + ("moe-ep-a2a" if moe else "dense")
 

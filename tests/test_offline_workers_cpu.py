@@ -62,3 +62,32 @@ def test_two_spawned_ranks_match_one(monkeypatch, tmp_path):
         dist.destroy_process_group()
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
         os.environ.pop(k, None)
+
+
+def test_eagle3_head_runs_replicated_under_tensor_parallelism(monkeypatch, tmp_path):
+    """Two ranks, the target sharded, the EAGLE-3 head whole on each: greedy output equals the unspeculated
+    single-rank run, and drafts are proposed and verified."""
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        monkeypatch.delenv(k, raising=False)
+    model = _write_checkpoint(tmp_path)
+    kw = dict(dtype="float32", block_size=16, num_blocks=64, max_seqs_per_batch=4, max_tokens_per_batch=128,
+              enable_graph=False)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (17, 30)]
+    sp = SamplingParams(max_tokens=10, temperature=0.0, ignore_eos=True)
+    plain = [o.outputs[0].token_ids for o in LLM(model, devices="cpu", **kw).generate(prompts, sp)]
+    llm = LLM(model, devices="cpu,cpu", num_speculative_tokens=2, speculative_method="eagle3", **kw)
+    try:
+        eng = llm.engine
+        assert eng.ps.tp_size == 2 and eng.eagle3.ps.tp_size == 1 and eng.eagle3.kv_heads_full == 2
+        assert eng.spec.drafter.kv[0].shape[1] == 2 and eng.runner.kv_caches[0][0].shape[1] == 1
+        spec = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+        stats = eng.spec.stats() if hasattr(eng.spec, "stats") else {}
+    finally:
+        llm.close()
+    assert spec == plain, (spec, plain, stats)
+    import torch.distributed as dist
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        os.environ.pop(k, None)

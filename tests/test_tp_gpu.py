@@ -74,6 +74,14 @@ def test_tp_engine_matches_single_gpu(push_min):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_eagle3_head_under_tensor_parallelism():
+    """TP2 target reducing through NCCL, the EAGLE-3 head replicated: speculation leaves the greedy output
+    where the single-GPU engine puts it (same tolerance as the plain TP run)."""
+    out = _run("mp_tp_engine.py", 2, {"SPEC": "eagle3"})
+    assert "TP_ENGINE_OK eagle3-replicated-head" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_moe_engine_with_expert_parallel_all_to_all():
     """Qwen3-MoE-shaped model, TP=EP=2: prefill through the all-to-all path, decode graphs through the
     replicate path; tokens must match the single-GPU engine."""

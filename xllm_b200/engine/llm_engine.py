@@ -131,7 +131,11 @@ class LLMEngine:
         else:
             self.dtype = _DTYPES[cfg.dtype]
         # ---- fused tensor-parallel communicator (symmetric memory), before the model is built
-        if self.ps.tp_size > 1 and self.device.type == "cuda" and self.ps.comm is None:
+        # An EAGLE-3 head reads whole hidden states of three target layers on every rank; the fused reductions
+        # keep the residual stream sharded by rows between layers, so the target then reduces through the
+        # process group instead (replicated activations) and the head itself runs replicated.
+        eagle_tp = cfg.num_speculative_tokens > 0 and cfg.speculative_method == "eagle3" and self.ps.tp_size > 1
+        if self.ps.tp_size > 1 and self.device.type == "cuda" and self.ps.comm is None and not eagle_tp:
             from ..parallel import symm
             tp = self.ps.tp_size
             shard = (self.args.vocab_size + tp - 1) // tp

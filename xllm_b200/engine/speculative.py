@@ -104,7 +104,12 @@ class MTPDrafter:
         self.mtp = head if head is not None else engine.mtp
         self.takes_aux = bool(getattr(self.mtp, "takes_aux", False))
         k0, v0 = engine.runner.kv_caches[0]
-        self.kv = (torch.zeros_like(k0), torch.zeros_like(v0))
+        heads = int(getattr(self.mtp, "kv_heads_full", 0) or k0.shape[1])
+        if heads != k0.shape[1]:                     # a replicated head under tensor parallelism: all KV heads here
+            shape = (k0.shape[0], heads) + tuple(k0.shape[2:])
+            self.kv = (torch.zeros(shape, dtype=k0.dtype, device=k0.device), torch.zeros(shape, dtype=v0.dtype, device=v0.device))
+        else:
+            self.kv = (torch.zeros_like(k0), torch.zeros_like(v0))
         self.draft = {}
         engine.runner.keep_hidden = True
 

@@ -34,8 +34,11 @@ class Eagle3Draft(Module):
     def __init__(self, args, target, dtype, device, ps=None, draft_vocab: int = 0):
         super().__init__()
         self.args = args
-        self.ps = ps or single()
-        assert self.ps.tp_size == 1, "the EAGLE-3 head runs unsharded"
+        # The head is one layer: under tensor parallelism every rank runs the WHOLE head on the same
+        # (replicated) inputs and so proposes the same drafts; only the token embedding, which it shares
+        # with the target, is sharded.  Its KV cache holds all KV heads on every rank (`kv_heads_full`).
+        self.target_ps = ps or single()
+        self.ps = single()
         H, d = args.hidden_size, args.head_dim
         self.embed = target.embed
         self.rope = target.rope
@@ -62,6 +65,7 @@ class Eagle3Draft(Module):
         self.d2t = self.add_param("d2t", torch.zeros(self.draft_vocab, dtype=torch.int64, device=device))
         self.scale = 1.0 / math.sqrt(d)
         self.kv_shape_like = None
+        self.kv_heads_full = self.nkv
 
     def init_random(self, std=0.02, seed=0):
         super().init_random(std, seed)
