@@ -81,7 +81,11 @@ def _hf_names(model):
             yield base + "k_proj.weight", k
             yield base + "v_proj.weight", v
         elif n.endswith("gate_up_proj.weight"):
-            g, u = t.chunk(2)
+            if getattr(t, "_xllm_interleaved", False):      # rows stored as [64 gate | 64 up] groups
+                from xllm_b200.ops.gemm_tcgen05 import deinterleave_gate_up
+                g, u = deinterleave_gate_up(t)
+            else:
+                g, u = t.chunk(2)
             base = n[: -len("gate_up_proj.weight")]
             yield base + "gate_proj.weight", g
             yield base + "up_proj.weight", u

@@ -141,6 +141,10 @@ struct GemmMode {
   int64_t push_off;        // byte offset of the inbox inside the symmetric buffer
   int64_t push_sig_idx;    // uint32 index of the arrival counter inside a signal pad
   int push_S, push_rank, push_world;
+  // Gated-activation epilogue: the weight rows are interleaved in groups of 128 output columns =
+  // [gate of 64 features | up of the same 64 features]; the epilogue writes act(gate) * up, 64 columns per
+  // group, into an output of N / 2 columns.  0 = off, 1 = SiLU, 2 = GELU(erf), 3 = GELU(tanh).
+  int act_mul;
 };
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -215,6 +219,49 @@ __device__ __forceinline__ void epilogue_slice(uint32_t taddr, const CUtensorMap
                                                int row0, int n0, const bf16* __restrict__ bias, int N, int lane,
                                                int& buf, const GemmMode mode = GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0},
                                                int M = 0, uint32_t taddr2 = 0) {
+  if (mode.act_mul != 0) {
+    if constexpr (BN % 128 == 0) {
+#pragma unroll 1
+      for (int c = 0; c < BN / 128; ++c) {
+        uint32_t g[64], u[64];
+        tmem_ld32(taddr + c * 128, g);
+        tmem_ld32(taddr + c * 128 + 32, g + 32);
+        tmem_ld32(taddr + c * 128 + 64, u);
+        tmem_ld32(taddr + c * 128 + 96, u + 32);
+        tmem_ld_wait();
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
+        const uint32_t sb = warp_stage + buf * kEpiBufBytes;
+        const int col0 = (n0 >> 1) + c * kEpiCols;       // output column: half of the interleaved one
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float x = __uint_as_float(g[j * 8 + e]);
+            float a;
+            if (mode.act_mul == 1) a = x / (1.f + __expf(-x));
+            else if (mode.act_mul == 2) a = 0.5f * x * (1.f + erff(x * 0.70710678f));
+            else a = 0.5f * x * (1.f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x)));
+            f[e] = a * __uint_as_float(u[j * 8 + e]);
+          }
+          const bf16x8 v = pack8(f);
+          const uint4 w4 = *reinterpret_cast<const uint4*>(&v);
+          const uint32_t dst = sb + lane * 128 + ((j ^ (lane & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w4.x), "r"(w4.y), "r"(w4.z), "r"(w4.w)
+                       : "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(tmap_c, sb, col0, row0);
+          bulk_commit();
+        }
+        buf ^= 1;
+      }
+    }
+    return;
+  }
   float a_s = 1.f;
   if (mode.fp8 && mode.a_scale != nullptr) {
     const int r = row0 + lane;
@@ -930,8 +977,10 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const _
         steps_done += n_steps;
       }
       if (ks == 1) {
+        GemmMode pm{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0};
+        pm.act_mul = mode.act_mul;
         epilogue_slice<BN>(taddr, &tma_c, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, m0 + q * 32, n0, bias, N, lane, ebuf,
-                           GemmMode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0}, 0, taddr2);
+                           pm, 0, taddr2);
       } else {
         // one counter per (tile, CTA of the pair): each CTA finishes its own 128 rows
         const bool last = splitk_dump<BN>(taddr, &tma_ws, sbase + S::EPI_OFF + q * 2 * kEpiBufBytes, mode,
@@ -1097,7 +1146,8 @@ static int launch_gemm(const void* a, const void* w, void* c, const void* bias, 
 
 template <int BN, int STAGES, int KS = 1, bool DUAL = false>
 static int launch_gemm_pair(const void* a, const void* w, void* c, const void* bias, int M, int N, int K, int64_t lda,
-                            int64_t ldw, int64_t ldc, int max_ctas, int w_packed, cudaStream_t s, int split_k = 1) {
+                            int64_t ldw, int64_t ldc, int max_ctas, int w_packed, cudaStream_t s, int split_k = 1,
+                            int act_mul = 0) {
   using S = GemmSmem2<BN, STAGES, KS>;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1115,10 +1165,12 @@ static int launch_gemm_pair(const void* a, const void* w, void* c, const void* b
   CUtensorMap ta, tb, tc;
   const bool okb = w_packed ? make_tmap(&tb, w, (int64_t)N * (K / 64), 64, 64, BN / 2 < 64 ? BN / 2 : 64)
                             : make_tmap(&tb, w, N, K, ldw, BN / 2);
-  if (!make_tmap(&ta, a, M, K, lda, kBM) || !okb || !make_tmap(&tc, c, M, N, ldc, 32, false))
+  if (!make_tmap(&ta, a, M, K, lda, kBM) || !okb || !make_tmap(&tc, c, M, act_mul ? N / 2 : N, ldc, 32, false))
     return (int)cudaErrorInvalidValue;
   const int tiles = ((M + 2 * kBM - 1) / (2 * kBM)) * ((N + BN - 1) / BN);
   GemmMode mode{nullptr, nullptr, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0, 0, 0, 0};
+  mode.act_mul = act_mul;
+  if (act_mul) split_k = 1;
   if (split_k > 1) {
     mode.ks = usable_split(split_k, M, N, K, KS, 2 * tiles, dev, s);
     mode.ws = g_split_ws[dev & 63];
@@ -1133,6 +1185,19 @@ static int launch_gemm_pair(const void* a, const void* w, void* c, const void* b
   launch_pdl(gemm_bf16_tcgen05_pair_kernel<BN, STAGES, KS, DUAL>, dim3(2 * pairs), dim3(DUAL ? 224 : 192), S::TOTAL, s, ta, tb, tc, tws, (const bf16*)bias, M, N, K,
                                                                             w_packed, mode, g_err_word[dev & 63]);
   return XLLM_LAUNCH_CHECK();
+}
+
+// C[M, N / 2] = act(A W_gate^T) * (A W_up^T) in one launch.  W [N, K] holds the fused gate|up projection with its
+// rows interleaved in groups of 128 = [64 gate rows | the 64 up rows of the same features] (N % 256 == 0); the
+// 256-wide tiles of the CTA-pair kernel then hold both halves of 128 features and the epilogue applies the gated
+// activation on the fp32 accumulators before anything is written.  act: 1 SiLU, 2 GELU(erf), 3 GELU(tanh).
+XLLM_API int xllm_gemm_bf16_act_mul(const void* a, const void* w, void* c, int M, int N, int K, int64_t lda, int64_t ldw,
+                                    int64_t ldc, int act, void* stream) {
+  using namespace xllm;
+  if (M == 0 || N == 0) return 0;
+  if (K % 8 || N % 256 || lda % 8 || ldw % 8 || ldc % 8 || act < 1 || act > 3) return (int)cudaErrorInvalidValue;
+  if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15) return (int)cudaErrorInvalidValue;
+  return launch_gemm_pair<256, 6>(a, w, c, nullptr, M, N, K, lda, ldw, ldc, 148, 0, (cudaStream_t)stream, 1, act);
 }
 
 // ===================================================================================== block-scaled fp8

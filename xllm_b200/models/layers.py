@@ -8,6 +8,8 @@ ops from ``xllm_b200.ops`` (sm_100a kernels on CUDA, PyTorch references on CPU).
 """
 from __future__ import annotations
 
+import os
+
 import math
 from dataclasses import dataclass
 from typing import Callable, Dict, Iterable, List, Optional, Tuple
@@ -277,9 +279,10 @@ class MergedColumnLinear(Module):
     (KV heads when n_kv_heads < tp)."""
 
     def __init__(self, in_f, sizes: List[int], names: List[str], bias, dtype, device,
-                 ps: ParallelState = None, shard_counts: Optional[List[int]] = None, quant=None):
+                 ps: ParallelState = None, shard_counts: Optional[List[int]] = None, quant=None, interleave: bool = False):
         super().__init__()
         self.ps = ps or single()
+        self.interleaved = False
         tp, rank = self.ps.tp_size, self.ps.tp_rank
         counts = shard_counts or [tp] * len(sizes)
         self.local_sizes = [s // c for s, c in zip(sizes, counts)]
@@ -301,13 +304,22 @@ class MergedColumnLinear(Module):
             return
         self.weight = torch.empty(total, in_f, dtype=dtype, device=device)
         self.bias = torch.zeros(total, dtype=dtype, device=device) if bias else None
+        # gate|up of a gated MLP, rows interleaved in groups of 128 = [64 gate | the same 64 up]: the layout
+        # whose GEMM applies the activation in its epilogue (ops/gemm_tcgen05.gemm_act_mul)
+        self.interleaved = bool(interleave and len(sizes) == 2 and not bias and self.local_sizes[0] == self.local_sizes[1]
+                                and self.local_sizes[0] % 64 == 0)
+        self.weight._xllm_interleaved = self.interleaved
         loaders = {}
         off = 0
-        for name, full, cnt, loc in zip(names, sizes, counts, self.local_sizes):
+        for part, (name, full, cnt, loc) in enumerate(zip(names, sizes, counts, self.local_sizes)):
             idx = rank * cnt // tp  # which shard of this projection the rank holds
 
-            def lw(w, o=off, n=loc, i=idx, t=self.weight):
-                t[o:o + n].copy_(w.narrow(0, i * n, n).to(t.dtype))
+            def lw(w, o=off, n=loc, i=idx, t=self.weight, p=part):
+                src = w.narrow(0, i * n, n).to(t.dtype)
+                if self.interleaved:
+                    t.view(n // 64, 2, 64, t.shape[1])[:, p].copy_(src.reshape(n // 64, 64, t.shape[1]))
+                else:
+                    t[o:o + n].copy_(src)
 
             loaders[f"{name}.weight"] = lw
             if bias:
@@ -539,8 +551,12 @@ class DenseMLP(Module):
         super().__init__()
         self.ps = ps or single()
         self.act = act
+        # on a CUDA device the gate and up rows are stored interleaved, so that prompt-size batches run the
+        # GEMM whose epilogue applies the gated activation (XLLM_FUSED_ACT=0 keeps the plain layout)
+        il = (torch.device(device).type == "cuda" and dtype == torch.bfloat16 and quant is None
+              and act in ("silu", "gelu", "gelu_tanh", "gelu_pytorch_tanh") and os.environ.get("XLLM_FUSED_ACT", "1") != "0")
         self.gate_up = self.add_module("gate_up_proj", MergedColumnLinear(
-            hidden, [inter, inter], ["gate_proj", "up_proj"], False, dtype, device, self.ps, quant=quant))
+            hidden, [inter, inter], ["gate_proj", "up_proj"], False, dtype, device, self.ps, quant=quant, interleave=il))
         self.down = self.add_module("down_proj", Linear(inter, hidden, False, dtype, device, self.ps,
                                                         parallel="row", reduce=reduce, fuse_reduce=fuse_reduce,
                                                         quant=quant))
@@ -550,6 +566,14 @@ class DenseMLP(Module):
             yield n.replace("gate_up_proj.", ""), f
 
     def forward(self, x):
-        return self.down(ops.act_and_mul(self.gate_up(x), self.act))
+        gu = self.gate_up
+        if gu.interleaved:
+            from ..ops import gemm, gemm_tcgen05
+            if (x.is_cuda and x.dim() == 2 and x.shape[0] > 512 and gemm.gemm_mode() != "cublas" and gu.weight.shape[0] % 256 == 0
+                    and gemm_tcgen05.supported(x, gu.weight)):
+                return self.down(gemm_tcgen05.gemm_act_mul(x, gu.weight, self.act))
+            y = gu(x)
+            return self.down(gemm_tcgen05.act_and_mul_interleaved(y.view(-1, y.shape[-1]), self.act).view(*y.shape[:-1], -1))
+        return self.down(ops.act_and_mul(gu(x), self.act))
 
     __call__ = forward

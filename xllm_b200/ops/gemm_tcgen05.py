@@ -83,6 +83,58 @@ def gemm_nt(x, w, bias=None, out=None, tile_n: int = 0, pair: int = -1, split_k:
     return out.reshape(*x.shape[:-1], N)
 
 
+_lib.register_signature("xllm_gemm_bf16_act_mul", [P, P, P, I, I, I, L, L, L, I, P])
+_lib.register_signature("xllm_act_and_mul_interleaved", [P, P, L, I, L, I, P])
+
+ACT_CODES = {"silu": 1, "gelu": 2, "gelu_tanh": 3, "gelu_pytorch_tanh": 3}
+
+
+def gemm_act_mul(x, w_interleaved, act: str = "silu", out=None):
+    """act(x W_gate^T) * (x W_up^T) in one launch.  `w_interleaved` [2I, K]: groups of 128 rows =
+    [64 gate rows | the 64 up rows of the same features] (see `interleave_gate_up`); returns [T, I]."""
+    T, K = x.shape
+    N = w_interleaved.shape[0]
+    if out is None:
+        out = torch.empty((T, N // 2), dtype=x.dtype, device=x.device)
+    check(_lib.load().xllm_gemm_bf16_act_mul(ptr(x), ptr(w_interleaved), ptr(out), T, N, K, x.stride(0),
+                                             w_interleaved.stride(0), out.stride(0), ACT_CODES[act], stream()),
+          "gemm_bf16_act_mul")
+    from . import _count
+    _count()
+    return out
+
+
+def act_and_mul_interleaved(y, act: str = "silu", out=None):
+    """Gated activation of a [T, 2I] tensor in the interleaved (64 gate | 64 up) column layout -> [T, I]."""
+    T, N = y.shape
+    if not y.is_cuda:
+        g, u = y.view(T, N // 128, 2, 64).unbind(2)
+        f = {"silu": torch.nn.functional.silu, "gelu": torch.nn.functional.gelu}.get(
+            act, lambda t: torch.nn.functional.gelu(t, approximate="tanh"))
+        return (f(g.float()) * u.float()).to(y.dtype).reshape(T, N // 2)
+    if out is None:
+        out = torch.empty((T, N // 2), dtype=y.dtype, device=y.device)
+    code = {"silu": 0, "gelu": 1, "gelu_tanh": 2, "gelu_pytorch_tanh": 2}[act]
+    check(_lib.load().xllm_act_and_mul_interleaved(ptr(out), ptr(y), T, N // 2, y.stride(0), code, stream()),
+          "act_and_mul_interleaved")
+    from . import _count
+    _count()
+    return out
+
+
+def interleave_gate_up(gate, up):
+    """[I, K] + [I, K] -> [2I, K] with groups of 128 rows = 64 of gate, then the same 64 of up."""
+    I, K = gate.shape
+    return torch.stack([gate.view(I // 64, 64, K), up.view(I // 64, 64, K)], dim=1).reshape(2 * I, K)
+
+
+def deinterleave_gate_up(w):
+    """Inverse of `interleave_gate_up`: (gate [I, K], up [I, K])."""
+    N, K = w.shape
+    v = w.view(N // 128, 2, 64, K)
+    return v[:, 0].reshape(N // 2, K), v[:, 1].reshape(N // 2, K)
+
+
 def set_k_per_stage(n: int):
     """1 = one 64-element K block per ring stage; 2 (default) = two for tiles narrower than 256."""
     _lib.load().xllm_gemm_set_k_per_stage(int(n))
