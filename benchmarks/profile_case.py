@@ -18,6 +18,7 @@ hundred MB on the device, a handful of launches).
     python benchmarks/profile_case.py --kernel route      # MoE routing, 8192 tokens x 256 experts
     python benchmarks/profile_case.py --kernel topk       # radix top-k, 1024 rows x 151936, k = 64
     python benchmarks/profile_case.py --kernel logsoftmax # log-softmax, 1024 rows x 151936
+    python benchmarks/profile_case.py --kernel gemm_act   # gate_up GEMM with the SiLU-mul epilogue, 2304 x 24576 x 4096
     python benchmarks/profile_case.py --kernel xattn      # beam attention: 16 requests x 128 beams over 2048-token prompts
     python benchmarks/profile_case.py --kernel gdn_prefill # gated-delta-rule prompt chunk, 4096 tokens x 32 heads
 """
@@ -150,6 +151,18 @@ def main():
         from xllm_b200.ops import select
         logits = torch.randn(1024, 151936, device=dev, dtype=torch.bfloat16)
         fn = (lambda: select.topk(logits, 64)) if a.kernel == "topk" else (lambda: select.log_softmax(logits))
+    elif a.kernel == "gemm_act":
+        M, I, K = 2304, 12288, 4096
+        x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(2 * I, K, device=dev, dtype=torch.bfloat16) * 0.02
+        out = torch.empty(M, I, device=dev, dtype=torch.bfloat16)
+        fn = lambda: gemm_tcgen05.gemm_act_mul(x, w, "silu", out=out)
+        if os.environ.get("GEMM_ACT_COMPARE"):   # the two-launch form: GEMM into [M, 2I], then the activation kernel
+            mid = torch.empty(M, 2 * I, device=dev, dtype=torch.bfloat16)
+
+            def fn():
+                gemm_tcgen05.gemm_nt(x, w, out=mid)
+                gemm_tcgen05.act_and_mul_interleaved(mid, "silu", out=out)
     elif a.kernel == "xattn":
         from xllm_b200.ops import xattn
         R, W, ctx, nq, nkv, d, page, cap = 16, 128, 2048, 32, 8, 128, 16, 2
