@@ -140,9 +140,13 @@ def decode_splits(batch, nkv, group, max_kv_len=None, n_sm=148):
     split's set-up and its share of the merge), never less than 256 tokens per split — so that 128 CTAs of
     16k tokens become 2 x 8k in one wave instead of 3 x 5.5k in two."""
     ctas = batch * nkv * ((group + 15) // 16)
-    if max_kv_len is None:
-        return max(1, min(16, (2 * n_sm + ctas - 1) // ctas))
     slots = 2 * n_sm
+    if max_kv_len is None:
+        # the context is not known (a graph captured per batch size): of the two factors around one wave of
+        # CTAs, the one that fills its waves better (128 CTAs: 2 x 128 in one wave, not 3 x 128 in 1.3)
+        lo, hi = max(1, min(16, slots // ctas)), max(1, min(16, (slots + ctas - 1) // ctas))
+        eff = lambda s_: (ctas * s_) / (((ctas * s_ + slots - 1) // slots) * slots)
+        return hi if eff(hi) >= eff(lo) else lo
     best, best_cost = 1, None
     for s in range(1, 17):
         if s > 1 and max_kv_len // s < 256:
