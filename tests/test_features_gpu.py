@@ -201,3 +201,27 @@ def test_qwen3_next_hybrid_on_gpu_matches_cpu_tokens():
             hit += sum(int(x == y) for x, y in zip(pred, c))
             tot += len(c)
     assert tot >= 10 and hit >= 0.8 * tot, (hit, tot, outs)
+
+
+def test_flux_transformer_on_device_matches_cpu():
+    """The Flux-family transformer in bf16 on the GPU (linears on the tcgen05 GEMM) against the same weights in
+    fp32 on the CPU."""
+    from xllm_b200.dit.flux import FluxArgs, FluxTransformer, image_ids, pack_latents
+    from xllm_b200.ops import launches
+    args = FluxArgs(in_channels=16, num_layers=2, num_single_layers=2, attention_head_dim=32, num_attention_heads=4,
+                    joint_attention_dim=64, pooled_projection_dim=32, axes_dims_rope=(8, 12, 12))
+    cpu = FluxTransformer(args)
+    cpu.init_random(std=0.05, seed=1)
+    gpu = FluxTransformer(args, dtype=torch.bfloat16, device="cuda")
+    gpu.load_weights(cpu.p.items())
+    g = torch.Generator().manual_seed(0)
+    lat = pack_latents(torch.randn(2, 4, 16, 16, generator=g))
+    text, pooled, t = torch.randn(2, 12, 64, generator=g), torch.randn(2, 32, generator=g), torch.tensor([0.8, 0.3])
+    gd = torch.tensor([3.5, 3.5])
+    want = cpu.forward(lat, text, pooled, t, image_ids(16, 16), torch.zeros(12, 3), gd)
+    n0 = launches()
+    got = gpu.forward(lat.cuda(), text.cuda(), pooled.cuda(), t.cuda(), image_ids(16, 16, "cuda"), torch.zeros(12, 3, device="cuda"),
+                      gd.cuda())
+    assert launches() > n0                                    # the hand-written GEMM ran
+    err = (got.float().cpu() - want).abs().max().item()
+    assert err < 0.05 * max(1.0, want.abs().max().item()), err

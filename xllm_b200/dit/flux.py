@@ -155,7 +155,12 @@ class FluxTransformer:
 
     # ---------------------------------------------------------------------------------------- pieces
     def _lin(self, name, x):
-        return F.linear(x, self.p[name + ".weight"], self.p.get(name + ".bias"))
+        w, b = self.p[name + ".weight"], self.p.get(name + ".bias")
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            # the tcgen05 GEMM with its bias epilogue (ops/gemm.py); shapes it cannot take are counted as fallbacks
+            from ..ops import gemm
+            return gemm.linear(x.reshape(-1, x.shape[-1]), w, b).view(*x.shape[:-1], w.shape[0])
+        return F.linear(x, w, b)
 
     def conditioning(self, timestep, guidance, pooled):
         """temb [B, D] from t in [0, 1], the guidance scale and the pooled text state."""
