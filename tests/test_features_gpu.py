@@ -95,8 +95,7 @@ def test_vlm_on_gpu_matches_cpu_tokens():
             vlm.engine.model.init_random(std=0.05, seed=3)
             cpu_params = dict(vlm.engine.model.named_params())
         else:   # the same weights on the GPU (random generators differ between devices)
-            for n, t in vlm.engine.model.named_params():
-                t.copy_(cpu_params[n].to(t.dtype))
+            vlm.engine.model.copy_params_from(cpu_params)
         vlm.processor = Qwen2VLImageProcessor(14, 2, 2, min_pixels=56 * 56, max_pixels=112 * 112)
         vlm.image_token_id = IMG
         outs[dev] = vlm.generate_mm(reqs, SamplingParams(max_tokens=5, temperature=0.0, ignore_eos=True))[0]
@@ -182,8 +181,7 @@ def test_qwen3_next_hybrid_on_gpu_matches_cpu_tokens():
             llm.engine.model.init_random(std=0.05, seed=5)
             params = dict(llm.engine.model.named_params())
         else:
-            for n, t in llm.engine.model.named_params():
-                t.copy_(params[n].to(t.dtype))
+            llm.engine.model.copy_params_from(params)
         outs[dev] = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
         # teacher-forced logits over prompt + the CPU continuation, one pass
         logits[dev] = [llm.engine.model.logits(hidden_states(llm.engine, p + c)).float().cpu()

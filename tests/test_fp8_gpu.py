@@ -124,7 +124,11 @@ def test_fp8_execution_engine_tracks_dequantised_engine():
             if src.dim() == 3:
                 t.copy_(torch.stack([f8.dequant_block128_ref(src[e], sc[e]) for e in range(src.shape[0])]))
             else:
-                t.copy_(f8.dequant_block128_ref(src, sc))
+                d = f8.dequant_block128_ref(src, sc)
+                if getattr(t, "_xllm_interleaved", False):       # the bf16 model keeps dense gate|up rows interleaved
+                    from xllm_b200.ops.gemm_tcgen05 import interleave_gate_up
+                    d = interleave_gate_up(*d.chunk(2))
+                t.copy_(d)
         else:
             t.copy_(src)
     g = torch.Generator().manual_seed(1)

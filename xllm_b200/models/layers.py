@@ -68,6 +68,20 @@ class Module:
         self._loaders: Dict[str, Callable[[torch.Tensor], None]] = {}
         self._children: Dict[str, "Module"] = {}
 
+    def copy_params_from(self, src: Dict[str, torch.Tensor]):
+        """Copies another instance's parameters (name -> tensor, e.g. `dict(other.named_params())`) into this
+        one, converting between the plain and the interleaved gate|up row layouts where the two differ (a CUDA
+        bf16 model stores dense-MLP gate_up weights interleaved, a CPU model does not)."""
+        from ..ops.gemm_tcgen05 import deinterleave_gate_up, interleave_gate_up
+        for n, t in self.named_params():
+            s = src[n]
+            di, si = bool(getattr(t, "_xllm_interleaved", False)), bool(getattr(s, "_xllm_interleaved", False))
+            if di and not si:
+                s = interleave_gate_up(*s.chunk(2))
+            elif si and not di:
+                s = torch.cat(deinterleave_gate_up(s))
+            t.copy_(s.to(t.dtype))
+
     def add_param(self, name, tensor, loaders: Optional[Dict[str, Callable]] = None):
         self._params[name] = tensor
         if loaders is None:
@@ -565,15 +579,19 @@ class DenseMLP(Module):
         for n, f in super().named_loaders(prefix):
             yield n.replace("gate_up_proj.", ""), f
 
-    def forward(self, x):
+    def hidden(self, x):
+        """act(x W_gate^T) * (x W_up^T): the input of the down projection, whatever the row layout of gate|up."""
         gu = self.gate_up
         if gu.interleaved:
             from ..ops import gemm, gemm_tcgen05
             if (x.is_cuda and x.dim() == 2 and x.shape[0] > 512 and gemm.gemm_mode() != "cublas" and gu.weight.shape[0] % 256 == 0
                     and gemm_tcgen05.supported(x, gu.weight)):
-                return self.down(gemm_tcgen05.gemm_act_mul(x, gu.weight, self.act))
+                return gemm_tcgen05.gemm_act_mul(x, gu.weight, self.act)
             y = gu(x)
-            return self.down(gemm_tcgen05.act_and_mul_interleaved(y.view(-1, y.shape[-1]), self.act).view(*y.shape[:-1], -1))
-        return self.down(ops.act_and_mul(gu(x), self.act))
+            return gemm_tcgen05.act_and_mul_interleaved(y.view(-1, y.shape[-1]), self.act).view(*y.shape[:-1], -1)
+        return ops.act_and_mul(gu(x), self.act)
+
+    def forward(self, x):
+        return self.down(self.hidden(x))
 
     __call__ = forward

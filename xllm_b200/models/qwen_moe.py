@@ -119,7 +119,7 @@ class SparseMoeBlock(Module):
             # the shared expert is TP-sharded like a dense MLP: its partial joins the routed partial.
             # With EP every rank would add the full shared output, so only the rank that owns
             # expert 0 contributes it.
-            hs = ops.act_and_mul(self.shared.gate_up(x), a.hidden_act)
+            hs = self.shared.hidden(x)
             if self.shared.down.fp8 is not None:
                 from .layers import _fp8_linear
                 shared_out = _fp8_linear(hs, self.shared.down.fp8.q, self.shared.down.fp8.scale)
