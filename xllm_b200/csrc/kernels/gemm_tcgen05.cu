@@ -238,12 +238,14 @@ __device__ __forceinline__ void epilogue_slice(uint32_t taddr, const CUtensorMap
           float f[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const float x = __uint_as_float(g[j * 8 + e]);
+            // gate and up are rounded to bf16 first, as the two-launch form stores them: a request's tokens
+            // must not depend on which of the two forms its batch size selects
+            const float x = __bfloat162float(__float2bfloat16(__uint_as_float(g[j * 8 + e])));
             float a;
             if (mode.act_mul == 1) a = x / (1.f + __expf(-x));
             else if (mode.act_mul == 2) a = 0.5f * x * (1.f + erff(x * 0.70710678f));
             else a = 0.5f * x * (1.f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x)));
-            f[e] = a * __uint_as_float(u[j * 8 + e]);
+            f[e] = a * __bfloat162float(__float2bfloat16(__uint_as_float(u[j * 8 + e])));
           }
           const bf16x8 v = pack8(f);
           const uint4 w4 = *reinterpret_cast<const uint4*>(&v);
