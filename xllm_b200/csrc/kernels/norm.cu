@@ -120,8 +120,11 @@ template <int QUANT>
 static int launch_rmsnorm(bf16* out, uint8_t* out_q, float* scales, const bf16* x, bf16* residual, const bf16* w,
                           const float* qscale, int tokens, int hidden, float eps, int64_t x_stride,
                           int64_t out_stride, int gemma, cudaStream_t s) {
-  const int tpr = row_group_threads(hidden);
+  int tpr = row_group_threads(hidden);
   if (hidden % 8 != 0 || tpr == 0) return (int)cudaErrorInvalidValue;
+  // few rows (decode steps): spread a row over more threads, so that the launch has at least one CTA per SM
+  // and a thread has fewer dependent loads (256 rows x 4096: 64 CTAs of 4 rows -> 256 CTAs of one row)
+  while (tpr < kRowThreads && (tokens + kRowThreads / tpr - 1) / (kRowThreads / tpr) < 148 && (hidden >> 3) >= 2 * tpr) tpr <<= 1;
   const int rows = kRowThreads / tpr;
   const dim3 grid((unsigned)((tokens + rows - 1) / rows)), block(kRowThreads);
 #define XLLM_NORM_CASE(T)                                                                                       \
