@@ -98,9 +98,10 @@ int main() {
   llm.WakeUp();
   std::string b = llm.Completions("[[1, 2, 3, 4, 5]]", sp);
   std::string beams = llm.Call("beam_search", R"({"prompt": [1, 2, 3, 4, 5], "beam_width": 2, "max_tokens": 3})");
+  std::string rec = llm.Recommend("[[1, 2, 3, 4, 5, 6, 7, 8]]", 3, 2);
   bool threw = false;
   try { llm.Call("no_such_method", "{}"); } catch (const std::exception& e) { threw = true; }
-  std::cout << "RESULT " << a << "\nAGAIN " << b << "\nBEAMS " << beams << "\nTHREW " << threw << "\n";
+  std::cout << "RESULT " << a << "\nAGAIN " << b << "\nBEAMS " << beams << "\nREC " << rec << "\nTHREW " << threw << "\n";
   return 0;
 }
 ''')
@@ -115,3 +116,6 @@ int main() {
     lines = {l.split(" ", 1)[0]: l.split(" ", 1)[1] for l in r.stdout.splitlines() if " " in l}
     assert json.loads(lines["RESULT"]) == json.loads(lines["AGAIN"]) and len(json.loads(lines["RESULT"])[0]["token_ids"]) == 4
     assert len(json.loads(lines["BEAMS"])) == 2 and lines["THREW"] == "1"
+    rec = json.loads(lines["REC"])
+    assert len(rec) == 1 and len(rec[0]) == 3 and all(len(it["token_ids"]) == 2 for it in rec[0])
+    assert rec[0][0]["logprob"] >= rec[0][1]["logprob"] >= rec[0][2]["logprob"]

@@ -45,6 +45,11 @@ def call(llm: LLM, method: str, args_json: str) -> str:
                               ignore_eos=bool(a.get("ignore_eos", False)))[0]     # one prompt -> its beams
         return json.dumps([{"token_ids": list(r.token_ids), "score": float(r.score),
                             "cumulative_logprob": float(r.cumulative_logprob)} for r in res])
+    if method == "recommend":
+        # the rec entry points of the reference's C API (c_api/rec.h): histories in, items with scores out
+        res = llm.recommend(a["prompts"], beam_width=int(a.get("beam_width", 32)), num_steps=int(a.get("num_steps", 3)),
+                            num_return=a.get("num_return"), valid_items=a.get("valid_items"))
+        return json.dumps([[{"token_ids": list(it.token_ids), "logprob": float(it.logprob)} for it in items] for items in res])
     if method == "sleep":
         llm.sleep(int(a.get("level", 1)))
         return json.dumps({"ok": True})

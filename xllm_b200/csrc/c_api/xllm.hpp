@@ -42,6 +42,11 @@ class LLM {
     return Call("chat", "{\"messages\": " + messages_json + ", \"sampling\": " + sampling_json + "}");
   }
   std::string Embeddings(const std::string& prompts_json) { return Call("embed", "{\"prompts\": " + prompts_json + "}"); }
+  // Generative recommendation: histories (JSON list of token-id lists) -> per history the best items with scores.
+  std::string Recommend(const std::string& histories_json, int beam_width = 32, int num_steps = 3) {
+    return Call("recommend", "{\"prompts\": " + histories_json + ", \"beam_width\": " + std::to_string(beam_width) +
+                                 ", \"num_steps\": " + std::to_string(num_steps) + "}");
+  }
   std::string Stats() { return take(xllm_llm_stats(need())); }
   void Sleep(int level = 1) { Call("sleep", "{\"level\": " + std::to_string(level) + "}"); }
   void WakeUp() { Call("wake_up", "{}"); }
