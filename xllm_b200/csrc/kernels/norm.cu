@@ -120,11 +120,12 @@ template <int QUANT>
 static int launch_rmsnorm(bf16* out, uint8_t* out_q, float* scales, const bf16* x, bf16* residual, const bf16* w,
                           const float* qscale, int tokens, int hidden, float eps, int64_t x_stride,
                           int64_t out_stride, int gemma, cudaStream_t s) {
-  int tpr = row_group_threads(hidden);
+  // The thread group of a row depends on the row width only, never on the number of rows: the order of the
+  // sum-of-squares reduction, and so every rounded output, is then the same whatever batch a row arrives in
+  // (spreading a row over more threads for small batches gains ~4 us per launch at 256 rows but makes a request's
+  // tokens depend on the batch it shares).
+  const int tpr = row_group_threads(hidden);
   if (hidden % 8 != 0 || tpr == 0) return (int)cudaErrorInvalidValue;
-  // few rows (decode steps): spread a row over more threads, so that the launch has at least one CTA per SM
-  // and a thread has fewer dependent loads (256 rows x 4096: 64 CTAs of 4 rows -> 256 CTAs of one row)
-  while (tpr < kRowThreads && (tokens + kRowThreads / tpr - 1) / (kRowThreads / tpr) < 148 && (hidden >> 3) >= 2 * tpr) tpr <<= 1;
   const int rows = kRowThreads / tpr;
   const dim3 grid((unsigned)((tokens + rows - 1) / rows)), block(kRowThreads);
 #define XLLM_NORM_CASE(T)                                                                                       \
