@@ -1490,6 +1490,15 @@ XLLM_API int xllm_gemm_bf16(const void* a, const void* w, void* c, const void* b
     sms = e ? atoi(e) : 148;
     if (sms < 2 || sms > 148) sms = 148;
   }
+  // Split-K sums its fp32 partial tiles with reduce-adds that land in L2 in whatever order the slices finish, so
+  // the last bits of a result can differ from run to run.  XLLM_GEMM_DETERMINISTIC=1 turns split-K off (one fixed
+  // summation order per output) at the cost of idle SMs on decode-size GEMMs.
+  static int deterministic = -1;
+  if (deterministic < 0) {
+    const char* e = getenv("XLLM_GEMM_DETERMINISTIC");
+    deterministic = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  if (deterministic) split_k = 1;
   if ((pair < 0 || tile_n == 0 || split_k == 0) && M <= 512) {
     // Decode-size batches (few row tiles).  Measured on B200: an MMA instruction costs ~75 cycles
     // whatever its width below 128 columns, so tiles narrower than 128 waste the tensor pipe; a
