@@ -10,7 +10,7 @@ the items of a catalogue.
 
 How one call runs on the device
   1. all prompts are prefilled together through the engine's model runner into paged KV blocks;
-  2. round 0 takes the top `W` first tokens of every request from the prefill logits;
+  2. the first beam step takes the top `W` first tokens of every request from the prefill logits;
   3. every later round is ONE forward of R x W rows: the rows' new KV goes to a tail cache
      [R*W, nkv, num_steps, d] and attention is x-attention (ops/xattn.py: the prompt's pages are read once
      per request on the tensor cores, the tail is merged per beam);
@@ -161,7 +161,7 @@ class RecEngine:
                           meta, kv)
         last = torch.tensor([c - 1 for c in cu[1:]], dtype=torch.long, device=dev)
         logits = self._logits(model, h[last])                              # [R, V]
-        # ---- round 0: the W best first tokens of every request
+        # ---- first beam step: the W best first tokens of every request
         lp, ids = self._candidates(logits, W, trie, [()] * R, dev)         # [R, W]
         cum = lp
         seqs = ids.to(torch.int64)[:, :, None]                             # [R, W, 1] tokens so far
