@@ -159,3 +159,84 @@ def test_vae_decoder_geometry_and_pipeline_end_to_end():
     calls["n"] = 0
     cached = pipe(ids, ids, height=32, width=48, steps=8, seed=1, cache=make_cache("residual", skip_interval=2, warmup=1))
     assert calls["n"] < n_exact and (cached - exact).abs().mean() < 0.2
+
+
+def _write_flux_checkpoint(root):
+    """A tiny checkpoint directory in the layout of the public releases."""
+    import json
+
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+    import transformers as t
+    from xllm_b200.utils.loader import save_file
+    args = FluxArgs(in_channels=16, num_layers=1, num_single_layers=1, attention_head_dim=16, num_attention_heads=2,
+                    joint_attention_dim=32, pooled_projection_dim=32, guidance_embeds=True, axes_dims_rope=(4, 6, 6))
+    tr = FluxTransformer(args)
+    tr.init_random(std=0.1, seed=7)
+    (root / "transformer").mkdir(parents=True)
+    (root / "transformer" / "config.json").write_text(json.dumps({**{k: getattr(args, k) for k in args.__dataclass_fields__},
+                                                                   "axes_dims_rope": list(args.axes_dims_rope)}))
+    save_file({k: v.contiguous() for k, v in tr.p.items()}, str(root / "transformer" / "diffusion_pytorch_model.safetensors"))
+    vae = VaeDecoder(latent_channels=4, block_out_channels=(8, 8, 16, 16), layers_per_block=1, norm_groups=4)
+    vae.init_random(seed=8)
+    (root / "vae").mkdir()
+    (root / "vae" / "config.json").write_text(json.dumps({"latent_channels": 4, "block_out_channels": [8, 8, 16, 16], "layers_per_block": 1,
+                                                          "norm_num_groups": 4, "scaling_factor": 0.3611, "shift_factor": 0.1159}))
+    save_file({k: v.contiguous() for k, v in vae.p.items()}, str(root / "vae" / "diffusion_pytorch_model.safetensors"))
+    torch.manual_seed(0)
+    t.CLIPTextModel(t.CLIPTextConfig(vocab_size=300, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2,
+                                     max_position_embeddings=16, eos_token_id=2, bos_token_id=0, pad_token_id=1)
+                    ).save_pretrained(str(root / "text_encoder"), safe_serialization=True)
+    t.T5EncoderModel(t.T5Config(vocab_size=300, d_model=32, d_kv=8, d_ff=64, num_layers=1, num_heads=4, relative_attention_num_buckets=8,
+                                relative_attention_max_distance=16, feed_forward_proj="gated-gelu", dropout_rate=0.0)
+                     ).save_pretrained(str(root / "text_encoder_2"), safe_serialization=True)
+    for sub in ("tokenizer", "tokenizer_2"):
+        tok = Tokenizer(models.BPE())
+        tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+        tok.decoder = decoders.ByteLevel()
+        tok.train_from_iterator(["a photo of a small red house by the sea at dusk " * 4],
+                                trainers.BpeTrainer(vocab_size=290, special_tokens=["<s>", "<pad>", "</s>"],
+                                                    initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
+        (root / sub).mkdir()
+        tok.save(str(root / sub / "tokenizer.json"))
+    (root / "model_index.json").write_text(json.dumps({"_class_name": "FluxPipeline"}))
+
+
+def test_flux_checkpoint_directory_and_image_route(tmp_path):
+    import base64
+    import http.client
+    import json
+    import threading
+    import zlib
+
+    from xllm_b200.api.server import ApiServer
+    from xllm_b200.dit.pipeline import FluxImagePipeline
+    from xllm_b200.engine.llm_engine import EngineConfig, LLMEngine
+    _write_flux_checkpoint(tmp_path / "flux")
+    pipe = FluxImagePipeline.from_pretrained(str(tmp_path / "flux"), steps=3)
+    assert pipe.pipe.transformer.args.num_layers == 1 and pipe.clip_len == 16
+    a = pipe.generate("a red house", size="32x48", seed=5)
+    b = pipe.generate("a red house", size="32x48", seed=5)
+    c = pipe.generate("the sea at dusk", size="32x48", seed=5)
+    assert a[0].shape == (48, 32, 3) and (a[0] == b[0]).all() and (a[0] != c[0]).any()       # the prompt matters
+    eng = LLMEngine(EngineConfig(model="tiny", device="cpu", dtype="float32", num_blocks=16, enable_graph=False))
+    srv = ApiServer(eng, None, model_name="flux-tiny", host="127.0.0.1", port=0, backend="dit")
+    srv.image_pipeline = pipe
+    t = threading.Thread(target=srv.serve_forever, args=(10,), daemon=True)
+    t.start()
+    try:
+        conn = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=120)
+        conn.request("POST", "/v1/images/generations", json.dumps({"prompt": "a red house", "size": "32x32", "n": 2, "seed": 1,
+                                                                    "num_inference_steps": 2}), {"Content-Type": "application/json"})
+        r = conn.getresponse()
+        out = json.loads(r.read().decode())
+        assert r.status == 200 and len(out["data"]) == 2
+        png = base64.b64decode(out["data"][0]["b64_json"])
+        assert png[:8] == b"\x89PNG\r\n\x1a\n" and int.from_bytes(png[16:20], "big") == 32 and int.from_bytes(png[20:24], "big") == 32
+        conn.request("POST", "/v1/images/generations", json.dumps({"prompt": "x", "size": "30x32"}), {"Content-Type": "application/json"})
+        r = conn.getresponse()
+        r.read()
+        assert r.status == 400
+        conn.close()
+    finally:
+        srv.shutdown()
+        t.join(timeout=5)

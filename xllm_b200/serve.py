@@ -89,8 +89,12 @@ def main(argv=None):
         os.environ.setdefault("RANK", str(flags.get_int("node_rank")))
         os.environ.setdefault("LOCAL_RANK", str(flags.get_int("node_rank")))
         ps = init_parallel(dp_size=flags.get_int("dp_size"), ep_size=flags.get_int("ep_size"))
-    engine = LLMEngine(build_engine_config(flags), ps=ps)
+    ecfg = build_engine_config(flags)
     model = flags.get("model")
+    if (flags.get("backend") or "") == "dit" and model and os.path.exists(os.path.join(model, "model_index.json")):
+        # the text engine is not what a diffusion instance serves: a placeholder keeps the server's plumbing uniform
+        ecfg.model, ecfg.device, ecfg.num_blocks, ecfg.enable_graph = "tiny", "cpu", 16, False
+    engine = LLMEngine(ecfg, ps=ps)
     tok = load_tokenizer(model) if model and os.path.isdir(model) else None
     name = flags.get("model_id") or (os.path.basename(model.rstrip("/")) if model else "xllm_b200")
     if ps is not None and ps.rank != 0:
@@ -103,6 +107,13 @@ def main(argv=None):
     if ps is not None:
         from .engine.replica import lead_ranks
         lead_ranks(srv, ps)
+    if (flags.get("backend") or "") == "dit" and model and os.path.exists(os.path.join(model, "model_index.json")):
+        # a diffusion checkpoint directory: /v1/images/generations runs its pipeline (the DiT master of the reference)
+        from .dit.pipeline import FluxImagePipeline
+        import torch
+        on_gpu = torch.cuda.is_available()
+        srv.image_pipeline = FluxImagePipeline.from_pretrained(model, torch.bfloat16 if on_gpu else torch.float32,
+                                                               "cuda:0" if on_gpu else "cpu")
     etcd = None
     if flags.get("etcd_addr"):
         # discovery as in the reference: the instance writes itself under a leased key that a keepalive

@@ -83,6 +83,8 @@ def load_tokenizer(model_dir: str, model_type: str = "") -> Optional[TokenizerWr
                 model_type = json.load(f).get("model_type", "")
     tj = os.path.join(model_dir, "tokenizer.json")
     spm_file = os.path.join(model_dir, "tokenizer.model")
+    if not os.path.exists(spm_file) and os.path.exists(os.path.join(model_dir, "spiece.model")):
+        spm_file = os.path.join(model_dir, "spiece.model")           # the name T5-family releases use
     rwkv = [x for x in os.listdir(model_dir) if x.startswith("rwkv_vocab") and x.endswith(".txt")]
     if not os.path.exists(tj) and os.path.exists(spm_file):
         from .tokenizer_extra import SentencePieceTokenizer
