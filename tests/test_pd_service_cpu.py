@@ -148,3 +148,47 @@ def test_decode_side_reclaims_when_the_prefill_instance_goes_away():
     d.drain()
     assert dsvc.stopped and d.scheduler.num_reserved() == 0
     assert d.scheduler.block_stats(0).num_used == 0 and dsvc.reclaimed_blocks > 0
+
+
+def test_offline_requests_decode_on_the_prefill_instance():
+    """Online / offline co-location: offline requests are not handed over; they decode on the prefill instance
+    between the online prompts, give the single-engine tokens, and go on when the decode instance is gone."""
+    g = torch.Generator().manual_seed(12)
+    online = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (20, 45)]
+    offline = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (30, 12, 60)]
+    llm = LLM("tiny", devices="cpu", dtype="float32", block_size=16, num_blocks=64, max_seqs_per_batch=8,
+              max_tokens_per_batch=128, enable_graph=False)
+    sp = SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)
+    want_on = [o.outputs[0].token_ids for o in llm.generate(online, sp)]
+    want_off = [o.outputs[0].token_ids for o in llm.generate(offline, sp)]
+    srv = Channel.listen()
+    child = _spawn_decode(srv.getsockname()[1])
+    try:
+        p, svc = _prefill_side(srv)
+        for i, pr in enumerate(offline):
+            assert svc.add_request(f"off{i}", pr, max_tokens=8, temperature=0.0, ignore_eos=True, offline=True)
+        for i, pr in enumerate(online):
+            assert svc.add_request(f"on{i}", pr, max_tokens=8, temperature=0.0, ignore_eos=True)
+        got, fin = {}, set()
+
+        def on(ev):
+            if ev.token >= 0:
+                got.setdefault(ev.request_id, []).append(ev.token)
+            if ev.request_finished:
+                fin.add(ev.request_id)
+
+        assert svc.run_until_done(on, max_seconds=120.0)
+        assert [got[f"on{i}"] for i in range(2)] == want_on and [got[f"off{i}"] for i in range(3)] == want_off
+        assert svc.handed_over == 2 and svc.kept_local == 3 and not svc.local and not svc.failed
+        assert p.scheduler.block_stats(0).num_used == 0
+        # the decode instance leaves: an offline request still runs to the end here
+        svc.close()
+        out, _ = child.communicate(timeout=60)
+        assert "adopted=2" in out, out
+        assert svc.add_request("late", offline[0], max_tokens=8, temperature=0.0, ignore_eos=True, offline=True)
+        got.pop("off0", None)
+        assert svc.run_until_done(on, max_seconds=60.0)
+        assert got["late"] == want_off[0]
+    finally:
+        if child.poll() is None:
+            child.kill()

@@ -427,6 +427,8 @@ class PrefillService:
         self.prompts: Dict[str, List[int]] = {}
         self.dst_blocks: Dict[str, List[int]] = {}
         self.pushed_upto: Dict[str, int] = {}        # first block index not yet pushed completely
+        self.local: set = set()                       # offline requests that decode on this instance
+        self.kept_local = 0
         self.retry_at: Dict[str, float] = {}
         self.awaiting_adopt: set = set()
         self.remote: set = set()                     # decoding on the peer
@@ -483,9 +485,20 @@ class PrefillService:
 
     # ---- intake
     def add_request(self, request_id: str, prompt_token_ids, max_tokens=16, **kw) -> bool:
+        """`offline=True`: the request is throughput work without a latency target (online / offline
+        co-location, xllm/core/scheduler/pd_ooc_scheduler.cpp): it is not handed to the decode instance but
+        decodes HERE, in the steps the scheduler has left after the online prompts, which preempt it
+        (`enable_online_preempt_offline`); the decode instance's capacity stays with the online requests."""
         toks = [int(t) for t in prompt_token_ids]
         if len(toks) + 1 >= self.e.max_model_len or request_id in self.params:
             return False
+        if kw.get("offline"):
+            pkw = {k: v for k, v in kw.items() if k != "stop_sequences"}
+            if not self.e.add_request(request_id, toks, max_tokens=int(max_tokens), **pkw):
+                return False
+            self.local.add(request_id)
+            self.kept_local += 1
+            return True
         self.params[request_id] = dict(kw, max_tokens=int(max_tokens))
         self.prompts[request_id] = toks
         if max_tokens <= 1:
@@ -495,6 +508,11 @@ class PrefillService:
         return True
 
     def abort(self, request_id: str):
+        if request_id in self.local:
+            self.local.discard(request_id)
+            self.e.abort(request_id)
+            self.e.scheduler.release_held(request_id)
+            return
         self.ch.send({"op": "cancel", "rid": request_id})
         self.e.abort(request_id)
         self._forget(request_id)
@@ -554,19 +572,27 @@ class PrefillService:
                         self.remote.discard(rid)
         if self.ch.closed:
             # the decode side is gone: everything that was not finished fails here
-            for rid in list(self.remote) + list(self.params):
+            for rid in list(self.remote) + list(self.params):        # (offline requests run here and go on)
                 self.failed[rid] = "decode instance went away"
                 out.append(_failure(rid, self.failed[rid]))
                 self.e.abort(rid)
                 self.e.scheduler.release_held(rid)
                 self._forget(rid)
-            return out
+            if not self.local:
+                return out
         if self.e.has_unfinished():
             events = self.e.step()
             if not self.e.scheduler.has_unfinished():
                 events = events + self.e.drain()
-            self.t.end_step(self.ch)
+            if not self.ch.closed:
+                self.t.end_step(self.ch)
             for ev in events:
+                if ev.request_id in self.local:          # an offline request: its whole stream is produced here
+                    out.append(ev)
+                    if ev.request_finished:
+                        self.local.discard(ev.request_id)
+                        self.e.scheduler.release_held(ev.request_id)
+                    continue
                 if ev.token < 0:
                     continue
                 rid = ev.request_id
