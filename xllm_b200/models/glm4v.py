@@ -16,7 +16,7 @@ from ..parallel.state import single
 from .families import Glm4CausalLM
 from .layers import Module
 from .qwen import DenseCausalLM
-from .qwen_vl import Qwen2VLForConditionalGeneration, _rms, _rot_half
+from .qwen_vl import Qwen2VLForConditionalGeneration, _linear, _rms, _rot_half
 from .registry import register_model
 
 
@@ -93,7 +93,7 @@ class Glm4vVisionTower(Module):
         """pixel_values [N_patches, C*tp*p*p] -> image token embeddings [N_patches / merge^2, out_hidden]."""
         p = self._params
         dt = p["patch_embed.proj.weight"].dtype
-        x = F.linear(pixel_values.to(dt), p["patch_embed.proj.weight"], p["patch_embed.proj.bias"])
+        x = _linear(pixel_values.to(dt), p["patch_embed.proj.weight"], p["patch_embed.proj.bias"])
         x = _rms(x, p["post_conv_layernorm.weight"], self.eps)
         hc, wc = self._coords(grid_thw, x.device)
         hd = self.dim // self.heads
@@ -111,7 +111,7 @@ class Glm4vVisionTower(Module):
         for i in range(self.depth):
             b = f"blocks.{i}."
             h_ = _rms(x, p[b + "norm1.weight"], self.eps)
-            q, k, v = F.linear(h_, p[b + "attn.qkv.weight"], p.get(b + "attn.qkv.bias")).view(T, 3, self.heads, hd).unbind(1)
+            q, k, v = _linear(h_, p[b + "attn.qkv.weight"], p.get(b + "attn.qkv.bias")).view(T, 3, self.heads, hd).unbind(1)
             qf, kf = q.float(), k.float()
             q = (qf * cos + _rot_half(qf) * sin).to(x.dtype)
             k = (kf * cos + _rot_half(kf) * sin).to(x.dtype)
@@ -120,18 +120,18 @@ class Glm4vVisionTower(Module):
                 o = F.scaled_dot_product_attention(q[a:e].transpose(0, 1)[None], k[a:e].transpose(0, 1)[None],
                                                    v[a:e].transpose(0, 1)[None])[0]
                 outs.append(o.transpose(0, 1).reshape(e - a, D))
-            x = x + F.linear(torch.cat(outs), p[b + "attn.proj.weight"])
+            x = x + _linear(torch.cat(outs), p[b + "attn.proj.weight"])
             h_ = _rms(x, p[b + "norm2.weight"], self.eps)
-            x = x + F.linear(act(F.linear(h_, p[b + "mlp.gate_proj.weight"])) * F.linear(h_, p[b + "mlp.up_proj.weight"]),
+            x = x + _linear(act(_linear(h_, p[b + "mlp.gate_proj.weight"])) * _linear(h_, p[b + "mlp.up_proj.weight"]),
                              p[b + "mlp.down_proj.weight"])
         x = _rms(x, p["post_layernorm.weight"], self.eps)
         m = self.merge
         # each group of m*m consecutive patches is one window [m, m, D]; the convolution sees it as [D, m, m]
         x = x.view(-1, m, m, D).permute(0, 3, 1, 2).reshape(-1, D * m * m)
-        x = F.linear(x, p["downsample.weight"], p["downsample.bias"])
-        y = F.linear(x, p["merger.proj.weight"])
+        x = _linear(x, p["downsample.weight"], p["downsample.bias"])
+        y = _linear(x, p["merger.proj.weight"])
         y = F.gelu(F.layer_norm(y, (self.out,), p["merger.post_projection_norm.weight"], p["merger.post_projection_norm.bias"], 1e-5))
-        return F.linear(act(F.linear(y, p["merger.gate_proj.weight"])) * F.linear(y, p["merger.up_proj.weight"]),
+        return _linear(act(_linear(y, p["merger.gate_proj.weight"])) * _linear(y, p["merger.up_proj.weight"]),
                         p["merger.down_proj.weight"])
 
     __call__ = forward

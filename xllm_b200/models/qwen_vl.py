@@ -19,6 +19,15 @@ from .registry import register_model
 from ..parallel.state import single
 
 
+def _linear(x, w, b=None):
+    """Linear layer of a vision tower: the tcgen05 GEMM (with its bias epilogue) for bf16 on the device, the tensor
+    library otherwise (shapes the kernel cannot take are counted as fallbacks by ops/gemm.py)."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        from ..ops import gemm
+        return gemm.linear(x.reshape(-1, x.shape[-1]), w, b).view(*x.shape[:-1], w.shape[0])
+    return F.linear(x, w, b)
+
+
 def _rot_half(x):
     x1, x2 = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2:]
     return torch.cat([-x2, x1], dim=-1)
@@ -59,7 +68,7 @@ class VisionBlock(Module):
         else:
             h = F.layer_norm(x, x.shape[-1:], p["norm1.weight"], p["norm1.bias"], 1e-6)
         T, D = h.shape
-        q, k, v = F.linear(h, p["attn.qkv.weight"], p["attn.qkv.bias"]).view(T, 3, self.heads, D // self.heads).unbind(1)
+        q, k, v = _linear(h, p["attn.qkv.weight"], p["attn.qkv.bias"]).view(T, 3, self.heads, D // self.heads).unbind(1)
         q = q * cos + _rot_half(q) * sin
         k = k * cos + _rot_half(k) * sin
         outs = []
@@ -67,16 +76,16 @@ class VisionBlock(Module):
             o = F.scaled_dot_product_attention(q[a:b].transpose(0, 1)[None], k[a:b].transpose(0, 1)[None],
                                                v[a:b].transpose(0, 1)[None])[0]
             outs.append(o.transpose(0, 1).reshape(b - a, D))
-        x = x + F.linear(torch.cat(outs), p["attn.proj.weight"], p["attn.proj.bias"])
+        x = x + _linear(torch.cat(outs), p["attn.proj.weight"], p["attn.proj.bias"])
         if self.gated:
             h = _rms(x, p["norm2.weight"])
-            g = F.silu(F.linear(h, p["mlp.gate_proj.weight"], p["mlp.gate_proj.bias"]))
-            u = F.linear(h, p["mlp.up_proj.weight"], p["mlp.up_proj.bias"])
-            return x + F.linear(g * u, p["mlp.down_proj.weight"], p["mlp.down_proj.bias"])
+            g = F.silu(_linear(h, p["mlp.gate_proj.weight"], p["mlp.gate_proj.bias"]))
+            u = _linear(h, p["mlp.up_proj.weight"], p["mlp.up_proj.bias"])
+            return x + _linear(g * u, p["mlp.down_proj.weight"], p["mlp.down_proj.bias"])
         h = F.layer_norm(x, x.shape[-1:], p["norm2.weight"], p["norm2.bias"], 1e-6)
-        h = F.linear(h, p["mlp.fc1.weight"], p["mlp.fc1.bias"])
+        h = _linear(h, p["mlp.fc1.weight"], p["mlp.fc1.bias"])
         h = h * torch.sigmoid(1.702 * h) if self.act == "quick_gelu" else F.gelu(h)
-        return x + F.linear(h, p["mlp.fc2.weight"], p["mlp.fc2.bias"])
+        return x + _linear(h, p["mlp.fc2.weight"], p["mlp.fc2.bias"])
 
     __call__ = forward
 
@@ -155,7 +164,7 @@ class VisionTower(Module):
     def forward(self, pixel_values, grid_thw):
         """pixel_values [N_patches, C*tp*p*p] -> image token embeddings [N_patches / merge^2, hidden]."""
         p = self._params
-        x = F.linear(pixel_values.to(p["patch_embed.proj.weight"].dtype), p["patch_embed.proj.weight"])
+        x = _linear(pixel_values.to(p["patch_embed.proj.weight"].dtype), p["patch_embed.proj.weight"])
         cos, sin = self.rot_pos_emb(grid_thw, x.device)
         cos, sin = cos.to(x.dtype), sin.to(x.dtype)
         sizes = [int(t * h * w) for t, h, w in grid_thw.tolist()]
@@ -176,8 +185,8 @@ class VisionTower(Module):
                 x = blk(x, cos, sin, cu)
             x = F.layer_norm(x, x.shape[-1:], p["merger.ln_q.weight"], p["merger.ln_q.bias"], 1e-6)
         x = x.view(-1, self.dim * m2)
-        x = F.gelu(F.linear(x, p["merger.mlp.0.weight"], p["merger.mlp.0.bias"]))
-        x = F.linear(x, p["merger.mlp.2.weight"], p["merger.mlp.2.bias"])
+        x = F.gelu(_linear(x, p["merger.mlp.0.weight"], p["merger.mlp.0.bias"]))
+        x = _linear(x, p["merger.mlp.2.weight"], p["merger.mlp.2.bias"])
         return x[torch.argsort(order)] if self.v25 else x
 
     __call__ = forward
@@ -268,14 +277,14 @@ class VisionTowerV3(Module):
             x = F.layer_norm(x.view(-1, D * m2), (D * m2,), p[pre + "norm.weight"], p[pre + "norm.bias"], 1e-6)
         else:
             x = F.layer_norm(x, (D,), p[pre + "norm.weight"], p[pre + "norm.bias"], 1e-6).view(-1, D * m2)
-        x = F.gelu(F.linear(x, p[pre + "linear_fc1.weight"], p[pre + "linear_fc1.bias"]))
-        return F.linear(x, p[pre + "linear_fc2.weight"], p[pre + "linear_fc2.bias"])
+        x = F.gelu(_linear(x, p[pre + "linear_fc1.weight"], p[pre + "linear_fc1.bias"]))
+        return _linear(x, p[pre + "linear_fc2.weight"], p[pre + "linear_fc2.bias"])
 
     rot_pos_emb = VisionTower.rot_pos_emb
 
     def forward(self, pixel_values, grid_thw):
         p, D = self._params, self.dim
-        x = F.linear(pixel_values.to(p["patch_embed.proj.weight"].dtype), p["patch_embed.proj.weight"], p["patch_embed.proj.bias"])
+        x = _linear(pixel_values.to(p["patch_embed.proj.weight"].dtype), p["patch_embed.proj.weight"], p["patch_embed.proj.bias"])
         x = x + self._pos_embed(grid_thw, x.device)
         cos, sin = self.rot_pos_emb(grid_thw, x.device)
         cos, sin = cos.to(x.dtype), sin.to(x.dtype)
@@ -288,7 +297,7 @@ class VisionTowerV3(Module):
             b = f"blocks.{i}."
             h_ = F.layer_norm(x, (D,), p[b + "norm1.weight"], p[b + "norm1.bias"], 1e-6)
             T = h_.shape[0]
-            q, k, v = F.linear(h_, p[b + "attn.qkv.weight"], p[b + "attn.qkv.bias"]).view(T, 3, self.heads, D // self.heads).unbind(1)
+            q, k, v = _linear(h_, p[b + "attn.qkv.weight"], p[b + "attn.qkv.bias"]).view(T, 3, self.heads, D // self.heads).unbind(1)
             q = q * cos + _rot_half(q) * sin
             k = k * cos + _rot_half(k) * sin
             outs = []
@@ -296,11 +305,11 @@ class VisionTowerV3(Module):
                 o = F.scaled_dot_product_attention(q[a0:b0].transpose(0, 1)[None], k[a0:b0].transpose(0, 1)[None],
                                                    v[a0:b0].transpose(0, 1)[None])[0]
                 outs.append(o.transpose(0, 1).reshape(b0 - a0, D))
-            x = x + F.linear(torch.cat(outs), p[b + "attn.proj.weight"], p[b + "attn.proj.bias"])
+            x = x + _linear(torch.cat(outs), p[b + "attn.proj.weight"], p[b + "attn.proj.bias"])
             h_ = F.layer_norm(x, (D,), p[b + "norm2.weight"], p[b + "norm2.bias"], 1e-6)
-            h_ = F.gelu(F.linear(h_, p[b + "mlp.linear_fc1.weight"], p[b + "mlp.linear_fc1.bias"]),
+            h_ = F.gelu(_linear(h_, p[b + "mlp.linear_fc1.weight"], p[b + "mlp.linear_fc1.bias"]),
                         approximate="tanh" if "tanh" in self.act else "none")
-            x = x + F.linear(h_, p[b + "mlp.linear_fc2.weight"], p[b + "mlp.linear_fc2.bias"])
+            x = x + _linear(h_, p[b + "mlp.linear_fc2.weight"], p[b + "mlp.linear_fc2.bias"])
             if i in self.deep_idx:
                 deep.append(self._merge(f"deepstack_merger_list.{self.deep_idx.index(i)}.", x, True))
         return torch.cat([self._merge("merger.", x, False)] + deep, dim=-1)
