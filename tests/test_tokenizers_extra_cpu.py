@@ -48,3 +48,44 @@ def test_sentencepiece_roundtrip(tmp_path):
     ids = tw.encode("the quick dog")
     assert tw.decode(ids) == "the quick dog"
     assert tw.token_to_id("▁the") >= 0
+
+
+def test_clip_bpe_matches_huggingface(tmp_path):
+    """CLIP's tokenizer from vocab.json + merges.txt against transformers' slow CLIPTokenizer."""
+    import json
+
+    transformers = pytest.importorskip("transformers")
+    from xllm_b200.utils.tokenizer import load_tokenizer
+    from xllm_b200.utils.tokenizer_extra import ClipBpeTokenizer
+    probe = ClipBpeTokenizer.__new__(ClipBpeTokenizer)
+    # a small vocabulary: all byte symbols (plain and end-of-word), a few merges, the two specials
+    bs = list(range(ord("!"), ord("~") + 1)) + list(range(0xA1, 0xAD)) + list(range(0xAE, 0x100))
+    cs, n = bs[:], 0
+    for b in range(256):
+        if b not in bs:
+            bs.append(b)
+            cs.append(256 + n)
+            n += 1
+    symbols = [chr(c) for c in cs]
+    merges = [("h", "o"), ("ho", "u"), ("hou", "se</w>"), ("s", "e</w>"), ("r", "e"), ("re", "d</w>"), ("t", "h"), ("th", "e</w>"),
+              ("a</w>",) * 1 + ("x",)][:-1]
+    vocab = {}
+    for s in symbols:
+        vocab[s] = len(vocab)
+    for s in symbols:
+        vocab[s + "</w>"] = len(vocab)
+    for a, b in merges:
+        vocab[a + b] = len(vocab)
+    vocab["<|startoftext|>"] = len(vocab)
+    vocab["<|endoftext|>"] = len(vocab)
+    (tmp_path / "vocab.json").write_text(json.dumps(vocab))
+    (tmp_path / "merges.txt").write_text("#version: 0.2\n" + "\n".join(f"{a} {b}" for a, b in merges) + "\n")
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps({"tokenizer_class": "CLIPTokenizer"}))
+    hf = transformers.CLIPTokenizer(str(tmp_path / "vocab.json"), str(tmp_path / "merges.txt"))
+    mine = load_tokenizer(str(tmp_path))
+    assert isinstance(mine.impl, ClipBpeTokenizer)
+    for text in ("The red house", "  a  RED   house, the sea!  ", "it's 42 houses: théâtre", "x"):
+        want = hf(text, add_special_tokens=False)["input_ids"]
+        assert mine.encode(text) == want, text
+    assert mine.impl.encode("the house", add_special=True) == hf("the house")["input_ids"]
+    assert mine.decode(mine.encode("the red house")) == "the red house"

@@ -90,6 +90,12 @@ def load_tokenizer(model_dir: str, model_type: str = "") -> Optional[TokenizerWr
         from .tokenizer_extra import SentencePieceTokenizer
         return TokenizerWrapper(SentencePieceTokenizer(spm_file, bool(cfg.get("add_bos_token")),
                                                        bool(cfg.get("add_eos_token"))), model_dir, cfg, model_type)
+    if not os.path.exists(tj) and not os.path.exists(spm_file) and os.path.exists(os.path.join(model_dir, "merges.txt")) \
+            and os.path.exists(os.path.join(model_dir, "vocab.json")) and (model_type.startswith("clip") or
+                                                                          "CLIP" in str(cfg.get("tokenizer_class", ""))):
+        from .tokenizer_extra import ClipBpeTokenizer
+        return TokenizerWrapper(ClipBpeTokenizer(os.path.join(model_dir, "vocab.json"), os.path.join(model_dir, "merges.txt")),
+                                model_dir, cfg, model_type)
     if not os.path.exists(tj) and rwkv:
         from .tokenizer_extra import RwkvTokenizer
         return TokenizerWrapper(RwkvTokenizer(os.path.join(model_dir, rwkv[0])), model_dir, cfg, model_type)

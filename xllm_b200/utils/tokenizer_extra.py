@@ -122,3 +122,90 @@ class PyIncrementalDecoder:
             return ""
         out, self.sent = text[self.sent:], len(text)
         return out
+
+
+class ClipBpeTokenizer:
+    """CLIP's text tokenizer from its original file pair (`vocab.json`, `merges.txt`): lower-cased, whitespace
+    collapsed, split by CLIP's pattern, bytes mapped to printable code points, merges applied with the
+    end-of-word marker `</w>` on a word's last symbol.  The tokenizer of the first text encoder of the
+    diffusion pipelines (xllm/models/dit/ tokenizers of the reference)."""
+
+    def __init__(self, vocab_file: str, merges_file: str):
+        import json
+
+        import regex
+        with open(vocab_file, encoding="utf-8") as f:
+            self.vocab: Dict[str, int] = json.load(f)
+        self.inv = {i: t for t, i in self.vocab.items()}
+        with open(merges_file, encoding="utf-8") as f:
+            lines = [l.rstrip("\n") for l in f if l.strip() and not l.startswith("#version")]
+        self.ranks = {tuple(l.split()): i for i, l in enumerate(lines)}
+        bs = list(range(ord("!"), ord("~") + 1)) + list(range(ord("¡"), ord("¬") + 1)) + list(range(ord("®"), ord("ÿ") + 1))
+        cs = bs[:]
+        n = 0
+        for b in range(256):
+            if b not in bs:
+                bs.append(b)
+                cs.append(256 + n)
+                n += 1
+        self.byte_enc = {b: chr(c) for b, c in zip(bs, cs)}
+        self.byte_dec = {v: k for k, v in self.byte_enc.items()}
+        self.pat = regex.compile(r"<\|startoftext\|>|<\|endoftext\|>|'s|'t|'re|'ve|'m|'ll|'d|[\p{L}]+|[\p{N}]|[^\s\p{L}\p{N}]+",
+                                 regex.IGNORECASE)
+        self.bos_id = self.vocab.get("<|startoftext|>", -1)
+        self.eos_id = self.vocab.get("<|endoftext|>", -1)
+        self.cache: Dict[str, List[str]] = {}
+
+    @property
+    def vocab_size(self) -> int:
+        return len(self.vocab)
+
+    def _bpe(self, token: str) -> List[str]:
+        if token in self.cache:
+            return self.cache[token]
+        word = list(token[:-1]) + [token[-1] + "</w>"]
+        while len(word) > 1:
+            pairs = [(self.ranks.get((a, b), 1 << 30), i) for i, (a, b) in enumerate(zip(word, word[1:]))]
+            rank, _ = min(pairs)
+            if rank == 1 << 30:
+                break
+            first, second = next(p for p, r in self.ranks.items() if r == rank)
+            out, i = [], 0
+            while i < len(word):
+                if i + 1 < len(word) and word[i] == first and word[i + 1] == second:
+                    out.append(first + second)
+                    i += 2
+                else:
+                    out.append(word[i])
+                    i += 1
+            word = out
+        self.cache[token] = word
+        return word
+
+    def encode(self, text: str, add_special: bool = False) -> List[int]:
+        text = " ".join(text.split()).strip().lower()
+        ids: List[int] = []
+        for tok in self.pat.findall(text):
+            if tok in ("<|startoftext|>", "<|endoftext|>"):
+                ids.append(self.vocab[tok])
+                continue
+            mapped = "".join(self.byte_enc[b] for b in tok.encode("utf-8"))
+            unk = self.eos_id if self.eos_id >= 0 else 0
+            ids.extend(self.vocab.get(piece, unk) for piece in self._bpe(mapped))
+        if add_special:
+            ids = ([self.bos_id] if self.bos_id >= 0 else []) + ids + ([self.eos_id] if self.eos_id >= 0 else [])
+        return ids
+
+    def decode(self, ids, skip_special: bool = True) -> str:
+        toks = [self.inv.get(int(i), "") for i in ids]
+        if skip_special:
+            toks = [t for t in toks if t not in ("<|startoftext|>", "<|endoftext|>")]
+        words = "".join(toks).split("</w>")
+        return " ".join(bytearray(self.byte_dec[c] for c in w if c in self.byte_dec).decode("utf-8", errors="replace")
+                        for w in words).strip()
+
+    def token_to_id(self, tok: str) -> int:
+        return self.vocab.get(tok, -1)
+
+    def id_to_token(self, i: int) -> str:
+        return self.inv.get(int(i), "")
