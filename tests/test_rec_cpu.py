@@ -109,3 +109,45 @@ def test_rec_backend_over_http_and_offline_api():
     finally:
         srv.shutdown()
         t.join(timeout=5)
+
+
+def test_item_trie_masks_and_node_ids_match_brute_force():
+    """The CSR trie's masks and node transitions against sets built by hand, for a random catalogue with
+    shared prefixes, duplicates and beams that leave the catalogue."""
+    g = torch.Generator().manual_seed(5)
+    V, depth = 97, 3
+    items = torch.randint(0, 12, (400, depth), generator=g).tolist() + torch.randint(0, V, (300, depth), generator=g).tolist()
+    trie = ItemTrie(items + items[:50], V)
+    assert trie.n_items == len({tuple(i) for i in items}) and trie.depth == depth
+    cat = {tuple(i) for i in items}
+    assert tuple(items[3]) in trie
+    assert ((96, 96, 96) in trie) == ((96, 96, 96) in cat)
+    rows = 64
+    prefixes = [tuple(items[i][:0]) for i in range(rows)]
+    nodes = trie.root(rows)
+    for level in range(depth):
+        mask = trie.mask_of(level, nodes)
+        for r, pre in enumerate(prefixes):
+            want = {it[level] for it in cat if it[:level] == pre} if pre is not None else set()
+            assert set(mask[r].nonzero().flatten().tolist()) == want, (level, r)
+        # half the rows follow an item, a quarter take a random token, a quarter are already dead
+        nxt = []
+        for r, pre in enumerate(prefixes):
+            if pre is not None and r % 4 != 3:
+                nxt.append(items[(r * 7) % len(items)][level] if items[(r * 7) % len(items)][:level] == list(pre) else
+                           next(iter(sorted(it[level] for it in cat if it[:level] == pre))))
+            else:
+                nxt.append(int(torch.randint(0, V, (1,), generator=g)))
+        nodes = trie.advance(level, nodes, torch.tensor(nxt))
+        new_prefixes = []
+        for r, pre in enumerate(prefixes):
+            p = None if pre is None else pre + (nxt[r],)
+            if p is not None and not any(it[:level + 1] == p for it in cat):
+                p = None
+            new_prefixes.append(p)
+            assert (int(nodes[r]) >= 0) == (p is not None), (level, r)
+        prefixes = new_prefixes
+    assert any(p is None for p in prefixes) and any(p is not None for p in prefixes)
+    assert torch.equal(trie.allowed([tuple(items[0][:2]), tuple(items[1][:2])], "cpu"),
+                       torch.stack([torch.tensor([any(it[:2] == tuple(items[j][:2]) and it[2] == v for it in cat) for v in range(V)])
+                                    for j in (0, 1)]))

@@ -36,34 +36,99 @@ class RecItem:
 
 
 class ItemTrie:
-    """The catalogue of valid items as a prefix tree over their token tuples; `allowed(prefixes)` gives the
-    admissible next tokens of a batch of prefixes as a boolean mask (rows x vocab) built on the device from
-    one index tensor per call (core/framework/request/rec_type.h / valid path filter of the rec sampler)."""
+    """The catalogue of valid items as a prefix tree over their token tuples, stored as one CSR table per level
+    on the device: node n of level l has the children tokens `tok[l][ptr[l][n] : ptr[l][n + 1]]` (sorted), and
+    child j of that range is node `ptr[l][n] + j` of level l + 1.  A beam carries its node id; the admissible
+    next tokens of a batch of beams become a boolean mask with two tensor operations (`mask_of`), and after a
+    beam step the survivors' node ids follow by a binary search in their parents' ranges (`advance`) — no host
+    loop over rows, so catalogues of millions of items and thousands of beam rows cost the same few launches
+    (the valid-path filter of the reference's rec sampler, core/framework/sampling/valid_path_filter.cpp)."""
 
-    def __init__(self, items: Sequence[Sequence[int]], vocab_size: int):
-        self.vocab = vocab_size
-        self.depth = len(items[0]) if items else 0
-        self.children: Dict[Tuple[int, ...], List[int]] = {}
-        for it in items:
-            assert len(it) == self.depth, "items of one catalogue have the same number of tokens"
-            for i in range(self.depth):
-                self.children.setdefault(tuple(it[:i]), [])
-                if it[i] not in self.children[tuple(it[:i])]:
-                    self.children[tuple(it[:i])].append(int(it[i]))
+    def __init__(self, items: Sequence[Sequence[int]], vocab_size: int, device="cpu"):
+        import numpy as np
+        self.vocab = int(vocab_size)
+        arr = np.asarray([list(map(int, it)) for it in items], dtype=np.int64).reshape(len(items), -1)
+        self.depth = arr.shape[1] if arr.size else 0
+        self.n_items = 0
+        self.ptr: List[torch.Tensor] = []
+        self.tok: List[torch.Tensor] = []
+        self.key: List[torch.Tensor] = []                    # parent node * vocab + token of every child: sorted
+        self.device = torch.device(device)
+        if arr.size == 0:
+            return
+        arr = np.unique(arr, axis=0)                       # sorted lexicographically, duplicates dropped
+        self.n_items = arr.shape[0]
+        node = np.zeros(arr.shape[0], dtype=np.int64)        # node id (within its level) of every item's prefix
+        n_nodes = 1
+        for l in range(self.depth):
+            key = node * self.vocab + arr[:, l]
+            uniq, inv = np.unique(key, return_inverse=True)   # children of all nodes of this level, in node order
+            parent = uniq // self.vocab
+            ptr = np.zeros(n_nodes + 1, dtype=np.int64)
+            np.add.at(ptr, parent + 1, 1)
+            self.ptr.append(torch.from_numpy(np.cumsum(ptr)).to(self.device))
+            self.tok.append(torch.from_numpy(uniq % self.vocab).to(self.device))
+            self.key.append(torch.from_numpy(uniq).to(self.device))
+            node, n_nodes = inv.reshape(-1).astype(np.int64), uniq.shape[0]
 
-    def allowed(self, prefixes: Sequence[Sequence[int]], device) -> torch.Tensor:
-        rows, cols = [], []
-        for r, p in enumerate(prefixes):
-            nxt = self.children.get(tuple(int(t) for t in p), ())
-            rows.extend([r] * len(nxt))
-            cols.extend(nxt)
-        mask = torch.zeros((len(prefixes), self.vocab), dtype=torch.bool, device=device)
-        if rows:
-            mask[torch.tensor(rows, device=device), torch.tensor(cols, device=device)] = True
+    def to(self, device) -> "ItemTrie":
+        if torch.device(device) != self.device:
+            self.device = torch.device(device)
+            self.ptr = [t.to(device) for t in self.ptr]
+            self.tok = [t.to(device) for t in self.tok]
+            self.key = [t.to(device) for t in self.key]
+        return self
+
+    def root(self, rows: int) -> torch.Tensor:
+        return torch.zeros(rows, dtype=torch.int64, device=self.device)
+
+    def mask_of(self, level: int, nodes: torch.Tensor) -> torch.Tensor:
+        """Boolean [rows, vocab]: the tokens that continue the prefix of each row (node < 0: a dead row, none)."""
+        rows = nodes.shape[0]
+        mask = torch.zeros((rows, self.vocab), dtype=torch.bool, device=self.device)
+        live = nodes >= 0
+        n = nodes.clamp(min=0)
+        lo, hi = self.ptr[level][n], self.ptr[level][n + 1]
+        cnt = torch.where(live, hi - lo, torch.zeros_like(lo))
+        total = int(cnt.sum())
+        if total == 0:
+            return mask
+        row_of = torch.repeat_interleave(torch.arange(rows, device=self.device), cnt)
+        start = torch.repeat_interleave(lo, cnt)
+        within = torch.arange(total, device=self.device) - torch.repeat_interleave(torch.cumsum(cnt, 0) - cnt, cnt)
+        mask[row_of, self.tok[level][start + within]] = True
         return mask
 
+    def advance(self, level: int, nodes: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+        """Node ids (level + 1) of the rows after appending `tokens`; -1 where the token does not continue the row."""
+        live = nodes >= 0
+        n = nodes.clamp(min=0)
+        # (parent, token) keys of a level are sorted as a whole: one binary search finds the child
+        key = n * self.vocab + tokens.to(torch.int64)
+        run_key = self.key[level]
+        pos = torch.searchsorted(run_key, key)
+        ok = live & (run_key[pos.clamp(max=run_key.shape[0] - 1)] == key)
+        return torch.where(ok, pos, torch.full_like(pos, -1))
+
+    # ---- prefix-tuple interface (host side; tests and small catalogues)
+    def allowed(self, prefixes: Sequence[Sequence[int]], device) -> torch.Tensor:
+        self.to(device)
+        nodes = self.root(len(prefixes))
+        level = len(prefixes[0]) if len(prefixes) else 0
+        if level:
+            p = torch.tensor([[int(t) for t in pre] for pre in prefixes], dtype=torch.int64, device=self.device)
+            for l in range(level):
+                nodes = self.advance(l, nodes, p[:, l])
+        return self.mask_of(level, nodes)
+
     def __contains__(self, item):
-        return tuple(item[:-1]) in self.children and int(item[-1]) in self.children[tuple(item[:-1])]
+        if len(item) != self.depth or self.depth == 0:
+            return False
+        nodes = self.root(1)
+        t = torch.tensor([[int(x) for x in item]], dtype=torch.int64, device=self.device)
+        for l in range(self.depth):
+            nodes = self.advance(l, nodes, t[:, l])
+        return bool(nodes[0] >= 0)
 
 
 class _Tail:
@@ -162,7 +227,13 @@ class RecEngine:
         last = torch.tensor([c - 1 for c in cu[1:]], dtype=torch.long, device=dev)
         logits = self._logits(model, h[last])                              # [R, V]
         # ---- first beam step: the W best first tokens of every request
-        lp, ids = self._candidates(logits, W, trie, [()] * R, dev)         # [R, W]
+        nodes = None
+        if trie is not None:
+            trie.to(dev)
+            nodes = trie.root(R)
+        lp, ids = self._candidates(logits, W, None if trie is None else trie.mask_of(0, nodes))      # [R, W]
+        if trie is not None:
+            nodes = trie.advance(0, nodes.repeat_interleave(W), ids.reshape(-1).to(torch.int64))
         cum = lp
         seqs = ids.to(torch.int64)[:, :, None]                             # [R, W, 1] tokens so far
         rows = R * W
@@ -178,12 +249,13 @@ class RecEngine:
                                      kv_lens=kv_lens, cu_q=cu_b, max_q_len=W, max_kv_len=max(lens) + s, xattn=tail)
             h = model.forward(seqs[:, :, -1].reshape(rows).contiguous(), row_pos + (s - 1), meta, kv)
             logits = self._logits(model, h)                                # [R*W, V]
-            lp, ids = self._candidates(logits, k_cand, trie, None if trie is None else seqs.reshape(rows, -1).tolist(),
-                                       dev)                                # [R*W, k]
+            lp, ids = self._candidates(logits, k_cand, None if trie is None else trie.mask_of(s, nodes))    # [R*W, k]
             tok, par, cum = select.beam_step(lp.view(R, W, k_cand), ids.view(R, W, k_cand), cum, W)
             par64 = par.to(torch.int64)
             seqs = torch.cat([seqs.gather(1, par64[:, :, None].expand(R, W, seqs.shape[2])),
                               tok.to(torch.int64)[:, :, None]], dim=2)
+            if trie is not None and s + 1 < S:
+                nodes = trie.advance(s, nodes.view(R, W).gather(1, par64).reshape(-1), tok.reshape(-1).to(torch.int64))
             if s + 1 < S:                                                  # survivors inherit their parents' tails
                 gpar = (par64 + torch.arange(R, device=dev)[:, None] * W).reshape(rows)
                 tail.anc = tail.anc[:, gpar].contiguous()
@@ -197,13 +269,13 @@ class RecEngine:
         return out
 
     @staticmethod
-    def _candidates(logits, k, trie, prefixes, dev):
+    def _candidates(logits, k, mask=None):
         """The k most likely next tokens of every row with their log-probabilities under the model's full
-        distribution; with a catalogue, tokens that leave it score -inf."""
-        if trie is None:
+        distribution; with a catalogue mask, tokens that leave the catalogue score -inf."""
+        if mask is None:
             lp, ids = select.topk(logits, k, normalize=True)
         else:
-            full = select.log_softmax(logits).masked_fill(~trie.allowed(prefixes, dev), float("-inf"))
+            full = select.log_softmax(logits).masked_fill(~mask, float("-inf"))
             lp, ids = select.topk(full, k)
         lp = lp.float()
         return torch.where(torch.isfinite(lp), lp, torch.full_like(lp, float("-inf"))), ids

@@ -258,24 +258,32 @@ class OneRecModel:
         enc_mask = torch.zeros(R, 1, 1, L, device=dev).masked_fill(pad[:, None, None, :], float("-inf"))
         start = torch.full((R, 1), a.decoder_start_token_id, dtype=torch.long, device=dev)
 
-        def candidates(logits, k, prefixes):
-            if trie is None:
+        def candidates(logits, k, mask):
+            if mask is None:
                 lp, ids = select.topk(logits.float(), k, normalize=True)
             else:
-                full = select.log_softmax(logits.float()).masked_fill(~trie.allowed(prefixes, dev), float("-inf"))
+                full = select.log_softmax(logits.float()).masked_fill(~mask, float("-inf"))
                 lp, ids = select.topk(full, k)
             lp = lp.float()
             return torch.where(torch.isfinite(lp), lp, torch.full_like(lp, float("-inf"))), ids
 
-        cum, ids = candidates(self.decode(start, cross, enc_mask, 1), W, [()] * R)
+        nodes = None
+        if trie is not None:
+            trie.to(dev)
+            nodes = trie.root(R)
+        cum, ids = candidates(self.decode(start, cross, enc_mask, 1), W, None if trie is None else trie.mask_of(0, nodes))
+        if trie is not None:
+            nodes = trie.advance(0, nodes.repeat_interleave(W), ids.reshape(-1).to(torch.long))
         seqs = ids.to(torch.long)[:, :, None]                                      # [R, W, 1]
         k_cand = min(W, V)
         for s in range(1, num_steps):
             dec = torch.cat([start.repeat_interleave(W, 0), seqs.reshape(R * W, -1)], dim=1)
             logits = self.decode(dec, cross, enc_mask, W)
-            lp, ids = candidates(logits, k_cand, None if trie is None else seqs.reshape(R * W, -1).tolist())
+            lp, ids = candidates(logits, k_cand, None if trie is None else trie.mask_of(s, nodes))
             tok, par, cum = select.beam_step(lp.view(R, W, k_cand), ids.view(R, W, k_cand), cum, W)
             par = par.to(torch.long)
+            if trie is not None and s + 1 < num_steps:
+                nodes = trie.advance(s, nodes.view(R, W).gather(1, par).reshape(-1), tok.reshape(-1).to(torch.long))
             seqs = torch.cat([seqs.gather(1, par[:, :, None].expand(R, W, seqs.shape[2])), tok.to(torch.long)[:, :, None]], dim=2)
         cum_h, seq_h = cum.tolist(), seqs.tolist()
         out = []
