@@ -305,7 +305,8 @@ class LLM:
     def recommend(self, prompts, beam_width: int = 32, num_steps: int = 3, num_return: Optional[int] = None,
                   valid_items=None, prompt_embeds=None):
         """Generative recommendation: for every prompt (token-id list or string) the `beam_width` most likely
-        items of `num_steps` tokens, best first, optionally restricted to `valid_items` (token tuples).  All
+        items of `num_steps` tokens, best first, optionally restricted to `valid_items` (token tuples, or an
+        `ItemTrie` built once from them and passed to every call).  All
         prompts run as one batch (engine/rec.py; the reference's rec backend)."""
         from ..engine.rec import ItemTrie, RecEngine
         if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
@@ -313,7 +314,10 @@ class LLM:
         ids = [self._encode(p) if isinstance(p, str) else [int(t) for t in p] for p in prompts]
         if getattr(self, "_rec", None) is None:
             self._rec = RecEngine(self.engine)
-        trie = ItemTrie([tuple(i) for i in valid_items], self.engine.args.vocab_size) if valid_items else None
+        if isinstance(valid_items, ItemTrie):
+            trie = valid_items
+        else:
+            trie = ItemTrie([tuple(i) for i in valid_items], self.engine.args.vocab_size) if valid_items else None
         return self._rec.generate(ids, beam_width=beam_width, num_steps=num_steps, num_return=num_return, trie=trie,
                                   prompt_embeds=prompt_embeds)
 

@@ -47,7 +47,12 @@ class ItemTrie:
     def __init__(self, items: Sequence[Sequence[int]], vocab_size: int, device="cpu"):
         import numpy as np
         self.vocab = int(vocab_size)
-        arr = np.asarray([list(map(int, it)) for it in items], dtype=np.int64).reshape(len(items), -1)
+        if isinstance(items, torch.Tensor):
+            items = items.cpu().numpy()
+        if isinstance(items, np.ndarray):                    # [n_items, depth] already: no per-item Python work
+            arr = items.astype(np.int64).reshape(items.shape[0], -1)
+        else:
+            arr = np.asarray([list(map(int, it)) for it in items], dtype=np.int64).reshape(len(items), -1)
         self.depth = arr.shape[1] if arr.size else 0
         self.n_items = 0
         self.ptr: List[torch.Tensor] = []
