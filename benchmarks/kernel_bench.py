@@ -48,7 +48,28 @@ def bench(fn, iters=10, warmup=3):
         torch.cuda.synchronize()
         ts.append(e0.elapsed_time(e1))
     ts.sort()
-    return ts[len(ts) // 2] * 1e-3
+    return ts[len(ts) // 2] * 1e-3 if ts else 0.0
+
+
+def bench_pair(fa, fb, iters=10, warmup=3):
+    """Two alternatives timed alternately (a, b, a, b, ...), L2 flushed before each: clock drift under the
+    power cap hits both alike.  Returns the two medians in seconds."""
+    bench(fa, iters=0, warmup=warmup)
+    bench(fb, iters=0, warmup=warmup)
+    ta, tb = [], []
+    for _ in range(iters):
+        for f, ts in ((fa, ta), (fb, tb)):
+            _flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            f()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+    ta.sort()
+    tb.sort()
+    return ta[len(ta) // 2] * 1e-3, tb[len(tb) // 2] * 1e-3
 
 
 def bench_rotating(fns, rounds=5, warmup=1):
@@ -234,6 +255,28 @@ def fp8_rows(results, hbm, tf, tag):
               f"{t_pt*1e3:7.3f} ms | bf16 tcgen05 {t_bf*1e3:7.3f} ms | cuBLAS bf16 {t_lib*1e3:7.3f} ms")
 
 
+def moe_rows(results, hbm, tf, tag):
+    """The whole MoE layer (route, permute, grouped GEMM gate|up, SiLU-mul, grouped GEMM down, finalize) on
+    Qwen3-30B-A3B and DeepSeek-V3-like expert shapes: the three-launch expert form against the grouped GEMM
+    with the gated activation in its epilogue (interleaved expert weights)."""
+    from xllm_b200.ops import moe
+    for T, E, K, H, I, name in ((8192, 128, 8, 2048, 768, "qwen3-30b-a3b prefill"), (256, 128, 8, 2048, 768, "qwen3-30b-a3b decode"),
+                                (8192, 32, 8, 7168, 2048, "deepseek-v3 experts of one EP-8 rank")):
+        x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+        logits = torch.randn(T, E, device="cuda")
+        w1 = torch.randn(E, 2 * I, H, device="cuda", dtype=torch.bfloat16) * 0.05
+        w2 = torch.randn(E, H, I, device="cuda", dtype=torch.bfloat16) * 0.05
+        ws = moe.MoeWorkspace(T, K, E, E, H, I, "cuda")
+        out = torch.empty_like(x)
+        t_plain, t_fused = bench_pair(lambda: moe.fused_moe(x, logits, w1, w2, K, ws=ws, out=out),
+                                      lambda: moe.fused_moe(x, logits, w1, w2, K, ws=ws, out=out, interleaved=True))
+        fl = 2.0 * T * K * 3 * I * H
+        results.append(dict(kernel="fused_moe", shape=f"{name} T={T} E={E} top{K} H={H} I={I}", ms=t_fused * 1e3,
+                            tflops=fl / t_fused / 1e12, three_launch_ms=t_plain * 1e3, peaks=tag))
+        print(f"moe {name:<38} T={T:<5} {t_fused*1e3:7.3f} ms {fl/t_fused/1e12:7.1f} TF/s ({fl/t_fused/1e12/tf*100:5.1f}% of {tag} cuBLAS bf16)"
+              f" | GEMM, activation kernel, GEMM: {t_plain*1e3:7.3f} ms")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--what", default="gemm,decode,prefill,small")
@@ -243,7 +286,7 @@ def main():
     results = []
     for w in a.what.split(","):
         {"gemm": gemm_rows, "decode": decode_rows, "prefill": prefill_rows, "small": small_rows, "gdn": gdn_rows, "mla": mla_rows,
-         "fp8": fp8_rows}[w](results, hbm, tf, tag)
+         "fp8": fp8_rows, "moe": moe_rows}[w](results, hbm, tf, tag)
     if a.json:
         with open(a.json, "w") as f:
             json.dump(results, f, indent=1)

@@ -30,7 +30,11 @@ def hf_names(model):
         elif n.endswith("experts.gate_up"):
             base = n[: -len("gate_up")]
             for e in range(t.shape[0]):
-                g, u = t[e].chunk(2)
+                if getattr(t, "_xllm_interleaved", False):
+                    from xllm_b200.ops.gemm_tcgen05 import deinterleave_gate_up
+                    g, u = deinterleave_gate_up(t[e])
+                else:
+                    g, u = t[e].chunk(2)
                 yield f"{base}{e}.gate_proj.weight", g
                 yield f"{base}{e}.up_proj.weight", u
         elif n.endswith("experts.down"):

@@ -122,7 +122,11 @@ def test_fp8_execution_engine_tracks_dequantised_engine():
             sn = n + "_scale" if "experts." in n and not n.endswith("weight") else n + "_scale_inv"
             sc = p8[sn]
             if src.dim() == 3:
-                t.copy_(torch.stack([f8.dequant_block128_ref(src[e], sc[e]) for e in range(src.shape[0])]))
+                d = torch.stack([f8.dequant_block128_ref(src[e], sc[e]) for e in range(src.shape[0])])
+                if getattr(t, "_xllm_interleaved", False):       # ... and the experts' gate|up rows too
+                    from xllm_b200.ops.gemm_tcgen05 import interleave_gate_up
+                    d = interleave_gate_up(*d.chunk(2, dim=1))
+                t.copy_(d)
             else:
                 d = f8.dequant_block128_ref(src, sc)
                 if getattr(t, "_xllm_interleaved", False):       # the bf16 model keeps dense gate|up rows interleaved

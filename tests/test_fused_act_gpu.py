@@ -55,3 +55,49 @@ def test_dense_mlp_interleaved_equals_plain_layout(monkeypatch):
     for T in (16, 600, 2500):
         a, b = outs[("1", T)], outs[("0", T)]
         assert (a - b).abs().max() < 0.02 * max(1.0, b.abs().max().item()), T
+
+
+@pytest.mark.parametrize("T,E,top_k,H,I", [(300, 8, 2, 512, 256), (1500, 16, 4, 1024, 192), (64, 4, 2, 256, 64)])
+def test_fused_moe_interleaved_experts_equal_plain_layout(T, E, top_k, H, I):
+    """The grouped GEMM with the gated activation in its epilogue (interleaved expert weights, 256- and
+    128-wide tiles) against the three-launch form on the same numbers, and both against the fp32 reference."""
+    from xllm_b200.ops import gemm_tcgen05 as g
+    from xllm_b200.ops import moe as M
+    gen = torch.Generator(device="cuda").manual_seed(T + E)
+    x = (torch.randn(T, H, device="cuda", generator=gen) * 0.5).to(torch.bfloat16)
+    logits = torch.randn(T, E, device="cuda", generator=gen)
+    wgu = (torch.randn(E, 2 * I, H, device="cuda", generator=gen) * 0.05).to(torch.bfloat16)
+    wd = (torch.randn(E, I, H, device="cuda", generator=gen) * 0.05).to(torch.bfloat16).transpose(1, 2).contiguous()
+    wil = g.interleave_gate_up(*wgu.chunk(2, dim=1)).contiguous()
+    back = torch.cat(g.deinterleave_gate_up(wil), dim=1)
+    assert torch.equal(back, wgu)
+    plain = M.fused_moe(x, logits, wgu, wd, top_k)
+    fused = M.fused_moe(x, logits, wil, wd, top_k, interleaved=True)
+    assert g.error_status() == 0
+    assert torch.equal(plain, fused), (plain.float() - fused.float()).abs().max()
+    want = M.fused_moe_reference(x.float().cpu(), logits.float().cpu(), wgu.float().cpu(), wd.float().cpu(), top_k)
+    assert (fused.float().cpu() - want).abs().max() < 0.05 + 0.02 * want.abs().max()
+
+
+def test_moe_block_interleaves_on_the_device_and_loads_checkpoint_names(monkeypatch):
+    from xllm_b200.models import ModelArgs
+    from xllm_b200.models.qwen_moe import SparseMoeBlock as MoEBlock
+    args = ModelArgs(model_type="qwen3_moe", vocab_size=1000, hidden_size=256, num_hidden_layers=1, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=64, intermediate_size=512, moe_intermediate_size=128, num_experts=8,
+                     num_experts_per_tok=2)
+    gen = torch.Generator().manual_seed(0)
+    ckpt = {}
+    for e in range(8):
+        ckpt[f"experts.{e}.gate_proj.weight"] = torch.randn(128, 256, generator=gen) * 0.05
+        ckpt[f"experts.{e}.up_proj.weight"] = torch.randn(128, 256, generator=gen) * 0.05
+        ckpt[f"experts.{e}.down_proj.weight"] = torch.randn(256, 128, generator=gen) * 0.05
+    ckpt["gate.weight"] = torch.randn(8, 256, generator=gen)
+    x = (torch.randn(200, 256, generator=gen) * 0.5).to(torch.bfloat16).cuda()
+    outs = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("XLLM_FUSED_ACT", flag)
+        blk = MoEBlock(args, torch.bfloat16, "cuda:0")
+        assert blk.interleaved == (flag == "1")
+        blk.load_weights(list(ckpt.items()), strict=True)
+        outs.append(blk(x))
+    assert torch.equal(outs[0], outs[1])

@@ -1128,7 +1128,8 @@ static int launch_gemm(const void* a, const void* w, void* c, const void* bias, 
                             : make_tmap(&tb, w, (int64_t)N * n_experts, K, ldw, BN, true, mode.fp8 != 0);
   if (!make_tmap(&ta, a, M, K, lda, a_box, true, mode.fp8 != 0) || !okb) return (int)cudaErrorInvalidValue;
   if (mode.push_bufs != nullptr) tc = ta;  // push mode stores through peer pointers, the map is unused
-  else if (!make_tmap(&tc, c, M, N, ldc, 32, false)) return (int)cudaErrorInvalidValue;
+  // gated-activation epilogue: the output has one column per (gate, up) pair, half of the GEMM's N
+  else if (!make_tmap(&tc, c, M, mode.act_mul ? N / 2 : N, ldc, 32, false)) return (int)cudaErrorInvalidValue;
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
   if (split_k > 1 && tile_expert == nullptr && !mode.fp8) {
     mode.ks = usable_split(split_k, M, N, K, KS, tiles, dev, s);
@@ -1643,6 +1644,24 @@ XLLM_API int xllm_gemm_bf16_grouped(const void* a, const void* w, void* c, const
   if (N % 256 == 0) return launch_gemm<256, 4>(a, w, c, nullptr, M, N, K, lda, K, ldc, 148, 0, s, te, n_experts);
   if (N % 128 == 0) return launch_gemm<128, 6>(a, w, c, nullptr, M, N, K, lda, K, ldc, 148, 0, s, te, n_experts);
   return launch_gemm<64, 8>(a, w, c, nullptr, M, N, K, lda, K, ldc, 148, 0, s, te, n_experts);
+}
+
+// Grouped GEMM with the gated activation in the epilogue: every expert's N rows (gate | up) are stored
+// interleaved in groups of 128 = [64 gate rows | the 64 up rows of the same features], as for
+// xllm_gemm_bf16_act_mul; C is [M, N / 2] = act(gate) * up, and the [M, N] intermediate is never written.
+XLLM_API int xllm_gemm_bf16_grouped_act_mul(const void* a, const void* w, void* c, const void* tile_expert, int M,
+                                            int N, int K, int n_experts, int64_t lda, int64_t ldc, int act,
+                                            void* stream) {
+  using namespace xllm;
+  if (M == 0 || N == 0) return 0;
+  if (K % 8 || N % 128 || lda % 8 || ldc % 8 || M % kBM || act < 1 || act > 3) return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int32_t* te = (const int32_t*)tile_expert;
+  GemmMode mode{};
+  mode.ks = 1;
+  mode.act_mul = act;
+  if (N % 256 == 0) return launch_gemm<256, 4>(a, w, c, nullptr, M, N, K, lda, K, ldc, 148, 0, s, te, n_experts, mode);
+  return launch_gemm<128, 6>(a, w, c, nullptr, M, N, K, lda, K, ldc, 148, 0, s, te, n_experts, mode);
 }
 
 // fp8 (e4m3) scaled GEMM: C[M,N] (bf16) = (A_fp8[M,K] · W_fp8[N,K]^T) * a_scale * b_scale (+ bias).

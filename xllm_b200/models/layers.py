@@ -77,9 +77,9 @@ class Module:
             s = src[n]
             di, si = bool(getattr(t, "_xllm_interleaved", False)), bool(getattr(s, "_xllm_interleaved", False))
             if di and not si:
-                s = interleave_gate_up(*s.chunk(2))
+                s = interleave_gate_up(*s.chunk(2, dim=-2))
             elif si and not di:
-                s = torch.cat(deinterleave_gate_up(s))
+                s = torch.cat(deinterleave_gate_up(s), dim=-2)
             t.copy_(s.to(t.dtype))
 
     def add_param(self, name, tensor, loaders: Optional[Dict[str, Callable]] = None):

@@ -10,6 +10,8 @@ dense layers use — the reference reduces with two NCCL all-reduces (moe_tp the
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import ops
@@ -80,14 +82,27 @@ class SparseMoeBlock(Module):
             self.w_down = torch.empty(self.e_local, H, self.i_local, dtype=dtype, device=device)
             self._params["experts.gate_up"] = self.w_gate_up
             self._params["experts.down"] = self.w_down
+        # On the device, without expert parallelism, every expert's gate|up rows are stored in groups of
+        # 128 = [64 gate | 64 up of the same features]: the grouped GEMM's epilogue then applies SiLU(gate) * up
+        # itself (ops/moe.py).  Expert-parallel layers keep the plain layout (their weights move between ranks).
+        self.interleaved = (not self.fp8 and ep == 1 and il % 64 == 0 and dtype == torch.bfloat16
+                            and torch.device(device).type == "cuda" and os.environ.get("XLLM_FUSED_ACT", "1") != "0")
+        if self.interleaved:
+            self.w_gate_up._xllm_interleaved = True
         for e in range(self.e_local if not self.fp8 else 0):
             ge = e + self.e_begin
 
+            def half(e, p):
+                """Rows of expert e that hold gate (p = 0) or up (p = 1), as a [il // 64, 64, H] or [il, H] view."""
+                if self.interleaved:
+                    return self.w_gate_up[e].view(2 * il // 128, 2, 64, H)[:, p]
+                return self.w_gate_up[e, p * il:(p + 1) * il]
+
             def lg(w, e=e):
-                self.w_gate_up[e, :il].copy_(w.narrow(0, i_rank * il, il).to(dtype))
+                half(e, 0).copy_(w.narrow(0, i_rank * il, il).to(dtype).view(half(e, 0).shape))
 
             def lu(w, e=e):
-                self.w_gate_up[e, il:].copy_(w.narrow(0, i_rank * il, il).to(dtype))
+                half(e, 1).copy_(w.narrow(0, i_rank * il, il).to(dtype).view(half(e, 1).shape))
 
             def ld(w, e=e):
                 self.w_down[e].copy_(w.narrow(1, i_rank * il, il).to(dtype))
@@ -141,7 +156,8 @@ class SparseMoeBlock(Module):
         y = moe_ops.fused_moe(x, logits, self.w_gate_up, self.w_down, self.top_k, a.scoring_func, self.bias,
                               a.n_group, a.topk_group, a.norm_topk_prob, a.routed_scaling_factor, self.e_begin,
                               a.num_experts, shared_out, self._ws, out,
-                              w_scales=(self.s_gate_up, self.s_down) if self.fp8 else None)
+                              w_scales=(self.s_gate_up, self.s_down) if self.fp8 else None,
+                              interleaved=self.interleaved)
         if out is None and self.ps.tp_size > 1:
             y = self.ps.all_reduce(y)
         return y

@@ -123,16 +123,18 @@ def act_and_mul_interleaved(y, act: str = "silu", out=None):
 
 
 def interleave_gate_up(gate, up):
-    """[I, K] + [I, K] -> [2I, K] with groups of 128 rows = 64 of gate, then the same 64 of up."""
-    I, K = gate.shape
-    return torch.stack([gate.view(I // 64, 64, K), up.view(I // 64, 64, K)], dim=1).reshape(2 * I, K)
+    """[..., I, K] + [..., I, K] -> [..., 2I, K] with groups of 128 rows = 64 of gate, then the same 64 of up
+    (leading dimensions, e.g. experts, are kept)."""
+    *lead, I, K = gate.shape
+    return torch.stack([gate.reshape(*lead, I // 64, 64, K), up.reshape(*lead, I // 64, 64, K)],
+                       dim=-3).reshape(*lead, 2 * I, K)
 
 
 def deinterleave_gate_up(w):
-    """Inverse of `interleave_gate_up`: (gate [I, K], up [I, K])."""
-    N, K = w.shape
-    v = w.view(N // 128, 2, 64, K)
-    return v[:, 0].reshape(N // 2, K), v[:, 1].reshape(N // 2, K)
+    """Inverse of `interleave_gate_up`: (gate [..., I, K], up [..., I, K])."""
+    *lead, N, K = w.shape
+    v = w.reshape(*lead, N // 128, 2, 64, K)
+    return v[..., 0, :, :].reshape(*lead, N // 2, K), v[..., 1, :, :].reshape(*lead, N // 2, K)
 
 
 def set_k_per_stage(n: int):

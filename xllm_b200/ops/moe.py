@@ -17,6 +17,7 @@ _lib.register_signature("xllm_moe_offsets", [P, P, P, P, I, I, I, P])
 _lib.register_signature("xllm_moe_permute", [P, P, P, P, P, P, I, I, I, P])
 _lib.register_signature("xllm_moe_finalize", [P, P, P, P, P, I, I, I, P])
 _lib.register_signature("xllm_gemm_bf16_grouped", [P, P, P, P, I, I, I, I, L, L, P])
+_lib.register_signature("xllm_gemm_bf16_grouped_act_mul", [P, P, P, P, I, I, I, I, L, L, I, P])
 
 
 def route_reference(logits, top_k, scoring="softmax", bias=None, n_group=1, topk_group=1, renorm=True, scale=1.0):
@@ -81,12 +82,18 @@ class MoeWorkspace:
 
 def fused_moe(x, logits, w_gate_up, w_down, top_k, scoring="softmax", bias=None, n_group=1, topk_group=1,
               renorm=True, scale=1.0, expert_begin=0, n_experts=None, shared_out=None, ws: MoeWorkspace = None,
-              out=None, w_scales=None):
+              out=None, w_scales=None, interleaved=False):
     """x [T,H], logits [T,E]; w_gate_up [E_local, 2I, H], w_down [E_local, H, I] -> [T,H].
+    `interleaved`: every expert's gate|up rows are stored in groups of 128 = [64 gate | the 64 up rows of the
+    same features] (`ops.gemm_tcgen05.interleave_gate_up`); the first grouped GEMM then applies SiLU(gate) * up
+    in its epilogue and the [rows, 2I] intermediate is never written.
     `w_scales` = (s_gate_up [E_local, 2I/128, H/128], s_down [E_local, H/128, I/128]): the weights are e4m3
     with 128 x 128 block scales and both grouped GEMMs run block-scaled in fp8 (the rows are quantised
     per token in groups of 128 before each of them)."""
     if not x.is_cuda:
+        if interleaved:
+            from .gemm_tcgen05 import deinterleave_gate_up
+            w_gate_up = torch.cat(deinterleave_gate_up(w_gate_up), dim=-2)
         if w_scales is not None:
             from . import fp8
             w_gate_up = torch.stack([fp8.dequant_block128_ref(w_gate_up[e], w_scales[0][e], x.dtype) for e in range(w_gate_up.shape[0])])
@@ -120,9 +127,13 @@ def fused_moe(x, logits, w_gate_up, w_down, top_k, scoring="softmax", bias=None,
         aq, as_ = fp8.quant_group128(ws.a)
         fp8.block_scaled_mm_grouped(aq, as_, w_down, w_scales[1], ws.tile_expert, ws.y)
     else:
-        check(lib.xllm_gemm_bf16_grouped(ptr(ws.xp), ptr(w_gate_up), ptr(ws.h), ptr(ws.tile_expert), ws.rows, I2, H,
-                                         E_local, H, I2, s), "moe_gemm1")
-        act_and_mul(ws.h, "silu", out=ws.a)
+        if interleaved:
+            check(lib.xllm_gemm_bf16_grouped_act_mul(ptr(ws.xp), ptr(w_gate_up), ptr(ws.a), ptr(ws.tile_expert), ws.rows,
+                                                     I2, H, E_local, H, inter, 1, s), "moe_gemm1_act")
+        else:
+            check(lib.xllm_gemm_bf16_grouped(ptr(ws.xp), ptr(w_gate_up), ptr(ws.h), ptr(ws.tile_expert), ws.rows, I2, H,
+                                             E_local, H, I2, s), "moe_gemm1")
+            act_and_mul(ws.h, "silu", out=ws.a)
         check(lib.xllm_gemm_bf16_grouped(ptr(ws.a), ptr(w_down), ptr(ws.y), ptr(ws.tile_expert), ws.rows, H, inter,
                                          E_local, inter, H, s), "moe_gemm2")
     if out is None:
