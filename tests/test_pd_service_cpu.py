@@ -192,3 +192,47 @@ def test_offline_requests_decode_on_the_prefill_instance():
     finally:
         if child.poll() is None:
             child.kill()
+
+
+def test_idle_decode_instance_pulls_offline_requests_over():
+    """The decode instance signals spare capacity; the prefill instance moves offline requests that are
+    decoding locally over to it (prompt + tokens so far go through the ordinary handover).  The client sees one
+    uninterrupted stream per request, equal to a single engine's, and every block comes back on both sides."""
+    g = torch.Generator().manual_seed(21)
+    offline = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (30, 12, 44)]
+    llm = LLM("tiny", devices="cpu", dtype="float32", block_size=16, num_blocks=64, max_seqs_per_batch=8,
+              max_tokens_per_batch=128, enable_graph=False)
+    sp = SamplingParams(max_tokens=24, temperature=0.0, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in llm.generate(offline, sp)]
+    srv = Channel.listen()
+    child = _spawn_decode(srv.getsockname()[1], mode="pull")
+    try:
+        p, svc = _prefill_side(srv)
+        for i, pr in enumerate(offline):
+            assert svc.add_request(f"off{i}", pr, max_tokens=24, temperature=0.0, ignore_eos=True, offline=True)
+        got, fin = {}, []
+
+        def on(ev):
+            if ev.token >= 0:
+                got.setdefault(ev.request_id, []).append(ev.token)
+            if ev.request_finished:
+                fin.append(ev.request_id)
+
+        assert svc.run_until_done(on, max_seconds=120.0)
+        assert [got[f"off{i}"] for i in range(3)] == want
+        assert sorted(fin) == ["off0", "off1", "off2"]                  # one finish each: the local abort is not shown
+        assert svc.migrated >= 1 and svc.handed_over == svc.migrated and not svc.failed and not svc.migrating
+        assert not svc.local and not svc.local_state and not svc.remote
+        assert p.scheduler.block_stats(0).num_used == 0
+        svc.close()
+        out, _ = child.communicate(timeout=60)
+        assert f"adopted={svc.migrated}" in out and "used=0 reserved=0" in out, out
+    finally:
+        if child.poll() is None:
+            child.kill()
+
+
+def test_pull_frame_round_trips_in_both_codecs():
+    from xllm_b200 import proto
+    m = {"op": "pull", "free_blocks": 37, "max_requests": 1}
+    assert proto.decode(proto.encode(m)) == m

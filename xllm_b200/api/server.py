@@ -412,7 +412,10 @@ class ApiServer:
             return
         self._pd_listen.close()
         self._pd_listen = None
-        self.pd_decode = DecodeService(self.engine, Channel(conn), SocketCopy(self.engine.runner))
+        # XLLM_PD_PULL_OFFLINE=1: while idle, this decode instance asks the prefill instance for the offline
+        # requests it is decoding itself
+        self.pd_decode = DecodeService(self.engine, Channel(conn), SocketCopy(self.engine.runner),
+                                       pull_offline=os.environ.get("XLLM_PD_PULL_OFFLINE", "0") == "1")
 
     def _unlink_p2p(self, req, body):
         if self.pd_prefill is not None:

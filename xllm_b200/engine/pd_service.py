@@ -322,11 +322,17 @@ class RemoteEvent:
 class DecodeService:
     """Serves one prefill peer: reserves blocks, receives KV, adopts sequences, streams tokens back."""
 
-    def __init__(self, engine, channel: Channel, transport):
+    def __init__(self, engine, channel: Channel, transport, pull_offline: bool = False, pull_below: int = 1,
+                 pull_interval: float = 0.02):
+        """`pull_offline`: while fewer than `pull_below` requests run or are reserved here, ask the prefill
+        instance (at most every `pull_interval` seconds) to move one of its local offline requests over."""
         self.e, self.ch, self.t = engine, channel, transport
         self.peer_requests: set = set()
         self.stopped = False
         self.adopted = 0
+        self.pull_offline, self.pull_below, self.pull_interval = bool(pull_offline), int(pull_below), float(pull_interval)
+        self._last_pull = 0.0
+        self.pulls_sent = 0
         self.failed_waits = 0
         self.reclaimed_blocks = 0
 
@@ -381,11 +387,25 @@ class DecodeService:
         self.reclaimed_blocks += int(sch.block_stats().num_free) - before
         self.stopped = True
 
+    def _maybe_pull(self):
+        """Spare capacity here: ask the prefill instance for one of the offline requests it is decoding
+        itself (the pull signal of the reference's PD-OOC scheduler, xllm/core/scheduler/pd_ooc_scheduler.cpp)."""
+        if not self.pull_offline or self.stopped or self.ch.closed:
+            return
+        sch = self.e.scheduler
+        now = time.time()
+        if len(self.peer_requests) + int(sch.num_reserved()) >= self.pull_below or now - self._last_pull < self.pull_interval:
+            return
+        self._last_pull = now
+        self.pulls_sent += 1
+        self.ch.send({"op": "pull", "free_blocks": int(sch.block_stats().num_free), "max_requests": 1})
+
     def step(self, idle_wait: float = 0.0):
         for m in self.ch.poll(idle_wait):
             self._on_message(m)
         if self.ch.closed and not self.stopped:
             self._peer_gone()
+        self._maybe_pull()
         if self.e.has_unfinished():
             events = self.e.step()
         else:
@@ -429,6 +449,10 @@ class PrefillService:
         self.pushed_upto: Dict[str, int] = {}        # first block index not yet pushed completely
         self.local: set = set()                       # offline requests that decode on this instance
         self.kept_local = 0
+        self.local_state: Dict[str, dict] = {}        # their prompt, parameters and the tokens produced so far
+        self.migrating: set = set()                   # offline requests on their way to the decode instance
+        self.migrated = 0
+        self._deferred: List[dict] = []
         self.retry_at: Dict[str, float] = {}
         self.awaiting_adopt: set = set()
         self.remote: set = set()                     # decoding on the peer
@@ -498,6 +522,8 @@ class PrefillService:
                 return False
             self.local.add(request_id)
             self.kept_local += 1
+            self.local_state[request_id] = dict(prompt=toks, max_tokens=int(max_tokens), gen=[],
+                                                params={k: v for k, v in kw.items() if k != "offline"})
             return True
         self.params[request_id] = dict(kw, max_tokens=int(max_tokens))
         self.prompts[request_id] = toks
@@ -510,6 +536,7 @@ class PrefillService:
     def abort(self, request_id: str):
         if request_id in self.local:
             self.local.discard(request_id)
+            self.local_state.pop(request_id, None)
             self.e.abort(request_id)
             self.e.scheduler.release_held(request_id)
             return
@@ -522,6 +549,33 @@ class PrefillService:
             d.pop(rid, None)
         self.awaiting_adopt.discard(rid)
         self.remote.discard(rid)
+        self.migrating.discard(rid)
+
+    def _migrate_one(self, free_blocks: int) -> Optional[str]:
+        """The decode instance has spare capacity: hand it the local offline request with the most tokens
+        still to produce that fits into `free_blocks`.  The request is taken out of this engine and goes
+        through the ordinary handover with (prompt + tokens so far) as its prompt: with the prefix cache on,
+        its blocks are found again and only the push remains; without, the KV is recomputed once."""
+        best, best_left = None, 1
+        for rid in self.local:
+            st = self.local_state.get(rid)
+            if st is None or not st["gen"]:
+                continue                                   # still in its prompt: nothing to gain
+            left = st["max_tokens"] - len(st["gen"])
+            n_tok = len(st["prompt"]) + len(st["gen"]) + 1
+            if left > best_left and (n_tok + self.bs - 1) // self.bs <= free_blocks and n_tok + left < self.e.max_model_len:
+                best, best_left = rid, left
+        if best is None:
+            return None
+        st = self.local_state.pop(best)
+        self.local.discard(best)
+        self.e.abort(best)
+        self.e.scheduler.release_held(best)
+        self.params[best] = dict(st["params"], max_tokens=best_left)
+        self.prompts[best] = st["prompt"] + st["gen"]
+        self.migrating.add(best)
+        self.ch.send({"op": "reserve", "rid": best, "n_tokens": len(self.prompts[best]) + 1})
+        return best
 
     def has_unfinished(self) -> bool:
         return bool(self.params) or bool(self.remote) or self.e.has_unfinished()
@@ -534,10 +588,13 @@ class PrefillService:
             if now >= t:
                 del self.retry_at[rid]
                 self.ch.send({"op": "reserve", "rid": rid, "n_tokens": len(self.prompts[rid]) + 1})
-        for m in self.ch.poll(idle_wait if not self.e.has_unfinished() else 0.0):
+        msgs, self._deferred = self._deferred + self.ch.poll(idle_wait if not self.e.has_unfinished() else 0.0), []
+        for m in msgs:
             op = m.get("op")
             rid = m.get("rid")
-            if op == "reserved":
+            if op == "pull":
+                self._migrate_one(int(m.get("free_blocks", 0)))
+            elif op == "reserved":
                 if rid not in self.params:
                     if m["blocks"]:
                         self.ch.send({"op": "cancel", "rid": rid})
@@ -546,6 +603,10 @@ class PrefillService:
                     par = self.params[rid]
                     pkw = {k: v for k, v in par.items() if k not in ("stop_sequences", "max_tokens")}
                     if not self.e.add_request(rid, self.prompts[rid], max_tokens=1, **pkw):
+                        if rid in self.migrating and m.get("_tries", 0) < 100:
+                            # its aborted incarnation is still part of a step in flight: try again next step
+                            self._deferred.append(dict(m, _tries=m.get("_tries", 0) + 1))
+                            continue
                         self.ch.send({"op": "cancel", "rid": rid})
                         self.failed[rid] = "rejected by the prefill engine"
                         out.append(_failure(rid, self.failed[rid]))
@@ -557,6 +618,9 @@ class PrefillService:
                 self.e.scheduler.release_held(rid)
                 if m.get("ok"):
                     self.handed_over += 1
+                    if rid in self.migrating:
+                        self.migrating.discard(rid)
+                        self.migrated += 1
                     self.remote.add(rid)
                     for d in (self.params, self.prompts, self.dst_blocks, self.pushed_upto):
                         d.pop(rid, None)
@@ -589,8 +653,12 @@ class PrefillService:
             for ev in events:
                 if ev.request_id in self.local:          # an offline request: its whole stream is produced here
                     out.append(ev)
+                    st = self.local_state.get(ev.request_id)
+                    if st is not None and ev.token >= 0:
+                        st["gen"].append(int(ev.token))
                     if ev.request_finished:
                         self.local.discard(ev.request_id)
+                        self.local_state.pop(ev.request_id, None)
                         self.e.scheduler.release_held(ev.request_id)
                     continue
                 if ev.token < 0:

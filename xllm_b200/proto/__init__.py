@@ -79,6 +79,7 @@ SCHEMA: Dict[str, List[Tuple]] = {
                    ("finish_reason", "string", 5)],
     "Cancel": [("req_id", "string", 1)],
     "Bye": [],
+    "Pull": [("free_blocks", "int32", 1), ("max_requests", "int32", 2)],
     # ---- control events rank 0 sends to the other ranks of an instance, once per step
     "ControlEvent": [("kind", "string", 1), ("request_id", "string", 2), ("prompt_tokens", "int32", 3, "repeated"),
                      ("sampling", "SamplingFields", 4), ("mode", "string", 5)],
@@ -154,6 +155,7 @@ _OPS = {
     "gen": (8, "Generation", {"rid": "req_id", "reason": "finish_reason"}),
     "cancel": (9, "Cancel", {"rid": "req_id"}),
     "bye": (10, "Bye", {}),
+    "pull": (11, "Pull", {}),
 }
 _BY_ID = {v[0]: (k, v[1], {b: a for a, b in v[2].items()}) for k, v in _OPS.items()}
 
